@@ -1,0 +1,105 @@
+"""Builds the native libraries of this package in-tree with nvcc for sm_100a.
+
+    python -m cellerator_b200.build            # build what is out of date
+    python -m cellerator_b200.build --force    # rebuild everything
+
+Outputs (git-ignored, kept beside the sources so they travel with the tree):
+    cellerator_b200/lib/libcellerator_b200.so       kernels + C ABI (include/cellerator_b200.h)
+    cellerator_b200/lib/libcb200_synth.so           seeded workload generator used by bench/tests
+    cellerator_b200/lib/libcb200_cpmath.so          C++ operation-core backend over the C ABI
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+HOST = os.path.join(HERE, "host")
+LIB = os.path.join(HERE, "lib")
+OBJ = os.path.join(HERE, "build")
+
+NVCC = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+              "-I", os.path.join(ROOT, "include")]
+
+KERNEL_SOURCES = ["capi.cu", "qcsr_forward.cu", "qcsr_transpose.cu", "qbell_forward.cu", "qbell_tcgen05.cu",
+                  "codec.cu"]
+SYNTH_SOURCES = ["synth.cu"]
+
+TARGETS = {
+    "libcellerator_b200.so": [os.path.join(CSRC, s) for s in KERNEL_SOURCES],
+    "libcb200_synth.so": [os.path.join(CSRC, s) for s in SYNTH_SOURCES],
+}
+
+
+def _newer(target: str, deps: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+
+
+def _headers() -> list[str]:
+    out = [os.path.join(ROOT, "include", "cellerator_b200.h")]
+    for d in (CSRC, HOST):
+        if os.path.isdir(d):
+            out += [os.path.join(d, f) for f in os.listdir(d) if f.endswith((".cuh", ".hh", ".h"))]
+    return out
+
+
+def _run(cmd: list[str]) -> None:
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: " + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+
+
+def _compile(src: str, force: bool, extra: list[str]) -> str:
+    obj = os.path.join(OBJ, os.path.basename(src) + ".o")
+    if force or _newer(obj, [src] + _headers()):
+        _run([NVCC, *ARCH, *NVCC_FLAGS, *extra, "-c", src, "-o", obj])
+    return obj
+
+
+def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
+    os.makedirs(LIB, exist_ok=True)
+    os.makedirs(OBJ, exist_ok=True)
+    targets = {k: [s for s in v if os.path.exists(s)] for k, v in TARGETS.items()}
+    cpmath = os.path.join(HOST, "cpmath_backend.cc")
+    jobs = {}
+    with cf.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        for lib, srcs in targets.items():
+            for s in srcs:
+                jobs[s] = pool.submit(_compile, s, force, [])
+        objs = {s: f.result() for s, f in jobs.items()}
+    out = {}
+    for lib, srcs in targets.items():
+        if not srcs:
+            continue
+        path = os.path.join(LIB, lib)
+        deps = [objs[s] for s in srcs]
+        if force or _newer(path, deps):
+            _run([NVCC, *ARCH, "-shared", "-o", path, *deps])
+        out[lib] = path
+        if verbose:
+            print("built", path)
+    if os.path.exists(cpmath):
+        path = os.path.join(LIB, "libcb200_cpmath.so")
+        deps = [cpmath] + _headers()
+        if force or _newer(path, deps + [out["libcellerator_b200.so"]]):
+            cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+            _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(ROOT, "include"), "-I", HOST,
+                  "-o", path, cpmath, "-L", LIB, "-lcellerator_b200", "-Wl,-rpath,$ORIGIN"])
+        out["libcb200_cpmath.so"] = path
+        if verbose:
+            print("built", path)
+    return out
+
+
+if __name__ == "__main__":
+    build(force="--force" in sys.argv, verbose=True)

@@ -1,0 +1,167 @@
+"""ctypes binding of libcellerator_b200.so (the C ABI of include/cellerator_b200.h).
+
+This is a thin driver for tests and the benchmark: it passes raw device pointers (taken from
+torch tensors, which only provide memory and streams) to the library.  There is no fallback:
+if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libcellerator_b200.so")
+SYNTH_PATH = os.path.join(HERE, "lib", "libcb200_synth.so")
+
+ABI_VERSION = 1
+
+SUCCESS, INVALID_ARGUMENT, INVALID_SHAPE, UNSUPPORTED, CUDA_ERROR, INTERNAL_ERROR, STALE_STRUCTURE, \
+    INSUFFICIENT_WORKSPACE, INVALID_STREAM, SEALED = range(10)
+
+DTYPE_U8, DTYPE_U4, DTYPE_F16, DTYPE_BF16, DTYPE_F32, DTYPE_F64 = 2, 32, 6, 7, 8, 9
+DECODE_PER_GENE_AFFINE, DECODE_COLUMN_SCALE_ROW_OFFSET = 1, 2
+PROJECTION_CSR, PROJECTION_BLOCKED_ELL, PROJECTION_TRANSPOSE = 5, 8, 10
+CAP_DETERMINISTIC, CAP_GRAPH_CAPTURE, CAP_PERSISTENT_PREPROCESSING, CAP_COMPOSED_EPILOGUE = 1, 2, 4, 8
+
+
+class Cb200Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"cb200 status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class QCsr(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("rows", C.c_int64), ("cols", C.c_int64),
+                ("nnz", C.c_int64), ("bits", C.c_int32), ("policy", C.c_int32), ("row_ptr", C.c_void_p),
+                ("packed_row_ptr", C.c_void_p), ("col_idx", C.c_void_p), ("packed_values", C.c_void_p),
+                ("scales", C.c_void_p), ("offsets", C.c_void_p)]
+
+
+class CsrBlock(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in ("block_index", "row_begin", "row_end", "nnz_begin", "nnz_end",
+                                         "packed_begin", "packed_end")]
+
+
+class QBell(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("rows", C.c_int64), ("cols", C.c_int64),
+                ("block_size", C.c_int32), ("ell_cols", C.c_int32), ("row_stride_bytes", C.c_int64),
+                ("bits", C.c_int32), ("policy", C.c_int32), ("block_col_idx", C.c_void_p),
+                ("packed_values", C.c_void_p), ("scales", C.c_void_p), ("offsets", C.c_void_p)]
+
+
+class NumericPolicy(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("sparse_storage", C.c_int32),
+                ("dense_storage", C.c_int32), ("output_storage", C.c_int32), ("multiply", C.c_int32),
+                ("accumulation", C.c_int32), ("quantized", C.c_int32)]
+
+
+class Capability(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("supported", C.c_int32), ("flags", C.c_uint32),
+                ("persistent_bytes", C.c_uint64), ("transient_bytes", C.c_uint64), ("name", C.c_char_p)]
+
+
+class SpmmProblem(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("projection", C.c_int32), ("m", C.c_int64),
+                ("k", C.c_int64), ("n", C.c_int64), ("nnz", C.c_int64), ("bits", C.c_int32), ("policy", C.c_int32),
+                ("dense_dtype", C.c_int32), ("device", C.c_int32), ("structure_epoch", C.c_uint64),
+                ("host_row_ptr", C.c_void_p), ("deterministic", C.c_int32), ("reserved", C.c_int32)]
+
+
+class Launch(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("csr", C.POINTER(QCsr)), ("bell", C.POINTER(QBell)),
+                ("dense", C.c_void_p), ("dense_ld", C.c_int64), ("out", C.c_void_p), ("out_ld", C.c_int64),
+                ("alpha", C.c_float), ("beta", C.c_float), ("structure_epoch", C.c_uint64), ("row_begin", C.c_int64),
+                ("row_end", C.c_int64), ("stream", C.c_void_p), ("device", C.c_int32), ("workspace_device", C.c_int32),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64)]
+
+
+class SessionOptions(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32),
+                ("owned_stream_count", C.c_uint32), ("external_stream_count", C.c_uint32),
+                ("external_streams", C.POINTER(C.c_void_p))]
+
+
+class LaunchBinding(C.Structure):
+    _fields_ = [("status", C.c_int32), ("device", C.c_int32), ("stream", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_uint64)]
+
+
+# every symbol that include/cellerator_b200.h declares
+EXPORTED_SYMBOLS = [
+    "cb200_status_string", "cb200_last_error", "cb200_abi_version", "cb200_build_packed_row_ptr",
+    "cb200_block_count_for_rows", "cb200_build_uniform_block_row_ptr", "cb200_get_block", "cb200_quantize_rows",
+    "cb200_dequantize_rows", "cb200_qbell_quantize_rows", "cb200_qbell_dequantize_rows",
+    "cb200_backend_query", "cb200_spmm_prepare", "cb200_prepared_destroy",
+    "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_spmm_run", "cb200_kernel_launch_count",
+    "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
+    "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
+]
+
+_lib = None
+_synth = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(
+                f"{LIB_PATH} is missing: build it with `python -m cellerator_b200.build` (there is no CPU fallback)")
+        L = C.CDLL(LIB_PATH)
+        L.cb200_status_string.restype = C.c_char_p
+        L.cb200_last_error.restype = C.c_char_p
+        L.cb200_abi_version.restype = C.c_uint32
+        L.cb200_kernel_launch_count.restype = C.c_uint64
+        L.cb200_build_packed_row_ptr.restype = C.c_int64
+        L.cb200_build_packed_row_ptr.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_void_p]
+        L.cb200_block_count_for_rows.restype = C.c_int64
+        L.cb200_block_count_for_rows.argtypes = [C.c_int64, C.c_int64]
+        L.cb200_build_uniform_block_row_ptr.restype = C.c_int64
+        L.cb200_build_uniform_block_row_ptr.argtypes = [C.c_int64, C.c_int64, C.c_void_p]
+        L.cb200_get_block.argtypes = [C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                      C.POINTER(CsrBlock)]
+        L.cb200_quantize_rows.argtypes = [C.POINTER(QCsr), C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]
+        L.cb200_dequantize_rows.argtypes = [C.POINTER(QCsr), C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]
+        L.cb200_qbell_quantize_rows.argtypes = [C.POINTER(QBell), C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]
+        L.cb200_qbell_dequantize_rows.argtypes = [C.POINTER(QBell), C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]
+        L.cb200_backend_query.argtypes = [C.c_int32, C.POINTER(NumericPolicy), C.POINTER(Capability)]
+        L.cb200_spmm_prepare.argtypes = [C.POINTER(SpmmProblem), C.POINTER(C.c_void_p)]
+        L.cb200_prepared_destroy.argtypes = [C.c_void_p]
+        L.cb200_prepared_destroy.restype = None
+        L.cb200_prepared_workspace.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]
+        L.cb200_prepared_schedule.argtypes = [C.c_void_p]
+        L.cb200_prepared_schedule.restype = C.c_char_p
+        L.cb200_spmm_run.argtypes = [C.c_void_p, C.POINTER(Launch)]
+        L.cb200_session_create.argtypes = [C.POINTER(SessionOptions), C.POINTER(C.c_void_p)]
+        L.cb200_session_reserve_persistent.argtypes = [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]
+        L.cb200_session_reserve_transient.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]
+        L.cb200_session_seal.argtypes = [C.c_void_p]
+        L.cb200_session_bind.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]
+        L.cb200_session_bind.restype = LaunchBinding
+        L.cb200_session_synchronize.argtypes = [C.c_void_p]
+        L.cb200_session_destroy.argtypes = [C.c_void_p]
+        L.cb200_session_destroy.restype = None
+        _lib = L
+    return _lib
+
+
+def synth_lib() -> C.CDLL:
+    global _synth
+    if _synth is None:
+        if not os.path.exists(SYNTH_PATH):
+            raise FileNotFoundError(f"{SYNTH_PATH} is missing: build it with `python -m cellerator_b200.build`")
+        _synth = C.CDLL(SYNTH_PATH)
+    return _synth
+
+
+def check(status: int) -> None:
+    if status != SUCCESS:
+        raise Cb200Error(status, lib().cb200_last_error().decode() or lib().cb200_status_string(status).decode())
+
+
+def header(struct):
+    struct.version = ABI_VERSION
+    struct.size = C.sizeof(struct)
+    return struct

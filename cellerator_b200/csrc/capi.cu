@@ -1,0 +1,470 @@
+// extern "C" surface of libcellerator_b200.so (declared in include/cellerator_b200.h):
+// status/error plumbing, host layout helpers, capability query, the prepared-operation
+// lifecycle and the runtime session.  Kernels live in the other translation units.
+#include "kernels.cuh"
+
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+namespace cb200 {
+
+std::atomic<std::uint64_t> g_kernel_launches{0};
+
+char *last_error_buffer() {
+    thread_local char buffer[512] = "";
+    return buffer;
+}
+
+cb200_status fail(cb200_status status, const char *fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    std::vsnprintf(last_error_buffer(), 512, fmt, args);
+    va_end(args);
+    return status;
+}
+
+void clear_error() { last_error_buffer()[0] = '\0'; }
+
+namespace {
+
+template<typename T>
+bool valid_header(const T *desc) {
+    return desc != nullptr && desc->version == CB200_ABI_VERSION && desc->size >= sizeof(T);
+}
+
+bool supported_bits(int bits) { return bits == 4 || bits == 8; }
+bool supported_dense(int dtype) { return dtype == CB200_DTYPE_F32 || dtype == CB200_DTYPE_BF16; }
+
+qcsr_view view_of(const cb200_qcsr &m) {
+    return qcsr_view{m.rows, m.cols, m.nnz, m.bits, m.policy, m.row_ptr, m.packed_row_ptr,
+                     m.col_idx, m.packed_values, m.scales, m.offsets};
+}
+
+qbell_view view_of(const cb200_qbell &m) {
+    return qbell_view{m.rows, m.cols, m.block_size, m.ell_cols, m.row_stride_bytes, m.bits, m.policy,
+                      m.block_col_idx, m.packed_values, m.scales, m.offsets};
+}
+
+} // namespace
+} // namespace cb200
+
+using namespace cb200;
+
+// Prepared state: everything frozen at prepare time (operation_core.hh:167-181).  It owns no
+// launch pointer.
+struct cb200_prepared {
+    cb200_spmm_problem problem;
+    fwd_schedule schedule;
+    const char *schedule_name;
+    std::uint64_t workspace_bytes;
+    std::uint32_t workspace_alignment;
+    int sm_count;
+    double mean_row_nnz, max_row_nnz;
+};
+
+struct cb200_session {
+    int device;
+    bool sealed;
+    std::uint32_t stream_count;
+    cudaStream_t streams[8];
+    bool owned[8];
+    void *transient[8];
+    std::uint64_t transient_bytes[8];
+    void *persistent[64];
+    std::uint32_t persistent_count;
+};
+
+extern "C" {
+
+const char *cb200_status_string(cb200_status status) {
+    switch (status) {
+    case CB200_STATUS_SUCCESS: return "success";
+    case CB200_STATUS_INVALID_ARGUMENT: return "invalid argument";
+    case CB200_STATUS_INVALID_SHAPE: return "invalid shape";
+    case CB200_STATUS_UNSUPPORTED: return "unsupported";
+    case CB200_STATUS_CUDA_ERROR: return "CUDA error";
+    case CB200_STATUS_INTERNAL_ERROR: return "internal error";
+    case CB200_STATUS_STALE_STRUCTURE: return "stale structure";
+    case CB200_STATUS_INSUFFICIENT_WORKSPACE: return "insufficient workspace";
+    case CB200_STATUS_INVALID_STREAM: return "invalid stream";
+    case CB200_STATUS_SEALED: return "session sealed";
+    }
+    return "unknown status";
+}
+
+const char *cb200_last_error(void) { return last_error_buffer(); }
+uint32_t cb200_abi_version(void) { return CB200_ABI_VERSION; }
+uint64_t cb200_kernel_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
+
+/* ---- host layout helpers ------------------------------------------------------------ */
+
+int64_t cb200_build_packed_row_ptr(int32_t bits, const int64_t *row_ptr, int64_t rows, int64_t *packed_row_ptr) {
+    if (row_ptr == nullptr || packed_row_ptr == nullptr || rows < 0 || !(bits == 1 || bits == 2 || bits == 4 || bits == 8))
+        return -1;
+    const int64_t per_byte = 8 / bits;
+    int64_t total = 0;
+    packed_row_ptr[0] = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+        const int64_t count = row_ptr[r + 1] - row_ptr[r];
+        total += count <= 0 ? 0 : (count + per_byte - 1) / per_byte;
+        packed_row_ptr[r + 1] = total;
+    }
+    return total;
+}
+
+int64_t cb200_block_count_for_rows(int64_t rows, int64_t rows_per_block) {
+    return (rows <= 0 || rows_per_block <= 0) ? 0 : (rows + rows_per_block - 1) / rows_per_block;
+}
+
+int64_t cb200_build_uniform_block_row_ptr(int64_t rows, int64_t rows_per_block, int64_t *block_row_ptr) {
+    if (block_row_ptr == nullptr || rows < 0 || rows_per_block <= 0) return -1;
+    const int64_t count = cb200_block_count_for_rows(rows, rows_per_block);
+    for (int64_t b = 0; b < count; ++b) {
+        const int64_t start = b * rows_per_block;
+        block_row_ptr[b] = start < rows ? start : rows;
+    }
+    block_row_ptr[count] = rows;
+    return count;
+}
+
+cb200_status cb200_get_block(int64_t rows, const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                             const int64_t *block_row_ptr, int64_t block_count, int64_t block_index,
+                             cb200_csr_block *out) {
+    clear_error();
+    if (out == nullptr || row_ptr == nullptr || packed_row_ptr == nullptr)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "get_block needs row_ptr, packed_row_ptr and an output");
+    std::memset(out, 0, sizeof(*out));
+    out->block_index = block_index;
+    if (block_row_ptr == nullptr || block_count <= 0) {
+        out->block_index = 0;
+        out->row_end = rows;
+    } else if (block_index < 0 || block_index >= block_count) {
+        return CB200_STATUS_SUCCESS; /* all-zero block, like the reference */
+    } else {
+        out->row_begin = block_row_ptr[block_index];
+        out->row_end = block_row_ptr[block_index + 1];
+    }
+    out->nnz_begin = row_ptr[out->row_begin];
+    out->nnz_end = row_ptr[out->row_end];
+    out->packed_begin = packed_row_ptr[out->row_begin];
+    out->packed_end = packed_row_ptr[out->row_end];
+    return CB200_STATUS_SUCCESS;
+}
+
+/* ---- device codec ------------------------------------------------------------------- */
+
+cb200_status cb200_quantize_rows(const cb200_qcsr *m, int64_t row_begin, int64_t row_end, const float *values,
+                                 int32_t device, void *stream) {
+    clear_error();
+    if (!valid_header(m)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    return launch_quantize_rows(view_of(*m), row_begin, row_end, values, static_cast<cudaStream_t>(stream));
+}
+
+cb200_status cb200_dequantize_rows(const cb200_qcsr *m, int64_t row_begin, int64_t row_end, float *values,
+                                   int32_t device, void *stream) {
+    clear_error();
+    if (!valid_header(m)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    return launch_dequantize_rows(view_of(*m), row_begin, row_end, values, static_cast<cudaStream_t>(stream));
+}
+
+cb200_status cb200_qbell_quantize_rows(const cb200_qbell *m, int64_t row_begin, int64_t row_end,
+                                       const float *values_by_slot, int32_t device, void *stream) {
+    clear_error();
+    if (!valid_header(m)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qbell header");
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    return launch_qbell_quantize_rows(view_of(*m), row_begin, row_end, values_by_slot, static_cast<cudaStream_t>(stream));
+}
+
+cb200_status cb200_qbell_dequantize_rows(const cb200_qbell *m, int64_t row_begin, int64_t row_end,
+                                         float *values_by_slot, int32_t device, void *stream) {
+    clear_error();
+    if (!valid_header(m)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qbell header");
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    return launch_qbell_dequantize_rows(view_of(*m), row_begin, row_end, values_by_slot, static_cast<cudaStream_t>(stream));
+}
+
+/* ---- capability query ---------------------------------------------------------------- */
+
+cb200_status cb200_backend_query(int32_t projection, const cb200_numeric_policy *numeric, cb200_capability *out) {
+    clear_error();
+    if (!valid_header(numeric) || out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad query arguments");
+    out->version = CB200_ABI_VERSION;
+    out->size = sizeof(*out);
+    out->supported = 0;
+    out->flags = 0u;
+    out->persistent_bytes = 0u;
+    out->transient_bytes = 0u;
+    out->name = "";
+    const bool codes = numeric->sparse_storage == CB200_DTYPE_U8 || numeric->sparse_storage == CB200_DTYPE_U4;
+    const bool common = codes && numeric->quantized != 0 && numeric->output_storage == CB200_DTYPE_F32 &&
+                        numeric->accumulation == CB200_DTYPE_F32;
+    switch (projection) {
+    case CB200_PROJECTION_CSR:
+        out->name = "cb200.qcsr.forward.sm100a";
+        out->supported = common && supported_dense(numeric->dense_storage) && numeric->multiply == CB200_DTYPE_F32;
+        /* one warp owns a row and sums in a fixed order: repeated runs are bitwise identical */
+        out->flags = CB200_CAP_DETERMINISTIC | CB200_CAP_GRAPH_CAPTURE;
+        break;
+    case CB200_PROJECTION_TRANSPOSE:
+        out->name = "cb200.qcsr.transpose.sm100a";
+        out->supported = common && numeric->dense_storage == CB200_DTYPE_F32 && numeric->multiply == CB200_DTYPE_F32;
+        out->flags = CB200_CAP_GRAPH_CAPTURE; /* floating-point reductions: order not fixed */
+        break;
+    case CB200_PROJECTION_BLOCKED_ELL:
+        out->name = "cb200.qbell.forward.sm100a";
+        out->supported = common && supported_dense(numeric->dense_storage) &&
+                         (numeric->multiply == CB200_DTYPE_F32 || numeric->multiply == CB200_DTYPE_BF16);
+        out->flags = CB200_CAP_DETERMINISTIC | CB200_CAP_GRAPH_CAPTURE;
+        break;
+    default:
+        return fail(CB200_STATUS_UNSUPPORTED, "unknown projection %d", projection);
+    }
+    return CB200_STATUS_SUCCESS;
+}
+
+/* ---- prepared operation --------------------------------------------------------------- */
+
+cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepared **out) {
+    clear_error();
+    if (out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "prepare needs an output handle");
+    *out = nullptr;
+    if (!valid_header(problem)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_spmm_problem header");
+    if (problem->m < 0 || problem->k < 0 || problem->n < 0 || problem->nnz < 0)
+        return fail(CB200_STATUS_INVALID_SHAPE, "negative dimension");
+    if (problem->structure_epoch == 0u) return fail(CB200_STATUS_STALE_STRUCTURE, "structure epoch must be non-zero");
+    if (!supported_bits(problem->bits)) return fail(CB200_STATUS_UNSUPPORTED, "bits must be 4 or 8, got %d", problem->bits);
+    if (problem->policy != CB200_DECODE_PER_GENE_AFFINE && problem->policy != CB200_DECODE_COLUMN_SCALE_ROW_OFFSET)
+        return fail(CB200_STATUS_UNSUPPORTED, "unknown decode policy %d", problem->policy);
+    if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
+        if (problem->dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes fp32 G");
+        if (problem->deterministic) return fail(CB200_STATUS_UNSUPPORTED, "transpose is not deterministic");
+    } else if (problem->projection == CB200_PROJECTION_CSR || problem->projection == CB200_PROJECTION_BLOCKED_ELL) {
+        if (!supported_dense(problem->dense_dtype)) return fail(CB200_STATUS_UNSUPPORTED, "W must be fp32 or bf16");
+    } else {
+        return fail(CB200_STATUS_UNSUPPORTED, "unknown projection %d", problem->projection);
+    }
+
+    int device_count = 0;
+    CB200_CUDA_OK(cudaGetDeviceCount(&device_count));
+    if (problem->device < 0 || problem->device >= device_count)
+        return fail(CB200_STATUS_INVALID_STREAM, "device %d not present (%d visible)", problem->device, device_count);
+    cudaDeviceProp prop{};
+    CB200_CUDA_OK(cudaGetDeviceProperties(&prop, problem->device));
+    if (prop.major != 10)
+        return fail(CB200_STATUS_UNSUPPORTED, "this library is built for sm_100a only; device %d is sm_%d%d",
+                    problem->device, prop.major, prop.minor);
+
+    cb200_prepared *p = new (std::nothrow) cb200_prepared{};
+    if (p == nullptr) return fail(CB200_STATUS_INTERNAL_ERROR, "out of host memory");
+    p->problem = *problem;
+    p->problem.host_row_ptr = nullptr; /* borrowed for the analysis below only */
+    p->sm_count = prop.multiProcessorCount;
+    p->schedule = fwd_schedule::warp_per_row;
+    p->schedule_name = "warp_per_row";
+    p->workspace_alignment = 256u;
+    p->workspace_bytes = 0u;
+    p->mean_row_nnz = problem->m > 0 ? static_cast<double>(problem->nnz) / static_cast<double>(problem->m) : 0.0;
+    p->max_row_nnz = p->mean_row_nnz;
+    if (problem->host_row_ptr != nullptr && problem->projection != CB200_PROJECTION_BLOCKED_ELL) {
+        int64_t longest = 0;
+        for (int64_t r = 0; r < problem->m; ++r) {
+            const int64_t c = problem->host_row_ptr[r + 1] - problem->host_row_ptr[r];
+            if (c > longest) longest = c;
+        }
+        p->max_row_nnz = static_cast<double>(longest);
+    }
+    if (problem->projection == CB200_PROJECTION_TRANSPOSE)
+        p->workspace_bytes = qcsr_transpose_workspace_bytes(problem->k, problem->n, p->sm_count);
+    *out = p;
+    return CB200_STATUS_SUCCESS;
+}
+
+void cb200_prepared_destroy(cb200_prepared *prepared) { delete prepared; }
+
+cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment) {
+    clear_error();
+    if (prepared == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "null prepared operation");
+    if (minimum_bytes != nullptr) *minimum_bytes = prepared->workspace_bytes;
+    if (alignment != nullptr) *alignment = prepared->workspace_alignment;
+    return CB200_STATUS_SUCCESS;
+}
+
+const char *cb200_prepared_schedule(const cb200_prepared *prepared) {
+    return prepared != nullptr ? prepared->schedule_name : "";
+}
+
+cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch) {
+    clear_error();
+    if (prepared == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "null prepared operation");
+    if (!valid_header(launch)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_launch header");
+    const cb200_spmm_problem &pr = prepared->problem;
+    /* launch_bindings.hh:261-275,361-375: epoch, stream/device and workspace checks come first */
+    if (launch->structure_epoch != pr.structure_epoch)
+        return fail(CB200_STATUS_STALE_STRUCTURE, "launch epoch %llu != prepared epoch %llu",
+                    (unsigned long long)launch->structure_epoch, (unsigned long long)pr.structure_epoch);
+    if (launch->device != pr.device || launch->device < 0)
+        return fail(CB200_STATUS_INVALID_STREAM, "launch device %d != prepared device %d", launch->device, pr.device);
+    if (launch->workspace_device != launch->device)
+        return fail(CB200_STATUS_INVALID_STREAM, "workspace lives on device %d, stream on device %d",
+                    launch->workspace_device, launch->device);
+    if (launch->workspace_bytes < prepared->workspace_bytes ||
+        (prepared->workspace_bytes != 0u &&
+         (launch->workspace == nullptr ||
+          (reinterpret_cast<std::uintptr_t>(launch->workspace) & (prepared->workspace_alignment - 1u)) != 0u)))
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "workspace of %llu bytes needed, %llu given",
+                    (unsigned long long)prepared->workspace_bytes, (unsigned long long)launch->workspace_bytes);
+    if (launch->out == nullptr && pr.n != 0 && pr.m != 0)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "null output");
+    if (launch->dense == nullptr && pr.n != 0 && pr.k != 0) return fail(CB200_STATUS_INVALID_ARGUMENT, "null dense operand");
+    if (launch->out == launch->dense && launch->out != nullptr)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "output aliases the dense input");
+    if (launch->dense_ld < pr.n || launch->out_ld < pr.n)
+        return fail(CB200_STATUS_INVALID_SHAPE, "leading dimension smaller than n");
+
+    dense_args d{launch->dense, launch->dense_ld, pr.dense_dtype, launch->out, launch->out_ld, pr.n,
+                 launch->alpha, launch->beta};
+    cudaStream_t stream = static_cast<cudaStream_t>(launch->stream);
+    device_scope scope(launch->device);
+    CB200_CUDA_OK(scope.status);
+
+    int64_t row_begin = launch->row_begin, row_end = launch->row_end;
+    if (row_begin == 0 && row_end == 0) row_end = pr.m;
+    if (row_begin < 0 || row_end > pr.m || row_begin > row_end)
+        return fail(CB200_STATUS_INVALID_SHAPE, "row range [%lld,%lld) outside 0..%lld", (long long)row_begin,
+                    (long long)row_end, (long long)pr.m);
+
+    if (pr.projection == CB200_PROJECTION_BLOCKED_ELL) {
+        if (!valid_header(launch->bell)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qbell header");
+        const cb200_qbell &b = *launch->bell;
+        if (b.rows != pr.m || b.cols != pr.k || b.bits != pr.bits || b.policy != pr.policy)
+            return fail(CB200_STATUS_INVALID_SHAPE, "Blocked-ELL matrix disagrees with the prepared problem");
+        if (b.block_col_idx == nullptr || b.packed_values == nullptr)
+            return fail(CB200_STATUS_INVALID_ARGUMENT, "Blocked-ELL matrix has null arrays");
+        return launch_qbell_forward(view_of(b), d, row_begin, row_end, prepared->sm_count, stream);
+    }
+    if (!valid_header(launch->csr)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
+    const cb200_qcsr &x = *launch->csr;
+    if (x.rows != pr.m || x.cols != pr.k || x.bits != pr.bits || x.policy != pr.policy || x.nnz != pr.nnz)
+        return fail(CB200_STATUS_INVALID_SHAPE, "CSR matrix disagrees with the prepared problem");
+    if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed_values == nullptr)))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "CSR matrix has null arrays");
+    if (pr.projection == CB200_PROJECTION_TRANSPOSE)
+        return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, launch->workspace, launch->workspace_bytes,
+                                     prepared->sm_count, stream);
+    return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, nullptr, launch->workspace,
+                               prepared->sm_count, stream);
+}
+
+/* ---- session ------------------------------------------------------------------------------ */
+
+cb200_status cb200_session_create(const cb200_session_options *options, cb200_session **out) {
+    clear_error();
+    if (out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "session_create needs an output handle");
+    *out = nullptr;
+    if (!valid_header(options)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_session_options header");
+    const std::uint32_t total = options->owned_stream_count + options->external_stream_count;
+    if (total == 0u || total > 8u) return fail(CB200_STATUS_INVALID_ARGUMENT, "a session has 1..8 streams");
+    if (options->external_stream_count != 0u && options->external_streams == nullptr)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "external stream array is null");
+    device_scope scope(options->device);
+    CB200_CUDA_OK(scope.status);
+    cb200_session *s = new (std::nothrow) cb200_session{};
+    if (s == nullptr) return fail(CB200_STATUS_INTERNAL_ERROR, "out of host memory");
+    s->device = options->device;
+    for (std::uint32_t i = 0; i < options->external_stream_count; ++i) {
+        s->streams[s->stream_count] = static_cast<cudaStream_t>(options->external_streams[i]);
+        s->owned[s->stream_count++] = false;
+    }
+    for (std::uint32_t i = 0; i < options->owned_stream_count; ++i) {
+        cudaStream_t stream = nullptr;
+        const cudaError_t err = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+        if (err != cudaSuccess) {
+            cb200_session_destroy(s);
+            return fail(CB200_STATUS_CUDA_ERROR, "cudaStreamCreateWithFlags: %s", cudaGetErrorString(err));
+        }
+        s->streams[s->stream_count] = stream;
+        s->owned[s->stream_count++] = true;
+    }
+    *out = s;
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status cb200_session_reserve_persistent(cb200_session *s, uint64_t bytes, void **allocation) {
+    clear_error();
+    if (s == nullptr || allocation == nullptr || bytes == 0u) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad reserve arguments");
+    if (s->sealed) return fail(CB200_STATUS_SEALED, "session is sealed; nothing can grow");
+    if (s->persistent_count == 64u) return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "64 persistent allocations at most");
+    device_scope scope(s->device);
+    CB200_CUDA_OK(scope.status);
+    void *ptr = nullptr;
+    CB200_CUDA_OK(cudaMalloc(&ptr, bytes));
+    s->persistent[s->persistent_count++] = ptr;
+    *allocation = ptr;
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status cb200_session_reserve_transient(cb200_session *s, uint32_t stream_index, uint64_t bytes) {
+    clear_error();
+    if (s == nullptr || stream_index >= s->stream_count) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad stream index");
+    if (s->sealed) return fail(CB200_STATUS_SEALED, "session is sealed; nothing can grow");
+    if (bytes <= s->transient_bytes[stream_index]) return CB200_STATUS_SUCCESS;
+    device_scope scope(s->device);
+    CB200_CUDA_OK(scope.status);
+    void *ptr = nullptr;
+    CB200_CUDA_OK(cudaMalloc(&ptr, bytes));
+    if (s->transient[stream_index] != nullptr) cudaFree(s->transient[stream_index]);
+    s->transient[stream_index] = ptr;
+    s->transient_bytes[stream_index] = bytes;
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status cb200_session_seal(cb200_session *s) {
+    clear_error();
+    if (s == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "null session");
+    s->sealed = true;
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_launch_binding cb200_session_bind(cb200_session *s, uint32_t stream_index, uint64_t required_workspace_bytes) {
+    cb200_launch_binding b{};
+    b.status = CB200_STATUS_INVALID_ARGUMENT;
+    b.device = -1;
+    if (s == nullptr || stream_index >= s->stream_count) return b;
+    if (!s->sealed) { b.status = CB200_STATUS_SEALED; return b; } /* bind only works on a sealed session */
+    if (required_workspace_bytes > s->transient_bytes[stream_index]) { b.status = CB200_STATUS_INSUFFICIENT_WORKSPACE; return b; }
+    b.status = CB200_STATUS_SUCCESS;
+    b.device = s->device;
+    b.stream = s->streams[stream_index];
+    b.workspace = s->transient[stream_index];
+    b.workspace_bytes = s->transient_bytes[stream_index];
+    return b;
+}
+
+cb200_status cb200_session_synchronize(cb200_session *s) {
+    clear_error();
+    if (s == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "null session");
+    device_scope scope(s->device);
+    CB200_CUDA_OK(scope.status);
+    for (std::uint32_t i = 0; i < s->stream_count; ++i) CB200_CUDA_OK(cudaStreamSynchronize(s->streams[i]));
+    return CB200_STATUS_SUCCESS;
+}
+
+void cb200_session_destroy(cb200_session *s) {
+    if (s == nullptr) return;
+    device_scope scope(s->device);
+    for (std::uint32_t i = 0; i < s->stream_count; ++i) {
+        if (s->owned[i] && s->streams[i] != nullptr) cudaStreamDestroy(s->streams[i]);
+        if (s->transient[i] != nullptr) cudaFree(s->transient[i]);
+    }
+    for (std::uint32_t i = 0; i < s->persistent_count; ++i) cudaFree(s->persistent[i]);
+    delete s;
+}
+
+} // extern "C"

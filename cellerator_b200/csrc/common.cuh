@@ -1,0 +1,77 @@
+// Shared host-side plumbing of the cellerator_b200 library: status + thread-local error text,
+// a process-wide kernel-launch counter, and small device helpers used by several kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/cellerator_b200.h"
+
+namespace cb200 {
+
+// Thread-local message of the last failing call (the convention of the reference's public
+// C ABI, src/abi/abi.cu:40-74).
+char *last_error_buffer();
+cb200_status fail(cb200_status status, const char *fmt, ...);
+void clear_error();
+
+// Every kernel launch of this library goes through count_launch() so that callers can
+// report how many of its kernels ran inside a timed region.
+extern std::atomic<std::uint64_t> g_kernel_launches;
+inline void count_launch(std::uint64_t n = 1) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
+
+#define CB200_CUDA_OK(expr)                                                                       \
+    do {                                                                                          \
+        const cudaError_t cb200_err_ = (expr);                                                    \
+        if (cb200_err_ != cudaSuccess)                                                            \
+            return ::cb200::fail(CB200_STATUS_CUDA_ERROR, "%s: %s", #expr, cudaGetErrorString(cb200_err_)); \
+    } while (0)
+
+// Sets the device for the scope and restores the previous one (launchers may be called with
+// another device current).
+struct device_scope {
+    int previous = -1;
+    cudaError_t status = cudaSuccess;
+    explicit device_scope(int device) {
+        status = cudaGetDevice(&previous);
+        if (status == cudaSuccess && previous != device) status = cudaSetDevice(device);
+    }
+    ~device_scope() {
+        int now = -1;
+        if (cudaGetDevice(&now) == cudaSuccess && previous >= 0 && now != previous) cudaSetDevice(previous);
+    }
+};
+
+#if defined(__CUDACC__)
+// bf16 pair (low half = element 0) -> two floats, exact.
+__device__ __forceinline__ void bf16x2_to_f32(std::uint32_t packed, float &lo, float &hi) {
+    lo = __uint_as_float(packed << 16);
+    hi = __uint_as_float(packed & 0xffff0000u);
+}
+
+// Eight consecutive elements of a dense row as floats (16-byte aligned address).
+__device__ __forceinline__ void load8(const float *p, float (&w)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&w)[8]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(p));
+    bf16x2_to_f32(a.x, w[0], w[1]);
+    bf16x2_to_f32(a.y, w[2], w[3]);
+    bf16x2_to_f32(a.z, w[4], w[5]);
+    bf16x2_to_f32(a.w, w[6], w[7]);
+}
+__device__ __forceinline__ float load1(const float *p) { return __ldg(p); }
+__device__ __forceinline__ float load1(const __nv_bfloat16 *p) {
+    return __uint_as_float(static_cast<std::uint32_t>(__ldg(reinterpret_cast<const unsigned short *>(p))) << 16);
+}
+#endif
+
+} // namespace cb200

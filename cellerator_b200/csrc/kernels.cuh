@@ -1,0 +1,67 @@
+// Launchers of the sm_100a kernels, called by the C-ABI layer (capi.cu).  Each takes device
+// pointers and a stream, enqueues, and returns; none allocates or synchronises.
+#pragma once
+
+#include "common.cuh"
+
+namespace cb200 {
+
+struct qcsr_view {
+    std::int64_t rows, cols, nnz;
+    int bits, policy;
+    const std::int64_t *row_ptr;
+    const std::int64_t *packed_row_ptr; // may be null when bits == 8
+    const std::int32_t *col_idx;
+    const std::uint8_t *packed;
+    const float *scales;
+    const float *offsets;
+};
+
+struct dense_args {
+    const void *dense; // W or G
+    std::int64_t dense_ld;
+    int dense_dtype; // CB200_DTYPE_F32 | CB200_DTYPE_BF16
+    float *out;
+    std::int64_t out_ld;
+    std::int64_t n;
+    float alpha, beta;
+};
+
+enum class fwd_schedule : int { warp_per_row = 0, row_split = 1 };
+
+// Y[r,:] = alpha * sum_i deq(code_i) * W[col_i,:] + beta * Y[r,:]  for r in [row_begin,row_end)
+cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                 std::int64_t row_end, fwd_schedule schedule, const void *persistent,
+                                 void *workspace, int sm_count, cudaStream_t stream);
+
+// G'[g,:] = alpha * sum_{r in range, col_i == g} deq(code_i) * G[r,:] + beta * G'[g,:]
+cb200_status launch_qcsr_transpose(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                   std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                   int sm_count, cudaStream_t stream);
+std::uint64_t qcsr_transpose_workspace_bytes(std::int64_t cols, std::int64_t n, int sm_count);
+
+struct qbell_view {
+    std::int64_t rows, cols;
+    int block_size, ell_cols;
+    std::int64_t row_stride_bytes;
+    int bits, policy;
+    const std::uint32_t *block_col_idx;
+    const std::uint8_t *packed;
+    const float *scales;
+    const float *offsets;
+};
+
+cb200_status launch_qbell_forward(const qbell_view &x, const dense_args &d, std::int64_t row_begin,
+                                  std::int64_t row_end, int sm_count, cudaStream_t stream);
+
+cb200_status launch_quantize_rows(const qcsr_view &x, std::int64_t row_begin, std::int64_t row_end,
+                                  const float *values, cudaStream_t stream);
+cb200_status launch_dequantize_rows(const qcsr_view &x, std::int64_t row_begin, std::int64_t row_end,
+                                    float *values, cudaStream_t stream);
+
+cb200_status launch_qbell_quantize_rows(const qbell_view &x, std::int64_t row_begin, std::int64_t row_end,
+                                        const float *values_by_slot, cudaStream_t stream);
+cb200_status launch_qbell_dequantize_rows(const qbell_view &x, std::int64_t row_begin, std::int64_t row_end,
+                                          float *values_by_slot, cudaStream_t stream);
+
+} // namespace cb200

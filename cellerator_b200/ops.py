@@ -1,0 +1,307 @@
+"""Driver-side objects over the C ABI: device-resident quantized matrices and prepared SpMM
+operations.  torch supplies device memory and streams only; every computation is a call into
+libcellerator_b200.so through `capi`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from . import capi
+
+_TORCH_DENSE = {torch.float32: capi.DTYPE_F32, torch.bfloat16: capi.DTYPE_BF16}
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream_handle(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# ---- host helpers (no device) ----------------------------------------------------------
+
+def build_packed_row_ptr(bits: int, row_ptr: np.ndarray):
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int64)
+    out = np.zeros_like(row_ptr)
+    total = capi.lib().cb200_build_packed_row_ptr(bits, row_ptr.ctypes.data, len(row_ptr) - 1, out.ctypes.data)
+    if total < 0:
+        raise capi.Cb200Error(capi.INVALID_ARGUMENT, "build_packed_row_ptr rejected its arguments")
+    return out, int(total)
+
+
+def build_uniform_block_row_ptr(rows: int, rows_per_block: int) -> np.ndarray:
+    count = int(capi.lib().cb200_block_count_for_rows(rows, rows_per_block))
+    out = np.zeros(count + 1, dtype=np.int64)
+    rc = capi.lib().cb200_build_uniform_block_row_ptr(rows, rows_per_block, out.ctypes.data)
+    if rc < 0:
+        raise capi.Cb200Error(capi.INVALID_ARGUMENT, "build_uniform_block_row_ptr rejected its arguments")
+    return out
+
+
+def get_block(row_ptr, packed_row_ptr, block_row_ptr, block_index) -> dict:
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int64)
+    packed_row_ptr = np.ascontiguousarray(packed_row_ptr, dtype=np.int64)
+    brp = None if block_row_ptr is None else np.ascontiguousarray(block_row_ptr, dtype=np.int64)
+    out = capi.CsrBlock()
+    capi.check(capi.lib().cb200_get_block(len(row_ptr) - 1, row_ptr.ctypes.data, packed_row_ptr.ctypes.data,
+                                          None if brp is None else brp.ctypes.data,
+                                          0 if brp is None else len(brp) - 1, block_index, C.byref(out)))
+    return {n: getattr(out, n) for n, _ in capi.CsrBlock._fields_}
+
+
+def partition_rows(rows: int, parts: int) -> np.ndarray:
+    """Row range per shard: the reference's uniform rule with rows_per_block = ceil(rows/parts),
+    padded with empty trailing shards so that there are exactly `parts` of them."""
+    per = max(1, -(-rows // max(parts, 1)))
+    brp = build_uniform_block_row_ptr(rows, per)
+    if len(brp) - 1 < parts:
+        brp = np.concatenate([brp, np.full(parts - (len(brp) - 1), rows, dtype=np.int64)])
+    return brp
+
+
+# ---- device containers -------------------------------------------------------------------
+
+@dataclass
+class QuantizedCsr:
+    """Quantized CSR on one device (layout of cb200_qcsr)."""
+    rows: int
+    cols: int
+    bits: int
+    policy: int
+    row_ptr: torch.Tensor            # int64 [rows+1]
+    col_idx: torch.Tensor            # int32 [nnz]
+    packed: torch.Tensor             # uint8
+    scales: torch.Tensor | None      # float32 [cols]
+    offsets: torch.Tensor | None     # float32 [cols] or [rows]
+    packed_row_ptr: torch.Tensor | None = None   # int64 [rows+1]; None for 8-bit
+    host_row_ptr: np.ndarray | None = None
+    _desc: capi.QCsr | None = field(default=None, repr=False)
+
+    @property
+    def nnz(self) -> int:
+        return int(self.col_idx.numel())
+
+    @property
+    def device(self):
+        return self.row_ptr.device
+
+    def desc(self) -> capi.QCsr:
+        d = capi.header(capi.QCsr())
+        d.rows, d.cols, d.nnz, d.bits, d.policy = self.rows, self.cols, self.nnz, self.bits, self.policy
+        d.row_ptr = self.row_ptr.data_ptr()
+        d.packed_row_ptr = None if self.packed_row_ptr is None else self.packed_row_ptr.data_ptr()
+        d.col_idx = self.col_idx.data_ptr() if self.nnz else None
+        d.packed_values = self.packed.data_ptr() if self.packed.numel() else None
+        d.scales = None if self.scales is None else self.scales.data_ptr()
+        d.offsets = None if self.offsets is None else self.offsets.data_ptr()
+        self._desc = d
+        return d
+
+    @staticmethod
+    def from_host(h: dict, device) -> "QuantizedCsr":
+        def dev(a, dt):
+            return None if a is None else torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(device)
+        return QuantizedCsr(rows=int(h["rows"]), cols=int(h["cols"]), bits=int(h["bits"]), policy=int(h["policy"]),
+                            row_ptr=dev(h["row_ptr"], np.int64), col_idx=dev(h["col_idx"], np.int32),
+                            packed=dev(h["packed"], np.uint8), scales=dev(h.get("scales"), np.float32),
+                            offsets=dev(h.get("offsets"), np.float32),
+                            packed_row_ptr=None if int(h["bits"]) == 8 and h.get("packed_row_ptr") is None
+                            else dev(h["packed_row_ptr"], np.int64),
+                            host_row_ptr=np.ascontiguousarray(h["row_ptr"], dtype=np.int64))
+
+    def quantize_(self, values: torch.Tensor, row_begin=0, row_end=None) -> None:
+        """Overwrite the packed codes of rows [row_begin,row_end) from one float per entry."""
+        row_end = self.rows if row_end is None else row_end
+        dev = self.device
+        capi.check(capi.lib().cb200_quantize_rows(C.byref(self.desc()), row_begin, row_end, values.data_ptr(),
+                                                  dev.index, _stream_handle(dev)))
+
+    def dequantize(self, row_begin=0, row_end=None) -> torch.Tensor:
+        row_end = self.rows if row_end is None else row_end
+        dev = self.device
+        lo, hi = (int(v) for v in self.row_ptr[[row_begin, row_end]].tolist())
+        out = torch.empty(max(hi - lo, 1), dtype=torch.float32, device=dev)
+        capi.check(capi.lib().cb200_dequantize_rows(C.byref(self.desc()), row_begin, row_end, out.data_ptr(),
+                                                    dev.index, _stream_handle(dev)))
+        return out[: hi - lo]
+
+
+@dataclass
+class QuantizedBell:
+    """Quantized Blocked-ELL on one device (layout of cb200_qbell)."""
+    rows: int
+    cols: int
+    block_size: int
+    ell_cols: int
+    row_stride_bytes: int
+    bits: int
+    policy: int
+    block_col_idx: torch.Tensor      # uint32 stored as int32 bits [ceil(rows/bs) * ell_cols/bs]
+    packed: torch.Tensor             # uint8 [rows * row_stride_bytes]
+    scales: torch.Tensor | None
+    offsets: torch.Tensor | None
+    _desc: capi.QBell | None = field(default=None, repr=False)
+
+    @property
+    def device(self):
+        return self.packed.device
+
+    def desc(self) -> capi.QBell:
+        d = capi.header(capi.QBell())
+        d.rows, d.cols, d.block_size, d.ell_cols = self.rows, self.cols, self.block_size, self.ell_cols
+        d.row_stride_bytes, d.bits, d.policy = self.row_stride_bytes, self.bits, self.policy
+        d.block_col_idx = self.block_col_idx.data_ptr()
+        d.packed_values = self.packed.data_ptr()
+        d.scales = None if self.scales is None else self.scales.data_ptr()
+        d.offsets = None if self.offsets is None else self.offsets.data_ptr()
+        self._desc = d
+        return d
+
+    @staticmethod
+    def from_host(h: dict, device) -> "QuantizedBell":
+        def dev(a, dt):
+            return None if a is None else torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(device)
+        bci = np.ascontiguousarray(h["block_col_idx"], dtype=np.uint32).view(np.int32)
+        return QuantizedBell(rows=int(h["rows"]), cols=int(h["cols"]), block_size=int(h["block_size"]),
+                             ell_cols=int(h["ell_cols"]), row_stride_bytes=int(h["row_stride_bytes"]),
+                             bits=int(h["bits"]), policy=int(h["policy"]), block_col_idx=dev(bci, np.int32),
+                             packed=dev(h["packed"], np.uint8), scales=dev(h.get("scales"), np.float32),
+                             offsets=dev(h.get("offsets"), np.float32))
+
+
+def quantize_bell_(x: QuantizedBell, values_by_slot: torch.Tensor, row_begin=0, row_end=None) -> None:
+    row_end = x.rows if row_end is None else row_end
+    dev = x.device
+    capi.check(capi.lib().cb200_qbell_quantize_rows(C.byref(x.desc()), row_begin, row_end, values_by_slot.data_ptr(),
+                                                    dev.index, _stream_handle(dev)))
+
+
+def dequantize_bell(x: QuantizedBell, row_begin=0, row_end=None) -> torch.Tensor:
+    row_end = x.rows if row_end is None else row_end
+    dev = x.device
+    out = torch.empty((row_end - row_begin, x.ell_cols), dtype=torch.float32, device=dev)
+    capi.check(capi.lib().cb200_qbell_dequantize_rows(C.byref(x.desc()), row_begin, row_end, out.data_ptr(),
+                                                      dev.index, _stream_handle(dev)))
+    return out
+
+
+def backend_query(projection: int, sparse=capi.DTYPE_U8, dense=capi.DTYPE_BF16, output=capi.DTYPE_F32,
+                  multiply=capi.DTYPE_F32, accumulation=capi.DTYPE_F32, quantized=1) -> dict:
+    pol = capi.header(capi.NumericPolicy())
+    pol.sparse_storage, pol.dense_storage, pol.output_storage = sparse, dense, output
+    pol.multiply, pol.accumulation, pol.quantized = multiply, accumulation, quantized
+    cap = capi.Capability()
+    capi.check(capi.lib().cb200_backend_query(projection, C.byref(pol), C.byref(cap)))
+    return {"supported": bool(cap.supported), "flags": cap.flags, "persistent_bytes": cap.persistent_bytes,
+            "transient_bytes": cap.transient_bytes, "name": (cap.name or b"").decode()}
+
+
+class PreparedSpmm:
+    """prepare once, run many times (cb200_spmm_prepare / cb200_spmm_run)."""
+
+    def __init__(self, projection: int, m: int, k: int, n: int, nnz: int, bits: int, policy: int, dense_dtype,
+                 device, structure_epoch: int = 1, host_row_ptr: np.ndarray | None = None, deterministic=False):
+        self.device = torch.device(device)
+        pr = capi.header(capi.SpmmProblem())
+        pr.projection, pr.m, pr.k, pr.n, pr.nnz, pr.bits, pr.policy = projection, m, k, n, nnz, bits, policy
+        pr.dense_dtype = _TORCH_DENSE[dense_dtype] if isinstance(dense_dtype, torch.dtype) else dense_dtype
+        pr.device = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        pr.structure_epoch = structure_epoch
+        self._host_row_ptr = None
+        if host_row_ptr is not None:
+            self._host_row_ptr = np.ascontiguousarray(host_row_ptr, dtype=np.int64)
+            pr.host_row_ptr = self._host_row_ptr.ctypes.data
+        pr.deterministic = int(deterministic)
+        self.problem = pr
+        self.handle = C.c_void_p()
+        capi.check(capi.lib().cb200_spmm_prepare(C.byref(pr), C.byref(self.handle)))
+        nbytes, align = C.c_uint64(), C.c_uint32()
+        capi.check(capi.lib().cb200_prepared_workspace(self.handle, C.byref(nbytes), C.byref(align)))
+        self.workspace_bytes, self.workspace_alignment = nbytes.value, align.value
+        self.workspace = (torch.empty(self.workspace_bytes, dtype=torch.uint8, device=self.device)
+                          if self.workspace_bytes else None)
+        self.epoch = structure_epoch
+
+    @property
+    def schedule(self) -> str:
+        return capi.lib().cb200_prepared_schedule(self.handle).decode()
+
+    def make_launch(self, x, dense: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0, row_begin=0, row_end=0,
+                    stream: int | None = None, epoch: int | None = None) -> capi.Launch:
+        ln = capi.header(capi.Launch())
+        desc = x.desc()
+        if isinstance(x, QuantizedBell):
+            ln.bell = C.pointer(desc)
+        else:
+            ln.csr = C.pointer(desc)
+        ln.dense, ln.dense_ld = dense.data_ptr(), dense.stride(0)
+        ln.out, ln.out_ld = out.data_ptr(), out.stride(0)
+        ln.alpha, ln.beta = alpha, beta
+        ln.structure_epoch = self.epoch if epoch is None else epoch
+        ln.row_begin, ln.row_end = row_begin, row_end
+        dev_index = self.problem.device
+        ln.stream = _stream_handle(self.device) if stream is None else stream
+        ln.device = dev_index
+        ln.workspace_device = dev_index
+        ln.workspace = None if self.workspace is None else self.workspace.data_ptr()
+        ln.workspace_bytes = self.workspace_bytes
+        ln._keep = (desc, x, dense, out)
+        return ln
+
+    def run_launch(self, launch: capi.Launch) -> None:
+        capi.check(capi.lib().cb200_spmm_run(self.handle, C.byref(launch)))
+
+    def run(self, x, dense, out, **kw) -> torch.Tensor:
+        self.run_launch(self.make_launch(x, dense, out, **kw))
+        return out
+
+    def close(self):
+        if self.handle:
+            capi.lib().cb200_prepared_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0):
+    """Y = alpha * deq(X) W + beta * Y (one-shot convenience: prepare + run)."""
+    n = w.shape[1]
+    if out is None:
+        out = torch.empty(x.rows, n, dtype=torch.float32, device=x.device)
+    op = PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, n, x.nnz, x.bits, x.policy, w.dtype, x.device,
+                      host_row_ptr=x.host_row_ptr)
+    op.run(x, w, out, alpha=alpha, beta=beta)
+    op.close()
+    return out
+
+
+def spmm_transpose(x: QuantizedCsr, g: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
+                   row_begin=0, row_end=0):
+    """G' = alpha * deq(X)^T G + beta * G'."""
+    n = g.shape[1]
+    if out is None:
+        out = torch.empty(x.cols, n, dtype=torch.float32, device=x.device)
+    op = PreparedSpmm(capi.PROJECTION_TRANSPOSE, x.rows, x.cols, n, x.nnz, x.bits, x.policy, g.dtype, x.device)
+    op.run(x, g, out, alpha=alpha, beta=beta, row_begin=row_begin, row_end=row_end)
+    op.close()
+    return out
+
+
+def bell_forward(x: QuantizedBell, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0):
+    n = w.shape[1]
+    if out is None:
+        out = torch.empty(x.rows, n, dtype=torch.float32, device=x.device)
+    op = PreparedSpmm(capi.PROJECTION_BLOCKED_ELL, x.rows, x.cols, n, x.rows * x.ell_cols, x.bits, x.policy,
+                      w.dtype, x.device)
+    op.run(x, w, out, alpha=alpha, beta=beta)
+    op.close()
+    return out

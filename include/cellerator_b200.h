@@ -1,0 +1,286 @@
+/*
+ * cellerator_b200 — C ABI of the B200 (sm_100a) backend for Cellerator's quantized
+ * sparse-matrix path:  Y = dequant(X) * W  over a quantized CSR cells x genes matrix, its
+ * gene-side transpose  G' = dequant(X)^T * G,  and the quantized Blocked-ELL projection.
+ *
+ * Everything here is plain C: pointers, sizes, integer status codes.  Device pointers are
+ * CUDA device addresses on the device named by the call; `stream` is a cudaStream_t passed
+ * as void*.  No entry point falls back to the CPU: without a usable CUDA device the compute
+ * calls return CB200_STATUS_CUDA_ERROR.
+ *
+ * Each declaration cites the interface of the Cellerator reference that it stands in for
+ * (paths relative to the Cellerator project root).
+ *
+ * Conventions (after include/Cellerator/abi.h:14-55,100-118): every descriptor starts with
+ * {version, size}; functions return cb200_status; the text of the last failure on the calling
+ * thread is available from cb200_last_error().
+ */
+#ifndef CELLERATOR_B200_H
+#define CELLERATOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CB200_ABI_VERSION 1u
+
+/* include/Cellerator/abi.h:14-21 (cellerator_status), extended with the operation-core
+ * outcomes of operation_core.hh:118-131 that can cross this boundary. */
+typedef enum cb200_status {
+    CB200_STATUS_SUCCESS = 0,
+    CB200_STATUS_INVALID_ARGUMENT = 1,
+    CB200_STATUS_INVALID_SHAPE = 2,
+    CB200_STATUS_UNSUPPORTED = 3,
+    CB200_STATUS_CUDA_ERROR = 4,
+    CB200_STATUS_INTERNAL_ERROR = 5,
+    CB200_STATUS_STALE_STRUCTURE = 6,
+    CB200_STATUS_INSUFFICIENT_WORKSPACE = 7,
+    CB200_STATUS_INVALID_STREAM = 8,
+    CB200_STATUS_SEALED = 9
+} cb200_status;
+
+/* execution::numeric_type, include/Cellerator/execution/operands.hh:9-20 (same values) */
+typedef enum cb200_dtype {
+    CB200_DTYPE_INVALID = 0,
+    CB200_DTYPE_U8 = 2,
+    CB200_DTYPE_U4 = 32, /* 4-bit nibble-packed codes; no counterpart enum value in the reference */
+    CB200_DTYPE_F16 = 6,
+    CB200_DTYPE_BF16 = 7,
+    CB200_DTYPE_F32 = 8,
+    CB200_DTYPE_F64 = 9
+} cb200_dtype;
+
+/* quantized::blocked_ell decode policies, include/Cellerator/quantized/blocked_ell.cuh:10-14;
+ * metadata policies of include/Cellerator/quantized/metadata.cuh:7-56 */
+typedef enum cb200_decode_policy {
+    CB200_DECODE_PER_GENE_AFFINE = 1,        /* value = code*scales[gene] + offsets[gene] */
+    CB200_DECODE_COLUMN_SCALE_ROW_OFFSET = 2 /* value = code*scales[gene] + offsets[row]  */
+} cb200_decode_policy;
+
+/* core::projection_kind, operation_core.hh:25-37 (same values) */
+typedef enum cb200_projection {
+    CB200_PROJECTION_CSR = 5,
+    CB200_PROJECTION_BLOCKED_ELL = 8,
+    CB200_PROJECTION_TRANSPOSE = 10
+} cb200_projection;
+
+const char *cb200_status_string(cb200_status status); /* abi.h:100 */
+const char *cb200_last_error(void);                   /* abi.h:101, thread-local */
+uint32_t cb200_abi_version(void);
+
+/* ------------------------------------------------------------------------------------ */
+/* Quantized CSR layout.  quantized::csr_matrix, include/Cellerator/quantized/layout.cuh:12-38,
+ * with the index widths of the referee's logical_csr_view (referee.hh:40-48): int64 row
+ * pointers, int32 gene indices.  Code i of row r is byte packed_row_ptr[r] + i/cpb, bit shift
+ * (i mod cpb)*bits, cpb = 8/bits (format.cuh:39-48).  For bits == 8 packed_row_ptr may be
+ * NULL: it then equals row_ptr. `offsets` is per gene or per row according to `policy`;
+ * NULL scales mean 1, NULL offsets mean 0 (metadata.cuh:17-27). */
+typedef struct cb200_qcsr {
+    uint32_t version;
+    size_t size;
+    int64_t rows;
+    int64_t cols;
+    int64_t nnz;
+    int32_t bits;   /* 8 or 4 on the compute path; 1 and 2 on the codec path */
+    int32_t policy; /* cb200_decode_policy */
+    const int64_t *row_ptr;        /* rows+1 */
+    const int64_t *packed_row_ptr; /* rows+1 byte offsets, or NULL when bits == 8 */
+    const int32_t *col_idx;        /* nnz, ascending within a row */
+    const uint8_t *packed_values;
+    const float *scales;
+    const float *offsets;
+} cb200_qcsr;
+
+/* quantized::csr_block, layout.cuh:41-49 */
+typedef struct cb200_csr_block {
+    int64_t block_index, row_begin, row_end, nnz_begin, nnz_end, packed_begin, packed_end;
+} cb200_csr_block;
+
+/* Host helpers (no CUDA call).
+ * build_packed_row_ptr<Bits>, layout.cuh:111-129: returns total bytes, -1 on bad arguments. */
+int64_t cb200_build_packed_row_ptr(int32_t bits, const int64_t *row_ptr, int64_t rows, int64_t *packed_row_ptr);
+/* block_count_for_rows / build_uniform_block_row_ptr, layout.cuh:131-157: the row partition
+ * used to shard cells over GPUs.  Returns the block count, -1 on bad arguments. */
+int64_t cb200_block_count_for_rows(int64_t rows, int64_t rows_per_block);
+int64_t cb200_build_uniform_block_row_ptr(int64_t rows, int64_t rows_per_block, int64_t *block_row_ptr);
+/* get_block, access.cuh:7-44: host pointers. block_row_ptr NULL => one block over the matrix;
+ * an out-of-range index yields an all-zero block. */
+cb200_status cb200_get_block(int64_t rows, const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                             const int64_t *block_row_ptr, int64_t block_count, int64_t block_index,
+                             cb200_csr_block *out);
+
+/* Device codec over rows [row_begin,row_end) of a device-resident matrix.
+ * launch_quantize_block / launch_dequantize_block, portable_backend.cuh:23-61 with
+ * pack_row_values / unpack_row_values, packing.cuh:13-260.  `values` holds one float per nnz
+ * of the range, values[0] belonging to nnz index row_ptr[row_begin] (block-local, rule of
+ * packing.cuh:17-18).  Quantize writes m->packed_values (cast away const by the callee: the
+ * caller owns the buffer), with the host rounding rule of access.cuh:104-131. */
+cb200_status cb200_quantize_rows(const cb200_qcsr *m, int64_t row_begin, int64_t row_end, const float *values,
+                                 int32_t device, void *stream);
+cb200_status cb200_dequantize_rows(const cb200_qcsr *m, int64_t row_begin, int64_t row_end, float *values,
+                                   int32_t device, void *stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Quantized Blocked-ELL layout.  quantized::blocked_ell::matrix, blocked_ell.cuh:18-36 and
+ * sparse_ops::quantized_blocked_ell_view, src/compute/sparse/ops/ops.hh:28-42.  Row r, slot s
+ * is code s of the row starting at packed_values + r*row_stride_bytes; block_col_idx has
+ * ceil(rows/block_size) * (ell_cols/block_size) entries, 0xffffffff marks an empty block. */
+typedef struct cb200_qbell {
+    uint32_t version;
+    size_t size;
+    int64_t rows;
+    int64_t cols;
+    int32_t block_size;
+    int32_t ell_cols;
+    int64_t row_stride_bytes;
+    int32_t bits;
+    int32_t policy;
+    const uint32_t *block_col_idx;
+    const uint8_t *packed_values;
+    const float *scales;
+    const float *offsets;
+} cb200_qbell;
+
+/* Device codec of the Blocked-ELL layout over rows [row_begin,row_end): device-side form of
+ * pack_row_major_values / unpack_row_major_values, blocked_ell.cuh:165-231.  `values_by_slot`
+ * is row-major with ell_cols floats per row, values_by_slot[0] belonging to row_begin.
+ * Quantize codes EVERY slot (a slot of an empty block uses gene 0's scale/offset, like the
+ * reference) and zeroes the row padding; dequantize writes 0 for slots of empty blocks and
+ * for genes >= cols. */
+cb200_status cb200_qbell_quantize_rows(const cb200_qbell *m, int64_t row_begin, int64_t row_end,
+                                       const float *values_by_slot, int32_t device, void *stream);
+cb200_status cb200_qbell_dequantize_rows(const cb200_qbell *m, int64_t row_begin, int64_t row_end,
+                                         float *values_by_slot, int32_t device, void *stream);
+
+/* ------------------------------------------------------------------------------------ */
+/* Capability query.  operation_candidate.supports_numeric + capability flags and byte
+ * budgets, operation_core.hh:63-68,102-114,185,195-207.  Pure host; touches no device. */
+typedef struct cb200_numeric_policy {
+    uint32_t version;
+    size_t size;
+    int32_t sparse_storage; /* CB200_DTYPE_U8 | CB200_DTYPE_U4 */
+    int32_t dense_storage;  /* CB200_DTYPE_F32 | CB200_DTYPE_BF16 */
+    int32_t output_storage; /* CB200_DTYPE_F32 */
+    int32_t multiply;       /* CB200_DTYPE_F32 (CSR, transpose) | CB200_DTYPE_BF16 (Blocked-ELL) */
+    int32_t accumulation;   /* CB200_DTYPE_F32 */
+    int32_t quantized;      /* non-zero: quantization_granularity != none */
+} cb200_numeric_policy;
+
+enum { /* candidate_capability_flag, operation_core.hh:63-68 (same bits) */
+    CB200_CAP_DETERMINISTIC = 1u << 0,
+    CB200_CAP_GRAPH_CAPTURE = 1u << 1,
+    CB200_CAP_PERSISTENT_PREPROCESSING = 1u << 2,
+    CB200_CAP_COMPOSED_EPILOGUE = 1u << 3
+};
+
+typedef struct cb200_capability {
+    uint32_t version;
+    size_t size;
+    int32_t supported; /* 0 / 1 */
+    uint32_t flags;    /* CB200_CAP_* */
+    uint64_t persistent_bytes;
+    uint64_t transient_bytes;
+    const char *name;
+} cb200_capability;
+
+cb200_status cb200_backend_query(int32_t projection, const cb200_numeric_policy *numeric, cb200_capability *out);
+
+/* ------------------------------------------------------------------------------------ */
+/* Prepared-operation lifecycle.  operation_candidate.prepare -> prepared_operation ->
+ * run_prepared_operation, operation_core.hh:159-193 and operation_core.cc:133-147,179-240.
+ * Prepare does everything that may query the device, read row statistics or size scratch;
+ * run validates the launch, enqueues on the caller's stream and returns without
+ * synchronising or allocating (OPERATION_CORE.md:27-32). */
+typedef struct cb200_spmm_problem {
+    uint32_t version;
+    size_t size;
+    int32_t projection; /* cb200_projection */
+    int64_t m;          /* cells (rows of X) */
+    int64_t k;          /* genes (cols of X) */
+    int64_t n;          /* dense columns */
+    int64_t nnz;        /* CSR: stored entries; Blocked-ELL: rows*ell_cols */
+    int32_t bits;
+    int32_t policy;
+    int32_t dense_dtype; /* W (forward, Blocked-ELL) or G (transpose) */
+    int32_t device;
+    uint64_t structure_epoch; /* non-zero; a launch with another epoch is stale (launch_bindings.hh:261-275) */
+    /* Optional host copy of row_ptr (m+1) used to choose the row schedule; NULL = default. */
+    const int64_t *host_row_ptr;
+    int32_t deterministic; /* prepare_policy.deterministic, operation_core.hh:116-124 */
+    int32_t reserved;
+} cb200_spmm_problem;
+
+typedef struct cb200_prepared cb200_prepared;
+
+cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepared **out);
+void cb200_prepared_destroy(cb200_prepared *prepared);
+/* workspace_requirement, launch_bindings.hh:67-71 */
+cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
+/* kernel choice made at prepare time, as text ("warp_per_row", "row_split", ...) */
+const char *cb200_prepared_schedule(const cb200_prepared *prepared);
+
+/* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch. */
+typedef struct cb200_launch {
+    uint32_t version;
+    size_t size;
+    const cb200_qcsr *csr;   /* CSR and transpose projections */
+    const cb200_qbell *bell; /* Blocked-ELL projection */
+    const void *dense;       /* W: k x n (forward, Blocked-ELL);  G: m x n (transpose); row-major */
+    int64_t dense_ld;        /* elements */
+    float *out;              /* Y: m x n (forward, Blocked-ELL);  G': k x n (transpose); row-major fp32 */
+    int64_t out_ld;
+    float alpha;             /* out = alpha * product + beta * out; beta == 0 never reads out */
+    float beta;
+    uint64_t structure_epoch;
+    int64_t row_begin;       /* rows [row_begin,row_end) of X; out rows are indexed by absolute row */
+    int64_t row_end;         /* 0,0 = all rows */
+    void *stream;            /* stream_context, launch_bindings.hh:55-59 */
+    int32_t device;
+    int32_t workspace_device;
+    void *workspace;         /* transient_workspace, launch_bindings.hh:61-65 */
+    uint64_t workspace_bytes;
+} cb200_launch;
+
+cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch);
+
+/* Number of kernel launches this library has enqueued since it was loaded (all threads). */
+uint64_t cb200_kernel_launch_count(void);
+
+/* ------------------------------------------------------------------------------------ */
+/* Runtime session.  runtime::execution_session, include/Cellerator/runtime/session.cuh:106-177:
+ * init -> reserve persistent / transient -> seal -> bind per launch.  After sealing nothing
+ * grows, and bind makes no CUDA call (SESSION.md:20-29). */
+typedef struct cb200_session cb200_session;
+
+typedef struct cb200_session_options {
+    uint32_t version;
+    size_t size;
+    int32_t device;
+    uint32_t owned_stream_count;
+    uint32_t external_stream_count;
+    void *const *external_streams;
+} cb200_session_options;
+
+typedef struct cb200_launch_binding { /* launch_runtime_binding, session.cuh:122-129 */
+    cb200_status status;
+    int32_t device;
+    void *stream;
+    void *workspace;
+    uint64_t workspace_bytes;
+} cb200_launch_binding;
+
+cb200_status cb200_session_create(const cb200_session_options *options, cb200_session **out);
+cb200_status cb200_session_reserve_persistent(cb200_session *s, uint64_t bytes, void **allocation);
+cb200_status cb200_session_reserve_transient(cb200_session *s, uint32_t stream_index, uint64_t bytes);
+cb200_status cb200_session_seal(cb200_session *s);
+cb200_launch_binding cb200_session_bind(cb200_session *s, uint32_t stream_index, uint64_t required_workspace_bytes);
+cb200_status cb200_session_synchronize(cb200_session *s);
+void cb200_session_destroy(cb200_session *s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CELLERATOR_B200_H */

@@ -1,0 +1,318 @@
+"""ctypes front end of the CPU oracle.  TEST INFRASTRUCTURE ONLY.
+
+`Oracle()` loads ``oracle/liboracle.so`` (the C restatement in ``oracle.c``); `Reference()`
+loads ``oracle/_ref/libcellerator_ref.so`` (the reference's own sources compiled in place)
+when it has been built.  Both expose the same method names so that tests can run one
+against the other.  Nothing in the product package imports this module; the test-suite, the
+smoke check and the CPU-baseline leg of the benchmark do.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_LIB = os.path.join(_HERE, "liboracle.so")
+REF_LIB = os.path.join(_HERE, "_ref", "libcellerator_ref.so")
+
+POLICY_PER_GENE_AFFINE = 1
+POLICY_COLUMN_SCALE_ROW_OFFSET = 2
+
+EPILOGUE = {"none": 0, "bias": 1, "relu": 2, "gelu_erf": 3, "gelu_tanh": 4, "bias_relu": 5,
+            "bias_gelu_erf": 6, "bias_gelu_tanh": 7}
+
+
+def build(ref: bool | None = None) -> None:
+    """Compile liboracle.so, and the reference shim when the reference tree is present."""
+    targets = ["all"]
+    if ref is None:
+        ref = os.path.isdir(os.environ.get("CB200_REFERENCE", "/root/reference"))
+    if ref:
+        targets.append("ref")
+    subprocess.run(["make", "-C", _HERE, *targets], check=True, capture_output=True)
+
+
+def _p(a, ctype):
+    if a is None:
+        return None
+    return a.ctypes.data_as(C.POINTER(ctype))
+
+
+def _i64(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.int64)
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+class _Base:
+    prefix = ""
+
+    def __init__(self, path):
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.lib = C.CDLL(path)
+
+    def _fn(self, name, restype=C.c_int):
+        f = getattr(self.lib, self.prefix + name)
+        f.restype = restype
+        return f
+
+    # ---- layout ---------------------------------------------------------
+    def build_packed_row_ptr(self, bits, row_ptr):
+        row_ptr = _i64(row_ptr)
+        rows = len(row_ptr) - 1
+        out = np.zeros(rows + 1, dtype=np.int64)
+        total = self._fn("build_packed_row_ptr", C.c_int64)(
+            C.c_int(bits), _p(row_ptr, C.c_int64), C.c_int64(rows), _p(out, C.c_int64))
+        return out, int(total)
+
+    def build_uniform_block_row_ptr(self, rows, rows_per_block):
+        count = 0 if rows <= 0 or rows_per_block <= 0 else -(-rows // rows_per_block)
+        out = np.zeros(count + 1, dtype=np.int64)
+        rc = self._fn("build_uniform_block_row_ptr", C.c_int64)(
+            C.c_int64(rows), C.c_int64(rows_per_block), _p(out, C.c_int64))
+        return out, int(rc)
+
+    def get_block(self, row_ptr, packed_row_ptr, block_row_ptr, block_index):
+        row_ptr, packed_row_ptr = _i64(row_ptr), _i64(packed_row_ptr)
+        brp = _i64(block_row_ptr)
+        out = np.zeros(7, dtype=np.int64)
+        self._fn("get_block", None)(
+            C.c_int64(len(row_ptr) - 1), _p(row_ptr, C.c_int64), _p(packed_row_ptr, C.c_int64),
+            _p(brp, C.c_int64), C.c_int64(0 if brp is None else len(brp) - 1), C.c_int64(block_index),
+            _p(out, C.c_int64))
+        return dict(zip(("block_index", "row_begin", "row_end", "nnz_begin", "nnz_end", "packed_begin",
+                         "packed_end"), (int(v) for v in out)))
+
+    # ---- scalar code rules ---------------------------------------------
+    def quantize_code(self, bits, value, scale, offset):
+        return int(self._fn("quantize_code", C.c_uint)(C.c_int(bits), C.c_float(value), C.c_float(scale),
+                                                       C.c_float(offset)))
+
+    def dequantize_code(self, code, scale, offset):
+        return float(self._fn("dequantize_code", C.c_float)(C.c_uint(code), C.c_float(scale), C.c_float(offset)))
+
+    # ---- BELL -----------------------------------------------------------
+    def bell_pack(self, bits, policy, rows, cols, block_size, ell_cols, row_stride, block_col_idx, scales,
+                  offsets, values_by_slot):
+        bci = np.ascontiguousarray(block_col_idx, dtype=np.uint32)
+        scales, offsets, vals = _f32(scales), _f32(offsets), _f32(values_by_slot)
+        packed = np.full(rows * row_stride, 0xAA, dtype=np.uint8)
+        rc = self._fn(self._bell_pack_name)(
+            C.c_int(bits), C.c_int(policy), C.c_int64(rows), C.c_int64(cols), C.c_int(block_size),
+            C.c_int64(ell_cols), C.c_int64(row_stride), _p(bci, C.c_uint32), _p(scales, C.c_float),
+            _p(offsets, C.c_float), _p(vals, C.c_float), _p(packed, C.c_uint8))
+        assert rc == 0, rc
+        return packed
+
+    def bell_unpack(self, bits, policy, rows, cols, block_size, ell_cols, row_stride, block_col_idx, scales,
+                    offsets, packed):
+        bci = np.ascontiguousarray(block_col_idx, dtype=np.uint32)
+        scales, offsets = _f32(scales), _f32(offsets)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        out = np.zeros(rows * ell_cols, dtype=np.float32)
+        rc = self._fn(self._bell_unpack_name)(
+            C.c_int(bits), C.c_int(policy), C.c_int64(rows), C.c_int64(cols), C.c_int(block_size),
+            C.c_int64(ell_cols), C.c_int64(row_stride), _p(bci, C.c_uint32), _p(scales, C.c_float),
+            _p(offsets, C.c_float), _p(packed, C.c_uint8), _p(out, C.c_float))
+        assert rc == 0, rc
+        return out.reshape(rows, ell_cols)
+
+    # ---- referee ----------------------------------------------------------
+    def spmm_reference(self, m, k, n, row_offsets, columns, values, rhs, *, transpose_sparse=False,
+                       transpose_dense=False, rhs_col_major=False, rhs_ld=None, alpha=1.0, beta=0.0,
+                       initial=None, initial_col_major=False, initial_ld=0, epilogue="none", bias=None):
+        ro = np.ascontiguousarray(row_offsets, dtype=np.uint64)
+        ci = np.ascontiguousarray(columns, dtype=np.uint32)
+        vals, rhs, initial, bias = _f32(values), _f32(rhs), _f32(initial), _f32(bias)
+        if rhs_ld is None:
+            rr, rc_ = (n, k) if transpose_dense else (k, n)
+            rhs_ld = rr if rhs_col_major else rc_
+        ref = np.zeros(m * n, dtype=np.float64)
+        rc = self._fn("spmm_reference")(
+            C.c_uint64(m), C.c_uint64(k), C.c_uint64(n), C.c_int(int(transpose_sparse)),
+            C.c_int(int(transpose_dense)), C.c_uint64(len(ci)), _p(ro, C.c_uint64), _p(ci, C.c_uint32),
+            _p(vals, C.c_float), _p(rhs, C.c_float), C.c_int(int(rhs_col_major)), C.c_uint64(rhs_ld),
+            C.c_double(alpha), C.c_double(beta), _p(initial, C.c_float), C.c_int(int(initial_col_major)),
+            C.c_uint64(initial_ld), C.c_int(EPILOGUE[epilogue]), _p(bias, C.c_float), _p(ref, C.c_double),
+            C.c_uint64(m * n))
+        if rc != 0:
+            raise RuntimeError(f"spmm_reference status {rc}")
+        return ref.reshape(m, n)
+
+    def digest_f32(self, values):
+        v = _f32(values)
+        out = np.zeros(2, dtype=np.uint64)
+        self._digest(v, out)
+        return int(out[0]), int(out[1])
+
+
+class Oracle(_Base):
+    """The C restatement (oracle.c)."""
+    prefix = "orc_"
+    _bell_pack_name = "bell_pack_row_major"
+    _bell_unpack_name = "bell_unpack_row_major"
+
+    def __init__(self):
+        if not os.path.exists(ORACLE_LIB):
+            build(ref=False)
+        super().__init__(ORACLE_LIB)
+
+    def _digest(self, v, out):
+        self._fn("digest_f32", None)(_p(v, C.c_float), C.c_uint64(v.shape[0]), C.c_uint64(v.shape[1]),
+                                     C.c_uint64(v.shape[1]), C.c_uint32(4), _p(out, C.c_uint64))
+
+    def pack_csr(self, bits, policy, row_ptr, packed_row_ptr, col_idx, scales, offsets, values,
+                 row_begin=0, row_end=None, value_base=0, total_bytes=None):
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        scales, offsets, values = _f32(scales), _f32(offsets), _f32(values)
+        rows = len(row_ptr) - 1
+        row_end = rows if row_end is None else row_end
+        packed = np.zeros(int(prp[-1]) if total_bytes is None else total_bytes, dtype=np.uint8)
+        rc = self._fn("pack_csr_rows")(
+            C.c_int(bits), C.c_int(policy), C.c_int64(row_begin), C.c_int64(row_end), _p(row_ptr, C.c_int64),
+            _p(prp, C.c_int64), _p(col_idx, C.c_int32), _p(scales, C.c_float), _p(offsets, C.c_float),
+            C.c_int64(value_base), _p(values, C.c_float), _p(packed, C.c_uint8))
+        assert rc == 0, rc
+        return packed
+
+    def unpack_csr(self, bits, policy, row_ptr, packed_row_ptr, col_idx, scales, offsets, packed,
+                   row_begin=0, row_end=None, value_base=None):
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        scales, offsets = _f32(scales), _f32(offsets)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        rows = len(row_ptr) - 1
+        row_end = rows if row_end is None else row_end
+        base = int(row_ptr[row_begin]) if value_base is None else value_base
+        out = np.zeros(int(row_ptr[row_end]) - base, dtype=np.float32)
+        rc = self._fn("unpack_csr_rows")(
+            C.c_int(bits), C.c_int(policy), C.c_int64(row_begin), C.c_int64(row_end), _p(row_ptr, C.c_int64),
+            _p(prp, C.c_int64), _p(col_idx, C.c_int32), _p(scales, C.c_float), _p(offsets, C.c_float),
+            _p(packed, C.c_uint8), C.c_int64(base), _p(out, C.c_float))
+        assert rc == 0, rc
+        return out
+
+    def extract_codes(self, bits, row_ptr, packed_row_ptr, packed):
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        out = np.zeros(int(row_ptr[-1]), dtype=np.uint8)
+        rc = self._fn("extract_csr_codes")(C.c_int(bits), C.c_int64(len(row_ptr) - 1), _p(row_ptr, C.c_int64),
+                                           _p(prp, C.c_int64), _p(packed, C.c_uint8), _p(out, C.c_uint8))
+        assert rc == 0, rc
+        return out
+
+    def bell_to_csr(self, bits, policy, rows, cols, block_size, ell_cols, row_stride, block_col_idx, scales,
+                    offsets, packed):
+        bci = np.ascontiguousarray(block_col_idx, dtype=np.uint32)
+        scales, offsets = _f32(scales), _f32(offsets)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        ro = np.zeros(rows + 1, dtype=np.uint64)
+        f = self._fn("bell_to_csr", C.c_int64)
+        args = [C.c_int(bits), C.c_int(policy), C.c_int64(rows), C.c_int64(cols), C.c_int(block_size),
+                C.c_int64(ell_cols), C.c_int64(row_stride), _p(bci, C.c_uint32), _p(scales, C.c_float),
+                _p(offsets, C.c_float), _p(packed, C.c_uint8), _p(ro, C.c_uint64)]
+        count = f(*args, None, None)
+        assert count >= 0
+        cols_out = np.zeros(count, dtype=np.uint32)
+        vals = np.zeros(count, dtype=np.float32)
+        f(*args, _p(cols_out, C.c_uint32), _p(vals, C.c_float))
+        return ro, cols_out, vals
+
+    def _range_call(self, name, bits, policy, row_begin, row_end, cols, n, row_ptr, packed_row_ptr, col_idx,
+                    packed, scales, offsets, dense, out_rows):
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        scales, offsets, dense = _f32(scales), _f32(offsets), _f32(dense)
+        nnz = int(row_ptr[row_end] - row_ptr[row_begin])
+        sv = np.zeros(max(nnz, 1), dtype=np.float32)
+        so = np.zeros(row_end - row_begin + 1, dtype=np.uint64)
+        ref = np.zeros(out_rows * n, dtype=np.float64)
+        rc = self._fn(name)(
+            C.c_int(bits), C.c_int(policy), C.c_int64(row_begin), C.c_int64(row_end), C.c_int64(cols),
+            C.c_int64(n), _p(row_ptr, C.c_int64), _p(prp, C.c_int64), _p(col_idx, C.c_int32),
+            _p(packed, C.c_uint8), _p(scales, C.c_float), _p(offsets, C.c_float), _p(dense, C.c_float),
+            C.c_int64(dense.shape[1]), _p(sv, C.c_float), _p(so, C.c_uint64), _p(ref, C.c_double))
+        if rc != 0:
+            raise RuntimeError(f"{name} status {rc}")
+        return ref.reshape(out_rows, n)
+
+    def qcsr_forward(self, bits, policy, row_ptr, packed_row_ptr, col_idx, packed, scales, offsets, w,
+                     cols, row_begin=0, row_end=None):
+        """decode + referee over rows [row_begin, row_end): Y rows as float64."""
+        row_end = len(row_ptr) - 1 if row_end is None else row_end
+        return self._range_call("qcsr_forward_rows", bits, policy, row_begin, row_end, cols, w.shape[1],
+                                row_ptr, packed_row_ptr, col_idx, packed, scales, offsets, w,
+                                row_end - row_begin)
+
+    def qcsr_transpose(self, bits, policy, row_ptr, packed_row_ptr, col_idx, packed, scales, offsets, g,
+                       cols, row_begin=0, row_end=None):
+        """decode + transposed referee over rows [row_begin, row_end): partial G' (cols x n) as float64."""
+        row_end = len(row_ptr) - 1 if row_end is None else row_end
+        return self._range_call("qcsr_transpose_rows", bits, policy, row_begin, row_end, cols, g.shape[1],
+                                row_ptr, packed_row_ptr, col_idx, packed, scales, offsets, g, cols)
+
+    def compare(self, reference, candidate, tol_abs=0.0, tol_rel=0.0, rel_floor=1e-30):
+        ref = np.ascontiguousarray(reference, dtype=np.float64).ravel()
+        cand = _f32(candidate).ravel()
+        out = np.zeros(8, dtype=np.float64)
+        rc = self._fn("compare")(_p(ref, C.c_double), _p(cand, C.c_float), C.c_uint64(ref.size),
+                                 C.c_double(tol_abs), C.c_double(tol_rel), C.c_double(rel_floor),
+                                 _p(out, C.c_double))
+        keys = ("max_abs", "max_rel", "mean_abs", "rmse", "mismatch_count", "worst_index", "nonfinite_ref",
+                "nonfinite_cand")
+        d = dict(zip(keys, out.tolist()))
+        d["status"] = rc
+        return d
+
+
+class Reference(_Base):
+    """The reference's own sources (ref_shim.cc); whole-matrix calls only."""
+    prefix = "ref_"
+    _bell_pack_name = "bell_pack"
+    _bell_unpack_name = "bell_unpack"
+
+    def __init__(self):
+        super().__init__(REF_LIB)
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_LIB)
+
+    def _digest(self, v, out):
+        self._fn("digest_f32", None)(_p(v, C.c_float), C.c_uint64(v.shape[0]), C.c_uint64(v.shape[1]),
+                                     C.c_uint64(v.shape[1]), _p(out, C.c_uint64))
+
+    def pack_csr(self, bits, policy, row_ptr, packed_row_ptr, col_idx, scales, offsets, values, cols=None):
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        scales, offsets, values = _f32(scales), _f32(offsets), _f32(values)
+        cols = int(col_idx.max()) + 1 if cols is None else cols
+        packed = np.zeros(int(prp[-1]), dtype=np.uint8)
+        rc = self._fn("pack_csr")(
+            C.c_int(bits), C.c_int(policy), C.c_int64(len(row_ptr) - 1), C.c_int64(cols), _p(row_ptr, C.c_int64),
+            _p(prp, C.c_int64), _p(col_idx, C.c_int32), _p(scales, C.c_float), _p(offsets, C.c_float),
+            _p(values, C.c_float), _p(packed, C.c_uint8))
+        assert rc == 0, rc
+        return packed
+
+    def unpack_csr(self, bits, policy, row_ptr, packed_row_ptr, col_idx, scales, offsets, packed, cols=None):
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        scales, offsets = _f32(scales), _f32(offsets)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        cols = int(col_idx.max()) + 1 if cols is None else cols
+        out = np.zeros(int(row_ptr[-1]), dtype=np.float32)
+        rc = self._fn("unpack_csr")(
+            C.c_int(bits), C.c_int(policy), C.c_int64(len(row_ptr) - 1), C.c_int64(cols), _p(row_ptr, C.c_int64),
+            _p(prp, C.c_int64), _p(col_idx, C.c_int32), _p(scales, C.c_float), _p(offsets, C.c_float),
+            _p(packed, C.c_uint8), _p(out, C.c_float))
+        assert rc == 0, rc
+        return out

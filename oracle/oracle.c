@@ -1,0 +1,532 @@
+/*
+ * CPU oracle for the quantized sparse-matrix path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file restates, in plain C, the algorithms of the Cellerator reference
+ * for: the quantized CSR codec, the uniform row partition, the quantized
+ * Blocked-ELL codec, and the double-precision SpMM referee.  It exists so that
+ * the CUDA kernels of this repository can be checked against something that
+ * does not share any code with them.  Only the test-suite, the smoke check and
+ * the CPU-baseline leg of the benchmark may call it; no product code path may
+ * link or load it.
+ *
+ * Pinning: every function here is compared, on random and hand-written inputs,
+ * with the reference's own sources compiled in place (see build_ref.sh and
+ * ref_shim.cc) and with the known-answer vectors that the reference's tests
+ * hold (tests/golden/).  Each function cites the reference file:line whose
+ * behaviour it follows (paths are relative to the Cellerator project root).
+ *
+ * Index widths: row pointers are int64 and column indices int32 (the widths of
+ * the referee's logical CSR view widened to signed), instead of the `int`
+ * fields of quantized/layout.cuh; the arithmetic is otherwise the same.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+enum { ORC_POLICY_PER_GENE_AFFINE = 1, ORC_POLICY_COLUMN_SCALE_ROW_OFFSET = 2 };
+
+/* ------------------------------------------------------------------------ */
+/* format: include/Cellerator/quantized/format.cuh:14-55                    */
+
+static int orc_valid_bits(int bits) { return bits == 1 || bits == 2 || bits == 4 || bits == 8; }
+
+/* format.cuh:25-27  bytes of one packed row = ceil(nnz / codes_per_byte) */
+ORC_API int64_t orc_row_bytes(int bits, int64_t row_nnz) {
+    const int64_t cpb = 8 / bits;
+    return row_nnz <= 0 ? 0 : (row_nnz + cpb - 1) / cpb;
+}
+
+/* format.cuh:29-37  row bytes rounded up to `alignment` (BELL row stride) */
+ORC_API int64_t orc_aligned_row_bytes(int bits, int64_t row_nnz, int64_t alignment) {
+    const int64_t bytes = orc_row_bytes(bits, row_nnz);
+    return alignment <= 1 ? bytes : ((bytes + alignment - 1) / alignment) * alignment;
+}
+
+/* format.cuh:39-48  code i lives in byte i / cpb at bit shift (i mod cpb) * bits */
+static unsigned orc_unpack_code(int bits, const uint8_t *packed, int64_t local_index) {
+    const int64_t cpb = 8 / bits;
+    const int64_t slot = local_index / cpb;
+    const int lane = (int)(local_index & (cpb - 1));
+    return ((unsigned)packed[slot] >> (lane * bits)) & ((1u << bits) - 1u);
+}
+
+/* ------------------------------------------------------------------------ */
+/* layout: include/Cellerator/quantized/layout.cuh:106-157                  */
+
+/* layout.cuh:111-129  exclusive prefix sum of row_bytes; returns total or -1 */
+ORC_API int64_t orc_build_packed_row_ptr(int bits, const int64_t *row_ptr, int64_t rows,
+                                         int64_t *packed_row_ptr) {
+    if (row_ptr == NULL || packed_row_ptr == NULL || rows < 0 || !orc_valid_bits(bits)) return -1;
+    packed_row_ptr[0] = 0;
+    for (int64_t r = 0; r < rows; ++r)
+        packed_row_ptr[r + 1] = packed_row_ptr[r] + orc_row_bytes(bits, row_ptr[r + 1] - row_ptr[r]);
+    return packed_row_ptr[rows];
+}
+
+/* layout.cuh:131-136 */
+ORC_API int64_t orc_block_count_for_rows(int64_t rows, int64_t rows_per_block) {
+    if (rows <= 0 || rows_per_block <= 0) return 0;
+    return (rows + rows_per_block - 1) / rows_per_block;
+}
+
+/* layout.cuh:138-157  block b starts at min(b * rows_per_block, rows) */
+ORC_API int64_t orc_build_uniform_block_row_ptr(int64_t rows, int64_t rows_per_block,
+                                                int64_t *block_row_ptr) {
+    const int64_t count = orc_block_count_for_rows(rows, rows_per_block);
+    if (block_row_ptr == NULL || rows < 0 || rows_per_block <= 0) return -1;
+    int64_t row = 0;
+    for (int64_t b = 0; b < count; ++b) {
+        block_row_ptr[b] = row;
+        row += rows_per_block;
+        if (row > rows) row = rows;
+    }
+    block_row_ptr[count] = rows;
+    return count;
+}
+
+/* access.cuh:7-44  out = {block_index,row_begin,row_end,nnz_begin,nnz_end,packed_begin,packed_end};
+ * no block metadata -> one block over the matrix; out-of-range index -> all-zero block. */
+ORC_API void orc_get_block(int64_t rows, const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                           const int64_t *block_row_ptr, int64_t block_count, int64_t block_index,
+                           int64_t out[7]) {
+    out[0] = block_index;
+    for (int i = 1; i < 7; ++i) out[i] = 0;
+    if (row_ptr == NULL || packed_row_ptr == NULL) return;
+    if (block_row_ptr == NULL || block_count <= 0) {
+        out[0] = 0;
+        out[1] = 0;
+        out[2] = rows;
+    } else {
+        if (block_index < 0 || block_index >= block_count) return;
+        out[1] = block_row_ptr[block_index];
+        out[2] = block_row_ptr[block_index + 1];
+    }
+    out[3] = row_ptr[out[1]];
+    out[4] = row_ptr[out[2]];
+    out[5] = packed_row_ptr[out[1]];
+    out[6] = packed_row_ptr[out[2]];
+}
+
+/* ------------------------------------------------------------------------ */
+/* code <-> value: include/Cellerator/quantized/access.cuh:81-131           */
+
+/* access.cuh:104-131  scale==0 -> 0; true division; round half away from zero; clamp */
+ORC_API unsigned orc_quantize_code(int bits, float value, float scale, float offset) {
+    const int max_code = (1 << bits) - 1;
+    const float centered = value - offset;
+    if (scale == 0.0f) return 0u;
+    const float q = centered / scale;
+    int rounded = q >= 0.0f ? (int)(q + 0.5f) : (int)(q - 0.5f);
+    if (rounded < 0) return 0u;
+    if (rounded > max_code) rounded = max_code;
+    return (unsigned)rounded;
+}
+
+/* access.cuh:81-91 with numeric.cuh:34-36: float(code) * scale + offset, written as a
+ * product then a sum.  Kept unfused here (volatile) so the result does not depend on
+ * whether this file is built with FMA contraction; a fused device build may differ by
+ * one ulp, the integer code never does. */
+ORC_API float orc_dequantize_code(unsigned code, float scale, float offset) {
+    volatile float product = (float)code * scale;
+    return product + offset;
+}
+
+/* metadata.cuh:17-27,42-55  null scale array -> 1, null offset array -> 0; the row policy
+ * reads its offset from row_offsets[row] */
+static float orc_scale_for(const float *scales, int64_t column) {
+    return scales != NULL ? scales[column] : 1.0f;
+}
+static float orc_offset_for(int policy, const float *offsets, int64_t row, int64_t column) {
+    if (offsets == NULL) return 0.0f;
+    return policy == ORC_POLICY_COLUMN_SCALE_ROW_OFFSET ? offsets[row] : offsets[column];
+}
+
+/* ------------------------------------------------------------------------ */
+/* CSR pack / unpack: include/Cellerator/quantized/packing.cuh:13-328       */
+
+/* packing.cuh:13-146,262-277  The reference's 8-bit path peels a head, writes 16 codes at a
+ * time, then 4, then a tail; all of those store code i of the row at byte i, so the layout
+ * is the single loop below.  Sub-byte rows fill each byte low lane first and leave the
+ * lanes past the row end at 0.  `value_base` is the nnz index of values[0] (packing.cuh:17-18). */
+ORC_API int orc_pack_csr_rows(int bits, int policy, int64_t row_begin, int64_t row_end,
+                              const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                              const int32_t *col_idx, const float *scales, const float *offsets,
+                              int64_t value_base, const float *values, uint8_t *packed_values) {
+    if (!orc_valid_bits(bits) || row_ptr == NULL || packed_row_ptr == NULL || packed_values == NULL ||
+        values == NULL)
+        return -1;
+    const int cpb = 8 / bits;
+    const unsigned mask = (1u << bits) - 1u;
+    for (int64_t row = row_begin; row < row_end; ++row) {
+        int64_t index = row_ptr[row];
+        const int64_t end = row_ptr[row + 1];
+        uint8_t *out = packed_values + packed_row_ptr[row];
+        while (index < end) {
+            unsigned packed_byte = 0u;
+            for (int lane = 0; lane < cpb; ++lane) {
+                const int64_t current = index + lane;
+                if (current < end) {
+                    const int64_t column = col_idx[current];
+                    const unsigned code = orc_quantize_code(
+                        bits, values[current - value_base], orc_scale_for(scales, column),
+                        orc_offset_for(policy, offsets, row, column));
+                    packed_byte |= (code & mask) << (lane * bits);
+                }
+            }
+            *out++ = (uint8_t)(packed_byte & 0xffu);
+            index += cpb;
+        }
+    }
+    return 0;
+}
+
+/* packing.cuh:148-260,279-292 */
+ORC_API int orc_unpack_csr_rows(int bits, int policy, int64_t row_begin, int64_t row_end,
+                                const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                                const int32_t *col_idx, const float *scales, const float *offsets,
+                                const uint8_t *packed_values, int64_t value_base, float *values) {
+    if (!orc_valid_bits(bits) || row_ptr == NULL || packed_row_ptr == NULL || values == NULL) return -1;
+    for (int64_t row = row_begin; row < row_end; ++row) {
+        const int64_t begin = row_ptr[row];
+        const int64_t end = row_ptr[row + 1];
+        const uint8_t *in = packed_values + packed_row_ptr[row];
+        for (int64_t index = begin; index < end; ++index) {
+            const int64_t column = col_idx[index];
+            const unsigned code = orc_unpack_code(bits, in, index - begin);
+            values[index - value_base] = orc_dequantize_code(
+                code, orc_scale_for(scales, column), orc_offset_for(policy, offsets, row, column));
+        }
+    }
+    return 0;
+}
+
+/* The integer half of unpack on its own: codes[i] for every nnz (format.cuh:39-48). */
+ORC_API int orc_extract_csr_codes(int bits, int64_t rows, const int64_t *row_ptr,
+                                  const int64_t *packed_row_ptr, const uint8_t *packed_values,
+                                  uint8_t *codes) {
+    if (!orc_valid_bits(bits) || row_ptr == NULL || packed_row_ptr == NULL || codes == NULL) return -1;
+    for (int64_t row = 0; row < rows; ++row) {
+        const int64_t begin = row_ptr[row];
+        const int64_t end = row_ptr[row + 1];
+        for (int64_t index = begin; index < end; ++index)
+            codes[index] = (uint8_t)orc_unpack_code(bits, packed_values + packed_row_ptr[row], index - begin);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* Quantized Blocked-ELL: include/Cellerator/quantized/blocked_ell.cuh:99-231 */
+
+#define ORC_INVALID_BLOCK_COL 0xffffffffu
+
+/* blocked_ell.cuh:120-137  slot s of row r -> gene block_col_idx[(r/bs)*width + s/bs]*bs + s%bs,
+ * -1 for an empty block or an out-of-range argument */
+ORC_API int64_t orc_bell_column_for_slot(int64_t rows, int block_size, int64_t ell_cols,
+                                         const uint32_t *block_col_idx, int64_t row, int64_t slot) {
+    if (block_col_idx == NULL || row < 0 || row >= rows || slot < 0 || slot >= ell_cols || block_size <= 0)
+        return -1;
+    const int64_t width = ell_cols / block_size;
+    const uint32_t block_col = block_col_idx[(row / block_size) * width + slot / block_size];
+    if (block_col == ORC_INVALID_BLOCK_COL) return -1;
+    return (int64_t)block_col * block_size + slot % block_size;
+}
+
+/* blocked_ell.cuh:165-213  every slot is quantized (an empty block uses column 0's
+ * scale/offset); row padding bytes are 0 */
+ORC_API int orc_bell_pack_row_major(int bits, int policy, int64_t rows, int64_t cols, int block_size,
+                                    int64_t ell_cols, int64_t row_stride_bytes,
+                                    const uint32_t *block_col_idx, const float *scales,
+                                    const float *offsets, const float *values_by_slot,
+                                    uint8_t *packed_values) {
+    (void)cols;
+    if (!orc_valid_bits(bits) || values_by_slot == NULL || packed_values == NULL || rows < 0 || ell_cols < 0 ||
+        row_stride_bytes < orc_row_bytes(bits, ell_cols))
+        return -1;
+    const int cpb = 8 / bits;
+    const unsigned mask = (1u << bits) - 1u;
+    for (int64_t row = 0; row < rows; ++row) {
+        uint8_t *out = packed_values + row * row_stride_bytes;
+        int64_t out_byte = 0;
+        for (int64_t slot = 0; slot < ell_cols; slot += cpb) {
+            unsigned packed = 0u;
+            for (int lane = 0; lane < cpb; ++lane) {
+                const int64_t current = slot + lane;
+                if (current < ell_cols) {
+                    const int64_t column =
+                        orc_bell_column_for_slot(rows, block_size, ell_cols, block_col_idx, row, current);
+                    const int64_t safe_column = column >= 0 ? column : 0;
+                    const unsigned code = orc_quantize_code(
+                        bits, values_by_slot[row * ell_cols + current], orc_scale_for(scales, safe_column),
+                        orc_offset_for(policy, offsets, row, safe_column));
+                    packed |= (code & mask) << (lane * bits);
+                }
+            }
+            out[out_byte++] = (uint8_t)(packed & 0xffu);
+        }
+        while (out_byte < row_stride_bytes) out[out_byte++] = 0u;
+    }
+    return 0;
+}
+
+/* blocked_ell.cuh:139-163,215-231  a slot of an empty block, or one whose gene is >= cols,
+ * decodes to exactly 0 */
+ORC_API int orc_bell_unpack_row_major(int bits, int policy, int64_t rows, int64_t cols, int block_size,
+                                      int64_t ell_cols, int64_t row_stride_bytes,
+                                      const uint32_t *block_col_idx, const float *scales,
+                                      const float *offsets, const uint8_t *packed_values,
+                                      float *values_by_slot) {
+    if (!orc_valid_bits(bits) || values_by_slot == NULL || packed_values == NULL || rows < 0 || ell_cols < 0)
+        return -1;
+    for (int64_t row = 0; row < rows; ++row) {
+        const uint8_t *in = packed_values + row * row_stride_bytes;
+        for (int64_t slot = 0; slot < ell_cols; ++slot) {
+            const int64_t column = orc_bell_column_for_slot(rows, block_size, ell_cols, block_col_idx, row, slot);
+            float v = 0.0f;
+            if (column >= 0 && column < cols)
+                v = orc_dequantize_code(orc_unpack_code(bits, in, slot), orc_scale_for(scales, column),
+                                        orc_offset_for(policy, offsets, row, column));
+            values_by_slot[row * ell_cols + slot] = v;
+        }
+    }
+    return 0;
+}
+
+/* The slots that the reference's fused kernel multiplies
+ * (src/compute/sparse/project/kernels/quantized_blocked_ell_spmm_fwd_kernel_.cuh:18-37): every
+ * slot of a present block whose gene is < cols, structurally empty slots included.  Emits them
+ * as a CSR (row_offsets uint64, columns uint32, values float) for the referee below.
+ * Returns the number of entries, or -1.  Pass columns/values NULL to count only. */
+ORC_API int64_t orc_bell_to_csr(int bits, int policy, int64_t rows, int64_t cols, int block_size,
+                                int64_t ell_cols, int64_t row_stride_bytes, const uint32_t *block_col_idx,
+                                const float *scales, const float *offsets, const uint8_t *packed_values,
+                                uint64_t *row_offsets, uint32_t *columns, float *values) {
+    if (!orc_valid_bits(bits) || block_col_idx == NULL || packed_values == NULL || row_offsets == NULL ||
+        block_size <= 0)
+        return -1;
+    const int64_t width = ell_cols / block_size;
+    uint64_t count = 0;
+    row_offsets[0] = 0;
+    for (int64_t row = 0; row < rows; ++row) {
+        const uint8_t *in = packed_values + row * row_stride_bytes;
+        for (int64_t sb = 0; sb < width; ++sb) {
+            const uint32_t block_col = block_col_idx[(row / block_size) * width + sb];
+            if (block_col == ORC_INVALID_BLOCK_COL) continue;
+            for (int c = 0; c < block_size; ++c) {
+                const int64_t gene = (int64_t)block_col * block_size + c;
+                if (gene >= cols) break;
+                if (columns != NULL && values != NULL) {
+                    columns[count] = (uint32_t)gene;
+                    values[count] = orc_dequantize_code(orc_unpack_code(bits, in, sb * block_size + c),
+                                                        orc_scale_for(scales, gene),
+                                                        orc_offset_for(policy, offsets, row, gene));
+                }
+                ++count;
+            }
+        }
+        row_offsets[row + 1] = count;
+    }
+    return (int64_t)count;
+}
+
+/* ------------------------------------------------------------------------ */
+/* SpMM referee: src/compute/math/referee.cc:101-253                        */
+
+enum {
+    ORC_EPI_NONE = 0, ORC_EPI_BIAS = 1, ORC_EPI_RELU = 2, ORC_EPI_GELU_ERF = 3, ORC_EPI_GELU_TANH = 4,
+    ORC_EPI_BIAS_RELU = 5, ORC_EPI_BIAS_GELU_ERF = 6, ORC_EPI_BIAS_GELU_TANH = 7
+};
+
+static int orc_bias_epilogue(int kind) {
+    return kind == ORC_EPI_BIAS || kind == ORC_EPI_BIAS_RELU || kind == ORC_EPI_BIAS_GELU_ERF ||
+           kind == ORC_EPI_BIAS_GELU_TANH;
+}
+
+/* referee.cc:81-97 */
+static double orc_apply_epilogue(double value, double bias, int kind) {
+    if (orc_bias_epilogue(kind)) value += bias;
+    if (kind == ORC_EPI_RELU || kind == ORC_EPI_BIAS_RELU) return fmax(value, 0.0);
+    if (kind == ORC_EPI_GELU_ERF || kind == ORC_EPI_BIAS_GELU_ERF)
+        return 0.5 * value * (1.0 + erf(value * 0.7071067811865475244));
+    if (kind == ORC_EPI_GELU_TANH || kind == ORC_EPI_BIAS_GELU_TANH)
+        return 0.5 * value * (1.0 + tanh(0.7978845608028653559 * (value + 0.044715 * value * value * value)));
+    return value;
+}
+
+/* referee.cc:57-61  row-major: r*ld + c, column-major: c*ld + r */
+static uint64_t orc_dense_index(int col_major, uint64_t ld, uint64_t r, uint64_t c) {
+    return col_major ? c * ld + r : r * ld + c;
+}
+
+/*
+ * referee.cc:101-253, for fp32 sparse values, fp32 dense operand and fp32 initial output.
+ *   m,k,n         logical dims after the declared transposes (operation.hh:132-134)
+ *   transpose_sparse  0: stored CSR is m x k;  1: stored CSR is k x m and Xt is applied
+ *   transpose_dense   0: rhs is k x n;         1: rhs is n x k
+ *   reference     m*n doubles, row-major
+ * The accumulation order (stored row, entry, output column) and the product order
+ * alpha * a * b, all in double, are the reference's.  Returns 0, or the referee_status_code
+ * (referee.hh:16-27) of the first check that fails.
+ */
+ORC_API int orc_spmm_reference(uint64_t m, uint64_t k, uint64_t n, int transpose_sparse, int transpose_dense,
+                               uint64_t sparse_nnz, const uint64_t *row_offsets, const uint32_t *column_indices,
+                               const float *sparse_values, const float *rhs, int rhs_col_major, uint64_t rhs_ld,
+                               double alpha, double beta, const float *initial, int initial_col_major,
+                               uint64_t initial_ld, int epilogue, const float *bias, double *reference,
+                               uint64_t reference_capacity) {
+    const uint64_t out_count = m * n;
+    if (out_count > reference_capacity || (out_count != 0 && reference == NULL)) return 4;
+    const uint64_t sparse_rows = transpose_sparse ? k : m;
+    const uint64_t sparse_cols = transpose_sparse ? m : k;
+    if ((sparse_rows != 0 && row_offsets == NULL) ||
+        (sparse_nnz != 0 && (column_indices == NULL || sparse_values == NULL)))
+        return 2;
+    if (sparse_rows != 0 && (row_offsets[0] != 0 || row_offsets[sparse_rows] != sparse_nnz)) return 2;
+    if (beta != 0.0 && initial == NULL) return 2;
+    if (orc_bias_epilogue(epilogue) && bias == NULL) return 1;
+
+    for (uint64_t r = 0; r < m; ++r)
+        for (uint64_t c = 0; c < n; ++c) {
+            double init = 0.0;
+            if (beta != 0.0) init = (double)initial[orc_dense_index(initial_col_major, initial_ld, r, c)];
+            reference[r * n + c] = beta * init;
+        }
+
+    for (uint64_t prow = 0; prow < sparse_rows; ++prow) {
+        const uint64_t begin = row_offsets[prow];
+        const uint64_t end = row_offsets[prow + 1];
+        if (begin > end || end > sparse_nnz) return 2;
+        for (uint64_t e = begin; e < end; ++e) {
+            const uint64_t pcol = column_indices[e];
+            if (pcol >= sparse_cols) return 2;
+            const uint64_t out_row = transpose_sparse ? pcol : prow;
+            const uint64_t reduction = transpose_sparse ? prow : pcol;
+            const double a = (double)sparse_values[e];
+            for (uint64_t c = 0; c < n; ++c) {
+                const uint64_t rr = transpose_dense ? c : reduction;
+                const uint64_t rc = transpose_dense ? reduction : c;
+                const double b = (double)rhs[orc_dense_index(rhs_col_major, rhs_ld, rr, rc)];
+                reference[out_row * n + c] += alpha * a * b;
+            }
+        }
+    }
+
+    for (uint64_t r = 0; r < m; ++r)
+        for (uint64_t c = 0; c < n; ++c) {
+            const double b = orc_bias_epilogue(epilogue) ? (double)bias[c] : 0.0;
+            double *v = &reference[r * n + c];
+            *v = orc_apply_epilogue(*v, b, epilogue);
+            if (!isfinite(*v)) return 5;
+        }
+    return 0;
+}
+
+/*
+ * The composed CPU path that BASELINE times: decode (packing.cuh:279-292) then the referee,
+ * forward only, on the row range [row_begin, row_end) of a quantized CSR with int64 row
+ * pointers.  Offsets are rebased so the referee sees row_offsets[0] == 0
+ * (referee.cc:143-148).  `scratch_values` holds the decoded floats (nnz of the range),
+ * `scratch_offsets` row_end-row_begin+1 uint64.  Y rows land in `reference` (double).
+ */
+ORC_API int orc_qcsr_forward_rows(int bits, int policy, int64_t row_begin, int64_t row_end, int64_t cols,
+                                  int64_t n, const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                                  const int32_t *col_idx, const uint8_t *packed_values, const float *scales,
+                                  const float *offsets, const float *w, int64_t w_ld, float *scratch_values,
+                                  uint64_t *scratch_offsets, double *reference) {
+    const int64_t rows = row_end - row_begin;
+    const int64_t base = row_ptr[row_begin];
+    int rc = orc_unpack_csr_rows(bits, policy, row_begin, row_end, row_ptr, packed_row_ptr, col_idx, scales,
+                                 offsets, packed_values, base, scratch_values);
+    if (rc != 0) return rc;
+    for (int64_t r = 0; r <= rows; ++r) scratch_offsets[r] = (uint64_t)(row_ptr[row_begin + r] - base);
+    return orc_spmm_reference((uint64_t)rows, (uint64_t)cols, (uint64_t)n, 0, 0, scratch_offsets[rows],
+                              scratch_offsets, (const uint32_t *)(col_idx + base), scratch_values, w, 0,
+                              (uint64_t)w_ld, 1.0, 0.0, NULL, 0, 0, ORC_EPI_NONE, NULL, reference,
+                              (uint64_t)(rows * n));
+}
+
+/* Same for the gene-side transpose G' = deq(X)^T G over a row range: `reference` is cols*n
+ * doubles and receives this range's partial sum (transpose_sparse, referee.cc:130-133,207-210). */
+ORC_API int orc_qcsr_transpose_rows(int bits, int policy, int64_t row_begin, int64_t row_end, int64_t cols,
+                                    int64_t n, const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                                    const int32_t *col_idx, const uint8_t *packed_values, const float *scales,
+                                    const float *offsets, const float *g, int64_t g_ld, float *scratch_values,
+                                    uint64_t *scratch_offsets, double *reference) {
+    const int64_t rows = row_end - row_begin;
+    const int64_t base = row_ptr[row_begin];
+    int rc = orc_unpack_csr_rows(bits, policy, row_begin, row_end, row_ptr, packed_row_ptr, col_idx, scales,
+                                 offsets, packed_values, base, scratch_values);
+    if (rc != 0) return rc;
+    for (int64_t r = 0; r <= rows; ++r) scratch_offsets[r] = (uint64_t)(row_ptr[row_begin + r] - base);
+    /* stored CSR is rows x cols = k x m with m = cols, k = rows */
+    return orc_spmm_reference((uint64_t)cols, (uint64_t)rows, (uint64_t)n, 1, 0, scratch_offsets[rows],
+                              scratch_offsets, (const uint32_t *)(col_idx + base), scratch_values,
+                              g + row_begin * g_ld, 0, (uint64_t)g_ld, 1.0, 0.0, NULL, 0, 0, ORC_EPI_NONE, NULL,
+                              reference, (uint64_t)(cols * n));
+}
+
+/* ------------------------------------------------------------------------ */
+/* comparison: include/Cellerator/compute/math/referee.hh:143-217           */
+
+/* out = {max_abs, max_rel, mean_abs, rmse, mismatch_count, worst_index, nonfinite_ref, nonfinite_cand} */
+ORC_API int orc_compare(const double *reference, const float *candidate, uint64_t count, double tol_abs,
+                        double tol_rel, double rel_floor, double out[8]) {
+    if ((count != 0 && (reference == NULL || candidate == NULL)) || tol_abs < 0.0 || tol_rel < 0.0 ||
+        rel_floor <= 0.0)
+        return 1;
+    long double abs_sum = 0.0L, sq_sum = 0.0L;
+    double max_abs = 0.0, max_rel = 0.0;
+    uint64_t mismatch = 0, worst = 0, nf_ref = 0, nf_cand = 0;
+    for (uint64_t i = 0; i < count; ++i) {
+        const double expected = reference[i];
+        const double actual = (double)candidate[i];
+        if (!isfinite(expected)) { ++nf_ref; continue; }
+        if (!isfinite(actual)) { ++nf_cand; continue; }
+        const double a = fabs(actual - expected);
+        const double r = a / fmax(fabs(expected), rel_floor);
+        abs_sum += a;
+        sq_sum += (long double)a * a;
+        if (a > max_abs) { max_abs = a; worst = i; }
+        max_rel = fmax(max_rel, r);
+        if (a > tol_abs + tol_rel * fabs(expected)) ++mismatch;
+    }
+    out[0] = max_abs;
+    out[1] = max_rel;
+    out[2] = count ? (double)(abs_sum / count) : 0.0;
+    out[3] = count ? sqrt((double)(sq_sum / count)) : 0.0;
+    out[4] = (double)mismatch;
+    out[5] = (double)worst;
+    out[6] = (double)nf_ref;
+    out[7] = (double)nf_cand;
+    return nf_ref ? 5 : (nf_cand ? 6 : 0);
+}
+
+/* referee.hh:219-244 with :125-130  determinism digest of a row-major fp32 matrix:
+ * FNV-style low word, boost-style high word, over rows, columns, type code, then the bit
+ * pattern of every value widened to double. */
+ORC_API void orc_digest_f32(const float *values, uint64_t rows, uint64_t columns, uint64_t ld,
+                            uint32_t type_code, uint64_t out[2]) {
+    uint64_t low = 1469598103934665603ull, high = 0x6a09e667f3bcc909ull;
+#define ORC_MIX(v)                                                                  \
+    do {                                                                            \
+        const uint64_t x_ = (v);                                                    \
+        low ^= x_;                                                                  \
+        low *= 1099511628211ull;                                                    \
+        high ^= x_ + 0x9e3779b97f4a7c15ull + (high << 6) + (high >> 2);             \
+    } while (0)
+    ORC_MIX(rows);
+    ORC_MIX(columns);
+    ORC_MIX((uint64_t)type_code);
+    for (uint64_t r = 0; r < rows; ++r)
+        for (uint64_t c = 0; c < columns; ++c) {
+            const double d = (double)values[r * ld + c];
+            uint64_t bits;
+            memcpy(&bits, &d, sizeof bits);
+            ORC_MIX(bits);
+        }
+#undef ORC_MIX
+    out[0] = low;
+    out[1] = high;
+}
