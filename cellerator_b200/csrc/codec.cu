@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(256) bell_quantize_kernel(const bell_codec_par
                 const int slot = static_cast<int>(byte) * CPB + slot_in;
                 if (slot < p.ell_cols) {
                     const std::int64_t gene = bell_gene(p, row_block, slot);
-                    const std::int64_t safe = gene >= 0 ? gene : 0;
+                    const std::int64_t safe = (gene >= 0 && gene < p.cols) ? gene : 0; // never index past cols
                     const float scale = p.scales != nullptr ? __ldg(p.scales + safe) : 1.0f;
                     const float offset = row_policy ? row_offset : (p.offsets != nullptr ? __ldg(p.offsets + safe) : 0.0f);
                     packed |= quantize_one<BITS>(in[slot], scale, offset) << (slot_in * BITS);

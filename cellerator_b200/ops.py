@@ -305,3 +305,95 @@ def bell_forward(x: QuantizedBell, w: torch.Tensor, out: torch.Tensor | None = N
     op.run(x, w, out, alpha=alpha, beta=beta)
     op.close()
     return out
+
+
+# ---- host-buffer entry: what a caller with the matrix in host memory runs -------------------
+
+@dataclass
+class HostCsr:
+    """Pinned host copy of a quantized CSR (same arrays as QuantizedCsr)."""
+    rows: int
+    cols: int
+    bits: int
+    policy: int
+    row_ptr: torch.Tensor
+    col_idx: torch.Tensor
+    packed: torch.Tensor
+    scales: torch.Tensor | None
+    offsets: torch.Tensor | None
+    packed_row_ptr: torch.Tensor | None
+
+    @staticmethod
+    def from_device(x: QuantizedCsr) -> "HostCsr":
+        def pin(t):
+            if t is None:
+                return None
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            h.copy_(t)
+            return h
+        return HostCsr(x.rows, x.cols, x.bits, x.policy, pin(x.row_ptr), pin(x.col_idx), pin(x.packed), pin(x.scales),
+                       pin(x.offsets), pin(x.packed_row_ptr))
+
+
+class HostForward:
+    """Y_host = deq(X_host) W_host with every byte crossing PCIe inside the call: the row range is
+    cut into chunks; chunk i+1 is copied to the device while chunk i is multiplied and chunk
+    i-1's rows of Y are copied back.  Device buffers are the ones of `x` / `dense` / `out`, which
+    the call overwrites."""
+
+    def __init__(self, op: PreparedSpmm, x: QuantizedCsr, dense: torch.Tensor, out: torch.Tensor, host: HostCsr,
+                 w_host: torch.Tensor, y_host: torch.Tensor, chunks: int = 16):
+        self.op, self.x, self.dense, self.out = op, x, dense, out
+        self.host, self.w_host, self.y_host = host, w_host, y_host
+        dev = x.device
+        self.compute = torch.cuda.current_stream(dev)
+        self.h2d = torch.cuda.Stream(device=dev)
+        self.d2h = torch.cuda.Stream(device=dev)
+        rp = host.row_ptr.numpy()
+        prp = None if host.packed_row_ptr is None else host.packed_row_ptr.numpy()
+        bounds = np.linspace(0, x.rows, max(1, chunks) + 1).astype(np.int64)
+        self.parts = []
+        for i in range(len(bounds) - 1):
+            r0, r1 = int(bounds[i]), int(bounds[i + 1])
+            if r0 == r1:
+                continue
+            n0, n1 = int(rp[r0]), int(rp[r1])
+            p0, p1 = (n0, n1) if prp is None else (int(prp[r0]), int(prp[r1]))
+            launch = op.make_launch(x, dense, out, row_begin=r0, row_end=r1, stream=self.compute.cuda_stream)
+            self.parts.append((r0, r1, n0, n1, p0, p1, launch))
+        small = [host.row_ptr, host.scales, host.offsets, host.packed_row_ptr, w_host]
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in small if t is not None) \
+            + host.col_idx.numel() * 4 + host.packed.numel()
+        self.d2h_bytes = y_host.numel() * 4
+
+    def run(self) -> None:
+        x, h = self.x, self.host
+        begin = torch.cuda.Event()
+        begin.record(self.compute)
+        self.h2d.wait_event(begin)
+        self.d2h.wait_event(begin)
+        with torch.cuda.stream(self.h2d):
+            x.row_ptr.copy_(h.row_ptr, non_blocking=True)
+            if h.scales is not None:
+                x.scales.copy_(h.scales, non_blocking=True)
+            if h.offsets is not None:
+                x.offsets.copy_(h.offsets, non_blocking=True)
+            if h.packed_row_ptr is not None:
+                x.packed_row_ptr.copy_(h.packed_row_ptr, non_blocking=True)
+            self.dense.copy_(self.w_host, non_blocking=True)
+        for r0, r1, n0, n1, p0, p1, launch in self.parts:
+            with torch.cuda.stream(self.h2d):
+                x.col_idx[n0:n1].copy_(h.col_idx[n0:n1], non_blocking=True)
+                x.packed[p0:p1].copy_(h.packed[p0:p1], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(self.h2d)
+            self.compute.wait_event(ready)
+            self.op.run_launch(launch)
+            done = torch.cuda.Event()
+            done.record(self.compute)
+            self.d2h.wait_event(done)
+            with torch.cuda.stream(self.d2h):
+                self.y_host[r0:r1].copy_(self.out[r0:r1], non_blocking=True)
+        end = torch.cuda.Event()
+        end.record(self.d2h)
+        self.compute.wait_event(end)

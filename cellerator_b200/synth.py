@@ -129,6 +129,11 @@ def make_qbell_host(rows, cols, block_size, ell_blocks, fill, bits, seed=0, row_
     values = np.log1p(cnt / rowsum * 1e4).astype(np.float32)
     in_range = genes < cols
     scales, offsets = calibrate(values[in_range], genes[in_range], cols, bits)
+    # metadata padded to whole block columns; the padding repeats gene 0's entry, which is what
+    # slots of a ragged last block column are coded with
+    pad = block_cols * block_size - cols
+    scales = np.concatenate([scales, np.full(pad, scales[0], dtype=np.float32)])
+    offsets = np.concatenate([offsets, np.full(pad, offsets[0], dtype=np.float32)])
     safe = np.where(in_range, genes, 0)
     codes = quantize_codes(values.ravel(), scales[safe.ravel()], offsets[safe.ravel()], bits).reshape(rows, ell_cols)
     cpb = 8 // bits

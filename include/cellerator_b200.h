@@ -25,6 +25,11 @@
 extern "C" {
 #endif
 
+/* every entry point below is exported even when the library is built with hidden visibility */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
 #define CB200_ABI_VERSION 1u
 
 /* include/Cellerator/abi.h:14-21 (cellerator_status), extended with the operation-core
@@ -279,6 +284,10 @@ cb200_status cb200_session_seal(cb200_session *s);
 cb200_launch_binding cb200_session_bind(cb200_session *s, uint32_t stream_index, uint64_t required_workspace_bytes);
 cb200_status cb200_session_synchronize(cb200_session *s);
 void cb200_session_destroy(cb200_session *s);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 
 #ifdef __cplusplus
 }

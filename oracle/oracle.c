@@ -235,13 +235,15 @@ ORC_API int64_t orc_bell_column_for_slot(int64_t rows, int block_size, int64_t e
 }
 
 /* blocked_ell.cuh:165-213  every slot is quantized (an empty block uses column 0's
- * scale/offset); row padding bytes are 0 */
+ * scale/offset); row padding bytes are 0.  One deliberate difference: for a slot of a present
+ * block whose gene index is >= cols (ragged last block column) the reference indexes the
+ * metadata arrays at that gene, i.e. past `cols`; here such a slot uses gene 0's metadata, so
+ * the two agree whenever the caller's arrays repeat gene 0's entry in that padding. */
 ORC_API int orc_bell_pack_row_major(int bits, int policy, int64_t rows, int64_t cols, int block_size,
                                     int64_t ell_cols, int64_t row_stride_bytes,
                                     const uint32_t *block_col_idx, const float *scales,
                                     const float *offsets, const float *values_by_slot,
                                     uint8_t *packed_values) {
-    (void)cols;
     if (!orc_valid_bits(bits) || values_by_slot == NULL || packed_values == NULL || rows < 0 || ell_cols < 0 ||
         row_stride_bytes < orc_row_bytes(bits, ell_cols))
         return -1;
@@ -257,7 +259,7 @@ ORC_API int orc_bell_pack_row_major(int bits, int policy, int64_t rows, int64_t 
                 if (current < ell_cols) {
                     const int64_t column =
                         orc_bell_column_for_slot(rows, block_size, ell_cols, block_col_idx, row, current);
-                    const int64_t safe_column = column >= 0 ? column : 0;
+                    const int64_t safe_column = (column >= 0 && column < cols) ? column : 0;
                     const unsigned code = orc_quantize_code(
                         bits, values_by_slot[row * ell_cols + current], orc_scale_for(scales, safe_column),
                         orc_offset_for(policy, offsets, row, safe_column));

@@ -1,0 +1,111 @@
+"""GPU parity of the quantized Blocked-ELL projection, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from cellerator_b200 import capi, ops, synth
+from conftest import GOLDEN
+from gpu_util import dense
+
+pytestmark = pytest.mark.gpu
+
+
+def bell_reference(oracle, h, w_host):
+    a = (h["bits"], h["policy"], h["rows"], h["cols"], h["block_size"], h["ell_cols"], h["row_stride_bytes"],
+         h["block_col_idx"], h["scales"], h["offsets"])
+    ro, cols, vals = oracle.bell_to_csr(*a, h["packed"])
+    y = oracle.spmm_reference(h["rows"], h["cols"], w_host.shape[1], ro, cols, vals, w_host)
+    l1 = np.zeros(h["rows"])
+    counts = np.diff(ro.astype(np.int64))
+    nz = counts > 0
+    if len(vals):
+        l1[nz] = np.add.reduceat(np.abs(vals.astype(np.float64)), ro[:-1][nz].astype(np.int64))
+    return y, l1
+
+
+def assert_bell_close(y, ref, l1, wmax, bf16_multiply):
+    """CUDA-core kernel: the forward bound 1e-4 * ||row||_1 * max|W|.  Tensor-core kernel
+    (values rounded to bf16 before the multiply): 1e-2 relative to ||row||_1 * max|W|-scaled
+    magnitudes, the bf16 tolerance of the benchmark contract."""
+    err = np.abs(np.asarray(y, dtype=np.float64) - ref)
+    scale = l1[:, None] * wmax + 1e-30
+    tol = 1e-2 if bf16_multiply else 1e-4
+    assert np.all(err <= tol * scale), f"max err/scale {np.max(err / scale):.3e}"
+
+
+@pytest.mark.parametrize("bits,policy", [(8, 1), (4, 2)])
+def test_kat_bell_3x3(cuda_device, oracle, kats, bits, policy):
+    k = kats["bell_3x3"]
+    bci = np.array(k["block_col_idx"], dtype=np.uint32)
+    scales = np.array(k["per_gene_scales"] if policy == 1 else k["column_scales"], dtype=np.float32)
+    offsets = None if policy == 1 else np.array(k["row_offsets"], dtype=np.float32)
+    stride = -(-k["ell_cols"] * bits // 8)
+    packed = oracle.bell_pack(bits, policy, 3, 3, 1, 2, stride, bci, scales, offsets, k["slot_values"])
+    x = ops.QuantizedBell.from_host(dict(rows=3, cols=3, block_size=1, ell_cols=2, row_stride_bytes=stride, bits=bits,
+                                         policy=policy, block_col_idx=bci, packed=packed, scales=scales,
+                                         offsets=offsets), cuda_device)
+    w = torch.tensor(k["rhs"], dtype=torch.float32, device=cuda_device).reshape(3, 2)
+    y = ops.bell_forward(x, w).cpu().numpy()
+    assert np.allclose(y.ravel(), k["expected"], atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["bell8_small", "bell4_small"])
+def test_golden_bell_forward(cuda_device, oracle, name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    h = dict(rows=int(z["rows"]), cols=int(z["cols"]), block_size=int(z["block_size"]), ell_cols=int(z["ell_cols"]),
+             row_stride_bytes=int(z["row_stride_bytes"]), bits=int(z["bits"]), policy=1,
+             block_col_idx=z["block_col_idx"], packed=z["packed"], scales=z["scales"], offsets=z["offsets"])
+    x = ops.QuantizedBell.from_host(h, cuda_device)
+    w = torch.from_numpy(z["w"]).to(cuda_device)
+    y = ops.bell_forward(x, w).cpu().numpy()
+    _, l1 = bell_reference(oracle, h, z["w"])
+    assert_bell_close(y, z["y"], l1, float(np.abs(z["w"]).max()), bf16_multiply=False)
+
+
+@pytest.mark.parametrize("block_size,ell_blocks,cols,n,dtype,bits", [
+    (32, 4, 1000, 256, torch.bfloat16, 8),
+    (32, 16, 8192, 256, torch.bfloat16, 8),
+    (32, 3, 250, 64, torch.float32, 8),
+    (16, 5, 333, 40, torch.float32, 4),
+    (8, 6, 100, 128, torch.bfloat16, 4),
+])
+def test_random_bell_forward(cuda_device, oracle, block_size, ell_blocks, cols, n, dtype, bits):
+    rng = np.random.default_rng(block_size + n)
+    rows = 4 * block_size + 5          # last block row is ragged
+    h = synth.make_qbell_host(rows, cols, block_size, ell_blocks, 0.6, bits, seed=block_size)
+    bci = h["block_col_idx"].reshape(-1, ell_blocks).copy()
+    bci[1, -1] = 0xFFFFFFFF            # an empty block: skipped
+    h["block_col_idx"] = bci.ravel()
+    x = ops.QuantizedBell.from_host(h, cuda_device)
+    w, w_host = dense(rng, cols, n, dtype, cuda_device)
+    ref, l1 = bell_reference(oracle, h, w_host)
+    y = ops.bell_forward(x, w)
+    tensor_core = dtype == torch.bfloat16 and block_size == 32
+    assert_bell_close(y.cpu().numpy(), ref, l1, float(np.abs(w_host).max()), bf16_multiply=tensor_core)
+    y2 = ops.bell_forward(x, w)
+    assert torch.equal(y, y2)          # deterministic
+    init = torch.from_numpy(rng.normal(size=(rows, n)).astype(np.float32)).to(cuda_device)
+    y3 = ops.bell_forward(x, w, out=init.clone(), alpha=0.5, beta=2.0)
+    assert torch.allclose(y3, 0.5 * y + 2.0 * init, rtol=1e-4, atol=1e-4)
+
+
+def test_device_generated_bell_matches_oracle(cuda_device, oracle):
+    cfg = dict(synth.CONFIGS["c5_bell"])
+    cfg["rows"] = 32 * 40
+    x = synth.make_qbell_device(**cfg, device=cuda_device, seed=0)
+    rng = np.random.default_rng(2)
+    w, w_host = dense(rng, x.cols, cfg["n"], torch.bfloat16, cuda_device)
+    y = ops.bell_forward(x, w).cpu().numpy()
+    h = dict(rows=x.rows, cols=x.cols, block_size=x.block_size, ell_cols=x.ell_cols,
+             row_stride_bytes=x.row_stride_bytes, bits=x.bits, policy=x.policy,
+             block_col_idx=x.block_col_idx.cpu().numpy().view(np.uint32), packed=x.packed.cpu().numpy(),
+             scales=x.scales.cpu().numpy(), offsets=x.offsets.cpu().numpy())
+    ref, l1 = bell_reference(oracle, h, w_host)
+    assert_bell_close(y, ref, l1, float(np.abs(w_host).max()), bf16_multiply=True)
+    bci = h["block_col_idx"].reshape(-1, cfg["ell_blocks"])
+    assert np.all(np.diff(bci.astype(np.int64), axis=1) > 0) and bci.max() < 256
+    dec = ops.dequantize_bell(x).cpu().numpy()
+    frac = float((dec != 0).mean())
+    assert 0.5 < frac < 0.7            # about 60 % of the slots of present blocks are non-zero

@@ -1,0 +1,108 @@
+"""GPU parity of the gene-side transpose G' = deq(X)^T G, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from cellerator_b200 import capi, ops
+from conftest import GOLDEN, random_csr
+from gpu_util import dense, host_pack, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def assert_transpose_close(got, ref, col_l1, g_abs_max):
+    """max|d| <= 1e-4 * (||gene column||_1 * max|G|): the forward bound with the roles of the
+    axes exchanged (the sum for gene g runs over the entries of column g)."""
+    bound = 1e-4 * col_l1[:, None] * g_abs_max + 1e-30
+    err = np.abs(np.asarray(got, dtype=np.float64) - ref)
+    assert np.all(err <= bound), f"max excess {np.max(err - bound):.3e}"
+
+
+def col_l1_of(oracle, c):
+    dec = oracle.unpack_csr(c["bits"], c["policy"], c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["scales"],
+                            c["offsets"], c["packed"])
+    out = np.zeros(c["cols"])
+    np.add.at(out, c["col_idx"], np.abs(dec.astype(np.float64)))
+    return out
+
+
+def test_kat_bwd_rhs_3x3(cuda_device, kats):
+    k = kats["csr_3x3"]
+    vals = np.array(k["values"], dtype=np.float32)
+    x = to_dev(dict(rows=3, cols=3, bits=8, policy=1, row_ptr=np.array(k["major_ptr"]), packed_row_ptr=None,
+                    col_idx=np.array(k["minor_idx"]), packed=vals.astype(np.uint8), scales=None, offsets=None),
+               cuda_device)
+    g = torch.tensor(k["grad_out"], dtype=torch.float32, device=cuda_device).reshape(3, 2)
+    out = ops.spmm_transpose(x, g)
+    assert out.cpu().numpy().ravel().tolist() == k["bwd_rhs"]
+
+
+@pytest.mark.parametrize("name", ["csr8_small", "csr4_small"])
+def test_golden_transpose(cuda_device, oracle, name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    c = dict(rows=int(z["rows"]), cols=int(z["cols"]), bits=int(z["bits"]), policy=1, row_ptr=z["row_ptr"],
+             packed_row_ptr=z["packed_row_ptr"], col_idx=z["col_idx"], packed=z["packed"], scales=z["scales"],
+             offsets=z["offsets"])
+    x = to_dev(c, cuda_device)
+    g = torch.from_numpy(z["g"]).to(cuda_device)
+    out = ops.spmm_transpose(x, g).cpu().numpy()
+    assert_transpose_close(out, z["gt"], col_l1_of(oracle, c), float(np.abs(z["g"]).max()))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("n", [1, 3, 8, 16, 32, 64, 128, 24])
+def test_random_transpose(cuda_device, oracle, bits, n):
+    rng = np.random.default_rng(77 * bits + n)
+    policy = 1 + (n % 16 == 0)
+    c = host_pack(oracle, random_csr(rng, rows=120, cols=257, max_nnz=150, bits=bits, policy=policy))
+    x = to_dev(c, cuda_device)
+    g, g_host = dense(rng, c["rows"], n, torch.float32, cuda_device, std=1.0)
+    ref = oracle.qcsr_transpose(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                c["scales"], c["offsets"], g_host, c["cols"])
+    cl1 = col_l1_of(oracle, c)
+    gmax = float(np.abs(g_host).max())
+    out = ops.spmm_transpose(x, g).cpu().numpy()
+    assert_transpose_close(out, ref, cl1, gmax)
+    # alpha / beta, with a destination that must be honoured
+    init = torch.from_numpy(rng.normal(size=(c["cols"], n)).astype(np.float32)).to(cuda_device)
+    out2 = ops.spmm_transpose(x, g, out=init.clone(), alpha=2.0, beta=0.5).cpu().numpy()
+    assert np.allclose(out2, 2.0 * ref + 0.5 * init.cpu().numpy(), rtol=1e-4, atol=1e-4 * gmax * (cl1.max() + 1))
+    # beta == 0 never reads the destination
+    nan_out = torch.full((c["cols"], n), float("nan"), device=cuda_device)
+    assert np.isfinite(ops.spmm_transpose(x, g, out=nan_out).cpu().numpy()).all()
+
+
+def test_row_shards_sum_to_whole(cuda_device, oracle):
+    """The multi-GPU rule: per-shard partials over the uniform row partition add up to the
+    whole-matrix result (what the allreduce computes)."""
+    rng = np.random.default_rng(12)
+    c = host_pack(oracle, random_csr(rng, rows=301, cols=190, max_nnz=120, bits=8, policy=1))
+    x = to_dev(c, cuda_device)
+    g, g_host = dense(rng, c["rows"], 64, torch.float32, cuda_device, std=1.0)
+    whole = ops.spmm_transpose(x, g)
+    ref = oracle.qcsr_transpose(8, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
+                                c["offsets"], g_host, c["cols"])
+    for parts in (2, 4, 8):
+        brp = ops.partition_rows(c["rows"], parts)
+        total = torch.zeros_like(whole)
+        for p in range(parts):
+            r0, r1 = int(brp[p]), int(brp[p + 1])
+            if r0 == r1:
+                continue
+            part = ops.spmm_transpose(x, g, row_begin=r0, row_end=r1)
+            pref = oracle.qcsr_transpose(8, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                         c["scales"], c["offsets"], g_host, c["cols"], r0, r1)
+            assert np.allclose(part.cpu().numpy(), pref, rtol=1e-4, atol=1e-3)
+            total += part
+        assert torch.allclose(total, whole, rtol=1e-4, atol=1e-3)
+    assert_transpose_close(whole.cpu().numpy(), ref, col_l1_of(oracle, c), float(np.abs(g_host).max()))
+
+
+def test_transpose_rejects_deterministic_and_bf16(cuda_device):
+    with pytest.raises(capi.Cb200Error) as e:
+        ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, 8, 8, 8, 8, 8, 1, torch.float32, cuda_device, deterministic=True)
+    assert e.value.status == capi.UNSUPPORTED
+    with pytest.raises(capi.Cb200Error):
+        ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, 8, 8, 8, 8, 8, 1, torch.bfloat16, cuda_device)

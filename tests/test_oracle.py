@@ -248,8 +248,11 @@ def test_oracle_equals_reference_bell_random(oracle, reference, bits, policy, bs
     bci[1, 1] = 0xFFFFFFFF                  # an empty block
     ell = width * bs
     stride = -(-(-(-ell * bits // 8)) // 16) * 16
-    scales = rng.uniform(0.05, 0.4, size=cols).astype(np.float32)
-    offsets = rng.uniform(-1, 1, size=cols if policy == 1 else rows).astype(np.float32)
+    scales = rng.uniform(0.05, 0.4, size=5 * bs).astype(np.float32)
+    scales[cols:] = scales[0]               # metadata padding repeats gene 0 (see oracle.c)
+    offsets = rng.uniform(-1, 1, size=5 * bs if policy == 1 else rows).astype(np.float32)
+    if policy == 1:
+        offsets[cols:] = offsets[0]
     vals = rng.uniform(-1, 20, size=(rows, ell)).astype(np.float32)
     a = (bits, policy, rows, cols, bs, ell, stride, bci.ravel(), scales, offsets)
     po, pr = oracle.bell_pack(*a, vals), reference.bell_pack(*a, vals)
