@@ -35,7 +35,12 @@ __device__ __forceinline__ unsigned quantize_one(float value, float scale, float
     constexpr int max_code = (1 << BITS) - 1;
     if (scale == 0.0f) return 0u;
     const float q = __fdiv_rn(__fsub_rn(value, offset), scale);
-    int rounded = q >= 0.0f ? static_cast<int>(__fadd_rn(q, 0.5f)) : static_cast<int>(__fsub_rn(q, 0.5f));
+    const float shifted = q >= 0.0f ? __fadd_rn(q, 0.5f) : __fsub_rn(q, 0.5f);
+    // A float -> int conversion that overflows (or a NaN) is undefined in the host codec; on the
+    // x86-64 hosts it runs on the conversion yields INT_MIN, which the rule then maps to code 0.
+    // The device conversion would saturate to INT_MAX instead, so that case is decided here.
+    if (!(shifted < 2147483648.0f)) return 0u;
+    int rounded = static_cast<int>(shifted);
     if (rounded < 0) return 0u;
     if (rounded > max_code) rounded = max_code;
     return static_cast<unsigned>(rounded);

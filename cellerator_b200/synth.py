@@ -45,10 +45,13 @@ def quantize_codes(values, scale, offset, bits) -> np.ndarray:
     with np.errstate(divide="ignore", invalid="ignore"):
         q = (values - offset) / scale
     shifted = np.where(q >= 0, q + np.float32(0.5), q - np.float32(0.5)).astype(np.float32)
-    shifted = np.nan_to_num(shifted, nan=0.0, posinf=3e9, neginf=-3e9)
-    rounded = np.trunc(np.clip(shifted, -2.0e9, 2.0e9)).astype(np.int64)
+    # a conversion that overflows int32 (or a NaN) gives INT_MIN on the x86-64 hosts the host
+    # codec runs on, which the rule maps to code 0
+    overflow = ~(shifted < np.float32(2147483648.0))
+    shifted = np.nan_to_num(shifted, nan=0.0, posinf=0.0, neginf=-3e9)
+    rounded = np.trunc(np.clip(shifted, -2.0e9, 2.2e9)).astype(np.int64)
     rounded = np.clip(rounded, 0, (1 << bits) - 1)
-    rounded[scale == 0] = 0
+    rounded[(scale == 0) | overflow] = 0
     return rounded.astype(np.uint8)
 
 

@@ -113,13 +113,18 @@ ORC_API void orc_get_block(int64_t rows, const int64_t *row_ptr, const int64_t *
 /* ------------------------------------------------------------------------ */
 /* code <-> value: include/Cellerator/quantized/access.cuh:81-131           */
 
-/* access.cuh:104-131  scale==0 -> 0; true division; round half away from zero; clamp */
+/* access.cuh:104-131  scale==0 -> 0; true division; round half away from zero; clamp.
+ * When q +- 0.5 does not fit an int (or is NaN) the reference's conversion is undefined
+ * behaviour; on the x86-64 hosts it runs on the result is INT_MIN, hence code 0, and that is
+ * what this restatement, compiled for the same hosts, returns too. */
 ORC_API unsigned orc_quantize_code(int bits, float value, float scale, float offset) {
     const int max_code = (1 << bits) - 1;
     const float centered = value - offset;
     if (scale == 0.0f) return 0u;
     const float q = centered / scale;
-    int rounded = q >= 0.0f ? (int)(q + 0.5f) : (int)(q - 0.5f);
+    const float shifted = q >= 0.0f ? q + 0.5f : q - 0.5f;
+    if (!(shifted < 2147483648.0f)) return 0u; /* the INT_MIN case, made explicit */
+    int rounded = (int)shifted;
     if (rounded < 0) return 0u;
     if (rounded > max_code) rounded = max_code;
     return (unsigned)rounded;

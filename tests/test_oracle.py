@@ -209,6 +209,22 @@ def test_oracle_equals_reference_scalar_rules(oracle, reference):
             assert oracle.quantize_code(bits, v, s, o) == reference.quantize_code(bits, v, s, o)
         # exact .5 ties round away from zero
         assert oracle.quantize_code(bits, 0.5, 1.0, 0.0) == reference.quantize_code(bits, 0.5, 1.0, 0.0) == 1
+        # magnitudes that overflow the int conversion, and NaN: the host result is code 0
+        # (the reference's scalar helper may return INT_MIN as unsigned there; what its pack stores
+        # is that value masked to the code width, i.e. 0)
+        for v in (1e12, -1e12, 3e9, float("nan"), float("inf")):
+            assert oracle.quantize_code(bits, v, 0.5, 0.0) == 0
+            assert reference.quantize_code(bits, v, 0.5, 0.0) & ((1 << bits) - 1) == 0
+    rng2 = np.random.default_rng(8)
+    c = dict(row_ptr=np.array([0, 6], dtype=np.int64), col_idx=np.arange(6, dtype=np.int32),
+             scales=np.full(6, 0.5, dtype=np.float32), offsets=np.zeros(6, dtype=np.float32),
+             values=np.array([1e12, -1e12, 3e9, np.nan, np.inf, 3.0], dtype=np.float32))
+    for bits in (1, 2, 4, 8):
+        prp, _ = oracle.build_packed_row_ptr(bits, c["row_ptr"])
+        a = oracle.pack_csr(bits, 1, c["row_ptr"], prp, c["col_idx"], c["scales"], c["offsets"], c["values"])
+        b = reference.pack_csr(bits, 1, c["row_ptr"], prp, c["col_idx"], c["scales"], c["offsets"], c["values"], cols=6)
+        assert np.array_equal(a, b)
+    del rng2
     for _ in range(400):
         code, s, o = int(rng.integers(0, 256)), float(np.float32(rng.uniform(0, 1))), float(np.float32(rng.uniform(-1, 1)))
         assert oracle.dequantize_code(code, s, o) == reference.dequantize_code(code, s, o)
