@@ -282,6 +282,24 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     }
     if (problem->projection == CB200_PROJECTION_TRANSPOSE)
         p->workspace_bytes = qcsr_transpose_workspace_bytes(problem->k, problem->n, p->sm_count);
+    if (problem->projection == CB200_PROJECTION_CSR) {
+        // Row schedule from the nnz/row distribution: the gene-tiled kernel pays a fixed cost per
+        // (row, gene tile) visit, so it needs enough stored entries per visit and enough row
+        // groups to fill the SMs; short or few rows go to the warp-per-row kernel.
+        const std::int64_t row_bytes = problem->n * (problem->dense_dtype == CB200_DTYPE_BF16 ? 2 : 4);
+        const bool shape_ok = (problem->n == 32 || problem->n == 64 || problem->n == 128) && row_bytes <= 256;
+        const double tile_genes = row_bytes > 0 ? 98304.0 / static_cast<double>(row_bytes) : 0.0;
+        const double per_visit = problem->k > 0 ? p->mean_row_nnz * tile_genes / static_cast<double>(problem->k) : 0.0;
+        const char *force = std::getenv("CB200_FWD_SCHEDULE");
+        bool tiled = shape_ok && problem->m >= 16 * 128 && (per_visit >= 6.0 || tile_genes >= problem->k);
+        if (force != nullptr && std::strcmp(force, "warp_per_row") == 0) tiled = false;
+        if (force != nullptr && std::strcmp(force, "gene_tiled") == 0) tiled = shape_ok;
+        if (tiled) {
+            p->schedule = fwd_schedule::gene_tiled;
+            p->schedule_name = "gene_tiled";
+        }
+        p->workspace_bytes = 256u; // status word of the tiled kernel
+    }
     *out = p;
     return CB200_STATUS_SUCCESS;
 }

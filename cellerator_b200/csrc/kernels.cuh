@@ -27,7 +27,14 @@ struct dense_args {
     float alpha, beta;
 };
 
-enum class fwd_schedule : int { warp_per_row = 0, row_split = 1 };
+enum class fwd_schedule : int { warp_per_row = 0, gene_tiled = 1 };
+
+// Gene-tiled kernel (W staged through shared memory); *taken is false when the shape is outside
+// what it covers, and the caller then runs the warp-per-row kernel.
+bool qcsr_forward_tiled_supported(const qcsr_view &x, const dense_args &d);
+cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                       std::int64_t row_end, int *status_word, int sm_count, cudaStream_t stream,
+                                       bool *taken);
 
 // Y[r,:] = alpha * sum_i deq(code_i) * W[col_i,:] + beta * Y[r,:]  for r in [row_begin,row_end)
 cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,

@@ -11,6 +11,9 @@
 // Partial sums of the 32/LPN groups are combined with shuffles at the end of the row.
 #include "kernels.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace cb200 {
 namespace {
 
@@ -41,7 +44,28 @@ __device__ __forceinline__ unsigned load_code(const std::uint8_t *row_bytes, std
     }
 }
 
-// One warp per row, N == 8 * LPN, dense rows 16-byte aligned.
+// acc[0..7] += v * w[0..7] with packed two-wide fp32 FMAs (fma.rn.f32x2, sm_100): half the
+// issue slots of eight scalar FMAs.
+__device__ __forceinline__ void fma8(float (&acc)[8], float v, const float (&w)[8]) {
+    const float2 vv = make_float2(v, v);
+    unsigned long long vp;
+    memcpy(&vp, &vv, 8);
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        float2 a = make_float2(acc[i], acc[i + 1]);
+        const float2 b = make_float2(w[i], w[i + 1]);
+        unsigned long long ap, bp;
+        memcpy(&ap, &a, 8);
+        memcpy(&bp, &b, 8);
+        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(ap) : "l"(vp), "l"(bp));
+        memcpy(&a, &ap, 8);
+        acc[i] = a.x;
+        acc[i + 1] = a.y;
+    }
+}
+
+// One warp per row, N == 8 * LPN, dense rows 16-byte aligned.  The (gene, code, scale, offset)
+// loads of the next 32 entries are issued before the current 32 are multiplied.
 template<int BITS, typename WT, int LPN>
 __global__ void __launch_bounds__(256) qcsr_fwd_warp_row_kernel(const fwd_params p) {
     constexpr int NPS = 32 / LPN; // entries served per step
@@ -56,24 +80,31 @@ __global__ void __launch_bounds__(256) qcsr_fwd_warp_row_kernel(const fwd_params
     const float row_offset = (row_policy && p.offsets != nullptr) ? __ldg(p.offsets + row) : 0.0f;
     const WT *w = static_cast<const WT *>(p.w);
     const int group = lane / LPN;           // which entry of a step this lane serves
-    const int col0 = (lane % LPN) * 8;      // first output column held by this lane
+    const WT *wcol = w + (lane % LPN) * 8;  // first output column held by this lane
 
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
-    for (std::int64_t base = begin; base < end; base += 32) {
-        const int count = static_cast<int>(min(static_cast<std::int64_t>(32), end - base));
-        int gene = 0;
-        float value = 0.0f;
-        if (lane < count) {
-            const std::int64_t idx = base + lane;
+    // entry `idx` decoded by this lane: gene index and dequantised value (0 past the row end)
+    auto fetch = [&](std::int64_t idx, int &gene, float &value) {
+        gene = 0;
+        value = 0.0f;
+        if (idx < end) {
             gene = __ldg(p.col_idx + idx);
             const unsigned code = load_code<BITS>(row_bytes, idx - begin);
             const float scale = p.scales != nullptr ? __ldg(p.scales + gene) : 1.0f;
             const float offset = row_policy ? row_offset : (p.offsets != nullptr ? __ldg(p.offsets + gene) : 0.0f);
             value = fmaf(static_cast<float>(code), scale, offset);
         }
+    };
+
+    int gene, next_gene;
+    float value, next_value;
+    fetch(begin + lane, gene, value);
+    for (std::int64_t base = begin; base < end; base += 32) {
+        fetch(base + 32 + lane, next_gene, next_value);
+        const int count = static_cast<int>(min(static_cast<std::int64_t>(32), end - base));
         if (count == 32) {
 #pragma unroll
             for (int step = 0; step < LPN; ++step) {
@@ -81,9 +112,8 @@ __global__ void __launch_bounds__(256) qcsr_fwd_warp_row_kernel(const fwd_params
                 const int g = __shfl_sync(0xffffffffu, gene, src);
                 const float v = __shfl_sync(0xffffffffu, value, src);
                 float wv[8];
-                load8(w + static_cast<std::int64_t>(g) * p.w_ld + col0, wv);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = fmaf(v, wv[i], acc[i]);
+                load8(wcol + static_cast<std::int64_t>(g) * p.w_ld, wv);
+                fma8(acc, v, wv);
             }
         } else {
 #pragma unroll
@@ -93,12 +123,13 @@ __global__ void __launch_bounds__(256) qcsr_fwd_warp_row_kernel(const fwd_params
                 const float v = __shfl_sync(0xffffffffu, value, src);
                 if (src < count) {
                     float wv[8];
-                    load8(w + static_cast<std::int64_t>(g) * p.w_ld + col0, wv);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(v, wv[i], acc[i]);
+                    load8(wcol + static_cast<std::int64_t>(g) * p.w_ld, wv);
+                    fma8(acc, v, wv);
                 }
             }
         }
+        gene = next_gene;
+        value = next_value;
     }
 
 #pragma unroll
@@ -107,7 +138,7 @@ __global__ void __launch_bounds__(256) qcsr_fwd_warp_row_kernel(const fwd_params
         for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
     }
     if (lane < LPN) {
-        float *out = p.y + row * p.y_ld + col0;
+        float *out = p.y + row * p.y_ld + (lane % LPN) * 8;
         float4 lo = make_float4(p.alpha * acc[0], p.alpha * acc[1], p.alpha * acc[2], p.alpha * acc[3]);
         float4 hi = make_float4(p.alpha * acc[4], p.alpha * acc[5], p.alpha * acc[6], p.alpha * acc[7]);
         if (p.beta != 0.0f) {
@@ -169,7 +200,11 @@ __global__ void __launch_bounds__(256) qcsr_fwd_generic_kernel(const fwd_params 
 template<int BITS, typename WT>
 cb200_status dispatch_n(const fwd_params &p, bool vector_ok, cudaStream_t stream) {
     const std::int64_t rows = p.row_end - p.row_begin;
-    constexpr int threads = 256;
+    static const int threads = [] {
+        const char *e = std::getenv("CB200_FWD_THREADS");
+        const int t = e != nullptr ? std::atoi(e) : 0;
+        return (t >= 32 && t <= 256 && t % 32 == 0) ? t : 128;
+    }();
     const unsigned grid = static_cast<unsigned>((rows + (threads / 32) - 1) / (threads / 32));
     if (vector_ok && p.n % 8 == 0) {
         switch (p.n / 8) {
@@ -192,10 +227,16 @@ cb200_status dispatch_n(const fwd_params &p, bool vector_ok, cudaStream_t stream
 } // namespace
 
 cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
-                                 std::int64_t row_end, fwd_schedule, const void *, void *, int,
-                                 cudaStream_t stream) {
+                                 std::int64_t row_end, fwd_schedule schedule, const void *, void *workspace,
+                                 int sm_count, cudaStream_t stream) {
     if (row_end <= row_begin || d.n == 0) return CB200_STATUS_SUCCESS;
-    if ((row_end - row_begin + 7) / 8 > 0x7fffffffll) return fail(CB200_STATUS_INVALID_SHAPE, "row range too large for one launch");
+    if (row_end - row_begin > 0x7fffffffll) return fail(CB200_STATUS_INVALID_SHAPE, "row range too large for one launch");
+    if (schedule == fwd_schedule::gene_tiled) {
+        bool taken = false;
+        const cb200_status st = launch_qcsr_forward_tiled(x, d, row_begin, row_end, static_cast<int *>(workspace),
+                                                          sm_count, stream, &taken);
+        if (st != CB200_STATUS_SUCCESS || taken) return st;
+    }
     fwd_params p{};
     p.row_ptr = x.row_ptr; p.packed_row_ptr = x.packed_row_ptr; p.col_idx = x.col_idx; p.packed = x.packed;
     p.scales = x.scales; p.offsets = x.offsets; p.w = d.dense; p.y = d.out; p.w_ld = d.dense_ld; p.y_ld = d.out_ld;

@@ -1,0 +1,471 @@
+// Gene-tiled fused dequantise + SpMM for quantized CSR: the W operand is staged through shared
+// memory instead of being gathered row by row from L2.
+//
+// Why: at N = 64 every stored entry needs a 128-byte row of W.  Gathered from L2 that is
+// ~25x the HBM bytes of the entry itself and the L2 -> SM path saturates long before HBM does.
+// Here a CTA owns a group of 128 cell rows and sweeps the gene axis in tiles: tile t of W
+// (tile_genes consecutive rows, 96 KB) is brought into shared memory by one bulk async copy
+// (cp.async.bulk, completion on an mbarrier, double buffered), the per-gene scale / zero-point
+// of the tile sit beside it, and each warp multiplies the part of its 8 rows that falls into
+// the tile (gene indices are ascending within a row, so that part is a contiguous run found by
+// comparing against the tile's upper bound).  Accumulators for the warp's 8 rows stay in
+// registers across all tiles, so W crosses L2 -> SM once per 128 rows instead of once per entry.
+//
+// Rows of a group are dealt to the 16 warps longest-first in snake order, so that the warps of a
+// CTA reach the end of each tile at about the same time.
+//
+// Waiting on the copy barrier is bounded: if the bound is hit a flag is raised in the status
+// word (first int of the workspace) and the kernel carries on with memory-safe indices, so it
+// always terminates; a non-zero status means the output is not valid.
+#include "kernels.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace cb200 {
+namespace {
+
+constexpr int kWarps = 16;
+constexpr int kRowsPerWarp = 8;
+constexpr int kGroupRows = kWarps * kRowsPerWarp; // 128
+constexpr int kThreads = kWarps * 32;             // 512
+constexpr int kWBufBytes = 96 * 1024;
+
+struct tiled_params {
+    const std::int64_t *row_ptr;
+    const std::int64_t *packed_row_ptr;
+    const std::int32_t *col_idx;
+    const std::uint8_t *packed;
+    const float *scales;
+    const float *offsets;
+    const void *w;
+    float *y;
+    std::int64_t y_ld;
+    std::int64_t row_begin, row_end;
+    std::int64_t groups;
+    int genes;
+    int tile_genes;
+    int tiles;
+    int n;
+    int policy;
+    float alpha, beta;
+    int *status;
+};
+
+__device__ __forceinline__ std::uint32_t smem_u32(const void *p) {
+    return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(std::uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(std::uint32_t bar, std::uint32_t parity) {
+    std::uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0u;
+}
+// One contiguous global -> shared copy by the copy engine; `bytes` and both addresses are
+// multiples of 16.  Source is always this GPU's own memory.
+__device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes, std::uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void fma8_packed(float (&acc)[8], float v, const float (&w)[8]) {
+    const float2 vv = make_float2(v, v);
+    unsigned long long vp;
+    memcpy(&vp, &vv, 8);
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        float2 a = make_float2(acc[i], acc[i + 1]);
+        const float2 b = make_float2(w[i], w[i + 1]);
+        unsigned long long ap, bp;
+        memcpy(&ap, &a, 8);
+        memcpy(&bp, &b, 8);
+        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(ap) : "l"(vp), "l"(bp));
+        memcpy(&a, &ap, 8);
+        acc[i] = a.x;
+        acc[i + 1] = a.y;
+    }
+}
+
+// The 8 columns of a staged W row held by this lane.  bf16: 8 consecutive columns (one 16-byte
+// read).  fp32: columns [4t,4t+4) and [N/2+4t, N/2+4t+4) so that both 16-byte reads of a lane
+// group are contiguous across its lanes (no bank conflict).
+// Shared-memory accesses by 32-bit shared-window address (keeps 64-bit pointer arithmetic out of
+// the inner loop).  volatile: they stay ordered against the staging store and each other.
+__device__ __forceinline__ uint4 lds_b32x4(std::uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds_f32x2(std::uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_b32x2(std::uint32_t addr, int a, float b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(__float_as_int(b)) : "memory");
+}
+
+// `addr` = shared address of this lane's slice of a staged W row (row start + t * 16).
+template<typename WT, int LPN>
+__device__ __forceinline__ void load_w_smem(std::uint32_t addr, float (&w)[8]) {
+    if constexpr (sizeof(WT) == 2) {
+        const uint4 a = lds_b32x4(addr);
+        bf16x2_to_f32(a.x, w[0], w[1]);
+        bf16x2_to_f32(a.y, w[2], w[3]);
+        bf16x2_to_f32(a.z, w[4], w[5]);
+        bf16x2_to_f32(a.w, w[6], w[7]);
+    } else {
+        const uint4 a = lds_b32x4(addr);
+        const uint4 b = lds_b32x4(addr + LPN * 16);
+        w[0] = __uint_as_float(a.x); w[1] = __uint_as_float(a.y); w[2] = __uint_as_float(a.z); w[3] = __uint_as_float(a.w);
+        w[4] = __uint_as_float(b.x); w[5] = __uint_as_float(b.y); w[6] = __uint_as_float(b.z); w[7] = __uint_as_float(b.w);
+    }
+}
+
+template<int BITS, typename WT, int LPN>
+__global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled_params p) {
+    constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT)); // bytes of one W row
+    constexpr int NPS = 32 / LPN;                              // entries served per step
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tile_genes = p.tile_genes;
+    unsigned char *wbuf = smem;                                                  // [2][kWBufBytes]
+    float2 *sc = reinterpret_cast<float2 *>(smem + 2 * kWBufBytes);              // [2][tile_genes] {scale, offset}
+    float2 *stage = sc + 2 * tile_genes;                                         // [kWarps][32] {gene row offset, value}
+    int4 *meta = reinterpret_cast<int4 *>(stage + kWarps * 32);                  // [kWarps][8] {start, end, packed start, row}
+    float *rowoff = reinterpret_cast<float *>(meta + kGroupRows);                // [kWarps][8]
+    int *lens = reinterpret_cast<int *>(rowoff + kGroupRows);                    // [128]
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(lens + kGroupRows);  // [2]
+    int *abort_flag = reinterpret_cast<int *>(bars + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group_lane = lane / LPN, t_in_group = lane % LPN;
+    const bool row_policy = p.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+    const std::int64_t my_groups = (p.groups - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const std::int64_t total_tiles = my_groups * p.tiles;
+    const std::uint32_t bar_addr[2] = {smem_u32(bars), smem_u32(bars + 1)};
+    const std::uint32_t wbuf_addr[2] = {smem_u32(wbuf), smem_u32(wbuf + kWBufBytes)};
+
+    if (tid == 0) {
+        mbar_init(bar_addr[0], 1);
+        mbar_init(bar_addr[1], 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    auto issue_tile = [&](std::int64_t q) { // thread 0 only
+        const int t = static_cast<int>(q % p.tiles);
+        const int b = static_cast<int>(q & 1);
+        const int g0 = t * tile_genes;
+        const int count = min(tile_genes, p.genes - g0);
+        const std::uint32_t bytes = static_cast<std::uint32_t>(count) * RB;
+        mbar_expect_tx(bar_addr[b], bytes);
+        bulk_copy_g2s(wbuf_addr[b], static_cast<const unsigned char *>(p.w) + static_cast<std::size_t>(g0) * RB, bytes,
+                      bar_addr[b]);
+    };
+    if (tid == 0) {
+        if (total_tiles > 0) issue_tile(0);
+        if (total_tiles > 1) issue_tile(1);
+    }
+    // scale / zero-point of tile 0
+    for (int i = tid; i < min(tile_genes, p.genes); i += kThreads)
+        sc[i] = make_float2(__ldg(p.scales + i), (!row_policy && p.offsets != nullptr) ? __ldg(p.offsets + i) : 0.0f);
+    __syncthreads();
+
+    constexpr int SC_PER_THREAD = (kWBufBytes / RB + kThreads - 1) / kThreads;
+    std::int64_t q = 0;
+    for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+        const std::int64_t group = blockIdx.x + gi * gridDim.x;
+        const std::int64_t grow0 = p.row_begin + group * kGroupRows;
+        const int grows = static_cast<int>(min(static_cast<std::int64_t>(kGroupRows), p.row_end - grow0));
+        const std::int64_t gbase = __ldg(p.row_ptr + grow0);
+        const std::int64_t pbase = p.packed_row_ptr != nullptr ? __ldg(p.packed_row_ptr + grow0) : gbase;
+        const std::int32_t *col_g = p.col_idx + gbase;
+        const std::uint8_t *packed_g = p.packed + pbase;
+
+        // ---- deal the group's rows to warps: longest first, snake order
+        if (tid < kGroupRows)
+            lens[tid] = tid < grows ? static_cast<int>(__ldg(p.row_ptr + grow0 + tid + 1) - __ldg(p.row_ptr + grow0 + tid)) : -1;
+        __syncthreads();
+        if (tid < kGroupRows) {
+            const int mine = lens[tid];
+            int rank = 0;
+            for (int j = 0; j < kGroupRows; ++j) {
+                const int other = lens[j];
+                rank += (other > mine || (other == mine && j < tid)) ? 1 : 0;
+            }
+            const int round = rank / kWarps, pos = rank % kWarps;
+            const int w = (round & 1) ? kWarps - 1 - pos : pos;
+            int4 m = make_int4(0, 0, 0, -1);
+            float ro = 0.0f;
+            if (tid < grows) {
+                const std::int64_t rs = __ldg(p.row_ptr + grow0 + tid);
+                m.x = static_cast<int>(rs - gbase);
+                m.y = m.x + mine;
+                m.z = p.packed_row_ptr != nullptr ? static_cast<int>(__ldg(p.packed_row_ptr + grow0 + tid) - pbase) : m.x;
+                m.w = tid;
+                if (row_policy && p.offsets != nullptr) ro = __ldg(p.offsets + grow0 + tid);
+            }
+            meta[w * kRowsPerWarp + round] = m;
+            rowoff[w * kRowsPerWarp + round] = ro;
+        }
+        __syncthreads();
+
+        // Per row: cursor, and the (gene, code byte) of the 32 entries at the cursor, fetched one
+        // tile ahead so that no global-memory latency sits in front of a row's visit.
+        int cur[kRowsPerWarp];
+        int gene_pf[kRowsPerWarp];
+        unsigned code_pf[kRowsPerWarp];
+        float acc[kRowsPerWarp][8];
+        auto fetch_chunk = [&](const int4 &m, int c, int &gene, unsigned &code) {
+            gene = 0x7fffffff;
+            code = 0u;
+            if (lane < m.y - c) {
+                gene = __ldg(col_g + c + lane);
+                const int local = c - m.x + lane;
+                code = __ldg(packed_g + m.z + (BITS == 8 ? local : (local >> 1)));
+            }
+        };
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int4 m = meta[warp * kRowsPerWarp + r];
+            cur[r] = m.x;
+            fetch_chunk(m, m.x, gene_pf[r], code_pf[r]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+        }
+
+        for (int t = 0; t < p.tiles; ++t, ++q) {
+            const int b = static_cast<int>(q & 1);
+            const int g0 = t * tile_genes;
+            const int g1 = min(p.genes, g0 + tile_genes);
+            // ---- wait for the tile's bytes (bounded)
+            {
+                const std::uint32_t parity = static_cast<std::uint32_t>((q >> 1) & 1);
+                int spins = 0;
+                while (!mbar_try_wait(bar_addr[b], parity)) {
+                    if (++spins > (1 << 22)) {
+                        *abort_flag = 1;
+                        break;
+                    }
+                }
+            }
+            // ---- prefetch the next tile's scale / zero-point into registers
+            float s_next[SC_PER_THREAD], o_next[SC_PER_THREAD];
+            const bool has_next = q + 1 < total_tiles;
+            const int tn = static_cast<int>((q + 1) % p.tiles);
+            if (has_next) {
+#pragma unroll
+                for (int k = 0; k < SC_PER_THREAD; ++k) {
+                    const int local = tid + k * kThreads;
+                    const int gene = tn * tile_genes + local;
+                    s_next[k] = 1.0f;
+                    o_next[k] = 0.0f;
+                    if (local < tile_genes && gene < p.genes) {
+                        s_next[k] = __ldg(p.scales + gene);
+                        if (!row_policy && p.offsets != nullptr) o_next[k] = __ldg(p.offsets + gene);
+                    }
+                }
+            }
+            // 32-bit shared-window addresses for everything the inner loop touches
+            const std::uint32_t w_lane = wbuf_addr[b] + t_in_group * 16;             // this lane's slice of W row 0
+            const std::uint32_t sc_addr = smem_u32(sc) + b * tile_genes * 8;
+            const std::uint32_t stage_addr = smem_u32(stage) + warp * 256;
+            const std::uint32_t stage_rd = stage_addr + group_lane * 8;              // entry of step 0 for this lane
+
+            // ---- the warp's 8 rows: the run of each row that falls into [g0, g1)
+#pragma unroll
+            for (int r = 0; r < kRowsPerWarp; ++r) {
+                const int4 m = meta[warp * kRowsPerWarp + r];
+                const float row_offset = rowoff[warp * kRowsPerWarp + r];
+                int c = cur[r];
+                int gene = gene_pf[r];
+                unsigned code_byte = code_pf[r];
+                bool refetch = false;
+                while (true) {
+                    const int count = __popc(__ballot_sync(0xffffffffu, gene < g1));
+                    if (count == 0) break;
+                    // a full chunk with more of the row behind it: start fetching the following chunk now
+                    const bool more = count == 32 && c + 32 < m.y;
+                    int gene2 = 0x7fffffff;
+                    unsigned code2 = 0u;
+                    if (more) fetch_chunk(m, c + 32, gene2, code2);
+                    // decode without branches: lanes past `count` read a clamped (valid) tile slot and
+                    // stage value 0
+                    const int gl = min(max(gene - g0, 0), tile_genes - 1); // in-tile even for unsorted input
+                    unsigned code = code_byte;
+                    if constexpr (BITS == 4) code = ((c - m.x + lane) & 1) ? (code_byte >> 4) : (code_byte & 0xfu);
+                    const float2 so = lds_f32x2(sc_addr + gl * 8);
+                    const float decoded = fmaf(static_cast<float>(code), so.x, row_policy ? row_offset : so.y);
+                    const float value = lane < count ? decoded : 0.0f;
+                    __syncwarp();
+                    sts_b32x2(stage_addr + lane * 8, gl * RB, value);
+                    __syncwarp();
+                    if (count == 32) {
+#pragma unroll
+                        for (int step = 0; step < LPN; ++step) {
+                            const float2 e = lds_f32x2(stage_rd + step * NPS * 8);
+                            float wv[8];
+                            load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
+                            fma8_packed(acc[r], e.y, wv);
+                        }
+                    } else {
+                        // whole steps first, then one step in which only some lane groups have an entry
+                        const int whole = count / NPS;
+                        for (int step = 0; step < whole; ++step) {
+                            const float2 e = lds_f32x2(stage_rd + step * NPS * 8);
+                            float wv[8];
+                            load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
+                            fma8_packed(acc[r], e.y, wv);
+                        }
+                        if (whole * NPS + group_lane < count) {
+                            const float2 e = lds_f32x2(stage_rd + whole * NPS * 8);
+                            float wv[8];
+                            load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
+                            fma8_packed(acc[r], e.y, wv);
+                        }
+                    }
+                    c += count;
+                    if (!more) {
+                        refetch = true; // the cursor moved into (or past) the held chunk
+                        break;
+                    }
+                    gene = gene2;
+                    code_byte = code2;
+                }
+                cur[r] = c;
+                if (refetch) {
+                    fetch_chunk(m, c, gene_pf[r], code_pf[r]); // all lanes idle once the row is finished
+                } else {
+                    gene_pf[r] = gene; // the held chunk starts at the cursor: keep it for the next tile
+                    code_pf[r] = code_byte;
+                }
+            }
+
+            // ---- publish the next tile's scale / zero-point, release this tile's buffer
+            if (has_next) {
+                float2 *sc_next = sc + (b ^ 1) * tile_genes;
+#pragma unroll
+                for (int k = 0; k < SC_PER_THREAD; ++k) {
+                    const int local = tid + k * kThreads;
+                    if (local < tile_genes) sc_next[local] = make_float2(s_next[k], o_next[k]);
+                }
+            }
+            __syncthreads();
+            if (tid == 0 && q + 2 < total_tiles) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_tile(q + 2);
+            }
+        }
+
+        // ---- combine the lane groups' partial sums and write the 8 rows
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+#pragma unroll
+            for (int off = LPN; off < 32; off <<= 1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], off);
+            }
+            const int row_local = meta[warp * kRowsPerWarp + r].w;
+            if (lane < LPN && row_local >= 0) {
+                float *out = p.y + (grow0 + row_local) * p.y_ld;
+                float *out_a = out + (sizeof(WT) == 2 ? t_in_group * 8 : t_in_group * 4);
+                float *out_b = sizeof(WT) == 2 ? out_a + 4 : out + LPN * 4 + t_in_group * 4;
+                float4 lo = make_float4(p.alpha * acc[r][0], p.alpha * acc[r][1], p.alpha * acc[r][2], p.alpha * acc[r][3]);
+                float4 hi = make_float4(p.alpha * acc[r][4], p.alpha * acc[r][5], p.alpha * acc[r][6], p.alpha * acc[r][7]);
+                if (p.beta != 0.0f) {
+                    const float4 a = *reinterpret_cast<const float4 *>(out_a);
+                    const float4 bb = *reinterpret_cast<const float4 *>(out_b);
+                    lo.x = fmaf(p.beta, a.x, lo.x); lo.y = fmaf(p.beta, a.y, lo.y);
+                    lo.z = fmaf(p.beta, a.z, lo.z); lo.w = fmaf(p.beta, a.w, lo.w);
+                    hi.x = fmaf(p.beta, bb.x, hi.x); hi.y = fmaf(p.beta, bb.y, hi.y);
+                    hi.z = fmaf(p.beta, bb.z, hi.z); hi.w = fmaf(p.beta, bb.w, hi.w);
+                }
+                *reinterpret_cast<float4 *>(out_a) = lo;
+                *reinterpret_cast<float4 *>(out_b) = hi;
+            }
+        }
+        __syncthreads(); // meta / lens are rewritten by the next group
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template<typename WT, int LPN>
+constexpr std::size_t tiled_smem_bytes() {
+    constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT));
+    constexpr int tile_genes = kWBufBytes / RB;
+    return 2 * kWBufBytes + 2 * tile_genes * sizeof(float2) + kWarps * 32 * sizeof(float2) + kGroupRows * sizeof(int4) +
+           kGroupRows * sizeof(float) + kGroupRows * sizeof(int) + 2 * sizeof(std::uint64_t) + 16;
+}
+
+template<int BITS, typename WT, int LPN>
+cb200_status launch_one(tiled_params p, int sm_count, cudaStream_t stream) {
+    constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT));
+    p.tile_genes = kWBufBytes / RB;
+    p.tiles = (p.genes + p.tile_genes - 1) / p.tile_genes;
+    constexpr std::size_t smem = tiled_smem_bytes<WT, LPN>();
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_tiled_kernel<BITS, WT, LPN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+    const unsigned grid = static_cast<unsigned>(p.groups < sm_count ? p.groups : sm_count);
+    qcsr_fwd_tiled_kernel<BITS, WT, LPN><<<grid, kThreads, smem, stream>>>(p);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+template<int BITS, typename WT>
+cb200_status launch_lpn(const tiled_params &p, int sm_count, cudaStream_t stream, bool *taken) {
+    *taken = true;
+    switch (p.n / 8) {
+    case 4: return launch_one<BITS, WT, 4>(p, sm_count, stream);
+    case 8: return launch_one<BITS, WT, 8>(p, sm_count, stream);
+    case 16: return launch_one<BITS, WT, 16>(p, sm_count, stream);
+    default: *taken = false; return CB200_STATUS_SUCCESS;
+    }
+}
+
+} // namespace
+
+// Shapes the tiled kernel covers; everything else runs the warp-per-row kernel.
+bool qcsr_forward_tiled_supported(const qcsr_view &x, const dense_args &d) {
+    if (x.bits != 8 && x.bits != 4) return false;
+    if (d.n != 32 && d.n != 64 && d.n != 128) return false;
+    if (d.dense_dtype != CB200_DTYPE_BF16 && d.dense_dtype != CB200_DTYPE_F32) return false;
+    if (d.dense_dtype == CB200_DTYPE_F32 && d.n == 128) return false; // 512-byte rows: tile too short
+    if (d.dense_ld != d.n) return false;                               // W tile must be one contiguous range
+    if (reinterpret_cast<std::uintptr_t>(d.dense) % 16u != 0u) return false;
+    if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return false;
+    if (x.scales == nullptr) return false;
+    if (x.bits == 4 && x.packed_row_ptr == nullptr) return false;
+    if (x.cols > 0x7fffffff) return false;
+    return true;
+}
+
+cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                       std::int64_t row_end, int *status_word, int sm_count, cudaStream_t stream,
+                                       bool *taken) {
+    *taken = false;
+    if (!qcsr_forward_tiled_supported(x, d) || row_end <= row_begin) return CB200_STATUS_SUCCESS;
+    tiled_params p{};
+    p.row_ptr = x.row_ptr; p.packed_row_ptr = x.packed_row_ptr; p.col_idx = x.col_idx; p.packed = x.packed;
+    p.scales = x.scales; p.offsets = x.offsets; p.w = d.dense; p.y = d.out; p.y_ld = d.out_ld;
+    p.row_begin = row_begin; p.row_end = row_end; p.groups = (row_end - row_begin + kGroupRows - 1) / kGroupRows;
+    p.genes = static_cast<int>(x.cols); p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha;
+    p.beta = d.beta; p.status = status_word;
+    if (status_word != nullptr) CB200_CUDA_OK(cudaMemsetAsync(status_word, 0, sizeof(int), stream));
+    const bool bf16 = d.dense_dtype == CB200_DTYPE_BF16;
+    if (x.bits == 8) return bf16 ? launch_lpn<8, __nv_bfloat16>(p, sm_count, stream, taken) : launch_lpn<8, float>(p, sm_count, stream, taken);
+    return bf16 ? launch_lpn<4, __nv_bfloat16>(p, sm_count, stream, taken) : launch_lpn<4, float>(p, sm_count, stream, taken);
+}
+
+} // namespace cb200

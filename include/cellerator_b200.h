@@ -224,7 +224,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
 void cb200_prepared_destroy(cb200_prepared *prepared);
 /* workspace_requirement, launch_bindings.hh:67-71 */
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
-/* kernel choice made at prepare time, as text ("warp_per_row", "row_split", ...) */
+/* kernel choice made at prepare time, as text ("warp_per_row", "gene_tiled") */
 const char *cb200_prepared_schedule(const cb200_prepared *prepared);
 
 /* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch. */

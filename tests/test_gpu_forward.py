@@ -151,3 +151,41 @@ def test_full_scale_properties(cuda_device, oracle, bits, n):
         l1, _ = row_l1(oracle, sub)
         assert_forward_close(y1[r0:r1].cpu().numpy(), ref, l1, float(np.abs(w_host).max()), bf16=True)
         assert np.all(np.diff(sub["col_idx"][: int(sub["row_ptr"][1])]) > 0)   # genes ascending, distinct
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("dtype,n", [(torch.bfloat16, 64), (torch.bfloat16, 128), (torch.bfloat16, 32),
+                                     (torch.float32, 32), (torch.float32, 64)])
+@pytest.mark.parametrize("policy", [1, 2])
+def test_gene_tiled_schedule(cuda_device, oracle, monkeypatch, bits, dtype, n, policy):
+    """The shared-memory-staged kernel, forced on a small matrix that still spans several gene
+    tiles, several row groups per CTA and a ragged last group; bit-identical across row ranges
+    and to a second run, and the bounded-wait status word stays 0."""
+    monkeypatch.setenv("CB200_FWD_SCHEDULE", "gene_tiled")
+    rng = np.random.default_rng(31 * bits + n + policy)
+    rows, cols = 128 * 3 + 37, 4100
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=700, bits=bits, policy=policy))
+    x = to_dev(c, cuda_device)
+    w, w_host = dense(rng, cols, n, dtype, cuda_device)
+    op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, bits, policy, w.dtype, cuda_device,
+                          host_row_ptr=x.host_row_ptr)
+    assert op.schedule == "gene_tiled"
+    y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0
+    ref = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
+                              c["offsets"], w_host, cols)
+    l1, _ = row_l1(oracle, c)
+    assert_forward_close(y.cpu().numpy(), ref, l1, float(np.abs(w_host).max()), bf16=dtype == torch.bfloat16)
+    assert torch.equal(y, op.run(x, w, torch.empty_like(y)))
+    out = torch.full((rows, n), -3.0, device=cuda_device)
+    op.run(x, w, out, row_begin=100, row_end=300)
+    assert torch.equal(out[100:300], y[100:300]) and torch.all(out[:100] == -3.0) and torch.all(out[300:] == -3.0)
+    y0 = torch.from_numpy(rng.normal(size=(rows, n)).astype(np.float32)).to(cuda_device)
+    y1 = op.run(x, w, y0.clone(), alpha=2.0, beta=0.5)
+    assert torch.allclose(y1, 2.0 * y + 0.5 * y0, rtol=1e-5, atol=1e-6)
+    # the warp-per-row kernel agrees to rounding (different summation order)
+    monkeypatch.setenv("CB200_FWD_SCHEDULE", "warp_per_row")
+    op2 = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, bits, policy, w.dtype, cuda_device)
+    assert op2.schedule == "warp_per_row"
+    y2 = op2.run(x, w, torch.empty_like(y))
+    assert_forward_close(y2.cpu().numpy(), ref, l1, float(np.abs(w_host).max()), bf16=dtype == torch.bfloat16)

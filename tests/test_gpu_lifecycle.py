@@ -28,7 +28,7 @@ def test_prepare_run_lifecycle_and_rejections(cuda_device, problem):
     x, w, ref = problem
     op = ops.PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, 32, x.nnz, 8, 1, w.dtype, cuda_device,
                           structure_epoch=7, host_row_ptr=x.host_row_ptr, deterministic=True)
-    assert op.schedule in ("warp_per_row", "row_split")
+    assert op.schedule in ("warp_per_row", "gene_tiled")
     out = torch.zeros(x.rows, 32, device=cuda_device)
     before = capi.lib().cb200_kernel_launch_count()
     op.run(x, w, out)
