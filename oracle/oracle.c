@@ -10,7 +10,7 @@
  * link or load it.
  *
  * Pinning: every function here is compared, on random and hand-written inputs,
- * with the reference's own sources compiled in place (see build_ref.sh and
+ * with the reference's own sources compiled in place (see Makefile target `ref` and
  * ref_shim.cc) and with the known-answer vectors that the reference's tests
  * hold (tests/golden/).  Each function cites the reference file:line whose
  * behaviour it follows (paths are relative to the Cellerator project root).
