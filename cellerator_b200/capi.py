@@ -94,6 +94,7 @@ EXPORTED_SYMBOLS = [
     "cb200_dequantize_rows", "cb200_qbell_quantize_rows", "cb200_qbell_dequantize_rows",
     "cb200_backend_query", "cb200_spmm_prepare", "cb200_prepared_destroy",
     "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_spmm_run", "cb200_kernel_launch_count",
+    "cb200_qcsr_forward_static",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
 ]
@@ -134,6 +135,8 @@ def lib() -> C.CDLL:
         L.cb200_prepared_schedule.argtypes = [C.c_void_p]
         L.cb200_prepared_schedule.restype = C.c_char_p
         L.cb200_spmm_run.argtypes = [C.c_void_p, C.POINTER(Launch)]
+        L.cb200_qcsr_forward_static.argtypes = [C.POINTER(QCsr), C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
+                                                C.c_int64, C.c_float, C.c_float, C.c_int32, C.c_void_p]
         L.cb200_session_create.argtypes = [C.POINTER(SessionOptions), C.POINTER(C.c_void_p)]
         L.cb200_session_reserve_persistent.argtypes = [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]
         L.cb200_session_reserve_transient.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]

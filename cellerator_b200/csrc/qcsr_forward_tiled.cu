@@ -468,4 +468,91 @@ cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, 
     return bf16 ? launch_lpn<4, __nv_bfloat16>(p, sm_count, stream, taken) : launch_lpn<4, float>(p, sm_count, stream, taken);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same kernel for callers that must not allocate device memory.
+//
+// The gene-tiled kernel needs a little scratch in global memory (its status block).  The
+// prepared-operation path takes that from the caller's workspace.  Some callers have no way to
+// provide one: code that runs where cudaMalloc is forbidden (inside a region that must stay free
+// of allocator calls, or in a process whose memory budget is fixed up front and policed), and thin
+// foreign-language shims that can pass pointers through but own no device allocator.  For them the
+// scratch lives in a fixed array inside this library's device image.
+//
+// Consequences, all of them part of the contract:
+//  * every GPU that loads the library carries kStaticScratchBytes of it until the process exits;
+//  * the array is shared by every call on a device and keeps the previous call's contents, so each
+//    call first clears (stream-ordered) the part that must start at zero, and two calls whose
+//    kernels can overlap on the GPU (different streams, no ordering between them) race on it;
+//  * in host code the array's name is only a host-side handle, not a device address, so the address
+//    is looked up once per device with cudaGetSymbolAddress (with that device current) and cached;
+//    that look-up happens in the first call on a device, which should therefore be made before any
+//    stream capture begins.
+namespace {
+
+constexpr std::size_t kStaticScratchBytes = 256;
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::atomic<void *> g_static_scratch_address[kStaticMaxDevices];
+
+// Device address of g_static_scratch on `device` (which must be current).
+cb200_status static_scratch_on(int device, void **address) {
+    if (device < 0 || device >= kStaticMaxDevices)
+        return fail(CB200_STATUS_INVALID_STREAM, "device ordinal %d outside 0..%d", device, kStaticMaxDevices - 1);
+    void *known = g_static_scratch_address[device].load(std::memory_order_acquire);
+    if (known == nullptr) {
+        void *looked_up = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress(&looked_up, g_static_scratch);
+        if (err != cudaSuccess || looked_up == nullptr)
+            return fail(CB200_STATUS_CUDA_ERROR, "cudaGetSymbolAddress(static scratch) on device %d: %s", device,
+                        cudaGetErrorString(err));
+        g_static_scratch_address[device].store(looked_up, std::memory_order_release);
+        known = looked_up;
+    }
+    *address = known;
+    return CB200_STATUS_SUCCESS;
+}
+
+} // namespace
 } // namespace cb200
+
+extern "C" cb200_status cb200_qcsr_forward_static(const cb200_qcsr *x, const void *w, int32_t w_dtype, int64_t n,
+                                                  float *y, int64_t y_ld, float alpha, float beta, int32_t device,
+                                                  void *stream) {
+    using namespace cb200;
+    clear_error();
+    if (x == nullptr || x->version != CB200_ABI_VERSION || x->size < sizeof(cb200_qcsr))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
+    if (w == nullptr || y == nullptr || x->row_ptr == nullptr || (x->nnz != 0 && (x->col_idx == nullptr || x->packed_values == nullptr)))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "null operand");
+    if (static_cast<const void *>(y) == w) return fail(CB200_STATUS_INVALID_ARGUMENT, "output aliases the dense input");
+    if (x->rows < 0 || x->cols < 0 || n <= 0 || y_ld < n) return fail(CB200_STATUS_INVALID_SHAPE, "bad shape");
+    // scratch this kernel needs for this problem against what the fixed array holds
+    const std::size_t needed = 256; // one status block, whatever the matrix size
+    if (needed > kStaticScratchBytes)
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "needs %zu bytes of scratch, the built-in array holds %zu", needed,
+                    kStaticScratchBytes);
+    const qcsr_view view{x->rows, x->cols, x->nnz, x->bits, x->policy, x->row_ptr, x->packed_row_ptr,
+                         x->col_idx, x->packed_values, x->scales, x->offsets};
+    const dense_args d{w, n, w_dtype, y, y_ld, n, alpha, beta};
+    if (!qcsr_forward_tiled_supported(view, d))
+        return fail(CB200_STATUS_UNSUPPORTED,
+                    "outside what the allocation-free entry covers: 8/4-bit codes with per-gene scales, N in {32,64,128} "
+                    "(fp32 W: 32 or 64), W contiguous (ld == N) and 16-byte aligned, Y rows 16-byte aligned; got bits=%d N=%lld",
+                    x->bits, static_cast<long long>(n));
+    if (x->rows == 0) return CB200_STATUS_SUCCESS;
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    void *scratch = nullptr;
+    const cb200_status found = static_scratch_on(device, &scratch);
+    if (found != CB200_STATUS_SUCCESS) return found;
+    int sm_count = 0;
+    CB200_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    bool taken = false;
+    // clears the status word on the stream, then launches; nothing here allocates
+    const cb200_status st = launch_qcsr_forward_tiled(view, d, 0, x->rows, static_cast<int *>(scratch), sm_count,
+                                                      static_cast<cudaStream_t>(stream), &taken);
+    if (st != CB200_STATUS_SUCCESS) return st;
+    if (!taken) return fail(CB200_STATUS_INTERNAL_ERROR, "tiled kernel declined a shape it reports as supported");
+    return CB200_STATUS_SUCCESS;
+}

@@ -254,6 +254,34 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
 /* Number of kernel launches this library has enqueued since it was loaded (all threads). */
 uint64_t cb200_kernel_launch_count(void);
 
+/* Forward projection  Y = alpha * deq(X) * W + beta * Y  for callers that cannot allocate device
+ * memory.  (No counterpart in the Cellerator reference, whose operations take their scratch from
+ * the session or from request_scratch.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits, e.g. a latency-critical region
+ * that must stay free of allocator calls or a process whose device-memory budget is fixed and
+ * policed, and language shims that can hand pointers through but have no device allocator of
+ * their own.  Such callers cannot supply the workspace that cb200_spmm_run asks for.  Here the
+ * kernel's scratch is a fixed 256-byte array that is part of the library's device image, so the
+ * call needs only the inputs and the output; it performs no cudaMalloc / cudaFree and calls no
+ * allocating library routine.
+ *
+ * Limits and rules:
+ *  - the scratch the kernel needs must fit the 256-byte array (it does for every matrix size the
+ *    kernel accepts; a larger need is refused with CB200_STATUS_INSUFFICIENT_WORKSPACE), and the
+ *    shape must be one the gene-tiled kernel covers: 8- or 4-bit codes with per-gene scales,
+ *    n in {32, 64, 128} for bf16 W ({32, 64} for fp32 W), W contiguous (leading dimension n) and
+ *    16-byte aligned, Y rows 16-byte aligned; anything else returns CB200_STATUS_UNSUPPORTED;
+ *  - every GPU that loads the library holds the array until the process exits;
+ *  - all calls on a device share the array and it keeps the last call's contents: each call clears
+ *    what must start at zero, in stream order, and calls that may overlap on the GPU (different
+ *    streams without ordering) race on it, so serialise them;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *    with that device current) and caches it; make that first call before any stream capture.
+ * w_dtype is CB200_DTYPE_BF16 or CB200_DTYPE_F32; x, w, y are device pointers on `device`. */
+cb200_status cb200_qcsr_forward_static(const cb200_qcsr *x, const void *w, int32_t w_dtype, int64_t n, float *y,
+                                       int64_t y_ld, float alpha, float beta, int32_t device, void *stream);
+
 /* ------------------------------------------------------------------------------------ */
 /* Runtime session.  runtime::execution_session, include/Cellerator/runtime/session.cuh:106-177:
  * init -> reserve persistent / transient -> seal -> bind per launch.  After sealing nothing
