@@ -265,6 +265,9 @@ def run_ours(args):
         if transpose_reduce:
             dist.all_reduce(out, op=dist.ReduceOp.SUM)
 
+    # clocks are sampled from the warm-up on (nvidia-smi needs a moment to start); every sample is
+    # taken with the GPU under this load
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
@@ -272,7 +275,6 @@ def run_ours(args):
         dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local) if rank == 0 else None
     launches0 = L.cb200_kernel_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kstart = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]

@@ -3,9 +3,11 @@
 // lifecycle and the runtime session.  Kernels live in the other translation units.
 #include "kernels.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <vector>
 
 namespace cb200 {
 
@@ -61,6 +63,10 @@ struct cb200_prepared {
     std::uint32_t workspace_alignment;
     int sm_count;
     double mean_row_nnz, max_row_nnz;
+    // persistent state built at prepare time (persistent_kernel_state, operation_core.hh:126-129):
+    // the rows in descending order of length, on the device; null when no host row_ptr was given
+    std::int32_t *row_order;
+    std::uint64_t persistent_bytes;
 };
 
 struct cb200_session {
@@ -299,12 +305,41 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             p->schedule_name = "gene_tiled";
         }
         p->workspace_bytes = 256u; // status word of the tiled kernel
+        // The tiled kernel gives each row to one lane group, so a CTA is as slow as its longest row.
+        // With the row lengths at hand, order the rows by length once (persistent preprocessing):
+        // every CTA then works on rows of nearly equal length.
+        if (tiled && problem->host_row_ptr != nullptr && problem->m > 0 && problem->m <= 0x7fffffff) {
+            std::vector<std::int32_t> order(static_cast<std::size_t>(problem->m));
+            for (std::int64_t r = 0; r < problem->m; ++r) order[static_cast<std::size_t>(r)] = static_cast<std::int32_t>(r);
+            const std::int64_t *rp = problem->host_row_ptr;
+            std::stable_sort(order.begin(), order.end(), [rp](std::int32_t a, std::int32_t b) {
+                return rp[a + 1] - rp[a] > rp[b + 1] - rp[b];
+            });
+            device_scope scope(problem->device);
+            const std::size_t bytes = order.size() * sizeof(std::int32_t);
+            cudaError_t err = scope.status;
+            if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&p->row_order), bytes);
+            if (err == cudaSuccess) err = cudaMemcpy(p->row_order, order.data(), bytes, cudaMemcpyHostToDevice);
+            if (err != cudaSuccess) {
+                if (p->row_order != nullptr) cudaFree(p->row_order);
+                delete p;
+                return fail(CB200_STATUS_CUDA_ERROR, "row order upload: %s", cudaGetErrorString(err));
+            }
+            p->persistent_bytes = bytes;
+        }
     }
     *out = p;
     return CB200_STATUS_SUCCESS;
 }
 
-void cb200_prepared_destroy(cb200_prepared *prepared) { delete prepared; }
+void cb200_prepared_destroy(cb200_prepared *prepared) {
+    if (prepared == nullptr) return;
+    if (prepared->row_order != nullptr) {
+        device_scope scope(prepared->problem.device);
+        cudaFree(prepared->row_order);
+    }
+    delete prepared;
+}
 
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment) {
     clear_error();
@@ -376,7 +411,7 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     if (pr.projection == CB200_PROJECTION_TRANSPOSE)
         return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, launch->workspace, launch->workspace_bytes,
                                      prepared->sm_count, stream);
-    return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, nullptr, launch->workspace,
+    return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, launch->workspace,
                                prepared->sm_count, stream);
 }
 

@@ -33,8 +33,8 @@ enum class fwd_schedule : int { warp_per_row = 0, gene_tiled = 1 };
 // what it covers, and the caller then runs the warp-per-row kernel.
 bool qcsr_forward_tiled_supported(const qcsr_view &x, const dense_args &d);
 cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
-                                       std::int64_t row_end, int *status_word, int sm_count, cudaStream_t stream,
-                                       bool *taken);
+                                       std::int64_t row_end, int *status_word, const std::int32_t *row_order,
+                                       int sm_count, cudaStream_t stream, bool *taken);
 
 // Y[r,:] = alpha * sum_i deq(code_i) * W[col_i,:] + beta * Y[r,:]  for r in [row_begin,row_end)
 cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,

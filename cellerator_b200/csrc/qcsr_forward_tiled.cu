@@ -3,16 +3,25 @@
 //
 // Why: at N = 64 every stored entry needs a 128-byte row of W.  Gathered from L2 that is
 // ~25x the HBM bytes of the entry itself and the L2 -> SM path saturates long before HBM does.
-// Here a CTA owns a group of 128 cell rows and sweeps the gene axis in tiles: tile t of W
-// (tile_genes consecutive rows, 96 KB) is brought into shared memory by one bulk async copy
+// Here a CTA owns a group of cell rows and sweeps the gene axis in tiles: tile t of W
+// (tile_genes consecutive rows, 80-96 KB) is brought into shared memory by one bulk async copy
 // (cp.async.bulk, completion on an mbarrier, double buffered), the per-gene scale / zero-point
-// of the tile sit beside it, and each warp multiplies the part of its 8 rows that falls into
-// the tile (gene indices are ascending within a row, so that part is a contiguous run found by
-// comparing against the tile's upper bound).  Accumulators for the warp's 8 rows stay in
-// registers across all tiles, so W crosses L2 -> SM once per 128 rows instead of once per entry.
+// of the tile sit beside it, and the part of every row that falls into the tile is multiplied
+// (gene indices are ascending within a row, so that part is a contiguous run found by comparing
+// against the tile's upper bound).  W crosses L2 -> SM once per row group instead of once per
+// stored entry.
 //
-// Rows of a group are dealt to the 16 warps longest-first in snake order, so that the warps of a
-// CTA reach the end of each tile at about the same time.
+// Work split inside a CTA (1024 threads): a warp is cut into groups of LPN = N/8 lanes; a group
+// owns two rows outright and keeps their N accumulators in registers (8 columns per lane), so no
+// accumulator is replicated and nothing is reduced across lanes at the end.  In one iteration
+// the LPN lanes of a group fetch and decode LPN consecutive entries of the group's row, park
+// {W-row offset, value} in a per-warp staging area, and then walk them: every lane reads the
+// same entry and its own 16-byte slice of that W row.  The groups of a warp run in lockstep, so
+// rows are dealt out sorted by length: neighbouring ranks share a warp (similar trip counts), and
+// warps get one long and one short bundle (snake order) so that all warps of the CTA reach the
+// end of a tile together.  A row is worked by one lane group, so a CTA is only as fast as its
+// longest row: when the caller's prepare step supplies a length-sorted row order, every CTA gets
+// rows of nearly equal length and the CTAs take row groups from both ends of that order in turn.
 //
 // Waiting on the copy barrier is bounded: if the bound is hit a flag is raised in the status
 // word (first int of the workspace) and the kernel carries on with memory-safe indices, so it
@@ -25,11 +34,16 @@
 namespace cb200 {
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kRowsPerWarp = 8;
-constexpr int kGroupRows = kWarps * kRowsPerWarp; // 128
-constexpr int kThreads = kWarps * 32;             // 512
-constexpr int kWBufBytes = 96 * 1024;
+constexpr int kWarps = 32;
+constexpr int kThreads = kWarps * 32; // 1024
+constexpr int kRowsPerGroup = 2;
+
+// per instantiation: lanes per group -> groups per warp, rows per CTA, W buffer size
+template<int LPN> struct tile_shape {
+    static constexpr int groups_per_warp = 32 / LPN;
+    static constexpr int cta_rows = kWarps * groups_per_warp * kRowsPerGroup; // 512 / 256 / 128
+    static constexpr int wbuf_bytes = (LPN == 4 ? 80 : 96) * 1024;
+};
 
 struct tiled_params {
     const std::int64_t *row_ptr;
@@ -50,6 +64,7 @@ struct tiled_params {
     int policy;
     float alpha, beta;
     int *status;
+    const std::int32_t *row_order; // optional: rows in processing order (length-sorted), else natural order
 };
 
 __device__ __forceinline__ std::uint32_t smem_u32(const void *p) {
@@ -96,9 +111,6 @@ __device__ __forceinline__ void fma8_packed(float (&acc)[8], float v, const floa
     }
 }
 
-// The 8 columns of a staged W row held by this lane.  bf16: 8 consecutive columns (one 16-byte
-// read).  fp32: columns [4t,4t+4) and [N/2+4t, N/2+4t+4) so that both 16-byte reads of a lane
-// group are contiguous across its lanes (no bank conflict).
 // Shared-memory accesses by 32-bit shared-window address (keeps 64-bit pointer arithmetic out of
 // the inner loop).  volatile: they stay ordered against the staging store and each other.
 __device__ __forceinline__ uint4 lds_b32x4(std::uint32_t addr) {
@@ -115,7 +127,10 @@ __device__ __forceinline__ void sts_b32x2(std::uint32_t addr, int a, float b) {
     asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(__float_as_int(b)) : "memory");
 }
 
-// `addr` = shared address of this lane's slice of a staged W row (row start + t * 16).
+// The 8 columns of a staged W row held by a lane; `addr` = row start + t * 16 for lane t of the
+// group.  bf16: 8 consecutive columns (one 16-byte read).  fp32: columns [4t, 4t+4) and
+// [N/2 + 4t, N/2 + 4t + 4), so that both 16-byte reads of a group are contiguous across its lanes
+// (no bank conflict).
 template<typename WT, int LPN>
 __device__ __forceinline__ void load_w_smem(std::uint32_t addr, float (&w)[8]) {
     if constexpr (sizeof(WT) == 2) {
@@ -134,30 +149,44 @@ __device__ __forceinline__ void load_w_smem(std::uint32_t addr, float (&w)[8]) {
 
 template<int BITS, typename WT, int LPN>
 __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled_params p) {
+    using shape = tile_shape<LPN>;
     constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT)); // bytes of one W row
-    constexpr int NPS = 32 / LPN;                              // entries served per step
+    constexpr int GPW = shape::groups_per_warp;
+    constexpr int CTA_ROWS = shape::cta_rows;
+    constexpr int WBUF = shape::wbuf_bytes;
+    constexpr int BUNDLES = CTA_ROWS / GPW;                    // 2 * kWarps
+    constexpr unsigned GROUP_MASK = LPN == 32 ? 0xffffffffu : ((1u << LPN) - 1u);
     extern __shared__ __align__(128) unsigned char smem[];
     const int tile_genes = p.tile_genes;
-    unsigned char *wbuf = smem;                                                  // [2][kWBufBytes]
-    float2 *sc = reinterpret_cast<float2 *>(smem + 2 * kWBufBytes);              // [2][tile_genes] {scale, offset}
-    float2 *stage = sc + 2 * tile_genes;                                         // [kWarps][32] {gene row offset, value}
-    int4 *meta = reinterpret_cast<int4 *>(stage + kWarps * 32);                  // [kWarps][8] {start, end, packed start, row}
-    float *rowoff = reinterpret_cast<float *>(meta + kGroupRows);                // [kWarps][8]
-    int *lens = reinterpret_cast<int *>(rowoff + kGroupRows);                    // [128]
-    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(lens + kGroupRows);  // [2]
+    unsigned char *wbuf = smem;                                                  // [2][WBUF]
+    float2 *sc = reinterpret_cast<float2 *>(smem + 2 * WBUF);                    // [2][tile_genes] {scale, offset}
+    float2 *stage = sc + 2 * tile_genes;                                         // [kWarps][32] {W row offset, value}
+    int4 *meta = reinterpret_cast<int4 *>(stage + kWarps * 32);                  // [CTA_ROWS] {entry start lo, hi, length, row}
+    longlong2 *meta2 = reinterpret_cast<longlong2 *>(meta + CTA_ROWS);           // [CTA_ROWS] {packed byte start, unused}
+    float *rowoff = reinterpret_cast<float *>(meta2 + CTA_ROWS);                 // [CTA_ROWS]
+    int *lens = reinterpret_cast<int *>(rowoff + CTA_ROWS);                      // [CTA_ROWS]
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(lens + CTA_ROWS);    // [2]
     int *abort_flag = reinterpret_cast<int *>(bars + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int group_lane = lane / LPN, t_in_group = lane % LPN;
+    const int g = lane / LPN, j = lane % LPN; // group within the warp, lane within the group
     const bool row_policy = p.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
-    const std::int64_t my_groups = (p.groups - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    // Row groups are taken in rounds of gridDim.x; odd rounds run through the CTAs backwards, so that
+    // with a length-sorted row order every CTA receives the same mix of long and short groups.
+    auto group_of_round = [&](std::int64_t round) -> std::int64_t {
+        const std::int64_t pos = (round & 1) ? static_cast<std::int64_t>(gridDim.x) - 1 - blockIdx.x : blockIdx.x;
+        return round * gridDim.x + pos;
+    };
+    const std::int64_t rounds = (p.groups + gridDim.x - 1) / gridDim.x;
+    std::int64_t my_groups = 0;
+    for (std::int64_t r = 0; r < rounds; ++r) my_groups += group_of_round(r) < p.groups ? 1 : 0;
     const std::int64_t total_tiles = my_groups * p.tiles;
-    const std::uint32_t bar_addr[2] = {smem_u32(bars), smem_u32(bars + 1)};
-    const std::uint32_t wbuf_addr[2] = {smem_u32(wbuf), smem_u32(wbuf + kWBufBytes)};
+    const std::int64_t rows_total = p.row_end - p.row_begin;
+    const std::uint32_t bar0 = smem_u32(bars), wbuf0 = smem_u32(wbuf);
 
     if (tid == 0) {
-        mbar_init(bar_addr[0], 1);
-        mbar_init(bar_addr[1], 1);
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -165,13 +194,13 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
 
     auto issue_tile = [&](std::int64_t q) { // thread 0 only
         const int t = static_cast<int>(q % p.tiles);
-        const int b = static_cast<int>(q & 1);
+        const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
         const int g0 = t * tile_genes;
         const int count = min(tile_genes, p.genes - g0);
         const std::uint32_t bytes = static_cast<std::uint32_t>(count) * RB;
-        mbar_expect_tx(bar_addr[b], bytes);
-        bulk_copy_g2s(wbuf_addr[b], static_cast<const unsigned char *>(p.w) + static_cast<std::size_t>(g0) * RB, bytes,
-                      bar_addr[b]);
+        mbar_expect_tx(bar0 + 8 * b, bytes);
+        bulk_copy_g2s(wbuf0 + b * WBUF, static_cast<const unsigned char *>(p.w) + static_cast<std::size_t>(g0) * RB, bytes,
+                      bar0 + 8 * b);
     };
     if (tid == 0) {
         if (total_tiles > 0) issue_tile(0);
@@ -182,78 +211,97 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
         sc[i] = make_float2(__ldg(p.scales + i), (!row_policy && p.offsets != nullptr) ? __ldg(p.offsets + i) : 0.0f);
     __syncthreads();
 
-    constexpr int SC_PER_THREAD = (kWBufBytes / RB + kThreads - 1) / kThreads;
-    std::int64_t q = 0;
-    for (std::int64_t gi = 0; gi < my_groups; ++gi) {
-        const std::int64_t group = blockIdx.x + gi * gridDim.x;
-        const std::int64_t grow0 = p.row_begin + group * kGroupRows;
-        const int grows = static_cast<int>(min(static_cast<std::int64_t>(kGroupRows), p.row_end - grow0));
-        const std::int64_t gbase = __ldg(p.row_ptr + grow0);
-        const std::int64_t pbase = p.packed_row_ptr != nullptr ? __ldg(p.packed_row_ptr + grow0) : gbase;
-        const std::int32_t *col_g = p.col_idx + gbase;
-        const std::uint8_t *packed_g = p.packed + pbase;
+    constexpr int SC_PER_THREAD = (WBUF / RB + kThreads - 1) / kThreads;
+    const int slot0 = (warp * GPW + g) * kRowsPerGroup; // this group's two rows in meta[]
+    const std::uint32_t stage_wr = smem_u32(stage) + warp * 256 + lane * 8;
+    const std::uint32_t stage_rd = smem_u32(stage) + warp * 256 + g * LPN * 8;
+    const std::uint32_t sc0 = smem_u32(sc);
 
-        // ---- deal the group's rows to warps: longest first, snake order
-        if (tid < kGroupRows)
-            lens[tid] = tid < grows ? static_cast<int>(__ldg(p.row_ptr + grow0 + tid + 1) - __ldg(p.row_ptr + grow0 + tid)) : -1;
+    std::int64_t q = 0;
+    for (std::int64_t round = 0; round < rounds; ++round) {
+        const std::int64_t group = group_of_round(round);
+        if (group >= p.groups) continue;
+        const std::int64_t first = group * CTA_ROWS; // position of this group's first row in the processing order
+
+        // ---- deal the rows: rank by length (longest first); GPW neighbouring ranks form a bundle
+        //      that shares a warp; bundle k goes to warp k (first row) or warp BUNDLES-1-k (second)
+        std::int64_t my_row = -1;
+        if (tid < CTA_ROWS && first + tid < rows_total)
+            my_row = p.row_order != nullptr ? static_cast<std::int64_t>(__ldg(p.row_order + first + tid)) : p.row_begin + first + tid;
+        if (tid < CTA_ROWS)
+            lens[tid] = my_row >= 0 ? static_cast<int>(__ldg(p.row_ptr + my_row + 1) - __ldg(p.row_ptr + my_row)) : -1;
         __syncthreads();
-        if (tid < kGroupRows) {
+        if (tid < CTA_ROWS) {
             const int mine = lens[tid];
             int rank = 0;
-            for (int j = 0; j < kGroupRows; ++j) {
-                const int other = lens[j];
-                rank += (other > mine || (other == mine && j < tid)) ? 1 : 0;
+            for (int k = 0; k < CTA_ROWS; ++k) {
+                const int other = lens[k];
+                rank += (other > mine || (other == mine && k < tid)) ? 1 : 0;
             }
-            const int round = rank / kWarps, pos = rank % kWarps;
-            const int w = (round & 1) ? kWarps - 1 - pos : pos;
+            const int bundle = rank / GPW, gg = rank % GPW;
+            const int w = bundle < kWarps ? bundle : BUNDLES - 1 - bundle;
+            const int rr = bundle < kWarps ? 0 : 1;
             int4 m = make_int4(0, 0, 0, -1);
+            longlong2 m2 = make_longlong2(0, 0);
             float ro = 0.0f;
-            if (tid < grows) {
-                const std::int64_t rs = __ldg(p.row_ptr + grow0 + tid);
-                m.x = static_cast<int>(rs - gbase);
-                m.y = m.x + mine;
-                m.z = p.packed_row_ptr != nullptr ? static_cast<int>(__ldg(p.packed_row_ptr + grow0 + tid) - pbase) : m.x;
-                m.w = tid;
-                if (row_policy && p.offsets != nullptr) ro = __ldg(p.offsets + grow0 + tid);
+            if (my_row >= 0) {
+                const std::int64_t rs = __ldg(p.row_ptr + my_row);
+                m.x = static_cast<int>(static_cast<std::uint64_t>(rs) & 0xffffffffu);
+                m.y = static_cast<int>(static_cast<std::uint64_t>(rs) >> 32);
+                m.z = mine;
+                m.w = static_cast<int>(my_row - p.row_begin);
+                m2.x = p.packed_row_ptr != nullptr ? __ldg(p.packed_row_ptr + my_row) : rs;
+                if (row_policy && p.offsets != nullptr) ro = __ldg(p.offsets + my_row);
             }
-            meta[w * kRowsPerWarp + round] = m;
-            rowoff[w * kRowsPerWarp + round] = ro;
+            meta[(w * GPW + gg) * kRowsPerGroup + rr] = m;
+            meta2[(w * GPW + gg) * kRowsPerGroup + rr] = m2;
+            rowoff[(w * GPW + gg) * kRowsPerGroup + rr] = ro;
         }
         __syncthreads();
 
-        // Per row: cursor, and the (gene, code byte) of the 32 entries at the cursor, fetched one
-        // tile ahead so that no global-memory latency sits in front of a row's visit.
-        int cur[kRowsPerWarp];
-        int gene_pf[kRowsPerWarp];
-        unsigned code_pf[kRowsPerWarp];
-        float acc[kRowsPerWarp][8];
-        auto fetch_chunk = [&](const int4 &m, int c, int &gene, unsigned &code) {
+        // Per row of this group: cursor (entries consumed), and the (gene, code byte) of entry
+        // cursor + j, fetched ahead so that no global-memory latency sits in front of a visit.
+        int cur[kRowsPerGroup];
+        int gene_pf[kRowsPerGroup];
+        unsigned code_pf[kRowsPerGroup];
+        float acc[kRowsPerGroup][8];
+        auto fetch_entry = [&](const std::int32_t *cols, const std::uint8_t *codes, int len, int at, int &gene, unsigned &code) {
             gene = 0x7fffffff;
             code = 0u;
-            if (lane < m.y - c) {
-                gene = __ldg(col_g + c + lane);
-                const int local = c - m.x + lane;
-                code = __ldg(packed_g + m.z + (BITS == 8 ? local : (local >> 1)));
+            if (at + j < len) {
+                gene = __ldg(cols + at + j);
+                code = __ldg(codes + (BITS == 8 ? at + j : ((at + j) >> 1)));
             }
         };
+        auto row_pointers = [&](int slot, const std::int32_t *&cols, const std::uint8_t *&codes, int &len) {
+            const int4 m = meta[slot];
+            const std::int64_t start = static_cast<std::int64_t>((static_cast<std::uint64_t>(static_cast<std::uint32_t>(m.y)) << 32) |
+                                                                 static_cast<std::uint32_t>(m.x));
+            cols = p.col_idx + start;
+            codes = p.packed + meta2[slot].x;
+            len = m.z;
+        };
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) {
-            const int4 m = meta[warp * kRowsPerWarp + r];
-            cur[r] = m.x;
-            fetch_chunk(m, m.x, gene_pf[r], code_pf[r]);
+        for (int rr = 0; rr < kRowsPerGroup; ++rr) {
+            const std::int32_t *cols;
+            const std::uint8_t *codes;
+            int len;
+            row_pointers(slot0 + rr, cols, codes, len);
+            cur[rr] = 0;
+            fetch_entry(cols, codes, len, 0, gene_pf[rr], code_pf[rr]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+            for (int i = 0; i < 8; ++i) acc[rr][i] = 0.0f;
         }
 
         for (int t = 0; t < p.tiles; ++t, ++q) {
-            const int b = static_cast<int>(q & 1);
+            const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
             const int g0 = t * tile_genes;
             const int g1 = min(p.genes, g0 + tile_genes);
             // ---- wait for the tile's bytes (bounded)
             {
                 const std::uint32_t parity = static_cast<std::uint32_t>((q >> 1) & 1);
                 int spins = 0;
-                while (!mbar_try_wait(bar_addr[b], parity)) {
+                while (!mbar_try_wait(bar0 + 8 * b, parity)) {
                     if (++spins > (1 << 22)) {
                         *abort_flag = 1;
                         break;
@@ -277,84 +325,59 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
                     }
                 }
             }
-            // 32-bit shared-window addresses for everything the inner loop touches
-            const std::uint32_t w_lane = wbuf_addr[b] + t_in_group * 16;             // this lane's slice of W row 0
-            const std::uint32_t sc_addr = smem_u32(sc) + b * tile_genes * 8;
-            const std::uint32_t stage_addr = smem_u32(stage) + warp * 256;
-            const std::uint32_t stage_rd = stage_addr + group_lane * 8;              // entry of step 0 for this lane
+            const std::uint32_t w_lane = wbuf0 + b * WBUF + j * 16; // this lane's slice of W row 0 of the tile
+            const std::uint32_t sc_addr = sc0 + b * tile_genes * 8;
 
-            // ---- the warp's 8 rows: the run of each row that falls into [g0, g1)
+            // ---- this group's two rows: the run of each that falls into [g0, g1)
 #pragma unroll
-            for (int r = 0; r < kRowsPerWarp; ++r) {
-                const int4 m = meta[warp * kRowsPerWarp + r];
-                const float row_offset = rowoff[warp * kRowsPerWarp + r];
-                int c = cur[r];
-                int gene = gene_pf[r];
-                unsigned code_byte = code_pf[r];
-                bool refetch = false;
+            for (int rr = 0; rr < kRowsPerGroup; ++rr) {
+                const std::int32_t *cols;
+                const std::uint8_t *codes;
+                int len;
+                row_pointers(slot0 + rr, cols, codes, len);
+                const float row_offset = rowoff[slot0 + rr];
+                int c = cur[rr];
+                int gene = gene_pf[rr];
+                unsigned code_byte = code_pf[rr];
                 while (true) {
-                    const int count = __popc(__ballot_sync(0xffffffffu, gene < g1));
-                    if (count == 0) break;
-                    // a full chunk with more of the row behind it: start fetching the following chunk now
-                    const bool more = count == 32 && c + 32 < m.y;
-                    int gene2 = 0x7fffffff;
-                    unsigned code2 = 0u;
-                    if (more) fetch_chunk(m, c + 32, gene2, code2);
-                    // decode without branches: lanes past `count` read a clamped (valid) tile slot and
-                    // stage value 0
-                    const int gl = min(max(gene - g0, 0), tile_genes - 1); // in-tile even for unsorted input
+                    const unsigned in_tile = __ballot_sync(0xffffffffu, gene < g1);
+                    if (in_tile == 0u) break;                                  // no group of the warp has entries left here
+                    const int count = __popc((in_tile >> (g * LPN)) & GROUP_MASK); // this group's entries (a prefix)
+                    const int most = __reduce_max_sync(0xffffffffu, count);
+                    // the window after this one; groups with nothing here keep theirs
+                    int gene_n = gene;
+                    unsigned code_n = code_byte;
+                    if (count > 0) fetch_entry(cols, codes, len, c + count, gene_n, code_n);
+                    // Decode entry c + j without branches.  Lanes past `count` stage value 0 against a
+                    // row of the tile that is certainly loaded; their product adds exactly 0 for finite W.
+                    const int gl = min(max(gene - g0, 0), g1 - g0 - 1);       // in-tile even for unsorted input
                     unsigned code = code_byte;
-                    if constexpr (BITS == 4) code = ((c - m.x + lane) & 1) ? (code_byte >> 4) : (code_byte & 0xfu);
+                    if constexpr (BITS == 4) code = ((c + j) & 1) ? (code_byte >> 4) : (code_byte & 0xfu);
                     const float2 so = lds_f32x2(sc_addr + gl * 8);
                     const float decoded = fmaf(static_cast<float>(code), so.x, row_policy ? row_offset : so.y);
-                    const float value = lane < count ? decoded : 0.0f;
                     __syncwarp();
-                    sts_b32x2(stage_addr + lane * 8, gl * RB, value);
+                    sts_b32x2(stage_wr, gl * RB, j < count ? decoded : 0.0f);
                     __syncwarp();
-                    if (count == 32) {
 #pragma unroll
-                        for (int step = 0; step < LPN; ++step) {
-                            const float2 e = lds_f32x2(stage_rd + step * NPS * 8);
-                            float wv[8];
-                            load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
-                            fma8_packed(acc[r], e.y, wv);
-                        }
-                    } else {
-                        // whole steps first, then one step in which only some lane groups have an entry
-                        const int whole = count / NPS;
-                        for (int step = 0; step < whole; ++step) {
-                            const float2 e = lds_f32x2(stage_rd + step * NPS * 8);
-                            float wv[8];
-                            load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
-                            fma8_packed(acc[r], e.y, wv);
-                        }
-                        if (whole * NPS + group_lane < count) {
-                            const float2 e = lds_f32x2(stage_rd + whole * NPS * 8);
-                            float wv[8];
-                            load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
-                            fma8_packed(acc[r], e.y, wv);
-                        }
+                    for (int s = 0; s < LPN; ++s) {
+                        if (s >= most) break;
+                        const float2 e = lds_f32x2(stage_rd + s * 8);
+                        float wv[8];
+                        load_w_smem<WT, LPN>(w_lane + __float_as_int(e.x), wv);
+                        fma8_packed(acc[rr], e.y, wv);
                     }
                     c += count;
-                    if (!more) {
-                        refetch = true; // the cursor moved into (or past) the held chunk
-                        break;
-                    }
-                    gene = gene2;
-                    code_byte = code2;
+                    gene = gene_n;
+                    code_byte = code_n;
                 }
-                cur[r] = c;
-                if (refetch) {
-                    fetch_chunk(m, c, gene_pf[r], code_pf[r]); // all lanes idle once the row is finished
-                } else {
-                    gene_pf[r] = gene; // the held chunk starts at the cursor: keep it for the next tile
-                    code_pf[r] = code_byte;
-                }
+                cur[rr] = c;
+                gene_pf[rr] = gene;
+                code_pf[rr] = code_byte;
             }
 
             // ---- publish the next tile's scale / zero-point, release this tile's buffer
             if (has_next) {
-                float2 *sc_next = sc + (b ^ 1) * tile_genes;
+                float2 *sc_next = sc + (b ^ 1u) * tile_genes;
 #pragma unroll
                 for (int k = 0; k < SC_PER_THREAD; ++k) {
                     const int local = tid + k * kThreads;
@@ -368,21 +391,16 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
             }
         }
 
-        // ---- combine the lane groups' partial sums and write the 8 rows
+        // ---- every lane writes its 8 columns of its group's two rows
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) {
-#pragma unroll
-            for (int off = LPN; off < 32; off <<= 1) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], off);
-            }
-            const int row_local = meta[warp * kRowsPerWarp + r].w;
-            if (lane < LPN && row_local >= 0) {
-                float *out = p.y + (grow0 + row_local) * p.y_ld;
-                float *out_a = out + (sizeof(WT) == 2 ? t_in_group * 8 : t_in_group * 4);
-                float *out_b = sizeof(WT) == 2 ? out_a + 4 : out + LPN * 4 + t_in_group * 4;
-                float4 lo = make_float4(p.alpha * acc[r][0], p.alpha * acc[r][1], p.alpha * acc[r][2], p.alpha * acc[r][3]);
-                float4 hi = make_float4(p.alpha * acc[r][4], p.alpha * acc[r][5], p.alpha * acc[r][6], p.alpha * acc[r][7]);
+        for (int rr = 0; rr < kRowsPerGroup; ++rr) {
+            const int row_local = meta[slot0 + rr].w; // row - row_begin, or -1 for an empty slot
+            if (row_local >= 0) {
+                float *out = p.y + (p.row_begin + row_local) * p.y_ld;
+                float *out_a = out + (sizeof(WT) == 2 ? j * 8 : j * 4);
+                float *out_b = sizeof(WT) == 2 ? out_a + 4 : out + LPN * 4 + j * 4;
+                float4 lo = make_float4(p.alpha * acc[rr][0], p.alpha * acc[rr][1], p.alpha * acc[rr][2], p.alpha * acc[rr][3]);
+                float4 hi = make_float4(p.alpha * acc[rr][4], p.alpha * acc[rr][5], p.alpha * acc[rr][6], p.alpha * acc[rr][7]);
                 if (p.beta != 0.0f) {
                     const float4 a = *reinterpret_cast<const float4 *>(out_a);
                     const float4 bb = *reinterpret_cast<const float4 *>(out_b);
@@ -402,17 +420,20 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
 
 template<typename WT, int LPN>
 constexpr std::size_t tiled_smem_bytes() {
+    using shape = tile_shape<LPN>;
     constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT));
-    constexpr int tile_genes = kWBufBytes / RB;
-    return 2 * kWBufBytes + 2 * tile_genes * sizeof(float2) + kWarps * 32 * sizeof(float2) + kGroupRows * sizeof(int4) +
-           kGroupRows * sizeof(float) + kGroupRows * sizeof(int) + 2 * sizeof(std::uint64_t) + 16;
+    constexpr int tile_genes = shape::wbuf_bytes / RB;
+    return 2 * shape::wbuf_bytes + 2 * tile_genes * sizeof(float2) + kWarps * 32 * sizeof(float2) +
+           shape::cta_rows * (sizeof(int4) + sizeof(longlong2) + sizeof(float) + sizeof(int)) + 2 * sizeof(std::uint64_t) + 16;
 }
 
 template<int BITS, typename WT, int LPN>
 cb200_status launch_one(tiled_params p, int sm_count, cudaStream_t stream) {
+    using shape = tile_shape<LPN>;
     constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT));
-    p.tile_genes = kWBufBytes / RB;
+    p.tile_genes = shape::wbuf_bytes / RB;
     p.tiles = (p.genes + p.tile_genes - 1) / p.tile_genes;
+    p.groups = (p.row_end - p.row_begin + shape::cta_rows - 1) / shape::cta_rows;
     constexpr std::size_t smem = tiled_smem_bytes<WT, LPN>();
     CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_tiled_kernel<BITS, WT, LPN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
@@ -452,16 +473,18 @@ bool qcsr_forward_tiled_supported(const qcsr_view &x, const dense_args &d) {
 }
 
 cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
-                                       std::int64_t row_end, int *status_word, int sm_count, cudaStream_t stream,
-                                       bool *taken) {
+                                       std::int64_t row_end, int *status_word, const std::int32_t *row_order,
+                                       int sm_count, cudaStream_t stream, bool *taken) {
     *taken = false;
     if (!qcsr_forward_tiled_supported(x, d) || row_end <= row_begin) return CB200_STATUS_SUCCESS;
     tiled_params p{};
     p.row_ptr = x.row_ptr; p.packed_row_ptr = x.packed_row_ptr; p.col_idx = x.col_idx; p.packed = x.packed;
     p.scales = x.scales; p.offsets = x.offsets; p.w = d.dense; p.y = d.out; p.y_ld = d.out_ld;
-    p.row_begin = row_begin; p.row_end = row_end; p.groups = (row_end - row_begin + kGroupRows - 1) / kGroupRows;
+    p.row_begin = row_begin; p.row_end = row_end; p.groups = 0; // set per instantiation
     p.genes = static_cast<int>(x.cols); p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha;
     p.beta = d.beta; p.status = status_word;
+    // a row order describes the whole matrix; a partial row range falls back to natural order
+    p.row_order = (row_begin == 0 && row_end == x.rows) ? row_order : nullptr;
     if (status_word != nullptr) CB200_CUDA_OK(cudaMemsetAsync(status_word, 0, sizeof(int), stream));
     const bool bf16 = d.dense_dtype == CB200_DTYPE_BF16;
     if (x.bits == 8) return bf16 ? launch_lpn<8, __nv_bfloat16>(p, sm_count, stream, taken) : launch_lpn<8, float>(p, sm_count, stream, taken);
@@ -550,7 +573,7 @@ extern "C" cb200_status cb200_qcsr_forward_static(const cb200_qcsr *x, const voi
     CB200_CUDA_OK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
     bool taken = false;
     // clears the status word on the stream, then launches; nothing here allocates
-    const cb200_status st = launch_qcsr_forward_tiled(view, d, 0, x->rows, static_cast<int *>(scratch), sm_count,
+    const cb200_status st = launch_qcsr_forward_tiled(view, d, 0, x->rows, static_cast<int *>(scratch), nullptr, sm_count,
                                                       static_cast<cudaStream_t>(stream), &taken);
     if (st != CB200_STATUS_SUCCESS) return st;
     if (!taken) return fail(CB200_STATUS_INTERNAL_ERROR, "tiled kernel declined a shape it reports as supported");
