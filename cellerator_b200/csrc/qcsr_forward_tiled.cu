@@ -93,7 +93,40 @@ __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src
                  : "memory");
 }
 
+#ifndef CB200_CVT_MODE
+#define CB200_CVT_MODE 0
+#endif
+#ifndef CB200_FMA_MODE
+#define CB200_FMA_MODE 0
+#endif
+
+// bf16 pair -> two floats (exact).  Three spellings (shift + mask, byte permute + mask, two byte
+// permutes) and scalar vs packed FMAs were timed against each other on the 1,000,000-cell
+// matrix: all within 3 % (19.7 - 20.6 ms), i.e. the kernel is not bound by the arithmetic pipes.
+__device__ __forceinline__ void widen_bf16x2(std::uint32_t packed, float &lo, float &hi) {
+#if CB200_CVT_MODE == 0
+    lo = __uint_as_float(packed << 16);
+    hi = __uint_as_float(packed & 0xffff0000u);
+#elif CB200_CVT_MODE == 1
+    std::uint32_t l;
+    asm("prmt.b32 %0, %1, 0, 0x1044;" : "=r"(l) : "r"(packed));
+    lo = __uint_as_float(l);
+    hi = __uint_as_float(packed & 0xffff0000u);
+#else
+    std::uint32_t l, h;
+    asm("prmt.b32 %0, %1, 0, 0x1044;" : "=r"(l) : "r"(packed));
+    asm("prmt.b32 %0, %1, 0, 0x3244;" : "=r"(h) : "r"(packed));
+    lo = __uint_as_float(l);
+    hi = __uint_as_float(h);
+#endif
+}
+
 __device__ __forceinline__ void fma8_packed(float (&acc)[8], float v, const float (&w)[8]) {
+#if CB200_FMA_MODE == 1
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(v, w[i], acc[i]);
+    return;
+#endif
     const float2 vv = make_float2(v, v);
     unsigned long long vp;
     memcpy(&vp, &vv, 8);
@@ -135,10 +168,10 @@ template<typename WT, int LPN>
 __device__ __forceinline__ void load_w_smem(std::uint32_t addr, float (&w)[8]) {
     if constexpr (sizeof(WT) == 2) {
         const uint4 a = lds_b32x4(addr);
-        bf16x2_to_f32(a.x, w[0], w[1]);
-        bf16x2_to_f32(a.y, w[2], w[3]);
-        bf16x2_to_f32(a.z, w[4], w[5]);
-        bf16x2_to_f32(a.w, w[6], w[7]);
+        widen_bf16x2(a.x, w[0], w[1]);
+        widen_bf16x2(a.y, w[2], w[3]);
+        widen_bf16x2(a.z, w[4], w[5]);
+        widen_bf16x2(a.w, w[6], w[7]);
     } else {
         const uint4 a = lds_b32x4(addr);
         const uint4 b = lds_b32x4(addr + LPN * 16);
@@ -160,8 +193,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
     const int tile_genes = p.tile_genes;
     unsigned char *wbuf = smem;                                                  // [2][WBUF]
     float2 *sc = reinterpret_cast<float2 *>(smem + 2 * WBUF);                    // [2][tile_genes] {scale, offset}
-    float2 *stage = sc + 2 * tile_genes;                                         // [kWarps][32] {W row offset, value}
-    int4 *meta = reinterpret_cast<int4 *>(stage + kWarps * 32);                  // [CTA_ROWS] {entry start lo, hi, length, row}
+    float2 *stage = sc + 2 * tile_genes;                                         // [kWarps][40] {W row offset, value}
+    int4 *meta = reinterpret_cast<int4 *>(stage + kWarps * 40);                  // [CTA_ROWS] {entry start lo, hi, length, row}
     longlong2 *meta2 = reinterpret_cast<longlong2 *>(meta + CTA_ROWS);           // [CTA_ROWS] {packed byte start, unused}
     float *rowoff = reinterpret_cast<float *>(meta2 + CTA_ROWS);                 // [CTA_ROWS]
     int *lens = reinterpret_cast<int *>(rowoff + CTA_ROWS);                      // [CTA_ROWS]
@@ -213,8 +246,10 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
 
     constexpr int SC_PER_THREAD = (WBUF / RB + kThreads - 1) / kThreads;
     const int slot0 = (warp * GPW + g) * kRowsPerGroup; // this group's two rows in meta[]
-    const std::uint32_t stage_wr = smem_u32(stage) + warp * 256 + lane * 8;
-    const std::uint32_t stage_rd = smem_u32(stage) + warp * 256 + g * LPN * 8;
+    // staging area of a warp: the groups' entry lists sit (LPN + 1) slots apart, so that the four
+    // (two, eight) groups read entry s of their lists from distinct banks in one pass
+    const std::uint32_t stage_rd = smem_u32(stage) + warp * 320 + g * (LPN + 1) * 8;
+    const std::uint32_t stage_wr = stage_rd + j * 8;
     const std::uint32_t sc0 = smem_u32(sc);
 
     std::int64_t q = 0;
@@ -423,7 +458,7 @@ constexpr std::size_t tiled_smem_bytes() {
     using shape = tile_shape<LPN>;
     constexpr int RB = LPN * 8 * static_cast<int>(sizeof(WT));
     constexpr int tile_genes = shape::wbuf_bytes / RB;
-    return 2 * shape::wbuf_bytes + 2 * tile_genes * sizeof(float2) + kWarps * 32 * sizeof(float2) +
+    return 2 * shape::wbuf_bytes + 2 * tile_genes * sizeof(float2) + kWarps * 40 * sizeof(float2) +
            shape::cta_rows * (sizeof(int4) + sizeof(longlong2) + sizeof(float) + sizeof(int)) + 2 * sizeof(std::uint64_t) + 16;
 }
 
