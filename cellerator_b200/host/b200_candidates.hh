@@ -1,0 +1,85 @@
+// Cellerator operation-core candidates backed by libcellerator_b200.so.
+//
+// This header and b200_candidates.cc are the host side of the backend in the reference's own
+// language and against the reference's own contracts: they compile against the Cellerator
+// headers (-I<cellerator>/include) and fill core::operation_candidate records
+// (include/Cellerator/compute/math/operation_core/operation_core.hh:195-207) whose
+// supports_numeric / prepare / run call the C ABI of include/cellerator_b200.h.  They are what a
+// Cellerator maintainer adds to the tree to register the backend; nothing in them is a copy of
+// Cellerator code.
+//
+// The operation core passes no shapes to prepare() -- only identities -- so the binding keeps a
+// small projection catalog: the owner of a structure registers, under the projection's runtime
+// handle, the dimensions and axis identities of the operation; prepare() looks them up.
+#pragma once
+
+#include <Cellerator/compute/math/operation_core/operation_core.hh>
+#include <Cellerator/planner/end_to_end_planner.hh>
+
+#include <cellerator_b200.h>
+
+#include <cstdint>
+
+namespace cellerator_b200::host {
+
+namespace core = ::cellerator::compute::math::core;
+namespace ex = ::cellerator::execution;
+
+// Device arrays of a quantized CSR structure: what sparse_relation_view.projection_data points at
+// for the CSR and transpose projections (operands.hh:97-107).
+struct csr_projection_data {
+    std::int64_t rows, cols, nnz;
+    const std::int64_t *row_ptr;
+    const std::int64_t *packed_row_ptr; // null for 8-bit codes
+    const std::int32_t *col_idx;
+};
+
+// Same for the Blocked-ELL projection.
+struct bell_projection_data {
+    std::int64_t rows, cols;
+    std::int32_t block_size, ell_cols;
+    std::int64_t row_stride_bytes;
+    const std::uint32_t *block_col_idx;
+};
+
+// One catalog entry = everything prepare() needs that the operation core does not carry.
+struct projection_catalog_entry {
+    ex::projection_handle projection{}; // key
+    std::int32_t projection_kind = 0;   // CB200_PROJECTION_*
+    std::int64_t m = 0, k = 0, n = 0, nnz = 0;
+    std::int32_t bits = 8;
+    std::int32_t decode_policy = CB200_DECODE_PER_GENE_AFFINE;
+    std::int32_t dense_dtype = CB200_DTYPE_BF16;
+    std::int32_t device = 0;
+    const std::int64_t *host_row_ptr = nullptr; // optional, for the row schedule
+    ex::axis_identity cells{}, genes{}, latent{};
+};
+
+inline constexpr std::uint32_t projection_catalog_capacity = 64u;
+
+// Returns false when the catalog is full or the handle is invalid.  Re-registering a handle
+// replaces its entry.  Callers serialise mutation (the reference's registries do the same).
+bool register_projection(const projection_catalog_entry &entry) noexcept;
+void clear_projection_catalog() noexcept;
+
+core::operation_candidate quantized_csr_forward_candidate() noexcept;
+core::operation_candidate quantized_csr_transpose_candidate() noexcept;
+core::operation_candidate quantized_blocked_ell_candidate() noexcept;
+
+// Registers the three candidates; returns the first failing status.
+core::operation_status register_all(core::candidate_registry *registry) noexcept;
+
+// Releases what prepare() attached to a prepared operation (the cb200_prepared handle and the
+// binding-contract arrays).  The operation core has no destroy hook: the plan owner calls this.
+void release_prepared(core::prepared_operation *prepared) noexcept;
+
+// planner_candidate record (end_to_end_planner.hh:118-126) with analytical phase costs from a
+// bandwidth model: kernel time = algorithmic bytes / `hbm_bytes_per_ns`, scaled by the fraction
+// of the roofline the kernel reaches.
+::cellerator::planner::planner_candidate make_planner_candidate(const core::operation_candidate &candidate,
+                                                                const core::projection_key &projection,
+                                                                const projection_catalog_entry &shape,
+                                                                double hbm_bytes_per_ns,
+                                                                double roofline_fraction) noexcept;
+
+} // namespace cellerator_b200::host

@@ -32,6 +32,9 @@ def build(ref: bool | None = None) -> None:
         ref = os.path.isdir(os.environ.get("CB200_REFERENCE", "/root/reference"))
     if ref:
         targets.append("ref")
+        product = os.path.join(os.path.dirname(_HERE), "cellerator_b200", "lib", "libcellerator_b200.so")
+        if os.path.exists(product):
+            targets.append("conformance")   # the reference's operation core driving the backend
     subprocess.run(["make", "-C", _HERE, *targets], check=True, capture_output=True)
 
 

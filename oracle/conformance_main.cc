@@ -1,0 +1,373 @@
+// Conformance driver: the REAL Cellerator operation core (register_candidate, prepare_candidate,
+// run_prepared_operation with validate_launch_bindings) driving the cellerator_b200 candidates.
+//
+// TEST INFRASTRUCTURE.  Built only where the Cellerator tree is available (oracle/Makefile target
+// `conformance`): it compiles the reference's operation_core.cc / referee.cc / operation.cc /
+// operation_signature.cc in place, cellerator_b200/host/b200_candidates.cc against the reference
+// headers, and links libcellerator_b200.so.  The binary lands in oracle/_ref/ and travels to the
+// GPU box with the tree.  Without a device it checks the host half of the seam (registration,
+// capability query, policy rejections, prepare failing loudly); with a B200 it prepares and runs
+// the forward, transpose and Blocked-ELL candidates through run_prepared_operation and compares
+// the results with the reference's own double-precision referee.
+#include "../cellerator_b200/host/b200_candidates.hh"
+
+#include <Cellerator/compute/math/referee.hh>
+#include <Cellerator/types.cuh>
+
+#include <cuda_runtime_api.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <vector>
+
+namespace core = ::cellerator::compute::math::core;
+namespace cm = ::cellerator::compute::math;
+namespace ex = ::cellerator::execution;
+namespace host = ::cellerator_b200::host;
+
+static int g_failures = 0;
+#define CHECK(cond, name)                                                        \
+    do {                                                                         \
+        if (cond) std::printf("PASS %s\n", name);                                \
+        else { std::printf("FAIL %s (%s:%d)\n", name, __FILE__, __LINE__); ++g_failures; } \
+    } while (0)
+
+template<typename Tag> static ex::identity_handle<Tag> handle(std::uint32_t slot) { return {slot, 1u}; }
+static ex::axis_identity axis(std::uint32_t base) {
+    return {handle<ex::domain_tag>(base), handle<ex::order_tag>(base + 1), handle<ex::geometry_tag>(base + 2),
+            handle<ex::partition_tag>(7u)};
+}
+
+static core::numeric_policy policy_u8(ex::numeric_type dense) {
+    core::numeric_policy n;
+    n.sparse_storage = ex::numeric_type::u8;
+    n.dense_storage = dense;
+    n.output_storage = ex::numeric_type::f32;
+    n.multiply = ex::numeric_type::f32;
+    n.accumulation = ex::numeric_type::f32;
+    n.scalar = ex::numeric_type::f32;
+    n.quantization = core::quantization_granularity::value_plane;
+    return n;
+}
+
+template<typename T> static T *to_device(const std::vector<T> &v) {
+    T *d = nullptr;
+    if (cudaMalloc(reinterpret_cast<void **>(&d), (v.size() + 1) * sizeof(T)) != cudaSuccess) std::abort();
+    cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
+    return d;
+}
+
+struct problem_ids {
+    core::operation_problem problem;
+    core::structure_set_key structures;
+    core::projection_key projection;
+};
+
+static problem_ids make_ids(std::uint32_t salt, core::projection_kind kind, std::uint64_t work) {
+    problem_ids ids{};
+    ids.problem.kind = core::operation_kind::sparse_dense_multiply;
+    ids.problem.operation = {0x5eedull + salt, 1ull};
+    ids.problem.input_count = 2u;
+    ids.problem.output_count = 1u;
+    ids.problem.logical_work_items = work;
+    ids.structures.count = 1u;
+    ids.structures.structures[0].persistent = {0x57ull + salt, 2ull};
+    ids.structures.structures[0].runtime = handle<ex::structure_tag>(10u + salt);
+    ids.structures.structures[0].epoch = {3u};
+    ids.projection.persistent = {0x9aull + salt, 4ull};
+    ids.projection.runtime = handle<ex::projection_tag>(20u + salt);
+    ids.projection.kind = kind;
+    ids.projection.schema_version = 1u;
+    return ids;
+}
+
+int main(int argc, char **argv) {
+    const bool host_only_requested = argc > 1 && std::strcmp(argv[1], "--host-only") == 0;
+    int device_count = 0;
+    const bool have_device = !host_only_requested && cudaGetDeviceCount(&device_count) == cudaSuccess && device_count > 0;
+    std::printf("device: %s\n", have_device ? "present" : "none");
+
+    // ---- registration and capability query (host only) ----------------------------------
+    static core::candidate_registry registry;
+    CHECK(static_cast<bool>(host::register_all(&registry)) && registry.size == 3u, "register three candidates");
+    CHECK(core::register_candidate(&registry, host::quantized_csr_forward_candidate()).code ==
+              core::operation_status_code::duplicate_candidate, "duplicate registration is rejected");
+    const core::operation_candidate *fwd = core::find_candidate(registry, host::quantized_csr_forward_candidate().identity);
+    const core::operation_candidate *tr = core::find_candidate(registry, host::quantized_csr_transpose_candidate().identity);
+    const core::operation_candidate *bell = core::find_candidate(registry, host::quantized_blocked_ell_candidate().identity);
+    CHECK(fwd != nullptr && tr != nullptr && bell != nullptr, "find_candidate by identity");
+    CHECK(fwd->supports_numeric(policy_u8(ex::numeric_type::bf16)) && fwd->supports_numeric(policy_u8(ex::numeric_type::f32)),
+          "forward supports bf16 and f32 W");
+    CHECK(!fwd->supports_numeric(policy_u8(ex::numeric_type::f16)), "forward rejects f16 W");
+    {
+        core::numeric_policy n = policy_u8(ex::numeric_type::bf16);
+        n.quantization = core::quantization_granularity::none;
+        CHECK(!fwd->supports_numeric(n), "forward rejects an unquantized policy");
+    }
+    CHECK(tr->supports_numeric(policy_u8(ex::numeric_type::f32)) && !tr->supports_numeric(policy_u8(ex::numeric_type::bf16)),
+          "transpose takes f32 G only");
+    CHECK((tr->capability_flags & core::candidate_deterministic) == 0u, "transpose does not claim determinism");
+
+    // ---- a small quantized CSR problem ---------------------------------------------------
+    const std::int64_t M = 300, K = 1000, N = 64;
+    std::mt19937 rng(7);
+    std::vector<std::int64_t> row_ptr(M + 1, 0);
+    std::vector<std::int32_t> col;
+    for (std::int64_t r = 0; r < M; ++r) {
+        std::vector<char> used(K, 0);
+        const int want = static_cast<int>(rng() % 120);
+        for (int i = 0; i < want; ++i) used[rng() % K] = 1;
+        for (std::int64_t g = 0; g < K; ++g) if (used[g]) col.push_back(static_cast<std::int32_t>(g));
+        row_ptr[r + 1] = static_cast<std::int64_t>(col.size());
+    }
+    const std::int64_t nnz = static_cast<std::int64_t>(col.size());
+    std::vector<std::uint8_t> codes(nnz);
+    for (auto &c : codes) c = static_cast<std::uint8_t>(rng() & 0xff);
+    std::vector<float> scales(K), offsets(K), w(K * N), g(M * N);
+    std::uniform_real_distribution<float> uni(0.01f, 0.05f), sym(-0.05f, 0.05f), one(-1.0f, 1.0f);
+    for (auto &v : scales) v = uni(rng);
+    for (auto &v : offsets) v = sym(rng);
+    for (auto &v : w) v = sym(rng);
+    for (auto &v : g) v = one(rng);
+
+    const ex::axis_identity cells = axis(100u), genes = axis(200u), latent = axis(300u);
+    problem_ids ids = make_ids(0u, core::projection_kind::csr, static_cast<std::uint64_t>(nnz));
+    host::projection_catalog_entry shape{};
+    shape.projection = ids.projection.runtime;
+    shape.projection_kind = CB200_PROJECTION_CSR;
+    shape.m = M; shape.k = K; shape.n = N; shape.nnz = nnz;
+    shape.bits = 8; shape.dense_dtype = CB200_DTYPE_F32; shape.device = 0;
+    shape.host_row_ptr = row_ptr.data();
+    shape.cells = cells; shape.genes = genes; shape.latent = latent;
+    CHECK(host::register_projection(shape), "projection catalog accepts the entry");
+
+    // ---- policy rejections happen in prepare_candidate, before the backend is asked --------
+    core::prepared_operation prepared{};
+    {
+        problem_ids t = make_ids(1u, core::projection_kind::transpose_or_backward, static_cast<std::uint64_t>(nnz));
+        core::prepare_policy p;
+        p.deterministic = true;
+        CHECK(core::prepare_candidate(*tr, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32), p, &prepared).code ==
+                  core::operation_status_code::capability_rejected, "deterministic policy rejects the transpose candidate");
+        CHECK(core::prepare_candidate(*fwd, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32), {}, &prepared).code ==
+                  core::operation_status_code::unsupported_projection, "projection kind mismatch is rejected");
+        problem_ids unknown = make_ids(9u, core::projection_kind::csr, 10u);
+        CHECK(core::prepare_candidate(*fwd, unknown.problem, unknown.structures, unknown.projection,
+                                      policy_u8(ex::numeric_type::f32), {}, &prepared).code ==
+                  core::operation_status_code::unsupported_projection, "unknown projection handle is rejected");
+    }
+    if (!have_device) {
+        const core::operation_status s = core::prepare_candidate(*fwd, ids.problem, ids.structures, ids.projection,
+                                                                 policy_u8(ex::numeric_type::f32), {}, &prepared);
+        CHECK(s.code == core::operation_status_code::preparation_failed && s.message != nullptr && s.message[0] != '\0',
+              "prepare without a device fails loudly (no CPU fallback)");
+        std::printf("%s: %d failure(s)\n", g_failures ? "FAILED" : "OK", g_failures);
+        return g_failures ? 1 : 0;
+    }
+
+    // ---- device run through run_prepared_operation ----------------------------------------
+    cudaSetDevice(0);
+    std::int64_t *d_row_ptr = to_device(row_ptr);
+    std::int32_t *d_col = to_device(col);
+    std::uint8_t *d_codes = to_device(codes);
+    float *d_scales = to_device(scales), *d_offsets = to_device(offsets), *d_w = to_device(w), *d_g = to_device(g);
+    float *d_y = nullptr, *d_gt = nullptr;
+    void *d_ws = nullptr;
+    cudaMalloc(reinterpret_cast<void **>(&d_y), M * N * sizeof(float));
+    cudaMalloc(reinterpret_cast<void **>(&d_gt), K * N * sizeof(float));
+    cudaMalloc(&d_ws, 4096);
+    cudaStream_t stream = nullptr;
+    cudaStreamCreate(&stream);
+
+    core::prepare_policy det;
+    det.deterministic = true;
+    core::operation_status st = core::prepare_candidate(*fwd, ids.problem, ids.structures, ids.projection,
+                                                        policy_u8(ex::numeric_type::f32), det, &prepared);
+    CHECK(static_cast<bool>(st), "prepare_candidate(forward, deterministic policy)");
+    if (!st) std::printf("  message: %s\n", st.message);
+
+    host::csr_projection_data proj{M, K, nnz, d_row_ptr, nullptr, d_col};
+    const ex::device_location dev_loc{ex::residency_kind::device, {0, 0, 0}, 0, 0u};
+    ex::relation_structure structure{ids.structures.structures[0].runtime, {3u}, cells, genes, {1u, 1u},
+                                     static_cast<std::uint64_t>(nnz)};
+    ex::value_plane plane{};
+    plane.structure = structure.identity;
+    plane.structure_epoch_value = {3u};
+    plane.values = d_codes;
+    plane.location = dev_loc;
+    plane.numeric = {ex::numeric_type::u8, ex::numeric_type::f32, ex::numeric_type::f32, 0u};
+    plane.quantization = {ex::quantization_kind::per_value_plane, ex::numeric_type::f32, ex::numeric_type::f32, 0u,
+                          d_scales, d_offsets, static_cast<std::uint64_t>(K)};
+    plane.layout = ex::value_layout_kind::logical_edge_order;
+    plane.generation = {5u};
+    plane.element_count = static_cast<std::uint64_t>(nnz);
+    plane.value_bytes = static_cast<std::uint64_t>(nnz);
+    ex::value_binding value{&plane, {5u}};
+
+    auto dense_view = [&](void *data, const ex::axis_identity &a0, std::uint64_t rows) {
+        ex::biological_operand_view v{};
+        v.kind = ex::operand_kind::dense_tensor;
+        v.storage.dense.data = data;
+        v.storage.dense.location = dev_loc;
+        v.storage.dense.value_type = ex::numeric_type::f32;
+        v.storage.dense.rank = 2u;
+        v.storage.dense.axes[0] = a0;
+        v.storage.dense.axes[1] = latent;
+        v.storage.dense.shape[0] = rows;
+        v.storage.dense.shape[1] = static_cast<std::uint64_t>(N);
+        v.storage.dense.stride[0] = N;
+        v.storage.dense.stride[1] = 1;
+        return v;
+    };
+    ex::biological_operand_view inputs[2]{};
+    inputs[0].kind = ex::operand_kind::sparse_relation;
+    inputs[0].storage.relation = {cells, genes, structure.identity, ids.projection.runtime, {3u}, &proj, sizeof proj,
+                                  static_cast<std::uint64_t>(nnz), dev_loc};
+    inputs[1] = dense_view(d_w, genes, static_cast<std::uint64_t>(K));
+    ex::biological_operand_view outputs[1] = {dense_view(d_y, cells, static_cast<std::uint64_t>(M))};
+
+    ex::launch_bindings launch{};
+    launch.structures = &structure;
+    launch.inputs = inputs;
+    launch.outputs = outputs;
+    launch.values = &value;
+    launch.input_count = 2u;
+    launch.output_count = 1u;
+    launch.value_count = 1u;
+    launch.structure_count = 1u;
+    launch.stream = {stream, 0, 0u};
+    launch.workspace = {d_ws, 4096u, dev_loc};
+
+    st = core::run_prepared_operation(prepared, launch);
+    CHECK(static_cast<bool>(st), "run_prepared_operation(forward)");
+    if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+    cudaStreamSynchronize(stream);
+    std::vector<float> y(M * N);
+    cudaMemcpy(y.data(), d_y, y.size() * sizeof(float), cudaMemcpyDeviceToHost);
+
+    // the reference's own referee on the decoded values
+    std::vector<float> decoded(nnz);
+    for (std::int64_t i = 0; i < nnz; ++i) decoded[i] = static_cast<float>(codes[i]) * scales[col[i]] + offsets[col[i]];
+    std::vector<cm::u64> offs(row_ptr.begin(), row_ptr.end());
+    std::vector<cm::u32> ucol(col.begin(), col.end());
+    auto referee = [&](bool transpose, const float *rhs, std::uint64_t rhs_rows, std::vector<double> *ref) {
+        cm::spmm_request r;
+        r.m = transpose ? K : M; r.k = transpose ? M : K; r.n = N; r.sparse_nnz = nnz;
+        r.sparse_structure.identity_version = 1u; r.sparse_structure.value = 77u;
+        r.transpose_sparse = transpose ? cm::transpose_kind::transpose : cm::transpose_kind::none;
+        r.dense_rhs_leading_dimension = N; r.output_leading_dimension = N;
+        r.sparse_storage_type_code = r.dense_storage_type_code = r.output_storage_type_code = ::cellerator::real::value_f32;
+        r.compute_type_code = r.accumulation_type_code = ::cellerator::real::value_f64;
+        r.alpha = cm::make_scalar(1.0); r.beta = cm::make_scalar(0.0);
+        r.sparse_feature_order.feature_count = static_cast<cm::u32>(r.k);
+        r.sparse_feature_order.feature_axis_identity_version = 1u;
+        r.sparse_feature_order.feature_axis_identity = 9u;
+        r.dense_feature_order = r.sparse_feature_order;
+        const cm::logical_csr_view sp{static_cast<cm::u64>(M), static_cast<cm::u64>(K), static_cast<cm::u64>(nnz), offs.data(),
+                                      ucol.data(), decoded.data(), static_cast<cm::u32>(::cellerator::real::value_f32)};
+        const cm::logical_dense_view dn{rhs, rhs_rows, static_cast<cm::u64>(N), static_cast<cm::u64>(N),
+                                        cm::dense_layout_kind::row_major, static_cast<cm::u32>(::cellerator::real::value_f32)};
+        ref->assign(r.m * r.n, 0.0);
+        return static_cast<bool>(cm::build_spmm_reference(r, sp, dn, {}, nullptr, ref->data(), ref->size()));
+    };
+    std::vector<double> ref;
+    CHECK(referee(false, w.data(), K, &ref), "referee(forward)");
+    {
+        const cm::logical_dense_view cand{y.data(), static_cast<cm::u64>(M), static_cast<cm::u64>(N), static_cast<cm::u64>(N),
+                                          cm::dense_layout_kind::row_major, static_cast<cm::u32>(::cellerator::real::value_f32)};
+        cm::numerical_comparison cmp;
+        const bool ok = static_cast<bool>(cm::compare_spmm_reference(ref.data(), ref.size(), cand, {1.0e-4, 1.0e-4, 1.0e-30}, &cmp));
+        std::printf("  forward max_abs=%.3e mismatches=%llu\n", cmp.max_absolute_error, static_cast<unsigned long long>(cmp.mismatch_count));
+        CHECK(ok && cmp.within_tolerance, "forward result within tolerance of the reference referee");
+        cm::determinism_digest d1, d2;
+        cm::digest_logical_dense(cand, &d1);
+        core::run_prepared_operation(prepared, launch);
+        cudaStreamSynchronize(stream);
+        std::vector<float> y2(M * N);
+        cudaMemcpy(y2.data(), d_y, y2.size() * sizeof(float), cudaMemcpyDeviceToHost);
+        const cm::logical_dense_view cand2{y2.data(), static_cast<cm::u64>(M), static_cast<cm::u64>(N), static_cast<cm::u64>(N),
+                                           cm::dense_layout_kind::row_major, static_cast<cm::u32>(::cellerator::real::value_f32)};
+        cm::digest_logical_dense(cand2, &d2);
+        CHECK(cm::same_digest(d1, d2), "deterministic candidate: identical digest on a second run");
+    }
+
+    // ---- launch-time rejections by the reference's validate_launch_bindings / by the backend ----
+    {
+        ex::relation_structure stale = structure;
+        stale.epoch = {4u};
+        ex::launch_bindings bad = launch;
+        bad.structures = &stale;
+        CHECK(core::run_prepared_operation(prepared, bad).code == core::operation_status_code::stale_structure,
+              "a launch with another structure epoch is stale");
+        bad = launch;
+        bad.workspace.bytes = 16u;
+        const core::operation_status s = core::run_prepared_operation(prepared, bad);
+        CHECK(s.code == core::operation_status_code::invalid_launch_bindings &&
+                  s.binding == ex::binding_validation_code::insufficient_workspace, "a workspace below the requirement is refused");
+        bad = launch;
+        bad.stream.device_ordinal = 1;
+        CHECK(core::run_prepared_operation(prepared, bad).binding == ex::binding_validation_code::invalid_stream,
+              "stream and workspace on different devices are refused");
+        ex::value_binding old_value{&plane, {4u}};
+        bad = launch;
+        bad.values = &old_value;
+        CHECK(core::run_prepared_operation(prepared, bad).binding == ex::binding_validation_code::stale_value,
+              "a stale value generation is refused");
+        ex::biological_operand_view alias_out[1] = {dense_view(d_w, cells, static_cast<std::uint64_t>(M))};
+        bad = launch;
+        bad.outputs = alias_out;
+        CHECK(core::run_prepared_operation(prepared, bad).binding == ex::binding_validation_code::illegal_operand_alias,
+              "an output aliasing an input is refused");
+    }
+    host::release_prepared(&prepared);
+
+    // ---- transpose candidate -------------------------------------------------------------------
+    {
+        problem_ids t = make_ids(1u, core::projection_kind::transpose_or_backward, static_cast<std::uint64_t>(nnz));
+        host::projection_catalog_entry ts = shape;
+        ts.projection = t.projection.runtime;
+        ts.projection_kind = CB200_PROJECTION_TRANSPOSE;
+        host::register_projection(ts);
+        core::prepared_operation pt{};
+        st = core::prepare_candidate(*tr, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32), {}, &pt);
+        CHECK(static_cast<bool>(st), "prepare_candidate(transpose)");
+        ex::relation_structure s2{t.structures.structures[0].runtime, {3u}, cells, genes, {1u, 1u}, static_cast<std::uint64_t>(nnz)};
+        ex::value_plane plane2 = plane;
+        plane2.structure = s2.identity;
+        ex::value_binding v2{&plane2, {5u}};
+        ex::biological_operand_view in2[2] = {inputs[0], dense_view(d_g, cells, static_cast<std::uint64_t>(M))};
+        in2[0].storage.relation.structure = s2.identity;
+        in2[0].storage.relation.projection = t.projection.runtime;
+        ex::biological_operand_view out2[1] = {dense_view(d_gt, genes, static_cast<std::uint64_t>(K))};
+        ex::launch_bindings l2 = launch;
+        l2.structures = &s2; l2.inputs = in2; l2.outputs = out2; l2.values = &v2;
+        st = core::run_prepared_operation(pt, l2);
+        CHECK(static_cast<bool>(st), "run_prepared_operation(transpose)");
+        if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+        cudaStreamSynchronize(stream);
+        std::vector<float> gt(K * N);
+        cudaMemcpy(gt.data(), d_gt, gt.size() * sizeof(float), cudaMemcpyDeviceToHost);
+        CHECK(referee(true, g.data(), M, &ref), "referee(transpose)");
+        const cm::logical_dense_view cand{gt.data(), static_cast<cm::u64>(K), static_cast<cm::u64>(N), static_cast<cm::u64>(N),
+                                          cm::dense_layout_kind::row_major, static_cast<cm::u32>(::cellerator::real::value_f32)};
+        cm::numerical_comparison cmp;
+        const bool ok = static_cast<bool>(cm::compare_spmm_reference(ref.data(), ref.size(), cand, {1.0e-3, 1.0e-4, 1.0e-30}, &cmp));
+        std::printf("  transpose max_abs=%.3e mismatches=%llu\n", cmp.max_absolute_error, static_cast<unsigned long long>(cmp.mismatch_count));
+        CHECK(ok && cmp.within_tolerance, "transpose result within tolerance of the reference referee");
+        host::release_prepared(&pt);
+    }
+
+    // ---- planner record ---------------------------------------------------------------------------
+    {
+        const auto rec = host::make_planner_candidate(*fwd, ids.projection, shape, 6553.9, 0.07);
+        CHECK(core::same_stable_id(rec.identity, fwd->identity) && rec.operation == fwd &&
+                  rec.projection.kind == fwd->projection && std::isfinite(rec.analytical.kernel_ns) &&
+                  rec.analytical.kernel_ns > 0.0 && (rec.flags & ::cellerator::planner::planner_candidate_correct) != 0u,
+              "planner_candidate record is well formed");
+    }
+    std::printf("%s: %d failure(s)\n", g_failures ? "FAILED" : "OK", g_failures);
+    return g_failures ? 1 : 0;
+}
