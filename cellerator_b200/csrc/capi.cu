@@ -288,6 +288,12 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     }
     if (problem->projection == CB200_PROJECTION_TRANSPOSE)
         p->workspace_bytes = qcsr_transpose_workspace_bytes(problem->k, problem->n, p->sm_count);
+    if (problem->projection == CB200_PROJECTION_BLOCKED_ELL && problem->dense_dtype == CB200_DTYPE_BF16 &&
+        (problem->n == 128 || problem->n == 256)) {
+        // the tensor-core kernel multiplies against W^T: room for that bf16 copy plus a status block
+        p->workspace_bytes = qbell_tcgen05_workspace_bytes(problem->k, problem->n);
+        p->schedule_name = "tcgen05_block_rows";
+    }
     if (problem->projection == CB200_PROJECTION_CSR) {
         // Row schedule from the nnz/row distribution: the gene-tiled kernel pays a fixed cost per
         // (row, gene tile) visit, so it needs enough stored entries per visit and enough row
@@ -400,7 +406,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
             return fail(CB200_STATUS_INVALID_SHAPE, "Blocked-ELL matrix disagrees with the prepared problem");
         if (b.block_col_idx == nullptr || b.packed_values == nullptr)
             return fail(CB200_STATUS_INVALID_ARGUMENT, "Blocked-ELL matrix has null arrays");
-        return launch_qbell_forward(view_of(b), d, row_begin, row_end, prepared->sm_count, stream);
+        return launch_qbell_forward(view_of(b), d, row_begin, row_end, launch->workspace, launch->workspace_bytes,
+                                    prepared->sm_count, stream);
     }
     if (!valid_header(launch->csr)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
     const cb200_qcsr &x = *launch->csr;

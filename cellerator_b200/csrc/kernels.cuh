@@ -58,8 +58,12 @@ struct qbell_view {
     const float *offsets;
 };
 
+// `workspace` (optional) holds the transposed bf16 copy of W that the tensor-core kernel needs;
+// without it (or for shapes that kernel does not cover) the CUDA-core kernel runs.
 cb200_status launch_qbell_forward(const qbell_view &x, const dense_args &d, std::int64_t row_begin,
-                                  std::int64_t row_end, int sm_count, cudaStream_t stream);
+                                  std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes, int sm_count,
+                                  cudaStream_t stream);
+std::uint64_t qbell_tcgen05_workspace_bytes(std::int64_t cols, std::int64_t n);
 
 cb200_status launch_quantize_rows(const qcsr_view &x, std::int64_t row_begin, std::int64_t row_end,
                                   const float *values, cudaStream_t stream);

@@ -1,14 +1,484 @@
-// Tensor-core (tcgen05) kernel of the quantized Blocked-ELL projection for 32x32 blocks.
-// Until its shape constraints hold the launcher reports "not taken" and the general kernel
-// in qbell_forward.cu runs.
+// Tensor-core kernel of the quantized Blocked-ELL projection for 32x32 blocks:
+//     Y[cells, N] = alpha * deq(X_bell)[cells, genes] * W[genes, N] + beta * Y,   N in {128, 256}.
+//
+// Reference counterpart: quantized_blocked_ell_spmm_fwd_kernel_ (scalar, one thread per output
+// element, src/compute/sparse/project/kernels/quantized_blocked_ell_spmm_fwd_kernel_.cuh:1-39) and
+// the cuSPARSE f16 Blocked-ELL route (src/compute/sparse/project/project.cu:258-298).
+//
+// Formulation.  A block row is 32 cells and ell_cols/32 present blocks, each naming 32 genes.  A
+// block row therefore is a dense contraction over K = 32 * blocks genes, but with only 32 rows --
+// too few for the M side of a tcgen05 MMA.  The product is computed transposed:
+//     D^T[N, 32 cells] += W^T[N, 32 genes of the block] * deq(X)^T[32 genes, 32 cells]
+// i.e. M = 128 output columns per MMA (two MMAs side by side for N = 256), N_mma = 32 cells,
+// K = 16 genes per instruction, fp32 accumulators in TMEM (lane = output column, TMEM column =
+// cell).  Both operands are K-major in shared memory in the no-swizzle core-matrix layout
+// (8 rows x 16 bytes per core matrix): that needs W^T, so a small kernel first writes W^T (bf16,
+// genes padded to a multiple of 32 with zeros) into the caller's workspace.
+//
+// One CTA (288 threads) streams (block row, block) items through a 6-stage ring:
+//   warps 4-7  producers: copy the block's 256 x 32 slice of W^T with cp.async (16 KB) and decode
+//              the block's 32 x 32 codes to bf16 (per-gene scale / zero-point applied in
+//              registers) straight into the operand layout;
+//   warp  8    one elected thread issues the MMAs, commits them to the stage's "empty" barrier
+//              and, after the last block of a block row, to the accumulator's "full" barrier;
+//   warps 0-3  epilogue: tcgen05.ld the accumulators (double buffered in TMEM so the next block
+//              row's MMAs overlap), apply alpha / beta, store Y rows coalesced.
+// Empty blocks (index 0xffffffff) are skipped; genes >= cols and cells past the last row decode
+// to 0.  Every barrier wait is bounded; on a time-out a status word is set, the waits stop
+// blocking, and the kernel still runs to completion and frees its TMEM.
 #include "kernels.cuh"
+
+#include <cuda_bf16.h>
 
 namespace cb200 {
 
-cb200_status launch_qbell_tcgen05(const qbell_view &, const dense_args &, std::int64_t, std::int64_t, int,
-                                  cudaStream_t, bool *taken) {
-    *taken = false;
+std::uint64_t qbell_tcgen05_workspace_bytes(std::int64_t cols, std::int64_t n) {
+    const std::int64_t kpad = (cols + 31) / 32 * 32;
+    return static_cast<std::uint64_t>(n * kpad * 2 + 256);
+}
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kLookahead = 2;
+constexpr int kMaxWidth = 16;                      // blocks per block row the staging area holds
+constexpr int kCodesStageBytes = 32 * 512;         // one block row of codes: 32 cells x up to 512 bytes
+constexpr int kMetaStageBytes = kMaxWidth * 256;   // per block: 32 scales + 32 offsets
+constexpr int kEpilogueThreads = 128; // warps 0-3
+constexpr int kProducerThreads = 128; // warps 4-7
+constexpr int kThreads = 288;         // + MMA warp 8
+constexpr int kATileBytes = 256 * 64; // 256 output columns x 32 genes bf16
+constexpr int kBTileBytes = 32 * 64;  // 32 cells x 32 genes bf16
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+
+struct tc_params {
+    std::int64_t rows, cols;
+    int width; // blocks per block row
+    std::int64_t row_stride;
+    const std::uint32_t *block_col_idx;
+    const std::uint8_t *packed;
+    const float *scales;
+    const float *offsets;
+    const __nv_bfloat16 *wt; // [n][kpad]
+    std::int64_t kpad;
+    float *y;
+    std::int64_t y_ld;
+    std::int64_t block_row_begin, block_row_end; // block rows of this launch
+    std::int64_t row_begin, row_end;             // cell rows of this launch
+    int n;
+    int policy;
+    float alpha, beta;
+    int *status;
+};
+
+__device__ __forceinline__ std::uint32_t smem_addr(const void *p) { return static_cast<std::uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void bar_init(std::uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(std::uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(std::uint32_t bar, std::uint32_t parity) {
+    std::uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0u;
+}
+// Bounded wait.  Once any wait of the CTA has timed out (`*abort_flag` set) waits return at once.
+__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag) {
+    int spins = 0;
+    while (!bar_try_wait(bar, parity)) {
+        if (*abort_flag != 0) return;
+        if (++spins > (1 << 22)) {
+            *abort_flag = 1;
+            return;
+        }
+    }
+}
+
+__device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// 16-byte copy of which only the first `bytes` (0..16) are read; the rest is filled with zeros
+__device__ __forceinline__ void cp_async_16_zfill(std::uint32_t dst, const void *src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lds_f32x4(std::uint32_t addr, float &a, float &b, float &c, float &d) {
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template<int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major, no swizzle: core matrices of 8 rows x 16 bytes; LBO (between the two core matrices a
+// K = 16 instruction reads) = 128 B, SBO (between groups of 8 rows) = 512 B.
+__device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
+    std::uint64_t d = 0;
+    d |= static_cast<std::uint64_t>((addr & 0x3ffffu) >> 4);
+    d |= static_cast<std::uint64_t>(128u >> 4) << 16;
+    d |= static_cast<std::uint64_t>(512u >> 4) << 32;
+    d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
+    return d;
+}
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 32, M = 128.
+constexpr std::uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate ? 1u : 0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(std::uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
+    std::uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+          "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// W [genes][n] (leading dimension ld) -> W^T [n][kpad], zero for genes >= cols.
+__global__ void __launch_bounds__(256) transpose_w_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
+                                                          __nv_bfloat16 *wt, std::int64_t kpad) {
+    __shared__ __nv_bfloat16 tile[32][33];
+    const int gx = blockIdx.x * 32, nx = blockIdx.y * 32; // gene tile, output-column tile
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+    for (int r = ty; r < 32; r += 8) {
+        const std::int64_t gene = gx + r;
+        const int col = nx + tx;
+        tile[r][tx] = (gene < cols && col < n) ? w[gene * ld + col] : __float2bfloat16(0.0f);
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int col = nx + r;
+        const std::int64_t gene = gx + tx;
+        if (col < n && gene < kpad) wt[col * kpad + gene] = tile[tx][r];
+    }
+}
+
+template<int BITS, int H /* N / 128 */>
+__global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_params p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    // [kStages][A 16 KB | B 2 KB] | staged codes [2] | staged scales/offsets [2] | barriers | tmem base | flags
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(smem + kStages * kStageBytes + 2 * kCodesStageBytes + 2 * kMetaStageBytes);
+    std::uint64_t *full_bar = bars;                  // [kStages]  producers -> MMA      (128 arrivals)
+    std::uint64_t *empty_bar = bars + kStages;       // [kStages]  MMA commit -> producers (1 arrival)
+    std::uint64_t *acc_full = bars + 2 * kStages;    // [2]        MMA commit -> epilogue  (1 arrival)
+    std::uint64_t *acc_empty = bars + 2 * kStages + 2; // [2]      epilogue -> MMA        (128 arrivals)
+    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(bars + 2 * kStages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    int *row_has_blocks = const_cast<int *>(reinterpret_cast<volatile int *>(tmem_slot + 2)); // [2] per accumulator buffer
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const std::uint32_t smem0 = smem_addr(smem);
+    constexpr int kTmemCols = 2 * H * 32; // two accumulator buffers
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            bar_init(smem_addr(full_bar + s), kProducerThreads);
+            bar_init(smem_addr(empty_bar + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            bar_init(smem_addr(acc_full + b), 1);
+            bar_init(smem_addr(acc_empty + b), kEpilogueThreads);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const std::uint32_t tmem_base = *tmem_slot;
+
+    const std::int64_t first = p.block_row_begin + blockIdx.x;
+    const std::int64_t step = gridDim.x;
+    const bool row_policy = p.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+
+    if (warp >= 4 && warp < 8) {
+        // ================= producers =================
+        const int pt = tid - 128;          // 0..127
+        const int cell = pt >> 2, chunk = pt & 3; // B tile: cell within the block row, 8-gene chunk
+        const std::uint32_t codes_stage = smem0 + kStages * kStageBytes;          // [2][32 cells][512 B]
+        const std::uint32_t meta_stage = codes_stage + 2 * kCodesStageBytes;       // [2][16 slots][32 scales | 32 offsets]
+        const int row_bytes = p.width * 32 * BITS / 8;
+        const int chunks_per_row = row_bytes / 16;
+        const bool stage_offsets = !row_policy && p.offsets != nullptr;
+
+        // Codes and per-gene metadata of a whole block row are brought into shared memory one block
+        // row ahead of their use, so that decoding an item never waits on DRAM.
+        auto prefetch_block_row = [&](std::int64_t br, int buf) {
+            for (int i = pt; i < 32 * chunks_per_row; i += kProducerThreads) {
+                const int c_cell = i / chunks_per_row, c = i % chunks_per_row;
+                const std::int64_t row = br * 32 + c_cell;
+                if (row >= p.row_begin && row < p.row_end)
+                    cp_async_16(codes_stage + buf * kCodesStageBytes + c_cell * 512 + c * 16, p.packed + row * p.row_stride + c * 16);
+            }
+            for (int i = pt; i < p.width * 16; i += kProducerThreads) {
+                const int slot = i >> 4, q = i & 15;
+                const bool is_offset = q >= 8;
+                const float *base = is_offset ? p.offsets : p.scales;
+                if (base == nullptr || (is_offset && !stage_offsets)) continue;
+                const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
+                if (bc == 0xffffffffu) continue;
+                const std::int64_t gene = static_cast<std::int64_t>(bc) * 32 + (q & 7) * 4;
+                const std::int64_t left = p.cols - gene;                          // genes >= cols are zero-filled
+                const int bytes = left >= 4 ? 16 : (left > 0 ? static_cast<int>(left) * 4 : 0);
+                cp_async_16_zfill(meta_stage + buf * kMetaStageBytes + slot * 256 + q * 16, bytes > 0 ? base + gene : base, bytes);
+            }
+        };
+
+        long long item = 0;                // items issued by this thread
+        long long signalled = 0;           // items whose "full" barrier this thread has arrived on
+        int iteration = 0;
+        if (first < p.block_row_end) prefetch_block_row(first, 0);
+        cp_async_commit();
+        for (std::int64_t br = first; br < p.block_row_end; br += step, ++iteration) {
+            const int buf = iteration & 1;
+            const std::int64_t row = br * 32 + cell;
+            const bool cell_valid = row >= p.row_begin && row < p.row_end;
+            const float row_offset = (row_policy && p.offsets != nullptr && cell_valid) ? __ldg(p.offsets + row) : 0.0f;
+            // this block row's staged data is complete for every producer thread, and everyone has
+            // finished decoding the previous block row (whose buffer the next prefetch overwrites)
+            cp_async_wait<0>();
+            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+            if (br + step < p.block_row_end) prefetch_block_row(br + step, buf ^ 1);
+            cp_async_commit();
+            const std::uint32_t my_codes = codes_stage + buf * kCodesStageBytes + cell * 512;
+            const std::uint32_t my_meta = meta_stage + buf * kMetaStageBytes + chunk * 32;
+            for (int slot = 0; slot < p.width; ++slot) {
+                const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
+                if (bc == 0xffffffffu) continue;
+                const int stage = static_cast<int>(item % kStages);
+                bar_wait(smem_addr(empty_bar + stage), static_cast<std::uint32_t>(((item / kStages) & 1) ^ 1), abort_flag);
+                const std::uint32_t a_tile = smem0 + stage * kStageBytes;
+                const std::uint32_t b_tile = a_tile + kATileBytes;
+                // ---- A: the block's 32 genes of W^T for all H*128 output columns (16-byte chunks)
+                const __nv_bfloat16 *src = p.wt + static_cast<std::int64_t>(bc) * 32;
+#pragma unroll
+                for (int it = 0; it < (H * 128 * 4) / kProducerThreads; ++it) {
+                    const int i = it * kProducerThreads + pt;
+                    const int m = i >> 2, c = i & 3;
+                    cp_async_16(a_tile + (m >> 3) * 512 + c * 128 + (m & 7) * 16, src + static_cast<std::int64_t>(m) * p.kpad + c * 8);
+                }
+                // ---- B: decode 8 codes of (cell, genes chunk) to bf16, from the staged copies
+                const std::int64_t gene0 = static_cast<std::int64_t>(bc) * 32 + chunk * 8;
+                __nv_bfloat162 out[4];
+                if (cell_valid) {
+                    unsigned code[8];
+                    if constexpr (BITS == 8) {
+                        std::uint32_t lo, hi;
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(my_codes + slot * 32 + chunk * 8));
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            code[e] = (lo >> (8 * e)) & 0xffu;
+                            code[4 + e] = (hi >> (8 * e)) & 0xffu;
+                        }
+                    } else {
+                        std::uint32_t raw;
+                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(my_codes + slot * 16 + chunk * 4));
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) code[e] = (raw >> (4 * e)) & 0xfu;
+                    }
+                    float sc[8], of[8];
+                    if (p.scales != nullptr) {
+                        lds_f32x4(my_meta + slot * 256, sc[0], sc[1], sc[2], sc[3]);
+                        lds_f32x4(my_meta + slot * 256 + 16, sc[4], sc[5], sc[6], sc[7]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) sc[e] = 1.0f;
+                    }
+                    if (stage_offsets) {
+                        lds_f32x4(my_meta + slot * 256 + 128, of[0], of[1], of[2], of[3]);
+                        lds_f32x4(my_meta + slot * 256 + 144, of[4], of[5], of[6], of[7]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) of[e] = row_offset;
+                    }
+                    float v[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = gene0 + e < p.cols ? fmaf(static_cast<float>(code[e]), sc[e], of[e]) : 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) out[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) out[e] = __floats2bfloat162_rn(0.0f, 0.0f);
+                }
+                {
+                    const std::uint32_t dst = b_tile + (cell >> 3) * 512 + chunk * 128 + (cell & 7) * 16;
+                    const std::uint32_t *w32 = reinterpret_cast<const std::uint32_t *>(out);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w32[0]), "r"(w32[1]), "r"(w32[2]), "r"(w32[3])
+                                 : "memory");
+                }
+                cp_async_commit();
+                ++item;
+                if (item - signalled > kLookahead) {
+                    cp_async_wait<kLookahead>();
+                    fence_async_proxy();
+                    bar_arrive(smem_addr(full_bar + static_cast<int>(signalled % kStages)));
+                    ++signalled;
+                }
+            }
+        }
+        cp_async_wait<0>();
+        fence_async_proxy();
+        while (signalled < item) {
+            bar_arrive(smem_addr(full_bar + static_cast<int>(signalled % kStages)));
+            ++signalled;
+        }
+    } else if (warp == 8) {
+        // ================= MMA issuer =================
+        long long item = 0;
+        long long use = 0; // block rows handled (accumulator buffer uses)
+        for (std::int64_t br = first; br < p.block_row_end; br += step, ++use) {
+            const int buf = static_cast<int>(use & 1);
+            bar_wait(smem_addr(acc_empty + buf), static_cast<std::uint32_t>(((use >> 1) & 1) ^ 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            bool any = false;
+            for (int slot = 0; slot < p.width; ++slot) {
+                const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
+                if (bc == 0xffffffffu) continue;
+                const int stage = static_cast<int>(item % kStages);
+                bar_wait(smem_addr(full_bar + stage), static_cast<std::uint32_t>((item / kStages) & 1), abort_flag);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    const std::uint32_t a_tile = smem0 + stage * kStageBytes;
+                    const std::uint32_t b_tile = a_tile + kATileBytes;
+#pragma unroll
+                    for (int h = 0; h < H; ++h) {
+#pragma unroll
+                        for (int kk = 0; kk < 2; ++kk) {
+                            mma_bf16(tmem_base + buf * (H * 32) + h * 32, smem_desc(a_tile + h * 8192 + kk * 256),
+                                     smem_desc(b_tile + kk * 256), any || kk > 0);
+                        }
+                    }
+                    mma_commit(smem_addr(empty_bar + stage)); // the stage is free once these MMAs have read it
+                }
+                __syncwarp();
+                any = true;
+                ++item;
+            }
+            if (lane == 0) {
+                row_has_blocks[buf] = any ? 1 : 0;
+                mma_commit(smem_addr(acc_full + buf));        // accumulators complete (or nothing was issued)
+            }
+            __syncwarp();
+        }
+    } else if (warp < 4) {
+        // ================= epilogue =================
+        long long use = 0;
+        for (std::int64_t br = first; br < p.block_row_end; br += step, ++use) {
+            const int buf = static_cast<int>(use & 1);
+            bar_wait(smem_addr(acc_full + buf), static_cast<std::uint32_t>((use >> 1) & 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool any = *reinterpret_cast<volatile int *>(row_has_blocks + buf) != 0;
+            const std::int64_t row0 = br * 32;
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+                float v[32];
+                if (any) {
+                    tmem_ld32(tmem_base + (static_cast<std::uint32_t>(warp * 32) << 16) + buf * (H * 32) + h * 32, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                }
+                const int col = h * 128 + warp * 32 + lane;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const std::int64_t row = row0 + c;
+                    if (row >= p.row_begin && row < p.row_end) {
+                        float *out = p.y + row * p.y_ld + col;
+                        float r = p.alpha * v[c];
+                        if (p.beta != 0.0f) r = fmaf(p.beta, *out, r);
+                        *out = r;
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            bar_arrive(smem_addr(acc_empty + buf));
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+constexpr std::size_t kSmemBytes = kStages * kStageBytes + 2 * kCodesStageBytes + 2 * kMetaStageBytes + (2 * kStages + 4) * sizeof(std::uint64_t) + 32;
+
+template<int BITS, int H>
+cb200_status launch(const tc_params &p, int sm_count, cudaStream_t stream) {
+    CB200_CUDA_OK(cudaFuncSetAttribute(qbell_tcgen05_kernel<BITS, H>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kSmemBytes)));
+    const std::int64_t block_rows = p.block_row_end - p.block_row_begin;
+    const unsigned grid = static_cast<unsigned>(block_rows < 2ll * sm_count ? block_rows : 2ll * sm_count);
+    qbell_tcgen05_kernel<BITS, H><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
+}
+
+} // namespace
+
+cb200_status launch_qbell_tcgen05(const qbell_view &x, const dense_args &d, std::int64_t row_begin,
+                                  std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes, int sm_count,
+                                  cudaStream_t stream, bool *taken) {
+    *taken = false;
+    if (x.block_size != 32 || (d.n != 128 && d.n != 256) || d.dense_dtype != CB200_DTYPE_BF16) return CB200_STATUS_SUCCESS;
+    if (x.bits != 8 && x.bits != 4) return CB200_STATUS_SUCCESS;
+    if (x.ell_cols <= 0 || x.ell_cols % 32 != 0 || x.ell_cols / 32 > kMaxWidth) return CB200_STATUS_SUCCESS;
+    // staging copies move 16 bytes at a time
+    if (x.row_stride_bytes % 16 != 0 || reinterpret_cast<std::uintptr_t>(x.packed) % 16u != 0u) return CB200_STATUS_SUCCESS;
+    if (reinterpret_cast<std::uintptr_t>(x.scales) % 16u != 0u || reinterpret_cast<std::uintptr_t>(x.offsets) % 16u != 0u) return CB200_STATUS_SUCCESS;
+    if (workspace == nullptr || workspace_bytes < qbell_tcgen05_workspace_bytes(x.cols, d.n)) return CB200_STATUS_SUCCESS;
+    if (reinterpret_cast<std::uintptr_t>(workspace) % 256u != 0u) return CB200_STATUS_SUCCESS;
+    if (row_end <= row_begin) return CB200_STATUS_SUCCESS;
+
+    const std::int64_t kpad = (x.cols + 31) / 32 * 32;
+    int *status = static_cast<int *>(workspace);
+    __nv_bfloat16 *wt = reinterpret_cast<__nv_bfloat16 *>(static_cast<unsigned char *>(workspace) + 256);
+    CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    {
+        const dim3 grid(static_cast<unsigned>(kpad / 32), static_cast<unsigned>((d.n + 31) / 32));
+        transpose_w_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols,
+                                                     static_cast<int>(d.n), wt, kpad);
+        count_launch();
+        CB200_CUDA_OK(cudaGetLastError());
+    }
+    tc_params p{};
+    p.rows = x.rows; p.cols = x.cols; p.width = x.ell_cols / 32; p.row_stride = x.row_stride_bytes;
+    p.block_col_idx = x.block_col_idx; p.packed = x.packed; p.scales = x.scales; p.offsets = x.offsets;
+    p.wt = wt; p.kpad = kpad; p.y = d.out; p.y_ld = d.out_ld;
+    p.block_row_begin = row_begin / 32; p.block_row_end = (row_end + 31) / 32;
+    p.row_begin = row_begin; p.row_end = row_end;
+    p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha; p.beta = d.beta; p.status = status;
+    *taken = true;
+    if (x.bits == 8) return d.n == 256 ? launch<8, 2>(p, sm_count, stream) : launch<8, 1>(p, sm_count, stream);
+    return d.n == 256 ? launch<4, 2>(p, sm_count, stream) : launch<4, 1>(p, sm_count, stream);
 }
 
 } // namespace cb200
