@@ -12,13 +12,18 @@
 // i.e. M = 128 output columns per MMA (two MMAs side by side for N = 256), N_mma = 32 cells,
 // K = 16 genes per instruction, fp32 accumulators in TMEM (lane = output column, TMEM column =
 // cell).  Both operands are K-major in shared memory in the no-swizzle core-matrix layout
-// (8 rows x 16 bytes per core matrix): that needs W^T, so a small kernel first writes W^T (bf16,
-// genes padded to a multiple of 32 with zeros) into the caller's workspace.
+// (8 rows x 16 bytes per core matrix): that needs W^T, so a small kernel first writes, into the
+// caller's workspace, W^T per gene block of 32 (genes padded with zeros) already in that operand
+// layout; a block's N x 32 slice is then one contiguous 16 KB range.
 //
-// One CTA (288 threads) streams (block row, block) items through a 6-stage ring:
-//   warps 4-7  producers: copy the block's 256 x 32 slice of W^T with cp.async (16 KB) and decode
-//              the block's 32 x 32 codes to bf16 (per-gene scale / zero-point applied in
-//              registers) straight into the operand layout;
+// One CTA (288 threads, two CTAs per SM) streams (block row, block) items through a 4-stage ring:
+//   warps 4-7  producers: one thread fetches the block's slice of W^T with a single bulk async copy
+//              (cp.async.bulk, byte-counted on the stage's mbarrier; fetching it as 1,024 separate
+//              16-byte cp.async chunks doubled the L2 sector traffic and ran at half the speed);
+//              all 128 decode the block's 32 x 32 codes to bf16 (per-gene scale / zero-point
+//              applied in registers) straight into the operand layout.  Codes and metadata of a
+//              whole block row are staged in shared memory one block row ahead, so decoding never
+//              waits on DRAM;
 //   warp  8    one elected thread issues the MMAs, commits them to the stage's "empty" barrier
 //              and, after the last block of a block row, to the accumulator's "full" barrier;
 //   warps 0-3  epilogue: tcgen05.ld the accumulators (double buffered in TMEM so the next block
@@ -40,7 +45,6 @@ std::uint64_t qbell_tcgen05_workspace_bytes(std::int64_t cols, std::int64_t n) {
 namespace {
 
 constexpr int kStages = 4;
-constexpr int kLookahead = 2;
 constexpr int kMaxWidth = 16;                      // blocks per block row the staging area holds
 constexpr int kCodesStageBytes = 32 * 512;         // one block row of codes: 32 cells x up to 512 bytes
 constexpr int kMetaStageBytes = kMaxWidth * 256;   // per block: 32 scales + 32 offsets
@@ -59,7 +63,7 @@ struct tc_params {
     const std::uint8_t *packed;
     const float *scales;
     const float *offsets;
-    const __nv_bfloat16 *wt; // [n][kpad]
+    const __nv_bfloat16 *wt; // [kpad/32 gene blocks][n x 32 slice of W^T in operand layout]
     std::int64_t kpad;
     float *y;
     std::int64_t y_ld;
@@ -100,6 +104,16 @@ __device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity
     }
 }
 
+__device__ __forceinline__ void bar_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One contiguous global -> shared copy by the copy engine (this GPU's own memory, no multicast);
+// completion is counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes, std::uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
 __device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -153,22 +167,20 @@ __device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// W [genes][n] (leading dimension ld) -> W^T [n][kpad], zero for genes >= cols.
-__global__ void __launch_bounds__(256) transpose_w_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
-                                                          __nv_bfloat16 *wt, std::int64_t kpad) {
-    __shared__ __nv_bfloat16 tile[32][33];
-    const int gx = blockIdx.x * 32, nx = blockIdx.y * 32; // gene tile, output-column tile
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
-    for (int r = ty; r < 32; r += 8) {
-        const std::int64_t gene = gx + r;
-        const int col = nx + tx;
-        tile[r][tx] = (gene < cols && col < n) ? w[gene * ld + col] : __float2bfloat16(0.0f);
-    }
-    __syncthreads();
-    for (int r = ty; r < 32; r += 8) {
-        const int col = nx + r;
-        const std::int64_t gene = gx + tx;
-        if (col < n && gene < kpad) wt[col * kpad + gene] = tile[tx][r];
+// W [genes][n] (leading dimension ld) -> per gene block of 32, the n x 32 slice of W^T already in
+// the shared-memory operand layout (core matrices of 8 output columns x 8 genes, 128 bytes each:
+// byte offset of (column m, gene e) = (m/8)*512 + (e/8)*128 + (m%8)*16 + (e%8)*2), zero for
+// genes >= cols.  A block's slice is one contiguous n*64-byte range, so the main kernel fetches it
+// with a single bulk copy.
+__global__ void __launch_bounds__(256) pack_w_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
+                                                     __nv_bfloat16 *packed_wt) {
+    const std::int64_t block = blockIdx.x;                     // gene block
+    __nv_bfloat16 *dst = packed_wt + block * static_cast<std::int64_t>(n) * 32;
+    for (int i = threadIdx.x; i < n * 32; i += blockDim.x) {
+        const int e = i / n, m = i % n;                        // consecutive threads read consecutive columns of one gene
+        const std::int64_t gene = block * 32 + e;
+        const __nv_bfloat16 v = gene < cols ? w[gene * ld + m] : __float2bfloat16(0.0f);
+        dst[((m >> 3) * 512 + (e >> 3) * 128 + (m & 7) * 16 + (e & 7) * 2) >> 1] = v;
     }
 }
 
@@ -249,7 +261,6 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
         };
 
         long long item = 0;                // items issued by this thread
-        long long signalled = 0;           // items whose "full" barrier this thread has arrived on
         int iteration = 0;
         if (first < p.block_row_end) prefetch_block_row(first, 0);
         cp_async_commit();
@@ -273,13 +284,10 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                 bar_wait(smem_addr(empty_bar + stage), static_cast<std::uint32_t>(((item / kStages) & 1) ^ 1), abort_flag);
                 const std::uint32_t a_tile = smem0 + stage * kStageBytes;
                 const std::uint32_t b_tile = a_tile + kATileBytes;
-                // ---- A: the block's 32 genes of W^T for all H*128 output columns (16-byte chunks)
-                const __nv_bfloat16 *src = p.wt + static_cast<std::int64_t>(bc) * 32;
-#pragma unroll
-                for (int it = 0; it < (H * 128 * 4) / kProducerThreads; ++it) {
-                    const int i = it * kProducerThreads + pt;
-                    const int m = i >> 2, c = i & 3;
-                    cp_async_16(a_tile + (m >> 3) * 512 + c * 128 + (m & 7) * 16, src + static_cast<std::int64_t>(m) * p.kpad + c * 8);
+                // ---- A: the block's slice of W^T, already in operand layout: one bulk copy
+                if (pt == 0) {
+                    bar_expect_tx(smem_addr(full_bar + stage), H * 128 * 64);
+                    bulk_copy_g2s(a_tile, p.wt + static_cast<std::int64_t>(bc) * (H * 128 * 32), H * 128 * 64, smem_addr(full_bar + stage));
                 }
                 // ---- B: decode 8 codes of (cell, genes chunk) to bf16, from the staged copies
                 const std::int64_t gene0 = static_cast<std::int64_t>(bc) * 32 + chunk * 8;
@@ -330,22 +338,12 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w32[0]), "r"(w32[1]), "r"(w32[2]), "r"(w32[3])
                                  : "memory");
                 }
-                cp_async_commit();
+                fence_async_proxy();                      // the B tile was written with ordinary stores
+                bar_arrive(smem_addr(full_bar + stage));
                 ++item;
-                if (item - signalled > kLookahead) {
-                    cp_async_wait<kLookahead>();
-                    fence_async_proxy();
-                    bar_arrive(smem_addr(full_bar + static_cast<int>(signalled % kStages)));
-                    ++signalled;
-                }
             }
         }
         cp_async_wait<0>();
-        fence_async_proxy();
-        while (signalled < item) {
-            bar_arrive(smem_addr(full_bar + static_cast<int>(signalled % kStages)));
-            ++signalled;
-        }
     } else if (warp == 8) {
         // ================= MMA issuer =================
         long long item = 0;
@@ -462,13 +460,10 @@ cb200_status launch_qbell_tcgen05(const qbell_view &x, const dense_args &d, std:
     int *status = static_cast<int *>(workspace);
     __nv_bfloat16 *wt = reinterpret_cast<__nv_bfloat16 *>(static_cast<unsigned char *>(workspace) + 256);
     CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    {
-        const dim3 grid(static_cast<unsigned>(kpad / 32), static_cast<unsigned>((d.n + 31) / 32));
-        transpose_w_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols,
-                                                     static_cast<int>(d.n), wt, kpad);
-        count_launch();
-        CB200_CUDA_OK(cudaGetLastError());
-    }
+    pack_w_kernel<<<static_cast<unsigned>(kpad / 32), 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld,
+                                                                        x.cols, static_cast<int>(d.n), wt);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
     tc_params p{};
     p.rows = x.rows; p.cols = x.cols; p.width = x.ell_cols / 32; p.row_stride = x.row_stride_bytes;
     p.block_col_idx = x.block_col_idx; p.packed = x.packed; p.scales = x.scales; p.offsets = x.offsets;
