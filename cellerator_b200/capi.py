@@ -65,7 +65,8 @@ class SpmmProblem(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("projection", C.c_int32), ("m", C.c_int64),
                 ("k", C.c_int64), ("n", C.c_int64), ("nnz", C.c_int64), ("bits", C.c_int32), ("policy", C.c_int32),
                 ("dense_dtype", C.c_int32), ("device", C.c_int32), ("structure_epoch", C.c_uint64),
-                ("host_row_ptr", C.c_void_p), ("deterministic", C.c_int32), ("reserved", C.c_int32)]
+                ("host_row_ptr", C.c_void_p), ("deterministic", C.c_int32), ("multiply", C.c_int32),
+                ("device_matrix", C.POINTER(QCsr))]
 
 
 class Launch(C.Structure):

@@ -66,6 +66,9 @@ struct cb200_prepared {
     // persistent state built at prepare time (persistent_kernel_state, operation_core.hh:126-129):
     // the rows in descending order of length, on the device; null when no host row_ptr was given
     std::int32_t *row_order;
+    // ... and, when prepare was given the device-resident matrix and bf16 products are allowed, the
+    // window-blocked copy the tensor-core kernel streams
+    blocked_layout blocked;
     std::uint64_t persistent_bytes;
 };
 
@@ -214,8 +217,11 @@ cb200_status cb200_backend_query(int32_t projection, const cb200_numeric_policy 
     switch (projection) {
     case CB200_PROJECTION_CSR:
         out->name = "cb200.qcsr.forward.sm100a";
-        out->supported = common && supported_dense(numeric->dense_storage) && numeric->multiply == CB200_DTYPE_F32;
-        /* one warp owns a row and sums in a fixed order: repeated runs are bitwise identical */
+        /* fp32 products for either W type; bf16 products (tensor cores) only with a bf16 W */
+        out->supported = common && supported_dense(numeric->dense_storage) &&
+                         (numeric->multiply == CB200_DTYPE_F32 ||
+                          (numeric->multiply == CB200_DTYPE_BF16 && numeric->dense_storage == CB200_DTYPE_BF16));
+        /* a row is summed by one owner in a fixed order: repeated runs are bitwise identical */
         out->flags = CB200_CAP_DETERMINISTIC | CB200_CAP_GRAPH_CAPTURE;
         break;
     case CB200_PROJECTION_TRANSPOSE:
@@ -248,6 +254,11 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     if (!supported_bits(problem->bits)) return fail(CB200_STATUS_UNSUPPORTED, "bits must be 4 or 8, got %d", problem->bits);
     if (problem->policy != CB200_DECODE_PER_GENE_AFFINE && problem->policy != CB200_DECODE_COLUMN_SCALE_ROW_OFFSET)
         return fail(CB200_STATUS_UNSUPPORTED, "unknown decode policy %d", problem->policy);
+    if (problem->multiply != 0 && problem->multiply != CB200_DTYPE_F32 && problem->multiply != CB200_DTYPE_BF16)
+        return fail(CB200_STATUS_UNSUPPORTED, "multiply must be fp32 or bf16, got %d", problem->multiply);
+    if (problem->multiply == CB200_DTYPE_BF16 &&
+        (problem->projection == CB200_PROJECTION_TRANSPOSE || problem->dense_dtype != CB200_DTYPE_BF16))
+        return fail(CB200_STATUS_UNSUPPORTED, "bf16 products need a forward projection with a bf16 dense operand");
     if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         if (problem->dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes fp32 G");
         if (problem->deterministic) return fail(CB200_STATUS_UNSUPPORTED, "transpose is not deterministic");
@@ -271,6 +282,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     if (p == nullptr) return fail(CB200_STATUS_INTERNAL_ERROR, "out of host memory");
     p->problem = *problem;
     p->problem.host_row_ptr = nullptr; /* borrowed for the analysis below only */
+    p->problem.device_matrix = nullptr;
     p->sm_count = prop.multiProcessorCount;
     p->schedule = fwd_schedule::warp_per_row;
     p->schedule_name = "warp_per_row";
@@ -311,6 +323,49 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             p->schedule_name = "gene_tiled";
         }
         p->workspace_bytes = 256u; // status word of the tiled kernel
+        // bf16 products allowed: the tensor-core kernel, which treats 512-row x 64-gene windows as
+        // dense.  That pays once a window holds enough stored entries (density) and there are row
+        // groups for every SM; otherwise the exact kernels above run (they satisfy the policy too).
+        const bool tensor_ok = problem->multiply == CB200_DTYPE_BF16 && problem->dense_dtype == CB200_DTYPE_BF16 &&
+                               (problem->n == 32 || problem->n == 64 || problem->n == 128) && problem->k > 0;
+        bool tensor = tensor_ok && problem->m >= 512 && p->mean_row_nnz >= 0.10 * static_cast<double>(problem->k);
+        if (force != nullptr) tensor = tensor_ok && std::strcmp(force, "tensor_windows") == 0;
+        if (tensor) {
+            tiled = true; // same length-sorted row order
+            p->schedule = fwd_schedule::tensor_windows;
+            p->schedule_name = "tensor_windows";
+            p->workspace_bytes = qcsr_mma_workspace_bytes(problem->k, problem->n);
+        }
+        // With the device-resident matrix at hand, prepare re-lays it once into the window-blocked
+        // copy (persistent preprocessing) and the tensor-core kernel streams that instead of the CSR
+        // arrays.  Its cost follows the dense area m x k, so it needs a minimum density to pay.
+        bool blocked = tensor_ok && problem->device_matrix != nullptr &&
+                       qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype) &&
+                       problem->m >= 16 * 256 && p->mean_row_nnz >= 0.015 * static_cast<double>(problem->k);
+        if (force != nullptr)
+            blocked = tensor_ok && problem->device_matrix != nullptr && std::strcmp(force, "tensor_blocked") == 0 &&
+                      qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype);
+        if (blocked) {
+            const cb200_qcsr &dm = *problem->device_matrix;
+            if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
+                dm.bits != problem->bits) {
+                delete p;
+                return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
+            }
+            device_scope scope(problem->device);
+            cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
+                                                          : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), &p->blocked);
+            if (st != CB200_STATUS_SUCCESS) {
+                delete p;
+                return st;
+            }
+            if (p->schedule != fwd_schedule::tensor_windows) tiled = true; // the fallback for unaligned row ranges
+            p->schedule = fwd_schedule::tensor_blocked;
+            p->schedule_name = "tensor_blocked";
+            p->workspace_bytes = std::max<std::uint64_t>(qcsr_blocked_workspace_bytes(problem->k, problem->n), 256u);
+            p->persistent_bytes += p->blocked.bytes;
+        }
         // The tiled kernel gives each row to one lane group, so a CTA is as slow as its longest row.
         // With the row lengths at hand, order the rows by length once (persistent preprocessing):
         // every CTA then works on rows of nearly equal length.
@@ -328,10 +383,11 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             if (err == cudaSuccess) err = cudaMemcpy(p->row_order, order.data(), bytes, cudaMemcpyHostToDevice);
             if (err != cudaSuccess) {
                 if (p->row_order != nullptr) cudaFree(p->row_order);
+                free_blocked_layout(&p->blocked);
                 delete p;
                 return fail(CB200_STATUS_CUDA_ERROR, "row order upload: %s", cudaGetErrorString(err));
             }
-            p->persistent_bytes = bytes;
+            p->persistent_bytes += bytes;
         }
     }
     *out = p;
@@ -340,9 +396,10 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
 
 void cb200_prepared_destroy(cb200_prepared *prepared) {
     if (prepared == nullptr) return;
-    if (prepared->row_order != nullptr) {
+    if (prepared->row_order != nullptr || prepared->blocked.seg_ptr != nullptr) {
         device_scope scope(prepared->problem.device);
-        cudaFree(prepared->row_order);
+        if (prepared->row_order != nullptr) cudaFree(prepared->row_order);
+        free_blocked_layout(&prepared->blocked);
     }
     delete prepared;
 }
@@ -418,8 +475,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     if (pr.projection == CB200_PROJECTION_TRANSPOSE)
         return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, launch->workspace, launch->workspace_bytes,
                                      prepared->sm_count, stream);
-    return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, launch->workspace,
-                               prepared->sm_count, stream);
+    return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, &prepared->blocked,
+                               launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);
 }
 
 /* ---- session ------------------------------------------------------------------------------ */

@@ -27,7 +27,7 @@ struct dense_args {
     float alpha, beta;
 };
 
-enum class fwd_schedule : int { warp_per_row = 0, gene_tiled = 1 };
+enum class fwd_schedule : int { warp_per_row = 0, gene_tiled = 1, tensor_windows = 2, tensor_blocked = 3 };
 
 // Gene-tiled kernel (W staged through shared memory); *taken is false when the shape is outside
 // what it covers, and the caller then runs the warp-per-row kernel.
@@ -36,10 +36,42 @@ cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, 
                                        std::int64_t row_end, int *status_word, const std::int32_t *row_order,
                                        int sm_count, cudaStream_t stream, bool *taken);
 
+// Tensor-core kernel for bf16 products (decoded values rounded to bf16): entries are scattered
+// into dense operand tiles in shared memory, window by window of 64 genes.  `workspace` holds the
+// status word and W re-laid per window; *taken is false when the shape or workspace rules it out.
+bool qcsr_forward_mma_supported(const qcsr_view &x, const dense_args &d);
+std::uint64_t qcsr_mma_workspace_bytes(std::int64_t cols, std::int64_t n);
+cb200_status launch_qcsr_forward_mma(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                     std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                     const std::int32_t *row_order, int sm_count, cudaStream_t stream, bool *taken);
+
+// Window-blocked copy of a matrix, built once at prepare time for the tensor-core kernel below:
+// groups of 256 consecutive rows, inside a group the entries ordered by window of 128 genes, one
+// 32-bit word per entry; seg_ptr[group * windows + window] is the first word of a segment.
+struct blocked_layout {
+    std::uint32_t *entries = nullptr;
+    std::int64_t *seg_ptr = nullptr;
+    std::int64_t groups = 0;
+    int windows = 0;
+    std::int64_t total_entries = 0;
+    std::uint64_t bytes = 0;
+    const void *src_row_ptr = nullptr, *src_col_idx = nullptr, *src_packed = nullptr; // arrays it was built from
+};
+bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
+std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
+cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out); // current device; allocates and synchronises
+void free_blocked_layout(blocked_layout *layout);
+// *taken is false when the launch cannot use the copy (row range not starting on a group boundary,
+// workspace too small, ...); a matrix other than the one the copy was built from is an error.
+cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                         std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                         const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken);
+
 // Y[r,:] = alpha * sum_i deq(code_i) * W[col_i,:] + beta * Y[r,:]  for r in [row_begin,row_end)
 cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                  std::int64_t row_end, fwd_schedule schedule, const void *persistent,
-                                 void *workspace, int sm_count, cudaStream_t stream);
+                                 const blocked_layout *blocked, void *workspace, std::uint64_t workspace_bytes,
+                                 int sm_count, cudaStream_t stream);
 
 // G'[g,:] = alpha * sum_{r in range, col_i == g} deq(code_i) * G[r,:] + beta * G'[g,:]
 cb200_status launch_qcsr_transpose(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,

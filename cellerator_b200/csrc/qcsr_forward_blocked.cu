@@ -1,0 +1,636 @@
+// Quantized CSR forward projection on the tensor cores from a window-blocked copy of the matrix
+// (schedule "tensor_blocked"), for callers whose numeric policy allows bf16 products and who hand
+// the device-resident matrix to prepare:
+//     Y[cells, N] = alpha * deq(X)[cells, genes] * W[genes, N] + beta * Y,   N in {32, 64, 128}.
+//
+// Reference counterpart: csr_spmm_fwd over dequantised values (src/compute/sparse/ops/base_sparse.cu)
+// behind the CP-Math sparse_dense_multiply operation; the reference has no persistent re-layout,
+// its prepared_operation only carries one (persistent_kernel_state, operation_core.hh:126-129).
+//
+// Idea.  At N = 64 a stored entry costs 64 multiply-adds; the CUDA cores cannot do that at the
+// rate HBM delivers entries, the tensor cores can, even if a 256-cell x 128-gene window of the
+// matrix (1,750 stored entries on the 1M x 33,538 matrix) is multiplied as a dense tile.  So the
+// kernel densifies window by window: the window's entries are decoded to bf16 and scattered into
+// a zeroed operand tile in shared memory, and sixteen 128 x N x 16 tcgen05 MMAs multiply the tile
+// with the window's slice of W.  Feeding that from CSR needs one thread per row, which diverges
+// and issues one uncoalesced load per four entries.  Instead prepare re-lays the matrix once:
+// groups of 256 consecutive cell rows, and inside a group the entries ordered by gene window.
+// An entry of the copy is one 32-bit word {code, gene within window, byte position in the tile};
+// a (group, window) segment is contiguous, so the copy engine streams it into shared memory and
+// every lane of the CTA decodes entries, four at a time, with no divergence.
+//
+// Structure of a CTA (320 threads, one CTA per SM, row groups dealt round-robin):
+//   warps 0-7  zero the A tile, wait for the segment's chunks (8 KB each, 3-stage ring), decode
+//              and scatter; later thread t owns TMEM lane t: row t of the group, and writes Y;
+//   warp 8     one thread issues the MMAs (2 row sub-blocks x 8 K-steps per window), commits the
+//              window to the "A tile free" and "W stage free" barriers, the last window of a group
+//              to "accumulators complete";
+//   warp 9     one thread feeds both rings with bulk async copies: W slices (re-laid per window
+//              into the K-major core-matrix operand layout by a small kernel before the main one,
+//              followed by the window's {scale, zero-point} table) and entry chunks.
+// Every barrier wait is bounded; on a time-out a status word is raised, waits stop blocking, and
+// the kernel runs to completion and frees its TMEM.  A non-zero status means Y is not valid.
+#include "kernels.cuh"
+
+#include <cuda_bf16.h>
+
+namespace cb200 {
+namespace {
+
+constexpr int kWin = 128;                    // genes per window
+constexpr int kWinShift = 7;
+constexpr int kRows = 256;                   // cell rows per group
+constexpr int kRowsShift = 8;
+constexpr int kSubBlocks = kRows / 128;      // one M = 128 MMA each
+constexpr int kProducerWarps = 8;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kThreads = kProducerThreads + 64; // + MMA warp + loader warp
+constexpr int kABufBytes = kRows * kWin * 2;    // 64 KB
+constexpr int kSubBlockBytes = 128 * kWin * 2;  // 32 KB
+constexpr int kRowGroupBytes = kWin * 16;       // 8 rows x kWin genes of bf16
+constexpr int kChunkEntries = 2048;
+constexpr int kChunkBytes = kChunkEntries * 4;
+constexpr int kChunkStages = 3;
+constexpr std::uint32_t kInvalidEntry = 0x80000000u; // padding of a segment
+static_assert(kProducerThreads == kRows, "thread t owns row t of the group in the epilogue");
+
+__host__ __device__ constexpr int record_bytes(int n) { return n * kWin * 2 + kWin * 8; }
+__host__ __device__ constexpr int fixed_smem_bytes() { return 2 * kABufBytes + kChunkStages * kChunkBytes + kRows * 4 + 512; }
+__host__ __device__ constexpr int w_stages(int n) {
+    return (232448 - fixed_smem_bytes()) / record_bytes(n) >= 4 ? 4 : (232448 - fixed_smem_bytes()) / record_bytes(n);
+}
+
+// byte position of (row within group, gene within window) in the A tile: two sub-blocks of 128
+// rows, each K-major without swizzle (core matrices of 8 rows x 16 bytes; the 16 core matrices of
+// a row group side by side, row groups 2,048 bytes apart)
+__host__ __device__ constexpr std::uint32_t tile_offset(int rl, int gl) {
+    return static_cast<std::uint32_t>((rl >> 7) * kSubBlockBytes + ((rl & 127) >> 3) * kRowGroupBytes + (rl & 7) * 16 +
+                                      (gl >> 3) * 128 + (gl & 7) * 2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// prepare time: the window-blocked copy
+
+template<int BITS>
+__device__ __forceinline__ unsigned load_code(const std::uint8_t *row_bytes, std::int64_t local) {
+    if constexpr (BITS == 8) {
+        return row_bytes[local];
+    } else {
+        const unsigned byte = row_bytes[local >> 1];
+        return (local & 1) ? (byte >> 4) : (byte & 0xfu);
+    }
+}
+
+// One thread per row walks its entries; a run is a maximal stretch of consecutive entries in one
+// gene window (rows with ascending genes have one run per window they touch).  FILL == false adds
+// the run lengths to counts[group * windows + window]; FILL == true reserves the run's place in
+// the segment with one atomic and writes its entries.  Entries with a gene outside [0, cols) are
+// left out by both passes.
+template<int BITS, bool FILL>
+__global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *row_ptr, const std::int64_t *packed_row_ptr,
+                                                           const std::int32_t *col_idx, const std::uint8_t *packed,
+                                                           std::int64_t rows, std::int64_t cols, int windows,
+                                                           unsigned *counts, unsigned long long *cursor, std::uint32_t *entries) {
+    const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const std::int64_t group = r >> kRowsShift;
+    const int rl = static_cast<int>(r & (kRows - 1));
+    const std::int64_t begin = row_ptr[r], end = row_ptr[r + 1];
+    const std::uint8_t *row_bytes = packed + (packed_row_ptr != nullptr ? packed_row_ptr[r] : begin);
+    std::int64_t run_start = begin;
+    int run_window = -1;
+    auto close_run = [&](std::int64_t run_end) {
+        const std::int64_t length = run_end - run_start;
+        if (run_window < 0 || length <= 0) return;
+        const std::int64_t seg = group * windows + run_window;
+        if constexpr (!FILL) {
+            atomicAdd(counts + seg, static_cast<unsigned>(length));
+        } else {
+            std::uint32_t *dst = entries + atomicAdd(cursor + seg, static_cast<unsigned long long>(length));
+            for (std::int64_t i = run_start; i < run_end; ++i) {
+                const int gl = col_idx[i] & (kWin - 1);
+                dst[i - run_start] = load_code<BITS>(row_bytes, i - begin) | (static_cast<std::uint32_t>(gl) << 8) |
+                                     ((tile_offset(rl, gl) >> 1) << 15);
+            }
+        }
+    };
+    for (std::int64_t i = begin; i < end; ++i) {
+        const std::int64_t gene = col_idx[i];
+        const int window = (gene >= 0 && gene < cols) ? static_cast<int>(gene >> kWinShift) : -1;
+        if (window != run_window) {
+            close_run(i);
+            run_window = window;
+            run_start = i;
+        }
+    }
+    close_run(end);
+}
+
+// seg_ptr[i] = sum of counts[0..i) rounded up to multiples of 4 (16-byte segments for the copy
+// engine), cursor = seg_ptr.  One block; every thread scans a contiguous slice.
+__global__ void __launch_bounds__(1024) segment_scan_kernel(const unsigned *counts, std::int64_t segments, std::int64_t *seg_ptr,
+                                                            unsigned long long *cursor) {
+    __shared__ long long partial[1024];
+    const std::int64_t per = (segments + 1023) / 1024;
+    const std::int64_t lo = min(segments, per * threadIdx.x), hi = min(segments, lo + per);
+    long long sum = 0;
+    for (std::int64_t i = lo; i < hi; ++i) sum += (counts[i] + 3u) & ~3u;
+    partial[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long run = 0;
+        for (int i = 0; i < 1024; ++i) {
+            const long long v = partial[i];
+            partial[i] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    long long at = partial[threadIdx.x];
+    for (std::int64_t i = lo; i < hi; ++i) {
+        seg_ptr[i] = at;
+        cursor[i] = static_cast<unsigned long long>(at);
+        at += (counts[i] + 3u) & ~3u;
+    }
+    if (threadIdx.x == 1023) seg_ptr[segments] = at; // the last slice (possibly empty) ends at the total
+}
+
+// ---------------------------------------------------------------------------------------------
+// run time
+
+struct blocked_params {
+    const std::uint32_t *entries;
+    const std::int64_t *seg_ptr;
+    const float *row_offsets; // per cell row, row-offset policy only
+    const unsigned char *records;
+    float *y;
+    std::int64_t y_ld;
+    std::int64_t row_end;     // rows >= row_end are computed but not written
+    std::int64_t group_begin, group_end;
+    int windows;
+    float alpha, beta;
+    int *status;
+};
+
+__device__ __forceinline__ std::uint32_t smem_addr(const void *p) { return static_cast<std::uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bar_init(std::uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(std::uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bar_arrive_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(std::uint32_t bar, std::uint32_t parity) {
+    std::uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0u;
+}
+// Bounded wait.  Once any wait of the CTA has timed out (`*abort_flag` set) waits return at once.
+__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag) {
+    int spins = 0;
+    while (!bar_try_wait(bar, parity)) {
+        if (*abort_flag != 0) return;
+        if (++spins > (1 << 22)) {
+            *abort_flag = 1;
+            return;
+        }
+    }
+}
+// One contiguous global -> shared copy by the copy engine (this GPU's own memory, no multicast).
+__device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes, std::uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major operand, no swizzle: LBO = 128 B between the two core matrices one K = 16 step reads,
+// SBO = kRowGroupBytes between groups of 8 rows.
+__device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
+    std::uint64_t d = 0;
+    d |= static_cast<std::uint64_t>((addr & 0x3ffffu) >> 4);
+    d |= static_cast<std::uint64_t>(128u >> 4) << 16;
+    d |= static_cast<std::uint64_t>(static_cast<unsigned>(kRowGroupBytes) >> 4) << 32;
+    d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
+    return d;
+}
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, M = 128.
+__host__ __device__ constexpr std::uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((static_cast<std::uint32_t>(n) >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b, std::uint32_t idesc,
+                                         bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(std::uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
+    std::uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+          "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// W [genes][n] (leading dimension ld) -> one record per window of 128 genes: the n x 128 slice of
+// W^T in operand layout (byte offset of (column c, gene e) = (c/8)*2048 + (e/8)*128 + (c%8)*16 +
+// (e%8)*2, zero for genes >= cols) followed by 128 x {scale, zero-point}.
+__global__ void __launch_bounds__(256) pack_windows_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
+                                                           const float *scales, const float *offsets, int per_gene_offsets,
+                                                           unsigned char *records) {
+    const std::int64_t window = blockIdx.x;
+    unsigned char *rec = records + window * record_bytes(n);
+    __nv_bfloat16 *wt = reinterpret_cast<__nv_bfloat16 *>(rec);
+    for (int i = threadIdx.x; i < n * kWin; i += blockDim.x) {
+        const int e = i / n, c = i % n; // consecutive threads read consecutive columns of one gene
+        const std::int64_t gene = window * kWin + e;
+        const __nv_bfloat16 v = gene < cols ? w[gene * ld + c] : __float2bfloat16(0.0f);
+        wt[((c >> 3) * kRowGroupBytes + (e >> 3) * 128 + (c & 7) * 16 + (e & 7) * 2) >> 1] = v;
+    }
+    float2 *table = reinterpret_cast<float2 *>(rec + n * kWin * 2);
+    for (int e = threadIdx.x; e < kWin; e += blockDim.x) {
+        const std::int64_t gene = window * kWin + e;
+        float2 so = make_float2(0.0f, 0.0f);
+        if (gene < cols) {
+            so.x = scales != nullptr ? scales[gene] : 1.0f;
+            so.y = (per_gene_offsets && offsets != nullptr) ? offsets[gene] : 0.0f;
+        }
+        table[e] = so;
+    }
+}
+
+template<int NC>
+__global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blocked_params p) {
+    constexpr int REC = record_bytes(NC);
+    constexpr int STAGES = w_stages(NC);
+    constexpr int kTmemCols = kSubBlocks * NC < 32 ? 32 : kSubBlocks * NC; // one accumulator per row sub-block
+    constexpr std::uint32_t IDESC = instr_desc(NC);
+    extern __shared__ __align__(1024) unsigned char smem[];
+    // [2][A tile] | [STAGES][W record] | [kChunkStages][entry chunk] | row offsets | barriers | chunk meta | tmem | abort
+    unsigned char *chunk_base = smem + 2 * kABufBytes + STAGES * REC;
+    float *row_offset_s = reinterpret_cast<float *>(chunk_base + kChunkStages * kChunkBytes);
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(row_offset_s + kRows);
+    std::uint64_t *a_full = bars;                      // [2]            scatter warps -> MMA (one arrival per warp)
+    std::uint64_t *a_empty = bars + 2;                 // [2]            MMA commit -> scatter warps
+    std::uint64_t *w_full = bars + 4;                  // [STAGES]       copy engine -> MMA, scatter warps
+    std::uint64_t *w_empty = w_full + STAGES;          // [STAGES]       MMA commit -> loader
+    std::uint64_t *c_full = w_empty + STAGES;          // [kChunkStages] copy engine -> scatter warps
+    std::uint64_t *c_empty = c_full + kChunkStages;    // [kChunkStages] scatter warps -> loader (one arrival per warp)
+    std::uint64_t *acc_full = c_empty + kChunkStages;  // MMA commit -> scatter warps
+    std::uint64_t *acc_empty = acc_full + 1;           // scatter warps -> MMA (one arrival per warp)
+    volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [kChunkStages] (entries << 1) | last chunk of its window
+    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + kChunkStages + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const std::uint32_t smem0 = smem_addr(smem);
+    const std::uint32_t wstage0 = smem0 + 2 * kABufBytes;
+    const std::uint32_t chunk0 = wstage0 + STAGES * REC;
+
+    if (tid == 0) {
+        for (int b = 0; b < 2; ++b) {
+            bar_init(smem_addr(a_full + b), kProducerWarps);
+            bar_init(smem_addr(a_empty + b), 1);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            bar_init(smem_addr(w_full + s), 1);
+            bar_init(smem_addr(w_empty + s), 1);
+        }
+        for (int s = 0; s < kChunkStages; ++s) {
+            bar_init(smem_addr(c_full + s), 1);
+            bar_init(smem_addr(c_empty + s), kProducerWarps);
+        }
+        bar_init(smem_addr(acc_full), 1);
+        bar_init(smem_addr(acc_empty), kProducerWarps);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const std::uint32_t tmem_base = *tmem_slot;
+
+    // this CTA's row groups: group_begin + blockIdx.x, + gridDim.x, ...
+    const std::int64_t first_group = p.group_begin + blockIdx.x;
+    const std::int64_t my_groups = first_group < p.group_end ? (p.group_end - first_group + gridDim.x - 1) / gridDim.x : 0;
+
+    if (warp < kProducerWarps) {
+        // ================= zero, scatter, epilogue =================
+        const int sub = tid >> 7;
+        const bool use_row_offset = p.row_offsets != nullptr;
+        long long q = 0;  // windows done by this CTA
+        long long qc = 0; // chunks done by this CTA
+        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+            const std::int64_t group = first_group + gi * gridDim.x;
+            const std::int64_t row = group * kRows + tid;
+            if (use_row_offset) {
+                asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the previous group's scatter is over
+                row_offset_s[tid] = row < p.row_end ? __ldg(p.row_offsets + row) : 0.0f;
+                asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+            }
+            for (int w = 0; w < p.windows; ++w, ++q) {
+                const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
+                const int s = static_cast<int>(q % STAGES);
+                bar_wait(smem_addr(a_empty + b), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
+                unsigned char *tile = smem + b * kABufBytes;
+#pragma unroll
+                for (int k = 0; k < kABufBytes / (kProducerThreads * 16); ++k)
+                    *reinterpret_cast<uint4 *>(tile + k * (kProducerThreads * 16) + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the whole tile is zero before anyone scatters
+                bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag);
+                const float2 *table = reinterpret_cast<const float2 *>(smem + 2 * kABufBytes + s * REC + NC * kWin * 2);
+                bool last = false;
+                int guard = 0;
+                while (!last && ++guard < (1 << 20)) {
+                    const int cs = static_cast<int>(qc % kChunkStages);
+                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kChunkStages) & 1), abort_flag);
+                    const int meta = chunk_meta[cs];
+                    const int count = *abort_flag != 0 ? 0 : (meta >> 1);
+                    last = (meta & 1) != 0 || *abort_flag != 0;
+                    const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunkBytes);
+                    for (int i = tid * 4; i < count; i += kProducerThreads * 4) {
+                        const uint4 e4 = chunk[i >> 2];
+                        const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+                        float2 t[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) t[k] = table[(e[k] >> 8) & (kWin - 1)];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const std::uint32_t off = ((e[k] >> 15) & 0x7fffu) << 1;
+                            float add = t[k].y;
+                            if (use_row_offset) // row within the group, back from the byte position in the tile
+                                add = row_offset_s[((off >> 15) << 7) | (((off >> 11) & 15u) << 3) | ((off >> 4) & 7u)];
+                            const float value = fmaf(static_cast<float>(e[k] & 0xffu), t[k].x, add);
+                            if (static_cast<int>(e[k]) >= 0) *reinterpret_cast<__nv_bfloat16 *>(tile + off) = __float2bfloat16_rn(value);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
+                    ++qc;
+                }
+                fence_async_proxy(); // the tile was written with ordinary stores, the MMA reads it through the async proxy
+                __syncwarp();
+                if (lane == 0) bar_arrive(smem_addr(a_full + b));
+            }
+
+            // ---- thread t writes row t of the group: TMEM lane = row within the sub-block
+            bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(gi & 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int h = 0; h < NC / 32; ++h) {
+                float v[32];
+                tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
+                if (row < p.row_end) {
+                    float *out = p.y + row * p.y_ld + h * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        float4 r = make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]);
+                        if (p.beta != 0.0f) {
+                            const float4 o = *reinterpret_cast<const float4 *>(out + c);
+                            r.x = fmaf(p.beta, o.x, r.x); r.y = fmaf(p.beta, o.y, r.y);
+                            r.z = fmaf(p.beta, o.z, r.z); r.w = fmaf(p.beta, o.w, r.w);
+                        }
+                        *reinterpret_cast<float4 *>(out + c) = r;
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(smem_addr(acc_empty));
+        }
+    } else if (warp == kProducerWarps) {
+        // ================= MMA issuer =================
+        long long q = 0;
+        for (std::int64_t g = 0; g < my_groups; ++g) {
+            bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((g & 1) ^ 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int w = 0; w < p.windows; ++w, ++q) {
+                const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
+                const int s = static_cast<int>(q % STAGES);
+                bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag);
+                bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    const std::uint32_t a_tile = smem0 + b * kABufBytes;
+                    const std::uint32_t b_tile = wstage0 + s * REC;
+#pragma unroll
+                    for (int kk = 0; kk < kWin / 16; ++kk) {
+                        const std::uint64_t db = smem_desc(b_tile + kk * 256);
+#pragma unroll
+                        for (int sb = 0; sb < kSubBlocks; ++sb)
+                            mma_bf16(tmem_base + sb * NC, smem_desc(a_tile + sb * kSubBlockBytes + kk * 256), db, IDESC,
+                                     w > 0 || kk > 0);
+                    }
+                    mma_commit(smem_addr(a_empty + b));
+                    mma_commit(smem_addr(w_empty + s));
+                    if (w == p.windows - 1) mma_commit(smem_addr(acc_full));
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ================= loader: W slices and entry chunks =================
+        long long q = 0, qc = 0;
+        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+            const std::int64_t seg0 = (first_group + gi * gridDim.x) * p.windows;
+            for (int wbase = 0; wbase < p.windows; wbase += 31) {
+                // segment bounds of up to 31 windows in one coalesced read
+                const int span = min(31, p.windows - wbase);
+                const std::int64_t mine = lane <= span ? __ldg(p.seg_ptr + seg0 + wbase + lane) : 0;
+                for (int j = 0; j < span; ++j, ++q) {
+                    const std::int64_t lo = __shfl_sync(0xffffffffu, mine, j), hi = __shfl_sync(0xffffffffu, mine, j + 1);
+                    if (lane != 0) continue;
+                    const int s = static_cast<int>(q % STAGES);
+                    bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag);
+                    bar_arrive_expect_tx(smem_addr(w_full + s), REC);
+                    bulk_copy_g2s(wstage0 + s * REC, p.records + static_cast<std::size_t>(wbase + j) * REC, REC, smem_addr(w_full + s));
+                    std::int64_t at = lo;
+                    do {
+                        const int count = static_cast<int>(min(static_cast<std::int64_t>(kChunkEntries), hi - at));
+                        const int cs = static_cast<int>(qc % kChunkStages);
+                        bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / kChunkStages) & 1) ^ 1), abort_flag);
+                        chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
+                        if (count > 0) {
+                            bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(count) * 4u);
+                            bulk_copy_g2s(chunk0 + cs * kChunkBytes, p.entries + at, static_cast<std::uint32_t>(count) * 4u,
+                                          smem_addr(c_full + cs));
+                        } else {
+                            bar_arrive(smem_addr(c_full + cs)); // an empty window still hands over one (empty) chunk
+                        }
+                        at += count;
+                        ++qc;
+                    } while (at < hi);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template<int NC> constexpr std::size_t blocked_smem_bytes() {
+    return 2 * kABufBytes + w_stages(NC) * record_bytes(NC) + kChunkStages * kChunkBytes + kRows * 4 +
+           (6 + 2 * w_stages(NC) + 2 * kChunkStages) * sizeof(std::uint64_t) + (kChunkStages + 1) * 4 + 16;
+}
+
+template<int NC>
+cb200_status launch_one(const blocked_params &p, int sm_count, cudaStream_t stream) {
+    constexpr std::size_t smem = blocked_smem_bytes<NC>();
+    static_assert(smem <= 232448, "shared memory budget");
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+    const std::int64_t groups = p.group_end - p.group_begin;
+    const unsigned grid = static_cast<unsigned>(groups < sm_count ? groups : sm_count);
+    qcsr_fwd_blocked_kernel<NC><<<grid, kThreads, smem, stream>>>(p);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+} // namespace
+
+std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n) {
+    const std::int64_t windows = (cols + kWin - 1) / kWin;
+    return static_cast<std::uint64_t>(256 + windows * record_bytes(static_cast<int>(n)));
+}
+
+bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype) {
+    if (bits != 8 && bits != 4) return false;
+    if (n != 32 && n != 64 && n != 128) return false;
+    if (dense_dtype != CB200_DTYPE_BF16) return false;
+    if (rows <= 0 || cols <= 0 || cols > 0x7fffffff - kWin) return false;
+    const std::int64_t groups = (rows + kRows - 1) / kRows, windows = (cols + kWin - 1) / kWin;
+    return groups * windows < (static_cast<std::int64_t>(1) << 31);
+}
+
+void free_blocked_layout(blocked_layout *layout) {
+    if (layout == nullptr) return;
+    if (layout->entries != nullptr) cudaFree(layout->entries);
+    if (layout->seg_ptr != nullptr) cudaFree(layout->seg_ptr);
+    *layout = blocked_layout{};
+}
+
+// Builds the window-blocked copy of `x` on the current device; synchronises.
+cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out) {
+    *out = blocked_layout{};
+    if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed == nullptr)))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "the matrix handed to prepare has null arrays");
+    if (x.bits == 4 && x.packed_row_ptr == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "4-bit codes need packed_row_ptr");
+    const std::int64_t groups = (x.rows + kRows - 1) / kRows;
+    const int windows = static_cast<int>((x.cols + kWin - 1) / kWin);
+    const std::int64_t segments = groups * windows;
+    unsigned *counts = nullptr;
+    unsigned long long *cursor = nullptr;
+    cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&counts), static_cast<std::size_t>(segments) * sizeof(unsigned));
+    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&cursor), static_cast<std::size_t>(segments) * sizeof(unsigned long long));
+    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->seg_ptr), static_cast<std::size_t>(segments + 1) * sizeof(std::int64_t));
+    if (err == cudaSuccess) err = cudaMemset(counts, 0, static_cast<std::size_t>(segments) * sizeof(unsigned));
+    const unsigned grid = static_cast<unsigned>((x.rows + 255) / 256);
+    std::int64_t total = 0;
+    if (err == cudaSuccess) {
+        if (x.bits == 8)
+            blocked_pass_kernel<8, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr);
+        else
+            blocked_pass_kernel<4, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr);
+        count_launch();
+        segment_scan_kernel<<<1, 1024>>>(counts, segments, out->seg_ptr, cursor);
+        count_launch();
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) err = cudaMemcpy(&total, out->seg_ptr + segments, sizeof(total), cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess && total > 0) {
+        err = cudaMalloc(reinterpret_cast<void **>(&out->entries), static_cast<std::size_t>(total) * sizeof(std::uint32_t));
+        if (err == cudaSuccess) err = cudaMemset(out->entries, 0x80, static_cast<std::size_t>(total) * sizeof(std::uint32_t)); // padding = invalid
+        if (err == cudaSuccess) {
+            if (x.bits == 8)
+                blocked_pass_kernel<8, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries);
+            else
+                blocked_pass_kernel<4, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries);
+            count_launch();
+            err = cudaGetLastError();
+        }
+    }
+    if (err == cudaSuccess) err = cudaDeviceSynchronize();
+    if (counts != nullptr) cudaFree(counts);
+    if (cursor != nullptr) cudaFree(cursor);
+    if (err != cudaSuccess) {
+        free_blocked_layout(out);
+        return fail(CB200_STATUS_CUDA_ERROR, "building the window-blocked copy: %s", cudaGetErrorString(err));
+    }
+    out->groups = groups;
+    out->windows = windows;
+    out->total_entries = total;
+    out->bytes = static_cast<std::uint64_t>(total) * 4u + static_cast<std::uint64_t>(segments + 1) * 8u;
+    out->src_row_ptr = x.row_ptr;
+    out->src_col_idx = x.col_idx;
+    out->src_packed = x.packed;
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                         std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                         const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken) {
+    *taken = false;
+    if (layout.seg_ptr == nullptr || row_end <= row_begin) return CB200_STATUS_SUCCESS;
+    if (!qcsr_blocked_shape_ok(x.rows, x.cols, d.n, x.bits, d.dense_dtype)) return CB200_STATUS_SUCCESS;
+    if (row_begin % kRows != 0) return CB200_STATUS_SUCCESS; // a launch starts on a group boundary, else another kernel runs
+    if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return CB200_STATUS_SUCCESS;
+    if (workspace == nullptr || workspace_bytes < qcsr_blocked_workspace_bytes(x.cols, d.n)) return CB200_STATUS_SUCCESS;
+    if (reinterpret_cast<std::uintptr_t>(workspace) % 256u != 0u) return CB200_STATUS_SUCCESS;
+    if (x.row_ptr != layout.src_row_ptr || x.col_idx != layout.src_col_idx || x.packed != layout.src_packed)
+        return fail(CB200_STATUS_STALE_STRUCTURE, "the launch's matrix is not the one the window-blocked copy was built from");
+
+    int *status = static_cast<int *>(workspace);
+    unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
+    const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+    CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    pack_windows_kernel<<<static_cast<unsigned>(layout.windows), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), x.scales, x.offsets,
+        row_policy ? 0 : 1, records);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+
+    blocked_params p{};
+    p.entries = layout.entries; p.seg_ptr = layout.seg_ptr; p.row_offsets = row_policy ? x.offsets : nullptr;
+    p.records = records; p.y = d.out; p.y_ld = d.out_ld; p.row_end = row_end;
+    p.group_begin = row_begin / kRows; p.group_end = (row_end + kRows - 1) / kRows; p.windows = layout.windows;
+    p.alpha = d.alpha; p.beta = d.beta; p.status = status;
+    *taken = true;
+    switch (d.n) {
+    case 32: return launch_one<32>(p, sm_count, stream);
+    case 64: return launch_one<64>(p, sm_count, stream);
+    default: return launch_one<128>(p, sm_count, stream);
+    }
+}
+
+} // namespace cb200

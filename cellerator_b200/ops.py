@@ -205,7 +205,8 @@ class PreparedSpmm:
     """prepare once, run many times (cb200_spmm_prepare / cb200_spmm_run)."""
 
     def __init__(self, projection: int, m: int, k: int, n: int, nnz: int, bits: int, policy: int, dense_dtype,
-                 device, structure_epoch: int = 1, host_row_ptr: np.ndarray | None = None, deterministic=False):
+                 device, structure_epoch: int = 1, host_row_ptr: np.ndarray | None = None, deterministic=False,
+                 multiply: int = 0, device_matrix=None):
         self.device = torch.device(device)
         pr = capi.header(capi.SpmmProblem())
         pr.projection, pr.m, pr.k, pr.n, pr.nnz, pr.bits, pr.policy = projection, m, k, n, nnz, bits, policy
@@ -217,6 +218,11 @@ class PreparedSpmm:
             self._host_row_ptr = np.ascontiguousarray(host_row_ptr, dtype=np.int64)
             pr.host_row_ptr = self._host_row_ptr.ctypes.data
         pr.deterministic = int(deterministic)
+        pr.multiply = multiply  # 0 / DTYPE_F32: exact fp32 products; DTYPE_BF16: tensor-core products
+        self._matrix_desc = None
+        if device_matrix is not None:  # lets prepare build its persistent window-blocked copy
+            self._matrix_desc = device_matrix.desc()
+            pr.device_matrix = C.pointer(self._matrix_desc)
         self.problem = pr
         self.handle = C.c_void_p()
         capi.check(capi.lib().cb200_spmm_prepare(C.byref(pr), C.byref(self.handle)))
@@ -272,13 +278,16 @@ class PreparedSpmm:
             pass
 
 
-def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0):
-    """Y = alpha * deq(X) W + beta * Y (one-shot convenience: prepare + run)."""
+def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
+                 multiply: int = 0):
+    """Y = alpha * deq(X) W + beta * Y (one-shot convenience: prepare + run).
+
+    multiply=capi.DTYPE_BF16 with a bf16 W asks for tensor-core products (decoded values rounded to bf16)."""
     n = w.shape[1]
     if out is None:
         out = torch.empty(x.rows, n, dtype=torch.float32, device=x.device)
     op = PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, n, x.nnz, x.bits, x.policy, w.dtype, x.device,
-                      host_row_ptr=x.host_row_ptr)
+                      host_row_ptr=x.host_row_ptr, multiply=multiply)
     op.run(x, w, out, alpha=alpha, beta=beta)
     op.close()
     return out

@@ -215,7 +215,17 @@ typedef struct cb200_spmm_problem {
     /* Optional host copy of row_ptr (m+1) used to choose the row schedule; NULL = default. */
     const int64_t *host_row_ptr;
     int32_t deterministic; /* prepare_policy.deterministic, operation_core.hh:116-124 */
-    int32_t reserved;
+    /* numeric_policy.multiply of the request: 0 or CB200_DTYPE_F32 = exact fp32 products;
+     * CB200_DTYPE_BF16 = decoded values may be rounded to bf16 and multiplied on the tensor cores
+     * (CSR forward with bf16 W: schedule "tensor_windows"; Blocked-ELL with bf16 W always does). */
+    int32_t multiply;
+    /* Optional: the device-resident matrix itself (arrays on `device`, final contents).  With bf16
+     * products allowed, prepare then builds a persistent window-blocked copy of it (one 32-bit
+     * word per stored entry plus 8 bytes per 256-row x 128-gene segment; persistent_kernel_state,
+     * operation_core.hh:126-129) and the schedule becomes "tensor_blocked".  Prepare launches
+     * kernels on the device's default stream and synchronises.  Launches must then pass the same
+     * arrays: other pointers are refused as a stale structure; changed codes need a new prepare. */
+    const cb200_qcsr *device_matrix;
 } cb200_spmm_problem;
 
 typedef struct cb200_prepared cb200_prepared;
@@ -224,7 +234,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
 void cb200_prepared_destroy(cb200_prepared *prepared);
 /* workspace_requirement, launch_bindings.hh:67-71 */
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
-/* kernel choice made at prepare time, as text ("warp_per_row", "gene_tiled") */
+/* kernel choice made at prepare time, as text: "warp_per_row", "gene_tiled" (exact fp32 products);
+ * "tensor_windows", "tensor_blocked" (CSR, bf16 products on tcgen05); "tcgen05_block_rows" (Blocked-ELL) */
 const char *cb200_prepared_schedule(const cb200_prepared *prepared);
 
 /* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch. */

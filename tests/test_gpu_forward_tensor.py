@@ -1,0 +1,167 @@
+"""GPU parity of the tensor-core forward schedules (decoded values rounded to bf16, bf16 W, fp32
+accumulation in TMEM), through the C ABI, against the oracle: "tensor_windows" reads the CSR arrays
+with one thread per row, "tensor_blocked" streams the window-blocked copy that prepare builds when
+it is handed the device-resident matrix.
+
+Tolerance: each product carries the bf16 rounding of the decoded value (relative 2^-9), so the
+error of an output is at most 2^-9 * ||row||_1 * max|W| plus fp32 summation error; the test bound is
+the benchmark contract's 1e-2 relative, taken against ||row||_1 * max|W|."""
+import numpy as np
+import pytest
+import torch
+
+from cellerator_b200 import capi, ops, synth
+from conftest import random_csr
+from gpu_util import dense, host_pack, row_l1, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def assert_tensor_close(y, ref, l1, wmax):
+    err = np.abs(np.asarray(y, dtype=np.float64) - ref)
+    scale = l1[:, None] * wmax + 1e-30
+    assert np.all(err <= 1e-2 * scale), f"max err/scale {np.max(err / scale):.3e}"
+    # the rounding is unbiased: the typical error is far below the bound
+    assert np.median(err / scale) < 1e-3
+
+
+def prepared(x, n, w, device, blocked=False, **kw):
+    return ops.PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, n, x.nnz, x.bits, x.policy, w.dtype, device,
+                            host_row_ptr=x.host_row_ptr, multiply=capi.DTYPE_BF16,
+                            device_matrix=x if blocked else None, **kw)
+
+
+@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked"])
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("n", [32, 64, 128])
+@pytest.mark.parametrize("policy", [1, 2])
+def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits, n, policy):
+    """Forced on a small matrix: several row groups (ragged last one, empty rows), a ragged last
+    gene window, row starts at every alignment; row ranges, alpha/beta, determinism."""
+    monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)
+    rng = np.random.default_rng(77 * bits + n + policy)
+    rows, cols = 512 * 2 + 171, 1000
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=300, bits=bits, policy=policy))
+    x = to_dev(c, cuda_device)
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    op = prepared(x, n, w, cuda_device, blocked=schedule == "tensor_blocked")
+    assert op.schedule == schedule
+    y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0          # no bounded wait ran out
+    ref = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
+                              c["offsets"], w_host, cols)
+    l1, _ = row_l1(oracle, c)
+    wmax = float(np.abs(w_host).max())
+    assert_tensor_close(y.cpu().numpy(), ref, l1, wmax)
+    counts = np.diff(c["row_ptr"])
+    assert torch.all(y[torch.from_numpy(counts == 0).to(cuda_device)] == 0.0)  # empty rows: exact zeros
+    assert torch.equal(y, op.run(x, w, torch.empty_like(y)))                   # a row has one owner: repeatable
+    # row ranges: only the rows of the range are written, bit-identical to the full run
+    # (the blocked copy serves ranges that start on a 256-row boundary; others run an exact kernel)
+    lo = 256 if schedule == "tensor_blocked" else 100
+    out = torch.full((rows, n), -3.0, device=cuda_device)
+    op.run(x, w, out, row_begin=lo, row_end=900)
+    assert torch.equal(out[lo:900], y[lo:900]) and torch.all(out[:lo] == -3.0) and torch.all(out[900:] == -3.0)
+    if schedule == "tensor_blocked":
+        out.fill_(-3.0)
+        op.run(x, w, out, row_begin=100, row_end=900)
+        assert_tensor_close(out[100:900].cpu().numpy(), ref[100:900], l1[100:900], wmax)
+        assert torch.all(out[:100] == -3.0) and torch.all(out[900:] == -3.0)
+        # the copy belongs to the arrays prepare saw
+        other = to_dev(c, cuda_device)
+        with pytest.raises(capi.Cb200Error):
+            op.run(other, w, torch.empty_like(y))
+    # alpha / beta applied in fp32 in the epilogue
+    y0 = torch.from_numpy(rng.normal(size=(rows, n)).astype(np.float32)).to(cuda_device)
+    y1 = op.run(x, w, y0.clone(), alpha=2.0, beta=0.5)
+    assert torch.allclose(y1, 2.0 * y + 0.5 * y0, rtol=1e-5, atol=1e-6)
+    op.close()
+
+
+def test_tensor_schedule_is_opt_in(cuda_device, oracle):
+    """Without multiply = bf16 in the request the exact kernels run; with it, and a matrix dense
+    enough, prepare picks the tensor schedule and sizes the workspace for the re-laid W."""
+    rng = np.random.default_rng(3)
+    rows, cols, n = 2048, 640, 64
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=200, bits=8, empty_rows=False))
+    x = to_dev(c, cuda_device)
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    exact = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, 8, 1, w.dtype, cuda_device,
+                             host_row_ptr=x.host_row_ptr)
+    assert exact.schedule != "tensor_windows"
+    op = prepared(x, n, w, cuda_device)
+    assert op.schedule == "tensor_windows"
+    assert op.workspace_bytes >= 256 + cols * n * 2 + cols * 8          # W re-laid per gene window + tables
+    y_exact = exact.run(x, w, torch.empty(rows, n, device=cuda_device)).cpu().numpy()
+    y = op.run(x, w, torch.empty(rows, n, device=cuda_device)).cpu().numpy()
+    l1, _ = row_l1(oracle, c)
+    assert_tensor_close(y, y_exact.astype(np.float64), l1, float(np.abs(w_host).max()))
+    # bf16 products are refused where they make no sense
+    with pytest.raises(capi.Cb200Error):
+        ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, 8, 1, torch.float32, cuda_device,
+                         multiply=capi.DTYPE_BF16)
+    assert ops.backend_query(capi.PROJECTION_CSR, dense=capi.DTYPE_BF16, multiply=capi.DTYPE_BF16)["supported"]
+    assert not ops.backend_query(capi.PROJECTION_CSR, dense=capi.DTYPE_F32, multiply=capi.DTYPE_BF16)["supported"]
+    op.close()
+    exact.close()
+
+
+@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked"])
+@pytest.mark.parametrize("bits,n", [(8, 64), (4, 128)])
+def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule, bits, n):
+    """Genes as in the benchmark configuration, 1/8 of its cells, device-generated: agreement with
+    the exact schedule on every row, row-partition invariance, sampled rows against the oracle."""
+    cfg = dict(synth.CONFIGS["c2_forward" if bits == 8 else "c4_4bit"])
+    cfg["rows"] //= 8
+    x = synth.make_qcsr_device(**{**cfg, "bits": bits}, device=cuda_device, seed=0)
+    rng = np.random.default_rng(9)
+    w1, w_host = dense(rng, x.cols, n, torch.bfloat16, cuda_device)
+    if schedule == "tensor_windows":
+        monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)   # prepare's own choice needs a denser matrix
+    op = prepared(x, n, w1, cuda_device, blocked=schedule == "tensor_blocked")
+    monkeypatch.delenv("CB200_FWD_SCHEDULE", raising=False)
+    assert op.schedule == schedule
+    y1 = op.run(x, w1, torch.empty(x.rows, n, device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0
+    exact = ops.PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, n, x.nnz, bits, x.policy, w1.dtype, cuda_device,
+                             host_row_ptr=x.host_row_ptr)
+    y_exact = exact.run(x, w1, torch.empty(x.rows, n, device=cuda_device))
+    # ||row||_1 bound from the decoded values on the device
+    vals = x.dequantize()
+    wmax = float(np.abs(w_host).max())
+    csum = torch.zeros(x.nnz + 1, dtype=torch.float64, device=cuda_device)
+    csum[1:] = torch.cumsum(vals.abs().double(), 0)
+    del vals
+    l1 = (csum[x.row_ptr[1:]] - csum[x.row_ptr[:-1]]).float()
+    del csum
+    assert torch.all((y1 - y_exact).abs() <= 1e-2 * (l1[:, None] * wmax) + 1e-30)
+    for parts in (2, 8):
+        brp = ops.partition_rows(x.rows, parts)
+        if schedule == "tensor_blocked":
+            brp = (brp // 256) * 256                          # shards on group boundaries use the copy
+            brp[-1] = x.rows
+        out = torch.empty(x.rows, n, device=cuda_device)
+        for p in range(parts):
+            op.run(x, w1, out, row_begin=int(brp[p]), row_end=int(brp[p + 1]))
+        assert torch.equal(out, y1)
+    rp = x.host_row_ptr
+    for r0 in (0, x.rows // 2 - 3, x.rows - 40):
+        r1 = r0 + 40
+        lo, hi = int(rp[r0]), int(rp[r1])
+        sub = dict(rows=40, cols=x.cols, bits=bits, policy=1, row_ptr=rp[r0:r1 + 1] - lo,
+                   col_idx=x.col_idx[lo:hi].cpu().numpy(), scales=x.scales.cpu().numpy(), offsets=x.offsets.cpu().numpy())
+        if bits == 8:
+            sub["packed"] = x.packed[lo:hi].cpu().numpy()
+            sub["packed_row_ptr"] = sub["row_ptr"]
+        else:
+            prp = x.packed_row_ptr[r0:r1 + 1].cpu().numpy()
+            sub["packed"] = x.packed[int(prp[0]):int(prp[-1])].cpu().numpy()
+            sub["packed_row_ptr"] = prp - prp[0]
+        ref = oracle.qcsr_forward(bits, 1, sub["row_ptr"], sub["packed_row_ptr"], sub["col_idx"], sub["packed"],
+                                  sub["scales"], sub["offsets"], w_host, x.cols)
+        l1s, _ = row_l1(oracle, sub)
+        assert_tensor_close(y1[r0:r1].cpu().numpy(), ref, l1s, wmax)
+    op.close()
+    exact.close()
