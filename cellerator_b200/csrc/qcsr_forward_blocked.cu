@@ -19,17 +19,24 @@
 // a (group, window) segment is contiguous, so the copy engine streams it into shared memory and
 // every lane of the CTA decodes entries, four at a time, with no divergence.
 //
-// Structure of a CTA (320 threads, one CTA per SM, row groups dealt round-robin):
-//   warps 0-7  zero the A tile, wait for the segment's chunks (8 KB each, 3-stage ring), decode
-//              and scatter; later thread t owns TMEM lane t: row t of the group, and writes Y;
-//   warp 8     one thread issues the MMAs (2 row sub-blocks x 8 K-steps per window), commits the
-//              window to the "A tile free" and "W stage free" barriers, the last window of a group
-//              to "accumulators complete";
-//   warp 9     one thread feeds both rings with bulk async copies: W slices (re-laid per window
-//              into the K-major core-matrix operand layout by a small kernel before the main one,
-//              followed by the window's {scale, zero-point} table) and entry chunks.
+// Structure of a CTA (672 threads, one CTA per SM, row groups dealt round-robin):
+//   warps 0-15  zero the A tile (128-byte swizzled K-major layout), wait for the segment's chunks
+//               (8 KB each, 3-stage ring), decode and scatter; later thread t < 256 owns TMEM lane t:
+//               row t of the group, and writes that row of Y;
+//   warp 16     one thread issues the MMAs (2 row sub-blocks x 8 K-steps per window), commits the
+//               window to the "A tile free" and "W stage free" barriers, the last window of a group
+//               to "accumulators complete";
+//   warp 17     one thread feeds the W ring with bulk async copies: W slices, re-laid per window
+//               into the K-major core-matrix operand layout by a small kernel before the main one,
+//               each followed by the window's {scale, zero-point} table;
+//   warps 18-20 one thread each feeds the entry-chunk ring (chunks are dealt to them in turn).
 // Every barrier wait is bounded; on a time-out a status word is raised, waits stop blocking, and
 // the kernel runs to completion and frees its TMEM.  A non-zero status means Y is not valid.
+//
+// What bounds it.  Per window the shared memory moves ~64 KB of zeroes, ~20 KB of entries, tables and
+// scattered values, ~24 KB of copies coming in and 96 KB of MMA operand reads (the A tile once, the
+// W slice once per row sub-block): the kernel runs at the shared-memory bandwidth of the SM, not at
+// the tensor pipe's (about a quarter busy) nor at HBM's.
 #include "kernels.cuh"
 
 #include <cuda_bf16.h>
@@ -37,35 +44,47 @@
 namespace cb200 {
 namespace {
 
+// Geometry.  A (group, window) tile is 256 cells x 128 genes = 64 KB of bf16, double buffered.
+// (512 cells x 64 genes halves the W bytes per unit of work but leaves 13 instead of 26 groups per
+// SM on a 1M-cell shard; the coarser deal costs more than the W traffic saves: 8.0 ms against 7.5.)
 constexpr int kWin = 128;                    // genes per window
 constexpr int kWinShift = 7;
 constexpr int kRows = 256;                   // cell rows per group
 constexpr int kRowsShift = 8;
 constexpr int kSubBlocks = kRows / 128;      // one M = 128 MMA each
-constexpr int kProducerWarps = 8;
+constexpr int kProducerWarps = 16;           // zero + scatter; the first kEpilogueWarps of them also write Y
+constexpr int kEpilogueWarps = kRows / 32;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kThreads = kProducerThreads + 64; // + MMA warp + loader warp
+constexpr int kChunkLoaders = 3;                // warps whose elected lane issues entry-chunk copies
+constexpr int kThreads = kProducerThreads + 32 * (2 + kChunkLoaders); // + MMA warp + W loader warp + chunk loader warps
 constexpr int kABufBytes = kRows * kWin * 2;    // 64 KB
-constexpr int kSubBlockBytes = 128 * kWin * 2;  // 32 KB
-constexpr int kRowGroupBytes = kWin * 16;       // 8 rows x kWin genes of bf16
+constexpr int kSubBlockBytes = 128 * kWin * 2;  // 16 KB
+constexpr int kRowGroupBytes = kWin * 16;       // W slice: 8 columns x kWin genes of bf16
 constexpr int kChunkEntries = 2048;
 constexpr int kChunkBytes = kChunkEntries * 4;
-constexpr int kChunkStages = 3;
+constexpr int kChunkStages = 3;                // a multiple of kChunkLoaders: a loader always refills the same stages
+constexpr int kMaxWStages = 6;
 constexpr std::uint32_t kInvalidEntry = 0x80000000u; // padding of a segment
-static_assert(kProducerThreads == kRows, "thread t owns row t of the group in the epilogue");
+static_assert(kProducerWarps >= kEpilogueWarps && kABufBytes % (kProducerThreads * 16) == 0, "thread t < kRows owns row t in the epilogue");
+static_assert(kABufBytes <= 65536, "an entry holds the byte position in the tile, halved, in 15 bits");
 
 __host__ __device__ constexpr int record_bytes(int n) { return n * kWin * 2 + kWin * 8; }
 __host__ __device__ constexpr int fixed_smem_bytes() { return 2 * kABufBytes + kChunkStages * kChunkBytes + kRows * 4 + 512; }
 __host__ __device__ constexpr int w_stages(int n) {
-    return (232448 - fixed_smem_bytes()) / record_bytes(n) >= 4 ? 4 : (232448 - fixed_smem_bytes()) / record_bytes(n);
+    return (232448 - fixed_smem_bytes()) / record_bytes(n) >= kMaxWStages ? kMaxWStages
+                                                                          : (232448 - fixed_smem_bytes()) / record_bytes(n);
 }
 
-// byte position of (row within group, gene within window) in the A tile: two sub-blocks of 128
-// rows, each K-major without swizzle (core matrices of 8 rows x 16 bytes; the 16 core matrices of
-// a row group side by side, row groups 2,048 bytes apart)
+// Byte position of (row within group, gene within window) in the A tile.  The tile is made of
+// sub-blocks of 128 rows; a sub-block is K-major with the 128-byte swizzle: per 64 genes (a "half",
+// kHalfBytes; one half when the window is 64 genes wide) 8-row atoms of 1,024 bytes in which row r
+// holds its 64 genes in one 128-byte line whose 16-byte pieces are permuted by r mod 8.  The
+// permutation spreads the scattered 2-byte stores of one row, and of neighbouring rows, over all
+// shared-memory banks.
+constexpr int kHalfBytes = 128 * 64 * 2; // 16 KB: 128 rows x 64 genes
 __host__ __device__ constexpr std::uint32_t tile_offset(int rl, int gl) {
-    return static_cast<std::uint32_t>((rl >> 7) * kSubBlockBytes + ((rl & 127) >> 3) * kRowGroupBytes + (rl & 7) * 16 +
-                                      (gl >> 3) * 128 + (gl & 7) * 2);
+    return static_cast<std::uint32_t>((rl >> 7) * kSubBlockBytes + (gl >> 6) * kHalfBytes + ((rl & 127) >> 3) * 1024 +
+                                      (rl & 7) * 128 + ((((gl & 63) >> 3) ^ (rl & 7)) * 16) + (gl & 7) * 2);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -220,6 +239,19 @@ __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
     d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
     return d;
 }
+// K-major operand with the 128-byte swizzle (the A tile): 8-row atoms of 1,024 bytes follow each
+// other (SBO = 1,024 B), the leading offset is not used for this layout (encoded as 1), and a
+// K = 16 step inside a 64-gene half moves the start address by 32 bytes.  Atoms are 1,024-byte
+// aligned, so the base-offset field stays 0.
+__device__ __forceinline__ std::uint64_t smem_desc_sw128(std::uint32_t addr) {
+    std::uint64_t d = 0;
+    d |= static_cast<std::uint64_t>((addr & 0x3ffffu) >> 4);
+    d |= static_cast<std::uint64_t>(1) << 16;
+    d |= static_cast<std::uint64_t>(1024u >> 4) << 32;
+    d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
+    d |= static_cast<std::uint64_t>(2) << 61; // 128-byte swizzle
+    return d;
+}
 // kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, M = 128.
 __host__ __device__ constexpr std::uint32_t instr_desc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((static_cast<std::uint32_t>(n) >> 3) << 17) | ((128u >> 4) << 24);
@@ -300,6 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
     volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [kChunkStages] (entries << 1) | last chunk of its window
     std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + kChunkStages + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const std::uint32_t smem0 = smem_addr(smem);
@@ -320,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
             bar_init(smem_addr(c_empty + s), kProducerWarps);
         }
         bar_init(smem_addr(acc_full), 1);
-        bar_init(smem_addr(acc_empty), kProducerWarps);
+        bar_init(smem_addr(acc_empty), kEpilogueWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -349,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
             const std::int64_t row = group * kRows + tid;
             if (use_row_offset) {
                 asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the previous group's scatter is over
-                row_offset_s[tid] = row < p.row_end ? __ldg(p.row_offsets + row) : 0.0f;
+                if (tid < kRows) row_offset_s[tid] = row < p.row_end ? __ldg(p.row_offsets + row) : 0.0f;
                 asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
             }
             for (int w = 0; w < p.windows; ++w, ++q) {
@@ -372,7 +405,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                     const int count = *abort_flag != 0 ? 0 : (meta >> 1);
                     last = (meta & 1) != 0 || *abort_flag != 0;
                     const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunkBytes);
-                    for (int i = tid * 4; i < count; i += kProducerThreads * 4) {
+                    for (int i = tid * 4; i < count; i += kProducerThreads * 4) { // segments are padded to multiples of 4
                         const uint4 e4 = chunk[i >> 2];
                         const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
                         float2 t[4];
@@ -383,9 +416,11 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                             const std::uint32_t off = ((e[k] >> 15) & 0x7fffu) << 1;
                             float add = t[k].y;
                             if (use_row_offset) // row within the group, back from the byte position in the tile
-                                add = row_offset_s[((off >> 15) << 7) | (((off >> 11) & 15u) << 3) | ((off >> 4) & 7u)];
+                                add = row_offset_s[((off / kSubBlockBytes) << 7) | (((off >> 10) & 15u) << 3) | ((off >> 7) & 7u)];
                             const float value = fmaf(static_cast<float>(e[k] & 0xffu), t[k].x, add);
-                            if (static_cast<int>(e[k]) >= 0) *reinterpret_cast<__nv_bfloat16 *>(tile + off) = __float2bfloat16_rn(value);
+                            // padding words (top bit set) are stored to a scratch slot instead of branching
+                            unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + off : scratch_slot;
+                            *reinterpret_cast<__nv_bfloat16 *>(dst) = __float2bfloat16_rn(value);
                         }
                     }
                     __syncwarp();
@@ -397,7 +432,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                 if (lane == 0) bar_arrive(smem_addr(a_full + b));
             }
 
-            // ---- thread t writes row t of the group: TMEM lane = row within the sub-block
+            // ---- thread t < 256 writes row t of the group: TMEM lane = row within the sub-block
+            if (warp >= kEpilogueWarps) continue;
             bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(gi & 1), abort_flag);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -442,7 +478,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                         const std::uint64_t db = smem_desc(b_tile + kk * 256);
 #pragma unroll
                         for (int sb = 0; sb < kSubBlocks; ++sb)
-                            mma_bf16(tmem_base + sb * NC, smem_desc(a_tile + sb * kSubBlockBytes + kk * 256), db, IDESC,
+                            mma_bf16(tmem_base + sb * NC,
+                                     smem_desc_sw128(a_tile + sb * kSubBlockBytes + (kk >> 2) * kHalfBytes + (kk & 3) * 32), db, IDESC,
                                      w > 0 || kk > 0);
                     }
                     mma_commit(smem_addr(a_empty + b));
@@ -453,37 +490,53 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
             }
         }
     } else {
-        // ================= loader: W slices and entry chunks =================
-        long long q = 0, qc = 0;
-        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
-            const std::int64_t seg0 = (first_group + gi * gridDim.x) * p.windows;
-            for (int wbase = 0; wbase < p.windows; wbase += 31) {
-                // segment bounds of up to 31 windows in one coalesced read
-                const int span = min(31, p.windows - wbase);
-                const std::int64_t mine = lane <= span ? __ldg(p.seg_ptr + seg0 + wbase + lane) : 0;
-                for (int j = 0; j < span; ++j, ++q) {
-                    const std::int64_t lo = __shfl_sync(0xffffffffu, mine, j), hi = __shfl_sync(0xffffffffu, mine, j + 1);
-                    if (lane != 0) continue;
+        // ================= loaders =================
+        // Issuing a bulk copy costs its thread several hundred cycles (barrier wait, expect-tx, the
+        // copy itself), so the copies of a window are spread over threads: one warp's elected lane
+        // feeds the W ring, kChunkLoaders warps take the entry chunks in turn (chunk number modulo
+        // kChunkLoaders); each of them walks all segments and issues only its own chunks.
+        const int role = warp - kProducerWarps - 1; // 0: W slices, 1..kChunkLoaders: entry chunks
+        if (role == 0) {
+            if (lane == 0) {
+                const long long total = my_groups * p.windows;
+                for (long long q = 0; q < total; ++q) {
                     const int s = static_cast<int>(q % STAGES);
                     bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag);
                     bar_arrive_expect_tx(smem_addr(w_full + s), REC);
-                    bulk_copy_g2s(wstage0 + s * REC, p.records + static_cast<std::size_t>(wbase + j) * REC, REC, smem_addr(w_full + s));
-                    std::int64_t at = lo;
-                    do {
-                        const int count = static_cast<int>(min(static_cast<std::int64_t>(kChunkEntries), hi - at));
-                        const int cs = static_cast<int>(qc % kChunkStages);
-                        bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / kChunkStages) & 1) ^ 1), abort_flag);
-                        chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
-                        if (count > 0) {
-                            bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(count) * 4u);
-                            bulk_copy_g2s(chunk0 + cs * kChunkBytes, p.entries + at, static_cast<std::uint32_t>(count) * 4u,
-                                          smem_addr(c_full + cs));
-                        } else {
-                            bar_arrive(smem_addr(c_full + cs)); // an empty window still hands over one (empty) chunk
-                        }
-                        at += count;
-                        ++qc;
-                    } while (at < hi);
+                    bulk_copy_g2s(wstage0 + s * REC, p.records + static_cast<std::size_t>(q % p.windows) * REC, REC,
+                                  smem_addr(w_full + s));
+                }
+            }
+        } else {
+            const int mine_mod = role - 1;
+            long long qc = 0;
+            for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+                const std::int64_t seg0 = (first_group + gi * gridDim.x) * p.windows;
+                for (int wbase = 0; wbase < p.windows; wbase += 31) {
+                    // segment bounds of up to 31 windows in one coalesced read
+                    const int span = min(31, p.windows - wbase);
+                    const std::int64_t bound = lane <= span ? __ldg(p.seg_ptr + seg0 + wbase + lane) : 0;
+                    for (int j = 0; j < span; ++j) {
+                        const std::int64_t lo = __shfl_sync(0xffffffffu, bound, j), hi = __shfl_sync(0xffffffffu, bound, j + 1);
+                        std::int64_t at = lo;
+                        do {
+                            const int count = static_cast<int>(min(static_cast<std::int64_t>(kChunkEntries), hi - at));
+                            if (lane == 0 && qc % kChunkLoaders == mine_mod) {
+                                const int cs = static_cast<int>(qc % kChunkStages);
+                                bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / kChunkStages) & 1) ^ 1), abort_flag);
+                                chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
+                                if (count > 0) {
+                                    bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(count) * 4u);
+                                    bulk_copy_g2s(chunk0 + cs * kChunkBytes, p.entries + at, static_cast<std::uint32_t>(count) * 4u,
+                                                  smem_addr(c_full + cs));
+                                } else {
+                                    bar_arrive(smem_addr(c_full + cs)); // an empty window still hands over one (empty) chunk
+                                }
+                            }
+                            at += count;
+                            ++qc;
+                        } while (at < hi);
+                    }
                 }
             }
         }

@@ -2,29 +2,37 @@
 // bf16 products (decoded values rounded to bf16, W in bf16, fp32 accumulation):
 //     Y[cells, N] = alpha * deq(X)[cells, genes] * W[genes, N] + beta * Y,   N in {32, 64, 128}.
 //
-// Why a second forward kernel.  With N = 64 every stored entry costs 64 fp32 FMAs and a 128-byte
+// Schedule "tensor_windows": the tensor-core kernel that reads the CSR arrays as they are.  It is
+// the fallback of the tensor path when prepare was not handed the matrix (with it, the kernel in
+// qcsr_forward_blocked.cu streams a window-blocked copy and is ~3x faster); it beats the exact
+// CUDA-core kernels only on dense matrices (>= 10 % stored entries), where prepare selects it.
+//
+// Why tensor cores at all.  With N = 64 every stored entry costs 64 fp32 FMAs and a 128-byte
 // row of W.  On the CUDA cores that is bound by the FMA pipe and by shared-memory reads (one
 // 128-byte wavefront per stored entry) at a small fraction of what HBM could deliver.  The tensor
-// pipe has the arithmetic to spare even when the matrix is treated as dense: a 512-cell x 64-gene
+// pipe has the arithmetic to spare even when the matrix is treated as dense: a 256-cell x 128-gene
 // window holds ~1,750 stored entries of the 1M x 33,538 matrix and costs sixteen 128 x N x 16 MMAs.
 // So the kernel densifies: the stored entries of a window are decoded and scattered, as bf16, into
 // a zeroed operand tile in shared memory, and the tile is multiplied against the window's slice
 // of W.  Entries are read once, in row order, straight from HBM.
 //
-// Structure of a CTA (576 threads, one CTA per SM, persistent over groups of 512 cell rows):
-//   warps 0-15  one thread per cell row.  A thread streams its row's (gene, code) pairs through
-//               registers (aligned 32-byte loads of gene indices, one octet ahead), and per window
-//               zeroes its own 128-byte row of the A tile, then writes the entries whose gene falls
-//               into the window (scale and zero-point of the window's genes come from a table that
-//               travels with the W slice).  Because a thread owns its row of the tile, no two
-//               threads write the same bytes and nothing is atomic.  A tiles are double buffered.
-//               The same thread later owns TMEM lane = its row and writes that row of Y.
-//   warp 16     one thread issues, per window, 4 K-steps x 4 row sub-blocks of tcgen05.mma
-//               (M = 128, N, K = 16; fp32 accumulators in TMEM, 4 x N columns), commits the window
+// Structure of a CTA (320 threads, one CTA per SM, persistent over groups of 256 cell rows):
+//   warps 0-7   one thread per cell row.  A thread brings its row's (gene, code) pairs in as aligned
+//               16-byte quartets with cp.async into its own slots of a small ring in shared memory
+//               (three quartets ahead, L2 prefetch 128 entries ahead), and per window zeroes its own
+//               256-byte row of the A tile, then writes the entries whose gene falls into the window
+//               (scale and zero-point of the window's genes come from a table that travels with the
+//               W slice).  Because a thread owns its row of the tile, no two threads write the same
+//               bytes and nothing is atomic.  A tiles are double buffered.  The same thread later
+//               owns TMEM lane = its row and writes that row of Y.  Rows diverge (a warp runs as
+//               long as its busiest row in the window) and every quartet is its own L1 request:
+//               that, not HBM, bounds this kernel.
+//   warp 8      one thread issues, per window, 8 K-steps x 2 row sub-blocks of tcgen05.mma
+//               (M = 128, N, K = 16; fp32 accumulators in TMEM, 2 x N columns), commits the window
 //               to the "A buffer free" and "W stage free" barriers and, after the last window of a
 //               row group, to the "accumulators complete" barrier.
-//   warp 17     one thread keeps a 4-stage ring of W slices filled with bulk async copies.  A small
-//               kernel beforehand writes W, per window of 64 genes, transposed into the K-major
+//   warp 9      one thread keeps a ring of W slices filled with bulk async copies.  A small kernel
+//               beforehand writes W, per window of 128 genes, transposed into the K-major
 //               core-matrix operand layout (8 x 16-byte core matrices, no swizzle) followed by the
 //               window's {scale, zero-point} table, so a window is one contiguous record.
 // Every barrier wait is bounded; on a time-out a status word is raised, waits stop blocking, and
