@@ -36,7 +36,11 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (bytes per stored entry, measured on a smaller case and
 # scaled by the entries one launch processes).  None until a capture exists.
-NCU_DRAM_BYTES_PER_NNZ = {"c2_forward": None, "c3_transpose": None, "c4_4bit": None, "c5_bell": None}
+NCU_DRAM_BYTES_PER_NNZ = {
+    ("c2_forward", "tensor_blocked"): 4.21,   # profiles/qcsr_fwd_blocked__c2_303104_rows.md
+    ("c2_forward", "gene_tiled"): 5.32,       # profiles/qcsr_fwd_tiled__c2_75776_rows.md
+    ("c2_forward", "warp_per_row"): 5.21,     # profiles/qcsr_fwd_warp_row__c2_60k_rows.md
+}
 
 
 def measured_peak():
@@ -368,7 +372,7 @@ def run_ours(args):
                               "tensor_peak_source": tkind}
     else:
         achieved = wl["bytes"] / (kernel_ms * 1e-3) / 1e9
-        per_nnz = NCU_DRAM_BYTES_PER_NNZ.get(args.workload)
+        per_nnz = NCU_DRAM_BYTES_PER_NNZ.get((args.workload, op.schedule)) if not args.rows else None
         result["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                               "frac": achieved / peak, "traffic": None if per_nnz is None else per_nnz * wl["units"],
                               "peak_source": peak_kind, "kernel_ms": kernel_ms,

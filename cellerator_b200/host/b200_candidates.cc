@@ -184,6 +184,9 @@ core::operation_status prepare_any(int projection_kind, const core::operation_ca
     // the optional length-sorted row order is persistent preprocessing: only when the policy allows it
     p.host_row_ptr = policy.allow_persistent_preprocessing ? shape->host_row_ptr : nullptr;
     p.deterministic = policy.deterministic ? 1 : 0;
+    // bf16 products (tensor-core schedules) only when the request's numeric policy says so
+    p.multiply = dtype_of(numeric.multiply);
+    p.device_matrix = policy.allow_persistent_preprocessing ? shape->device_matrix : nullptr;
 
     auto *state = new (std::nothrow) prepared_state;
     if (state == nullptr) return status(core::operation_status_code::preparation_failed, "out of host memory");

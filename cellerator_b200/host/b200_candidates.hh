@@ -52,6 +52,9 @@ struct projection_catalog_entry {
     std::int32_t dense_dtype = CB200_DTYPE_BF16;
     std::int32_t device = 0;
     const std::int64_t *host_row_ptr = nullptr; // optional, for the row schedule
+    // optional: the device-resident matrix (final contents).  With numeric_policy.multiply == bf16 and
+    // prepare_policy.allow_persistent_preprocessing, prepare builds the window-blocked copy from it
+    const cb200_qcsr *device_matrix = nullptr;
     ex::axis_identity cells{}, genes{}, latent{};
 };
 
