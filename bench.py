@@ -153,8 +153,11 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         n = 64
         dense = torch.randn(rows, n, generator=g).to(device)
         out = torch.empty(cfg["cols"], n, dtype=torch.float32, device=device)
+        # --multiply bf16 (default): tensor-core schedule over the window-blocked copy (decoded values and
+        # G rounded to bf16, fp32 accumulation); --multiply f32: exact products, L2 vector reductions
         op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype,
-                              device)
+                              device, multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
+                              device_matrix=x if multiply == "bf16" else None)
         kind, dbytes = "transpose", 4
     else:
         n = cfg["n"]

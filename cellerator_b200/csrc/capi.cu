@@ -226,7 +226,9 @@ cb200_status cb200_backend_query(int32_t projection, const cb200_numeric_policy 
         break;
     case CB200_PROJECTION_TRANSPOSE:
         out->name = "cb200.qcsr.transpose.sm100a";
-        out->supported = common && numeric->dense_storage == CB200_DTYPE_F32 && numeric->multiply == CB200_DTYPE_F32;
+        /* G is fp32 storage either way; bf16 products round both factors (tensor-core schedule) */
+        out->supported = common && numeric->dense_storage == CB200_DTYPE_F32 &&
+                         (numeric->multiply == CB200_DTYPE_F32 || numeric->multiply == CB200_DTYPE_BF16);
         out->flags = CB200_CAP_GRAPH_CAPTURE; /* floating-point reductions: order not fixed */
         break;
     case CB200_PROJECTION_BLOCKED_ELL:
@@ -256,9 +258,9 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         return fail(CB200_STATUS_UNSUPPORTED, "unknown decode policy %d", problem->policy);
     if (problem->multiply != 0 && problem->multiply != CB200_DTYPE_F32 && problem->multiply != CB200_DTYPE_BF16)
         return fail(CB200_STATUS_UNSUPPORTED, "multiply must be fp32 or bf16, got %d", problem->multiply);
-    if (problem->multiply == CB200_DTYPE_BF16 &&
-        (problem->projection == CB200_PROJECTION_TRANSPOSE || problem->dense_dtype != CB200_DTYPE_BF16))
-        return fail(CB200_STATUS_UNSUPPORTED, "bf16 products need a forward projection with a bf16 dense operand");
+    if (problem->multiply == CB200_DTYPE_BF16 && problem->projection != CB200_PROJECTION_TRANSPOSE &&
+        problem->dense_dtype != CB200_DTYPE_BF16)
+        return fail(CB200_STATUS_UNSUPPORTED, "bf16 products on a forward projection need a bf16 dense operand");
     if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         if (problem->dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes fp32 G");
         if (problem->deterministic) return fail(CB200_STATUS_UNSUPPORTED, "transpose is not deterministic");
@@ -298,8 +300,38 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         }
         p->max_row_nnz = static_cast<double>(longest);
     }
-    if (problem->projection == CB200_PROJECTION_TRANSPOSE)
+    if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         p->workspace_bytes = qcsr_transpose_workspace_bytes(problem->k, problem->n, p->sm_count);
+        p->schedule_name = "vector_reductions";
+        // bf16 products allowed (G is rounded to bf16 as well) and the matrix at hand: the tensor-core
+        // kernel over the window-blocked copy; its cost follows the dense area, so it needs density
+        const char *force = std::getenv("CB200_TRANSPOSE_SCHEDULE");
+        bool blocked = problem->multiply == CB200_DTYPE_BF16 && problem->device_matrix != nullptr &&
+                       qcsr_transpose_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits);
+        if (force == nullptr)
+            blocked = blocked && problem->m >= 16 * 256 && p->mean_row_nnz >= 0.004 * static_cast<double>(problem->k);
+        else
+            blocked = blocked && std::strcmp(force, "tensor_blocked") == 0;
+        if (blocked) {
+            const cb200_qcsr &dm = *problem->device_matrix;
+            if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
+                dm.bits != problem->bits) {
+                delete p;
+                return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
+            }
+            device_scope scope(problem->device);
+            cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
+                                                          : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), &p->blocked);
+            if (st != CB200_STATUS_SUCCESS) {
+                delete p;
+                return st;
+            }
+            p->schedule_name = "tensor_blocked";
+            p->workspace_bytes = qcsr_transpose_blocked_workspace_bytes(problem->m, problem->n);
+            p->persistent_bytes += p->blocked.bytes;
+        }
+    }
     if (problem->projection == CB200_PROJECTION_BLOCKED_ELL && problem->dense_dtype == CB200_DTYPE_BF16 &&
         (problem->n == 128 || problem->n == 256)) {
         // the tensor-core kernel multiplies against W^T: room for that bf16 copy plus a status block
@@ -473,8 +505,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed_values == nullptr)))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "CSR matrix has null arrays");
     if (pr.projection == CB200_PROJECTION_TRANSPOSE)
-        return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, launch->workspace, launch->workspace_bytes,
-                                     prepared->sm_count, stream);
+        return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, &prepared->blocked, launch->workspace,
+                                     launch->workspace_bytes, prepared->sm_count, stream);
     return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, &prepared->blocked,
                                launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);
 }

@@ -1,0 +1,517 @@
+// Gene-side transpose on the tensor cores from the window-blocked copy of the matrix (schedule
+// "tensor_blocked" of the transpose projection), for callers whose numeric policy allows bf16
+// products and who hand the device-resident matrix to prepare:
+//     G'[genes, N] = alpha * deq(X)^T[genes, cells] * G[cells, N] + beta * G',   N in {32, 64}.
+//
+// Reference counterpart: csr_spmm_bwd_rhs_kernel_ (one scalar atomicAdd per stored entry and output
+// column, src/compute/sparse/ops/kernels/base_sparse/csr_spmm_bwd_rhs_kernel_.cuh:1-22).  The exact
+// kernel of this library (qcsr_transpose.cu) does the same with 128-bit vector reductions and is
+// bound by the L2 atomic units: 256 bytes of reductions per stored entry.
+//
+// Formulation.  For a group of 256 cells and a window of 128 genes the product is a dense
+// contraction over the cells:  D_w[128 genes, N] += X_gw^T[128 genes, 256 cells] * G_g[256 cells, N].
+// The window-blocked copy (see qcsr_forward_blocked.cu) delivers the entries of (group, window)
+// as one contiguous segment; they are decoded to bf16 and scattered into a zeroed operand tile in
+// shared memory, laid out gene-major this time (M = gene, K = cell; K-major with the 128-byte
+// swizzle), and sixteen 128 x N x 16 tcgen05 MMAs multiply it with the group's rows of G.  G is
+// converted to bf16 once per launch into one 256 x N record per group, already in the K-major
+// core-matrix operand layout (rows outside the launch's row range are written as zero, which is how a
+// partial row range is honoured).  A CTA keeps the fp32 accumulators of eight windows (1,024 genes)
+// in TMEM (8 x N columns x 128 lanes) while it walks a run of groups, so the group's G record is
+// fetched once per eight windows; at the end of the run the accumulators are added into G' with
+// vector reductions (the (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so
+// several CTAs contribute to the same genes; G' is first scaled by beta by a small kernel).
+//
+// Structure of a CTA (672 threads, one CTA per SM): warps 0-15 zero, decode and scatter, and read
+// the accumulators back at the end of a run; warp 16 issues the MMAs; warp 17 feeds the G ring (2
+// stages of 32 KB); warps 18-20 feed the entry-chunk ring.  Every barrier wait is bounded; on a
+// time-out a status word is raised, waits stop blocking, and the kernel runs to completion and frees
+// its TMEM.  A non-zero status means G' is not valid.
+#include "kernels.cuh"
+
+#include <algorithm>
+#include <cuda_bf16.h>
+
+namespace cb200 {
+namespace {
+
+constexpr int kWin = 128;                     // genes per window (as in the blocked copy)
+constexpr int kRows = 256;                    // cells per group (as in the blocked copy)
+constexpr int kSetWindows = 8;                // windows whose accumulators a CTA holds in TMEM
+constexpr int kProducerWarps = 16;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kChunkLoaders = 3;
+constexpr int kThreads = kProducerThreads + 32 * (2 + kChunkLoaders);
+constexpr int kTileBytes = kWin * kRows * 2;  // 64 KB: [cell quarter][gene][64 cells]
+constexpr int kQuarterBytes = kWin * 128;     // 16 KB: 128 genes x 64 cells
+constexpr int kGStages = 2;
+constexpr int kChunkEntries = 2048;
+constexpr int kChunkBytes = kChunkEntries * 4;
+constexpr int kChunkStages = 3;
+
+__host__ __device__ constexpr int g_record_bytes(int n) { return kRows * n * 2; }
+
+struct tb_params {
+    const std::uint32_t *entries;
+    const std::int64_t *seg_ptr;
+    const float *scales;
+    const float *gene_offsets; // per gene, per-gene-affine policy
+    const float *row_offsets;  // per cell, row-offset policy
+    const unsigned char *records; // G as bf16, one record per group
+    float *out;
+    std::int64_t out_ld;
+    std::int64_t cols;
+    std::int64_t group_begin, group_count;
+    int windows;
+    float alpha;
+    int *status;
+};
+
+__device__ __forceinline__ std::int64_t dmin(std::int64_t a, std::int64_t b) { return a < b ? a : b; }
+__device__ __forceinline__ std::uint32_t smem_addr(const void *p) { return static_cast<std::uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bar_init(std::uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(std::uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bar_arrive_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(std::uint32_t bar, std::uint32_t parity) {
+    std::uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0u;
+}
+// Bounded wait.  Once any wait of the CTA has timed out (`*abort_flag` set) waits return at once.
+__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag) {
+    int spins = 0;
+    while (!bar_try_wait(bar, parity)) {
+        if (*abort_flag != 0) return;
+        if (++spins > (1 << 22)) {
+            *abort_flag = 1;
+            return;
+        }
+    }
+}
+// One contiguous global -> shared copy by the copy engine (this GPU's own memory, no multicast).
+__device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes, std::uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major operand, no swizzle (the G record): core matrices of 8 columns x 16 bytes (8 cells); the
+// 32 core matrices of 8 output columns sit side by side (LBO = 128 B), groups of 8 columns 4 KB apart.
+__device__ __forceinline__ std::uint64_t smem_desc_g(std::uint32_t addr) {
+    std::uint64_t d = 0;
+    d |= static_cast<std::uint64_t>((addr & 0x3ffffu) >> 4);
+    d |= static_cast<std::uint64_t>(128u >> 4) << 16;
+    d |= static_cast<std::uint64_t>(static_cast<unsigned>(kRows * 16) >> 4) << 32;
+    d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
+    return d;
+}
+// K-major operand with the 128-byte swizzle (the tile): 8-gene atoms of 1,024 bytes follow each other.
+__device__ __forceinline__ std::uint64_t smem_desc_sw128(std::uint32_t addr) {
+    std::uint64_t d = 0;
+    d |= static_cast<std::uint64_t>((addr & 0x3ffffu) >> 4);
+    d |= static_cast<std::uint64_t>(1) << 16;
+    d |= static_cast<std::uint64_t>(1024u >> 4) << 32;
+    d |= static_cast<std::uint64_t>(1) << 46;
+    d |= static_cast<std::uint64_t>(2) << 61; // 128-byte swizzle
+    return d;
+}
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, M = 128.
+__host__ __device__ constexpr std::uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((static_cast<std::uint32_t>(n) >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b, std::uint32_t idesc,
+                                         bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(std::uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
+    std::uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+          "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// out = beta * out (beta == 0 writes zeros without reading).
+__global__ void __launch_bounds__(256) scale_output_kernel(float *out, std::int64_t rows, int n, std::int64_t ld, float beta) {
+    const std::int64_t total = rows * n;
+    for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+        float *p = out + (i / n) * ld + (i % n);
+        *p = beta == 0.0f ? 0.0f : beta * *p;
+    }
+}
+
+// G [cells][n] fp32 (leading dimension ld) -> one bf16 record per group of 256 cells: the n x 256
+// slice of G^T in the no-swizzle K-major operand layout (byte offset of (column c, cell r) =
+// (c/8)*4096 + (r/8)*128 + (c%8)*16 + (r%8)*2).  Cells outside [row_begin, row_end) are zero.
+__global__ void __launch_bounds__(256) pack_g_kernel(const float *g, std::int64_t ld, int n, std::int64_t row_begin,
+                                                     std::int64_t row_end, std::int64_t group_begin, unsigned char *records) {
+    const std::int64_t group = group_begin + blockIdx.x;
+    __nv_bfloat16 *rec = reinterpret_cast<__nv_bfloat16 *>(records + static_cast<std::size_t>(blockIdx.x) * g_record_bytes(n));
+    for (int i = threadIdx.x; i < kRows * n; i += blockDim.x) {
+        const int r = i / n, c = i % n; // consecutive threads read consecutive columns of one cell
+        const std::int64_t row = group * kRows + r;
+        const float v = (row >= row_begin && row < row_end) ? g[row * ld + c] : 0.0f;
+        rec[((c >> 3) * (kRows * 16) + (r >> 3) * 128 + (c & 7) * 16 + (r & 7) * 2) >> 1] = __float2bfloat16_rn(v);
+    }
+}
+
+template<int NC>
+__global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(const tb_params p) {
+    constexpr int GREC = g_record_bytes(NC);
+    constexpr int kTmemCols = kSetWindows * NC; // 512 (N = 64) or 256 (N = 32)
+    constexpr std::uint32_t IDESC = instr_desc(NC);
+    extern __shared__ __align__(1024) unsigned char smem[];
+    // [2][tile] | [kGStages][G record] | [kChunkStages][entry chunk] | tables | row offsets | barriers | ...
+    unsigned char *chunk_base = smem + 2 * kTileBytes + kGStages * GREC;
+    float2 *table = reinterpret_cast<float2 *>(chunk_base + kChunkStages * kChunkBytes); // [kSetWindows][kWin] {scale, offset}
+    float *row_offset_s = reinterpret_cast<float *>(table + kSetWindows * kWin);         // [kRows]
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(row_offset_s + kRows);
+    std::uint64_t *a_full = bars;                      // [2]            scatter warps -> MMA (one arrival per warp)
+    std::uint64_t *a_empty = bars + 2;                 // [2]            MMA commit -> scatter warps
+    std::uint64_t *g_full = bars + 4;                  // [kGStages]     copy engine -> MMA
+    std::uint64_t *g_empty = g_full + kGStages;        // [kGStages]     MMA commit -> loader
+    std::uint64_t *c_full = g_empty + kGStages;        // [kChunkStages] copy engine -> scatter warps
+    std::uint64_t *c_empty = c_full + kChunkStages;    // [kChunkStages] scatter warps -> loaders
+    std::uint64_t *acc_full = c_empty + kChunkStages;  // MMA commit -> scatter warps
+    std::uint64_t *acc_empty = acc_full + 1;           // scatter warps -> MMA
+    volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [kChunkStages]
+    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + kChunkStages + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const std::uint32_t smem0 = smem_addr(smem);
+    const std::uint32_t grec0 = smem0 + 2 * kTileBytes;
+    const std::uint32_t chunk0 = grec0 + kGStages * GREC;
+
+    if (tid == 0) {
+        for (int b = 0; b < 2; ++b) {
+            bar_init(smem_addr(a_full + b), kProducerWarps);
+            bar_init(smem_addr(a_empty + b), 1);
+        }
+        for (int s = 0; s < kGStages; ++s) {
+            bar_init(smem_addr(g_full + s), 1);
+            bar_init(smem_addr(g_empty + s), 1);
+        }
+        for (int s = 0; s < kChunkStages; ++s) {
+            bar_init(smem_addr(c_full + s), 1);
+            bar_init(smem_addr(c_empty + s), kProducerWarps);
+        }
+        bar_init(smem_addr(acc_full), 1);
+        bar_init(smem_addr(acc_empty), kProducerWarps);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const std::uint32_t tmem_base = *tmem_slot;
+
+    // Work: units (window set, group), numbered set * group_count + group; this CTA owns the units
+    // [u0, u1).  A run = the consecutive units of one window set; it ends with the accumulators being
+    // added into G'.  Every role walks the same runs.
+    const std::int64_t sets = (p.windows + kSetWindows - 1) / kSetWindows;
+    const std::int64_t total_units = sets * p.group_count;
+    const std::int64_t u0 = total_units * blockIdx.x / gridDim.x, u1 = total_units * (blockIdx.x + 1) / gridDim.x;
+
+    if (warp < kProducerWarps) {
+        // ================= zero, scatter, read back =================
+        const bool use_row_offset = p.row_offsets != nullptr;
+        long long q = 0, qc = 0; // tiles and chunks done by this CTA
+        int run = 0;
+        for (std::int64_t u = u0; u < u1; ++run) {
+            const std::int64_t set = u / p.group_count, gi0 = u % p.group_count;
+            const std::int64_t count = dmin(p.group_count - gi0, u1 - u);
+            const int nwin = static_cast<int>(dmin(kSetWindows, p.windows - set * kSetWindows));
+            // scale / zero-point of the set's genes; nobody still reads the previous run's table
+            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+            for (int i = tid; i < kSetWindows * kWin; i += kProducerThreads) {
+                const std::int64_t gene = set * kSetWindows * kWin + i;
+                float2 so = make_float2(0.0f, 0.0f);
+                if (gene < p.cols) {
+                    so.x = p.scales != nullptr ? __ldg(p.scales + gene) : 1.0f;
+                    so.y = p.gene_offsets != nullptr ? __ldg(p.gene_offsets + gene) : 0.0f;
+                }
+                table[i] = so;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+            for (std::int64_t gi = gi0; gi < gi0 + count; ++gi) {
+                const std::int64_t group = p.group_begin + gi;
+                if (use_row_offset) {
+                    asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the previous group's scatter is over
+                    if (tid < kRows) row_offset_s[tid] = __ldg(p.row_offsets + group * kRows + tid); // padded by the launcher's check
+                    asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+                }
+                for (int wl = 0; wl < nwin; ++wl, ++q) {
+                    const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
+                    bar_wait(smem_addr(a_empty + b), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
+                    unsigned char *tile = smem + b * kTileBytes;
+#pragma unroll
+                    for (int k = 0; k < kTileBytes / (kProducerThreads * 16); ++k)
+                        *reinterpret_cast<uint4 *>(tile + k * (kProducerThreads * 16) + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the whole tile is zero before anyone scatters
+                    const float2 *wtable = table + wl * kWin;
+                    bool last = false;
+                    int guard = 0;
+                    while (!last && ++guard < (1 << 20)) {
+                        const int cs = static_cast<int>(qc % kChunkStages);
+                        bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kChunkStages) & 1), abort_flag);
+                        const int meta = chunk_meta[cs];
+                        const int n_entries = *abort_flag != 0 ? 0 : (meta >> 1);
+                        last = (meta & 1) != 0 || *abort_flag != 0;
+                        const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunkBytes);
+                        for (int i = tid * 4; i < n_entries; i += kProducerThreads * 4) { // segments are padded to multiples of 4
+                            const uint4 e4 = chunk[i >> 2];
+                            const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+                            float2 t[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) t[k] = wtable[(e[k] >> 8) & (kWin - 1)];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                // the copy stores the byte position in the forward (cell-major) tile; take the cell back
+                                // out of it and place the value gene-major: [cell quarter][gene][64 cells], 16-byte pieces
+                                // of a gene's line permuted by gene mod 8
+                                const std::uint32_t gl = (e[k] >> 8) & (kWin - 1);
+                                const std::uint32_t fwd = ((e[k] >> 15) & 0x7fffu) << 1;
+                                const std::uint32_t rl = ((fwd >> 15) << 7) | (((fwd >> 10) & 15u) << 3) | ((fwd >> 7) & 7u);
+                                const std::uint32_t off = (rl >> 6) * kQuarterBytes + (gl >> 3) * 1024u + (gl & 7u) * 128u +
+                                                          ((((rl & 63u) >> 3) ^ (gl & 7u)) << 4) + ((rl & 7u) << 1);
+                                const float add = use_row_offset ? row_offset_s[rl] : t[k].y;
+                                const float value = fmaf(static_cast<float>(e[k] & 0xffu), t[k].x, add);
+                                // padding words (top bit set) are stored to a scratch slot instead of branching
+                                unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + off : scratch_slot;
+                                *reinterpret_cast<__nv_bfloat16 *>(dst) = __float2bfloat16_rn(value);
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
+                        ++qc;
+                    }
+                    fence_async_proxy(); // ordinary stores, read by the MMA through the async proxy
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(smem_addr(a_full + b));
+                }
+            }
+            // ---- end of the run: add the accumulators into G'.  TMEM lane = gene within the window;
+            //      a warp reads the lane quarter its number allows, for two of the eight windows.
+            bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(run & 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quarter = warp & 3;
+            for (int wl = warp >> 2; wl < kSetWindows; wl += kProducerWarps / 4) {
+                if (wl >= nwin) break; // warp-uniform
+                const std::int64_t gene = (set * kSetWindows + wl) * kWin + quarter * 32 + lane;
+#pragma unroll
+                for (int h = 0; h < NC / 32; ++h) {
+                    float v[32];
+                    tmem_ld32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + wl * NC + h * 32, v);
+                    if (gene < p.cols && *abort_flag == 0) {
+                        float *out = p.out + gene * p.out_ld + h * 32;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            atomicAdd(reinterpret_cast<float4 *>(out + c),
+                                      make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(smem_addr(acc_empty));
+            u += count;
+        }
+    } else if (warp == kProducerWarps) {
+        // ================= MMA issuer =================
+        long long q = 0, qg = 0;
+        int run = 0;
+        for (std::int64_t u = u0; u < u1; ++run) {
+            const std::int64_t set = u / p.group_count, gi0 = u % p.group_count;
+            const std::int64_t count = dmin(p.group_count - gi0, u1 - u);
+            const int nwin = static_cast<int>(dmin(kSetWindows, p.windows - set * kSetWindows));
+            bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((run & 1) ^ 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (std::int64_t gi = 0; gi < count; ++gi, ++qg) {
+                const int gs = static_cast<int>(qg % kGStages);
+                bar_wait(smem_addr(g_full + gs), static_cast<std::uint32_t>((qg / kGStages) & 1), abort_flag);
+                for (int wl = 0; wl < nwin; ++wl, ++q) {
+                    const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
+                    bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (lane == 0) {
+                        const std::uint32_t a_tile = smem0 + b * kTileBytes;
+                        const std::uint32_t g_rec = grec0 + gs * GREC;
+#pragma unroll
+                        for (int kk = 0; kk < kRows / 16; ++kk)
+                            mma_bf16(tmem_base + wl * NC, smem_desc_sw128(a_tile + (kk >> 2) * kQuarterBytes + (kk & 3) * 32),
+                                     smem_desc_g(g_rec + kk * 256), IDESC, gi > 0 || kk > 0);
+                        mma_commit(smem_addr(a_empty + b));
+                        if (wl == nwin - 1) mma_commit(smem_addr(g_empty + gs));
+                        if (wl == nwin - 1 && gi == count - 1) mma_commit(smem_addr(acc_full));
+                    }
+                    __syncwarp();
+                }
+            }
+            u += count;
+        }
+    } else {
+        const int role = warp - kProducerWarps - 1; // 0: G records, 1..kChunkLoaders: entry chunks
+        if (role == 0) {
+            if (lane == 0) {
+                long long qg = 0;
+                for (std::int64_t u = u0; u < u1; ++u, ++qg) {
+                    const std::int64_t gi = u % p.group_count;
+                    const int gs = static_cast<int>(qg % kGStages);
+                    bar_wait(smem_addr(g_empty + gs), static_cast<std::uint32_t>(((qg / kGStages) & 1) ^ 1), abort_flag);
+                    bar_arrive_expect_tx(smem_addr(g_full + gs), GREC);
+                    bulk_copy_g2s(grec0 + gs * GREC, p.records + static_cast<std::size_t>(gi) * GREC, GREC, smem_addr(g_full + gs));
+                }
+            }
+        } else {
+            const int mine_mod = role - 1;
+            long long qc = 0;
+            for (std::int64_t u = u0; u < u1; ++u) {
+                const std::int64_t set = u / p.group_count, group = p.group_begin + u % p.group_count;
+                const int nwin = static_cast<int>(dmin(kSetWindows, p.windows - set * kSetWindows));
+                // the unit's segments are consecutive: their bounds in one coalesced read
+                const std::int64_t bound = lane <= nwin ? __ldg(p.seg_ptr + group * p.windows + set * kSetWindows + lane) : 0;
+                for (int j = 0; j < nwin; ++j) {
+                    const std::int64_t lo = __shfl_sync(0xffffffffu, bound, j), hi = __shfl_sync(0xffffffffu, bound, j + 1);
+                    std::int64_t at = lo;
+                    do {
+                        const int n_entries = static_cast<int>(dmin(kChunkEntries, hi - at));
+                        if (lane == 0 && qc % kChunkLoaders == mine_mod) {
+                            const int cs = static_cast<int>(qc % kChunkStages);
+                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / kChunkStages) & 1) ^ 1), abort_flag);
+                            chunk_meta[cs] = (n_entries << 1) | (at + n_entries >= hi ? 1 : 0);
+                            if (n_entries > 0) {
+                                bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(n_entries) * 4u);
+                                bulk_copy_g2s(chunk0 + cs * kChunkBytes, p.entries + at, static_cast<std::uint32_t>(n_entries) * 4u,
+                                              smem_addr(c_full + cs));
+                            } else {
+                                bar_arrive(smem_addr(c_full + cs)); // an empty segment still hands over one (empty) chunk
+                            }
+                        }
+                        at += n_entries;
+                        ++qc;
+                    } while (at < hi);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template<int NC> constexpr std::size_t tb_smem_bytes() {
+    return 2 * kTileBytes + kGStages * g_record_bytes(NC) + kChunkStages * kChunkBytes + kSetWindows * kWin * 8 + kRows * 4 +
+           (6 + 2 * kGStages + 2 * kChunkStages) * sizeof(std::uint64_t) + (kChunkStages + 1) * 4 + 16;
+}
+
+template<int NC>
+cb200_status launch_one(const tb_params &p, int sm_count, cudaStream_t stream) {
+    constexpr std::size_t smem = tb_smem_bytes<NC>();
+    static_assert(smem <= 232448, "shared memory budget");
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_transpose_blocked_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+    const std::int64_t sets = (p.windows + kSetWindows - 1) / kSetWindows;
+    const std::int64_t units = sets * p.group_count;
+    const unsigned grid = static_cast<unsigned>(units < sm_count ? units : sm_count);
+    qcsr_transpose_blocked_kernel<NC><<<grid, kThreads, smem, stream>>>(p);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+} // namespace
+
+// status block + one bf16 record of G per group of 256 cells
+std::uint64_t qcsr_transpose_blocked_workspace_bytes(std::int64_t rows, std::int64_t n) {
+    const std::int64_t groups = (rows + kRows - 1) / kRows;
+    return static_cast<std::uint64_t>(256 + groups * g_record_bytes(static_cast<int>(n)));
+}
+
+bool qcsr_transpose_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits) {
+    return (bits == 8 || bits == 4) && (n == 32 || n == 64) && rows > 0 && cols > 0 && cols <= 0x7fffffff - kWin;
+}
+
+cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                           std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                           const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken) {
+    *taken = false;
+    if (layout.seg_ptr == nullptr || d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS;
+    if (!qcsr_transpose_blocked_shape_ok(x.rows, x.cols, d.n, x.bits) || d.dense_dtype != CB200_DTYPE_F32) return CB200_STATUS_SUCCESS;
+    if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return CB200_STATUS_SUCCESS;
+    if (workspace == nullptr || workspace_bytes < qcsr_transpose_blocked_workspace_bytes(x.rows, d.n)) return CB200_STATUS_SUCCESS;
+    if (reinterpret_cast<std::uintptr_t>(workspace) % 256u != 0u) return CB200_STATUS_SUCCESS;
+    const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+    // the kernel reads 256 row offsets per group: the last group must not run past the array
+    if (row_policy && x.offsets != nullptr && x.rows % kRows != 0) return CB200_STATUS_SUCCESS;
+    if (x.row_ptr != layout.src_row_ptr || x.col_idx != layout.src_col_idx || x.packed != layout.src_packed)
+        return fail(CB200_STATUS_STALE_STRUCTURE, "the launch's matrix is not the one the window-blocked copy was built from");
+
+    *taken = true;
+    // G' = beta * G', also for an empty row range
+    {
+        const std::int64_t total = x.cols * d.n;
+        const unsigned grid = static_cast<unsigned>(std::min<std::int64_t>((total + 255) / 256, static_cast<std::int64_t>(sm_count) * 8));
+        scale_output_kernel<<<grid, 256, 0, stream>>>(d.out, x.cols, static_cast<int>(d.n), d.out_ld, d.beta);
+        count_launch();
+        CB200_CUDA_OK(cudaGetLastError());
+    }
+    if (row_end <= row_begin) return CB200_STATUS_SUCCESS;
+
+    int *status = static_cast<int *>(workspace);
+    unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
+    const std::int64_t group_begin = row_begin / kRows, group_end = (row_end + kRows - 1) / kRows;
+    CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    pack_g_kernel<<<static_cast<unsigned>(group_end - group_begin), 256, 0, stream>>>(
+        static_cast<const float *>(d.dense), d.dense_ld, static_cast<int>(d.n), row_begin, row_end, group_begin, records);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+
+    tb_params p{};
+    p.entries = layout.entries; p.seg_ptr = layout.seg_ptr; p.scales = x.scales;
+    p.gene_offsets = row_policy ? nullptr : x.offsets; p.row_offsets = row_policy ? x.offsets : nullptr;
+    p.records = records; p.out = d.out; p.out_ld = d.out_ld; p.cols = x.cols;
+    p.group_begin = group_begin; p.group_count = group_end - group_begin; p.windows = layout.windows;
+    p.alpha = d.alpha; p.status = status;
+    return d.n == 64 ? launch_one<64>(p, sm_count, stream) : launch_one<32>(p, sm_count, stream);
+}
+
+} // namespace cb200

@@ -294,12 +294,15 @@ def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = No
 
 
 def spmm_transpose(x: QuantizedCsr, g: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
-                   row_begin=0, row_end=0):
-    """G' = alpha * deq(X)^T G + beta * G'."""
+                   row_begin=0, row_end=0, multiply: int = 0):
+    """G' = alpha * deq(X)^T G + beta * G'.
+
+    multiply=capi.DTYPE_BF16 asks for tensor-core products (decoded values and G rounded to bf16)."""
     n = g.shape[1]
     if out is None:
         out = torch.empty(x.cols, n, dtype=torch.float32, device=x.device)
-    op = PreparedSpmm(capi.PROJECTION_TRANSPOSE, x.rows, x.cols, n, x.nnz, x.bits, x.policy, g.dtype, x.device)
+    op = PreparedSpmm(capi.PROJECTION_TRANSPOSE, x.rows, x.cols, n, x.nnz, x.bits, x.policy, g.dtype, x.device,
+                      multiply=multiply, device_matrix=x if multiply == capi.DTYPE_BF16 else None)
     op.run(x, g, out, alpha=alpha, beta=beta, row_begin=row_begin, row_end=row_end)
     op.close()
     return out

@@ -217,7 +217,9 @@ typedef struct cb200_spmm_problem {
     int32_t deterministic; /* prepare_policy.deterministic, operation_core.hh:116-124 */
     /* numeric_policy.multiply of the request: 0 or CB200_DTYPE_F32 = exact fp32 products;
      * CB200_DTYPE_BF16 = decoded values may be rounded to bf16 and multiplied on the tensor cores
-     * (CSR forward with bf16 W: schedule "tensor_windows"; Blocked-ELL with bf16 W always does). */
+     * (CSR forward with bf16 W: schedules "tensor_windows" / "tensor_blocked"; transpose with the
+     * matrix handed to prepare: "tensor_blocked", which rounds the fp32 G to bf16 as well;
+     * Blocked-ELL with bf16 W always does). */
     int32_t multiply;
     /* Optional: the device-resident matrix itself (arrays on `device`, final contents).  With bf16
      * products allowed, prepare then builds a persistent window-blocked copy of it (one 32-bit
@@ -235,7 +237,8 @@ void cb200_prepared_destroy(cb200_prepared *prepared);
 /* workspace_requirement, launch_bindings.hh:67-71 */
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
 /* kernel choice made at prepare time, as text: "warp_per_row", "gene_tiled" (exact fp32 products);
- * "tensor_windows", "tensor_blocked" (CSR, bf16 products on tcgen05); "tcgen05_block_rows" (Blocked-ELL) */
+ * "tensor_windows", "tensor_blocked" (CSR, bf16 products on tcgen05); "tcgen05_block_rows" (Blocked-ELL);
+ * transpose: "vector_reductions" (exact) or "tensor_blocked" */
 const char *cb200_prepared_schedule(const cb200_prepared *prepared);
 
 /* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch. */

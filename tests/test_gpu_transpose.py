@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from cellerator_b200 import capi, ops
+from cellerator_b200 import capi, ops, synth
 from conftest import GOLDEN, random_csr
 from gpu_util import dense, host_pack, to_dev
 
@@ -106,3 +106,81 @@ def test_transpose_rejects_deterministic_and_bf16(cuda_device):
     assert e.value.status == capi.UNSUPPORTED
     with pytest.raises(capi.Cb200Error):
         ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, 8, 8, 8, 8, 8, 1, torch.bfloat16, cuda_device)
+
+
+def assert_tensor_transpose_close(got, ref, col_l1, g_abs_max):
+    """bf16 products: decoded values and G both rounded to bf16 (2^-9 each), fp32 accumulation:
+    1e-2 relative to ||gene column||_1 * max|G|, the benchmark contract's bf16 tolerance."""
+    err = np.abs(np.asarray(got, dtype=np.float64) - ref)
+    scale = col_l1[:, None] * g_abs_max + 1e-30
+    assert np.all(err <= 1e-2 * scale), f"max err/scale {np.max(err / scale):.3e}"
+    assert np.median(err / scale) < 2e-3
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("n", [32, 64])
+@pytest.mark.parametrize("policy", [1, 2])
+def test_tensor_transpose_parity(cuda_device, oracle, monkeypatch, bits, n, policy):
+    """The tcgen05 schedule over the window-blocked copy, forced on a small matrix: several row
+    groups, more than one set of eight gene windows with a ragged last set and a ragged last window,
+    row ranges (rows outside the range contribute nothing), alpha / beta."""
+    monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+    rng = np.random.default_rng(91 * bits + n + policy)
+    rows, cols = 256 * 5, 1300
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=200, bits=bits, policy=policy))
+    x = to_dev(c, cuda_device)
+    g, g_host = dense(rng, rows, n, torch.float32, cuda_device, std=1.0)
+    op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cols, n, x.nnz, bits, policy, g.dtype, cuda_device,
+                          multiply=capi.DTYPE_BF16, device_matrix=x)
+    assert op.schedule == "tensor_blocked"
+    out = op.run(x, g, torch.full((cols, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0          # no bounded wait ran out
+    ref = oracle.qcsr_transpose(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                c["scales"], c["offsets"], g_host, cols)
+    cl1 = col_l1_of(oracle, c)
+    gmax = float(np.abs(g_host).max())
+    assert_tensor_transpose_close(out.cpu().numpy(), ref, cl1, gmax)
+    # a row range that starts and ends inside groups
+    r0, r1 = 300, 1000
+    part = op.run(x, g, torch.empty(cols, n, device=cuda_device), row_begin=r0, row_end=r1)
+    pref = oracle.qcsr_transpose(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                 c["scales"], c["offsets"], g_host, cols, r0, r1)
+    assert_tensor_transpose_close(part.cpu().numpy(), pref, cl1, gmax)
+    # alpha / beta
+    init = torch.from_numpy(rng.normal(size=(cols, n)).astype(np.float32)).to(cuda_device)
+    out2 = op.run(x, g, init.clone(), alpha=2.0, beta=0.5).cpu().numpy()
+    assert np.allclose(out2, 2.0 * out.cpu().numpy() + 0.5 * init.cpu().numpy(), rtol=1e-4, atol=1e-4 * gmax * (cl1.max() + 1))
+    # without the opt-in the exact kernel runs
+    exact = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cols, n, x.nnz, bits, policy, g.dtype, cuda_device)
+    assert exact.schedule == "vector_reductions"
+    assert_transpose_close(exact.run(x, g, torch.empty(cols, n, device=cuda_device)).cpu().numpy(), ref, cl1, gmax)
+    op.close()
+    exact.close()
+
+
+def test_tensor_transpose_full_scale(cuda_device):
+    """Genes as in the benchmark configuration, 1/8 of its cells: the tensor schedule against the
+    exact kernel on every gene, and the shard rule (partials of row halves add up)."""
+    cfg = dict(synth.CONFIGS["c2_forward"])
+    cfg["rows"] //= 8
+    x = synth.make_qcsr_device(**cfg, device=cuda_device, seed=0)
+    n = 64
+    g = torch.randn(x.rows, n, device=cuda_device)
+    op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, x.rows, x.cols, n, x.nnz, x.bits, x.policy, g.dtype, cuda_device,
+                          multiply=capi.DTYPE_BF16, device_matrix=x)
+    assert op.schedule == "tensor_blocked"
+    out = op.run(x, g, torch.empty(x.cols, n, device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0
+    exact = ops.spmm_transpose(x, g)
+    vals = x.dequantize().abs().double()
+    col_l1 = torch.zeros(x.cols, dtype=torch.float64, device=cuda_device).index_add_(0, x.col_idx.long(), vals)
+    del vals
+    gmax = float(g.abs().max())
+    assert torch.all((out - exact).abs() <= 1e-2 * (col_l1[:, None] * gmax).float() + 1e-30)
+    half = (x.rows // 2 // 256) * 256 + 77
+    a = op.run(x, g, torch.empty(x.cols, n, device=cuda_device), row_begin=0, row_end=half)
+    b = op.run(x, g, a, row_begin=half, row_end=x.rows, beta=1.0)
+    assert torch.allclose(b, out, rtol=1e-3, atol=1e-3 * gmax)
+    op.close()
