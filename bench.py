@@ -115,7 +115,7 @@ def algorithmic_bytes(kind, m, k, n, nnz, bits, dense_bytes):
     return nnz * (bits / 8 + 4) + (m + 1) * 8 + m * n * 4 + k * n * dense_bytes + k * 8
 
 
-def build_workload(name, device, rank, world, seed=0, rows_override=None, multiply="bf16"):
+def build_workload(name, device, rank, world, seed=0, rows_override=None, multiply="bf16", prepare_matrix=True):
     import torch
 
     from cellerator_b200 import capi, ops, synth
@@ -155,12 +155,14 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         n = 64
         dense = torch.randn(rows, n, generator=g).to(device)
         out = torch.empty(cfg["cols"], n, dtype=torch.float32, device=device)
-        # G is fp32, for which the contract's bound is 1e-4 * ||.||_1 * max|G|: the default arm runs the
-        # exact-product kernel (L2 vector reductions).  --multiply bf16 times the tensor-core schedule over
-        # the window-blocked copy (decoded values and G rounded to bf16, fp32 accumulation; 1e-2 bound)
+        # G is fp32, for which the contract's bound is 1e-4 * ||.||_1 * max|G|: the default arm asks for
+        # fp32 products and hands the matrix to prepare, which selects the tensor-core schedule with
+        # split products (three bf16 passes rebuild each product to ~3 * 2^-17; "tensor_blocked_x3").
+        # --multiply bf16: one pass, values and G rounded to bf16 (1e-2 bound).  --no-prepare-matrix:
+        # the fp32-FMA kernel with L2 vector reductions.
         op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype,
                               device, multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
-                              device_matrix=x if multiply == "bf16" else None)
+                              device_matrix=x if prepare_matrix else None)
         kind, dbytes = "transpose", 4
     else:
         n = cfg["n"]
@@ -171,7 +173,7 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype, device,
                               host_row_ptr=x.host_row_ptr,
                               multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
-                              device_matrix=x if multiply == "bf16" else None)
+                              device_matrix=x if (multiply == "bf16" and prepare_matrix) else None)
         kind, dbytes = "forward", 2
     wl.update(x=x, dense=dense, out=out, op=op, units=x.nnz, kind=kind, n=n,
               bytes=algorithmic_bytes(kind, rows, cfg["cols"], n, x.nnz, x.bits, dbytes), flops=2.0 * x.nnz * n)
@@ -270,7 +272,8 @@ def run_ours(args):
 
     if args.multiply is None:  # what the contract's tolerance for the workload's dense operand allows
         args.multiply = "f32" if args.workload == "c3_transpose" else "bf16"
-    wl = build_workload(args.workload, device, rank, world, rows_override=args.rows, multiply=args.multiply)
+    wl = build_workload(args.workload, device, rank, world, rows_override=args.rows, multiply=args.multiply,
+                        prepare_matrix=not args.no_prepare_matrix)
     op, x, dense, out = wl["op"], wl["x"], wl["dense"], wl["out"]
     launch = op.make_launch(x, dense, out)
     L = capi.lib()
@@ -361,6 +364,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": f"u{x.bits} codes -> " + ("bf16 products (tcgen05), f32 accumulate"
                                            if op.schedule in ("tensor_windows", "tensor_blocked", "tcgen05_block_rows")
+                                           else "3 x bf16 split products (tcgen05), f32 accumulate" if op.schedule == "tensor_blocked_x3"
                                            else "f32 products, f32 accumulate"),
         "data": "synthetic (seeded, device-generated; shapes and value model of the named configuration)",
         "config": {"workload": args.workload, "cells_per_gpu": wl["rows"], "genes": wl["cfg"]["cols"], "n": wl["n"],
@@ -467,6 +471,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_forward", choices=["c2_forward", "c3_transpose", "c4_4bit", "c5_bell"])
     ap.add_argument("--rows", type=int, default=0, help="override cells per GPU (profiling on a small case)")
+    ap.add_argument("--no-prepare-matrix", action="store_true",
+                    help="do not hand the matrix to prepare: no window-blocked copy, CSR-only schedules")
     ap.add_argument("--multiply", default=None, choices=["bf16", "f32"],
                     help="products: bf16 (tensor cores; default where the dense operand is bf16) or exact fp32 "
                          "(CUDA cores; default for the transpose, whose G is fp32)")

@@ -303,10 +303,13 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         p->workspace_bytes = qcsr_transpose_workspace_bytes(problem->k, problem->n, p->sm_count);
         p->schedule_name = "vector_reductions";
-        // bf16 products allowed (G is rounded to bf16 as well) and the matrix at hand: the tensor-core
-        // kernel over the window-blocked copy; its cost follows the dense area, so it needs density
+        // With the matrix at hand: the tensor-core kernel over the window-blocked copy.  bf16 products
+        // allowed: one pass (decoded values and G rounded to bf16).  fp32 products: three bf16 passes
+        // (hi*hi + hi*lo + lo*hi) rebuild each product to ~3 * 2^-17 relative, inside the 1e-4 bound of
+        // an fp32 G; that is not bit-equal to an fp32 multiply, and callers that need the fp32-FMA kernel
+        // do not hand the matrix to prepare.  The cost follows the dense area, so it needs density.
         const char *force = std::getenv("CB200_TRANSPOSE_SCHEDULE");
-        bool blocked = problem->multiply == CB200_DTYPE_BF16 && problem->device_matrix != nullptr &&
+        bool blocked = problem->device_matrix != nullptr &&
                        qcsr_transpose_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits);
         if (force == nullptr)
             blocked = blocked && problem->m >= 16 * 256 && p->mean_row_nnz >= 0.004 * static_cast<double>(problem->k);
@@ -327,7 +330,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
                 delete p;
                 return st;
             }
-            p->schedule_name = "tensor_blocked";
+            p->schedule_name = problem->multiply == CB200_DTYPE_BF16 ? "tensor_blocked" : "tensor_blocked_x3";
             p->workspace_bytes = qcsr_transpose_blocked_workspace_bytes(problem->m, problem->n);
             p->persistent_bytes += p->blocked.bytes;
         }
@@ -505,8 +508,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed_values == nullptr)))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "CSR matrix has null arrays");
     if (pr.projection == CB200_PROJECTION_TRANSPOSE)
-        return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, &prepared->blocked, launch->workspace,
-                                     launch->workspace_bytes, prepared->sm_count, stream);
+        return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, &prepared->blocked, pr.multiply != CB200_DTYPE_BF16,
+                                     launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);
     return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, &prepared->blocked,
                                launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);
 }

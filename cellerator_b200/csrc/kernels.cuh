@@ -73,18 +73,20 @@ cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::i
                                  const blocked_layout *blocked, void *workspace, std::uint64_t workspace_bytes,
                                  int sm_count, cudaStream_t stream);
 
-// Transpose on the tensor cores from the window-blocked copy (bf16 products, N in {32, 64}).
+// Transpose on the tensor cores from the window-blocked copy (N in {32, 64}).  split_products == false:
+// one pass of bf16 products; true: fp32 products rebuilt from three bf16 passes (hi*hi + hi*lo + lo*hi).
 bool qcsr_transpose_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits);
 std::uint64_t qcsr_transpose_blocked_workspace_bytes(std::int64_t rows, std::int64_t n);
 cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                            std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
-                                           const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken);
+                                           const blocked_layout &layout, bool split_products, int sm_count,
+                                           cudaStream_t stream, bool *taken);
 
 // G'[g,:] = alpha * sum_{r in range, col_i == g} deq(code_i) * G[r,:] + beta * G'[g,:]
 // `blocked` (optional): the window-blocked copy of a prepared bf16-product operation.
 cb200_status launch_qcsr_transpose(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
-                                   std::int64_t row_end, const blocked_layout *blocked, void *workspace,
-                                   std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream);
+                                   std::int64_t row_end, const blocked_layout *blocked, bool split_products,
+                                   void *workspace, std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream);
 std::uint64_t qcsr_transpose_workspace_bytes(std::int64_t cols, std::int64_t n, int sm_count);
 
 struct qbell_view {

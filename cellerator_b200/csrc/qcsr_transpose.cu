@@ -160,14 +160,14 @@ cb200_status dispatch(const tr_params &p, bool vector_ok, cudaStream_t stream) {
 std::uint64_t qcsr_transpose_workspace_bytes(std::int64_t, std::int64_t, int) { return 0; }
 
 cb200_status launch_qcsr_transpose(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
-                                   std::int64_t row_end, const blocked_layout *blocked, void *workspace,
-                                   std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                                   std::int64_t row_end, const blocked_layout *blocked, bool split_products,
+                                   void *workspace, std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream) {
     if (d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS;
     if (d.dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes an fp32 dense operand");
     if (blocked != nullptr && blocked->seg_ptr != nullptr) {
         bool taken = false;
         const cb200_status st = launch_qcsr_transpose_blocked(x, d, row_begin, row_end, workspace, workspace_bytes, *blocked,
-                                                              sm_count, stream, &taken);
+                                                              split_products, sm_count, stream, &taken);
         if (st != CB200_STATUS_SUCCESS || taken) return st;
     }
     // The output is initialised even for an empty row range: G' = beta * G'.

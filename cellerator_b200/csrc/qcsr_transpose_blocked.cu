@@ -65,6 +65,7 @@ struct tb_params {
     int windows;
     float alpha;
     int *status;
+    int value_part; // 0: tile holds hi = bf16(value); 1: lo = bf16(value - hi)
 };
 
 __device__ __forceinline__ std::int64_t dmin(std::int64_t a, std::int64_t b) { return a < b ? a : b; }
@@ -170,15 +171,19 @@ __global__ void __launch_bounds__(256) scale_output_kernel(float *out, std::int6
 // G [cells][n] fp32 (leading dimension ld) -> one bf16 record per group of 256 cells: the n x 256
 // slice of G^T in the no-swizzle K-major operand layout (byte offset of (column c, cell r) =
 // (c/8)*4096 + (r/8)*128 + (c%8)*16 + (r%8)*2).  Cells outside [row_begin, row_end) are zero.
+// part 0 writes hi = bf16(g); part 1 writes lo = bf16(g - hi), the next 8 bits of the mantissa.
 __global__ void __launch_bounds__(256) pack_g_kernel(const float *g, std::int64_t ld, int n, std::int64_t row_begin,
-                                                     std::int64_t row_end, std::int64_t group_begin, unsigned char *records) {
+                                                     std::int64_t row_end, std::int64_t group_begin, int part,
+                                                     unsigned char *records) {
     const std::int64_t group = group_begin + blockIdx.x;
     __nv_bfloat16 *rec = reinterpret_cast<__nv_bfloat16 *>(records + static_cast<std::size_t>(blockIdx.x) * g_record_bytes(n));
     for (int i = threadIdx.x; i < kRows * n; i += blockDim.x) {
         const int r = i / n, c = i % n; // consecutive threads read consecutive columns of one cell
         const std::int64_t row = group * kRows + r;
         const float v = (row >= row_begin && row < row_end) ? g[row * ld + c] : 0.0f;
-        rec[((c >> 3) * (kRows * 16) + (r >> 3) * 128 + (c & 7) * 16 + (r & 7) * 2) >> 1] = __float2bfloat16_rn(v);
+        __nv_bfloat16 b = __float2bfloat16_rn(v);
+        if (part != 0) b = __float2bfloat16_rn(v - __bfloat162float(b));
+        rec[((c >> 3) * (kRows * 16) + (r >> 3) * 128 + (c & 7) * 16 + (r & 7) * 2) >> 1] = b;
     }
 }
 
@@ -312,7 +317,9 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                                 const float value = fmaf(static_cast<float>(e[k] & 0xffu), t[k].x, add);
                                 // padding words (top bit set) are stored to a scratch slot instead of branching
                                 unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + off : scratch_slot;
-                                *reinterpret_cast<__nv_bfloat16 *>(dst) = __float2bfloat16_rn(value);
+                                __nv_bfloat16 b = __float2bfloat16_rn(value);
+                                if (p.value_part != 0) b = __float2bfloat16_rn(value - __bfloat162float(b)); // the next 8 mantissa bits
+                                *reinterpret_cast<__nv_bfloat16 *>(dst) = b;
                             }
                         }
                         __syncwarp();
@@ -472,7 +479,8 @@ bool qcsr_transpose_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::
 
 cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                            std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
-                                           const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken) {
+                                           const blocked_layout &layout, bool split_products, int sm_count,
+                                           cudaStream_t stream, bool *taken) {
     *taken = false;
     if (layout.seg_ptr == nullptr || d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS;
     if (!qcsr_transpose_blocked_shape_ok(x.rows, x.cols, d.n, x.bits) || d.dense_dtype != CB200_DTYPE_F32) return CB200_STATUS_SUCCESS;
@@ -500,10 +508,6 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
     unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
     const std::int64_t group_begin = row_begin / kRows, group_end = (row_end + kRows - 1) / kRows;
     CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    pack_g_kernel<<<static_cast<unsigned>(group_end - group_begin), 256, 0, stream>>>(
-        static_cast<const float *>(d.dense), d.dense_ld, static_cast<int>(d.n), row_begin, row_end, group_begin, records);
-    count_launch();
-    CB200_CUDA_OK(cudaGetLastError());
 
     tb_params p{};
     p.entries = layout.entries; p.seg_ptr = layout.seg_ptr; p.scales = x.scales;
@@ -511,7 +515,22 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
     p.records = records; p.out = d.out; p.out_ld = d.out_ld; p.cols = x.cols;
     p.group_begin = group_begin; p.group_count = group_end - group_begin; p.windows = layout.windows;
     p.alpha = d.alpha; p.status = status;
-    return d.n == 64 ? launch_one<64>(p, sm_count, stream) : launch_one<32>(p, sm_count, stream);
+    // One pass multiplies bf16(value) with bf16(G).  With split products the fp32 product is rebuilt
+    // from three passes, hi*hi + hi*lo + lo*hi (v = hi + lo + O(2^-17 v), likewise G): relative error
+    // per product about 3 * 2^-17, inside the 1e-4 bound of an fp32 dense operand.  The passes run
+    // back to back on the stream, share the record buffer and add into the same G'.
+    const int passes = split_products ? 3 : 1;
+    for (int pass = 0; pass < passes; ++pass) {
+        const int g_part = pass == 1 ? 1 : 0;
+        p.value_part = pass == 2 ? 1 : 0;
+        pack_g_kernel<<<static_cast<unsigned>(group_end - group_begin), 256, 0, stream>>>(
+            static_cast<const float *>(d.dense), d.dense_ld, static_cast<int>(d.n), row_begin, row_end, group_begin, g_part, records);
+        count_launch();
+        CB200_CUDA_OK(cudaGetLastError());
+        const cb200_status st = d.n == 64 ? launch_one<64>(p, sm_count, stream) : launch_one<32>(p, sm_count, stream);
+        if (st != CB200_STATUS_SUCCESS) return st;
+    }
+    return CB200_STATUS_SUCCESS;
 }
 
 } // namespace cb200

@@ -184,3 +184,37 @@ def test_tensor_transpose_full_scale(cuda_device):
     b = op.run(x, g, a, row_begin=half, row_end=x.rows, beta=1.0)
     assert torch.allclose(b, out, rtol=1e-3, atol=1e-3 * gmax)
     op.close()
+
+
+@pytest.mark.parametrize("bits,policy", [(8, 1), (4, 2)])
+def test_tensor_transpose_split_products_meet_the_fp32_bound(cuda_device, oracle, monkeypatch, bits, policy):
+    """fp32 products requested and the matrix handed to prepare: three bf16 passes (hi*hi + hi*lo +
+    lo*hi) rebuild each product; the result meets the fp32 bound 1e-4 * ||gene column||_1 * max|G|
+    with a wide margin, also on a row range and with alpha / beta."""
+    monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+    rng = np.random.default_rng(17 * bits + policy)
+    rows, cols, n = 256 * 4, 1100, 64
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=220, bits=bits, policy=policy))
+    x = to_dev(c, cuda_device)
+    g, g_host = dense(rng, rows, n, torch.float32, cuda_device, std=1.0)
+    op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cols, n, x.nnz, bits, policy, g.dtype, cuda_device,
+                          device_matrix=x)
+    assert op.schedule == "tensor_blocked_x3"
+    out = op.run(x, g, torch.full((cols, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0
+    ref = oracle.qcsr_transpose(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                c["scales"], c["offsets"], g_host, cols)
+    cl1 = col_l1_of(oracle, c)
+    gmax = float(np.abs(g_host).max())
+    assert_transpose_close(out.cpu().numpy(), ref, cl1, gmax)
+    err = np.abs(out.cpu().numpy().astype(np.float64) - ref) / (cl1[:, None] * gmax + 1e-30)
+    assert err.max() < 3e-5                                             # ~3 * 2^-17 per product, fp32 sums
+    part = op.run(x, g, torch.empty(cols, n, device=cuda_device), row_begin=130, row_end=777)
+    pref = oracle.qcsr_transpose(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                 c["scales"], c["offsets"], g_host, cols, 130, 777)
+    assert_transpose_close(part.cpu().numpy(), pref, cl1, gmax)
+    init = torch.from_numpy(rng.normal(size=(cols, n)).astype(np.float32)).to(cuda_device)
+    out2 = op.run(x, g, init.clone(), alpha=2.0, beta=0.5).cpu().numpy()
+    assert np.allclose(out2, 2.0 * ref + 0.5 * init.cpu().numpy(), rtol=1e-4, atol=1e-4 * gmax * (cl1.max() + 1))
+    op.close()
