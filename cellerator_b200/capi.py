@@ -94,7 +94,7 @@ EXPORTED_SYMBOLS = [
     "cb200_block_count_for_rows", "cb200_build_uniform_block_row_ptr", "cb200_get_block", "cb200_quantize_rows",
     "cb200_dequantize_rows", "cb200_qbell_quantize_rows", "cb200_qbell_dequantize_rows",
     "cb200_backend_query", "cb200_spmm_prepare", "cb200_prepared_destroy",
-    "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_spmm_run", "cb200_kernel_launch_count",
+    "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_prepared_persistent_bytes", "cb200_spmm_run", "cb200_kernel_launch_count",
     "cb200_qcsr_forward_static",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
@@ -135,6 +135,8 @@ def lib() -> C.CDLL:
         L.cb200_prepared_workspace.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]
         L.cb200_prepared_schedule.argtypes = [C.c_void_p]
         L.cb200_prepared_schedule.restype = C.c_char_p
+        L.cb200_prepared_persistent_bytes.argtypes = [C.c_void_p]
+        L.cb200_prepared_persistent_bytes.restype = C.c_uint64
         L.cb200_spmm_run.argtypes = [C.c_void_p, C.POINTER(Launch)]
         L.cb200_qcsr_forward_static.argtypes = [C.POINTER(QCsr), C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
                                                 C.c_int64, C.c_float, C.c_float, C.c_int32, C.c_void_p]

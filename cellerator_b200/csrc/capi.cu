@@ -451,6 +451,10 @@ const char *cb200_prepared_schedule(const cb200_prepared *prepared) {
     return prepared != nullptr ? prepared->schedule_name : "";
 }
 
+uint64_t cb200_prepared_persistent_bytes(const cb200_prepared *prepared) {
+    return prepared != nullptr ? prepared->persistent_bytes : 0u;
+}
+
 cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch) {
     clear_error();
     if (prepared == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "null prepared operation");

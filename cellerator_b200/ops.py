@@ -237,6 +237,11 @@ class PreparedSpmm:
     def schedule(self) -> str:
         return capi.lib().cb200_prepared_schedule(self.handle).decode()
 
+    @property
+    def persistent_bytes(self) -> int:
+        """Device bytes the prepared operation owns (row order, window-blocked copy)."""
+        return int(capi.lib().cb200_prepared_persistent_bytes(self.handle))
+
     def make_launch(self, x, dense: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0, row_begin=0, row_end=0,
                     stream: int | None = None, epoch: int | None = None) -> capi.Launch:
         ln = capi.header(capi.Launch())

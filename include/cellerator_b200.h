@@ -245,6 +245,9 @@ cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *
  * "tensor_windows", "tensor_blocked" (CSR, bf16 products on tcgen05); "tcgen05_block_rows" (Blocked-ELL);
  * transpose: "vector_reductions" (exact) or "tensor_blocked" */
 const char *cb200_prepared_schedule(const cb200_prepared *prepared);
+/* device bytes the prepared operation owns (row order, window-blocked copy): prepared_operation.persistent.bytes,
+ * operation_core.hh:126-129,167-181; freed by cb200_prepared_destroy */
+uint64_t cb200_prepared_persistent_bytes(const cb200_prepared *prepared);
 
 /* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch. */
 typedef struct cb200_launch {

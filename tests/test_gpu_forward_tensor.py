@@ -46,6 +46,8 @@ def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits
     w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
     op = prepared(x, n, w, cuda_device, blocked=schedule == "tensor_blocked")
     assert op.schedule == schedule
+    if schedule == "tensor_blocked":                                    # one word per stored entry + segment table
+        assert 4 * x.nnz <= op.persistent_bytes <= 4 * x.nnz + 64 * ((rows + 255) // 256) * ((cols + 127) // 128) + 4 * rows
     y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
     torch.cuda.synchronize()
     assert int(op.workspace[:4].view(torch.int32).item()) == 0          # no bounded wait ran out
