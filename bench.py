@@ -486,7 +486,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16)
-    ap.add_argument("--cpu-rows-per-thread", type=int, default=1500)
+    ap.add_argument("--cpu-rows-per-thread", type=int, default=4000,
+                    help="rows of the CPU sample per host thread (4,000 rows x 16 threads: ~25 CPU-seconds per pass)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
