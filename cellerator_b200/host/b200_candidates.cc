@@ -330,6 +330,11 @@ void release_prepared(core::prepared_operation *prepared) noexcept {
     prepared->run = nullptr;
 }
 
+const char *prepared_schedule(const core::prepared_operation &prepared) noexcept {
+    const auto *state = static_cast<const prepared_state *>(prepared.persistent.data);
+    return state != nullptr && state->handle != nullptr ? cb200_prepared_schedule(state->handle) : "";
+}
+
 ::cellerator::planner::planner_candidate make_planner_candidate(const core::operation_candidate &candidate,
                                                                 const core::projection_key &projection,
                                                                 const projection_catalog_entry &shape,

@@ -76,6 +76,10 @@ core::operation_status register_all(core::candidate_registry *registry) noexcept
 // binding-contract arrays).  The operation core has no destroy hook: the plan owner calls this.
 void release_prepared(core::prepared_operation *prepared) noexcept;
 
+// Kernel schedule the backend chose at prepare time ("gene_tiled", "tensor_blocked", ...), "" when the
+// prepared operation is not one of this library's.
+const char *prepared_schedule(const core::prepared_operation &prepared) noexcept;
+
 // planner_candidate record (end_to_end_planner.hh:118-126) with analytical phase costs from a
 // bandwidth model: kernel time = algorithmic bytes / `hbm_bytes_per_ns`, scaled by the fraction
 // of the roofline the kernel reaches.

@@ -360,6 +360,66 @@ int main(int argc, char **argv) {
         host::release_prepared(&pt);
     }
 
+    // ---- transpose with the matrix handed to prepare: tensor-core schedule, split products --------
+    {
+        problem_ids t = make_ids(2u, core::projection_kind::transpose_or_backward, static_cast<std::uint64_t>(nnz));
+        cb200_qcsr dm{};
+        dm.version = CB200_ABI_VERSION; dm.size = sizeof dm; dm.rows = M; dm.cols = K; dm.nnz = nnz; dm.bits = 8;
+        dm.policy = CB200_DECODE_PER_GENE_AFFINE; dm.row_ptr = d_row_ptr; dm.col_idx = d_col; dm.packed_values = d_codes;
+        dm.scales = d_scales; dm.offsets = d_offsets;
+        host::projection_catalog_entry ts = shape;
+        ts.projection = t.projection.runtime;
+        ts.projection_kind = CB200_PROJECTION_TRANSPOSE;
+        ts.device_matrix = &dm;
+        host::register_projection(ts);
+        setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked", 1); // the matrix is far below the size prepare would pick it for
+        core::prepared_operation pt{};
+        core::prepare_policy with_preprocessing;
+        with_preprocessing.allow_persistent_preprocessing = true;
+        st = core::prepare_candidate(*tr, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32),
+                                     with_preprocessing, &pt);
+        unsetenv("CB200_TRANSPOSE_SCHEDULE");
+        CHECK(static_cast<bool>(st), "prepare_candidate(transpose, matrix handed to prepare)");
+        if (!st) std::printf("  message: %s\n", st.message);
+        CHECK(std::strcmp(host::prepared_schedule(pt), "tensor_blocked_x3") == 0, "fp32 products + matrix at prepare -> split-product tensor schedule");
+        CHECK(pt.binding_contract.workspace.minimum_bytes > 4096u, "the schedule reports its workspace (bf16 records of G)");
+        void *d_ws2 = nullptr;
+        const std::size_t ws2 = static_cast<std::size_t>(pt.binding_contract.workspace.minimum_bytes);
+        cudaMalloc(&d_ws2, ws2);
+        ex::relation_structure s2{t.structures.structures[0].runtime, {3u}, cells, genes, {1u, 1u}, static_cast<std::uint64_t>(nnz)};
+        ex::value_plane plane2 = plane;
+        plane2.structure = s2.identity;
+        ex::value_binding v2{&plane2, {5u}};
+        ex::biological_operand_view in2[2] = {inputs[0], dense_view(d_g, cells, static_cast<std::uint64_t>(M))};
+        in2[0].storage.relation.structure = s2.identity;
+        in2[0].storage.relation.projection = t.projection.runtime;
+        ex::biological_operand_view out2[1] = {dense_view(d_gt, genes, static_cast<std::uint64_t>(K))};
+        ex::launch_bindings l2 = launch;
+        l2.structures = &s2; l2.inputs = in2; l2.outputs = out2; l2.values = &v2;
+        l2.workspace = {d_ws2, ws2, dev_loc};
+        st = core::run_prepared_operation(pt, l2);
+        CHECK(static_cast<bool>(st), "run_prepared_operation(transpose, split products)");
+        if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+        cudaStreamSynchronize(stream);
+        std::vector<float> gt(K * N);
+        cudaMemcpy(gt.data(), d_gt, gt.size() * sizeof(float), cudaMemcpyDeviceToHost);
+        CHECK(referee(true, g.data(), M, &ref), "referee(transpose)");
+        // the contract's bound for an fp32 dense operand: 1e-4 * ||gene column||_1 * max|G|
+        std::vector<double> col_l1(K, 0.0);
+        for (std::int64_t i = 0; i < nnz; ++i) col_l1[col[i]] += std::fabs(static_cast<double>(decoded[i]));
+        double gmax = 0.0, worst = 0.0;
+        for (float v : g) gmax = std::max(gmax, static_cast<double>(std::fabs(v)));
+        for (std::int64_t gene = 0; gene < K; ++gene)
+            for (std::int64_t c = 0; c < N; ++c) {
+                const double scale = col_l1[gene] * gmax + 1e-30;
+                worst = std::max(worst, std::fabs(static_cast<double>(gt[gene * N + c]) - ref[gene * N + c]) / scale);
+            }
+        std::printf("  transpose (split products) max |d| / (||column||_1 max|G|) = %.3e\n", worst);
+        CHECK(worst <= 1.0e-4, "split-product transpose within the fp32 bound of the reference referee's result");
+        host::release_prepared(&pt);
+        cudaFree(d_ws2);
+    }
+
     // ---- planner record ---------------------------------------------------------------------------
     {
         const auto rec = host::make_planner_candidate(*fwd, ids.projection, shape, 6553.9, 0.07);
