@@ -374,12 +374,16 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         // With the device-resident matrix at hand, prepare re-lays it once into the window-blocked
         // copy (persistent preprocessing) and the tensor-core kernel streams that instead of the CSR
         // arrays.  Its cost follows the dense area m x k, so it needs a minimum density to pay.
-        bool blocked = tensor_ok && problem->device_matrix != nullptr &&
-                       qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype) &&
-                       problem->m >= 16 * 256 && p->mean_row_nnz >= 0.015 * static_cast<double>(problem->k);
-        if (force != nullptr)
-            blocked = tensor_ok && problem->device_matrix != nullptr && std::strcmp(force, "tensor_blocked") == 0 &&
-                      qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype);
+        // Two ways in: bf16 products allowed (one pass), or fp32 products requested, which the kernel
+        // rebuilds from bf16 pieces in two (bf16 W) or three (fp32 W) passes: not bit-equal to fp32
+        // multiplies, but inside the 1e-4 bound; callers that need the fp32-FMA kernel do not hand the
+        // matrix to prepare.  Split passes cost 2-3x, so they need a denser matrix to beat the exact kernel.
+        const bool split = problem->multiply != CB200_DTYPE_BF16;
+        const bool blocked_ok = problem->device_matrix != nullptr && (tensor_ok || split) &&
+                                qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype);
+        const double min_density = !split ? 0.015 : (problem->dense_dtype == CB200_DTYPE_BF16 ? 0.04 : 0.06);
+        bool blocked = blocked_ok && problem->m >= 16 * 256 && p->mean_row_nnz >= min_density * static_cast<double>(problem->k);
+        if (force != nullptr) blocked = blocked_ok && std::strcmp(force, "tensor_blocked") == 0;
         if (blocked) {
             const cb200_qcsr &dm = *problem->device_matrix;
             if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
@@ -397,7 +401,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             }
             if (p->schedule != fwd_schedule::tensor_windows) tiled = true; // the fallback for unaligned row ranges
             p->schedule = fwd_schedule::tensor_blocked;
-            p->schedule_name = "tensor_blocked";
+            p->schedule_name = !split ? "tensor_blocked"
+                                      : (problem->dense_dtype == CB200_DTYPE_BF16 ? "tensor_blocked_x2" : "tensor_blocked_x3");
             p->workspace_bytes = std::max<std::uint64_t>(qcsr_blocked_workspace_bytes(problem->k, problem->n), 256u);
             p->persistent_bytes += p->blocked.bytes;
         }
@@ -515,7 +520,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
         return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, &prepared->blocked, pr.multiply != CB200_DTYPE_BF16,
                                      launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);
     return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, &prepared->blocked,
-                               launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);
+                               pr.multiply != CB200_DTYPE_BF16, launch->workspace, launch->workspace_bytes, prepared->sm_count,
+                               stream);
 }
 
 /* ---- session ------------------------------------------------------------------------------ */

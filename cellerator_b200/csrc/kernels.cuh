@@ -63,15 +63,18 @@ cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out); // c
 void free_blocked_layout(blocked_layout *layout);
 // *taken is false when the launch cannot use the copy (row range not starting on a group boundary,
 // workspace too small, ...); a matrix other than the one the copy was built from is an error.
+// split_products == false: one pass of bf16 products (bf16 W only); true: fp32 products rebuilt from
+// bf16 pieces in two (bf16 W) or three (fp32 W) passes.
 cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                          std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
-                                         const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken);
+                                         const blocked_layout &layout, bool split_products, int sm_count,
+                                         cudaStream_t stream, bool *taken);
 
 // Y[r,:] = alpha * sum_i deq(code_i) * W[col_i,:] + beta * Y[r,:]  for r in [row_begin,row_end)
 cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                  std::int64_t row_end, fwd_schedule schedule, const void *persistent,
-                                 const blocked_layout *blocked, void *workspace, std::uint64_t workspace_bytes,
-                                 int sm_count, cudaStream_t stream);
+                                 const blocked_layout *blocked, bool split_products, void *workspace,
+                                 std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 // Transpose on the tensor cores from the window-blocked copy (N in {32, 64}).  split_products == false:
 // one pass of bf16 products; true: fp32 products rebuilt from three bf16 passes (hi*hi + hi*lo + lo*hi).

@@ -228,15 +228,15 @@ cb200_status dispatch_n(const fwd_params &p, bool vector_ok, cudaStream_t stream
 
 cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                  std::int64_t row_end, fwd_schedule schedule, const void *persistent,
-                                 const blocked_layout *blocked, void *workspace, std::uint64_t workspace_bytes, int sm_count,
-                                 cudaStream_t stream) {
+                                 const blocked_layout *blocked, bool split_products, void *workspace,
+                                 std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream) {
     if (row_end <= row_begin || d.n == 0) return CB200_STATUS_SUCCESS;
     if (row_end - row_begin > 0x7fffffffll) return fail(CB200_STATUS_INVALID_SHAPE, "row range too large for one launch");
     if (schedule == fwd_schedule::tensor_blocked && blocked != nullptr) {
         // a row range that does not start on a group boundary runs the exact gene-tiled kernel below
         bool taken = false;
         const cb200_status st = launch_qcsr_forward_blocked(x, d, row_begin, row_end, workspace, workspace_bytes, *blocked,
-                                                            sm_count, stream, &taken);
+                                                            split_products, sm_count, stream, &taken);
         if (st != CB200_STATUS_SUCCESS || taken) return st;
     }
     if (schedule == fwd_schedule::tensor_windows) {

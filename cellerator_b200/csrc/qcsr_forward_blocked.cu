@@ -189,6 +189,7 @@ struct blocked_params {
     int windows;
     float alpha, beta;
     int *status;
+    int value_part; // 0: the tile holds hi = bf16(value); 1: lo = bf16(value - hi)
 };
 
 __device__ __forceinline__ std::uint32_t smem_addr(const void *p) { return static_cast<std::uint32_t>(__cvta_generic_to_shared(p)); }
@@ -285,8 +286,10 @@ __device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
 
 // W [genes][n] (leading dimension ld) -> one record per window of 128 genes: the n x 128 slice of
 // W^T in operand layout (byte offset of (column c, gene e) = (c/8)*2048 + (e/8)*128 + (c%8)*16 +
-// (e%8)*2, zero for genes >= cols) followed by 128 x {scale, zero-point}.
-__global__ void __launch_bounds__(256) pack_windows_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
+// (e%8)*2, zero for genes >= cols) followed by 128 x {scale, zero-point}.  part 0 writes
+// hi = bf16(w) (w itself for a bf16 W); part 1 writes lo = bf16(w - hi), the next 8 mantissa bits.
+template<typename WT>
+__global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int64_t ld, std::int64_t cols, int n, int part,
                                                            const float *scales, const float *offsets, int per_gene_offsets,
                                                            unsigned char *records) {
     const std::int64_t window = blockIdx.x;
@@ -295,7 +298,13 @@ __global__ void __launch_bounds__(256) pack_windows_kernel(const __nv_bfloat16 *
     for (int i = threadIdx.x; i < n * kWin; i += blockDim.x) {
         const int e = i / n, c = i % n; // consecutive threads read consecutive columns of one gene
         const std::int64_t gene = window * kWin + e;
-        const __nv_bfloat16 v = gene < cols ? w[gene * ld + c] : __float2bfloat16(0.0f);
+        float value = 0.0f;
+        if (gene < cols) {
+            if constexpr (sizeof(WT) == 2) value = __bfloat162float(w[gene * ld + c]);
+            else value = w[gene * ld + c];
+        }
+        __nv_bfloat16 v = __float2bfloat16_rn(value);
+        if (part != 0) v = __float2bfloat16_rn(value - __bfloat162float(v));
         wt[((c >> 3) * kRowGroupBytes + (e >> 3) * 128 + (c & 7) * 16 + (e & 7) * 2) >> 1] = v;
     }
     float2 *table = reinterpret_cast<float2 *>(rec + n * kWin * 2);
@@ -420,7 +429,9 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                             const float value = fmaf(static_cast<float>(e[k] & 0xffu), t[k].x, add);
                             // padding words (top bit set) are stored to a scratch slot instead of branching
                             unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + off : scratch_slot;
-                            *reinterpret_cast<__nv_bfloat16 *>(dst) = __float2bfloat16_rn(value);
+                            __nv_bfloat16 bv = __float2bfloat16_rn(value);
+                            if (p.value_part != 0) bv = __float2bfloat16_rn(value - __bfloat162float(bv)); // the next 8 mantissa bits
+                            *reinterpret_cast<__nv_bfloat16 *>(dst) = bv;
                         }
                     }
                     __syncwarp();
@@ -580,7 +591,7 @@ std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n) {
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype) {
     if (bits != 8 && bits != 4) return false;
     if (n != 32 && n != 64 && n != 128) return false;
-    if (dense_dtype != CB200_DTYPE_BF16) return false;
+    if (dense_dtype != CB200_DTYPE_BF16 && dense_dtype != CB200_DTYPE_F32) return false; // fp32 W: split products only
     if (rows <= 0 || cols <= 0 || cols > 0x7fffffff - kWin) return false;
     const std::int64_t groups = (rows + kRows - 1) / kRows, windows = (cols + kWin - 1) / kWin;
     return groups * windows < (static_cast<std::int64_t>(1) << 31);
@@ -652,10 +663,13 @@ cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out) {
 
 cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                          std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
-                                         const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken) {
+                                         const blocked_layout &layout, bool split_products, int sm_count,
+                                         cudaStream_t stream, bool *taken) {
     *taken = false;
     if (layout.seg_ptr == nullptr || row_end <= row_begin) return CB200_STATUS_SUCCESS;
     if (!qcsr_blocked_shape_ok(x.rows, x.cols, d.n, x.bits, d.dense_dtype)) return CB200_STATUS_SUCCESS;
+    const bool w_bf16 = d.dense_dtype == CB200_DTYPE_BF16;
+    if (!w_bf16 && !split_products) return CB200_STATUS_SUCCESS; // one bf16 pass over an fp32 W is never asked for
     if (row_begin % kRows != 0) return CB200_STATUS_SUCCESS; // a launch starts on a group boundary, else another kernel runs
     if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return CB200_STATUS_SUCCESS;
     if (workspace == nullptr || workspace_bytes < qcsr_blocked_workspace_bytes(x.cols, d.n)) return CB200_STATUS_SUCCESS;
@@ -667,23 +681,50 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
     const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
     CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    pack_windows_kernel<<<static_cast<unsigned>(layout.windows), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), x.scales, x.offsets,
-        row_policy ? 0 : 1, records);
-    count_launch();
-    CB200_CUDA_OK(cudaGetLastError());
 
     blocked_params p{};
     p.entries = layout.entries; p.seg_ptr = layout.seg_ptr; p.row_offsets = row_policy ? x.offsets : nullptr;
     p.records = records; p.y = d.out; p.y_ld = d.out_ld; p.row_end = row_end;
     p.group_begin = row_begin / kRows; p.group_end = (row_end + kRows - 1) / kRows; p.windows = layout.windows;
-    p.alpha = d.alpha; p.beta = d.beta; p.status = status;
+    p.alpha = d.alpha; p.status = status;
     *taken = true;
-    switch (d.n) {
-    case 32: return launch_one<32>(p, sm_count, stream);
-    case 64: return launch_one<64>(p, sm_count, stream);
-    default: return launch_one<128>(p, sm_count, stream);
+    // One pass multiplies bf16(value) with bf16 W.  With split products the fp32 product is rebuilt
+    // from bf16 pieces, value = hi + lo and (fp32 W) W = hi + lo:  bf16 W: hi*w + lo*w (two passes, exact
+    // up to the 2^-17 of the value that lo leaves);  fp32 W: hi*hi + hi*lo + lo*hi (three passes,
+    // ~3 * 2^-17 per product).  The passes run back to back on the stream, share the record buffer and
+    // accumulate into Y (beta of the call on the first pass, 1 afterwards); every pass sums a row in
+    // the same fixed order, so the result is repeatable.
+    struct pass_spec { int w_part, value_part; };
+    const pass_spec plain[1] = {{0, 0}}, split_bf16[2] = {{0, 0}, {0, 1}}, split_f32[3] = {{0, 0}, {1, 0}, {0, 1}};
+    const pass_spec *passes = !split_products ? plain : (w_bf16 ? split_bf16 : split_f32);
+    const int pass_count = !split_products ? 1 : (w_bf16 ? 2 : 3);
+    int packed_part = -1;
+    for (int i = 0; i < pass_count; ++i) {
+        if (passes[i].w_part != packed_part) {
+            const unsigned grid = static_cast<unsigned>(layout.windows);
+            if (w_bf16)
+                pack_windows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld,
+                                                                              x.cols, static_cast<int>(d.n), passes[i].w_part, x.scales,
+                                                                              x.offsets, row_policy ? 0 : 1, records);
+            else
+                pack_windows_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float *>(d.dense), d.dense_ld, x.cols,
+                                                                      static_cast<int>(d.n), passes[i].w_part, x.scales, x.offsets,
+                                                                      row_policy ? 0 : 1, records);
+            count_launch();
+            CB200_CUDA_OK(cudaGetLastError());
+            packed_part = passes[i].w_part;
+        }
+        p.value_part = passes[i].value_part;
+        p.beta = i == 0 ? d.beta : 1.0f;
+        cb200_status st;
+        switch (d.n) {
+        case 32: st = launch_one<32>(p, sm_count, stream); break;
+        case 64: st = launch_one<64>(p, sm_count, stream); break;
+        default: st = launch_one<128>(p, sm_count, stream); break;
+        }
+        if (st != CB200_STATUS_SUCCESS) return st;
     }
+    return CB200_STATUS_SUCCESS;
 }
 
 } // namespace cb200

@@ -220,11 +220,12 @@ typedef struct cb200_spmm_problem {
      * (CSR forward with bf16 W: schedules "tensor_windows" / "tensor_blocked"; transpose with the
      * matrix handed to prepare: "tensor_blocked", which rounds the fp32 G to bf16 as well;
      * Blocked-ELL with bf16 W always does).
-     * Transpose with fp32 products requested AND the matrix handed to prepare: schedule
-     * "tensor_blocked_x3" rebuilds each fp32 product from three bf16 tensor-core passes (value and G
-     * split into hi + lo; hi*hi + hi*lo + lo*hi), relative error about 3 * 2^-17 per product: inside
-     * the 1e-4 bound of an fp32 G, not bit-equal to an fp32 multiply.  Without device_matrix the
-     * fp32-FMA kernel ("vector_reductions") runs. */
+     * fp32 products requested AND the matrix handed to prepare (dense enough): schedules
+     * "tensor_blocked_x2" (forward, bf16 W) / "tensor_blocked_x3" (forward with fp32 W; transpose)
+     * rebuild each fp32 product from bf16 tensor-core passes (value = hi + lo, fp32 dense operand =
+     * hi + lo; hi*hi + hi*lo + lo*hi), relative error about 3 * 2^-17 per product: inside the 1e-4
+     * bound of an fp32 operand, not bit-equal to an fp32 multiply.  Without device_matrix the fp32-FMA
+     * kernels ("gene_tiled" / "warp_per_row", "vector_reductions") run. */
     int32_t multiply;
     /* Optional: the device-resident matrix itself (arrays on `device`, final contents).  With bf16
      * products allowed, prepare then builds a persistent window-blocked copy of it (one 32-bit

@@ -167,3 +167,39 @@ def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule
         assert_tensor_close(y1[r0:r1].cpu().numpy(), ref, l1s, wmax)
     op.close()
     exact.close()
+
+
+@pytest.mark.parametrize("dtype,expected", [(torch.bfloat16, "tensor_blocked_x2"), (torch.float32, "tensor_blocked_x3")])
+@pytest.mark.parametrize("bits,n,policy", [(8, 64, 1), (4, 128, 2), (8, 32, 2)])
+def test_split_products_meet_the_fp32_bound(cuda_device, oracle, monkeypatch, dtype, expected, bits, n, policy):
+    """fp32 products requested and the matrix handed to prepare: the tensor-core kernel rebuilds each
+    product from bf16 pieces (two passes for a bf16 W, three for an fp32 W) and meets the bound of
+    the exact kernels, 1e-4 * ||row||_1 * max|W|; repeatable, alpha / beta, row ranges."""
+    from gpu_util import assert_forward_close
+    monkeypatch.setenv("CB200_FWD_SCHEDULE", "tensor_blocked")
+    rng = np.random.default_rng(5 * bits + n + policy)
+    rows, cols = 256 * 3 + 99, 900
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=260, bits=bits, policy=policy))
+    x = to_dev(c, cuda_device)
+    w, w_host = dense(rng, cols, n, dtype, cuda_device)
+    op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, bits, policy, w.dtype, cuda_device,
+                          host_row_ptr=x.host_row_ptr, device_matrix=x)
+    assert op.schedule == expected
+    y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0
+    ref = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
+                              c["offsets"], w_host, cols)
+    l1, _ = row_l1(oracle, c)
+    wmax = float(np.abs(w_host).max())
+    assert_forward_close(y.cpu().numpy(), ref, l1, wmax, bf16=dtype == torch.bfloat16)
+    err = np.abs(y.cpu().numpy().astype(np.float64) - ref) / (l1[:, None] * wmax + 1e-30)
+    assert err.max() < 3e-5
+    assert torch.equal(y, op.run(x, w, torch.empty_like(y)))
+    y0 = torch.from_numpy(rng.normal(size=(rows, n)).astype(np.float32)).to(cuda_device)
+    y1 = op.run(x, w, y0.clone(), alpha=2.0, beta=0.5)
+    assert torch.allclose(y1, 2.0 * y + 0.5 * y0, rtol=1e-5, atol=1e-5)
+    out = torch.full((rows, n), -3.0, device=cuda_device)
+    op.run(x, w, out, row_begin=256, row_end=700)
+    assert torch.equal(out[256:700], y[256:700]) and torch.all(out[:256] == -3.0) and torch.all(out[700:] == -3.0)
+    op.close()
