@@ -19,9 +19,9 @@
 // a (group, window) segment is contiguous, so the copy engine streams it into shared memory and
 // every lane of the CTA decodes entries, four at a time, with no divergence.
 //
-// Structure of a CTA (672 threads, one CTA per SM, row groups dealt round-robin):
+// Structure of a CTA (608 threads, one CTA per SM, row groups dealt round-robin):
 //   warps 0-15  zero the A tile (128-byte swizzled K-major layout), wait for the segment's chunks
-//               (8 KB each, 3-stage ring), decode and scatter; later thread t < 256 owns TMEM lane t:
+//               (8 KB each, 2-stage ring), decode and scatter; later thread t < 256 owns TMEM lane t:
 //               row t of the group, and writes that row of Y;
 //   warp 16     one thread issues the MMAs (2 row sub-blocks x 8 K-steps per window), commits the
 //               window to the "A tile free" and "W stage free" barriers, the last window of a group
@@ -29,7 +29,8 @@
 //   warp 17     one thread feeds the W ring with bulk async copies: W slices, re-laid per window
 //               into the K-major core-matrix operand layout by a small kernel before the main one,
 //               each followed by the window's {scale, zero-point} table;
-//   warps 18-20 one thread each feeds the entry-chunk ring (chunks are dealt to them in turn).
+//   warp 18     one thread feeds the entry-chunk ring (the code deals chunks to kChunkLoaders such warps
+//               in turn; one measured best).
 // Every barrier wait is bounded; on a time-out a status word is raised, waits stop blocking, and
 // the kernel runs to completion and frees its TMEM.  A non-zero status means Y is not valid.
 //
@@ -55,24 +56,26 @@ constexpr int kSubBlocks = kRows / 128;      // one M = 128 MMA each
 constexpr int kProducerWarps = 16;           // zero + scatter; the first kEpilogueWarps of them also write Y
 constexpr int kEpilogueWarps = kRows / 32;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kChunkLoaders = 3;                // warps whose elected lane issues entry-chunk copies
+// Measured on the 1M x 33,538 matrix (ms per launch) for (chunk loader warps, chunk stages): (1, 2) 7.11,
+// (2, 2) 7.13, (1, 3) 7.36, (2, 4) 7.38, (3, 3) 7.55, (1, 1) 8.96; W stages 4 / 3 / 2: 7.13 / 7.38 / 7.68.
+constexpr int kChunkLoaders = 1;                // warps whose elected lane issues entry-chunk copies
 constexpr int kThreads = kProducerThreads + 32 * (2 + kChunkLoaders); // + MMA warp + W loader warp + chunk loader warps
 constexpr int kABufBytes = kRows * kWin * 2;    // 64 KB
 constexpr int kSubBlockBytes = 128 * kWin * 2;  // 16 KB
 constexpr int kRowGroupBytes = kWin * 16;       // W slice: 8 columns x kWin genes of bf16
 constexpr int kChunkEntries = 2048;
 constexpr int kChunkBytes = kChunkEntries * 4;
-constexpr int kChunkStages = 3;                // a multiple of kChunkLoaders: a loader always refills the same stages
+// chunk stages (template parameter CS of the kernel): 2 when a segment fits one chunk, 3 for denser matrices
 constexpr int kMaxWStages = 6;
 constexpr std::uint32_t kInvalidEntry = 0x80000000u; // padding of a segment
 static_assert(kProducerWarps >= kEpilogueWarps && kABufBytes % (kProducerThreads * 16) == 0, "thread t < kRows owns row t in the epilogue");
 static_assert(kABufBytes <= 65536, "an entry holds the byte position in the tile, halved, in 15 bits");
 
 __host__ __device__ constexpr int record_bytes(int n) { return n * kWin * 2 + kWin * 8; }
-__host__ __device__ constexpr int fixed_smem_bytes() { return 2 * kABufBytes + kChunkStages * kChunkBytes + kRows * 4 + 512; }
-__host__ __device__ constexpr int w_stages(int n) {
-    return (232448 - fixed_smem_bytes()) / record_bytes(n) >= kMaxWStages ? kMaxWStages
-                                                                          : (232448 - fixed_smem_bytes()) / record_bytes(n);
+__host__ __device__ constexpr int fixed_smem_bytes(int cs) { return 2 * kABufBytes + cs * kChunkBytes + kRows * 4 + 512; }
+__host__ __device__ constexpr int w_stages(int n, int cs) {
+    return (232448 - fixed_smem_bytes(cs)) / record_bytes(n) >= kMaxWStages ? kMaxWStages
+                                                                            : (232448 - fixed_smem_bytes(cs)) / record_bytes(n);
 }
 
 // Byte position of (row within group, gene within window) in the A tile.  The tile is made of
@@ -319,27 +322,27 @@ __global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int
     }
 }
 
-template<int NC>
+template<int NC, int CS>
 __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blocked_params p) {
     constexpr int REC = record_bytes(NC);
-    constexpr int STAGES = w_stages(NC);
+    constexpr int STAGES = w_stages(NC, CS);
     constexpr int kTmemCols = kSubBlocks * NC < 32 ? 32 : kSubBlocks * NC; // one accumulator per row sub-block
     constexpr std::uint32_t IDESC = instr_desc(NC);
     extern __shared__ __align__(1024) unsigned char smem[];
-    // [2][A tile] | [STAGES][W record] | [kChunkStages][entry chunk] | row offsets | barriers | chunk meta | tmem | abort
+    // [2][A tile] | [STAGES][W record] | [CS][entry chunk] | row offsets | barriers | chunk meta | tmem | abort
     unsigned char *chunk_base = smem + 2 * kABufBytes + STAGES * REC;
-    float *row_offset_s = reinterpret_cast<float *>(chunk_base + kChunkStages * kChunkBytes);
+    float *row_offset_s = reinterpret_cast<float *>(chunk_base + CS * kChunkBytes);
     std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(row_offset_s + kRows);
     std::uint64_t *a_full = bars;                      // [2]            scatter warps -> MMA (one arrival per warp)
     std::uint64_t *a_empty = bars + 2;                 // [2]            MMA commit -> scatter warps
     std::uint64_t *w_full = bars + 4;                  // [STAGES]       copy engine -> MMA, scatter warps
     std::uint64_t *w_empty = w_full + STAGES;          // [STAGES]       MMA commit -> loader
-    std::uint64_t *c_full = w_empty + STAGES;          // [kChunkStages] copy engine -> scatter warps
-    std::uint64_t *c_empty = c_full + kChunkStages;    // [kChunkStages] scatter warps -> loader (one arrival per warp)
-    std::uint64_t *acc_full = c_empty + kChunkStages;  // MMA commit -> scatter warps
+    std::uint64_t *c_full = w_empty + STAGES;          // [CS] copy engine -> scatter warps
+    std::uint64_t *c_empty = c_full + CS;    // [CS] scatter warps -> loader (one arrival per warp)
+    std::uint64_t *acc_full = c_empty + CS;  // MMA commit -> scatter warps
     std::uint64_t *acc_empty = acc_full + 1;           // scatter warps -> MMA (one arrival per warp)
-    volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [kChunkStages] (entries << 1) | last chunk of its window
-    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + kChunkStages + 1);
+    volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [CS] (entries << 1) | last chunk of its window
+    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + CS + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
 
@@ -357,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
             bar_init(smem_addr(w_full + s), 1);
             bar_init(smem_addr(w_empty + s), 1);
         }
-        for (int s = 0; s < kChunkStages; ++s) {
+        for (int s = 0; s < CS; ++s) {
             bar_init(smem_addr(c_full + s), 1);
             bar_init(smem_addr(c_empty + s), kProducerWarps);
         }
@@ -408,8 +411,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                 bool last = false;
                 int guard = 0;
                 while (!last && ++guard < (1 << 20)) {
-                    const int cs = static_cast<int>(qc % kChunkStages);
-                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kChunkStages) & 1), abort_flag);
+                    const int cs = static_cast<int>(qc % CS);
+                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / CS) & 1), abort_flag);
                     const int meta = chunk_meta[cs];
                     const int count = *abort_flag != 0 ? 0 : (meta >> 1);
                     last = (meta & 1) != 0 || *abort_flag != 0;
@@ -533,8 +536,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                         do {
                             const int count = static_cast<int>(min(static_cast<std::int64_t>(kChunkEntries), hi - at));
                             if (lane == 0 && qc % kChunkLoaders == mine_mod) {
-                                const int cs = static_cast<int>(qc % kChunkStages);
-                                bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / kChunkStages) & 1) ^ 1), abort_flag);
+                                const int cs = static_cast<int>(qc % CS);
+                                bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / CS) & 1) ^ 1), abort_flag);
                                 chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
                                 if (count > 0) {
                                     bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(count) * 4u);
@@ -562,23 +565,31 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
     if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-template<int NC> constexpr std::size_t blocked_smem_bytes() {
-    return 2 * kABufBytes + w_stages(NC) * record_bytes(NC) + kChunkStages * kChunkBytes + kRows * 4 +
-           (6 + 2 * w_stages(NC) + 2 * kChunkStages) * sizeof(std::uint64_t) + (kChunkStages + 1) * 4 + 16;
+template<int NC, int CS> constexpr std::size_t blocked_smem_bytes() {
+    return 2 * kABufBytes + w_stages(NC, CS) * record_bytes(NC) + CS * kChunkBytes + kRows * 4 +
+           (6 + 2 * w_stages(NC, CS) + 2 * CS) * sizeof(std::uint64_t) + (CS + 1) * 4 + 16;
 }
 
-template<int NC>
-cb200_status launch_one(const blocked_params &p, int sm_count, cudaStream_t stream) {
-    constexpr std::size_t smem = blocked_smem_bytes<NC>();
+template<int NC, int CS>
+cb200_status launch_cs(const blocked_params &p, int sm_count, cudaStream_t stream) {
+    constexpr std::size_t smem = blocked_smem_bytes<NC, CS>();
     static_assert(smem <= 232448, "shared memory budget");
-    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    static_assert(CS % kChunkLoaders == 0, "a loader always refills the same stages");
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked_kernel<NC, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
     const std::int64_t groups = p.group_end - p.group_begin;
     const unsigned grid = static_cast<unsigned>(groups < sm_count ? groups : sm_count);
-    qcsr_fwd_blocked_kernel<NC><<<grid, kThreads, smem, stream>>>(p);
+    qcsr_fwd_blocked_kernel<NC, CS><<<grid, kThreads, smem, stream>>>(p);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
+}
+
+// Two chunk stages when a segment normally fits one 8 KB chunk (measured best on the 5 %-dense
+// 33,538-gene matrix), three when segments span several chunks (the 17 %-dense 4,000-gene one).
+template<int NC>
+cb200_status launch_one(const blocked_params &p, bool long_segments, int sm_count, cudaStream_t stream) {
+    return long_segments ? launch_cs<NC, 3>(p, sm_count, stream) : launch_cs<NC, 2>(p, sm_count, stream);
 }
 
 } // namespace
@@ -717,10 +728,11 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
         p.value_part = passes[i].value_part;
         p.beta = i == 0 ? d.beta : 1.0f;
         cb200_status st;
+        const bool long_segments = layout.total_entries > static_cast<std::int64_t>(kChunkEntries) * layout.groups * layout.windows;
         switch (d.n) {
-        case 32: st = launch_one<32>(p, sm_count, stream); break;
-        case 64: st = launch_one<64>(p, sm_count, stream); break;
-        default: st = launch_one<128>(p, sm_count, stream); break;
+        case 32: st = launch_one<32>(p, long_segments, sm_count, stream); break;
+        case 64: st = launch_one<64>(p, long_segments, sm_count, stream); break;
+        default: st = launch_one<128>(p, long_segments, sm_count, stream); break;
         }
         if (st != CB200_STATUS_SUCCESS) return st;
     }

@@ -22,9 +22,9 @@
 // vector reductions (the (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so
 // several CTAs contribute to the same genes; G' is first scaled by beta by a small kernel).
 //
-// Structure of a CTA (672 threads, one CTA per SM): warps 0-15 zero, decode and scatter, and read
+// Structure of a CTA (608 threads, one CTA per SM): warps 0-15 zero, decode and scatter, and read
 // the accumulators back at the end of a run; warp 16 issues the MMAs; warp 17 feeds the G ring (2
-// stages of 32 KB); warps 18-20 feed the entry-chunk ring.  Every barrier wait is bounded; on a
+// stages of 32 KB); warp 18 feeds the entry-chunk ring (2 stages of 8 KB).  Every barrier wait is bounded; on a
 // time-out a status word is raised, waits stop blocking, and the kernel runs to completion and frees
 // its TMEM.  A non-zero status means G' is not valid.
 #include "kernels.cuh"
@@ -40,14 +40,14 @@ constexpr int kRows = 256;                    // cells per group (as in the bloc
 constexpr int kSetWindows = 8;                // windows whose accumulators a CTA holds in TMEM
 constexpr int kProducerWarps = 16;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kChunkLoaders = 3;
+constexpr int kChunkLoaders = 1;
 constexpr int kThreads = kProducerThreads + 32 * (2 + kChunkLoaders);
 constexpr int kTileBytes = kWin * kRows * 2;  // 64 KB: [cell quarter][gene][64 cells]
 constexpr int kQuarterBytes = kWin * 128;     // 16 KB: 128 genes x 64 cells
 constexpr int kGStages = 2;
 constexpr int kChunkEntries = 2048;
 constexpr int kChunkBytes = kChunkEntries * 4;
-constexpr int kChunkStages = 3;
+constexpr int kChunkStages = 2;
 
 __host__ __device__ constexpr int g_record_bytes(int n) { return kRows * n * 2; }
 
