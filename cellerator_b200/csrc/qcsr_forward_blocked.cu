@@ -103,49 +103,52 @@ __device__ __forceinline__ unsigned load_code(const std::uint8_t *row_bytes, std
     }
 }
 
-// One thread per row walks its entries; a run is a maximal stretch of consecutive entries in one
-// gene window (rows with ascending genes have one run per window they touch).  FILL == false adds
-// the run lengths to counts[group * windows + window]; FILL == true reserves the run's place in
-// the segment with one atomic and writes its entries.  Entries with a gene outside [0, cols) are
-// left out by both passes.
+// One warp per row; the lanes read 32 consecutive entries at a time (coalesced).  A run is a
+// maximal stretch of consecutive entries, within those 32, in one gene window (rows with ascending
+// genes have one run per window they touch, plus one where a window straddles two reads).  The first
+// lane of a run speaks for it: FILL == false adds the run length to counts[group * windows + window];
+// FILL == true reserves the run's place in the segment with one atomic, and every lane of the run
+// writes its entry there.  Entries with a gene outside [0, cols) are left out by both passes.
 template<int BITS, bool FILL>
 __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *row_ptr, const std::int64_t *packed_row_ptr,
                                                            const std::int32_t *col_idx, const std::uint8_t *packed,
                                                            std::int64_t rows, std::int64_t cols, int windows,
                                                            unsigned *counts, unsigned long long *cursor, std::uint32_t *entries) {
-    const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return; // warp-uniform
     const std::int64_t group = r >> kRowsShift;
     const int rl = static_cast<int>(r & (kRows - 1));
     const std::int64_t begin = row_ptr[r], end = row_ptr[r + 1];
     const std::uint8_t *row_bytes = packed + (packed_row_ptr != nullptr ? packed_row_ptr[r] : begin);
-    std::int64_t run_start = begin;
-    int run_window = -1;
-    auto close_run = [&](std::int64_t run_end) {
-        const std::int64_t length = run_end - run_start;
-        if (run_window < 0 || length <= 0) return;
-        const std::int64_t seg = group * windows + run_window;
-        if constexpr (!FILL) {
-            atomicAdd(counts + seg, static_cast<unsigned>(length));
-        } else {
-            std::uint32_t *dst = entries + atomicAdd(cursor + seg, static_cast<unsigned long long>(length));
-            for (std::int64_t i = run_start; i < run_end; ++i) {
-                const int gl = col_idx[i] & (kWin - 1);
-                dst[i - run_start] = load_code<BITS>(row_bytes, i - begin) | (static_cast<std::uint32_t>(gl) << 8) |
-                                     ((tile_offset(rl, gl) >> 1) << 15);
-            }
+    for (std::int64_t base = begin; base < end; base += 32) {
+        const std::int64_t i = base + lane;
+        int window = -2; // past the row's end
+        int gl = 0;
+        if (i < end) {
+            const std::int64_t gene = col_idx[i];
+            window = (gene >= 0 && gene < cols) ? static_cast<int>(gene >> kWinShift) : -1;
+            gl = static_cast<int>(gene & (kWin - 1));
         }
-    };
-    for (std::int64_t i = begin; i < end; ++i) {
-        const std::int64_t gene = col_idx[i];
-        const int window = (gene >= 0 && gene < cols) ? static_cast<int>(gene >> kWinShift) : -1;
-        if (window != run_window) {
-            close_run(i);
-            run_window = window;
-            run_start = i;
+        const int before = __shfl_up_sync(0xffffffffu, window, 1);
+        const bool head = lane == 0 || window != before;
+        const unsigned heads = __ballot_sync(0xffffffffu, head);
+        const int start = 31 - __clz(static_cast<int>(heads & (0xffffffffu >> (31 - lane)))); // first lane of this lane's run
+        const unsigned later = lane == 31 ? 0u : (heads >> (lane + 1)) << (lane + 1);         // run heads after this lane
+        const int next = later != 0u ? __ffs(static_cast<int>(later)) - 1 : 32;
+        unsigned long long place = 0;
+        if (head && window >= 0) {
+            const std::int64_t seg = group * windows + window;
+            if constexpr (!FILL) atomicAdd(counts + seg, static_cast<unsigned>(next - lane));
+            else place = atomicAdd(cursor + seg, static_cast<unsigned long long>(next - lane));
+        }
+        if constexpr (FILL) {
+            place = __shfl_sync(0xffffffffu, place, start);
+            if (window >= 0)
+                entries[place + static_cast<unsigned>(lane - start)] =
+                    load_code<BITS>(row_bytes, i - begin) | (static_cast<std::uint32_t>(gl) << 8) | ((tile_offset(rl, gl) >> 1) << 15);
         }
     }
-    close_run(end);
 }
 
 // seg_ptr[i] = sum of counts[0..i) rounded up to multiples of 4 (16-byte segments for the copy
@@ -630,7 +633,7 @@ cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out) {
     if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&cursor), static_cast<std::size_t>(segments) * sizeof(unsigned long long));
     if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->seg_ptr), static_cast<std::size_t>(segments + 1) * sizeof(std::int64_t));
     if (err == cudaSuccess) err = cudaMemset(counts, 0, static_cast<std::size_t>(segments) * sizeof(unsigned));
-    const unsigned grid = static_cast<unsigned>((x.rows + 255) / 256);
+    const unsigned grid = static_cast<unsigned>((x.rows + 7) / 8); // one warp per row, 8 rows per block
     std::int64_t total = 0;
     if (err == cudaSuccess) {
         if (x.bits == 8)
