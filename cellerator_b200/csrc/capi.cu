@@ -399,7 +399,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
                 delete p;
                 return st;
             }
-            if (p->schedule != fwd_schedule::tensor_windows) tiled = true; // the fallback for unaligned row ranges
+            tiled = false; // no length-sorted row order: the copy works in natural row order, and the
+                           // exact kernel that serves unaligned row ranges runs in natural order too
             p->schedule = fwd_schedule::tensor_blocked;
             p->schedule_name = !split ? "tensor_blocked"
                                       : (problem->dense_dtype == CB200_DTYPE_BF16 ? "tensor_blocked_x2" : "tensor_blocked_x3");
