@@ -520,13 +520,18 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
     // per product about 3 * 2^-17, inside the 1e-4 bound of an fp32 dense operand.  The passes run
     // back to back on the stream, share the record buffer and add into the same G'.
     const int passes = split_products ? 3 : 1;
-    for (int pass = 0; pass < passes; ++pass) {
-        const int g_part = pass == 1 ? 1 : 0;
-        p.value_part = pass == 2 ? 1 : 0;
-        pack_g_kernel<<<static_cast<unsigned>(group_end - group_begin), 256, 0, stream>>>(
-            static_cast<const float *>(d.dense), d.dense_ld, static_cast<int>(d.n), row_begin, row_end, group_begin, g_part, records);
-        count_launch();
-        CB200_CUDA_OK(cudaGetLastError());
+    int packed_part = -1;
+    for (int pass = 0; pass < passes; ++pass) { // (G hi, value hi), (G hi, value lo), (G lo, value hi): G hi is packed once
+        const int g_part = pass == 2 ? 1 : 0;
+        p.value_part = pass == 1 ? 1 : 0;
+        if (g_part != packed_part) {
+            pack_g_kernel<<<static_cast<unsigned>(group_end - group_begin), 256, 0, stream>>>(
+                static_cast<const float *>(d.dense), d.dense_ld, static_cast<int>(d.n), row_begin, row_end, group_begin, g_part,
+                records);
+            count_launch();
+            CB200_CUDA_OK(cudaGetLastError());
+            packed_part = g_part;
+        }
         const cb200_status st = d.n == 64 ? launch_one<64>(p, sm_count, stream) : launch_one<32>(p, sm_count, stream);
         if (st != CB200_STATUS_SUCCESS) return st;
     }
