@@ -115,7 +115,8 @@ def algorithmic_bytes(kind, m, k, n, nnz, bits, dense_bytes):
     return nnz * (bits / 8 + 4) + (m + 1) * 8 + m * n * 4 + k * n * dense_bytes + k * 8
 
 
-def build_workload(name, device, rank, world, seed=0, rows_override=None, multiply="bf16", prepare_matrix=True):
+def build_workload(name, device, rank, world, seed=0, rows_override=None, multiply="bf16", prepare_matrix=True,
+                   persistent_limit_bytes=0):
     import torch
 
     from cellerator_b200 import capi, ops, synth
@@ -177,7 +178,7 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype, device,
                               host_row_ptr=x.host_row_ptr,
                               multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
-                              device_matrix=x if prepare_matrix else None)
+                              device_matrix=x if prepare_matrix else None, persistent_limit_bytes=persistent_limit_bytes)
         kind, dbytes = "forward", 2
     torch.cuda.synchronize(device)
     wl.update(x=x, dense=dense, out=out, op=op, units=x.nnz, kind=kind, n=n,
@@ -279,7 +280,8 @@ def run_ours(args):
     if args.multiply is None:  # what the contract's tolerance for the workload's dense operand allows
         args.multiply = "f32" if args.workload == "c3_transpose" else "bf16"
     wl = build_workload(args.workload, device, rank, world, rows_override=args.rows, multiply=args.multiply,
-                        prepare_matrix=not args.no_prepare_matrix)
+                        prepare_matrix=not args.no_prepare_matrix,
+                        persistent_limit_bytes=int(args.persistent_limit_gb * 1e9))
     op, x, dense, out = wl["op"], wl["x"], wl["dense"], wl["out"]
     launch = op.make_launch(x, dense, out)
     L = capi.lib()
@@ -375,7 +377,7 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": f"u{x.bits} codes -> " + ("bf16 products (tcgen05), f32 accumulate"
-                                           if op.schedule in ("tensor_windows", "tensor_blocked", "tcgen05_block_rows")
+                                           if op.schedule in ("tensor_windows", "tensor_blocked", "tensor_dense", "tcgen05_block_rows")
                                            else "split bf16 products (tcgen05, %s passes), f32 accumulate" % op.schedule[-1]
                                            if op.schedule in ("tensor_blocked_x2", "tensor_blocked_x3")
                                            else "f32 products, f32 accumulate"),
@@ -487,6 +489,9 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override cells per GPU (profiling on a small case)")
     ap.add_argument("--no-prepare-matrix", action="store_true",
                     help="do not hand the matrix to prepare: no window-blocked copy, CSR-only schedules")
+    ap.add_argument("--persistent-limit-gb", type=float, default=0.0,
+                    help="device memory prepare may keep per GPU (0 = no limit); below rows x genes x 2 bytes the forward "
+                         "projection keeps the window-blocked copy (tensor_blocked) instead of dense tiles (tensor_dense)")
     ap.add_argument("--multiply", default=None, choices=["bf16", "f32"],
                     help="products: bf16 (tensor cores; default where the dense operand is bf16) or exact fp32 "
                          "(CUDA cores; default for the transpose, whose G is fp32)")

@@ -318,7 +318,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         if (blocked) {
             const cb200_qcsr &dm = *problem->device_matrix;
             if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
-                dm.bits != problem->bits) {
+                dm.bits != problem->bits || dm.policy != problem->policy) {
                 delete p;
                 return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
             }
@@ -383,11 +383,14 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
                                 qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype);
         const double min_density = !split ? 0.015 : (problem->dense_dtype == CB200_DTYPE_BF16 ? 0.04 : 0.06);
         bool blocked = blocked_ok && problem->m >= 16 * 256 && p->mean_row_nnz >= min_density * static_cast<double>(problem->k);
-        if (force != nullptr) blocked = blocked_ok && std::strcmp(force, "tensor_blocked") == 0;
+        if (force != nullptr)
+            blocked = blocked_ok && (std::strcmp(force, "tensor_blocked") == 0 || (!split && std::strcmp(force, "tensor_dense") == 0));
+        const std::uint64_t limit = problem->persistent_limit_bytes;
+        if (blocked && limit != 0u && static_cast<std::uint64_t>(problem->nnz) * 4u > limit) blocked = false; // a word per entry
         if (blocked) {
             const cb200_qcsr &dm = *problem->device_matrix;
             if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
-                dm.bits != problem->bits) {
+                dm.bits != problem->bits || dm.policy != problem->policy) {
                 delete p;
                 return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
             }
@@ -405,6 +408,24 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             p->schedule_name = !split ? "tensor_blocked"
                                       : (problem->dense_dtype == CB200_DTYPE_BF16 ? "tensor_blocked_x2" : "tensor_blocked_x3");
             p->workspace_bytes = std::max<std::uint64_t>(qcsr_blocked_workspace_bytes(problem->k, problem->n), 256u);
+            // Dense enough, bf16 products, and room for rows x genes x 2 bytes: keep the decoded operand
+            // tiles instead of the entry words; a launch then streams them and decodes nothing.
+            const std::uint64_t tile_bytes = qcsr_dense_tile_bytes(problem->m, problem->k);
+            std::size_t free_bytes = 0, total_bytes = 0;
+            bool dense = !split && p->mean_row_nnz >= 0.08 * static_cast<double>(problem->k) &&
+                         cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess && tile_bytes <= free_bytes / 2u;
+            if (force != nullptr) dense = !split && std::strcmp(force, "tensor_dense") == 0;
+            if (limit != 0u && tile_bytes > limit) dense = false;
+            if (dense) {
+                bool built = false;
+                st = densify_blocked_layout(view_of(dm), &p->blocked, &built);
+                if (st != CB200_STATUS_SUCCESS) {
+                    free_blocked_layout(&p->blocked);
+                    delete p;
+                    return st;
+                }
+                if (built) p->schedule_name = "tensor_dense";
+            }
             p->persistent_bytes += p->blocked.bytes;
         }
         // The tiled kernel gives each row to one lane group, so a CTA is as slow as its longest row.
@@ -437,7 +458,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
 
 void cb200_prepared_destroy(cb200_prepared *prepared) {
     if (prepared == nullptr) return;
-    if (prepared->row_order != nullptr || prepared->blocked.seg_ptr != nullptr) {
+    if (prepared->row_order != nullptr || prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr) {
         device_scope scope(prepared->problem.device);
         if (prepared->row_order != nullptr) cudaFree(prepared->row_order);
         free_blocked_layout(&prepared->blocked);
@@ -489,8 +510,17 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     if (launch->dense_ld < pr.n || launch->out_ld < pr.n)
         return fail(CB200_STATUS_INVALID_SHAPE, "leading dimension smaller than n");
 
+    /* operation.cc:45-64: the eight epilogue kinds; the bias kinds need a bias vector */
+    if (launch->epilogue < CB200_EPILOGUE_NONE || launch->epilogue > CB200_EPILOGUE_BIAS_GELU_TANH)
+        return fail(CB200_STATUS_UNSUPPORTED, "unknown epilogue kind %d", launch->epilogue);
+    const bool bias_kind = launch->epilogue == CB200_EPILOGUE_BIAS || launch->epilogue >= CB200_EPILOGUE_BIAS_RELU;
+    if (bias_kind && launch->bias == nullptr && pr.n != 0)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "epilogue kind %d needs a bias vector", launch->epilogue);
+    if (launch->epilogue != CB200_EPILOGUE_NONE && pr.projection == CB200_PROJECTION_TRANSPOSE)
+        return fail(CB200_STATUS_UNSUPPORTED, "the transpose has no composed epilogue");
+
     dense_args d{launch->dense, launch->dense_ld, pr.dense_dtype, launch->out, launch->out_ld, pr.n,
-                 launch->alpha, launch->beta};
+                 launch->alpha, launch->beta, bias_kind ? launch->bias : nullptr, launch->epilogue};
     cudaStream_t stream = static_cast<cudaStream_t>(launch->stream);
     device_scope scope(launch->device);
     CB200_CUDA_OK(scope.status);

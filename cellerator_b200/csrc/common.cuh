@@ -68,6 +68,26 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&w)[8]) {
     bf16x2_to_f32(a.z, w[4], w[5]);
     bf16x2_to_f32(a.w, w[6], w[7]);
 }
+// Composed epilogue of the forward projections: act(value + bias), the rule of the reference's
+// referee (src/compute/math/referee.cc:81-97).  `value` already holds alpha * product + beta * out.
+__device__ __forceinline__ bool epilogue_has_bias(int kind) {
+    return kind == CB200_EPILOGUE_BIAS || kind >= CB200_EPILOGUE_BIAS_RELU;
+}
+__device__ __forceinline__ float apply_epilogue(float value, float bias, int kind) {
+    if (epilogue_has_bias(kind)) value += bias;
+    if (kind == CB200_EPILOGUE_RELU || kind == CB200_EPILOGUE_BIAS_RELU) return fmaxf(value, 0.0f);
+    if (kind == CB200_EPILOGUE_GELU_ERF || kind == CB200_EPILOGUE_BIAS_GELU_ERF)
+        return 0.5f * value * (1.0f + erff(value * 0.70710678118654752f));
+    if (kind == CB200_EPILOGUE_GELU_TANH || kind == CB200_EPILOGUE_BIAS_GELU_TANH)
+        return 0.5f * value * (1.0f + tanhf(0.79788456080286536f * (value + 0.044715f * value * value * value)));
+    return value;
+}
+// The epilogue of one output element at column `col`; `bias` may be null for kinds without bias.
+__device__ __forceinline__ float finish_output(float value, const float *bias, int col, int kind) {
+    if (kind == CB200_EPILOGUE_NONE) return value;
+    return apply_epilogue(value, epilogue_has_bias(kind) ? __ldg(bias + col) : 0.0f, kind);
+}
+
 __device__ __forceinline__ float load1(const float *p) { return __ldg(p); }
 __device__ __forceinline__ float load1(const __nv_bfloat16 *p) {
     return __uint_as_float(static_cast<std::uint32_t>(__ldg(reinterpret_cast<const unsigned short *>(p))) << 16);

@@ -25,6 +25,8 @@ struct dense_args {
     std::int64_t out_ld;
     std::int64_t n;
     float alpha, beta;
+    const float *bias = nullptr;          // composed epilogue of the forward projections:
+    int epilogue = CB200_EPILOGUE_NONE;   // out = act(alpha * product + beta * out + bias[column])
 };
 
 enum class fwd_schedule : int { warp_per_row = 0, gene_tiled = 1, tensor_windows = 2, tensor_blocked = 3 };
@@ -56,11 +58,19 @@ struct blocked_layout {
     std::int64_t total_entries = 0;
     std::uint64_t bytes = 0;
     const void *src_row_ptr = nullptr, *src_col_idx = nullptr, *src_packed = nullptr; // arrays it was built from
+    // Dense operand tiles (forward, bf16 products): per (group, window) the 64 KB tile of decoded bf16
+    // values in the shared-memory image the MMA reads.  When set, entries / seg_ptr are gone.
+    unsigned char *dense_tiles = nullptr;
+    const void *src_scales = nullptr, *src_offsets = nullptr; // baked into the tiles
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
 cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out); // current device; allocates and synchronises
 void free_blocked_layout(blocked_layout *layout);
+// Dense operand tiles from the window-blocked copy (decoded values of `x` baked in; the entry words
+// are freed).  *built stays false, the copy untouched, when the device has no room.  Synchronises.
+std::uint64_t qcsr_dense_tile_bytes(std::int64_t rows, std::int64_t cols);
+cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, bool *built);
 // *taken is false when the launch cannot use the copy (row range not starting on a group boundary,
 // workspace too small, ...); a matrix other than the one the copy was built from is an error.
 // split_products == false: one pass of bf16 products (bf16 W only); true: fp32 products rebuilt from

@@ -37,6 +37,8 @@ struct bell_params {
     std::int64_t row_begin, row_end;
     int n, policy;
     float alpha, beta;
+    const float *bias;
+    int epilogue;
 };
 
 template<int BITS>
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(256) qbell_fwd_warp_row_kernel(const bell_para
         for (int i = 0; i < 8; ++i) {
             float r = p.alpha * acc[i];
             if (p.beta != 0.0f) r = fmaf(p.beta, out[i], r);
-            out[i] = r;
+            out[i] = finish_output(r, p.bias, col0 + i, p.epilogue);
         }
     }
 }
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(256) qbell_fwd_generic_kernel(const bell_param
             float *out = p.y + row * p.y_ld + col;
             float r = p.alpha * acc;
             if (p.beta != 0.0f) r = fmaf(p.beta, *out, r);
-            *out = r;
+            *out = finish_output(r, p.bias, col, p.epilogue);
         }
     }
 }
@@ -200,7 +202,7 @@ cb200_status launch_qbell_forward(const qbell_view &x, const dense_args &d, std:
     p.width = x.ell_cols / x.block_size; p.row_stride = x.row_stride_bytes; p.block_col_idx = x.block_col_idx;
     p.packed = x.packed; p.scales = x.scales; p.offsets = x.offsets; p.w = d.dense; p.y = d.out; p.w_ld = d.dense_ld;
     p.y_ld = d.out_ld; p.row_begin = row_begin; p.row_end = row_end; p.n = static_cast<int>(d.n); p.policy = x.policy;
-    p.alpha = d.alpha; p.beta = d.beta;
+    p.alpha = d.alpha; p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue;
     const std::size_t elem = d.dense_dtype == CB200_DTYPE_BF16 ? 2u : 4u;
     const bool vector_ok = (reinterpret_cast<std::uintptr_t>(d.dense) % 16u == 0u) && ((d.dense_ld * elem) % 16u == 0u);
     if (x.bits == 8) {

@@ -72,6 +72,8 @@ struct tc_params {
     int n;
     int policy;
     float alpha, beta;
+    const float *bias;
+    int epilogue;
     int *status;
 };
 
@@ -408,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                         float *out = p.y + row * p.y_ld + col;
                         float r = p.alpha * v[c];
                         if (p.beta != 0.0f) r = fmaf(p.beta, *out, r);
-                        *out = r;
+                        *out = finish_output(r, p.bias, col, p.epilogue);
                     }
                 }
             }
@@ -470,7 +472,7 @@ cb200_status launch_qbell_tcgen05(const qbell_view &x, const dense_args &d, std:
     p.wt = wt; p.kpad = kpad; p.y = d.out; p.y_ld = d.out_ld;
     p.block_row_begin = row_begin / 32; p.block_row_end = (row_end + 31) / 32;
     p.row_begin = row_begin; p.row_end = row_end;
-    p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha; p.beta = d.beta; p.status = status;
+    p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha; p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue; p.status = status;
     *taken = true;
     if (x.bits == 8) return d.n == 256 ? launch<8, 2>(p, sm_count, stream) : launch<8, 1>(p, sm_count, stream);
     return d.n == 256 ? launch<4, 2>(p, sm_count, stream) : launch<4, 1>(p, sm_count, stream);

@@ -31,6 +31,8 @@ struct fwd_params {
     int n;
     int policy;
     float alpha, beta;
+    const float *bias;
+    int epilogue;
 };
 
 // Code of entry `local` (index within its row) for a row whose packed bytes start at `row_bytes`.
@@ -149,6 +151,13 @@ __global__ void __launch_bounds__(256) qcsr_fwd_warp_row_kernel(const fwd_params
             hi.x = fmaf(p.beta, b.x, hi.x); hi.y = fmaf(p.beta, b.y, hi.y);
             hi.z = fmaf(p.beta, b.z, hi.z); hi.w = fmaf(p.beta, b.w, hi.w);
         }
+        if (p.epilogue != CB200_EPILOGUE_NONE) {
+            const int c = (lane % LPN) * 8;
+            lo.x = finish_output(lo.x, p.bias, c + 0, p.epilogue); lo.y = finish_output(lo.y, p.bias, c + 1, p.epilogue);
+            lo.z = finish_output(lo.z, p.bias, c + 2, p.epilogue); lo.w = finish_output(lo.w, p.bias, c + 3, p.epilogue);
+            hi.x = finish_output(hi.x, p.bias, c + 4, p.epilogue); hi.y = finish_output(hi.y, p.bias, c + 5, p.epilogue);
+            hi.z = finish_output(hi.z, p.bias, c + 6, p.epilogue); hi.w = finish_output(hi.w, p.bias, c + 7, p.epilogue);
+        }
         *reinterpret_cast<float4 *>(out) = lo;
         *reinterpret_cast<float4 *>(out + 4) = hi;
     }
@@ -192,7 +201,7 @@ __global__ void __launch_bounds__(256) qcsr_fwd_generic_kernel(const fwd_params 
             float *out = p.y + row * p.y_ld + col;
             float r = p.alpha * acc;
             if (p.beta != 0.0f) r = fmaf(p.beta, *out, r);
-            *out = r;
+            *out = finish_output(r, p.bias, col, p.epilogue);
         }
     }
 }
@@ -257,7 +266,7 @@ cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::i
     p.row_ptr = x.row_ptr; p.packed_row_ptr = x.packed_row_ptr; p.col_idx = x.col_idx; p.packed = x.packed;
     p.scales = x.scales; p.offsets = x.offsets; p.w = d.dense; p.y = d.out; p.w_ld = d.dense_ld; p.y_ld = d.out_ld;
     p.row_begin = row_begin; p.row_end = row_end; p.n = static_cast<int>(d.n); p.policy = x.policy;
-    p.alpha = d.alpha; p.beta = d.beta;
+    p.alpha = d.alpha; p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue;
 
     const std::size_t elem = d.dense_dtype == CB200_DTYPE_BF16 ? 2u : 4u;
     const bool vector_ok = (reinterpret_cast<std::uintptr_t>(d.dense) % 16u == 0u) && ((d.dense_ld * elem) % 16u == 0u) &&

@@ -85,6 +85,8 @@ struct mma_params {
     std::int64_t groups;
     int windows;
     float alpha, beta;
+    const float *bias;
+    int epilogue;
     int *status;
     const std::int32_t *row_order;
 };
@@ -409,6 +411,12 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_mma_kernel(const mma_par
                             r.x = fmaf(p.beta, o.x, r.x); r.y = fmaf(p.beta, o.y, r.y);
                             r.z = fmaf(p.beta, o.z, r.z); r.w = fmaf(p.beta, o.w, r.w);
                         }
+                        if (p.epilogue != CB200_EPILOGUE_NONE) {
+                            r.x = finish_output(r.x, p.bias, h * 32 + c + 0, p.epilogue);
+                            r.y = finish_output(r.y, p.bias, h * 32 + c + 1, p.epilogue);
+                            r.z = finish_output(r.z, p.bias, h * 32 + c + 2, p.epilogue);
+                            r.w = finish_output(r.w, p.bias, h * 32 + c + 3, p.epilogue);
+                        }
                         *reinterpret_cast<float4 *>(out + c) = r;
                     }
                 }
@@ -535,7 +543,7 @@ cb200_status launch_qcsr_forward_mma(const qcsr_view &x, const dense_args &d, st
     p.row_ptr = x.row_ptr; p.packed_row_ptr = x.packed_row_ptr; p.col_idx = x.col_idx; p.packed = x.packed;
     p.row_offsets = row_policy ? x.offsets : nullptr; p.records = records; p.y = d.out; p.y_ld = d.out_ld;
     p.row_begin = row_begin; p.row_end = row_end; p.groups = (row_end - row_begin + kRows - 1) / kRows;
-    p.windows = windows; p.alpha = d.alpha; p.beta = d.beta; p.status = status;
+    p.windows = windows; p.alpha = d.alpha; p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue; p.status = status;
     // a row order describes the whole matrix; a partial row range runs in natural order
     p.row_order = (row_begin == 0 && row_end == x.rows) ? row_order : nullptr;
     *taken = true;

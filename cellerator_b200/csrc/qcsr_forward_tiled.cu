@@ -63,6 +63,8 @@ struct tiled_params {
     int n;
     int policy;
     float alpha, beta;
+    const float *bias;
+    int epilogue;
     int *status;
     const std::int32_t *row_order; // optional: rows in processing order (length-sorted), else natural order
 };
@@ -444,6 +446,13 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
                     hi.x = fmaf(p.beta, bb.x, hi.x); hi.y = fmaf(p.beta, bb.y, hi.y);
                     hi.z = fmaf(p.beta, bb.z, hi.z); hi.w = fmaf(p.beta, bb.w, hi.w);
                 }
+                if (p.epilogue != CB200_EPILOGUE_NONE) {
+                    const int ca = static_cast<int>(out_a - out), cb = static_cast<int>(out_b - out);
+                    lo.x = finish_output(lo.x, p.bias, ca + 0, p.epilogue); lo.y = finish_output(lo.y, p.bias, ca + 1, p.epilogue);
+                    lo.z = finish_output(lo.z, p.bias, ca + 2, p.epilogue); lo.w = finish_output(lo.w, p.bias, ca + 3, p.epilogue);
+                    hi.x = finish_output(hi.x, p.bias, cb + 0, p.epilogue); hi.y = finish_output(hi.y, p.bias, cb + 1, p.epilogue);
+                    hi.z = finish_output(hi.z, p.bias, cb + 2, p.epilogue); hi.w = finish_output(hi.w, p.bias, cb + 3, p.epilogue);
+                }
                 *reinterpret_cast<float4 *>(out_a) = lo;
                 *reinterpret_cast<float4 *>(out_b) = hi;
             }
@@ -517,7 +526,7 @@ cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, 
     p.scales = x.scales; p.offsets = x.offsets; p.w = d.dense; p.y = d.out; p.y_ld = d.out_ld;
     p.row_begin = row_begin; p.row_end = row_end; p.groups = 0; // set per instantiation
     p.genes = static_cast<int>(x.cols); p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha;
-    p.beta = d.beta; p.status = status_word;
+    p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue; p.status = status_word;
     // a row order describes the whole matrix; a partial row range falls back to natural order
     p.row_order = (row_begin == 0 && row_end == x.rows) ? row_order : nullptr;
     if (status_word != nullptr) CB200_CUDA_OK(cudaMemsetAsync(status_word, 0, sizeof(int), stream));

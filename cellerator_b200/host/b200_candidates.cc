@@ -40,6 +40,8 @@ bool query(int projection, const core::numeric_policy &n) noexcept {
     return cb200_backend_query(projection, &p, &cap) == CB200_STATUS_SUCCESS && cap.supported != 0;
 }
 
+bool bias_epilogue(int kind) noexcept { return kind == CB200_EPILOGUE_BIAS || kind >= CB200_EPILOGUE_BIAS_RELU; }
+
 bool supports_csr(const core::numeric_policy &n) noexcept { return query(CB200_PROJECTION_CSR, n); }
 bool supports_transpose(const core::numeric_policy &n) noexcept { return query(CB200_PROJECTION_TRANSPOSE, n); }
 bool supports_bell(const core::numeric_policy &n) noexcept { return query(CB200_PROJECTION_BLOCKED_ELL, n); }
@@ -51,7 +53,8 @@ struct prepared_state {
     std::int32_t projection_kind = 0;
     std::int32_t bits = 8;
     std::int32_t decode_policy = CB200_DECODE_PER_GENE_AFFINE;
-    ex::operand_axis_contract inputs[2]{};
+    std::int32_t epilogue = CB200_EPILOGUE_NONE;
+    ex::operand_axis_contract inputs[3]{}; // X, dense, and the bias vector of a bias epilogue
     ex::operand_axis_contract outputs[1]{};
     ex::output_axis_contract orders[2]{};
     ex::output_effect_contract effects[1]{};
@@ -136,6 +139,13 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
     l.out_ld = out.stride[0];
     l.alpha = 1.0f; // output effect is `overwrite`: out = product
     l.beta = 0.0f;
+    l.epilogue = state->epilogue;
+    if (bias_epilogue(state->epilogue)) {
+        if (launch.input_count < 3u || launch.inputs[2].storage.dense.data == nullptr)
+            return {core::operation_status_code::invalid_launch_bindings, ex::binding_validation_code::ok,
+                    "the bias vector of the composed epilogue is not bound"};
+        l.bias = static_cast<const float *>(launch.inputs[2].storage.dense.data);
+    }
     l.structure_epoch = launch.structures[0].epoch.value;
     l.stream = launch.stream.stream;
     l.device = launch.stream.device_ordinal;
@@ -156,7 +166,7 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
     }
 }
 
-core::operation_status prepare_any(int projection_kind, const core::operation_candidate &candidate,
+core::operation_status prepare_any(int projection_kind, bool composed, const core::operation_candidate &candidate,
                                    const core::operation_problem &problem, const core::structure_set_key &structures,
                                    const core::projection_key &projection, const core::numeric_policy &numeric,
                                    const core::prepare_policy &policy, core::prepared_operation *out) noexcept {
@@ -165,8 +175,19 @@ core::operation_status prepare_any(int projection_kind, const core::operation_ca
         return status(core::operation_status_code::unsupported_projection, "projection is not in the backend catalog");
     if (structures.count != 1u)
         return status(core::operation_status_code::unsupported_problem, "the quantized projections bind one structure");
-    if (problem.input_count != 2u || problem.output_count != 1u)
-        return status(core::operation_status_code::unsupported_problem, "expected inputs {X, dense} and one output");
+    if (!composed && shape->epilogue != CB200_EPILOGUE_NONE)
+        return status(core::operation_status_code::unsupported_problem,
+                      "the projection composes an epilogue: prepare the composed-epilogue candidate");
+    if (composed && (shape->epilogue <= CB200_EPILOGUE_NONE || shape->epilogue > CB200_EPILOGUE_BIAS_GELU_TANH))
+        return status(core::operation_status_code::unsupported_problem, "the projection names no epilogue to compose");
+    const bool with_bias = composed && bias_epilogue(shape->epilogue);
+    if (with_bias && numeric.bias != ex::numeric_type::f32)
+        return status(core::operation_status_code::unsupported_numeric_policy, "the bias vector is fp32");
+    const std::uint32_t input_count = with_bias ? 3u : 2u;
+    if (problem.input_count != input_count || problem.output_count != 1u)
+        return status(core::operation_status_code::unsupported_problem,
+                      with_bias ? "expected inputs {X, dense, bias} and one output"
+                                : "expected inputs {X, dense} and one output");
 
     cb200_spmm_problem p{};
     p.version = CB200_ABI_VERSION;
@@ -187,6 +208,7 @@ core::operation_status prepare_any(int projection_kind, const core::operation_ca
     // bf16 products (tensor-core schedules) only when the request's numeric policy says so
     p.multiply = dtype_of(numeric.multiply);
     p.device_matrix = policy.allow_persistent_preprocessing ? shape->device_matrix : nullptr;
+    p.persistent_limit_bytes = policy.persistent_memory_limit;
 
     auto *state = new (std::nothrow) prepared_state;
     if (state == nullptr) return status(core::operation_status_code::preparation_failed, "out of host memory");
@@ -197,11 +219,18 @@ core::operation_status prepare_any(int projection_kind, const core::operation_ca
     state->projection_kind = projection_kind;
     state->bits = shape->bits;
     state->decode_policy = shape->decode_policy;
+    state->epilogue = composed ? shape->epilogue : CB200_EPILOGUE_NONE;
     const bool transpose = projection_kind == CB200_PROJECTION_TRANSPOSE;
     // forward / Blocked-ELL: X(cells, genes) . W(genes, latent) -> Y(cells, latent)
     // transpose:             X(cells, genes)^T . G(cells, latent) -> G'(genes, latent)
     state->inputs[0] = axis_contract(ex::operand_kind::sparse_relation, shape->cells, shape->genes);
     state->inputs[1] = axis_contract(ex::operand_kind::dense_tensor, transpose ? shape->cells : shape->genes, shape->latent);
+    if (with_bias) {
+        state->inputs[2] = {};
+        state->inputs[2].kind = ex::operand_kind::dense_tensor;
+        state->inputs[2].rank = 1u;
+        state->inputs[2].axes[0] = shape->latent;
+    }
     state->outputs[0] = axis_contract(ex::operand_kind::dense_tensor, transpose ? shape->genes : shape->cells, shape->latent);
     state->orders[0] = preserve_order(transpose ? shape->genes : shape->cells, 0u);
     state->orders[1] = preserve_order(shape->latent, 1u);
@@ -223,7 +252,7 @@ core::operation_status prepare_any(int projection_kind, const core::operation_ca
     prepared.binding_contract.outputs = state->outputs;
     prepared.binding_contract.output_orders = state->orders;
     prepared.binding_contract.output_effects = state->effects;
-    prepared.binding_contract.input_count = 2u;
+    prepared.binding_contract.input_count = input_count;
     prepared.binding_contract.output_count = 1u;
     prepared.binding_contract.output_order_count = 2u;
     prepared.binding_contract.output_effect_count = 1u;
@@ -246,19 +275,31 @@ core::operation_status prepare_csr(const core::operation_candidate &c, const cor
                                    const core::structure_set_key &s, const core::projection_key &pj,
                                    const core::numeric_policy &n, const core::prepare_policy &po,
                                    core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_CSR, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_CSR, false, c, pr, s, pj, n, po, out);
+}
+core::operation_status prepare_csr_epilogue(const core::operation_candidate &c, const core::operation_problem &pr,
+                                            const core::structure_set_key &s, const core::projection_key &pj,
+                                            const core::numeric_policy &n, const core::prepare_policy &po,
+                                            core::prepared_operation *out) noexcept {
+    return prepare_any(CB200_PROJECTION_CSR, true, c, pr, s, pj, n, po, out);
+}
+core::operation_status prepare_bell_epilogue(const core::operation_candidate &c, const core::operation_problem &pr,
+                                             const core::structure_set_key &s, const core::projection_key &pj,
+                                             const core::numeric_policy &n, const core::prepare_policy &po,
+                                             core::prepared_operation *out) noexcept {
+    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, true, c, pr, s, pj, n, po, out);
 }
 core::operation_status prepare_transpose(const core::operation_candidate &c, const core::operation_problem &pr,
                                          const core::structure_set_key &s, const core::projection_key &pj,
                                          const core::numeric_policy &n, const core::prepare_policy &po,
                                          core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_TRANSPOSE, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_TRANSPOSE, false, c, pr, s, pj, n, po, out);
 }
 core::operation_status prepare_bell(const core::operation_candidate &c, const core::operation_problem &pr,
                                     const core::structure_set_key &s, const core::projection_key &pj,
                                     const core::numeric_policy &n, const core::prepare_policy &po,
                                     core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, false, c, pr, s, pj, n, po, out);
 }
 
 core::operation_candidate make_candidate(std::uint64_t id, const char *name, core::projection_kind projection,
@@ -311,9 +352,22 @@ core::operation_candidate quantized_blocked_ell_candidate() noexcept {
                           core::candidate_deterministic | core::candidate_graph_capture, &supports_bell, &prepare_bell, 0u);
 }
 
+core::operation_candidate quantized_csr_forward_epilogue_candidate() noexcept {
+    return make_candidate(0xcb200c5a00000004ull, "cb200.qcsr.forward.epilogue.sm100a", core::projection_kind::csr,
+                          core::candidate_deterministic | core::candidate_graph_capture | core::candidate_composed_epilogue,
+                          &supports_csr, &prepare_csr_epilogue, 256u);
+}
+
+core::operation_candidate quantized_blocked_ell_epilogue_candidate() noexcept {
+    return make_candidate(0xcb200c5a00000005ull, "cb200.qbell.forward.epilogue.sm100a", core::projection_kind::blocked_ell,
+                          core::candidate_deterministic | core::candidate_graph_capture | core::candidate_composed_epilogue,
+                          &supports_bell, &prepare_bell_epilogue, 0u);
+}
+
 core::operation_status register_all(core::candidate_registry *registry) noexcept {
     const core::operation_candidate all[] = {quantized_csr_forward_candidate(), quantized_csr_transpose_candidate(),
-                                             quantized_blocked_ell_candidate()};
+                                             quantized_blocked_ell_candidate(), quantized_csr_forward_epilogue_candidate(),
+                                             quantized_blocked_ell_epilogue_candidate()};
     for (const core::operation_candidate &c : all) {
         const core::operation_status s = core::register_candidate(registry, c);
         if (!s) return s;

@@ -55,6 +55,10 @@ struct projection_catalog_entry {
     // optional: the device-resident matrix (final contents).  With numeric_policy.multiply == bf16 and
     // prepare_policy.allow_persistent_preprocessing, prepare builds the window-blocked copy from it
     const cb200_qcsr *device_matrix = nullptr;
+    // epilogue the operation composes into the projection (cb200_epilogue; epilogue_kind of the
+    // request, operation.hh:49-61).  Anything but none is served by the composed-epilogue
+    // candidates only; the bias kinds bind the bias vector (latent axis, fp32) as third input.
+    std::int32_t epilogue = CB200_EPILOGUE_NONE;
     ex::axis_identity cells{}, genes{}, latent{};
 };
 
@@ -68,8 +72,13 @@ void clear_projection_catalog() noexcept;
 core::operation_candidate quantized_csr_forward_candidate() noexcept;
 core::operation_candidate quantized_csr_transpose_candidate() noexcept;
 core::operation_candidate quantized_blocked_ell_candidate() noexcept;
+// The forward projections with the catalog entry's epilogue applied in the kernel's output stage:
+// out = act(product + bias[latent]).  They carry candidate_composed_epilogue, so
+// prepare_policy.allow_composed_epilogue == false rejects them (operation_core.cc:226-230).
+core::operation_candidate quantized_csr_forward_epilogue_candidate() noexcept;
+core::operation_candidate quantized_blocked_ell_epilogue_candidate() noexcept;
 
-// Registers the three candidates; returns the first failing status.
+// Registers the five candidates; returns the first failing status.
 core::operation_status register_all(core::candidate_registry *registry) noexcept;
 
 // Releases what prepare() attached to a prepared operation (the cb200_prepared handle and the

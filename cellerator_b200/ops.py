@@ -206,7 +206,7 @@ class PreparedSpmm:
 
     def __init__(self, projection: int, m: int, k: int, n: int, nnz: int, bits: int, policy: int, dense_dtype,
                  device, structure_epoch: int = 1, host_row_ptr: np.ndarray | None = None, deterministic=False,
-                 multiply: int = 0, device_matrix=None):
+                 multiply: int = 0, device_matrix=None, persistent_limit_bytes: int = 0):
         self.device = torch.device(device)
         pr = capi.header(capi.SpmmProblem())
         pr.projection, pr.m, pr.k, pr.n, pr.nnz, pr.bits, pr.policy = projection, m, k, n, nnz, bits, policy
@@ -223,6 +223,7 @@ class PreparedSpmm:
         if device_matrix is not None:  # lets prepare build its persistent window-blocked copy
             self._matrix_desc = device_matrix.desc()
             pr.device_matrix = C.pointer(self._matrix_desc)
+        pr.persistent_limit_bytes = persistent_limit_bytes  # 0: no limit on what prepare may keep on the device
         self.problem = pr
         self.handle = C.c_void_p()
         capi.check(capi.lib().cb200_spmm_prepare(C.byref(pr), C.byref(self.handle)))
@@ -243,7 +244,8 @@ class PreparedSpmm:
         return int(capi.lib().cb200_prepared_persistent_bytes(self.handle))
 
     def make_launch(self, x, dense: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0, row_begin=0, row_end=0,
-                    stream: int | None = None, epoch: int | None = None) -> capi.Launch:
+                    stream: int | None = None, epoch: int | None = None, epilogue: str | int = 0,
+                    bias: torch.Tensor | None = None) -> capi.Launch:
         ln = capi.header(capi.Launch())
         desc = x.desc()
         if isinstance(x, QuantizedBell):
@@ -261,7 +263,12 @@ class PreparedSpmm:
         ln.workspace_device = dev_index
         ln.workspace = None if self.workspace is None else self.workspace.data_ptr()
         ln.workspace_bytes = self.workspace_bytes
-        ln._keep = (desc, x, dense, out)
+        ln.epilogue = capi.EPILOGUE[epilogue] if isinstance(epilogue, str) else int(epilogue)
+        if bias is not None:
+            if bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != self.problem.n:
+                raise ValueError("bias must be a contiguous float32 vector with one value per output column")
+            ln.bias = bias.data_ptr()
+        ln._keep = (desc, x, dense, out, bias)
         return ln
 
     def run_launch(self, launch: capi.Launch) -> None:
@@ -284,8 +291,10 @@ class PreparedSpmm:
 
 
 def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
-                 multiply: int = 0):
-    """Y = alpha * deq(X) W + beta * Y (one-shot convenience: prepare + run).
+                 multiply: int = 0, epilogue: str | int = 0, bias: torch.Tensor | None = None):
+    """Y = act(alpha * deq(X) W + beta * Y + bias) (one-shot convenience: prepare + run).
+
+    epilogue names one of capi.EPILOGUE ("none", "bias", "relu", "gelu_erf", "gelu_tanh", "bias_relu", ...).
 
     multiply=capi.DTYPE_BF16 with a bf16 W asks for tensor-core products (decoded values rounded to bf16)."""
     n = w.shape[1]
@@ -293,7 +302,7 @@ def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = No
         out = torch.empty(x.rows, n, dtype=torch.float32, device=x.device)
     op = PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, n, x.nnz, x.bits, x.policy, w.dtype, x.device,
                       host_row_ptr=x.host_row_ptr, multiply=multiply)
-    op.run(x, w, out, alpha=alpha, beta=beta)
+    op.run(x, w, out, alpha=alpha, beta=beta, epilogue=epilogue, bias=bias)
     op.close()
     return out
 
@@ -313,13 +322,14 @@ def spmm_transpose(x: QuantizedCsr, g: torch.Tensor, out: torch.Tensor | None = 
     return out
 
 
-def bell_forward(x: QuantizedBell, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0):
+def bell_forward(x: QuantizedBell, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
+                 epilogue: str | int = 0, bias: torch.Tensor | None = None):
     n = w.shape[1]
     if out is None:
         out = torch.empty(x.rows, n, dtype=torch.float32, device=x.device)
     op = PreparedSpmm(capi.PROJECTION_BLOCKED_ELL, x.rows, x.cols, n, x.rows * x.ell_cols, x.bits, x.policy,
                       w.dtype, x.device)
-    op.run(x, w, out, alpha=alpha, beta=beta)
+    op.run(x, w, out, alpha=alpha, beta=beta, epilogue=epilogue, bias=bias)
     op.close()
     return out
 

@@ -65,6 +65,18 @@ typedef enum cb200_decode_policy {
     CB200_DECODE_COLUMN_SCALE_ROW_OFFSET = 2 /* value = code*scales[gene] + offsets[row]  */
 } cb200_decode_policy;
 
+/* epilogue_kind of the SpMM request, include/Cellerator/compute/math/operation.hh:49-61 */
+typedef enum cb200_epilogue {
+    CB200_EPILOGUE_NONE = 0,
+    CB200_EPILOGUE_BIAS = 1,
+    CB200_EPILOGUE_RELU = 2,
+    CB200_EPILOGUE_GELU_ERF = 3,
+    CB200_EPILOGUE_GELU_TANH = 4,
+    CB200_EPILOGUE_BIAS_RELU = 5,
+    CB200_EPILOGUE_BIAS_GELU_ERF = 6,
+    CB200_EPILOGUE_BIAS_GELU_TANH = 7
+} cb200_epilogue;
+
 /* core::projection_kind, operation_core.hh:25-37 (same values) */
 typedef enum cb200_projection {
     CB200_PROJECTION_CSR = 5,
@@ -232,8 +244,19 @@ typedef struct cb200_spmm_problem {
      * word per stored entry plus 8 bytes per 256-row x 128-gene segment; persistent_kernel_state,
      * operation_core.hh:126-129) and the schedule becomes "tensor_blocked".  Prepare launches
      * kernels on the device's default stream and synchronises.  Launches must then pass the same
-     * arrays: other pointers are refused as a stale structure; changed codes need a new prepare. */
+     * arrays: other pointers are refused as a stale structure; changed codes need a new prepare.
+     *
+     * Forward with bf16 products on a matrix of 8 % density or more: prepare goes one step further
+     * and keeps the decoded operand tiles themselves (schedule "tensor_dense": rows x genes x 2 bytes,
+     * rounded up to 256 x 128 tiles; codes, scales and offsets are baked in, so a change of any of
+     * them needs a new prepare).  A launch then streams the tiles into the tensor cores and does no
+     * decoding.  Taken only when the tiles fit persistent_limit_bytes and half of the free device
+     * memory; otherwise "tensor_blocked" stays. */
     const cb200_qcsr *device_matrix;
+    /* prepare_policy.persistent_memory_limit (operation_core.hh:116-124): device bytes the prepared
+     * operation may keep; 0 = no limit.  A copy that would exceed it is not built (the schedule
+     * falls back to the next one that fits). */
+    uint64_t persistent_limit_bytes;
 } cb200_spmm_problem;
 
 typedef struct cb200_prepared cb200_prepared;
@@ -243,7 +266,8 @@ void cb200_prepared_destroy(cb200_prepared *prepared);
 /* workspace_requirement, launch_bindings.hh:67-71 */
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
 /* kernel choice made at prepare time, as text: "warp_per_row", "gene_tiled" (exact fp32 products);
- * "tensor_windows", "tensor_blocked" (CSR, bf16 products on tcgen05); "tcgen05_block_rows" (Blocked-ELL);
+ * "tensor_windows", "tensor_blocked", "tensor_dense" (CSR, bf16 products on tcgen05);
+ * "tensor_blocked_x2" / "_x3" (fp32 products from bf16 passes); "tcgen05_block_rows" (Blocked-ELL);
  * transpose: "vector_reductions" (exact) or "tensor_blocked" */
 const char *cb200_prepared_schedule(const cb200_prepared *prepared);
 /* device bytes the prepared operation owns (row order, window-blocked copy): prepared_operation.persistent.bytes,
@@ -270,6 +294,13 @@ typedef struct cb200_launch {
     int32_t workspace_device;
     void *workspace;         /* transient_workspace, launch_bindings.hh:61-65 */
     uint64_t workspace_bytes;
+    /* Composed epilogue of the forward projections (CSR, Blocked-ELL), the request contract's
+     * epilogue_kind with the referee's rule (operation.hh:49-61, referee.cc:81-97):
+     *     out = act(alpha * product + beta * out + bias[column]).
+     * bias has n floats on the device and is read only by the bias kinds; the transpose accepts
+     * CB200_EPILOGUE_NONE only. */
+    const float *bias;
+    int32_t epilogue;        /* cb200_epilogue */
 } cb200_launch;
 
 cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch);

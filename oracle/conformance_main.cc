@@ -92,7 +92,7 @@ int main(int argc, char **argv) {
 
     // ---- registration and capability query (host only) ----------------------------------
     static core::candidate_registry registry;
-    CHECK(static_cast<bool>(host::register_all(&registry)) && registry.size == 3u, "register three candidates");
+    CHECK(static_cast<bool>(host::register_all(&registry)) && registry.size == 5u, "register five candidates");
     CHECK(core::register_candidate(&registry, host::quantized_csr_forward_candidate()).code ==
               core::operation_status_code::duplicate_candidate, "duplicate registration is rejected");
     const core::operation_candidate *fwd = core::find_candidate(registry, host::quantized_csr_forward_candidate().identity);
@@ -323,6 +323,97 @@ int main(int argc, char **argv) {
               "an output aliasing an input is refused");
     }
     host::release_prepared(&prepared);
+
+    // ---- forward with a composed epilogue: out = gelu_erf(product + bias) -----------------------
+    {
+        const core::operation_candidate *epi =
+            core::find_candidate(registry, host::quantized_csr_forward_epilogue_candidate().identity);
+        CHECK(epi != nullptr && (epi->capability_flags & core::candidate_composed_epilogue) != 0u,
+              "the composed-epilogue candidate carries its capability flag");
+        problem_ids e = make_ids(3u, core::projection_kind::csr, static_cast<std::uint64_t>(nnz));
+        host::projection_catalog_entry es = shape;
+        es.projection = e.projection.runtime;
+        es.epilogue = CB200_EPILOGUE_BIAS_GELU_ERF;
+        CHECK(host::register_projection(es), "catalog accepts the epilogue projection");
+        core::numeric_policy np = policy_u8(ex::numeric_type::f32);
+        np.bias = ex::numeric_type::f32;
+        core::prepare_policy no_epilogue;
+        no_epilogue.allow_composed_epilogue = false;
+        CHECK(core::prepare_candidate(*epi, e.problem, e.structures, e.projection, np, no_epilogue, &prepared).code ==
+                  core::operation_status_code::capability_rejected, "a policy without composed epilogues rejects the candidate");
+        CHECK(core::prepare_candidate(*fwd, e.problem, e.structures, e.projection, np, {}, &prepared).code ==
+                  core::operation_status_code::unsupported_problem, "the plain candidate refuses a projection that composes an epilogue");
+        CHECK(core::prepare_candidate(*epi, e.problem, e.structures, e.projection, np, {}, &prepared).code ==
+                  core::operation_status_code::unsupported_problem, "a bias epilogue needs the bias as third input");
+        e.problem.input_count = 3u;
+        st = core::prepare_candidate(*epi, e.problem, e.structures, e.projection, np, {}, &prepared);
+        CHECK(static_cast<bool>(st), "prepare_candidate(forward + bias + exact GELU)");
+        if (!st) std::printf("  message: %s\n", st.message);
+
+        std::vector<float> bias(N);
+        for (auto &v : bias) v = one(rng);
+        float *d_bias = to_device(bias);
+        ex::relation_structure es_structure = structure;
+        es_structure.identity = e.structures.structures[0].runtime;
+        ex::value_plane eplane = plane;
+        eplane.structure = es_structure.identity;
+        ex::value_binding evalue{&eplane, {5u}};
+        ex::biological_operand_view in3[3] = {inputs[0], inputs[1], {}};
+        in3[0].storage.relation.structure = es_structure.identity;
+        in3[0].storage.relation.projection = e.projection.runtime;
+        in3[2].kind = ex::operand_kind::dense_tensor;
+        in3[2].storage.dense.data = d_bias;
+        in3[2].storage.dense.location = dev_loc;
+        in3[2].storage.dense.value_type = ex::numeric_type::f32;
+        in3[2].storage.dense.rank = 1u;
+        in3[2].storage.dense.axes[0] = latent;
+        in3[2].storage.dense.shape[0] = static_cast<std::uint64_t>(N);
+        in3[2].storage.dense.stride[0] = 1;
+        ex::launch_bindings el = launch;
+        el.structures = &es_structure;
+        el.values = &evalue;
+        el.inputs = in3;
+        el.input_count = 3u;
+        cudaMemset(d_y, 0xff, M * N * sizeof(float));
+        st = core::run_prepared_operation(prepared, el);
+        CHECK(static_cast<bool>(st), "run_prepared_operation(forward + epilogue)");
+        if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+        cudaStreamSynchronize(stream);
+        cudaMemcpy(y.data(), d_y, y.size() * sizeof(float), cudaMemcpyDeviceToHost);
+
+        cm::spmm_request r;
+        r.m = M; r.k = K; r.n = N; r.sparse_nnz = nnz;
+        r.sparse_structure.identity_version = 1u; r.sparse_structure.value = 77u;
+        r.dense_rhs_leading_dimension = N; r.output_leading_dimension = N;
+        r.sparse_storage_type_code = r.dense_storage_type_code = r.output_storage_type_code = ::cellerator::real::value_f32;
+        r.compute_type_code = r.accumulation_type_code = ::cellerator::real::value_f64;
+        r.alpha = cm::make_scalar(1.0); r.beta = cm::make_scalar(0.0);
+        r.sparse_feature_order.feature_count = static_cast<cm::u32>(K);
+        r.sparse_feature_order.feature_axis_identity_version = 1u;
+        r.sparse_feature_order.feature_axis_identity = 9u;
+        r.dense_feature_order = r.sparse_feature_order;
+        r.epilogue.kind = cm::epilogue_kind::bias_gelu_exact_erf;
+        r.epilogue.bias_type_code = ::cellerator::real::value_f32;
+        r.epilogue.bias_element_count = static_cast<cm::u64>(N);
+        const cm::logical_csr_view sp{static_cast<cm::u64>(M), static_cast<cm::u64>(K), static_cast<cm::u64>(nnz), offs.data(),
+                                      ucol.data(), decoded.data(), static_cast<cm::u32>(::cellerator::real::value_f32)};
+        const cm::logical_dense_view dn{w.data(), static_cast<cm::u64>(K), static_cast<cm::u64>(N), static_cast<cm::u64>(N),
+                                        cm::dense_layout_kind::row_major, static_cast<cm::u32>(::cellerator::real::value_f32)};
+        std::vector<double> eref(M * N, 0.0);
+        CHECK(static_cast<bool>(cm::build_spmm_reference(r, sp, dn, {}, bias.data(), eref.data(), eref.size())),
+              "referee(forward + bias + exact GELU)");
+        const cm::logical_dense_view cand{y.data(), static_cast<cm::u64>(M), static_cast<cm::u64>(N), static_cast<cm::u64>(N),
+                                          cm::dense_layout_kind::row_major, static_cast<cm::u32>(::cellerator::real::value_f32)};
+        cm::numerical_comparison cmp;
+        const bool ok = static_cast<bool>(cm::compare_spmm_reference(eref.data(), eref.size(), cand, {1.0e-4, 1.0e-4, 1.0e-30}, &cmp));
+        std::printf("  forward + epilogue max_abs=%.3e mismatches=%llu\n", cmp.max_absolute_error,
+                    static_cast<unsigned long long>(cmp.mismatch_count));
+        CHECK(ok && cmp.within_tolerance, "composed epilogue within tolerance of the reference referee");
+        el.input_count = 2u;
+        CHECK(!static_cast<bool>(core::run_prepared_operation(prepared, el)), "a launch without the bias operand is refused");
+        host::release_prepared(&prepared);
+        cudaFree(d_bias);
+    }
 
     // ---- transpose candidate -------------------------------------------------------------------
     {

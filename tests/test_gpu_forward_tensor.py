@@ -1,7 +1,8 @@
 """GPU parity of the tensor-core forward schedules (decoded values rounded to bf16, bf16 W, fp32
 accumulation in TMEM), through the C ABI, against the oracle: "tensor_windows" reads the CSR arrays
 with one thread per row, "tensor_blocked" streams the window-blocked copy that prepare builds when
-it is handed the device-resident matrix.
+it is handed the device-resident matrix, "tensor_dense" streams the decoded operand tiles that
+prepare keeps instead of that copy when the matrix is dense enough and the device has room.
 
 Tolerance: each product carries the bf16 rounding of the decoded value (relative 2^-9), so the
 error of an output is at most 2^-9 * ||row||_1 * max|W| plus fp32 summation error; the test bound is
@@ -31,7 +32,10 @@ def prepared(x, n, w, device, blocked=False, **kw):
                             device_matrix=x if blocked else None, **kw)
 
 
-@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked"])
+BLOCKED = ("tensor_blocked", "tensor_dense")          # schedules that need the matrix at prepare
+
+
+@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked", "tensor_dense"])
 @pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("n", [32, 64, 128])
 @pytest.mark.parametrize("policy", [1, 2])
@@ -44,10 +48,12 @@ def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=300, bits=bits, policy=policy))
     x = to_dev(c, cuda_device)
     w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
-    op = prepared(x, n, w, cuda_device, blocked=schedule == "tensor_blocked")
+    op = prepared(x, n, w, cuda_device, blocked=schedule in BLOCKED)
     assert op.schedule == schedule
     if schedule == "tensor_blocked":                                    # one word per stored entry + segment table
         assert 4 * x.nnz <= op.persistent_bytes <= 4 * x.nnz + 64 * ((rows + 255) // 256) * ((cols + 127) // 128) + 4 * rows
+    if schedule == "tensor_dense":                                      # one 64 KB tile per 256 rows x 128 genes
+        assert op.persistent_bytes == 65536 * ((rows + 255) // 256) * ((cols + 127) // 128)
     y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
     torch.cuda.synchronize()
     assert int(op.workspace[:4].view(torch.int32).item()) == 0          # no bounded wait ran out
@@ -61,11 +67,11 @@ def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits
     assert torch.equal(y, op.run(x, w, torch.empty_like(y)))                   # a row has one owner: repeatable
     # row ranges: only the rows of the range are written, bit-identical to the full run
     # (the blocked copy serves ranges that start on a 256-row boundary; others run an exact kernel)
-    lo = 256 if schedule == "tensor_blocked" else 100
+    lo = 256 if schedule in BLOCKED else 100
     out = torch.full((rows, n), -3.0, device=cuda_device)
     op.run(x, w, out, row_begin=lo, row_end=900)
     assert torch.equal(out[lo:900], y[lo:900]) and torch.all(out[:lo] == -3.0) and torch.all(out[900:] == -3.0)
-    if schedule == "tensor_blocked":
+    if schedule in BLOCKED:
         out.fill_(-3.0)
         op.run(x, w, out, row_begin=100, row_end=900)
         assert_tensor_close(out[100:900].cpu().numpy(), ref[100:900], l1[100:900], wmax)
@@ -109,7 +115,30 @@ def test_tensor_schedule_is_opt_in(cuda_device, oracle):
     exact.close()
 
 
-@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked"])
+def test_dense_tiles_respect_the_memory_limit(cuda_device, oracle, monkeypatch):
+    """persistent_limit_bytes below the tiles' size: the window-blocked copy stays; below that too: an
+    exact schedule.  The limit is prepare_policy.persistent_memory_limit of the reference."""
+    rng = np.random.default_rng(11)
+    rows, cols, n = 4096, 512, 64
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=200, bits=8, empty_rows=False))
+    x = to_dev(c, cuda_device)
+    w, _ = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    tiles = 65536 * (rows // 256) * (cols // 128)
+    free = prepared(x, n, w, cuda_device, blocked=True)
+    assert free.schedule == "tensor_dense" and free.persistent_bytes == tiles
+    capped = prepared(x, n, w, cuda_device, blocked=True, persistent_limit_bytes=tiles - 1)
+    assert capped.schedule == "tensor_blocked" and capped.persistent_bytes < tiles
+    tiny = prepared(x, n, w, cuda_device, blocked=True, persistent_limit_bytes=1024)
+    assert tiny.schedule not in BLOCKED
+    y = [o.run(x, w, torch.empty(rows, n, device=cuda_device)) for o in (free, capped, tiny)]
+    l1, _ = row_l1(oracle, c)
+    scale = torch.from_numpy(l1).to(cuda_device)[:, None].float() * float(w.float().abs().max())
+    assert torch.all((y[0] - y[2]).abs() <= 1e-2 * scale) and torch.all((y[1] - y[2]).abs() <= 1e-2 * scale)
+    for o in (free, capped, tiny):
+        o.close()
+
+
+@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked", "tensor_dense"])
 @pytest.mark.parametrize("bits,n", [(8, 64), (4, 128)])
 def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule, bits, n):
     """Genes as in the benchmark configuration, 1/8 of its cells, device-generated: agreement with
@@ -119,9 +148,12 @@ def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule
     x = synth.make_qcsr_device(**{**cfg, "bits": bits}, device=cuda_device, seed=0)
     rng = np.random.default_rng(9)
     w1, w_host = dense(rng, x.cols, n, torch.bfloat16, cuda_device)
-    if schedule == "tensor_windows":
-        monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)   # prepare's own choice needs a denser matrix
-    op = prepared(x, n, w1, cuda_device, blocked=schedule == "tensor_blocked")
+    # prepare's own choice: the 5 %-dense 33,538-gene matrix keeps the window-blocked copy, the 17 %-dense
+    # 4,000-gene one the dense tiles; the other combinations are forced
+    own = {8: "tensor_blocked", 4: "tensor_dense"}[bits]
+    if schedule != own:
+        monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)
+    op = prepared(x, n, w1, cuda_device, blocked=schedule in BLOCKED)
     monkeypatch.delenv("CB200_FWD_SCHEDULE", raising=False)
     assert op.schedule == schedule
     y1 = op.run(x, w1, torch.empty(x.rows, n, device=cuda_device))
@@ -141,7 +173,7 @@ def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule
     assert torch.all((y1 - y_exact).abs() <= 1e-2 * (l1[:, None] * wmax) + 1e-30)
     for parts in (2, 8):
         brp = ops.partition_rows(x.rows, parts)
-        if schedule == "tensor_blocked":
+        if schedule in BLOCKED:
             brp = (brp // 256) * 256                          # shards on group boundaries use the copy
             brp[-1] = x.rows
         out = torch.empty(x.rows, n, device=cuda_device)
