@@ -83,6 +83,34 @@ EPILOGUE = {"none": 0, "bias": 1, "relu": 2, "gelu_erf": 3, "gelu_tanh": 4, "bia
             "bias_gelu_erf": 6, "bias_gelu_tanh": 7}
 
 
+class BellLoweringInput(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("rows", C.c_uint32), ("features", C.c_uint32),
+                ("nnz", C.c_uint32), ("value_size_bytes", C.c_uint32), ("row_offsets", C.c_void_p),
+                ("feature_ids", C.c_void_p), ("values", C.c_void_p), ("feature_block_count", C.c_uint32),
+                ("feature_block_offsets", C.c_void_p), ("feature_permutation", C.c_void_p),
+                ("inverse_feature_permutation", C.c_void_p), ("row_permutation", C.c_void_p),
+                ("inverse_row_permutation", C.c_void_p), ("device", C.c_int32)]
+
+
+class BellLoweringPolicy(C.Structure):
+    _fields_ = [("maximum_value_slot_expansion", C.c_double), ("maximum_storage_expansion", C.c_double),
+                ("maximum_persistent_bytes", C.c_uint64)]
+
+
+class BellGeometry(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("state", C.c_int32), ("block_size", C.c_uint32),
+                ("rows", C.c_uint32), ("features", C.c_uint32), ("padded_rows", C.c_uint32),
+                ("padded_features", C.c_uint32), ("block_rows", C.c_uint32), ("ell_blocks_per_row", C.c_uint32),
+                ("ell_columns", C.c_uint32), ("feature_block_offset_count", C.c_uint64),
+                ("column_index_count", C.c_uint64), ("value_bytes", C.c_uint64), ("occupied_blocks", C.c_uint64),
+                ("stored_blocks", C.c_uint64), ("dense_value_slots", C.c_uint64), ("persistent_bytes", C.c_uint64),
+                ("source_bytes", C.c_uint64), ("scalar_occupancy", C.c_double), ("ell_slot_utilization", C.c_double),
+                ("value_slot_expansion", C.c_double), ("storage_expansion", C.c_double)]
+
+
+BELL_VALUES_BLOCK_MAJOR, BELL_VALUES_ROW_MAJOR = 0, 1
+
+
 class SessionOptions(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32),
                 ("owned_stream_count", C.c_uint32), ("external_stream_count", C.c_uint32),
@@ -102,6 +130,7 @@ EXPORTED_SYMBOLS = [
     "cb200_backend_query", "cb200_spmm_prepare", "cb200_prepared_destroy",
     "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_prepared_persistent_bytes", "cb200_spmm_run", "cb200_kernel_launch_count",
     "cb200_qcsr_forward_static",
+    "cb200_bell_lowering_workspace", "cb200_bell_lowering_query", "cb200_bell_lowering_materialize",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
 ]

@@ -334,6 +334,69 @@ def bell_forward(x: QuantizedBell, w: torch.Tensor, out: torch.Tensor | None = N
     return out
 
 
+# ---- CSR -> physical Blocked-ELL lowering on the device ---------------------------------------
+
+class BellLowering:
+    """cb200_bell_lowering_query / _materialize over device tensors.
+
+    row_offsets / feature_ids: uint32 CSR with canonical feature ids (held as int32 tensors of the same
+    bits); values: any dtype, one element (or one row of a 2-D tensor) per stored entry, copied bytewise;
+    fb_offsets: host array of the semantic feature blocks in execution order; fperm[execution] =
+    canonical feature, rperm[execution row] = canonical row."""
+
+    def __init__(self, row_offsets, feature_ids, values, features: int, fb_offsets, fperm, rperm, device):
+        self.device = torch.device(device)
+        as_i32 = lambda a: torch.as_tensor(np.ascontiguousarray(a, dtype=np.uint32).view(np.int32)).to(self.device) \
+            if not isinstance(a, torch.Tensor) else a.to(self.device)
+        self.row_offsets, self.feature_ids = as_i32(row_offsets), as_i32(feature_ids)
+        self.values = (values if isinstance(values, torch.Tensor) else torch.as_tensor(np.ascontiguousarray(values))).to(self.device).contiguous()
+        self.fperm, self.rperm = as_i32(fperm), as_i32(rperm)
+        self.rows, self.features, self.nnz = self.row_offsets.numel() - 1, int(features), self.feature_ids.numel()
+        self.finv = torch.empty_like(self.fperm)
+        self.finv[self.fperm.long()] = torch.arange(self.features, dtype=torch.int32, device=self.device)
+        self.rinv = torch.empty_like(self.rperm)
+        if self.rows:
+            self.rinv[self.rperm.long()] = torch.arange(self.rows, dtype=torch.int32, device=self.device)
+        self._fb = np.ascontiguousarray(fb_offsets, dtype=np.uint32)
+        self.value_size = self.values.element_size() * (self.values.shape[1] if self.values.dim() == 2 else 1)
+        inp = capi.header(capi.BellLoweringInput())
+        inp.rows, inp.features, inp.nnz, inp.value_size_bytes = self.rows, self.features, self.nnz, self.value_size
+        inp.row_offsets, inp.feature_ids = self.row_offsets.data_ptr(), self.feature_ids.data_ptr()
+        inp.values = self.values.data_ptr() if self.nnz else None
+        inp.feature_block_count = len(self._fb) - 1
+        inp.feature_block_offsets = self._fb.ctypes.data
+        inp.feature_permutation, inp.inverse_feature_permutation = self.fperm.data_ptr(), self.finv.data_ptr()
+        inp.row_permutation, inp.inverse_row_permutation = self.rperm.data_ptr(), self.rinv.data_ptr()
+        inp.device = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.input = inp
+        need = C.c_uint64()
+        capi.check(capi.lib().cb200_bell_lowering_workspace(C.byref(inp), C.byref(need)))
+        self.workspace = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+
+    def query(self, block_size: int, max_value_expansion=64.0, max_storage_expansion=64.0,
+              max_persistent=2 ** 63) -> capi.BellGeometry:
+        policy = capi.BellLoweringPolicy(max_value_expansion, max_storage_expansion, max_persistent)
+        geo = capi.BellGeometry()
+        capi.check(capi.lib().cb200_bell_lowering_query(C.byref(self.input), C.c_uint32(block_size), C.byref(policy),
+                                                        C.c_void_p(self.workspace.data_ptr()),
+                                                        C.c_uint64(self.workspace.numel()),
+                                                        C.c_void_p(_stream_handle(self.device)), C.byref(geo)))
+        return geo
+
+    def materialize(self, geo: capi.BellGeometry, layout=capi.BELL_VALUES_BLOCK_MAJOR, row_stride_bytes=0):
+        """-> (padded feature-block offsets int32[blocks + 1], column indices int32, value bytes uint8)"""
+        pfo = torch.empty(len(self._fb), dtype=torch.int32, device=self.device)
+        cols = torch.empty(geo.column_index_count, dtype=torch.int32, device=self.device)
+        nbytes = geo.padded_rows * row_stride_bytes if layout == capi.BELL_VALUES_ROW_MAJOR else geo.value_bytes
+        vals = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        capi.check(capi.lib().cb200_bell_lowering_materialize(
+            C.byref(self.input), C.byref(geo), C.c_int32(layout), C.c_uint64(row_stride_bytes),
+            C.c_void_p(pfo.data_ptr()), C.c_void_p(cols.data_ptr() if cols.numel() else None),
+            C.c_void_p(vals.data_ptr() if vals.numel() else None), C.c_void_p(self.workspace.data_ptr()),
+            C.c_uint64(self.workspace.numel()), C.c_void_p(_stream_handle(self.device))))
+        return pfo, cols, vals
+
+
 # ---- host-buffer entry: what a caller with the matrix in host memory runs -------------------
 
 @dataclass

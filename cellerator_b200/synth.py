@@ -153,6 +153,48 @@ def make_qbell_host(rows, cols, block_size, ell_blocks, fill, bits, seed=0, row_
 
 # ---- device generators ---------------------------------------------------------------
 
+def make_lowering_host(rows, features, feature_blocks, mean_nnz, seed=0, value_dtype=np.float32, clustered=True) -> dict:
+    """A canonical CSR with uint32 offsets plus a row order and a feature order, the inputs of the
+    CSR -> Blocked-ELL lowering: `feature_blocks` semantic blocks of random widths, random feature and
+    row permutations (feature_permutation[execution] = canonical, row_permutation[execution row] =
+    canonical row).  clustered: a row draws most of its features from two of the semantic blocks, so
+    that block rows share block columns as ordered single-cell data does."""
+    rng = np.random.default_rng(seed)
+    cuts = np.sort(rng.choice(np.arange(1, features), size=feature_blocks - 1, replace=False)) if feature_blocks > 1 else []
+    fb_offsets = np.concatenate([[0], cuts, [features]]).astype(np.uint32)
+    fperm = rng.permutation(features).astype(np.uint32)
+    rperm = rng.permutation(rows).astype(np.uint32)
+    finv = np.empty(features, dtype=np.uint32)
+    finv[fperm] = np.arange(features, dtype=np.uint32)
+    counts = np.minimum(rng.poisson(mean_nnz, size=rows), features)
+    counts[rng.random(rows) < 0.05] = 0                       # some empty rows
+    row_offsets = np.zeros(rows + 1, dtype=np.uint32)
+    np.cumsum(counts, out=row_offsets[1:])
+    ids = np.empty(int(row_offsets[-1]), dtype=np.uint32)
+    for r in range(rows):
+        k = int(counts[r])
+        if k == 0:
+            continue
+        if clustered and feature_blocks > 1:
+            a, b = rng.integers(0, feature_blocks, size=2)
+            pool = np.concatenate([np.arange(fb_offsets[a], fb_offsets[a + 1]), np.arange(fb_offsets[b], fb_offsets[b + 1])])
+            pool = np.unique(pool)
+            take = min(k, len(pool))
+            execution = rng.choice(pool, size=take, replace=False)
+            if take < k:
+                rest = np.setdiff1d(np.arange(features), execution)
+                execution = np.concatenate([execution, rng.choice(rest, size=k - take, replace=False)])
+        else:
+            execution = rng.choice(features, size=k, replace=False)
+        ids[row_offsets[r]:row_offsets[r + 1]] = np.sort(fperm[execution])
+    if np.issubdtype(value_dtype, np.floating):
+        values = rng.uniform(0.5, 9.0, size=len(ids)).astype(value_dtype)
+    else:
+        values = rng.integers(1, np.iinfo(value_dtype).max, size=len(ids), endpoint=True).astype(value_dtype)
+    return dict(rows=rows, features=features, row_offsets=row_offsets, feature_ids=ids, values=values,
+                fb_offsets=fb_offsets, fperm=fperm, finv=finv, rperm=rperm)
+
+
 def make_qcsr_device(rows, cols, median, sigma, lo, hi, bits, device, seed=0, row_base=0, total_rows=None, **_):
     """Rows [row_base, row_base+rows) of the seeded matrix, generated on `device`.
     Row lengths and per-gene means come from numpy (cheap), everything per-entry from CUDA.

@@ -367,6 +367,86 @@ cb200_launch_binding cb200_session_bind(cb200_session *s, uint32_t stream_index,
 cb200_status cb200_session_synchronize(cb200_session *s);
 void cb200_session_destroy(cb200_session *s);
 
+/* ------------------------------------------------------------------------------------------
+ * CSR -> physical Blocked-ELL lowering on the device: the reference's host loops
+ * query_bell_candidates_host / materialize_bell_candidate_host
+ * (include/Cellerator/compute/math/physical_bell.hh:48-192, src/compute/math/physical_bell.cc:98-200,
+ * src/compute/math/physical_bell_candidates.cc:131-238) for one block size, with the same geometry,
+ * metrics, column indices and value placement, bit for bit.  The reference's identity hashes
+ * (FNV-1a chains over arrays the caller owns) are not computed here.
+ * Conventions (physical_bell.cc:44-58): feature_permutation[execution] = canonical,
+ * inverse_feature_permutation[canonical] = execution, row_permutation[execution row] = canonical row. */
+typedef struct cb200_bell_lowering_input {
+    uint32_t version;
+    size_t size;
+    /* bell_csr_source_view, physical_bell.hh:48-56: canonical feature ids, strictly increasing per row */
+    uint32_t rows, features, nnz, value_size_bytes; /* value_size_bytes 1..16, copied bytewise */
+    const uint32_t *row_offsets; /* device, rows + 1 */
+    const uint32_t *feature_ids; /* device, nnz */
+    const void *values;          /* device, nnz * value_size_bytes */
+    /* bell_semantic_plan_view, physical_bell.hh:61-71 */
+    uint32_t feature_block_count;
+    const uint32_t *feature_block_offsets;       /* HOST, feature_block_count + 1, execution order */
+    const uint32_t *feature_permutation;         /* device, features */
+    const uint32_t *inverse_feature_permutation; /* device, features */
+    /* cellpack::local_cell_order_view (CellPack/local_cell_ordering.hh:47-67), the two maps it carries */
+    const uint32_t *row_permutation;         /* device, rows */
+    const uint32_t *inverse_row_permutation; /* device, rows */
+    int32_t device;
+} cb200_bell_lowering_input;
+
+typedef struct cb200_bell_lowering_policy { /* bell_lowering_policy, physical_bell.hh:90-94 (defaults 64, 64, no limit) */
+    double maximum_value_slot_expansion;
+    double maximum_storage_expansion;
+    uint64_t maximum_persistent_bytes;
+} cb200_bell_lowering_policy;
+
+typedef enum cb200_bell_state { /* bell_candidate_state, physical_bell.hh:15-22 */
+    CB200_BELL_STATE_LEGAL = 0,
+    CB200_BELL_STATE_EMPTY_SOURCE = 1,
+    CB200_BELL_STATE_VALUE_EXPANSION_EXCEEDED = 2,
+    CB200_BELL_STATE_STORAGE_EXPANSION_EXCEEDED = 3,
+    CB200_BELL_STATE_PERSISTENT_BYTES_EXCEEDED = 4,
+    CB200_BELL_STATE_OVERFLOW = 5
+} cb200_bell_state;
+
+typedef struct cb200_bell_geometry { /* bell_candidate_requirements + bell_candidate_metrics, physical_bell.hh:96-123 */
+    uint32_t version;
+    size_t size;
+    int32_t state; /* cb200_bell_state */
+    uint32_t block_size, rows, features, padded_rows, padded_features, block_rows, ell_blocks_per_row, ell_columns;
+    uint64_t feature_block_offset_count, column_index_count, value_bytes;
+    uint64_t occupied_blocks, stored_blocks, dense_value_slots, persistent_bytes, source_bytes;
+    double scalar_occupancy, ell_slot_utilization, value_slot_expansion, storage_expansion;
+} cb200_bell_geometry;
+
+typedef enum cb200_bell_values_layout {
+    /* the reference's: values[((block_row * ell_blocks + slot) * bs + row_in_block) * bs + column_in_block]
+     * (physical_bell.cc:183-189) */
+    CB200_BELL_VALUES_BLOCK_MAJOR = 0,
+    /* execution row r, slot s, column c at r * row_stride_bytes + (s * bs + c) * value_size_bytes: with
+     * one-byte codes this is the packed_values array of a cb200_qbell, whose block_col_idx is the
+     * column_indices array reinterpreted (-1 = 0xffffffff = empty) */
+    CB200_BELL_VALUES_ROW_MAJOR = 1
+} cb200_bell_values_layout;
+
+/* workspace both calls need (device memory, 16-byte aligned) */
+cb200_status cb200_bell_lowering_workspace(const cb200_bell_lowering_input *in, uint64_t *bytes);
+/* Validates the input on the device (maps are inverses, CSR sorted and in range: the checks of
+ * physical_bell.cc:27-80) and computes the geometry and metrics of one block size (8, 16 or 32).
+ * Reads counters back: synchronises `stream`. */
+cb200_status cb200_bell_lowering_query(const cb200_bell_lowering_input *in, uint32_t block_size,
+                                       const cb200_bell_lowering_policy *policy, void *workspace,
+                                       uint64_t workspace_bytes, void *stream, cb200_bell_geometry *out);
+/* Writes padded_feature_block_offsets (feature_block_count + 1), column_indices (column_index_count,
+ * -1 = empty, slots in ascending block column) and the values (zero where nothing is stored) into
+ * device buffers, for a geometry that cb200_bell_lowering_query returned as legal for this input.
+ * Enqueues on `stream`, does not synchronise. */
+cb200_status cb200_bell_lowering_materialize(const cb200_bell_lowering_input *in, const cb200_bell_geometry *geometry,
+                                             int32_t values_layout, uint64_t row_stride_bytes,
+                                             uint32_t *padded_feature_block_offsets, int32_t *column_indices, void *values,
+                                             void *workspace, uint64_t workspace_bytes, void *stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -148,6 +148,48 @@ class _Base:
             raise RuntimeError(f"spmm_reference status {rc}")
         return ref.reshape(m, n)
 
+    # ---- CSR -> physical Blocked-ELL lowering ------------------------------
+    BELL_GEOMETRY = ("state", "padded_rows", "padded_features", "block_rows", "ell_blocks_per_row", "ell_columns",
+                     "column_index_count", "value_bytes", "occupied_blocks", "stored_blocks", "dense_value_slots",
+                     "persistent_bytes", "source_bytes")
+    BELL_METRICS = ("scalar_occupancy", "ell_slot_utilization", "value_slot_expansion", "storage_expansion")
+
+    def bell_lowering(self, row_offsets, feature_ids, values, features, fb_offsets, fperm, rperm, block_size, *,
+                      materialize=True, max_value_expansion=64.0, max_storage_expansion=64.0,
+                      max_persistent=2 ** 63, values_layout=0, row_stride_bytes=0):
+        """query (+ materialize) for one block size.  Returns (status, geometry dict, padded feature-block
+        offsets, column indices, value bytes); the arrays are None for a query or a rejected candidate."""
+        u32 = lambda a: np.ascontiguousarray(a, dtype=np.uint32)
+        ro, fid, fbo, fp, rp = u32(row_offsets), u32(feature_ids), u32(fb_offsets), u32(fperm), u32(rperm)
+        vals = np.ascontiguousarray(values)
+        rows, nnz = len(ro) - 1, len(fid)
+        value_size = vals.dtype.itemsize if vals.ndim == 1 else vals.shape[1] * vals.dtype.itemsize
+        finv = np.zeros(features, dtype=np.uint32)
+        finv[fp % max(features, 1)] = np.arange(len(fp), dtype=np.uint32)
+        rinv = np.zeros(rows, dtype=np.uint32)
+        if rows:
+            rinv[rp % rows] = np.arange(len(rp), dtype=np.uint32)
+        geo, met = np.zeros(13, dtype=np.uint64), np.zeros(4, dtype=np.float64)
+        fn = self._fn("bell_lowering")
+        args = lambda pfo, ci, vo: (
+            C.c_uint32(rows), C.c_uint32(features), C.c_uint32(nnz), C.c_uint32(value_size), _p(ro, C.c_uint32),
+            _p(fid, C.c_uint32), vals.ctypes.data_as(C.c_void_p), C.c_uint32(len(fbo) - 1), _p(fbo, C.c_uint32),
+            _p(fp, C.c_uint32), _p(finv, C.c_uint32), _p(rp, C.c_uint32), _p(rinv, C.c_uint32), C.c_uint32(block_size),
+            C.c_double(max_value_expansion), C.c_double(max_storage_expansion), C.c_uint64(max_persistent),
+            _p(geo, C.c_uint64), _p(met, C.c_double), _p(pfo, C.c_uint32), _p(ci, C.c_int32),
+            None if vo is None else vo.ctypes.data_as(C.c_void_p), C.c_uint64(0 if ci is None else len(ci)),
+            C.c_uint64(0 if vo is None else len(vo)), C.c_int(values_layout), C.c_uint64(row_stride_bytes))
+        status = fn(*args(None, None, None))
+        summary = lambda: {**dict(zip(self.BELL_GEOMETRY, (int(v) for v in geo))), **dict(zip(self.BELL_METRICS, met.tolist()))}
+        if status != 0 or not materialize or int(geo[0]) != 0:
+            return status, summary(), None, None, None
+        pfo = np.zeros(len(fbo), dtype=np.uint32)
+        ci = np.zeros(int(geo[6]), dtype=np.int32)
+        nbytes = int(geo[1]) * row_stride_bytes if values_layout == 1 else int(geo[7])
+        vo = np.full(nbytes, 0xCD, dtype=np.uint8)
+        status = fn(*args(pfo, ci, vo))
+        return status, summary(), pfo, ci, vo
+
     def digest_f32(self, values):
         v = _f32(values)
         out = np.zeros(2, dtype=np.uint64)

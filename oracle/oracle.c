@@ -22,6 +22,7 @@
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #define ORC_API __attribute__((visibility("default")))
@@ -536,4 +537,189 @@ ORC_API void orc_digest_f32(const float *values, uint64_t rows, uint64_t columns
 #undef ORC_MIX
     out[0] = low;
     out[1] = high;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * CSR -> physical Blocked-ELL lowering under a row order and a feature (gene) order.
+ *
+ * Follows query_bell_candidates_host / evaluate (src/compute/math/physical_bell_candidates.cc:131-238,
+ * validation :13-52), validate (src/compute/math/physical_bell.cc:27-80) and
+ * materialize_bell_candidate_host (physical_bell.cc:98-200) for ONE block size.  The identity hashes
+ * of the reference (FNV-1a chains over the arrays) are not part of this restatement: they do not
+ * influence geometry, column indices or values.
+ *
+ * Conventions (physical_bell.cc:44-58): feature_permutation[execution] = canonical,
+ * inverse_feature_permutation[canonical] = execution, row_permutation[execution row] = canonical row.
+ * Every semantic feature block [fb_offsets[b], fb_offsets[b+1]) of the execution order is padded on
+ * its own to a multiple of the block size; a physical block column never spans two semantic blocks.
+ *
+ * geometry[13]: state, padded_rows, padded_features, block_rows, ell_blocks_per_row, ell_columns,
+ *               column_index_count, value_bytes, occupied_blocks, stored_blocks, dense_value_slots,
+ *               persistent_bytes, source_bytes.
+ * metrics[4]:   scalar_occupancy, ell_slot_utilization, value_slot_expansion, storage_expansion.
+ * column_indices == NULL: geometry only.  values_layout 0: block-major, as the reference
+ * (values[(block_row * ell_blocks + slot) * bs^2 + row_in_block * bs + column_in_block]); 1: row-major
+ * with row_stride_bytes per row (value of execution row r, slot s, column c at
+ * r * row_stride_bytes + (s * bs + c) * value_size), the layout of the quantized Blocked-ELL
+ * matrices (include/Cellerator/quantized/blocked_ell.cuh:29-47).
+ * Returns the reference's bell_lowering_status_code (physical_bell.hh:24-34). */
+static uint32_t orc_semantic_block(uint32_t fb_count, const uint32_t *fb_offsets, uint32_t execution) {
+    uint32_t first = 0, last = fb_count;
+    while (first + 1u < last) {
+        const uint32_t middle = first + (last - first) / 2u;
+        if (fb_offsets[middle] <= execution) first = middle;
+        else last = middle;
+    }
+    return first;
+}
+
+ORC_API int orc_bell_lowering(uint32_t rows, uint32_t features, uint32_t nnz, uint32_t value_size,
+                              const uint32_t *row_offsets, const uint32_t *feature_ids, const void *values,
+                              uint32_t fb_count, const uint32_t *fb_offsets, const uint32_t *fperm,
+                              const uint32_t *finv, const uint32_t *rperm, const uint32_t *rinv, uint32_t bs,
+                              double max_value_expansion, double max_storage_expansion, uint64_t max_persistent,
+                              uint64_t *geometry, double *metrics, uint32_t *padded_fb_offsets, int32_t *column_indices,
+                              void *values_out, uint64_t column_capacity, uint64_t value_capacity, int values_layout,
+                              uint64_t row_stride_bytes) {
+    enum { OK = 0, INVALID_ARGUMENT = 1, INVALID_SOURCE = 2, INCOMPATIBLE_PLAN = 3, INCOMPATIBLE_ORDER = 4,
+           INSUFFICIENT_CAPACITY = 5, CANDIDATE_REJECTED = 6, CANDIDATE_MISMATCH = 7, OVERFLOW_ = 8 };
+    if (geometry == NULL || metrics == NULL || !(max_value_expansion > 0.0) || !(max_storage_expansion > 0.0) ||
+        isinf(max_value_expansion) || isinf(max_storage_expansion))
+        return INVALID_ARGUMENT;
+    if (bs != 8u && bs != 16u && bs != 32u) return CANDIDATE_MISMATCH;
+    if (features == 0u || fb_count == 0u || fb_offsets == NULL || fperm == NULL || finv == NULL) return INCOMPATIBLE_PLAN;
+    if (value_size == 0u || value_size > 16u || row_offsets == NULL || (nnz != 0u && (feature_ids == NULL || values == NULL)))
+        return INVALID_SOURCE;
+    if (rperm == NULL || rinv == NULL) return INCOMPATIBLE_ORDER;
+    if (fb_offsets[0] != 0u || fb_offsets[fb_count] != features) return INCOMPATIBLE_PLAN;
+    for (uint32_t b = 0; b < fb_count; ++b)
+        if (fb_offsets[b] >= fb_offsets[b + 1u]) return INCOMPATIBLE_PLAN;
+    const uint64_t marker_count = rows > features ? rows : features;
+    uint32_t *markers = (uint32_t *)calloc(marker_count + 1u, sizeof(uint32_t));
+    uint32_t *block_offsets = (uint32_t *)calloc((size_t)fb_count + 1u, sizeof(uint32_t));
+    if (markers == NULL || block_offsets == NULL) { free(markers); free(block_offsets); return INSUFFICIENT_CAPACITY; }
+    int status = OK;
+    for (uint32_t e = 0; e < features && status == OK; ++e) {
+        const uint32_t c = fperm[e];
+        if (c >= features || markers[c] != 0u || finv[c] != e) status = INCOMPATIBLE_PLAN;
+        else markers[c] = 1u;
+    }
+    memset(markers, 0, (marker_count + 1u) * sizeof(uint32_t));
+    for (uint32_t e = 0; e < rows && status == OK; ++e) {
+        const uint32_t c = rperm[e];
+        if (c >= rows || markers[c] != 0u || rinv[c] != e) status = INCOMPATIBLE_ORDER;
+        else markers[c] = 1u;
+    }
+    if (status == OK && (row_offsets[0] != 0u || row_offsets[rows] != nnz)) status = INVALID_SOURCE;
+    for (uint32_t r = 0; r < rows && status == OK; ++r) {
+        const uint32_t begin = row_offsets[r], end = row_offsets[r + 1u];
+        if (begin > end || end > nnz) { status = INVALID_SOURCE; break; }
+        for (uint32_t i = begin; i < end; ++i)
+            if (feature_ids[i] >= features || (i != begin && feature_ids[i] <= feature_ids[i - 1u])) { status = INVALID_SOURCE; break; }
+    }
+    if (status != OK) { free(markers); free(block_offsets); return status; }
+
+    /* physical_bell_candidates.cc:96-110  every semantic block padded independently */
+    uint64_t physical_blocks = 0;
+    for (uint32_t b = 0; b < fb_count; ++b) {
+        const uint64_t width = fb_offsets[b + 1u] - fb_offsets[b];
+        physical_blocks += (width + bs - 1u) / bs;
+        if (physical_blocks > 0x7fffffffull) { free(markers); free(block_offsets); return OVERFLOW_; }
+        block_offsets[b + 1u] = (uint32_t)physical_blocks;
+    }
+    const uint64_t block_rows = ((uint64_t)rows + bs - 1u) / bs;
+    const uint64_t padded_rows = block_rows * bs, padded_features = physical_blocks * bs;
+    memset(geometry, 0, 13 * sizeof(uint64_t));
+    memset(metrics, 0, 4 * sizeof(double));
+    geometry[0] = 5; /* overflow until proven otherwise */
+    if (padded_rows > 0xffffffffull || padded_features > 0xffffffffull) { free(markers); free(block_offsets); return OK; }
+    uint32_t *epochs = (uint32_t *)calloc((size_t)physical_blocks + 1u, sizeof(uint32_t));
+    if (epochs == NULL) { free(markers); free(block_offsets); return INSUFFICIENT_CAPACITY; }
+#define ORC_PHYSICAL(execution, out_semantic)                                                        \
+    (*(out_semantic) = orc_semantic_block(fb_count, fb_offsets, (execution)),                         \
+     block_offsets[*(out_semantic)] + ((execution) - fb_offsets[*(out_semantic)]) / bs)
+    /* :146-166  distinct physical blocks per block row; ELL width = their maximum */
+    uint32_t maximum = 0;
+    uint64_t occupied = 0;
+    for (uint64_t br = 0; br < block_rows; ++br) {
+        uint32_t active = 0;
+        const uint32_t begin = (uint32_t)(br * bs), end = (uint32_t)(begin + bs < rows ? begin + bs : rows);
+        for (uint32_t er = begin; er < end; ++er) {
+            const uint32_t r = rperm[er];
+            for (uint32_t i = row_offsets[r]; i < row_offsets[r + 1u]; ++i) {
+                uint32_t semantic;
+                const uint32_t p = ORC_PHYSICAL(finv[feature_ids[i]], &semantic);
+                if (epochs[p] != (uint32_t)(br + 1u)) { epochs[p] = (uint32_t)(br + 1u); ++active; }
+            }
+        }
+        occupied += active;
+        if (active > maximum) maximum = active;
+    }
+    const uint64_t stored = block_rows * maximum;
+    const uint64_t slots = stored * bs * bs;
+    const uint64_t bytes = slots * value_size;
+    const uint64_t persistent = stored * 4u + bytes + ((uint64_t)fb_count + 1u) * 4u;
+    const uint64_t source_bytes = ((uint64_t)rows + 1u) * 4u + (uint64_t)nnz * (4u + value_size);
+    geometry[1] = padded_rows; geometry[2] = padded_features; geometry[3] = block_rows; geometry[4] = maximum;
+    geometry[5] = (uint64_t)maximum * bs; geometry[6] = stored; geometry[7] = bytes; geometry[8] = occupied;
+    geometry[9] = stored; geometry[10] = slots; geometry[11] = persistent; geometry[12] = source_bytes;
+    metrics[0] = slots == 0u ? 0.0 : (double)nnz / (double)slots;
+    metrics[1] = stored == 0u ? 0.0 : (double)occupied / (double)stored;
+    metrics[2] = nnz == 0u ? 0.0 : (double)slots / nnz;
+    metrics[3] = source_bytes == 0u ? 0.0 : (double)persistent / (double)source_bytes;
+    if (nnz == 0u) geometry[0] = 1;
+    else if (metrics[2] > max_value_expansion) geometry[0] = 2;
+    else if (metrics[3] > max_storage_expansion) geometry[0] = 3;
+    else if (persistent > max_persistent) geometry[0] = 4;
+    else geometry[0] = 0;
+
+    if (column_indices != NULL) {
+        /* physical_bell.cc:113-200 */
+        if (geometry[0] != 0) status = CANDIDATE_REJECTED;
+        else if (values_layout == 1 && row_stride_bytes < (uint64_t)maximum * bs * value_size) status = INSUFFICIENT_CAPACITY;
+        else if (padded_fb_offsets == NULL || column_capacity < stored || (bytes != 0u && values_out == NULL) ||
+                 value_capacity < (values_layout == 1 ? padded_rows * row_stride_bytes : bytes))
+            status = INSUFFICIENT_CAPACITY;
+        if (status == OK) {
+            for (uint32_t b = 0; b <= fb_count; ++b) padded_fb_offsets[b] = block_offsets[b] * bs;
+            for (uint64_t i = 0; i < stored; ++i) column_indices[i] = -1;
+            memset(values_out, 0, values_layout == 1 ? padded_rows * row_stride_bytes : bytes);
+            const unsigned char *src = (const unsigned char *)values;
+            unsigned char *dst = (unsigned char *)values_out;
+            for (uint64_t br = 0; br < block_rows; ++br) {
+                memset(epochs, 0, ((size_t)physical_blocks + 1u) * sizeof(uint32_t));
+                const uint32_t begin = (uint32_t)(br * bs), end = (uint32_t)(begin + bs < rows ? begin + bs : rows);
+                for (uint32_t er = begin; er < end; ++er) {
+                    const uint32_t r = rperm[er];
+                    for (uint32_t i = row_offsets[r]; i < row_offsets[r + 1u]; ++i) {
+                        uint32_t semantic;
+                        epochs[ORC_PHYSICAL(finv[feature_ids[i]], &semantic)] = 1u;
+                    }
+                }
+                uint32_t slot = 0; /* slots in ascending physical block column */
+                for (uint64_t p = 0; p < physical_blocks; ++p) {
+                    if (epochs[p] == 0u) continue;
+                    epochs[p] = ++slot;
+                    column_indices[br * maximum + slot - 1u] = (int32_t)p;
+                }
+                for (uint32_t er = begin; er < end; ++er) {
+                    const uint32_t r = rperm[er];
+                    for (uint32_t i = row_offsets[r]; i < row_offsets[r + 1u]; ++i) {
+                        uint32_t semantic;
+                        const uint32_t execution = finv[feature_ids[i]];
+                        const uint32_t p = ORC_PHYSICAL(execution, &semantic);
+                        const uint32_t local = (execution - fb_offsets[semantic]) % bs;
+                        const uint64_t s = epochs[p] - 1u;
+                        const uint64_t at = values_layout == 1
+                                                ? (uint64_t)er * row_stride_bytes + (s * bs + local) * value_size
+                                                : ((br * maximum + s) * bs * bs + (uint64_t)(er - begin) * bs + local) * value_size;
+                        memcpy(dst + at, src + (uint64_t)i * value_size, value_size);
+                    }
+                }
+            }
+        }
+    }
+#undef ORC_PHYSICAL
+    free(epochs); free(markers); free(block_offsets);
+    return status;
 }

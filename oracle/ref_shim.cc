@@ -3,12 +3,13 @@
 // TEST INFRASTRUCTURE ONLY.  This translation unit includes the reference's own headers
 // (found through -I at build time; nothing of the reference is copied into this
 // repository) and is linked with the reference's referee.cc / operation.cc /
-// operation_signature.cc.  The resulting library, oracle/_ref/libcellerator_ref.so, is what
+// operation_signature.cc / physical_bell.cc / physical_bell_candidates.cc.  The resulting library, oracle/_ref/libcellerator_ref.so, is what
 // the C restatement in oracle.c is validated against, and it can serve as the CPU baseline.
 //
 // The reference's quantized CSR uses `int` row pointers; the entry points here take the
 // int64 arrays that the rest of this repository uses and narrow them (the caller keeps
 // nnz below 2^31 on this path).
+#include <Cellerator/compute/math/physical_bell.hh>
 #include <Cellerator/compute/math/referee.hh>
 #include <Cellerator/quantized/blocked_ell.cuh>
 #include <Cellerator/quantized/packing.cuh>
@@ -248,6 +249,72 @@ void ref_digest_f32(const float *values, std::uint64_t rows, std::uint64_t colum
     cm::digest_logical_dense(view, &d);
     out[0] = d.low;
     out[1] = d.high;
+}
+
+// query_bell_candidates_host + materialize_bell_candidate_host (physical_bell.hh:172-192) for one
+// block size, same arguments and outputs as orc_bell_lowering in oracle.c.  The reference writes
+// block-major values only (values_layout 0).
+int ref_bell_lowering(std::uint32_t rows, std::uint32_t features, std::uint32_t nnz, std::uint32_t value_size,
+                      const std::uint32_t *row_offsets, const std::uint32_t *feature_ids, const void *values,
+                      std::uint32_t fb_count, const std::uint32_t *fb_offsets, const std::uint32_t *fperm,
+                      const std::uint32_t *finv, const std::uint32_t *rperm, const std::uint32_t *rinv, std::uint32_t bs,
+                      double max_value_expansion, double max_storage_expansion, std::uint64_t max_persistent,
+                      std::uint64_t *geometry, double *metrics, std::uint32_t *padded_fb_offsets,
+                      std::int32_t *column_indices, void *values_out, std::uint64_t column_capacity,
+                      std::uint64_t value_capacity, int values_layout, std::uint64_t) {
+    if (values_layout != 0) return -3;
+    if (bs != 8u && bs != 16u && bs != 32u) return static_cast<int>(cm::bell_lowering_status_code::candidate_mismatch);
+    cm::bell_csr_source_view source{rows, features, nnz, value_size, row_offsets, feature_ids, values};
+    cm::bell_semantic_plan_view plan{};
+    plan.semantic_schema_version = cellpack::packing_plan_semantic_schema_version;
+    plan.full_row_count = rows == 0u ? 1u : rows;
+    plan.feature_count = features;
+    plan.feature_block_count = fb_count;
+    plan.feature_block_geometry_identity = 0x12345678ull;
+    plan.row_domain_identity = 0xabcddcbaull;
+    plan.feature_block_offsets = fb_offsets;
+    plan.feature_permutation = fperm;
+    plan.inverse_feature_permutation = finv;
+    cellpack::local_cell_order_view order{};
+    order.order_schema_version = cellpack::local_cell_order_schema_version;
+    order.signature_algorithm_version = cellpack::local_cell_signature_algorithm_version;
+    order.window_size = 1024u;
+    order.group_width = 32u;
+    order.ordering_identity = 0xfedcba98ull;
+    order.full_row_count = plan.full_row_count;
+    order.row_count = rows;
+    order.feature_block_count = fb_count;
+    order.feature_block_geometry_identity = plan.feature_block_geometry_identity;
+    order.row_domain_identity = plan.row_domain_identity;
+    order.row_permutation = rperm;
+    order.inverse_row_permutation = rinv;
+    cm::bell_lowering_workspace_requirements need;
+    cm::bell_lowering_status st = cm::query_bell_lowering_workspace_requirements(source, plan, order, &need);
+    if (!st) return static_cast<int>(st.code);
+    std::vector<std::uint32_t> markers(need.marker_count + 1u), block_offsets(need.feature_block_offset_count);
+    const cm::bell_lowering_workspace ws{markers.size(), markers.data(), block_offsets.size(), block_offsets.data()};
+    cm::bell_lowering_policy policy;
+    policy.maximum_value_slot_expansion = max_value_expansion;
+    policy.maximum_storage_expansion = max_storage_expansion;
+    policy.maximum_persistent_bytes = static_cast<std::size_t>(max_persistent);
+    cm::bell_candidate_set set;
+    st = cm::query_bell_candidates_host(source, plan, order, policy, ws, &set);
+    if (!st) return static_cast<int>(st.code);
+    const cm::bell_candidate_requirements &c = set.candidates[bs == 8u ? 0 : (bs == 16u ? 1 : 2)];
+    geometry[0] = static_cast<std::uint64_t>(c.state);
+    geometry[1] = c.padded_row_count; geometry[2] = c.padded_feature_count; geometry[3] = c.block_row_count;
+    geometry[4] = c.ell_blocks_per_row; geometry[5] = c.ell_columns; geometry[6] = c.column_index_count;
+    geometry[7] = c.value_bytes; geometry[8] = c.metrics.occupied_blocks; geometry[9] = c.metrics.stored_blocks;
+    geometry[10] = c.metrics.dense_value_slots; geometry[11] = c.metrics.persistent_bytes; geometry[12] = c.metrics.source_bytes;
+    metrics[0] = c.metrics.scalar_occupancy; metrics[1] = c.metrics.ell_slot_utilization;
+    metrics[2] = c.metrics.value_slot_expansion; metrics[3] = c.metrics.storage_expansion;
+    if (column_indices == nullptr) return 0;
+    const cm::bell_candidate_buffers buffers{padded_fb_offsets == nullptr ? 0u : static_cast<std::size_t>(fb_count) + 1u,
+                                             padded_fb_offsets, static_cast<std::size_t>(column_capacity), column_indices,
+                                             static_cast<std::size_t>(value_capacity), values_out};
+    cm::physical_bell_view view;
+    st = cm::materialize_bell_candidate_host(source, plan, order, policy, c, ws, buffers, &view);
+    return static_cast<int>(st.code);
 }
 
 } // extern "C"

@@ -82,6 +82,24 @@ def bell_case(ref, name, rows, cols, block_size, ell_blocks, fill, bits, n, seed
     print(name, "slots", rows * h["ell_cols"])
 
 
+def lowering_case(ref, name, seed):
+    """CSR -> physical Blocked-ELL lowering by the reference's query_bell_candidates_host /
+    materialize_bell_candidate_host, for the three block sizes."""
+    h = synth.make_lowering_host(rows=150, features=420, feature_blocks=5, mean_nnz=14, seed=seed)
+    out = dict(rows=h["rows"], features=h["features"], row_offsets=h["row_offsets"], feature_ids=h["feature_ids"],
+               values=h["values"], fb_offsets=h["fb_offsets"], fperm=h["fperm"], rperm=h["rperm"])
+    for bs in (8, 16, 32):
+        status, geo, pfo, cols, vals = ref.bell_lowering(h["row_offsets"], h["feature_ids"], h["values"], h["features"],
+                                                         h["fb_offsets"], h["fperm"], h["rperm"], bs,
+                                                         max_value_expansion=1e9, max_storage_expansion=1e9)
+        assert status == 0 and geo["state"] == 0
+        out[f"geometry{bs}"] = np.array([geo[k] for k in ref.BELL_GEOMETRY], dtype=np.uint64)
+        out[f"metrics{bs}"] = np.array([geo[k] for k in ref.BELL_METRICS], dtype=np.float64)
+        out[f"padded_offsets{bs}"], out[f"columns{bs}"], out[f"values{bs}"] = pfo, cols, vals
+    np.savez_compressed(os.path.join(OUT, name + ".npz"), **out)
+    print(name, "nnz", len(h["feature_ids"]))
+
+
 if __name__ == "__main__":
     orc.build(ref=True)
     ref = orc.Reference()
@@ -90,3 +108,4 @@ if __name__ == "__main__":
     bell_case(ref, "bell8_small", rows=96, cols=250, block_size=32, ell_blocks=3, fill=0.6, bits=8, n=32, seed=13)
     bell_case(ref, "bell4_small", rows=64, cols=128, block_size=8, ell_blocks=4, fill=0.5, bits=4, n=8, seed=14)
     c1_case(ref)
+    lowering_case(ref, "bell_lowering_small", seed=21)
