@@ -40,6 +40,7 @@ NCU_DRAM_BYTES_PER_NNZ = {
     ("c2_forward", "tensor_blocked"): 4.21,   # profiles/qcsr_fwd_blocked__c2_303104_rows.md
     ("c2_forward", "gene_tiled"): 5.32,       # profiles/qcsr_fwd_tiled__c2_75776_rows.md
     ("c2_forward", "warp_per_row"): 5.21,     # profiles/qcsr_fwd_warp_row__c2_60k_rows.md
+    ("c4_4bit", "tensor_dense"): 12.8,        # profiles/qcsr_fwd_dense__c4_131072_rows.md
 }
 
 
@@ -426,6 +427,118 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def lowering_cpu_seconds(sample):
+    """query + materialize of one block size by the reference's host loops (compiled reference sources
+    when oracle/_ref exists, else the restatement in oracle.c); single-threaded, as shipped."""
+    import oracle as orc
+    orc.build()
+    lib, kind = (orc.Reference(), "reference") if orc.Reference.available() else (orc.Oracle(), "port")
+    t0 = time.perf_counter()
+    status, geo, _, _, _ = lib.bell_lowering(sample["row_offsets"], sample["feature_ids"], sample["values"], sample["features"],
+                                             sample["fb_offsets"], sample["fperm"], sample["rperm"], sample["block_size"])
+    dt = time.perf_counter() - t0
+    if status != 0 or geo["state"] != 0:
+        raise SystemExit(f"CPU lowering failed: status {status}, state {geo['state']}")
+    return dt, kind
+
+
+def lowering_sample(low_in, block_size, sample_rows):
+    per_row = low_in["per_row"]
+    return dict(row_offsets=low_in["row_offsets"][: sample_rows + 1].cpu().numpy().view(np.uint32),
+                feature_ids=low_in["feature_ids"][: sample_rows * per_row].cpu().numpy().view(np.uint32),
+                values=low_in["values"][: sample_rows * per_row].cpu().numpy(), features=low_in["features"],
+                fb_offsets=low_in["fb_offsets"], fperm=low_in["fperm"].cpu().numpy().view(np.uint32),
+                rperm=np.arange(sample_rows, dtype=np.uint32), block_size=block_size)
+
+
+def run_lowering(args):
+    """Workload c5_lowering: the CSR -> physical Blocked-ELL lowering (query + materialize, block size 32)
+    of the Blocked-ELL configuration's shard, one-byte codes.  A step lowers the resident CSR once."""
+    import torch
+    import torch.distributed as dist
+
+    from cellerator_b200 import capi, ops, synth
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = dict(synth.CONFIGS["c5_bell"])
+    bs = cfg["block_size"]
+    rows = args.rows or cfg["rows"] // 8 // bs * bs
+    low_in = synth.make_lowering_device(**{**cfg, "rows": rows}, device=device, seed=rank)
+    low = ops.BellLowering(low_in["row_offsets"], low_in["feature_ids"], low_in["values"], low_in["features"],
+                           low_in["fb_offsets"], low_in["fperm"], low_in["rperm"], device)
+    L = capi.lib()
+    state = {}
+
+    def step():
+        state["geo"] = low.query(bs)
+        state["out"] = None                      # the previous step's buffers go back to the allocator first
+        state["out"] = low.materialize(state["geo"])
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    launches0 = L.cb200_kernel_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    launches = L.cb200_kernel_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+    units = torch.tensor([float(low.nnz)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(units, op=dist.ReduceOp.SUM)
+    ms_per_step = float(t.item()) / args.steps
+    geo = state["geo"]
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+    # compulsory traffic: offsets, ids (read by the query and again by the fill), codes, the zeroed and
+    # written value array, the column indices
+    bytes_ = (2 * (rows + 1) * 4 + 2 * low.nnz * 4 + low.nnz * low.value_size + geo.value_bytes
+              + geo.column_index_count * 4)
+    peak, peak_kind = measured_peak()
+    achieved = bytes_ / (ms_per_step * 1e-3) / 1e9
+    result = {
+        "metric": "CSR -> Blocked-ELL lowering throughput (query + materialize)",
+        "value": float(units.item()) / (ms_per_step * 1e-3) / 1e9, "unit": "Gnnz/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8 codes copied bytewise, u32 indices",
+        "data": "synthetic (seeded, device-generated; shape of the Blocked-ELL configuration)",
+        "config": {"workload": "c5_lowering", "cells_per_gpu": rows, "genes": cfg["cols"], "block_size": bs,
+                   "ell_blocks_per_row": geo.ell_blocks_per_row, "units_per_gpu": low.nnz,
+                   "value_bytes": int(geo.value_bytes), "parallelism": f"row-sharded x{world}",
+                   "l2": "inputs and outputs larger than L2 (126 MB); no flush needed"},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_kind, "kernel_ms": ms_per_step,
+                     "algorithmic_bytes_per_launch": bytes_},
+    }
+    if world == 1 and not args.no_cpu:
+        sample_rows = min(rows, 20000 // bs * bs)
+        dt, kind = lowering_cpu_seconds(lowering_sample(low_in, bs, sample_rows))
+        nnz_s = sample_rows * low_in["per_row"]
+        result["cpu_baseline"] = {"value": nnz_s / dt / 1e9, "unit": "Gnnz/s", "cores": 1, "kind": kind,
+                                  "sample": f"first {sample_rows} rows ({nnz_s} stored entries), query + materialize, "
+                                            f"the reference's single-threaded host loops", "seconds": dt}
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     """The reference's CPU implementation of the path, timed on the host cores (rank 0 only)."""
     rank = int(os.environ.get("RANK", "0"))
@@ -435,7 +548,7 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     threads = cpu_threads()
     kind = "transpose" if args.workload == "c3_transpose" else "forward"
-    if args.workload == "c5_bell":
+    if args.workload in ("c5_bell", "c5_lowering"):
         print(json.dumps({"impl": "reference", "unavailable": "the CPU arm covers the CSR workloads only"}))
         return
     sample_rows = args.cpu_rows_per_thread * threads
@@ -485,7 +598,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2_forward", choices=["c2_forward", "c3_transpose", "c4_4bit", "c5_bell"])
+    ap.add_argument("--workload", default="c2_forward", choices=["c2_forward", "c3_transpose", "c4_4bit", "c5_bell", "c5_lowering"])
     ap.add_argument("--rows", type=int, default=0, help="override cells per GPU (profiling on a small case)")
     ap.add_argument("--no-prepare-matrix", action="store_true",
                     help="do not hand the matrix to prepare: no window-blocked copy, CSR-only schedules")
@@ -504,6 +617,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c5_lowering":
+        run_lowering(args)
     else:
         run_ours(args)
 

@@ -195,6 +195,29 @@ def make_lowering_host(rows, features, feature_blocks, mean_nnz, seed=0, value_d
                 fb_offsets=fb_offsets, fperm=fperm, finv=finv, rperm=rperm)
 
 
+def make_lowering_device(rows, cols, block_size, ell_blocks, fill, device, seed=0, **_):
+    """The Blocked-ELL configuration as a canonical CSR of one-byte codes on the device (uint32 offsets
+    and feature ids, held as int32 tensors): every block row of `block_size` cells touches `ell_blocks`
+    distinct block columns, and a cell stores round(fill * ell_blocks * block_size) of those slots.
+    Identity row and feature orders, one semantic feature block."""
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    per_row = int(round(fill * ell_blocks * block_size))
+    block_rows = (rows + block_size - 1) // block_size
+    patterns = torch.stack([torch.randperm(cols // block_size, generator=g)[:ell_blocks] for _ in range(256)])
+    pattern = patterns[torch.randint(0, 256, (block_rows,), generator=g)].repeat_interleave(block_size, dim=0)[:rows].to(device)
+    gd = torch.Generator(device=device).manual_seed(seed + 1)
+    pick = torch.rand(rows, ell_blocks * block_size, device=device, generator=gd).argsort(dim=1)[:, :per_row]
+    feature = (pattern.gather(1, pick // block_size) * block_size + pick % block_size).sort(dim=1).values.to(torch.int32)
+    del pick, pattern
+    row_offsets = (torch.arange(rows + 1, device=device, dtype=torch.int64) * per_row).to(torch.int32)
+    values = torch.randint(1, 256, (rows * per_row,), device=device, dtype=torch.uint8, generator=gd)
+    return dict(row_offsets=row_offsets, feature_ids=feature.reshape(-1), values=values, features=cols,
+                fb_offsets=np.array([0, cols], dtype=np.uint32),
+                fperm=torch.arange(cols, dtype=torch.int32, device=device),
+                rperm=torch.arange(rows, dtype=torch.int32, device=device), per_row=per_row)
+
+
 def make_qcsr_device(rows, cols, median, sigma, lo, hi, bits, device, seed=0, row_base=0, total_rows=None, **_):
     """Rows [row_base, row_base+rows) of the seeded matrix, generated on `device`.
     Row lengths and per-gene means come from numpy (cheap), everything per-entry from CUDA.
