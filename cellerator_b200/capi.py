@@ -111,6 +111,15 @@ class BellGeometry(C.Structure):
 BELL_VALUES_BLOCK_MAJOR, BELL_VALUES_ROW_MAJOR = 0, 1
 
 
+class DensePack(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("feature_permutation", C.c_void_p),
+                ("source", C.c_void_p), ("features", C.c_uint32), ("columns", C.c_uint64),
+                ("leading_dimension", C.c_uint64), ("source_col_major", C.c_int32), ("value_size_bytes", C.c_uint32),
+                ("feature_block_count", C.c_uint32), ("feature_block_offsets", C.c_void_p),
+                ("padded_feature_block_offsets", C.c_void_p), ("packed", C.c_void_p),
+                ("packed_capacity_bytes", C.c_uint64), ("status_word", C.c_void_p), ("device", C.c_int32)]
+
+
 class SessionOptions(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32),
                 ("owned_stream_count", C.c_uint32), ("external_stream_count", C.c_uint32),
@@ -131,6 +140,7 @@ EXPORTED_SYMBOLS = [
     "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_prepared_persistent_bytes", "cb200_spmm_run", "cb200_kernel_launch_count",
     "cb200_qcsr_forward_static",
     "cb200_bell_lowering_workspace", "cb200_bell_lowering_query", "cb200_bell_lowering_materialize",
+    "cb200_pack_dense_operand",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
 ]

@@ -461,3 +461,116 @@ extern "C" cb200_status cb200_bell_lowering_materialize(const cb200_bell_lowerin
     return bs == 8u ? launch_fill_vs<8>(p, grid, smem, stream)
                     : (bs == 16u ? launch_fill_vs<16>(p, grid, smem, stream) : launch_fill_vs<32>(p, grid, smem, stream));
 }
+
+// ---------------------------------------------------------------------------------------------
+// Feature-order pack of a dense operand (the W that goes with a lowered matrix):
+//     packed[execution][column] = source[feature_permutation[execution]][column],
+// contiguous row-major.  Reference counterpart: pack_dense_operand_cuda
+// (src/compute/math/packed_dense_operand.cu:131-170,227-262; one thread per element, grid-stride).
+// Here a row-major source whose rows are 16-byte aligned moves as 16-byte pieces (a bf16 row of 64
+// columns is 8 of them), anything else element by element.
+namespace cb200 {
+namespace {
+
+template<typename T>
+__global__ void __launch_bounds__(256) pack_dense_kernel(const std::uint32_t *fperm, const T *source, std::uint32_t rows,
+                                                         std::uint64_t columns, std::uint64_t ld, int col_major,
+                                                         std::uint32_t features, T *packed, unsigned *flags) {
+    const std::uint64_t count = static_cast<std::uint64_t>(rows) * columns;
+    for (std::uint64_t i = static_cast<std::uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<std::uint64_t>(blockDim.x) * gridDim.x) {
+        const std::uint32_t execution = static_cast<std::uint32_t>(i / columns);
+        const std::uint64_t column = i - static_cast<std::uint64_t>(execution) * columns;
+        const std::uint32_t feature = __ldg(fperm + execution);
+        if (feature >= features) { // physical_view_status invalid_geometry; nothing is read out of range
+            if (column == 0u) atomicOr(flags, 1u);
+            continue;
+        }
+        packed[i] = source[col_major ? column * ld + feature : static_cast<std::uint64_t>(feature) * ld + column];
+    }
+}
+
+struct bytes16 { uint4 v; };
+struct bytes_n { unsigned char b; };
+
+template<typename T>
+cb200_status launch_pack(const std::uint32_t *fperm, const void *source, std::uint32_t rows, std::uint64_t columns,
+                         std::uint64_t ld, int col_major, std::uint32_t features, void *packed, unsigned *flags,
+                         cudaStream_t stream) {
+    const std::uint64_t count = static_cast<std::uint64_t>(rows) * columns;
+    if (count == 0u) return CB200_STATUS_SUCCESS;
+    const unsigned grid = static_cast<unsigned>(std::min<std::uint64_t>((count + 255u) / 256u, 148u * 32u));
+    pack_dense_kernel<T><<<grid, 256, 0, stream>>>(fperm, static_cast<const T *>(source), rows, columns, ld, col_major, features,
+                                                   static_cast<T *>(packed), flags);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+} // namespace
+} // namespace cb200
+
+extern "C" cb200_status cb200_pack_dense_operand(const cb200_dense_pack *d, void *stream_handle) {
+    using namespace cb200;
+    clear_error();
+    if (d == nullptr || d->version != CB200_ABI_VERSION || d->size < sizeof(cb200_dense_pack))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_dense_pack header");
+    const std::uint32_t vs = d->value_size_bytes;
+    if (vs != 1u && vs != 2u && vs != 4u && vs != 8u && vs != 16u)
+        return fail(CB200_STATUS_UNSUPPORTED, "value size %u is not 1, 2, 4, 8 or 16 bytes", vs);
+    if (d->feature_permutation == nullptr || d->status_word == nullptr ||
+        (d->features != 0u && d->columns != 0u && (d->source == nullptr || d->packed == nullptr)))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "null argument");
+    if (d->packed == d->source && d->source != nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "packed output aliases its source");
+    if (d->leading_dimension < (d->source_col_major ? d->features : d->columns))
+        return fail(CB200_STATUS_INVALID_SHAPE, "leading dimension smaller than the contiguous extent");
+    const std::uint32_t blocks = d->feature_block_count;
+    std::uint64_t packed_rows = d->features;
+    if (blocks != 0u) {
+        if (d->feature_block_offsets == nullptr || d->padded_feature_block_offsets == nullptr)
+            return fail(CB200_STATUS_INVALID_ARGUMENT, "feature blocks without their offsets");
+        if (d->feature_block_offsets[0] != 0u || d->feature_block_offsets[blocks] != d->features || d->padded_feature_block_offsets[0] != 0u)
+            return fail(CB200_STATUS_INVALID_SHAPE, "feature-block endpoints are invalid");
+        for (std::uint32_t b = 0; b < blocks; ++b)
+            if (d->feature_block_offsets[b + 1u] <= d->feature_block_offsets[b] ||
+                d->padded_feature_block_offsets[b + 1u] - d->padded_feature_block_offsets[b] <
+                    d->feature_block_offsets[b + 1u] - d->feature_block_offsets[b])
+                return fail(CB200_STATUS_INVALID_SHAPE, "a padded feature block is narrower than the block it pads");
+        packed_rows = d->padded_feature_block_offsets[blocks];
+    }
+    const std::uint64_t need = packed_rows * d->columns * vs;
+    if (d->packed_capacity_bytes < need)
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "packed operand needs %llu bytes, %llu given",
+                    static_cast<unsigned long long>(need), static_cast<unsigned long long>(d->packed_capacity_bytes));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    device_scope scope(d->device);
+    CB200_CUDA_OK(scope.status);
+    CB200_CUDA_OK(cudaMemsetAsync(d->status_word, 0, sizeof(unsigned), stream));
+    if (blocks != 0u && need != 0u) CB200_CUDA_OK(cudaMemsetAsync(d->packed, 0, need, stream)); // rows of the padding
+
+    // a row-major source with 16-byte aligned rows moves as 16-byte pieces
+    const std::uint64_t row_bytes = d->columns * vs;
+    const bool wide = !d->source_col_major && row_bytes % 16u == 0u && (d->leading_dimension * vs) % 16u == 0u &&
+                      reinterpret_cast<std::uintptr_t>(d->source) % 16u == 0u && reinterpret_cast<std::uintptr_t>(d->packed) % 16u == 0u;
+    const std::uint32_t piece = wide ? 16u : vs;
+    const std::uint64_t columns = row_bytes / piece, ld = d->leading_dimension * vs / piece;
+    const std::uint32_t runs = blocks == 0u ? 1u : blocks;
+    for (std::uint32_t b = 0; b < runs; ++b) {
+        const std::uint32_t first = blocks == 0u ? 0u : d->feature_block_offsets[b];
+        const std::uint32_t rows = blocks == 0u ? d->features : d->feature_block_offsets[b + 1u] - first;
+        const std::uint64_t row0 = blocks == 0u ? 0u : d->padded_feature_block_offsets[b];
+        void *dst = static_cast<unsigned char *>(d->packed) + row0 * row_bytes;
+        const std::uint32_t *perm = d->feature_permutation + first;
+        unsigned *flags = static_cast<unsigned *>(d->status_word);
+        cb200_status st;
+        switch (piece) {
+        case 1: st = launch_pack<unsigned char>(perm, d->source, rows, columns, ld, d->source_col_major, d->features, dst, flags, stream); break;
+        case 2: st = launch_pack<unsigned short>(perm, d->source, rows, columns, ld, d->source_col_major, d->features, dst, flags, stream); break;
+        case 4: st = launch_pack<unsigned>(perm, d->source, rows, columns, ld, d->source_col_major, d->features, dst, flags, stream); break;
+        case 8: st = launch_pack<uint2>(perm, d->source, rows, columns, ld, d->source_col_major, d->features, dst, flags, stream); break;
+        default: st = launch_pack<uint4>(perm, d->source, rows, columns, ld, d->source_col_major, d->features, dst, flags, stream); break;
+        }
+        if (st != CB200_STATUS_SUCCESS) return st;
+    }
+    return CB200_STATUS_SUCCESS;
+}

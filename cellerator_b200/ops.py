@@ -397,6 +397,36 @@ class BellLowering:
         return pfo, cols, vals
 
 
+def pack_dense_operand(source: torch.Tensor, fperm: torch.Tensor, col_major=False, fb_offsets=None,
+                       padded_offsets=None) -> torch.Tensor:
+    """packed[execution] = source[fperm[execution]] (cb200_pack_dense_operand).  source: 2-D, [features][columns]
+    or, with col_major, [columns][features]; any stride along dim 0.  With fb_offsets / padded_offsets (host
+    arrays) the rows follow the padded physical feature order of a Blocked-ELL lowering."""
+    assert source.dim() == 2 and source.stride(1) == 1
+    features, columns = (source.shape[1], source.shape[0]) if col_major else source.shape
+    d = capi.header(capi.DensePack())
+    d.feature_permutation, d.source = fperm.data_ptr(), source.data_ptr()
+    d.features, d.columns, d.leading_dimension = features, columns, source.stride(0)
+    d.source_col_major, d.value_size_bytes = int(col_major), source.element_size()
+    rows = features
+    keep = None
+    if fb_offsets is not None:
+        fbo = np.ascontiguousarray(fb_offsets, dtype=np.uint32)
+        pfo = np.ascontiguousarray(padded_offsets, dtype=np.uint32)
+        d.feature_block_count, d.feature_block_offsets, d.padded_feature_block_offsets = len(fbo) - 1, fbo.ctypes.data, pfo.ctypes.data
+        rows, keep = int(pfo[-1]), (fbo, pfo)
+    out = torch.empty(rows, columns, dtype=source.dtype, device=source.device)
+    status = torch.zeros(1, dtype=torch.int32, device=source.device)
+    d.packed, d.packed_capacity_bytes, d.status_word = out.data_ptr(), out.numel() * out.element_size(), status.data_ptr()
+    d.device = source.device.index if source.device.index is not None else torch.cuda.current_device()
+    capi.check(capi.lib().cb200_pack_dense_operand(C.byref(d), C.c_void_p(_stream_handle(source.device))))
+    if int(status.item()) != 0:
+        raise capi.Cb200Error(capi.STATUS_INVALID_SHAPE if hasattr(capi, "STATUS_INVALID_SHAPE") else 2,
+                              "invalid geometry: feature permutation is out of range")
+    del keep
+    return out
+
+
 # ---- host-buffer entry: what a caller with the matrix in host memory runs -------------------
 
 @dataclass

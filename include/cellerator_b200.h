@@ -447,6 +447,39 @@ cb200_status cb200_bell_lowering_materialize(const cb200_bell_lowering_input *in
                                              uint32_t *padded_feature_block_offsets, int32_t *column_indices, void *values,
                                              void *workspace, uint64_t workspace_bytes, void *stream);
 
+/* Feature-order pack of a dense operand on the device, pack_dense_operand_cuda
+ * (include/Cellerator/compute/math/packed_dense_operand.hh:65-70,
+ * src/compute/math/packed_dense_operand.cu:131-170,227-262):
+ *     packed[execution][column] = source[feature_permutation[execution]][column],
+ * contiguous row-major from a row- or column-major source, values copied bytewise.
+ * With feature_block_count != 0 the rows follow the padded physical feature order of a Blocked-ELL
+ * lowering instead (cb200_bell_lowering_materialize's padded_feature_block_offsets, here on the
+ * HOST): semantic block b fills rows [padded[b], padded[b] + width_b), the rows of the padding are
+ * zero, and the operand has padded[feature_block_count] rows -- the W the lowered matrix multiplies.
+ * Enqueues on `stream`.  status_word (device, 4 bytes) is cleared first and holds 1 afterwards when a
+ * permutation entry was out of range (those rows are left unwritten; the reference's
+ * invalid_geometry). */
+typedef struct cb200_dense_pack {
+    uint32_t version;
+    size_t size;
+    const uint32_t *feature_permutation; /* device, features */
+    const void *source;                  /* device */
+    uint32_t features;
+    uint64_t columns;
+    uint64_t leading_dimension; /* of the source, in elements */
+    int32_t source_col_major;   /* dense_layout_kind: 0 row-major [feature][column], 1 column-major */
+    uint32_t value_size_bytes;  /* 1, 2, 4, 8 or 16 */
+    uint32_t feature_block_count;                 /* 0: plain execution order */
+    const uint32_t *feature_block_offsets;        /* HOST, feature_block_count + 1 */
+    const uint32_t *padded_feature_block_offsets; /* HOST, feature_block_count + 1 */
+    void *packed;                                 /* device */
+    uint64_t packed_capacity_bytes;
+    void *status_word; /* device, 4 bytes */
+    int32_t device;
+} cb200_dense_pack;
+
+cb200_status cb200_pack_dense_operand(const cb200_dense_pack *pack, void *stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

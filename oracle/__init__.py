@@ -190,6 +190,25 @@ class _Base:
         status = fn(*args(pfo, ci, vo))
         return status, summary(), pfo, ci, vo
 
+    def pack_dense_operand(self, source, fperm, *, col_major=False, fb_offsets=None, padded_offsets=None):
+        """packed[execution] = source[fperm[execution]] (2-D source [features][columns], or its transpose when
+        col_major); with feature blocks, in the padded physical feature order of a Blocked-ELL lowering."""
+        src = np.ascontiguousarray(source)
+        features, columns = (src.shape[1], src.shape[0]) if col_major else src.shape
+        fp = np.ascontiguousarray(fperm, dtype=np.uint32)
+        fbo = None if fb_offsets is None else np.ascontiguousarray(fb_offsets, dtype=np.uint32)
+        pfo = None if padded_offsets is None else np.ascontiguousarray(padded_offsets, dtype=np.uint32)
+        rows = features if fbo is None else int(pfo[-1])
+        out = np.full((rows, columns), 0, dtype=src.dtype)
+        rc = self._fn("pack_dense_operand")(
+            C.c_uint32(features), C.c_uint64(columns), C.c_uint64(src.shape[1]), C.c_int(int(col_major)),
+            C.c_uint32(src.dtype.itemsize), _p(fp, C.c_uint32), src.ctypes.data_as(C.c_void_p),
+            C.c_uint32(0 if fbo is None else len(fbo) - 1), _p(fbo, C.c_uint32), _p(pfo, C.c_uint32),
+            out.ctypes.data_as(C.c_void_p))
+        if rc != 0:
+            raise RuntimeError(f"pack_dense_operand status {rc}")
+        return out
+
     def digest_f32(self, values):
         v = _f32(values)
         out = np.zeros(2, dtype=np.uint64)

@@ -723,3 +723,36 @@ ORC_API int orc_bell_lowering(uint32_t rows, uint32_t features, uint32_t nnz, ui
     free(epochs); free(markers); free(block_offsets);
     return status;
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * Feature-order pack of a dense operand: packed[execution][column] = source[feature_permutation[execution]][column],
+ * contiguous row-major, from a row- or column-major source.  Follows pack_dense_operand_host
+ * (src/compute/math/packed_dense_operand.cu:186-226).  That file needs nvcc and the CUDA runtime to
+ * build, so it is not part of oracle/_ref; this restatement is pinned on the expected vector of the
+ * reference's own test (tests/math_execution_csr_test.cu:93-112).
+ * With fb_count != 0 the rows are laid out in the padded physical feature order of a Blocked-ELL
+ * lowering: semantic block b occupies rows [padded_offsets[b], padded_offsets[b] + width_b), the
+ * rows of the padding are zero, and `packed` holds padded_offsets[fb_count] rows.
+ * Returns 0, or 1 when a permutation entry is out of range (physical_view_status invalid_geometry). */
+ORC_API int orc_pack_dense_operand(uint32_t features, uint64_t columns, uint64_t ld, int col_major, uint32_t value_size,
+                                   const uint32_t *fperm, const void *source, uint32_t fb_count,
+                                   const uint32_t *fb_offsets, const uint32_t *padded_offsets, void *packed) {
+    const unsigned char *src = (const unsigned char *)source;
+    unsigned char *dst = (unsigned char *)packed;
+    if (fb_count != 0u) memset(dst, 0, (size_t)padded_offsets[fb_count] * columns * value_size);
+    uint32_t block = 0;
+    for (uint32_t execution = 0; execution < features; ++execution) {
+        const uint32_t feature = fperm[execution];
+        if (feature >= features) return 1;
+        uint64_t row = execution;
+        if (fb_count != 0u) {
+            while (fb_offsets[block + 1u] <= execution) ++block;
+            row = (uint64_t)padded_offsets[block] + (execution - fb_offsets[block]);
+        }
+        for (uint64_t column = 0; column < columns; ++column) {
+            const uint64_t at = col_major ? column * ld + feature : (uint64_t)feature * ld + column;
+            memcpy(dst + (row * columns + column) * value_size, src + at * value_size, value_size);
+        }
+    }
+    return 0;
+}

@@ -155,3 +155,66 @@ def test_full_scale_properties(cuda_device):
     assert bool((c >= 0).all()) and bool((c[:, 1:] > c[:, :-1]).all())
     assert int((vals != 0).sum()) == rows * per_row
     assert int(vals.sum(dtype=torch.int64)) == int(values.sum(dtype=torch.int64))
+
+
+def test_pack_dense_operand_kat_and_random(cuda_device, oracle):
+    """pack_dense_operand_cuda's contract: the reference test's vector (tests/math_execution_csr_test.cu:93-112),
+    then random shapes, value sizes, both source layouts, strided sources, and the padded physical order."""
+    src = torch.arange(1, 9, dtype=torch.float32, device=cuda_device).reshape(4, 2)
+    perm = torch.tensor([2, 0, 3, 1], dtype=torch.int32, device=cuda_device)
+    assert ops.pack_dense_operand(src, perm).flatten().tolist() == [5.0, 6.0, 1.0, 2.0, 7.0, 8.0, 3.0, 4.0]
+    assert ops.pack_dense_operand(src.t().contiguous(), perm, col_major=True).flatten().tolist() == [5.0, 6.0, 1.0, 2.0, 7.0, 8.0, 3.0, 4.0]
+    rng = np.random.default_rng(0)
+    for features, columns, dtype, pad in [(1000, 64, torch.bfloat16, 0), (333, 7, torch.float32, 3), (257, 128, torch.float64, 0),
+                                          (512, 33, torch.uint8, 5), (4096, 256, torch.bfloat16, 8)]:
+        full = torch.from_numpy(rng.integers(0, 200, size=(features, columns + pad)).astype(np.float32)).to(cuda_device).to(dtype)
+        view = full[:, :columns]
+        fperm = rng.permutation(features).astype(np.uint32)
+        d_perm = torch.from_numpy(fperm.view(np.int32)).to(cuda_device)
+        host = view.cpu().contiguous().view(torch.uint8).numpy().reshape(features, -1)       # bytes of every row
+        want = oracle.pack_dense_operand(host, fperm)
+        got = ops.pack_dense_operand(view, d_perm)
+        assert np.array_equal(got.cpu().view(torch.uint8).numpy().reshape(features, -1), want)
+        col = view.t().contiguous()                                                          # [columns][features]
+        got_c = ops.pack_dense_operand(col, d_perm, col_major=True)
+        assert torch.equal(got_c, got)
+        cuts = np.sort(rng.choice(np.arange(1, features), size=3, replace=False))
+        fbo = np.concatenate([[0], cuts, [features]]).astype(np.uint32)
+        widths = np.diff(fbo.astype(np.int64))
+        pfo = np.concatenate([[0], np.cumsum((widths + 31) // 32 * 32)]).astype(np.uint32)
+        want_p = oracle.pack_dense_operand(host, fperm, fb_offsets=fbo, padded_offsets=pfo)
+        got_p = ops.pack_dense_operand(view, d_perm, fb_offsets=fbo, padded_offsets=pfo)
+        assert np.array_equal(got_p.cpu().view(torch.uint8).numpy().reshape(int(pfo[-1]), -1), want_p)
+    bad = torch.tensor([2, 0, 9, 1], dtype=torch.int32, device=cuda_device)
+    with pytest.raises(capi.Cb200Error, match="invalid geometry"):
+        ops.pack_dense_operand(src, bad)
+
+
+def test_permuted_lowering_and_packed_operand_project_like_the_csr(cuda_device, oracle):
+    """The two prepare-time steps together, under random row and feature orders and three semantic blocks:
+    lowered codes (row-major) x W packed in the padded physical order = the CSR projection, with the rows
+    of the result in execution order."""
+    rng = np.random.default_rng(17)
+    rows, genes, n, bs = 32 * 30 + 11, 1500, 128, 32
+    h = synth.make_lowering_host(rows=rows, features=genes, feature_blocks=3, mean_nnz=50, seed=4, value_dtype=np.uint8)
+    low = ops.BellLowering(h["row_offsets"], h["feature_ids"], h["values"], genes, h["fb_offsets"], h["fperm"], h["rperm"], cuda_device)
+    geo = low.query(bs, max_value_expansion=1e9, max_storage_expansion=1e9)
+    stride = (geo.ell_columns + 15) // 16 * 16
+    pfo, cols, codes = low.materialize(geo, layout=capi.BELL_VALUES_ROW_MAJOR, row_stride_bytes=stride)
+    scales = rng.uniform(0.01, 0.05, genes).astype(np.float32)
+    w = torch.from_numpy(rng.normal(0, 0.02, (genes, n)).astype(np.float32)).to(cuda_device)
+    pfo_host = pfo.cpu().numpy().view(np.uint32)
+    w_phys = ops.pack_dense_operand(w, low.fperm, fb_offsets=h["fb_offsets"], padded_offsets=pfo_host)
+    s_phys = ops.pack_dense_operand(torch.from_numpy(scales).to(cuda_device)[:, None].contiguous(), low.fperm,
+                                    fb_offsets=h["fb_offsets"], padded_offsets=pfo_host)[:, 0].contiguous()
+    bell = ops.QuantizedBell.from_host(dict(rows=rows, cols=geo.padded_features, block_size=bs, ell_cols=geo.ell_columns,
+                                            row_stride_bytes=stride, bits=8, policy=1,
+                                            block_col_idx=cols.cpu().numpy().view(np.uint32),
+                                            packed=codes.cpu().numpy()[:rows * stride], scales=s_phys.cpu().numpy(),
+                                            offsets=None), cuda_device)
+    csr = ops.QuantizedCsr.from_host(dict(rows=rows, cols=genes, bits=8, policy=1, row_ptr=h["row_offsets"].astype(np.int64),
+                                          packed_row_ptr=None, col_idx=h["feature_ids"].astype(np.int32), packed=h["values"],
+                                          scales=scales, offsets=None), cuda_device)
+    y_bell = ops.bell_forward(bell, w_phys)                      # rows in execution order
+    y_csr = ops.spmm_forward(csr, w)                             # rows in canonical order
+    assert torch.allclose(y_bell, y_csr[low.rperm.long()], rtol=1e-4, atol=1e-5)
