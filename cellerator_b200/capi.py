@@ -111,6 +111,18 @@ class BellGeometry(C.Structure):
 BELL_VALUES_BLOCK_MAJOR, BELL_VALUES_ROW_MAJOR = 0, 1
 
 
+class PublicLayout(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("layout", C.c_int32), ("rows", C.c_uint32),
+                ("cols", C.c_uint32), ("nnz", C.c_uint32), ("block_size", C.c_uint32), ("ell_cols", C.c_uint32),
+                ("row_stride_bytes", C.c_uint32), ("bits", C.c_uint32), ("decode_policy", C.c_uint32),
+                ("major_ptr", C.c_void_p), ("minor_idx", C.c_void_p), ("block_col_idx", C.c_void_p),
+                ("packed_values", C.c_void_p), ("column_scales", C.c_void_p), ("column_offsets", C.c_void_p),
+                ("row_offsets", C.c_void_p)]
+
+
+PUBLIC_LAYOUT_QUANTIZED_BLOCKED_ELL, PUBLIC_LAYOUT_QUANTIZED_CSR = 4, 5
+
+
 class DensePack(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("feature_permutation", C.c_void_p),
                 ("source", C.c_void_p), ("features", C.c_uint32), ("columns", C.c_uint64),
@@ -141,6 +153,7 @@ EXPORTED_SYMBOLS = [
     "cb200_qcsr_forward_static",
     "cb200_bell_lowering_workspace", "cb200_bell_lowering_query", "cb200_bell_lowering_materialize",
     "cb200_pack_dense_operand",
+    "cb200_public_projection_scratch", "cb200_public_projection_forward", "cb200_public_projection_backward_rhs",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
 ]

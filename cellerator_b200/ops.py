@@ -427,6 +427,50 @@ def pack_dense_operand(source: torch.Tensor, fperm: torch.Tensor, col_major=Fals
     return out
 
 
+# ---- the reference's public projection calls, routed ------------------------------------------
+
+def public_layout(x) -> capi.PublicLayout:
+    """cellerator_sparse_layout_desc fields of a quantized matrix: 32-bit row offsets for CSR (a uint32 copy
+    of row_ptr is attached to the descriptor), the arrays of the matrix otherwise."""
+    l = capi.header(capi.PublicLayout())
+    l.rows, l.cols, l.bits, l.decode_policy = x.rows, x.cols, x.bits, x.policy
+    l.packed_values = x.packed.data_ptr()
+    l.column_scales = x.scales.data_ptr() if x.scales is not None else None
+    off = x.offsets.data_ptr() if x.offsets is not None else None
+    if x.policy == capi.DECODE_COLUMN_SCALE_ROW_OFFSET:
+        l.row_offsets = off
+    else:
+        l.column_offsets = off
+    if isinstance(x, QuantizedBell):
+        l.layout = capi.PUBLIC_LAYOUT_QUANTIZED_BLOCKED_ELL
+        l.block_size, l.ell_cols, l.row_stride_bytes = x.block_size, x.ell_cols, x.row_stride_bytes
+        l.block_col_idx = x.block_col_idx.data_ptr()
+        l._keep = (x,)
+    else:
+        l.layout = capi.PUBLIC_LAYOUT_QUANTIZED_CSR
+        l.nnz = x.nnz
+        narrow = x.row_ptr.to(torch.int32)                     # nnz < 2^32: the bits of a uint32
+        l.major_ptr, l.minor_idx = narrow.data_ptr(), x.col_idx.data_ptr()
+        l._keep = (x, narrow)
+    return l
+
+
+def public_projection(x, dense: torch.Tensor, backward=False) -> torch.Tensor:
+    """cb200_public_projection_forward (out = deq(X) dense) or _backward_rhs (grad_rhs = deq(X)^T dense)."""
+    l = public_layout(x)
+    n = dense.shape[1]
+    need = C.c_uint64()
+    capi.check(capi.lib().cb200_public_projection_scratch(C.byref(l), C.c_int64(n), C.byref(need)))
+    scratch = torch.empty(need.value, dtype=torch.uint8, device=dense.device)
+    out = torch.empty(x.cols if backward else x.rows, n, dtype=torch.float32, device=dense.device)
+    fn = capi.lib().cb200_public_projection_backward_rhs if backward else capi.lib().cb200_public_projection_forward
+    dev = dense.device.index if dense.device.index is not None else torch.cuda.current_device()
+    capi.check(fn(C.byref(l), C.c_void_p(dense.data_ptr()), C.c_int64(dense.stride(0)), C.c_int64(n), C.c_void_p(out.data_ptr()),
+                  C.c_int64(out.stride(0)), C.c_int32(dev), C.c_void_p(_stream_handle(dense.device)),
+                  C.c_void_p(scratch.data_ptr()), C.c_uint64(scratch.numel())))
+    return out
+
+
 # ---- host-buffer entry: what a caller with the matrix in host memory runs -------------------
 
 @dataclass

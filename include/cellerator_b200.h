@@ -480,6 +480,46 @@ typedef struct cb200_dense_pack {
 
 cb200_status cb200_pack_dense_operand(const cb200_dense_pack *pack, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Routing of the reference's public projection calls: cellerator_sparse_projection_forward /
+ * _backward (include/Cellerator/abi.h:111-124, src/abi/abi.cu:278-396) for the quantized layouts,
+ * which the reference declares (CELLERATOR_LAYOUT_QUANTIZED_BLOCKED_ELL, abi.h:31-36) and rejects
+ * (abi.cu:325-326).  cb200_public_layout carries the fields of cellerator_sparse_layout_desc
+ * (abi.h:68-89) these layouts use, with the same widths: 32-bit shapes and row offsets. */
+typedef enum cb200_public_layout_kind {
+    CB200_PUBLIC_LAYOUT_QUANTIZED_BLOCKED_ELL = 4, /* = CELLERATOR_LAYOUT_QUANTIZED_BLOCKED_ELL */
+    CB200_PUBLIC_LAYOUT_QUANTIZED_CSR = 5          /* no counterpart yet: the next free value of cellerator_sparse_layout */
+} cb200_public_layout_kind;
+
+typedef struct cb200_public_layout {
+    uint32_t version;
+    size_t size;
+    int32_t layout; /* cb200_public_layout_kind */
+    uint32_t rows, cols, nnz;
+    uint32_t block_size, ell_cols, row_stride_bytes; /* Blocked-ELL */
+    uint32_t bits, decode_policy;                    /* cb200_decode_policy */
+    const uint32_t *major_ptr;     /* CSR: rows + 1 */
+    const uint32_t *minor_idx;     /* CSR: nnz gene indices */
+    const uint32_t *block_col_idx; /* Blocked-ELL */
+    const uint8_t *packed_values;
+    const float *column_scales;
+    const float *column_offsets; /* per-gene affine policy */
+    const float *row_offsets;    /* column-scale / row-offset policy */
+} cb200_public_layout;
+
+/* scratch the calls below need for this layout (device memory, 256-byte aligned); they never allocate */
+cb200_status cb200_public_projection_scratch(const cb200_public_layout *layout, int64_t out_cols, uint64_t *bytes);
+/* out[rows, out_cols] = deq(X) * rhs[cols, out_cols]; fp32 row-major operands with leading dimensions
+ * (matrix_ld_ of abi.cu), exact fp32 products; enqueues on `stream` */
+cb200_status cb200_public_projection_forward(const cb200_public_layout *layout, const float *rhs, int64_t rhs_ld,
+                                             int64_t out_cols, float *out, int64_t out_ld, int32_t device, void *stream,
+                                             void *scratch, uint64_t scratch_bytes);
+/* grad_rhs[cols, out_cols] = deq(X)^T * grad_out[rows, out_cols] (csr_spmm_bwd_rhs of abi.cu:376-389);
+ * quantized CSR only.  grad_values has no meaning for integer codes and is not served. */
+cb200_status cb200_public_projection_backward_rhs(const cb200_public_layout *layout, const float *grad_out,
+                                                  int64_t grad_out_ld, int64_t out_cols, float *grad_rhs, int64_t grad_rhs_ld,
+                                                  int32_t device, void *stream, void *scratch, uint64_t scratch_bytes);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif
