@@ -24,6 +24,10 @@ PROJECTION_CSR, PROJECTION_BLOCKED_ELL, PROJECTION_TRANSPOSE = 5, 8, 10
 CAP_DETERMINISTIC, CAP_GRAPH_CAPTURE, CAP_PERSISTENT_PREPROCESSING, CAP_COMPOSED_EPILOGUE = 1, 2, 4, 8
 
 
+# cb200_status values the Python side names
+STATUS_SUCCESS, STATUS_INVALID_ARGUMENT, STATUS_INVALID_SHAPE, STATUS_UNSUPPORTED = 0, 1, 2, 3
+
+
 class Cb200Error(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"cb200 status {status}: {message}")

@@ -325,7 +325,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             device_scope scope(problem->device);
             cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
                                                           : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), &p->blocked);
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), false, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) {
                 delete p;
                 return st;
@@ -397,7 +397,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             device_scope scope(problem->device);
             cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
                                                           : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), &p->blocked);
+            // one pass of bf16 products: the entry words hold the decoded values (no look-up at launch)
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !split, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) {
                 delete p;
                 return st;

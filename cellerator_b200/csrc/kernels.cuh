@@ -61,11 +61,15 @@ struct blocked_layout {
     // Dense operand tiles (forward, bf16 products): per (group, window) the 64 KB tile of decoded bf16
     // values in the shared-memory image the MMA reads.  When set, entries / seg_ptr are gone.
     unsigned char *dense_tiles = nullptr;
-    const void *src_scales = nullptr, *src_offsets = nullptr; // baked into the tiles
+    // baked: an entry word holds the decoded bf16 value (bits 0-15) and the byte position / 2 (bits
+    // 16-30) instead of code and gene: the forward kernel stores it as it is, no table look-up.
+    bool baked = false;
+    const void *src_scales = nullptr, *src_offsets = nullptr; // baked into the entries / the tiles
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
-cb200_status build_blocked_layout(const qcsr_view &x, blocked_layout *out); // current device; allocates and synchronises
+// current device; allocates and synchronises.  bake: decoded values in the entry words (forward, bf16 products only)
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, blocked_layout *out);
 void free_blocked_layout(blocked_layout *layout);
 // Dense operand tiles from the window-blocked copy (decoded values of `x` baked in; the entry words
 // are freed).  *built stays false, the copy untouched, when the device has no room.  Synchronises.

@@ -482,7 +482,7 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
                                            const blocked_layout &layout, bool split_products, int sm_count,
                                            cudaStream_t stream, bool *taken) {
     *taken = false;
-    if (layout.seg_ptr == nullptr || d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS;
+    if (layout.seg_ptr == nullptr || layout.baked || d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS; // this kernel decodes codes
     if (!qcsr_transpose_blocked_shape_ok(x.rows, x.cols, d.n, x.bits) || d.dense_dtype != CB200_DTYPE_F32) return CB200_STATUS_SUCCESS;
     if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return CB200_STATUS_SUCCESS;
     if (workspace == nullptr || workspace_bytes < qcsr_transpose_blocked_workspace_bytes(x.rows, d.n)) return CB200_STATUS_SUCCESS;

@@ -421,8 +421,7 @@ def pack_dense_operand(source: torch.Tensor, fperm: torch.Tensor, col_major=Fals
     d.device = source.device.index if source.device.index is not None else torch.cuda.current_device()
     capi.check(capi.lib().cb200_pack_dense_operand(C.byref(d), C.c_void_p(_stream_handle(source.device))))
     if int(status.item()) != 0:
-        raise capi.Cb200Error(capi.STATUS_INVALID_SHAPE if hasattr(capi, "STATUS_INVALID_SHAPE") else 2,
-                              "invalid geometry: feature permutation is out of range")
+        raise capi.Cb200Error(capi.STATUS_INVALID_SHAPE, "invalid geometry: feature permutation is out of range")
     del keep
     return out
 

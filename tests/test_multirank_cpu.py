@@ -66,3 +66,61 @@ def test_empty_trailing_shards():
     brp = ops.partition_rows(5, 8)                              # more ranks than row blocks
     assert brp.tolist() == [0, 1, 2, 3, 4, 5, 5, 5, 5]
     assert ops.partition_rows(0, 2).tolist() == [0, 0, 0]
+
+
+def _lowering_worker(rank, world, port, result_dir):
+    """Row-sharded CSR -> Blocked-ELL lowering: shards on block-row boundaries lower on their own; the
+    common ELL width is the all-reduce MAX of the shards' widths, and with it the shards' column
+    indices and values tile the whole-matrix result."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle as orc
+        from cellerator_b200 import synth
+        checker = orc.Oracle()
+        bs = 16
+        h = synth.make_lowering_host(rows=bs * 13 + 5, features=400, feature_blocks=3, mean_nnz=10, seed=2,
+                                     value_dtype=np.uint8)
+        relaxed = dict(max_value_expansion=1e9, max_storage_expansion=1e9)
+        # execution rows [e0, e1) of the row order, whole block rows per rank
+        block_rows = (h["rows"] + bs - 1) // bs
+        per = (block_rows + world - 1) // world
+        e0, e1 = min(h["rows"], rank * per * bs), min(h["rows"], (rank + 1) * per * bs)
+        # the shard as a CSR of its own: rows = the canonical rows its execution rows name, local order identity
+        canon = h["rperm"][e0:e1].astype(np.int64)
+        counts = (h["row_offsets"][canon + 1] - h["row_offsets"][canon]).astype(np.int64)
+        ro = np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32)
+        take = np.concatenate([np.arange(h["row_offsets"][c], h["row_offsets"][c + 1]) for c in canon]).astype(np.int64) \
+            if len(canon) else np.zeros(0, dtype=np.int64)
+        shard = (ro, h["feature_ids"][take], h["values"][take], h["features"], h["fb_offsets"], h["fperm"],
+                 np.arange(len(canon), dtype=np.uint32))
+        _, geo, _, cols, vals = checker.bell_lowering(*shard, bs, **relaxed)
+        width = torch.tensor([geo["ell_blocks_per_row"]], dtype=torch.int64)
+        occupied = torch.tensor([geo["occupied_blocks"]], dtype=torch.int64)
+        dist.all_reduce(width, op=dist.ReduceOp.MAX)
+        dist.all_reduce(occupied, op=dist.ReduceOp.SUM)
+        whole = checker.bell_lowering(h["row_offsets"], h["feature_ids"], h["values"], h["features"], h["fb_offsets"],
+                                      h["fperm"], h["rperm"], bs, **relaxed)
+        ok = int(width) == whole[1]["ell_blocks_per_row"] and int(occupied) == whole[1]["occupied_blocks"]
+        # my block rows of the whole result, cut to my own width, are my shard's result
+        w_all, w_mine = whole[1]["ell_blocks_per_row"], geo["ell_blocks_per_row"]
+        b0, b1 = e0 // bs, (e1 + bs - 1) // bs
+        ref_cols = whole[3].reshape(-1, w_all)[b0:b1]
+        ok = ok and np.array_equal(ref_cols[:, :w_mine], cols.reshape(-1, max(w_mine, 1))[:, :w_mine] if w_mine else ref_cols[:, :0])
+        ok = ok and bool((ref_cols[:, w_mine:] == -1).all())
+        ref_vals = whole[4].reshape(-1, w_all, bs * bs)[b0:b1]
+        ok = ok and np.array_equal(ref_vals[:, :w_mine].ravel(), vals) and not ref_vals[:, w_mine:].any()
+        flag = torch.tensor([int(ok)])
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            np.save(os.path.join(result_dir, "lowering_ok.npy"), np.array([int(flag)]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_row_sharded_lowering_on_cpu_ranks(tmp_path, world):
+    port = _free_port()
+    mp.spawn(_lowering_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert int(np.load(tmp_path / "lowering_ok.npy")[0]) == 1
