@@ -32,6 +32,7 @@
 // to 0.  Every barrier wait is bounded; on a time-out a status word is set, the waits stop
 // blocking, and the kernel still runs to completion and frees its TMEM.
 #include "kernels.cuh"
+#include "sm100_primitives.cuh"
 
 #include <cuda_bf16.h>
 
@@ -77,44 +78,8 @@ struct tc_params {
     int *status;
 };
 
-__device__ __forceinline__ std::uint32_t smem_addr(const void *p) { return static_cast<std::uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void bar_init(std::uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(std::uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool bar_try_wait(std::uint32_t bar, std::uint32_t parity) {
-    std::uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0u;
-}
-// Bounded wait.  Once any wait of the CTA has timed out (`*abort_flag` set) waits return at once.
-__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag) {
-    int spins = 0;
-    while (!bar_try_wait(bar, parity)) {
-        if (*abort_flag != 0) return;
-        if (++spins > (1 << 22)) {
-            *abort_flag = 1;
-            return;
-        }
-    }
-}
-
 __device__ __forceinline__ void bar_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
     asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// One contiguous global -> shared copy by the copy engine (this GPU's own memory, no multicast);
-// completion is counted in bytes on `bar`.
-__device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes, std::uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
 }
 __device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -128,8 +93,6 @@ __device__ __forceinline__ void lds_f32x4(std::uint32_t addr, float &a, float &b
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template<int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 // K-major, no swizzle: core matrices of 8 rows x 16 bytes; LBO (between the two core matrices a
 // K = 16 instruction reads) = 128 B, SBO (between groups of 8 rows) = 512 B.
 __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
@@ -151,24 +114,6 @@ __device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t des
         : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate ? 1u : 0u), "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ void mma_commit(std::uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
-    std::uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
-        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
-          "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
-          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // W [genes][n] (leading dimension ld) -> per gene block of 32, the n x 32 slice of W^T already in
 // the shared-memory operand layout (core matrices of 8 output columns x 8 genes, 128 bytes each:
 // byte offset of (column m, gene e) = (m/8)*512 + (e/8)*128 + (m%8)*16 + (e%8)*2), zero for
