@@ -348,6 +348,9 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                 }
                 const int col = h * 128 + warp * 32 + lane;
+                // this thread writes one output column of 32 rows: its bias is loaded once
+                const bool composed = p.epilogue != CB200_EPILOGUE_NONE;
+                const float bias = composed && epilogue_has_bias(p.epilogue) ? __ldg(p.bias + col) : 0.0f;
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const std::int64_t row = row0 + c;
@@ -355,7 +358,8 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                         float *out = p.y + row * p.y_ld + col;
                         float r = p.alpha * v[c];
                         if (p.beta != 0.0f) r = fmaf(p.beta, *out, r);
-                        *out = finish_output(r, p.bias, col, p.epilogue);
+                        if (composed) r = apply_epilogue(r, bias, p.epilogue);
+                        *out = r;
                     }
                 }
             }
