@@ -552,6 +552,267 @@ cb200_status launch_one(const blocked_params &p, bool long_segments, bool baked,
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same window kernel for baked entry words, with the scatter warps in two groups of eight that
+// take alternate windows (group g owns tile buffer g and its own ring of entry chunks).  A window's
+// chain -- wait for the tile, zero it, barrier, wait for the chunk, scatter, proxy fence, hand over --
+// is mostly latency; with two groups the chains of consecutive windows overlap instead of following
+// each other.  Measured on the 1M x 33,538 matrix (ms per launch): one group 6.86; two groups with
+// (chunk entries, stages per group) (2048, 2) 6.30, (2048, 1) 6.44, (1024, 2) 6.55, (1024, 3) 6.57,
+// (512, 4) 7.98; (2048, 2) with three instead of four W stages 6.45.  A matrix whose segments span
+// several chunks (the 17 %-dense 4,000-gene one) is slower this way (1.30 against 1.06 ms) and keeps
+// the one-group kernel.
+constexpr int kGroupWarps = kProducerWarps / 2;
+constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kChunk2Entries = 2048;
+constexpr int kChunk2Bytes = kChunk2Entries * 4;
+constexpr int kRing2 = 2; // chunk stages per scatter group
+__host__ __device__ constexpr int w2_stages(int n) {
+    return (232448 - 2 * kABufBytes - 2 * kRing2 * kChunk2Bytes - 1024) / (n * kWin * 2) >= kMaxWStages
+               ? kMaxWStages
+               : (232448 - 2 * kABufBytes - 2 * kRing2 * kChunk2Bytes - 1024) / (n * kWin * 2);
+}
+
+template<int NC>
+__global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const blocked_params p) {
+    constexpr int REC = record_bytes(NC);   // distance of the W records in global memory
+    constexpr int WREC = NC * kWin * 2;     // the W part of a record (the decode table is not needed)
+    constexpr int STAGES = w2_stages(NC);
+    constexpr int CHUNKS = 2 * kRing2;
+    constexpr int kTmemCols = kSubBlocks * NC < 32 ? 32 : kSubBlocks * NC;
+    constexpr std::uint32_t IDESC = instr_desc(NC);
+    extern __shared__ __align__(1024) unsigned char smem[];
+    // [2][A tile] | [STAGES][W window] | [2][kRing2][entry chunk] | barriers | chunk meta | tmem | abort | scratch
+    unsigned char *chunk_base = smem + 2 * kABufBytes + STAGES * WREC;
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(chunk_base + CHUNKS * kChunk2Bytes);
+    std::uint64_t *a_full = bars;                 // [2]      scatter group -> MMA (one arrival per warp of the group)
+    std::uint64_t *a_empty = bars + 2;            // [2]      MMA commit -> scatter group
+    std::uint64_t *w_full = bars + 4;             // [STAGES] copy engine -> MMA
+    std::uint64_t *w_empty = w_full + STAGES;     // [STAGES] MMA commit -> W loader
+    std::uint64_t *c_full = w_empty + STAGES;     // [CHUNKS] copy engine -> scatter group
+    std::uint64_t *c_empty = c_full + CHUNKS;     // [CHUNKS] scatter group -> chunk loader (one arrival per warp)
+    std::uint64_t *acc_full = c_empty + CHUNKS;   // MMA commit -> epilogue warps
+    std::uint64_t *acc_empty = acc_full + 1;      // epilogue warps -> MMA
+    volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [CHUNKS] (entries << 1) | last chunk of its window
+    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + CHUNKS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const std::uint32_t smem0 = smem_addr(smem);
+    const std::uint32_t wstage0 = smem0 + 2 * kABufBytes;
+    const std::uint32_t chunk0 = wstage0 + STAGES * WREC;
+
+    if (tid == 0) {
+        for (int b = 0; b < 2; ++b) {
+            bar_init(smem_addr(a_full + b), kGroupWarps);
+            bar_init(smem_addr(a_empty + b), 1);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            bar_init(smem_addr(w_full + s), 1);
+            bar_init(smem_addr(w_empty + s), 1);
+        }
+        for (int s = 0; s < CHUNKS; ++s) {
+            bar_init(smem_addr(c_full + s), 1);
+            bar_init(smem_addr(c_empty + s), kGroupWarps);
+        }
+        bar_init(smem_addr(acc_full), 1);
+        bar_init(smem_addr(acc_empty), kEpilogueWarps);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const std::uint32_t tmem_base = *tmem_slot;
+
+    const std::int64_t first_group = p.group_begin + blockIdx.x;
+    const std::int64_t my_groups = first_group < p.group_end ? (p.group_end - first_group + gridDim.x - 1) / gridDim.x : 0;
+
+    if (warp < kProducerWarps) {
+        // ================= two scatter groups; group 0 also writes Y =================
+        const int grp = warp / kGroupWarps, gtid = tid - grp * kGroupThreads;
+        const int sub = tid >> 7;
+        unsigned char *tile = smem + grp * kABufBytes;
+        long long q = 0;  // windows of this CTA, both groups count all of them
+        long long qc = 0; // chunks this group has consumed
+        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+            const std::int64_t row = (first_group + gi * gridDim.x) * kRows + tid;
+            for (int w = 0; w < p.windows; ++w, ++q) {
+                if (static_cast<int>(q & 1) != grp) continue;
+                bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
+#pragma unroll
+                for (int k = 0; k < kABufBytes / (kGroupThreads * 16); ++k)
+                    *reinterpret_cast<uint4 *>(tile + k * (kGroupThreads * 16) + gtid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                // the whole tile is zero before anyone of the group scatters (named barrier 1 or 2)
+                if (grp == 0) asm volatile("bar.sync 1, %0;" ::"n"(kGroupThreads) : "memory");
+                else asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory");
+                bool last = false;
+                int guard = 0;
+                while (!last && ++guard < (1 << 20)) {
+                    const int cs = grp * kRing2 + static_cast<int>(qc % kRing2);
+                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing2) & 1), abort_flag);
+                    const int meta = chunk_meta[cs];
+                    const int count = *abort_flag != 0 ? 0 : (meta >> 1);
+                    last = (meta & 1) != 0 || *abort_flag != 0;
+                    const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunk2Bytes);
+                    for (int i = gtid * 4; i < count; i += kGroupThreads * 4) { // segments are padded to multiples of 4
+                        const uint4 e4 = chunk[i >> 2];
+                        const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) { // padding words (top bit set) go to a scratch slot instead of branching
+                            unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + (((e[k] >> 16) & 0x7fffu) << 1) : scratch_slot;
+                            *reinterpret_cast<unsigned short *>(dst) = static_cast<unsigned short>(e[k] & 0xffffu);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
+                    ++qc;
+                }
+                fence_async_proxy(); // the tile was written with ordinary stores, the MMA reads it through the async proxy
+                __syncwarp();
+                if (lane == 0) bar_arrive(smem_addr(a_full + grp));
+            }
+
+            // ---- thread t < 256 (group 0) writes row t of the row group: TMEM lane = row within the sub-block
+            if (grp != 0) continue;
+            bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(gi & 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int h = 0; h < NC / 32; ++h) {
+                float v[32];
+                tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
+                if (row < p.row_end) {
+                    float *out = p.y + row * p.y_ld + h * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        float4 r = make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]);
+                        if (p.beta != 0.0f) {
+                            const float4 o = *reinterpret_cast<const float4 *>(out + c);
+                            r.x = fmaf(p.beta, o.x, r.x); r.y = fmaf(p.beta, o.y, r.y);
+                            r.z = fmaf(p.beta, o.z, r.z); r.w = fmaf(p.beta, o.w, r.w);
+                        }
+                        if (p.epilogue != CB200_EPILOGUE_NONE) {
+                            r.x = finish_output(r.x, p.bias, h * 32 + c + 0, p.epilogue);
+                            r.y = finish_output(r.y, p.bias, h * 32 + c + 1, p.epilogue);
+                            r.z = finish_output(r.z, p.bias, h * 32 + c + 2, p.epilogue);
+                            r.w = finish_output(r.w, p.bias, h * 32 + c + 3, p.epilogue);
+                        }
+                        *reinterpret_cast<float4 *>(out + c) = r;
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(smem_addr(acc_empty));
+        }
+    } else if (warp == kProducerWarps) {
+        // ================= MMA issuer =================
+        long long q = 0;
+        for (std::int64_t g = 0; g < my_groups; ++g) {
+            bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((g & 1) ^ 1), abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int w = 0; w < p.windows; ++w, ++q) {
+                const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
+                const int s = static_cast<int>(q % STAGES);
+                bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag);
+                bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    const std::uint32_t a_tile = smem0 + b * kABufBytes;
+                    const std::uint32_t b_tile = wstage0 + s * WREC;
+#pragma unroll
+                    for (int kk = 0; kk < kWin / 16; ++kk) {
+                        const std::uint64_t db = smem_desc(b_tile + kk * 256);
+#pragma unroll
+                        for (int sb = 0; sb < kSubBlocks; ++sb)
+                            mma_bf16(tmem_base + sb * NC,
+                                     smem_desc_sw128(a_tile + sb * kSubBlockBytes + (kk >> 2) * kHalfBytes + (kk & 3) * 32), db, IDESC,
+                                     w > 0 || kk > 0);
+                    }
+                    mma_commit(smem_addr(a_empty + b));
+                    mma_commit(smem_addr(w_empty + s));
+                    if (w == p.windows - 1) mma_commit(smem_addr(acc_full));
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == kProducerWarps + 1) {
+        // ================= W loader =================
+        if (lane == 0) {
+            const long long total = my_groups * p.windows;
+            for (long long q = 0; q < total; ++q) {
+                const int s = static_cast<int>(q % STAGES);
+                bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag);
+                bar_arrive_expect_tx(smem_addr(w_full + s), WREC);
+                bulk_copy_g2s(wstage0 + s * WREC, p.records + static_cast<std::size_t>(q % p.windows) * REC, WREC, smem_addr(w_full + s));
+            }
+        }
+    } else if (warp == kProducerWarps + 2) {
+        // ================= entry chunks: window q goes to the ring of scatter group q & 1 =================
+        long long q = 0;
+        long long qc0 = 0, qc1 = 0; // chunks issued into each ring
+        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+            const std::int64_t seg0 = (first_group + gi * gridDim.x) * p.windows;
+            for (int wbase = 0; wbase < p.windows; wbase += 31) {
+                const int span = min(31, p.windows - wbase); // segment bounds of up to 31 windows in one coalesced read
+                const std::int64_t bound = lane <= span ? __ldg(p.seg_ptr + seg0 + wbase + lane) : 0;
+                for (int j = 0; j < span; ++j, ++q) {
+                    const std::int64_t lo = __shfl_sync(0xffffffffu, bound, j), hi = __shfl_sync(0xffffffffu, bound, j + 1);
+                    const int ring = static_cast<int>(q & 1);
+                    std::int64_t at = lo;
+                    do {
+                        const int count = static_cast<int>(min(static_cast<std::int64_t>(kChunk2Entries), hi - at));
+                        const long long mine = ring == 0 ? qc0 : qc1;
+                        if (lane == 0) {
+                            const int cs = ring * kRing2 + static_cast<int>(mine % kRing2);
+                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((mine / kRing2) & 1) ^ 1), abort_flag);
+                            chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
+                            if (count > 0) {
+                                bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(count) * 4u);
+                                bulk_copy_g2s(chunk0 + cs * kChunk2Bytes, p.entries + at, static_cast<std::uint32_t>(count) * 4u,
+                                              smem_addr(c_full + cs));
+                            } else {
+                                bar_arrive(smem_addr(c_full + cs)); // an empty window still hands over one (empty) chunk
+                            }
+                        }
+                        at += count;
+                        if (ring == 0) ++qc0;
+                        else ++qc1;
+                    } while (at < hi);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template<int NC>
+cb200_status launch_blocked2(const blocked_params &p, int sm_count, cudaStream_t stream) {
+    constexpr std::size_t smem = 2 * kABufBytes + w2_stages(NC) * NC * kWin * 2 + 2 * kRing2 * kChunk2Bytes +
+                                 (6 + 2 * w2_stages(NC) + 4 * kRing2) * sizeof(std::uint64_t) + 2 * kRing2 * 4 + 24;
+    static_assert(smem <= 232448, "shared memory budget");
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked2_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    const std::int64_t groups = p.group_end - p.group_begin;
+    const unsigned grid = static_cast<unsigned>(groups < sm_count ? groups : sm_count);
+    qcsr_fwd_blocked2_kernel<NC><<<grid, kThreads, smem, stream>>>(p);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Dense operand tiles (schedule "tensor_dense").
 //
 // Above a few per cent of density the scatter is the whole cost of a window, and it repeats the
@@ -1040,11 +1301,17 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
         p.bias = d.bias;
         p.epilogue = i + 1 == pass_count ? d.epilogue : CB200_EPILOGUE_NONE;
         cb200_status st;
+        static const bool two_groups_enabled = [] {
+            const char *e = std::getenv("CB200_SCATTER_GROUPS");
+            return e == nullptr || std::atoi(e) != 1;
+        }();
         const bool long_segments = layout.total_entries > static_cast<std::int64_t>(kChunkEntries) * layout.groups * layout.windows;
+        // two scatter groups pay when a window is a chunk or two; long segments keep one group and deeper chunks
+        const bool two_groups = layout.baked && two_groups_enabled && !long_segments;
         switch (d.n) {
-        case 32: st = launch_one<32>(p, long_segments, layout.baked, sm_count, stream); break;
-        case 64: st = launch_one<64>(p, long_segments, layout.baked, sm_count, stream); break;
-        default: st = launch_one<128>(p, long_segments, layout.baked, sm_count, stream); break;
+        case 32: st = two_groups ? launch_blocked2<32>(p, sm_count, stream) : launch_one<32>(p, long_segments, layout.baked, sm_count, stream); break;
+        case 64: st = two_groups ? launch_blocked2<64>(p, sm_count, stream) : launch_one<64>(p, long_segments, layout.baked, sm_count, stream); break;
+        default: st = two_groups ? launch_blocked2<128>(p, sm_count, stream) : launch_one<128>(p, long_segments, layout.baked, sm_count, stream); break;
         }
         if (st != CB200_STATUS_SUCCESS) return st;
     }

@@ -29,7 +29,10 @@ def test_quantized_csr_forward_and_backward(cuda_device, oracle, policy, n):
     assert torch.equal(y, ops.spmm_forward(x, w))                                    # the operation-core path, bit for bit
     g, _ = dense(rng, c["rows"], n, torch.float32, cuda_device, std=1.0)
     gr = ops.public_projection(x, g, backward=True)
-    assert torch.allclose(gr, ops.spmm_transpose(x, g), rtol=1e-4, atol=1e-4)
+    # the same fp32 reductions in another order (L2 atomics): equal to summation error, which scales with
+    # the largest partial sums (~600 here), not with the element
+    direct = ops.spmm_transpose(x, g)
+    assert float((gr - direct).abs().max()) <= 1e-5 * float(direct.abs().max())
 
 
 def test_quantized_blocked_ell_forward(cuda_device, oracle):
