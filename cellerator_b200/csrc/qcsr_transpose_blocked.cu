@@ -22,9 +22,11 @@
 // vector reductions (the (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so
 // several CTAs contribute to the same genes; G' is first scaled by beta by a small kernel).
 //
-// Structure of a CTA (608 threads, one CTA per SM): warps 0-15 zero, decode and scatter, and read
-// the accumulators back at the end of a run; warp 16 issues the MMAs; warp 17 feeds the G ring (2
-// stages of 32 KB); warp 18 feeds the entry-chunk ring (2 stages of 8 KB).  Every barrier wait is bounded; on a
+// Structure of a CTA (608 threads, one CTA per SM): warps 0-15 zero, decode and scatter -- as two
+// groups of eight warps on alternate tiles, each with its own tile buffer and 8 KB chunk stage, so
+// that the per-tile chains of waits overlap (23.6 ms against 24.4 for the three split passes on the
+// 1M x 33,538 matrix) -- and read the accumulators back at the end of a run; warp 16 issues the MMAs;
+// warp 17 feeds the G ring (2 stages of 32 KB); warp 18 deals the entry chunks.  Every barrier wait is bounded; on a
 // time-out a status word is raised, waits stop blocking, and the kernel runs to completion and frees
 // its TMEM.  A non-zero status means G' is not valid.
 #include "kernels.cuh"
@@ -48,7 +50,11 @@ constexpr int kQuarterBytes = kWin * 128;     // 16 KB: 128 genes x 64 cells
 constexpr int kGStages = 2;
 constexpr int kChunkEntries = 2048;
 constexpr int kChunkBytes = kChunkEntries * 4;
-constexpr int kChunkStages = 2;
+constexpr int kChunkStages = 2;               // one per scatter group (two stages each do not fit beside the G ring)
+constexpr int kGroupWarps = kProducerWarps / 2;
+constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kRing = kChunkStages / 2;       // chunk stages per scatter group
+static_assert(kChunkLoaders == 1 && kRing >= 1, "one loader thread deals the chunks to the two groups' rings");
 
 __host__ __device__ constexpr int g_record_bytes(int n) { return kRows * n * 2; }
 
@@ -141,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            bar_init(smem_addr(a_full + b), kProducerWarps);
+            bar_init(smem_addr(a_full + b), kGroupWarps);
             bar_init(smem_addr(a_empty + b), 1);
         }
         for (int s = 0; s < kGStages; ++s) {
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
         }
         for (int s = 0; s < kChunkStages; ++s) {
             bar_init(smem_addr(c_full + s), 1);
-            bar_init(smem_addr(c_empty + s), kProducerWarps);
+            bar_init(smem_addr(c_empty + s), kGroupWarps);
         }
         bar_init(smem_addr(acc_full), 1);
         bar_init(smem_addr(acc_empty), kProducerWarps);
@@ -176,8 +182,12 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
 
     if (warp < kProducerWarps) {
         // ================= zero, scatter, read back =================
+        // Two scatter groups of eight warps take alternate tiles (group g owns tile buffer g and chunk
+        // stage g), so that the chains zero -> barrier -> chunk -> scatter -> fence of consecutive tiles overlap.
         const bool use_row_offset = p.row_offsets != nullptr;
-        long long q = 0, qc = 0; // tiles and chunks done by this CTA
+        const int grp = warp / kGroupWarps, gtid = tid - grp * kGroupThreads;
+        unsigned char *tile = smem + grp * kTileBytes;
+        long long q = 0, qc = 0; // tiles of this CTA (both groups count all of them); chunks this group consumed
         int run = 0;
         for (std::int64_t u = u0; u < u1; ++run) {
             const std::int64_t set = u / p.group_count, gi0 = u % p.group_count;
@@ -203,24 +213,25 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                     asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
                 }
                 for (int wl = 0; wl < nwin; ++wl, ++q) {
-                    const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
-                    bar_wait(smem_addr(a_empty + b), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
-                    unsigned char *tile = smem + b * kTileBytes;
+                    if (static_cast<int>(q & 1) != grp) continue;
+                    bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
 #pragma unroll
-                    for (int k = 0; k < kTileBytes / (kProducerThreads * 16); ++k)
-                        *reinterpret_cast<uint4 *>(tile + k * (kProducerThreads * 16) + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
-                    asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the whole tile is zero before anyone scatters
+                    for (int k = 0; k < kTileBytes / (kGroupThreads * 16); ++k)
+                        *reinterpret_cast<uint4 *>(tile + k * (kGroupThreads * 16) + gtid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    // the whole tile is zero before anyone of the group scatters (named barrier 2 or 3)
+                    if (grp == 0) asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory");
+                    else asm volatile("bar.sync 3, %0;" ::"n"(kGroupThreads) : "memory");
                     const float2 *wtable = table + wl * kWin;
                     bool last = false;
                     int guard = 0;
                     while (!last && ++guard < (1 << 20)) {
-                        const int cs = static_cast<int>(qc % kChunkStages);
-                        bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kChunkStages) & 1), abort_flag);
+                        const int cs = grp * kRing + static_cast<int>(qc % kRing);
+                        bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing) & 1), abort_flag);
                         const int meta = chunk_meta[cs];
                         const int n_entries = *abort_flag != 0 ? 0 : (meta >> 1);
                         last = (meta & 1) != 0 || *abort_flag != 0;
                         const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunkBytes);
-                        for (int i = tid * 4; i < n_entries; i += kProducerThreads * 4) { // segments are padded to multiples of 4
+                        for (int i = gtid * 4; i < n_entries; i += kGroupThreads * 4) { // segments are padded to multiples of 4
                             const uint4 e4 = chunk[i >> 2];
                             const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
                             float2 t[4];
@@ -251,7 +262,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                     }
                     fence_async_proxy(); // ordinary stores, read by the MMA through the async proxy
                     __syncwarp();
-                    if (lane == 0) bar_arrive(smem_addr(a_full + b));
+                    if (lane == 0) bar_arrive(smem_addr(a_full + grp));
                 }
             }
             // ---- end of the run: add the accumulators into G'.  TMEM lane = gene within the window;
@@ -327,21 +338,22 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                 }
             }
         } else {
-            const int mine_mod = role - 1;
-            long long qc = 0;
+            long long q = 0, qc0 = 0, qc1 = 0; // tiles; chunks issued into each group's ring
             for (std::int64_t u = u0; u < u1; ++u) {
                 const std::int64_t set = u / p.group_count, group = p.group_begin + u % p.group_count;
                 const int nwin = static_cast<int>(dmin(kSetWindows, p.windows - set * kSetWindows));
                 // the unit's segments are consecutive: their bounds in one coalesced read
                 const std::int64_t bound = lane <= nwin ? __ldg(p.seg_ptr + group * p.windows + set * kSetWindows + lane) : 0;
-                for (int j = 0; j < nwin; ++j) {
+                for (int j = 0; j < nwin; ++j, ++q) {
                     const std::int64_t lo = __shfl_sync(0xffffffffu, bound, j), hi = __shfl_sync(0xffffffffu, bound, j + 1);
+                    const int ring = static_cast<int>(q & 1); // tile q belongs to scatter group q & 1
                     std::int64_t at = lo;
                     do {
                         const int n_entries = static_cast<int>(dmin(kChunkEntries, hi - at));
-                        if (lane == 0 && qc % kChunkLoaders == mine_mod) {
-                            const int cs = static_cast<int>(qc % kChunkStages);
-                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((qc / kChunkStages) & 1) ^ 1), abort_flag);
+                        const long long mine = ring == 0 ? qc0 : qc1;
+                        if (lane == 0) {
+                            const int cs = ring * kRing + static_cast<int>(mine % kRing);
+                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((mine / kRing) & 1) ^ 1), abort_flag);
                             chunk_meta[cs] = (n_entries << 1) | (at + n_entries >= hi ? 1 : 0);
                             if (n_entries > 0) {
                                 bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(n_entries) * 4u);
@@ -352,7 +364,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                             }
                         }
                         at += n_entries;
-                        ++qc;
+                        if (ring == 0) ++qc0;
+                        else ++qc1;
                     } while (at < hi);
                 }
             }
