@@ -91,6 +91,34 @@ __device__ __forceinline__ float finish_output(float value, const float *bias, i
     return apply_epilogue(value, epilogue_has_bias(kind) ? __ldg(bias + col) : 0.0f, kind);
 }
 
+// One thread's 32 consecutive output columns of a row, starting at column col0 (16-byte aligned):
+//     out = act(alpha * v + beta * out + bias).
+// The phases are kept apart -- every load, then the arithmetic, then the optional epilogue calls,
+// then every store -- so that the eight loads of a beta != 0 launch are in flight together; with a
+// call between each load and store they would follow one another.
+__device__ __forceinline__ void store_row32(float *out, float (&v)[32], float alpha, float beta, const float *bias, int col0,
+                                            int kind) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) v[c] *= alpha;
+    if (beta != 0.0f) {
+        float4 o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) o[c] = *reinterpret_cast<const float4 *>(out + 4 * c);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            v[4 * c + 0] = fmaf(beta, o[c].x, v[4 * c + 0]); v[4 * c + 1] = fmaf(beta, o[c].y, v[4 * c + 1]);
+            v[4 * c + 2] = fmaf(beta, o[c].z, v[4 * c + 2]); v[4 * c + 3] = fmaf(beta, o[c].w, v[4 * c + 3]);
+        }
+    }
+    if (kind != CB200_EPILOGUE_NONE) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = finish_output(v[c], bias, col0 + c, kind);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<float4 *>(out + 4 * c) = make_float4(v[4 * c + 0], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+}
+
 __device__ __forceinline__ float load1(const float *p) { return __ldg(p); }
 __device__ __forceinline__ float load1(const __nv_bfloat16 *p) {
     return __uint_as_float(static_cast<std::uint32_t>(__ldg(reinterpret_cast<const unsigned short *>(p))) << 16);

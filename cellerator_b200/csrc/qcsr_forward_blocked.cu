@@ -408,22 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                 tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
                 if (row < p.row_end) {
                     float *out = p.y + row * p.y_ld + h * 32;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        float4 r = make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]);
-                        if (p.beta != 0.0f) {
-                            const float4 o = *reinterpret_cast<const float4 *>(out + c);
-                            r.x = fmaf(p.beta, o.x, r.x); r.y = fmaf(p.beta, o.y, r.y);
-                            r.z = fmaf(p.beta, o.z, r.z); r.w = fmaf(p.beta, o.w, r.w);
-                        }
-                        if (p.epilogue != CB200_EPILOGUE_NONE) {
-                            r.x = finish_output(r.x, p.bias, h * 32 + c + 0, p.epilogue);
-                            r.y = finish_output(r.y, p.bias, h * 32 + c + 1, p.epilogue);
-                            r.z = finish_output(r.z, p.bias, h * 32 + c + 2, p.epilogue);
-                            r.w = finish_output(r.w, p.bias, h * 32 + c + 3, p.epilogue);
-                        }
-                        *reinterpret_cast<float4 *>(out + c) = r;
-                    }
+                    store_row32(out, v, p.alpha, p.beta, p.bias, h * 32, p.epilogue);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -688,22 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
                 if (row < p.row_end) {
                     float *out = p.y + row * p.y_ld + h * 32;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        float4 r = make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]);
-                        if (p.beta != 0.0f) {
-                            const float4 o = *reinterpret_cast<const float4 *>(out + c);
-                            r.x = fmaf(p.beta, o.x, r.x); r.y = fmaf(p.beta, o.y, r.y);
-                            r.z = fmaf(p.beta, o.z, r.z); r.w = fmaf(p.beta, o.w, r.w);
-                        }
-                        if (p.epilogue != CB200_EPILOGUE_NONE) {
-                            r.x = finish_output(r.x, p.bias, h * 32 + c + 0, p.epilogue);
-                            r.y = finish_output(r.y, p.bias, h * 32 + c + 1, p.epilogue);
-                            r.z = finish_output(r.z, p.bias, h * 32 + c + 2, p.epilogue);
-                            r.w = finish_output(r.w, p.bias, h * 32 + c + 3, p.epilogue);
-                        }
-                        *reinterpret_cast<float4 *>(out + c) = r;
-                    }
+                    store_row32(out, v, p.alpha, p.beta, p.bias, h * 32, p.epilogue);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -964,22 +934,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) qcsr_fwd_dense_kernel(const 
                 tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + ab * kAccCols + sub * NC + h * 32, v);
                 if (row < p.row_end) {
                     float *out = p.y + row * p.y_ld + h * 32;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        float4 r = make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]);
-                        if (p.beta != 0.0f) {
-                            const float4 o = *reinterpret_cast<const float4 *>(out + c);
-                            r.x = fmaf(p.beta, o.x, r.x); r.y = fmaf(p.beta, o.y, r.y);
-                            r.z = fmaf(p.beta, o.z, r.z); r.w = fmaf(p.beta, o.w, r.w);
-                        }
-                        if (p.epilogue != CB200_EPILOGUE_NONE) {
-                            r.x = finish_output(r.x, p.bias, h * 32 + c + 0, p.epilogue);
-                            r.y = finish_output(r.y, p.bias, h * 32 + c + 1, p.epilogue);
-                            r.z = finish_output(r.z, p.bias, h * 32 + c + 2, p.epilogue);
-                            r.w = finish_output(r.w, p.bias, h * 32 + c + 3, p.epilogue);
-                        }
-                        *reinterpret_cast<float4 *>(out + c) = r;
-                    }
+                    store_row32(out, v, p.alpha, p.beta, p.bias, h * 32, p.epilogue);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
