@@ -503,6 +503,43 @@ def run_lowering(args):
         dist.all_reduce(units, op=dist.ReduceOp.SUM)
     ms_per_step = float(t.item()) / args.steps
     geo = state["geo"]
+
+    # ---- end to end: the CSR in pinned host memory -> device, lowered, the Blocked-ELL arrays back to the host
+    e2e = None
+    if not args.no_e2e:
+        host_in = {k: low_in[k].cpu().pin_memory() for k in ("row_offsets", "feature_ids", "values")}
+        dev_in = {k: torch.empty_like(low_in[k]) for k in host_in}
+        low_e = ops.BellLowering(dev_in["row_offsets"], dev_in["feature_ids"], dev_in["values"], low_in["features"],
+                                 low_in["fb_offsets"], low_in["fperm"], low_in["rperm"], device)
+        host_cols = torch.empty(int(geo.column_index_count), dtype=torch.int32).pin_memory()
+        host_vals = torch.empty(int(geo.value_bytes), dtype=torch.uint8).pin_memory()
+
+        def e2e_step():
+            for k in host_in:
+                dev_in[k].copy_(host_in[k], non_blocking=True)
+            g = low_e.query(bs)
+            _, cols, vals = low_e.materialize(g)
+            host_cols.copy_(cols, non_blocking=True)
+            host_vals.copy_(vals, non_blocking=True)
+
+        e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e_steps = max(1, min(args.steps, args.e2e_steps))
+        es, ee = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        es.record()
+        for _ in range(e_steps):
+            e2e_step()
+        ee.record()
+        torch.cuda.synchronize()
+        e_ms = torch.tensor([es.elapsed_time(ee) / e_steps], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
+        e2e = {"value": float(units.item()) / (float(e_ms.item()) * 1e-3) / 1e9, "unit": "Gnnz/s",
+               "h2d_bytes_per_step": int(sum(v.numel() * v.element_size() for v in host_in.values())),
+               "d2h_bytes_per_step": int(host_cols.numel() * 4 + host_vals.numel()), "ms_per_step": float(e_ms.item()),
+               "steps": e_steps}
     if rank != 0:
         dist.destroy_process_group()
         return
@@ -527,6 +564,8 @@ def run_lowering(args):
                      "traffic": None, "peak_source": peak_kind, "kernel_ms": ms_per_step,
                      "algorithmic_bytes_per_launch": bytes_},
     }
+    if e2e is not None:
+        result["e2e"] = e2e
     if world == 1 and not args.no_cpu:
         sample_rows = min(rows, 20000 // bs * bs)
         dt, kind = lowering_cpu_seconds(lowering_sample(low_in, bs, sample_rows))
@@ -548,8 +587,37 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     threads = cpu_threads()
     kind = "transpose" if args.workload == "c3_transpose" else "forward"
-    if args.workload in ("c5_bell", "c5_lowering"):
-        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm covers the CSR workloads only"}))
+    if args.workload == "c5_lowering":
+        # the reference's single-threaded host loops on a bounded sample of the Blocked-ELL configuration
+        from cellerator_b200 import synth
+        cfg = dict(synth.CONFIGS["c5_bell"])
+        bs, sample_rows = cfg["block_size"], 20000 // cfg["block_size"] * cfg["block_size"]
+        low_in = synth.make_lowering_device(**{**cfg, "rows": sample_rows}, device=torch.device("cpu"), seed=0)
+        sample = lowering_sample(low_in, bs, sample_rows)
+        nnz = sample_rows * low_in["per_row"]
+        for _ in range(args.warmup):
+            lowering_cpu_seconds(sample)
+        times, impl_kind = [], "port"
+        for _ in range(args.steps):
+            dt, impl_kind = lowering_cpu_seconds(sample)
+            times.append(dt)
+        dt = sum(times) / len(times)
+        value = nnz / dt / 1e9
+        print(json.dumps({
+            "impl": "reference", "metric": "CSR -> Blocked-ELL lowering throughput (query + materialize)",
+            "value": value, "unit": "Gnnz/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8 codes copied bytewise, u32 indices", "data": "synthetic (same generator as the GPU arm)",
+            "config": {"workload": "c5_lowering", "genes": cfg["cols"], "block_size": bs, "sample_rows": sample_rows,
+                       "sample_nnz": nnz},
+            "cpu_baseline": {"value": value, "unit": "Gnnz/s", "cores": 1, "kind": impl_kind,
+                             "sample": f"first {sample_rows} rows ({nnz} stored entries) per step"},
+            "e2e": {"value": value, "unit": "Gnnz/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }))
+        return
+    if args.workload == "c5_bell":
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm covers the CSR workloads and the lowering only"}))
         return
     sample_rows = args.cpu_rows_per_thread * threads
     if torch.cuda.is_available():

@@ -218,3 +218,26 @@ def test_permuted_lowering_and_packed_operand_project_like_the_csr(cuda_device, 
     y_bell = ops.bell_forward(bell, w_phys)                      # rows in execution order
     y_csr = ops.spmm_forward(csr, w)                             # rows in canonical order
     assert torch.allclose(y_bell, y_csr[low.rperm.long()], rtol=1e-4, atol=1e-5)
+
+
+def test_edge_shapes(cuda_device, oracle):
+    """No stored entry at all (state empty_source, nothing to materialize), fewer rows than a block,
+    one feature block narrower than a block, 16-byte values."""
+    ro = np.zeros(6, dtype=np.uint32)
+    empty = ops.BellLowering(ro, np.zeros(0, dtype=np.uint32), np.zeros(0, dtype=np.float32), 7, [0, 7],
+                             np.arange(7, dtype=np.uint32), np.arange(5, dtype=np.uint32), cuda_device)
+    geo = empty.query(8)
+    assert geo.state == 1 and geo.ell_blocks_per_row == 0 and geo.value_bytes == 0
+    want = oracle.bell_lowering(ro, [], np.zeros(0, dtype=np.float32), 7, [0, 7], np.arange(7), np.arange(5), 8, materialize=False)[1]
+    assert want["state"] == 1 and geo.padded_rows == want["padded_rows"] and geo.padded_features == want["padded_features"]
+    with pytest.raises(capi.Cb200Error):
+        empty.materialize(geo)
+    # three rows, features [0,3) | [3,5): every semantic block narrower than the smallest block size
+    ro = np.array([0, 2, 2, 5], dtype=np.uint32)
+    ids = np.array([1, 4, 0, 2, 3], dtype=np.uint32)
+    vals = np.arange(5 * 4, dtype=np.float32).reshape(5, 4)          # 16 bytes per stored entry
+    args = (ro, ids, vals, 5, [0, 3, 5], np.array([2, 0, 4, 1, 3], dtype=np.uint32), np.array([1, 2, 0], dtype=np.uint32))
+    low = ops.BellLowering(*args, cuda_device)
+    for bs in (8, 16, 32):
+        geo = assert_same(oracle, low, args, bs, max_value_expansion=1e9, max_storage_expansion=1e9)
+        assert geo.block_rows == 1 and geo.padded_features == 2 * bs
