@@ -127,6 +127,15 @@ class PublicLayout(C.Structure):
 PUBLIC_LAYOUT_QUANTIZED_BLOCKED_ELL, PUBLIC_LAYOUT_QUANTIZED_CSR = 4, 5
 
 
+class ExecutionCsr(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("rows", C.c_uint32), ("features", C.c_uint32),
+                ("nnz", C.c_uint32), ("row_offsets", C.c_void_p), ("block_ids", C.c_void_p),
+                ("local_feature_ids", C.c_void_p), ("canonical_feature_ids", C.c_void_p),
+                ("feature_block_count", C.c_uint32), ("feature_block_offsets", C.c_void_p),
+                ("feature_permutation", C.c_void_p), ("execution_feature_ids", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_uint64), ("status_word", C.c_void_p), ("device", C.c_int32)]
+
+
 class DensePack(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("feature_permutation", C.c_void_p),
                 ("source", C.c_void_p), ("features", C.c_uint32), ("columns", C.c_uint64),
@@ -156,7 +165,7 @@ EXPORTED_SYMBOLS = [
     "cb200_prepared_workspace", "cb200_prepared_schedule", "cb200_prepared_persistent_bytes", "cb200_spmm_run", "cb200_kernel_launch_count",
     "cb200_qcsr_forward_static",
     "cb200_bell_lowering_workspace", "cb200_bell_lowering_query", "cb200_bell_lowering_materialize",
-    "cb200_pack_dense_operand",
+    "cb200_pack_dense_operand", "cb200_build_execution_csr",
     "cb200_public_projection_scratch", "cb200_public_projection_forward", "cb200_public_projection_backward_rhs",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",

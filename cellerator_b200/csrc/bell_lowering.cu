@@ -574,3 +574,88 @@ extern "C" cb200_status cb200_pack_dense_operand(const cb200_dense_pack *d, void
     }
     return CB200_STATUS_SUCCESS;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Execution-order feature ids of an ordered plan partition (the CSR a packed-order projection or the
+// lowering above consumes): execution = feature_block_offsets[block] + local.  Reference counterpart:
+// the loop of build_execution_csr_view_host (src/compute/math/physical_csr.cc:47-75).  One warp per
+// row; the ascending check inside a row compares neighbours through a shuffle.
+namespace cb200 {
+namespace {
+
+// flags: 1 = geometry (offsets, block or local out of range), 2 = identity (canonical id or order)
+__global__ void __launch_bounds__(256) execution_ids_kernel(const std::uint32_t *row_offsets, const std::uint32_t *block_ids,
+                                                            const std::uint32_t *local_ids, const std::uint32_t *canonical_ids,
+                                                            const std::uint32_t *fb_offsets, const std::uint32_t *fperm,
+                                                            std::uint32_t rows, std::uint32_t nnz, std::uint32_t fb_count,
+                                                            std::uint32_t *execution_ids, unsigned *flags) {
+    const int lane = threadIdx.x & 31;
+    const std::uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const std::uint32_t begin = row_offsets[row], end = row_offsets[row + 1u];
+    unsigned bad = 0u;
+    if (end < begin || end > nnz || (row == 0u && begin != 0u) || (row + 1u == rows && end != nnz)) {
+        if (lane == 0) atomicOr(flags, 1u);
+        return;
+    }
+    std::uint32_t carry = 0xffffffffu; // execution id of the entry before this batch
+    for (std::uint32_t base = begin; base < end; base += 32u) {
+        const std::uint32_t i = base + lane;
+        std::uint32_t execution = 0xffffffffu;
+        bool geometry_ok = true;
+        if (i < end) {
+            const std::uint32_t block = block_ids[i];
+            if (block >= fb_count) geometry_ok = false;
+            else {
+                const std::uint32_t block_begin = __ldg(fb_offsets + block), block_end = __ldg(fb_offsets + block + 1u);
+                if (local_ids[i] >= block_end - block_begin) geometry_ok = false;
+                else execution = block_begin + local_ids[i];
+            }
+            if (!geometry_ok) bad |= 1u;
+            else if (__ldg(fperm + execution) != canonical_ids[i]) bad |= 2u;
+        }
+        std::uint32_t previous = __shfl_up_sync(0xffffffffu, execution, 1);
+        if (lane == 0) previous = carry;
+        if (i < end && geometry_ok) {
+            if (i != begin && previous != 0xffffffffu && execution <= previous) bad |= 2u;
+            execution_ids[i] = execution;
+        }
+        carry = __shfl_sync(0xffffffffu, execution, 31);
+    }
+    if (bad != 0u) atomicOr(flags, bad);
+}
+
+} // namespace
+} // namespace cb200
+
+extern "C" cb200_status cb200_build_execution_csr(const cb200_execution_csr *e, void *stream_handle) {
+    using namespace cb200;
+    clear_error();
+    if (e == nullptr || e->version != CB200_ABI_VERSION || e->size < sizeof(cb200_execution_csr))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_execution_csr header");
+    if (e->feature_block_count == 0u || e->feature_block_offsets == nullptr || (e->features != 0u && e->feature_permutation == nullptr) ||
+        e->feature_block_offsets[0] != 0u || e->feature_block_offsets[e->feature_block_count] != e->features)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "invalid argument: execution CSR requires a valid frozen plan view");
+    if (e->row_offsets == nullptr || e->status_word == nullptr ||
+        (e->nnz != 0u && (e->block_ids == nullptr || e->local_feature_ids == nullptr || e->canonical_feature_ids == nullptr)))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "incompatible identity: ordered partition disagrees with the frozen feature plan");
+    if (e->nnz != 0u && e->execution_feature_ids == nullptr)
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "insufficient capacity: execution feature buffer is missing");
+    const std::uint64_t table = (static_cast<std::uint64_t>(e->feature_block_count) + 1u) * 4u;
+    if (e->workspace == nullptr || e->workspace_bytes < table || reinterpret_cast<std::uintptr_t>(e->workspace) % 4u != 0u)
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "the feature-block offsets need %llu bytes of device workspace",
+                    static_cast<unsigned long long>(table));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    device_scope scope(e->device);
+    CB200_CUDA_OK(scope.status);
+    CB200_CUDA_OK(cudaMemsetAsync(e->status_word, 0, sizeof(unsigned), stream));
+    CB200_CUDA_OK(cudaMemcpyAsync(e->workspace, e->feature_block_offsets, table, cudaMemcpyHostToDevice, stream));
+    if (e->rows == 0u) return CB200_STATUS_SUCCESS;
+    execution_ids_kernel<<<(e->rows + 7u) / 8u, 256, 0, stream>>>(e->row_offsets, e->block_ids, e->local_feature_ids,
+                                                                 e->canonical_feature_ids, static_cast<const std::uint32_t *>(e->workspace),
+                                                                 e->feature_permutation, e->rows, e->nnz, e->feature_block_count,
+                                                                 e->execution_feature_ids, static_cast<unsigned *>(e->status_word));
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}

@@ -397,6 +397,26 @@ class BellLowering:
         return pfo, cols, vals
 
 
+def build_execution_csr(row_offsets, block_ids, local_ids, canonical_ids, features: int, fb_offsets, fperm):
+    """cb200_build_execution_csr over int32 device tensors (the bits of uint32 arrays).
+    -> (flags, execution feature ids); flags 0 = ok, bit 0 invalid geometry, bit 1 incompatible identity."""
+    device = row_offsets.device
+    fbo = np.ascontiguousarray(fb_offsets, dtype=np.uint32)
+    e = capi.header(capi.ExecutionCsr())
+    e.rows, e.features, e.nnz = row_offsets.numel() - 1, int(features), block_ids.numel()
+    e.row_offsets, e.block_ids = row_offsets.data_ptr(), block_ids.data_ptr()
+    e.local_feature_ids, e.canonical_feature_ids = local_ids.data_ptr(), canonical_ids.data_ptr()
+    e.feature_block_count, e.feature_block_offsets, e.feature_permutation = len(fbo) - 1, fbo.ctypes.data, fperm.data_ptr()
+    out = torch.full((e.nnz,), -1, dtype=torch.int32, device=device)
+    work = torch.empty(len(fbo), dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    e.execution_feature_ids, e.workspace, e.workspace_bytes = out.data_ptr(), work.data_ptr(), work.numel() * 4
+    e.status_word = status.data_ptr()
+    e.device = device.index if device.index is not None else torch.cuda.current_device()
+    capi.check(capi.lib().cb200_build_execution_csr(C.byref(e), C.c_void_p(_stream_handle(device))))
+    return int(status.item()), out
+
+
 def pack_dense_operand(source: torch.Tensor, fperm: torch.Tensor, col_major=False, fb_offsets=None,
                        padded_offsets=None) -> torch.Tensor:
     """packed[execution] = source[fperm[execution]] (cb200_pack_dense_operand).  source: 2-D, [features][columns]

@@ -480,6 +480,37 @@ typedef struct cb200_dense_pack {
 
 cb200_status cb200_pack_dense_operand(const cb200_dense_pack *pack, void *stream);
 
+/* Execution-order feature ids of an ordered plan partition on the device: the loop of
+ * build_execution_csr_view_host (include/Cellerator/compute/math/physical_csr.hh:172-177,
+ * src/compute/math/physical_csr.cc:47-75; cellpack::ordered_plan_partition_view,
+ * CellPack/apply_plan.hh:49-65): execution = feature_block_offsets[block] + local, which must map back
+ * to the entry's canonical id through the plan's feature permutation and ascend strictly inside a
+ * row.  The row offsets and values are used as they are (the reference's view aliases them too); the
+ * FNV structure identity of the view stays with the caller.
+ * Enqueues on `stream`.  status_word (device, 4 bytes): 0 = ok; bit 0 = invalid geometry (offsets do
+ * not span nnz or are not monotone, block or local out of range), bit 1 = incompatible identity (an
+ * entry does not map to packed order); with several violations both kinds are reported where the
+ * reference returns the first in row-major order. */
+typedef struct cb200_execution_csr {
+    uint32_t version;
+    size_t size;
+    uint32_t rows, features, nnz;
+    const uint32_t *row_offsets;           /* device, rows + 1 */
+    const uint32_t *block_ids;             /* device, nnz */
+    const uint32_t *local_feature_ids;     /* device, nnz */
+    const uint32_t *canonical_feature_ids; /* device, nnz */
+    uint32_t feature_block_count;
+    const uint32_t *feature_block_offsets; /* HOST, feature_block_count + 1 */
+    const uint32_t *feature_permutation;   /* device, features: execution -> canonical */
+    uint32_t *execution_feature_ids;       /* device, nnz: the result */
+    void *workspace;                       /* device, (feature_block_count + 1) * 4 bytes */
+    uint64_t workspace_bytes;
+    void *status_word;                     /* device, 4 bytes */
+    int32_t device;
+} cb200_execution_csr;
+
+cb200_status cb200_build_execution_csr(const cb200_execution_csr *view, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Routing of the reference's public projection calls: cellerator_sparse_projection_forward /
  * _backward (include/Cellerator/abi.h:111-124, src/abi/abi.cu:278-396) for the quantized layouts,

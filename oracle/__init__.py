@@ -209,6 +209,16 @@ class _Base:
             raise RuntimeError(f"pack_dense_operand status {rc}")
         return out
 
+    def build_execution_csr(self, row_offsets, block_ids, local_ids, canonical_ids, features, fb_offsets, fperm):
+        """-> (status, execution feature ids) of an ordered plan partition (see oracle.c)."""
+        u32 = lambda a: np.ascontiguousarray(a, dtype=np.uint32)
+        ro, bi, li, ci, fbo, fp = u32(row_offsets), u32(block_ids), u32(local_ids), u32(canonical_ids), u32(fb_offsets), u32(fperm)
+        out = np.full(len(bi), 0xFFFFFFFF, dtype=np.uint32)
+        status = self._fn("build_execution_csr")(
+            C.c_uint32(len(ro) - 1), C.c_uint32(len(bi)), C.c_uint32(features), C.c_uint32(len(fbo) - 1), _p(fbo, C.c_uint32),
+            _p(fp, C.c_uint32), _p(ro, C.c_uint32), _p(bi, C.c_uint32), _p(li, C.c_uint32), _p(ci, C.c_uint32), _p(out, C.c_uint32))
+        return status, out
+
     def digest_f32(self, values):
         v = _f32(values)
         out = np.zeros(2, dtype=np.uint64)

@@ -756,3 +756,39 @@ ORC_API int orc_pack_dense_operand(uint32_t features, uint64_t columns, uint64_t
     }
     return 0;
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * Execution-order feature ids of a partition-local CSR in packed feature order: entry i of an ordered
+ * plan partition names its feature as (semantic block, position inside the block); its execution
+ * feature id is fb_offsets[block] + local, which must map back to the entry's canonical id through
+ * the plan's feature permutation and must ascend strictly inside a row.
+ * Follows build_execution_csr_view_host (src/compute/math/physical_csr.cc:16-97), identities left out.
+ * Returns physical_view_status_code (physical_csr.hh:17-26): 0 ok, 1 invalid argument, 2 incompatible
+ * identity, 3 invalid geometry -- the first violation in row-major order, as the reference. */
+ORC_API int orc_build_execution_csr(uint32_t rows, uint32_t nnz, uint32_t features, uint32_t fb_count,
+                                    const uint32_t *fb_offsets, const uint32_t *fperm, const uint32_t *row_offsets,
+                                    const uint32_t *block_ids, const uint32_t *local_ids, const uint32_t *canonical_ids,
+                                    uint32_t *execution_ids) {
+    if (fb_count == 0u || fb_offsets == NULL || (features != 0u && fperm == NULL) || fb_offsets[0] != 0u ||
+        fb_offsets[fb_count] != features)
+        return 1;
+    if (row_offsets == NULL || (nnz != 0u && (block_ids == NULL || local_ids == NULL || canonical_ids == NULL))) return 2;
+    if (nnz != 0u && execution_ids == NULL) return 4;
+    if (row_offsets[0] != 0u || row_offsets[rows] != nnz) return 3;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint32_t begin = row_offsets[r], end = row_offsets[r + 1u];
+        if (end < begin || end > nnz) return 3;
+        uint32_t previous = 0xffffffffu;
+        for (uint32_t i = begin; i < end; ++i) {
+            const uint32_t block = block_ids[i];
+            if (block >= fb_count) return 3;
+            const uint32_t block_begin = fb_offsets[block], block_end = fb_offsets[block + 1u];
+            if (local_ids[i] >= block_end - block_begin) return 3;
+            const uint32_t execution = block_begin + local_ids[i];
+            if (fperm[execution] != canonical_ids[i] || (i != begin && execution <= previous)) return 2;
+            execution_ids[i] = execution;
+            previous = execution;
+        }
+    }
+    return 0;
+}

@@ -3,13 +3,14 @@
 // TEST INFRASTRUCTURE ONLY.  This translation unit includes the reference's own headers
 // (found through -I at build time; nothing of the reference is copied into this
 // repository) and is linked with the reference's referee.cc / operation.cc /
-// operation_signature.cc / physical_bell.cc / physical_bell_candidates.cc.  The resulting library, oracle/_ref/libcellerator_ref.so, is what
+// operation_signature.cc / physical_bell.cc / physical_bell_candidates.cc / physical_csr.cc.  The resulting library, oracle/_ref/libcellerator_ref.so, is what
 // the C restatement in oracle.c is validated against, and it can serve as the CPU baseline.
 //
 // The reference's quantized CSR uses `int` row pointers; the entry points here take the
 // int64 arrays that the rest of this repository uses and narrow them (the caller keeps
 // nnz below 2^31 on this path).
 #include <Cellerator/compute/math/physical_bell.hh>
+#include <Cellerator/compute/math/physical_csr.hh>
 #include <Cellerator/compute/math/referee.hh>
 #include <Cellerator/quantized/blocked_ell.cuh>
 #include <Cellerator/quantized/packing.cuh>
@@ -314,6 +315,40 @@ int ref_bell_lowering(std::uint32_t rows, std::uint32_t features, std::uint32_t 
                                              static_cast<std::size_t>(value_capacity), values_out};
     cm::physical_bell_view view;
     st = cm::materialize_bell_candidate_host(source, plan, order, policy, c, ws, buffers, &view);
+    return static_cast<int>(st.code);
+}
+
+// build_execution_csr_view_host (physical_csr.hh:172-177), same arguments as orc_build_execution_csr.
+int ref_build_execution_csr(std::uint32_t rows, std::uint32_t nnz, std::uint32_t features, std::uint32_t fb_count,
+                            const std::uint32_t *fb_offsets, const std::uint32_t *fperm, const std::uint32_t *row_offsets,
+                            const std::uint32_t *block_ids, const std::uint32_t *local_ids, const std::uint32_t *canonical_ids,
+                            std::uint32_t *execution_ids) {
+    cellpack::feature_weighted_row_reduction_plan_view plan;
+    plan.semantic_plan_schema_version = cellpack::packing_plan_semantic_schema_version;
+    plan.geometry_identity_version = cellpack::feature_block_geometry_identity_version;
+    plan.feature_count = features;
+    plan.feature_block_count = fb_count;
+    plan.feature_block_geometry_identity = 0x03030303ull;
+    plan.feature_block_offsets = fb_offsets;
+    plan.feature_permutation = fperm;
+    cellpack::ordered_plan_partition_view ordered;
+    ordered.semantic_plan_schema_version = cellpack::packing_plan_semantic_schema_version;
+    ordered.full_row_count = rows;
+    ordered.row_count = rows;
+    ordered.feature_count = features;
+    ordered.nnz_count = nnz;
+    ordered.value_size_bytes = 1u;
+    ordered.feature_axis_fingerprint = 0x0303a11ull;
+    ordered.feature_axis_fingerprint_version = 1u;
+    ordered.row_domain_identity = 0x303ull;
+    ordered.row_offsets = row_offsets;
+    ordered.block_ids = block_ids;
+    ordered.local_feature_ids = local_ids;
+    ordered.canonical_feature_ids = canonical_ids;
+    static const unsigned char nothing = 0;
+    ordered.values = &nothing; // only its presence is checked; the view aliases it
+    cm::execution_csr_view out;
+    const cm::physical_view_status st = cm::build_execution_csr_view_host(plan, ordered, {nnz, execution_ids}, &out);
     return static_cast<int>(st.code);
 }
 

@@ -241,3 +241,33 @@ def test_edge_shapes(cuda_device, oracle):
     for bs in (8, 16, 32):
         geo = assert_same(oracle, low, args, bs, max_value_expansion=1e9, max_storage_expansion=1e9)
         assert geo.block_rows == 1 and geo.padded_features == 2 * bs
+
+
+def test_execution_csr_ids(cuda_device, oracle):
+    """cb200_build_execution_csr: the reference test's fixture, random partitions against the oracle, and
+    the violation flags (1 geometry, 2 identity)."""
+    from test_lowering_oracle import ordered_partition
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint32).view(np.int32)).to(cuda_device)
+    flags, ids = ops.build_execution_csr(dev([0, 2, 4]), dev([0, 0, 1, 1]), dev([0, 1, 0, 1]), dev([2, 0, 3, 1]), 4, [0, 2, 4],
+                                         dev([2, 0, 3, 1]))
+    assert flags == 0 and ids.tolist() == [0, 1, 2, 3]
+    rng = np.random.default_rng(12)
+    for blocks, rows, mean in ((1, 300, 40), (4, 1000, 70), (16, 257, 5)):
+        p = ordered_partition(rng, rows=rows, features=2000, feature_blocks=blocks, mean_nnz=mean)
+        host = [p["row_offsets"], p["block_ids"], p["local_ids"], p["canonical_ids"]]
+        status, want = oracle.build_execution_csr(*host, p["features"], p["fb_offsets"], p["fperm"])
+        assert status == 0
+        flags, ids = ops.build_execution_csr(*[dev(a) for a in host], p["features"], p["fb_offsets"], dev(p["fperm"]))
+        assert flags == 0 and np.array_equal(ids.cpu().numpy().view(np.uint32), want)
+        for field, make_bad, flag in ((3, lambda v: (v + 1) % p["features"], 2), (1, lambda v: v + blocks, 1),
+                                      (2, lambda v: v + 10_000, 1)):
+            bad = [a.copy() for a in host]
+            bad[field][11] = make_bad(bad[field][11])
+            assert oracle.build_execution_csr(*bad, p["features"], p["fb_offsets"], p["fperm"])[0] == {1: 3, 2: 2}[flag]
+            assert ops.build_execution_csr(*[dev(a) for a in bad], p["features"], p["fb_offsets"], dev(p["fperm"]))[0] & flag
+        swapped = [a.copy() for a in host]                 # two neighbours of one row out of order
+        r = int(np.argmax(np.diff(p["row_offsets"].astype(np.int64)) >= 2))
+        i = int(p["row_offsets"][r])
+        for a in swapped[1:]:
+            a[i], a[i + 1] = a[i + 1], a[i]
+        assert ops.build_execution_csr(*[dev(a) for a in swapped], p["features"], p["fb_offsets"], dev(p["fperm"]))[0] == 2

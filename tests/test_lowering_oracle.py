@@ -142,3 +142,38 @@ def test_row_major_layout_is_the_block_major_one_transposed(oracle):
         b = blk.reshape(geo["block_rows"], ell, bs, bs).transpose(0, 2, 1, 3).reshape(geo["padded_rows"], ell * bs)
         r = row.reshape(geo["padded_rows"], stride)
         assert np.array_equal(r[:, :ell * bs], b) and not r[:, ell * bs:].any()
+
+
+def ordered_partition(rng, rows, features, feature_blocks, mean_nnz):
+    """An ordered plan partition: per entry (semantic block, position in block, canonical id), rows in
+    ascending execution order; plus the plan's block offsets and feature permutation."""
+    h = synth.make_lowering_host(rows=rows, features=features, feature_blocks=feature_blocks, mean_nnz=mean_nnz,
+                                 seed=int(rng.integers(1 << 30)), value_dtype=np.uint8)
+    fbo, fperm, finv = h["fb_offsets"], h["fperm"], h["finv"]
+    ro = h["row_offsets"]
+    execution = finv[h["feature_ids"]]
+    for r in range(rows):                                   # a row's entries ascend in execution order
+        execution[ro[r]:ro[r + 1]] = np.sort(execution[ro[r]:ro[r + 1]])
+    block = (np.searchsorted(fbo, execution, side="right") - 1).astype(np.uint32)
+    return dict(row_offsets=ro, block_ids=block, local_ids=(execution - fbo[block]).astype(np.uint32),
+                canonical_ids=fperm[execution], features=features, fb_offsets=fbo, fperm=fperm, execution=execution)
+
+
+def test_execution_csr_kat_and_reference(oracle, reference):
+    """The fixture of the reference's test (tests/math_execution_csr_test.cu:30-33,57-86): execution ids
+    0..3; then random partitions and one violation of each kind through both implementations."""
+    fixture = ([0, 2, 4], [0, 0, 1, 1], [0, 1, 0, 1], [2, 0, 3, 1], 4, [0, 2, 4], [2, 0, 3, 1])
+    for lib in (oracle, reference):
+        status, ids = lib.build_execution_csr(*fixture)
+        assert status == 0 and ids.tolist() == [0, 1, 2, 3]
+    rng = np.random.default_rng(4)
+    for blocks in (1, 3, 9):
+        p = ordered_partition(rng, rows=120, features=500, feature_blocks=blocks, mean_nnz=15)
+        args = [p["row_offsets"], p["block_ids"], p["local_ids"], p["canonical_ids"], p["features"], p["fb_offsets"], p["fperm"]]
+        a, b = oracle.build_execution_csr(*args), reference.build_execution_csr(*args)
+        assert a[0] == b[0] == 0 and np.array_equal(a[1], b[1]) and np.array_equal(a[1], p["execution"])
+        for field, make_bad in ((3, lambda v: (v + 1) % p["features"]), (1, lambda v: v + blocks), (2, lambda v: v + 10_000)):
+            bad = list(args)
+            bad[field] = args[field].copy()
+            bad[field][7] = make_bad(bad[field][7])
+            assert oracle.build_execution_csr(*bad)[0] == reference.build_execution_csr(*bad)[0] != 0
