@@ -70,7 +70,7 @@ class SpmmProblem(C.Structure):
                 ("k", C.c_int64), ("n", C.c_int64), ("nnz", C.c_int64), ("bits", C.c_int32), ("policy", C.c_int32),
                 ("dense_dtype", C.c_int32), ("device", C.c_int32), ("structure_epoch", C.c_uint64),
                 ("host_row_ptr", C.c_void_p), ("deterministic", C.c_int32), ("multiply", C.c_int32),
-                ("device_matrix", C.POINTER(QCsr)), ("persistent_limit_bytes", C.c_uint64)]
+                ("device_matrix", C.POINTER(QCsr)), ("persistent_limit_bytes", C.c_uint64), ("value_generation", C.c_uint64)]
 
 
 class Launch(C.Structure):
@@ -79,7 +79,7 @@ class Launch(C.Structure):
                 ("alpha", C.c_float), ("beta", C.c_float), ("structure_epoch", C.c_uint64), ("row_begin", C.c_int64),
                 ("row_end", C.c_int64), ("stream", C.c_void_p), ("device", C.c_int32), ("workspace_device", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64), ("bias", C.c_void_p),
-                ("epilogue", C.c_int32)]
+                ("epilogue", C.c_int32), ("value_generation", C.c_uint64)]
 
 
 # cb200_epilogue: epilogue_kind of the request contract (operation.hh:49-61, same values)

@@ -98,6 +98,7 @@ const char *cb200_status_string(cb200_status status) {
     case CB200_STATUS_INSUFFICIENT_WORKSPACE: return "insufficient workspace";
     case CB200_STATUS_INVALID_STREAM: return "invalid stream";
     case CB200_STATUS_SEALED: return "session sealed";
+    case CB200_STATUS_STALE_VALUE: return "stale value generation";
     }
     return "unknown status";
 }
@@ -503,6 +504,12 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
           (reinterpret_cast<std::uintptr_t>(launch->workspace) & (prepared->workspace_alignment - 1u)) != 0u)))
         return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "workspace of %llu bytes needed, %llu given",
                     (unsigned long long)prepared->workspace_bytes, (unsigned long long)launch->workspace_bytes);
+    /* lifetimes.hh:160-172: the expected generation of a bound value plane must be the live one; here the
+     * "live" values of a prepared copy are those it was built from */
+    if ((prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr) && pr.value_generation != 0u &&
+        launch->value_generation != 0u && launch->value_generation != pr.value_generation)
+        return fail(CB200_STATUS_STALE_VALUE, "the prepared operation keeps a copy of value generation %llu, the launch binds %llu",
+                    (unsigned long long)pr.value_generation, (unsigned long long)launch->value_generation);
     if (launch->out == nullptr && pr.n != 0 && pr.m != 0)
         return fail(CB200_STATUS_INVALID_ARGUMENT, "null output");
     if (launch->dense == nullptr && pr.n != 0 && pr.k != 0) return fail(CB200_STATUS_INVALID_ARGUMENT, "null dense operand");

@@ -139,6 +139,7 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
     l.out_ld = out.stride[0];
     l.alpha = 1.0f; // output effect is `overwrite`: out = product
     l.beta = 0.0f;
+    l.value_generation = plane.generation.value;
     l.epilogue = state->epilogue;
     if (bias_epilogue(state->epilogue)) {
         if (launch.input_count < 3u || launch.inputs[2].storage.dense.data == nullptr)
@@ -159,6 +160,8 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
     case CB200_STATUS_INSUFFICIENT_WORKSPACE:
         return {core::operation_status_code::invalid_launch_bindings, ex::binding_validation_code::insufficient_workspace,
                 cb200_last_error()};
+    case CB200_STATUS_STALE_VALUE:
+        return {core::operation_status_code::invalid_launch_bindings, ex::binding_validation_code::stale_value, cb200_last_error()};
     case CB200_STATUS_INVALID_STREAM:
         return {core::operation_status_code::invalid_launch_bindings, ex::binding_validation_code::invalid_stream,
                 cb200_last_error()};
@@ -209,6 +212,7 @@ core::operation_status prepare_any(int projection_kind, bool composed, const cor
     p.multiply = dtype_of(numeric.multiply);
     p.device_matrix = policy.allow_persistent_preprocessing ? shape->device_matrix : nullptr;
     p.persistent_limit_bytes = policy.persistent_memory_limit;
+    p.value_generation = p.device_matrix != nullptr ? shape->device_matrix_generation.value : 0u;
 
     auto *state = new (std::nothrow) prepared_state;
     if (state == nullptr) return status(core::operation_status_code::preparation_failed, "out of host memory");

@@ -55,6 +55,10 @@ struct projection_catalog_entry {
     // optional: the device-resident matrix (final contents).  With numeric_policy.multiply == bf16 and
     // prepare_policy.allow_persistent_preprocessing, prepare builds the window-blocked copy from it
     const cb200_qcsr *device_matrix = nullptr;
+    // generation of the value plane whose codes, scales and offsets device_matrix points at.  A copy that
+    // prepare builds from them is only valid for that generation: a launch binding another one is refused
+    // as a stale value (the reference does not freeze values in prepared state, lifetimes.hh:80-81)
+    ex::value_generation device_matrix_generation{};
     // epilogue the operation composes into the projection (cb200_epilogue; epilogue_kind of the
     // request, operation.hh:49-61).  Anything but none is served by the composed-epilogue
     // candidates only; the bias kinds bind the bias vector (latent axis, fp32) as third input.

@@ -206,7 +206,7 @@ class PreparedSpmm:
 
     def __init__(self, projection: int, m: int, k: int, n: int, nnz: int, bits: int, policy: int, dense_dtype,
                  device, structure_epoch: int = 1, host_row_ptr: np.ndarray | None = None, deterministic=False,
-                 multiply: int = 0, device_matrix=None, persistent_limit_bytes: int = 0):
+                 multiply: int = 0, device_matrix=None, persistent_limit_bytes: int = 0, value_generation: int = 0):
         self.device = torch.device(device)
         pr = capi.header(capi.SpmmProblem())
         pr.projection, pr.m, pr.k, pr.n, pr.nnz, pr.bits, pr.policy = projection, m, k, n, nnz, bits, policy
@@ -224,6 +224,7 @@ class PreparedSpmm:
             self._matrix_desc = device_matrix.desc()
             pr.device_matrix = C.pointer(self._matrix_desc)
         pr.persistent_limit_bytes = persistent_limit_bytes  # 0: no limit on what prepare may keep on the device
+        pr.value_generation = value_generation              # generation of the values device_matrix holds (0: not tracked)
         self.problem = pr
         self.handle = C.c_void_p()
         capi.check(capi.lib().cb200_spmm_prepare(C.byref(pr), C.byref(self.handle)))
@@ -245,7 +246,7 @@ class PreparedSpmm:
 
     def make_launch(self, x, dense: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0, row_begin=0, row_end=0,
                     stream: int | None = None, epoch: int | None = None, epilogue: str | int = 0,
-                    bias: torch.Tensor | None = None) -> capi.Launch:
+                    bias: torch.Tensor | None = None, value_generation: int = 0) -> capi.Launch:
         ln = capi.header(capi.Launch())
         desc = x.desc()
         if isinstance(x, QuantizedBell):
@@ -263,6 +264,7 @@ class PreparedSpmm:
         ln.workspace_device = dev_index
         ln.workspace = None if self.workspace is None else self.workspace.data_ptr()
         ln.workspace_bytes = self.workspace_bytes
+        ln.value_generation = value_generation
         ln.epilogue = capi.EPILOGUE[epilogue] if isinstance(epilogue, str) else int(epilogue)
         if bias is not None:
             if bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != self.problem.n:

@@ -44,7 +44,8 @@ typedef enum cb200_status {
     CB200_STATUS_STALE_STRUCTURE = 6,
     CB200_STATUS_INSUFFICIENT_WORKSPACE = 7,
     CB200_STATUS_INVALID_STREAM = 8,
-    CB200_STATUS_SEALED = 9
+    CB200_STATUS_SEALED = 9,
+    CB200_STATUS_STALE_VALUE = 10 /* lifetime_validation_code::stale_value_generation, lifetimes.hh:88-94 */
 } cb200_status;
 
 /* execution::numeric_type, include/Cellerator/execution/operands.hh:9-20 (same values) */
@@ -257,6 +258,12 @@ typedef struct cb200_spmm_problem {
      * operation may keep; 0 = no limit.  A copy that would exceed it is not built (the schedule
      * falls back to the next one that fits). */
     uint64_t persistent_limit_bytes;
+    /* value_plane.generation (include/Cellerator/execution/lifetimes.hh:62-85) of the codes, scales and
+     * offsets device_matrix points at; 0 = not tracked.  The reference's rule is that a prepared
+     * operation does not freeze mutable values (lifetimes.hh:80-81); a copy built from device_matrix
+     * does, so a launch that names another generation (cb200_launch.value_generation) is refused with
+     * CB200_STATUS_STALE_VALUE instead of multiplying stale values. */
+    uint64_t value_generation;
 } cb200_spmm_problem;
 
 typedef struct cb200_prepared cb200_prepared;
@@ -301,6 +308,10 @@ typedef struct cb200_launch {
      * CB200_EPILOGUE_NONE only. */
     const float *bias;
     int32_t epilogue;        /* cb200_epilogue */
+    /* value_binding.expected_generation of the launch's value plane (lifetimes.hh:82-85); 0 = not
+     * tracked.  Compared with cb200_spmm_problem.value_generation when the prepared operation keeps a
+     * copy of the values. */
+    uint64_t value_generation;
 } cb200_launch;
 
 cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch);

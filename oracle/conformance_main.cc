@@ -462,6 +462,7 @@ int main(int argc, char **argv) {
         ts.projection = t.projection.runtime;
         ts.projection_kind = CB200_PROJECTION_TRANSPOSE;
         ts.device_matrix = &dm;
+        ts.device_matrix_generation = {5u}; // the generation of `plane`
         host::register_projection(ts);
         setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked", 1); // the matrix is far below the size prepare would pick it for
         core::prepared_operation pt{};
@@ -507,6 +508,14 @@ int main(int argc, char **argv) {
             }
         std::printf("  transpose (split products) max |d| / (||column||_1 max|G|) = %.3e\n", worst);
         CHECK(worst <= 1.0e-4, "split-product transpose within the fp32 bound of the reference referee's result");
+        // new values under the same structure: the copy prepare built is of generation 5
+        plane2.generation = {6u};
+        ex::value_binding v3{&plane2, {6u}};
+        l2.values = &v3;
+        const core::operation_status newer = core::run_prepared_operation(pt, l2);
+        CHECK(newer.code == core::operation_status_code::invalid_launch_bindings &&
+                  newer.binding == ex::binding_validation_code::stale_value,
+              "a launch with a newer value generation is refused by an operation that keeps a copy of the values");
         host::release_prepared(&pt);
         cudaFree(d_ws2);
     }

@@ -235,3 +235,24 @@ def test_split_products_meet_the_fp32_bound(cuda_device, oracle, monkeypatch, dt
     op.run(x, w, out, row_begin=256, row_end=700)
     assert torch.equal(out[256:700], y[256:700]) and torch.all(out[:256] == -3.0) and torch.all(out[700:] == -3.0)
     op.close()
+
+
+def test_value_generation_is_checked_by_operations_that_keep_values(cuda_device, oracle, monkeypatch):
+    """The reference does not freeze values in prepared state; an operation that keeps a copy of them
+    (window-blocked copy, dense tiles) refuses a launch that names another value generation."""
+    monkeypatch.setenv("CB200_FWD_SCHEDULE", "tensor_blocked")
+    rng = np.random.default_rng(2)
+    c = host_pack(oracle, random_csr(rng, rows=600, cols=400, max_nnz=100, bits=8, policy=1))
+    x = to_dev(c, cuda_device)
+    w, _ = dense(rng, 400, 64, torch.bfloat16, cuda_device)
+    y = torch.empty(600, 64, device=cuda_device)
+    op = prepared(x, 64, w, cuda_device, blocked=True, value_generation=7)
+    op.run(x, w, y, value_generation=7)
+    op.run(x, w, y)                                             # a launch that does not track generations
+    with pytest.raises(capi.Cb200Error, match="value generation"):
+        op.run(x, w, y, value_generation=8)
+    op.close()
+    monkeypatch.setenv("CB200_FWD_SCHEDULE", "gene_tiled")      # reads the codes at launch: any generation
+    exact = ops.PreparedSpmm(capi.PROJECTION_CSR, 600, 400, 64, x.nnz, 8, 1, w.dtype, cuda_device, value_generation=7)
+    exact.run(x, w, y, value_generation=8)
+    exact.close()
