@@ -54,6 +54,8 @@ struct prepared_state {
     std::int32_t bits = 8;
     std::int32_t decode_policy = CB200_DECODE_PER_GENE_AFFINE;
     std::int32_t epilogue = CB200_EPILOGUE_NONE;
+    ex::output_update_kind update = ex::output_update_kind::overwrite;
+    std::uint32_t alpha_id = ex::invalid_scalar_binding_id, beta_id = ex::invalid_scalar_binding_id;
     ex::operand_axis_contract inputs[3]{}; // X, dense, and the bias vector of a bias epilogue
     ex::operand_axis_contract outputs[1]{};
     ex::output_axis_contract orders[2]{};
@@ -137,8 +139,32 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
     l.dense_ld = dense.stride[0];
     l.out = static_cast<float *>(out.data);
     l.out_ld = out.stride[0];
-    l.alpha = 1.0f; // output effect is `overwrite`: out = product
-    l.beta = 0.0f;
+    // the output effect of the contract: overwrite (out = product), accumulate (out += product) or
+    // affine_accumulate with the launch's scalars (validate_launch_bindings has checked that they are bound)
+    l.alpha = 1.0f;
+    l.beta = state->update == ex::output_update_kind::overwrite ? 0.0f : 1.0f;
+    if (state->update == ex::output_update_kind::affine_accumulate) {
+        bool have_alpha = false, have_beta = false;
+        for (std::uint32_t i = 0u; i < launch.scalars.count && i < ex::maximum_scalar_bindings; ++i) {
+            const ex::scalar_binding &s = launch.scalars.values[i];
+            float value;
+            if (s.type == ex::numeric_type::f32) {
+                const std::uint32_t bits = static_cast<std::uint32_t>(s.bits);
+                std::memcpy(&value, &bits, sizeof value);
+            } else if (s.type == ex::numeric_type::f64) {
+                double wide;
+                std::memcpy(&wide, &s.bits, sizeof wide);
+                value = static_cast<float>(wide);
+            } else {
+                continue;
+            }
+            if (s.binding_id == state->alpha_id) { l.alpha = value; have_alpha = true; }
+            if (s.binding_id == state->beta_id) { l.beta = value; have_beta = true; }
+        }
+        if (!have_alpha || !have_beta)
+            return {core::operation_status_code::invalid_launch_bindings, ex::binding_validation_code::ok,
+                    "alpha and beta must be bound as f32 or f64 scalars"};
+    }
     l.value_generation = plane.generation.value;
     l.epilogue = state->epilogue;
     if (bias_epilogue(state->epilogue)) {
@@ -224,6 +250,9 @@ core::operation_status prepare_any(int projection_kind, bool composed, const cor
     state->bits = shape->bits;
     state->decode_policy = shape->decode_policy;
     state->epilogue = composed ? shape->epilogue : CB200_EPILOGUE_NONE;
+    state->update = shape->output_update;
+    state->alpha_id = shape->alpha_binding_id;
+    state->beta_id = shape->beta_binding_id;
     const bool transpose = projection_kind == CB200_PROJECTION_TRANSPOSE;
     // forward / Blocked-ELL: X(cells, genes) . W(genes, latent) -> Y(cells, latent)
     // transpose:             X(cells, genes)^T . G(cells, latent) -> G'(genes, latent)
@@ -238,8 +267,24 @@ core::operation_status prepare_any(int projection_kind, bool composed, const cor
     state->outputs[0] = axis_contract(ex::operand_kind::dense_tensor, transpose ? shape->genes : shape->cells, shape->latent);
     state->orders[0] = preserve_order(transpose ? shape->genes : shape->cells, 0u);
     state->orders[1] = preserve_order(shape->latent, 1u);
-    state->effects[0] = {ex::output_update_kind::overwrite, false, false, 0u, ex::invalid_scalar_binding_id,
-                         ex::invalid_scalar_binding_id};
+    switch (shape->output_update) {
+    case ex::output_update_kind::overwrite:
+        state->effects[0] = {ex::output_update_kind::overwrite, false, false, 0u, ex::invalid_scalar_binding_id,
+                             ex::invalid_scalar_binding_id};
+        break;
+    case ex::output_update_kind::accumulate:
+        state->effects[0] = {ex::output_update_kind::accumulate, true, false, 0u, ex::invalid_scalar_binding_id,
+                             ex::invalid_scalar_binding_id};
+        break;
+    case ex::output_update_kind::affine_accumulate:
+        state->effects[0] = {ex::output_update_kind::affine_accumulate, true, false, 0u, shape->alpha_binding_id,
+                             shape->beta_binding_id};
+        break;
+    default:
+        cb200_prepared_destroy(state->handle);
+        delete state;
+        return status(core::operation_status_code::unsupported_problem, "partial writes are addressed by row ranges, not by an output effect");
+    }
 
     core::prepared_operation prepared{};
     prepared.problem = problem;

@@ -59,6 +59,12 @@ struct projection_catalog_entry {
     // prepare builds from them is only valid for that generation: a launch binding another one is refused
     // as a stale value (the reference does not freeze values in prepared state, lifetimes.hh:80-81)
     ex::value_generation device_matrix_generation{};
+    // how the result meets the destination (output_effect_contract, launch_bindings.hh:19-33): overwrite
+    // (out = product), accumulate (out += product; the destination must be initialised) or
+    // affine_accumulate (out = alpha * product + beta * out, alpha and beta bound per launch as f32 or
+    // f64 scalars under these two binding ids)
+    ex::output_update_kind output_update = ex::output_update_kind::overwrite;
+    std::uint32_t alpha_binding_id = ex::invalid_scalar_binding_id, beta_binding_id = ex::invalid_scalar_binding_id;
     // epilogue the operation composes into the projection (cb200_epilogue; epilogue_kind of the
     // request, operation.hh:49-61).  Anything but none is served by the composed-epilogue
     // candidates only; the bias kinds bind the bias vector (latent axis, fp32) as third input.

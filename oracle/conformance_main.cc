@@ -415,6 +415,59 @@ int main(int argc, char **argv) {
         cudaFree(d_bias);
     }
 
+    // ---- forward with the affine output effect: out = alpha * product + beta * out ---------------
+    {
+        problem_ids a = make_ids(4u, core::projection_kind::csr, static_cast<std::uint64_t>(nnz));
+        host::projection_catalog_entry as = shape;
+        as.projection = a.projection.runtime;
+        as.output_update = ex::output_update_kind::affine_accumulate;
+        as.alpha_binding_id = 11u;
+        as.beta_binding_id = 12u;
+        CHECK(host::register_projection(as), "catalog accepts the affine projection");
+        st = core::prepare_candidate(*fwd, a.problem, a.structures, a.projection, policy_u8(ex::numeric_type::f32), {}, &prepared);
+        CHECK(static_cast<bool>(st), "prepare_candidate(forward, affine_accumulate)");
+        if (!st) std::printf("  message: %s\n", st.message);
+        CHECK(prepared.binding_contract.output_effects[0].update == ex::output_update_kind::affine_accumulate &&
+                  prepared.binding_contract.output_effects[0].requires_initialized_destination,
+              "the contract declares the affine effect and an initialised destination");
+        ex::relation_structure a_structure = structure;
+        a_structure.identity = a.structures.structures[0].runtime;
+        ex::value_plane a_plane = plane;
+        a_plane.structure = a_structure.identity;
+        ex::value_binding a_value{&a_plane, {5u}};
+        ex::biological_operand_view a_in[2] = {inputs[0], inputs[1]};
+        a_in[0].storage.relation.structure = a_structure.identity;
+        a_in[0].storage.relation.projection = a.projection.runtime;
+        std::vector<float> y0(M * N);
+        for (auto &v : y0) v = one(rng);
+        cudaMemcpy(d_y, y0.data(), y0.size() * sizeof(float), cudaMemcpyHostToDevice);
+        ex::launch_bindings al = launch;
+        al.structures = &a_structure;
+        al.values = &a_value;
+        al.inputs = a_in;
+        const float alpha = 2.0f;
+        const double beta = 0.5; // one scalar of each accepted type
+        al.scalars.count = 2u;
+        al.scalars.values[0] = {11u, ex::numeric_type::f32, {}, 0u};
+        std::memcpy(&al.scalars.values[0].bits, &alpha, sizeof alpha);
+        al.scalars.values[1] = {12u, ex::numeric_type::f64, {}, 0u};
+        std::memcpy(&al.scalars.values[1].bits, &beta, sizeof beta);
+        st = core::run_prepared_operation(prepared, al);
+        CHECK(static_cast<bool>(st), "run_prepared_operation(forward, alpha = 2, beta = 0.5)");
+        if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+        cudaStreamSynchronize(stream);
+        cudaMemcpy(y.data(), d_y, y.size() * sizeof(float), cudaMemcpyDeviceToHost);
+        double worst = 0.0; // `ref` still holds the plain product of the forward leg
+        for (std::size_t i = 0; i < y.size(); ++i)
+            worst = std::max(worst, std::fabs(static_cast<double>(y[i]) - (2.0 * ref[i] + 0.5 * static_cast<double>(y0[i]))));
+        std::printf("  affine forward max_abs=%.3e\n", worst);
+        CHECK(worst <= 1.0e-4, "alpha * product + beta * out within tolerance of the referee's product");
+        ex::launch_bindings missing = al;
+        missing.scalars.count = 1u;
+        CHECK(!static_cast<bool>(core::run_prepared_operation(prepared, missing)), "a launch without the beta scalar is refused");
+        host::release_prepared(&prepared);
+    }
+
     // ---- transpose candidate -------------------------------------------------------------------
     {
         problem_ids t = make_ids(1u, core::projection_kind::transpose_or_backward, static_cast<std::uint64_t>(nnz));
