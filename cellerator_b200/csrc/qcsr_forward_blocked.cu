@@ -23,7 +23,14 @@
 // no wait for the W stage (6.93 ms against 7.11 on the 1M x 33,538 matrix); the split-product
 // schedules need the next mantissa bits too and keep the code words.
 //
-// Structure of a CTA (608 threads, one CTA per SM, row groups dealt round-robin):
+// Three kernels live in this file, all persistent with one CTA per SM and row groups dealt round-robin:
+//   qcsr_fwd_blocked_kernel   code words, one scatter group: the split-product schedules (x2 / x3), and
+//                             baked words whose segments span several chunks;
+//   qcsr_fwd_blocked2_kernel  baked words, two scatter groups on alternate windows: the default for one
+//                             bf16 pass (6.30 ms on the 1M x 33,538 matrix);
+//   qcsr_fwd_dense_kernel     no scatter at all: prepare kept the operand tiles ("tensor_dense").
+//
+// Structure of a CTA of the first kernel (608 threads):
 //   warps 0-15  zero the A tile (128-byte swizzled K-major layout), wait for the segment's chunks
 //               (8 KB each, 2-stage ring), decode and scatter; later thread t < 256 owns TMEM lane t:
 //               row t of the group, and writes that row of Y;
