@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the UNMODIFIED reference sources.
 
-Run in a checkout that has the Cellerator tree (default /root/reference):
+Run on a machine that has the Cellerator tree (the Makefile's REFERENCE, or CB200_REFERENCE):
 
     make -C oracle ref && python tests/golden/make_golden.py
 

@@ -169,7 +169,7 @@ def test_golden_config1_full(oracle):
     assert list(oracle.digest_f32(y.astype(np.float32))) == z["y_digest"].tolist()
 
 
-# ---- against the compiled reference itself (only where /root/reference exists) ---------------
+# ---- against the compiled reference itself (only where the reference tree is present) ---------------
 
 @pytest.mark.parametrize("bits", [1, 2, 4, 8])
 @pytest.mark.parametrize("policy", [1, 2])
