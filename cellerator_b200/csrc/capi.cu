@@ -326,7 +326,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             device_scope scope(problem->device);
             cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
                                                           : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), false, &p->blocked);
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), false, false, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) {
                 delete p;
                 return st;
@@ -398,8 +398,10 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             device_scope scope(problem->device);
             cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
                                                           : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            // one pass of bf16 products: the entry words hold the decoded values (no look-up at launch)
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !split, &p->blocked);
+            // the entry words hold the decoded values (no look-up at launch); the split-product schedules
+            // get a second array with the next eight mantissa bits when the limit has room for it
+            const bool lo_words = split && (limit == 0u || static_cast<std::uint64_t>(problem->nnz) * 8u <= limit);
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !split || lo_words, lo_words, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) {
                 delete p;
                 return st;

@@ -64,12 +64,16 @@ struct blocked_layout {
     // baked: an entry word holds the decoded bf16 value (bits 0-15) and the byte position / 2 (bits
     // 16-30) instead of code and gene: the forward kernel stores it as it is, no table look-up.
     bool baked = false;
+    // second array of baked words for the split-product schedules: bf16(value - hi) under the same
+    // seg_ptr, so that the hi and the lo pass both run the look-up-free kernels
+    std::uint32_t *entries_lo = nullptr;
     const void *src_scales = nullptr, *src_offsets = nullptr; // baked into the entries / the tiles
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
 // current device; allocates and synchronises.  bake: decoded values in the entry words (forward, bf16 products only)
-cb200_status build_blocked_layout(const qcsr_view &x, bool bake, blocked_layout *out);
+// bake_lo (needs bake): also the array of the next eight mantissa bits (split-product schedules)
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, blocked_layout *out);
 void free_blocked_layout(blocked_layout *layout);
 // Dense operand tiles from the window-blocked copy (decoded values of `x` baked in; the entry words
 // are freed).  *built stays false, the copy untouched, when the device has no room.  Synchronises.

@@ -20,14 +20,16 @@
 // every lane of the CTA decodes entries, four at a time, with no divergence.  When the operation
 // multiplies in one bf16 pass, prepare decodes as well ("baked" words {bf16 value, byte position}):
 // a launch then stores the words' low halves where their high halves say, with no table look-up and
-// no wait for the W stage (6.93 ms against 7.11 on the 1M x 33,538 matrix); the split-product
-// schedules need the next mantissa bits too and keep the code words.
+// no wait for the W stage (6.93 ms against 7.11 on the 1M x 33,538 matrix).  The split-product
+// schedules need the next eight mantissa bits too: prepare writes a second array of baked words,
+// bf16(value - hi), under the same segment table (12.7 ms against 14.4 for the two passes), or keeps
+// the code words when the caller's memory limit has no room for it.
 //
 // Three kernels live in this file, all persistent with one CTA per SM and row groups dealt round-robin:
-//   qcsr_fwd_blocked_kernel   code words, one scatter group: the split-product schedules (x2 / x3), and
-//                             baked words whose segments span several chunks;
-//   qcsr_fwd_blocked2_kernel  baked words, two scatter groups on alternate windows: the default for one
-//                             bf16 pass (6.30 ms on the 1M x 33,538 matrix);
+//   qcsr_fwd_blocked_kernel   one scatter group: code words (split-product schedules under a memory
+//                             limit), and baked words whose segments span several chunks;
+//   qcsr_fwd_blocked2_kernel  baked words, two scatter groups on alternate windows: every pass of the
+//                             default schedules (6.30 ms per pass on the 1M x 33,538 matrix);
 //   qcsr_fwd_dense_kernel     no scatter at all: prepare kept the operand tiles ("tensor_dense").
 //
 // Structure of a CTA of the first kernel (608 threads):
@@ -128,7 +130,8 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                                                            const std::int32_t *col_idx, const std::uint8_t *packed,
                                                            std::int64_t rows, std::int64_t cols, int windows,
                                                            unsigned *counts, unsigned long long *cursor, std::uint32_t *entries,
-                                                           int bake, const float *scales, const float *offsets) {
+                                                           int bake, const float *scales, const float *offsets,
+                                                           std::uint32_t *entries_lo) {
     const int lane = threadIdx.x & 31;
     const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= rows) return; // warp-uniform
@@ -166,8 +169,13 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                     const std::int64_t gene = col_idx[i];
                     const float scale = scales != nullptr ? scales[gene] : 1.0f;
                     const float add = offsets != nullptr ? offsets[bake == 2 ? r : gene] : 0.0f;
-                    const __nv_bfloat16 v = __float2bfloat16_rn(fmaf(static_cast<float>(code), scale, add));
+                    const float value = fmaf(static_cast<float>(code), scale, add);
+                    const __nv_bfloat16 v = __float2bfloat16_rn(value);
                     word = static_cast<std::uint32_t>(__bfloat16_as_ushort(v)) | ((tile_offset(rl, gl) >> 1) << 16);
+                    if (entries_lo != nullptr) // the next eight mantissa bits, for the split-product passes
+                        entries_lo[place + static_cast<unsigned>(lane - start)] =
+                            static_cast<std::uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(value - __bfloat162float(v)))) |
+                            ((tile_offset(rl, gl) >> 1) << 16);
                 } else {
                     word = code | (static_cast<std::uint32_t>(gl) << 8) | ((tile_offset(rl, gl) >> 1) << 15);
                 }
@@ -1052,13 +1060,14 @@ bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n,
 void free_blocked_layout(blocked_layout *layout) {
     if (layout == nullptr) return;
     if (layout->entries != nullptr) cudaFree(layout->entries);
+    if (layout->entries_lo != nullptr) cudaFree(layout->entries_lo);
     if (layout->seg_ptr != nullptr) cudaFree(layout->seg_ptr);
     if (layout->dense_tiles != nullptr) cudaFree(layout->dense_tiles);
     *layout = blocked_layout{};
 }
 
 // Builds the window-blocked copy of `x` on the current device; synchronises.
-cb200_status build_blocked_layout(const qcsr_view &x, bool bake, blocked_layout *out) {
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, blocked_layout *out) {
     *out = blocked_layout{};
     if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed == nullptr)))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "the matrix handed to prepare has null arrays");
@@ -1077,9 +1086,9 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, blocked_layout 
     std::int64_t total = 0;
     if (err == cudaSuccess) {
         if (x.bits == 8)
-            blocked_pass_kernel<8, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr);
+            blocked_pass_kernel<8, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr);
         else
-            blocked_pass_kernel<4, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr);
+            blocked_pass_kernel<4, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr);
         count_launch();
         segment_scan_kernel<<<1, 1024>>>(counts, segments, out->seg_ptr, cursor);
         count_launch();
@@ -1089,11 +1098,15 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, blocked_layout 
     if (err == cudaSuccess && total > 0) {
         err = cudaMalloc(reinterpret_cast<void **>(&out->entries), static_cast<std::size_t>(total) * sizeof(std::uint32_t));
         if (err == cudaSuccess) err = cudaMemset(out->entries, 0x80, static_cast<std::size_t>(total) * sizeof(std::uint32_t)); // padding = invalid
+        if (err == cudaSuccess && bake && bake_lo) {
+            err = cudaMalloc(reinterpret_cast<void **>(&out->entries_lo), static_cast<std::size_t>(total) * sizeof(std::uint32_t));
+            if (err == cudaSuccess) err = cudaMemset(out->entries_lo, 0x80, static_cast<std::size_t>(total) * sizeof(std::uint32_t));
+        }
         if (err == cudaSuccess) {
             if (x.bits == 8)
-                blocked_pass_kernel<8, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets);
+                blocked_pass_kernel<8, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo);
             else
-                blocked_pass_kernel<4, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets);
+                blocked_pass_kernel<4, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo);
             count_launch();
             err = cudaGetLastError();
         }
@@ -1108,7 +1121,7 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, blocked_layout 
     out->groups = groups;
     out->windows = windows;
     out->total_entries = total;
-    out->bytes = static_cast<std::uint64_t>(total) * 4u + static_cast<std::uint64_t>(segments + 1) * 8u;
+    out->bytes = static_cast<std::uint64_t>(total) * (out->entries_lo != nullptr ? 8u : 4u) + static_cast<std::uint64_t>(segments + 1) * 8u;
     out->src_row_ptr = x.row_ptr;
     out->src_col_idx = x.col_idx;
     out->src_packed = x.packed;
@@ -1219,7 +1232,7 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     if (x.row_ptr != layout.src_row_ptr || x.col_idx != layout.src_col_idx || x.packed != layout.src_packed ||
         (layout.baked && (x.scales != layout.src_scales || x.offsets != layout.src_offsets)))
         return fail(CB200_STATUS_STALE_STRUCTURE, "the launch's matrix is not the one the window-blocked copy was built from");
-    if (layout.baked && split_products) return CB200_STATUS_SUCCESS; // split passes decode from the codes
+    if (layout.baked && split_products && layout.entries_lo == nullptr) return CB200_STATUS_SUCCESS; // no lo words: another kernel runs
 
     int *status = static_cast<int *>(workspace);
     unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
@@ -1259,6 +1272,7 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
             packed_part = passes[i].w_part;
         }
         p.value_part = passes[i].value_part;
+        if (layout.baked) p.entries = passes[i].value_part != 0 ? layout.entries_lo : layout.entries; // baked words carry their part
         p.beta = i == 0 ? d.beta : 1.0f;
         p.bias = d.bias;
         p.epilogue = i + 1 == pass_count ? d.epilogue : CB200_EPILOGUE_NONE;
