@@ -79,6 +79,10 @@ void free_blocked_layout(blocked_layout *layout);
 // are freed).  *built stays false, the copy untouched, when the device has no room.  Synchronises.
 std::uint64_t qcsr_dense_tile_bytes(std::int64_t rows, std::int64_t cols);
 cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, bool *built);
+// *taken as for the blocked launch below; the tiles hold bf16(value): one pass of bf16 products only
+cb200_status launch_qcsr_forward_dense(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                       std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                       const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken);
 // *taken is false when the launch cannot use the copy (row range not starting on a group boundary,
 // workspace too small, ...); a matrix other than the one the copy was built from is an error.
 // split_products == false: one pass of bf16 products (bf16 W only); true: fp32 products rebuilt from
