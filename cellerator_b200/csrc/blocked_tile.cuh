@@ -56,6 +56,12 @@ __host__ __device__ constexpr std::uint32_t tile_offset(int rl, int gl) {
     return static_cast<std::uint32_t>((rl >> 7) * kSubBlockBytes + (gl >> 6) * kHalfBytes + ((rl & 127) >> 3) * 1024 +
                                       (rl & 7) * 128 + ((((gl & 63) >> 3) ^ (rl & 7)) * 16) + (gl & 7) * 2);
 }
+// The transpose kernel's tile of the same (group, window): M = gene, K = cell, K-major with the 128-byte
+// swizzle: [cell quarter of 64][gene][64 cells], the 16-byte pieces of a gene's line permuted by gene mod 8.
+__host__ __device__ constexpr std::uint32_t tile_offset_gene_major(int rl, int gl) {
+    return static_cast<std::uint32_t>((rl >> 6) * (kWin * 128) + (gl >> 3) * 1024 + (gl & 7) * 128 + ((((rl & 63) >> 3) ^ (gl & 7)) << 4) +
+                                      ((rl & 7) << 1));
+}
 
 
 // K-major operand, no swizzle: LBO = 128 B between the two core matrices one K = 16 step reads,

@@ -326,7 +326,12 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             device_scope scope(problem->device);
             cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
                                                           : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), false, false, &p->blocked);
+            // decoded values in the entry words, positions of this kernel's gene-major tile; a second
+            // array with the next eight mantissa bits for the split passes when the limit has room
+            const bool t_split = problem->multiply != CB200_DTYPE_BF16;
+            const std::uint64_t t_limit = problem->persistent_limit_bytes;
+            const bool t_lo = t_split && (t_limit == 0u || static_cast<std::uint64_t>(problem->nnz) * 8u <= t_limit);
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !t_split || t_lo, t_lo, true, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) {
                 delete p;
                 return st;
@@ -401,7 +406,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             // the entry words hold the decoded values (no look-up at launch); the split-product schedules
             // get a second array with the next eight mantissa bits when the limit has room for it
             const bool lo_words = split && (limit == 0u || static_cast<std::uint64_t>(problem->nnz) * 8u <= limit);
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !split || lo_words, lo_words, &p->blocked);
+            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !split || lo_words, lo_words, false, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) {
                 delete p;
                 return st;

@@ -67,13 +67,16 @@ struct blocked_layout {
     // second array of baked words for the split-product schedules: bf16(value - hi) under the same
     // seg_ptr, so that the hi and the lo pass both run the look-up-free kernels
     std::uint32_t *entries_lo = nullptr;
+    // the baked words hold byte positions in the transpose kernel's gene-major tile, not the forward one
+    bool baked_gene_major = false;
     const void *src_scales = nullptr, *src_offsets = nullptr; // baked into the entries / the tiles
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
 // current device; allocates and synchronises.  bake: decoded values in the entry words (forward, bf16 products only)
 // bake_lo (needs bake): also the array of the next eight mantissa bits (split-product schedules)
-cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, blocked_layout *out);
+// gene_major (needs bake): byte positions of the transpose kernel's tile in the baked words
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, bool gene_major, blocked_layout *out);
 void free_blocked_layout(blocked_layout *layout);
 // Dense operand tiles from the window-blocked copy (decoded values of `x` baked in; the entry words
 // are freed).  *built stays false, the copy untouched, when the device has no room.  Synchronises.

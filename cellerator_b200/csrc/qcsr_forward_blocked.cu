@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                                                            std::int64_t rows, std::int64_t cols, int windows,
                                                            unsigned *counts, unsigned long long *cursor, std::uint32_t *entries,
                                                            int bake, const float *scales, const float *offsets,
-                                                           std::uint32_t *entries_lo) {
+                                                           std::uint32_t *entries_lo, int gene_major) {
     const int lane = threadIdx.x & 31;
     const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= rows) return; // warp-uniform
@@ -126,11 +126,11 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                     const float add = offsets != nullptr ? offsets[bake == 2 ? r : gene] : 0.0f;
                     const float value = fmaf(static_cast<float>(code), scale, add);
                     const __nv_bfloat16 v = __float2bfloat16_rn(value);
-                    word = static_cast<std::uint32_t>(__bfloat16_as_ushort(v)) | ((tile_offset(rl, gl) >> 1) << 16);
+                    const std::uint32_t position = ((gene_major != 0 ? tile_offset_gene_major(rl, gl) : tile_offset(rl, gl)) >> 1) << 16;
+                    word = static_cast<std::uint32_t>(__bfloat16_as_ushort(v)) | position;
                     if (entries_lo != nullptr) // the next eight mantissa bits, for the split-product passes
                         entries_lo[place + static_cast<unsigned>(lane - start)] =
-                            static_cast<std::uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(value - __bfloat162float(v)))) |
-                            ((tile_offset(rl, gl) >> 1) << 16);
+                            static_cast<std::uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(value - __bfloat162float(v)))) | position;
                 } else {
                     word = code | (static_cast<std::uint32_t>(gl) << 8) | ((tile_offset(rl, gl) >> 1) << 15);
                 }
@@ -732,7 +732,7 @@ void free_blocked_layout(blocked_layout *layout) {
 }
 
 // Builds the window-blocked copy of `x` on the current device; synchronises.
-cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, blocked_layout *out) {
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, bool gene_major, blocked_layout *out) {
     *out = blocked_layout{};
     if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed == nullptr)))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "the matrix handed to prepare has null arrays");
@@ -751,9 +751,9 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     std::int64_t total = 0;
     if (err == cudaSuccess) {
         if (x.bits == 8)
-            blocked_pass_kernel<8, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr);
+            blocked_pass_kernel<8, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
         else
-            blocked_pass_kernel<4, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr);
+            blocked_pass_kernel<4, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
         count_launch();
         segment_scan_kernel<<<1, 1024>>>(counts, segments, out->seg_ptr, cursor);
         count_launch();
@@ -769,9 +769,9 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
         }
         if (err == cudaSuccess) {
             if (x.bits == 8)
-                blocked_pass_kernel<8, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo);
+                blocked_pass_kernel<8, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
             else
-                blocked_pass_kernel<4, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo);
+                blocked_pass_kernel<4, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
             count_launch();
             err = cudaGetLastError();
         }
@@ -791,6 +791,7 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     out->src_col_idx = x.col_idx;
     out->src_packed = x.packed;
     out->baked = bake;
+    out->baked_gene_major = bake && gene_major;
     out->src_scales = x.scales;
     out->src_offsets = x.offsets;
     return CB200_STATUS_SUCCESS;
@@ -807,7 +808,7 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
         if (split_products) return CB200_STATUS_SUCCESS; // the tiles hold bf16(value) only
         return launch_qcsr_forward_dense(x, d, row_begin, row_end, workspace, workspace_bytes, layout, sm_count, stream, taken);
     }
-    if (layout.seg_ptr == nullptr) return CB200_STATUS_SUCCESS;
+    if (layout.seg_ptr == nullptr || layout.baked_gene_major) return CB200_STATUS_SUCCESS; // the transpose's words are not ours
     if (!qcsr_blocked_shape_ok(x.rows, x.cols, d.n, x.bits, d.dense_dtype)) return CB200_STATUS_SUCCESS;
     const bool w_bf16 = d.dense_dtype == CB200_DTYPE_BF16;
     if (!w_bf16 && !split_products) return CB200_STATUS_SUCCESS; // one bf16 pass over an fp32 W is never asked for

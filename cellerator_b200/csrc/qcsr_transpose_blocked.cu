@@ -22,6 +22,12 @@
 // vector reductions (the (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so
 // several CTAs contribute to the same genes; G' is first scaled by beta by a small kernel).
 //
+// Entry words.  Prepare normally bakes them for this kernel: {bf16 value, byte position / 2 in the
+// gene-major tile}, a hi array and, for the split passes, a lo array with bf16(value - hi); the scatter
+// then stores words as they are (18.5 ms against 23.6 for the three split passes on the 1M x 33,538
+// matrix, 6.25 against 7.93 for one bf16 pass).  Code words {code, gene, forward-tile position} are
+// still decoded here when the caller's memory limit left no room for the second array.
+//
 // Structure of a CTA (608 threads, one CTA per SM): warps 0-15 zero, decode and scatter -- as two
 // groups of eight warps on alternate tiles, each with its own tile buffer and 8 KB chunk stage, so
 // that the per-tile chains of waits overlap (23.6 ms against 24.4 for the three split passes on the
@@ -116,7 +122,9 @@ __global__ void __launch_bounds__(256) pack_g_kernel(const float *g, std::int64_
     }
 }
 
-template<int NC>
+// BAKED: the entry words hold {bf16 value, byte position / 2 in this kernel's tile}, written at prepare
+// (hi and lo arrays for the split passes): the scatter stores them as they are, no table, no arithmetic.
+template<int NC, bool BAKED>
 __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(const tb_params p) {
     constexpr int GREC = g_record_bytes(NC);
     constexpr int kTmemCols = kSetWindows * NC; // 512 (N = 64) or 256 (N = 32)
@@ -234,6 +242,14 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                         for (int i = gtid * 4; i < n_entries; i += kGroupThreads * 4) { // segments are padded to multiples of 4
                             const uint4 e4 = chunk[i >> 2];
                             const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+                            if constexpr (BAKED) {
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) { // padding words (top bit set) go to a scratch slot
+                                    unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + (((e[k] >> 16) & 0x7fffu) << 1) : scratch_slot;
+                                    *reinterpret_cast<unsigned short *>(dst) = static_cast<unsigned short>(e[k] & 0xffffu);
+                                }
+                                continue;
+                            }
                             float2 t[4];
 #pragma unroll
                             for (int k = 0; k < 4; ++k) t[k] = wtable[(e[k] >> 8) & (kWin - 1)];
@@ -386,16 +402,16 @@ template<int NC> constexpr std::size_t tb_smem_bytes() {
            (6 + 2 * kGStages + 2 * kChunkStages) * sizeof(std::uint64_t) + (kChunkStages + 1) * 4 + 16;
 }
 
-template<int NC>
+template<int NC, bool BAKED>
 cb200_status launch_one(const tb_params &p, int sm_count, cudaStream_t stream) {
     constexpr std::size_t smem = tb_smem_bytes<NC>();
     static_assert(smem <= 232448, "shared memory budget");
-    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_transpose_blocked_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_transpose_blocked_kernel<NC, BAKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
     const std::int64_t sets = (p.windows + kSetWindows - 1) / kSetWindows;
     const std::int64_t units = sets * p.group_count;
     const unsigned grid = static_cast<unsigned>(units < sm_count ? units : sm_count);
-    qcsr_transpose_blocked_kernel<NC><<<grid, kThreads, smem, stream>>>(p);
+    qcsr_transpose_blocked_kernel<NC, BAKED><<<grid, kThreads, smem, stream>>>(p);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
@@ -418,7 +434,9 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
                                            const blocked_layout &layout, bool split_products, int sm_count,
                                            cudaStream_t stream, bool *taken) {
     *taken = false;
-    if (layout.seg_ptr == nullptr || layout.baked || d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS; // this kernel decodes codes
+    if (layout.seg_ptr == nullptr || d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS;
+    if (layout.baked && (!layout.baked_gene_major || (split_products && layout.entries_lo == nullptr)))
+        return CB200_STATUS_SUCCESS; // baked words of the forward tile, or no lo words for the split passes
     if (!qcsr_transpose_blocked_shape_ok(x.rows, x.cols, d.n, x.bits) || d.dense_dtype != CB200_DTYPE_F32) return CB200_STATUS_SUCCESS;
     if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return CB200_STATUS_SUCCESS;
     if (workspace == nullptr || workspace_bytes < qcsr_transpose_blocked_workspace_bytes(x.rows, d.n)) return CB200_STATUS_SUCCESS;
@@ -426,7 +444,8 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
     const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
     // the kernel reads 256 row offsets per group: the last group must not run past the array
     if (row_policy && x.offsets != nullptr && x.rows % kRows != 0) return CB200_STATUS_SUCCESS;
-    if (x.row_ptr != layout.src_row_ptr || x.col_idx != layout.src_col_idx || x.packed != layout.src_packed)
+    if (x.row_ptr != layout.src_row_ptr || x.col_idx != layout.src_col_idx || x.packed != layout.src_packed ||
+        (layout.baked && (x.scales != layout.src_scales || x.offsets != layout.src_offsets)))
         return fail(CB200_STATUS_STALE_STRUCTURE, "the launch's matrix is not the one the window-blocked copy was built from");
 
     *taken = true;
@@ -460,6 +479,7 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
     for (int pass = 0; pass < passes; ++pass) { // (G hi, value hi), (G hi, value lo), (G lo, value hi): G hi is packed once
         const int g_part = pass == 2 ? 1 : 0;
         p.value_part = pass == 1 ? 1 : 0;
+        if (layout.baked) p.entries = pass == 1 ? layout.entries_lo : layout.entries; // baked words carry their part
         if (g_part != packed_part) {
             pack_g_kernel<<<static_cast<unsigned>(group_end - group_begin), 256, 0, stream>>>(
                 static_cast<const float *>(d.dense), d.dense_ld, static_cast<int>(d.n), row_begin, row_end, group_begin, g_part,
@@ -468,7 +488,8 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
             CB200_CUDA_OK(cudaGetLastError());
             packed_part = g_part;
         }
-        const cb200_status st = d.n == 64 ? launch_one<64>(p, sm_count, stream) : launch_one<32>(p, sm_count, stream);
+        const cb200_status st = layout.baked ? (d.n == 64 ? launch_one<64, true>(p, sm_count, stream) : launch_one<32, true>(p, sm_count, stream))
+                                             : (d.n == 64 ? launch_one<64, false>(p, sm_count, stream) : launch_one<32, false>(p, sm_count, stream));
         if (st != CB200_STATUS_SUCCESS) return st;
     }
     return CB200_STATUS_SUCCESS;
