@@ -24,7 +24,7 @@
 //
 // Entry words.  Prepare normally bakes them for this kernel: {bf16 value, byte position / 2 in the
 // gene-major tile}, a hi array and, for the split passes, a lo array with bf16(value - hi); the scatter
-// then stores words as they are (18.5 ms against 23.6 for the three split passes on the 1M x 33,538
+// then stores words as they are (18.1 ms against 23.6 for the three split passes on the 1M x 33,538
 // matrix, 6.25 against 7.93 for one bf16 pass).  Code words {code, gene, forward-tile position} are
 // still decoded here when the caller's memory limit left no room for the second array.
 //
@@ -202,8 +202,9 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
             const std::int64_t count = dmin(p.group_count - gi0, u1 - u);
             const int nwin = static_cast<int>(dmin(kSetWindows, p.windows - set * kSetWindows));
             // scale / zero-point of the set's genes; nobody still reads the previous run's table
-            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
-            for (int i = tid; i < kSetWindows * kWin; i += kProducerThreads) {
+            // (baked words need neither the table nor the row offsets below)
+            if constexpr (!BAKED) asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+            for (int i = tid; !BAKED && i < kSetWindows * kWin; i += kProducerThreads) {
                 const std::int64_t gene = set * kSetWindows * kWin + i;
                 float2 so = make_float2(0.0f, 0.0f);
                 if (gene < p.cols) {
@@ -212,10 +213,10 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                 }
                 table[i] = so;
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
+            if constexpr (!BAKED) asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
             for (std::int64_t gi = gi0; gi < gi0 + count; ++gi) {
                 const std::int64_t group = p.group_begin + gi;
-                if (use_row_offset) {
+                if (!BAKED && use_row_offset) {
                     asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the previous group's scatter is over
                     if (tid < kRows) row_offset_s[tid] = __ldg(p.row_offsets + group * kRows + tid); // padded by the launcher's check
                     asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
