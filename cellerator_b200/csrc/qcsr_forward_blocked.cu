@@ -827,7 +827,8 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
 
     blocked_params p{};
-    p.entries = layout.entries; p.seg_ptr = layout.seg_ptr; p.row_offsets = row_policy ? x.offsets : nullptr;
+    p.entries = layout.entries; p.seg_ptr = layout.seg_ptr;
+    p.row_offsets = row_policy && !layout.baked ? x.offsets : nullptr; // baked words already hold the row's offset
     p.records = records; p.y = d.out; p.y_ld = d.out_ld; p.row_end = row_end;
     p.group_begin = row_begin / kRows; p.group_end = (row_end + kRows - 1) / kRows; p.windows = layout.windows;
     p.alpha = d.alpha; p.status = status;
