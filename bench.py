@@ -154,7 +154,6 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         return wl
     x = synth.make_qcsr_device(**cfg, device=device, seed=seed, row_base=row_base, total_rows=rows * world)
     torch.cuda.synchronize(device)
-    t_prepare = time.perf_counter()               # prepare is outside the timed region; its cost is reported
     if name == "c3_transpose":
         n = 64
         dense = torch.randn(rows, n, generator=g).to(device)
@@ -164,6 +163,8 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         # split products (three bf16 passes rebuild each product to ~3 * 2^-17; "tensor_blocked_x3").
         # --multiply bf16: one pass, values and G rounded to bf16 (1e-2 bound).  --no-prepare-matrix:
         # the fp32-FMA kernel with L2 vector reductions.
+        torch.cuda.synchronize(device)
+        t_prepare = time.perf_counter()           # prepare is outside the timed region; its cost is reported
         op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype,
                               device, multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
                               device_matrix=x if prepare_matrix else None)
@@ -176,6 +177,8 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         # allowed (tensor-core schedule, one pass).  --multiply f32: fp32 products, rebuilt on the tensor
         # cores from two bf16 passes when the matrix is handed to prepare, or computed by the fp32-FMA
         # kernel with --no-prepare-matrix
+        torch.cuda.synchronize(device)
+        t_prepare = time.perf_counter()           # prepare is outside the timed region; its cost is reported
         op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype, device,
                               host_row_ptr=x.host_row_ptr,
                               multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
