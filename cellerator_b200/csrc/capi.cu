@@ -316,6 +316,10 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             blocked = blocked && problem->m >= 16 * 256 && p->mean_row_nnz >= 0.004 * static_cast<double>(problem->k);
         else
             blocked = blocked && std::strcmp(force, "tensor_blocked") == 0;
+        // a word per entry has to fit under the caller's limit, as in the forward direction
+        if (blocked && problem->persistent_limit_bytes != 0u &&
+            static_cast<std::uint64_t>(problem->nnz) * 4u > problem->persistent_limit_bytes)
+            blocked = false;
         if (blocked) {
             const cb200_qcsr &dm = *problem->device_matrix;
             if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||

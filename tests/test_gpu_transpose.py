@@ -218,3 +218,33 @@ def test_tensor_transpose_split_products_meet_the_fp32_bound(cuda_device, oracle
     out2 = op.run(x, g, init.clone(), alpha=2.0, beta=0.5).cpu().numpy()
     assert np.allclose(out2, 2.0 * ref + 0.5 * init.cpu().numpy(), rtol=1e-4, atol=1e-4 * gmax * (cl1.max() + 1))
     op.close()
+
+
+def test_tensor_transpose_respects_the_memory_limit(cuda_device, oracle, monkeypatch):
+    """persistent_limit_bytes with room for one word per entry but not two: the split passes decode
+    the code words at launch and still meet the fp32 bound; below one word per entry the exact
+    kernel runs.  The limit is prepare_policy.persistent_memory_limit of the reference."""
+    monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+    rng = np.random.default_rng(91)
+    rows, cols, n = 256 * 3, 900, 64
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=200, bits=8, policy=1))
+    x = to_dev(c, cuda_device)
+    g, g_host = dense(rng, rows, n, torch.float32, cuda_device, std=1.0)
+    ref = oracle.qcsr_transpose(8, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"],
+                                c["scales"], c["offsets"], g_host, cols)
+    cl1 = col_l1_of(oracle, c)
+    gmax = float(np.abs(g_host).max())
+    one_word = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cols, n, x.nnz, 8, 1, g.dtype, cuda_device,
+                                device_matrix=x, persistent_limit_bytes=6 * x.nnz)
+    assert one_word.schedule == "tensor_blocked_x3"
+    out = one_word.run(x, g, torch.full((cols, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(one_word.workspace[:4].view(torch.int32).item()) == 0
+    assert_transpose_close(out.cpu().numpy(), ref, cl1, gmax)
+    one_word.close()
+    none = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cols, n, x.nnz, 8, 1, g.dtype, cuda_device,
+                            device_matrix=x, persistent_limit_bytes=2 * x.nnz)
+    assert none.schedule == "vector_reductions"
+    out = none.run(x, g, torch.full((cols, n), float("nan"), device=cuda_device))
+    assert_transpose_close(out.cpu().numpy(), ref, cl1, gmax)
+    none.close()
