@@ -117,7 +117,7 @@ def algorithmic_bytes(kind, m, k, n, nnz, bits, dense_bytes):
 
 
 def build_workload(name, device, rank, world, seed=0, rows_override=None, multiply="bf16", prepare_matrix=True,
-                   persistent_limit_bytes=0):
+                   persistent_limit_bytes=0, deterministic=False):
     import torch
 
     from cellerator_b200 import capi, ops, synth
@@ -162,12 +162,13 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         # fp32 products and hands the matrix to prepare, which selects the tensor-core schedule with
         # split products (three bf16 passes rebuild each product to ~3 * 2^-17; "tensor_blocked_x3").
         # --multiply bf16: one pass, values and G rounded to bf16 (1e-2 bound).  --no-prepare-matrix:
-        # the fp32-FMA kernel with L2 vector reductions.
+        # the fp32-FMA kernel with L2 vector reductions.  --deterministic: fp32 FMAs in a fixed order, gathered
+        # gene by gene from a gene-major copy that prepare builds ("gene_gather").
         torch.cuda.synchronize(device)
         t_prepare = time.perf_counter()           # prepare is outside the timed region; its cost is reported
         op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype,
                               device, multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
-                              device_matrix=x if prepare_matrix else None)
+                              device_matrix=x if prepare_matrix else None, deterministic=deterministic)
         kind, dbytes = "transpose", 4
     else:
         n = cfg["n"]
@@ -284,7 +285,7 @@ def run_ours(args):
     if args.multiply is None:  # what the contract's tolerance for the workload's dense operand allows
         args.multiply = "f32" if args.workload == "c3_transpose" else "bf16"
     wl = build_workload(args.workload, device, rank, world, rows_override=args.rows, multiply=args.multiply,
-                        prepare_matrix=not args.no_prepare_matrix,
+                        prepare_matrix=not args.no_prepare_matrix, deterministic=args.deterministic,
                         persistent_limit_bytes=int(args.persistent_limit_gb * 1e9))
     op, x, dense, out = wl["op"], wl["x"], wl["dense"], wl["out"]
     launch = op.make_launch(x, dense, out)
@@ -671,6 +672,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_forward", choices=["c2_forward", "c3_transpose", "c4_4bit", "c5_bell", "c5_lowering"])
     ap.add_argument("--rows", type=int, default=0, help="override cells per GPU (profiling on a small case)")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="c3_transpose: ask prepare for the schedule whose fp32 sums have a fixed order")
     ap.add_argument("--no-prepare-matrix", action="store_true",
                     help="do not hand the matrix to prepare: no window-blocked copy, CSR-only schedules")
     ap.add_argument("--persistent-limit-gb", type=float, default=0.0,

@@ -166,6 +166,7 @@ EXPORTED_SYMBOLS = [
     "cb200_qcsr_forward_static",
     "cb200_bell_lowering_workspace", "cb200_bell_lowering_query", "cb200_bell_lowering_materialize",
     "cb200_pack_dense_operand", "cb200_build_execution_csr",
+    "cb200_qcsr_gene_major_workspace", "cb200_qcsr_gene_major",
     "cb200_public_projection_scratch", "cb200_public_projection_forward", "cb200_public_projection_backward_rhs",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
@@ -200,6 +201,10 @@ def lib() -> C.CDLL:
         L.cb200_qbell_quantize_rows.argtypes = [C.POINTER(QBell), C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]
         L.cb200_qbell_dequantize_rows.argtypes = [C.POINTER(QBell), C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]
         L.cb200_backend_query.argtypes = [C.c_int32, C.POINTER(NumericPolicy), C.POINTER(Capability)]
+        L.cb200_qcsr_gene_major_workspace.restype = C.c_uint64
+        L.cb200_qcsr_gene_major_workspace.argtypes = [C.c_int64, C.c_int64]
+        L.cb200_qcsr_gene_major.argtypes = [C.POINTER(QCsr), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64,
+                                            C.c_int32, C.c_void_p]
         L.cb200_spmm_prepare.argtypes = [C.POINTER(SpmmProblem), C.POINTER(C.c_void_p)]
         L.cb200_prepared_destroy.argtypes = [C.c_void_p]
         L.cb200_prepared_destroy.restype = None

@@ -69,6 +69,8 @@ struct cb200_prepared {
     // ... and, when prepare was given the device-resident matrix and bf16 products are allowed, the
     // window-blocked copy the tensor-core kernel streams
     blocked_layout blocked;
+    // ... or, for a transpose that has to be deterministic, the gene-major copy the gather kernel reads
+    gene_major_layout gene_major;
     std::uint64_t persistent_bytes;
 };
 
@@ -264,7 +266,13 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         return fail(CB200_STATUS_UNSUPPORTED, "bf16 products on a forward projection need a bf16 dense operand");
     if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         if (problem->dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes fp32 G");
-        if (problem->deterministic) return fail(CB200_STATUS_UNSUPPORTED, "transpose is not deterministic");
+        // a fixed order of the sums needs the gene-major copy, which prepare builds from the matrix
+        if (problem->deterministic &&
+            (problem->device_matrix == nullptr || !qcsr_transpose_gather_shape_ok(problem->n) ||
+             !qcsr_gene_major_shape_ok(problem->m, problem->k, problem->bits)))
+            return fail(CB200_STATUS_UNSUPPORTED,
+                        "a deterministic transpose needs the device matrix at prepare time, N in {32, 64, 128} and a gene count "
+                        "whose counters fit shared memory; the other transpose kernels add in atomic order");
     } else if (problem->projection == CB200_PROJECTION_CSR || problem->projection == CB200_PROJECTION_BLOCKED_ELL) {
         if (!supported_dense(problem->dense_dtype)) return fail(CB200_STATUS_UNSUPPORTED, "W must be fp32 or bf16");
     } else {
@@ -310,8 +318,34 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         // an fp32 G; that is not bit-equal to an fp32 multiply, and callers that need the fp32-FMA kernel
         // do not hand the matrix to prepare.  The cost follows the dense area, so it needs density.
         const char *force = std::getenv("CB200_TRANSPOSE_SCHEDULE");
-        bool blocked = problem->device_matrix != nullptr &&
+        bool blocked = problem->device_matrix != nullptr && !problem->deterministic &&
                        qcsr_transpose_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits);
+        if (problem->deterministic) {
+            // same bits on every run: gather gene by gene from a gene-major copy, sums in a fixed order
+            const cb200_qcsr &dm = *problem->device_matrix;
+            if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
+                dm.bits != problem->bits || dm.policy != problem->policy) {
+                delete p;
+                return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
+            }
+            if (problem->persistent_limit_bytes != 0u &&
+                static_cast<std::uint64_t>(problem->nnz) * 5u + static_cast<std::uint64_t>(problem->k + 1) * 8u >
+                    problem->persistent_limit_bytes) {
+                delete p;
+                return fail(CB200_STATUS_UNSUPPORTED, "the gene-major copy of a deterministic transpose exceeds the persistent memory limit");
+            }
+            device_scope scope(problem->device);
+            cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
+                                                          : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
+            if (st == CB200_STATUS_SUCCESS) st = build_gene_major_layout(view_of(dm), &p->gene_major);
+            if (st != CB200_STATUS_SUCCESS) {
+                delete p;
+                return st;
+            }
+            p->schedule_name = "gene_gather";
+            p->workspace_bytes = qcsr_transpose_gather_workspace_bytes();
+            p->persistent_bytes += p->gene_major.bytes;
+        }
         if (force == nullptr)
             blocked = blocked && problem->m >= 16 * 256 && p->mean_row_nnz >= 0.004 * static_cast<double>(problem->k);
         else
@@ -471,10 +505,12 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
 
 void cb200_prepared_destroy(cb200_prepared *prepared) {
     if (prepared == nullptr) return;
-    if (prepared->row_order != nullptr || prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr) {
+    if (prepared->row_order != nullptr || prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr ||
+        prepared->gene_major.col_ptr != nullptr) {
         device_scope scope(prepared->problem.device);
         if (prepared->row_order != nullptr) cudaFree(prepared->row_order);
         free_blocked_layout(&prepared->blocked);
+        free_gene_major_layout(&prepared->gene_major);
     }
     delete prepared;
 }
@@ -566,6 +602,9 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
         return fail(CB200_STATUS_INVALID_SHAPE, "CSR matrix disagrees with the prepared problem");
     if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed_values == nullptr)))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "CSR matrix has null arrays");
+    if (pr.projection == CB200_PROJECTION_TRANSPOSE && prepared->gene_major.col_ptr != nullptr)
+        return launch_qcsr_transpose_gather(view_of(x), d, row_begin, row_end, prepared->gene_major, launch->workspace,
+                                            launch->workspace_bytes, prepared->sm_count, stream);
     if (pr.projection == CB200_PROJECTION_TRANSPOSE)
         return launch_qcsr_transpose(view_of(x), d, row_begin, row_end, &prepared->blocked, pr.multiply != CB200_DTYPE_BF16,
                                      launch->workspace, launch->workspace_bytes, prepared->sm_count, stream);

@@ -1,0 +1,466 @@
+// Gene-major copy (a CSC) of a quantized CSR matrix, built on the device, and the order-fixed
+// transpose  G' = alpha * deq(X)^T * G + beta * G'  that gathers from it.
+//
+// Reference counterpart of the build: the CSR -> CSC transpose kernels count_transpose_targets and
+// scatter_transpose (src/compute/matrix/convert/compressed.cu:146-178): count the entries of each
+// minor index with atomics, scan, then place every entry at atomicAdd(heads + minor, 1).  That leaves
+// the order of the cells inside a gene to the scheduler.  Here the placement is a stable counting
+// sort -- cells ascend inside every gene, the same arrays on every run -- in three steps:
+//   1. one CTA per block of 1,024 rows counts its entries per gene in shared memory and writes the
+//      counts row  counts[block][gene];
+//   2. per gene, the counts are scanned over the blocks (the offset of a block inside the gene's
+//      segment) and the totals over the genes (col_ptr);
+//   3. the CTA of a block walks its rows in order; the entries of one row go to different genes
+//      (column indices ascend strictly inside a row), so a row is placed in parallel and a barrier
+//      between rows keeps the cells of a gene in ascending order.
+// Codes are widened to one byte per entry in the copy (4-bit sources too): a gene's segment is
+// written by many CTAs at once and bytes need no read-modify-write.
+//
+// Reference counterpart of the transpose: csr_spmm_bwd_rhs_kernel_
+// (src/compute/sparse/ops/kernels/base_sparse/csr_spmm_bwd_rhs_kernel_.cuh:1-22), whose sums arrive
+// in atomic order.  The gather kernel below fixes the order, so the result is the same bits on every
+// run and the projection can serve a request that asks for determinism:
+//   a CTA of 8 warps owns a gene; the gene's entries (restricted to the row range) are cut into
+//   chunks of 256; warp w adds the chunks w, w + 8, ... entry after entry with one fp32 FMA per
+//   (entry, output column); the eight partial sums are added 0 + 1 + ... + 7; the result is
+//   alpha * sum, or fma(beta, old, alpha * sum) when beta != 0.
+#include "kernels.cuh"
+
+#include <algorithm>
+
+namespace cb200 {
+namespace {
+
+constexpr int kBlockRows = 1024;   // rows per CTA of the counting and the placing pass
+constexpr int kBuildThreads = 1024;
+constexpr int kGatherWarps = 8;
+constexpr int kGatherChunk = 256;
+
+struct gm_params {
+    const std::int64_t *row_ptr;
+    const std::int64_t *packed_row_ptr;
+    const std::int32_t *col_idx;
+    const std::uint8_t *packed;
+    std::int64_t rows, cols;
+    std::int64_t blocks;
+    std::uint32_t *counts; // [blocks][cols]
+    std::int64_t *col_ptr; // cols + 1
+    std::int32_t *row_idx;
+    std::uint8_t *codes;
+    int *status;
+};
+
+template<int BITS>
+__device__ __forceinline__ unsigned gm_load_code(const std::uint8_t *row_bytes, std::int64_t local) {
+    if constexpr (BITS == 8) {
+        return __ldg(row_bytes + local);
+    } else {
+        const unsigned byte = __ldg(row_bytes + (local >> 1));
+        return (local & 1) ? (byte >> 4) : (byte & 0xfu);
+    }
+}
+
+// step 1: counts[block][gene]
+__global__ void __launch_bounds__(kBuildThreads) gm_count_kernel(const gm_params p) {
+    extern __shared__ std::uint32_t gm_hist[];
+    const int cols = static_cast<int>(p.cols);
+    for (int c = threadIdx.x; c < cols; c += kBuildThreads) gm_hist[c] = 0u;
+    __syncthreads();
+    const std::int64_t r0 = static_cast<std::int64_t>(blockIdx.x) * kBlockRows;
+    const std::int64_t r1 = min(p.rows, r0 + kBlockRows);
+    const std::int64_t begin = __ldg(p.row_ptr + r0), end = __ldg(p.row_ptr + r1);
+    for (std::int64_t i = begin + threadIdx.x; i < end; i += kBuildThreads) {
+        const int c = __ldg(p.col_idx + i);
+        if (static_cast<unsigned>(c) < static_cast<unsigned>(cols)) atomicAdd(&gm_hist[c], 1u);
+        else atomicOr(p.status, 1); // a column outside the matrix: reported, entry left out
+    }
+    __syncthreads();
+    std::uint32_t *row = p.counts + static_cast<std::int64_t>(blockIdx.x) * cols;
+    for (int c = threadIdx.x; c < cols; c += kBuildThreads) row[c] = gm_hist[c];
+}
+
+// step 2a: per gene, exclusive scan of the counts over the blocks; the total goes to col_ptr[gene]
+__global__ void __launch_bounds__(256) gm_block_scan_kernel(const gm_params p) {
+    const std::int64_t c = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c >= p.cols) return;
+    std::uint32_t running = 0u;
+    std::uint32_t *cell = p.counts + c;
+    std::int64_t b = 0;
+    for (; b + 4 <= p.blocks; b += 4) {
+        const std::uint32_t t0 = cell[(b + 0) * p.cols], t1 = cell[(b + 1) * p.cols];
+        const std::uint32_t t2 = cell[(b + 2) * p.cols], t3 = cell[(b + 3) * p.cols];
+        cell[(b + 0) * p.cols] = running;
+        cell[(b + 1) * p.cols] = running + t0;
+        cell[(b + 2) * p.cols] = running + t0 + t1;
+        cell[(b + 3) * p.cols] = running + t0 + t1 + t2;
+        running += t0 + t1 + t2 + t3;
+    }
+    for (; b < p.blocks; ++b) {
+        const std::uint32_t t = cell[b * p.cols];
+        cell[b * p.cols] = running;
+        running += t;
+    }
+    p.col_ptr[c] = static_cast<std::int64_t>(running);
+}
+
+// step 2b: col_ptr = exclusive scan of the totals, in place (one CTA; a thread owns a run of genes)
+__global__ void __launch_bounds__(1024) gm_col_scan_kernel(std::int64_t *col_ptr, std::int64_t cols) {
+    __shared__ std::int64_t sums[1024];
+    const std::int64_t per = (cols + 1023) / 1024;
+    const std::int64_t c0 = min(cols, per * threadIdx.x), c1 = min(cols, c0 + per);
+    std::int64_t local = 0;
+    for (std::int64_t c = c0; c < c1; ++c) local += col_ptr[c];
+    sums[threadIdx.x] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        std::int64_t running = 0;
+        for (int t = 0; t < 1024; ++t) {
+            const std::int64_t s = sums[t];
+            sums[t] = running;
+            running += s;
+        }
+        col_ptr[cols] = running;
+    }
+    __syncthreads();
+    std::int64_t running = sums[threadIdx.x];
+    for (std::int64_t c = c0; c < c1; ++c) {
+        const std::int64_t t = col_ptr[c];
+        col_ptr[c] = running;
+        running += t;
+    }
+}
+
+// step 3: place the entries, rows of a block in order
+template<int BITS>
+__global__ void __launch_bounds__(kBuildThreads) gm_fill_kernel(const gm_params p) {
+    extern __shared__ std::uint32_t gm_head[]; // [cols] next free slot of this block inside each gene
+    const int cols = static_cast<int>(p.cols);
+    std::int64_t *row_start = reinterpret_cast<std::int64_t *>(gm_head + ((cols + 1) & ~1)); // [kBlockRows + 1]
+    const std::int64_t r0 = static_cast<std::int64_t>(blockIdx.x) * kBlockRows;
+    const int block_rows = static_cast<int>(min(p.rows, r0 + kBlockRows) - r0);
+    const std::uint32_t *mine = p.counts + static_cast<std::int64_t>(blockIdx.x) * cols;
+    for (int c = threadIdx.x; c < cols; c += kBuildThreads) gm_head[c] = mine[c];
+    for (int r = threadIdx.x; r <= block_rows; r += kBuildThreads) row_start[r] = __ldg(p.row_ptr + r0 + r);
+    __syncthreads();
+
+    // the first entry a thread places in the next row is fetched one row ahead
+    int next_col = -1;
+    unsigned next_code = 0u;
+    std::int64_t next_base = 0;
+    auto fetch = [&](int r) {
+        next_col = -1;
+        if (r >= block_rows) return;
+        const std::int64_t begin = row_start[r];
+        const std::int64_t i = begin + threadIdx.x;
+        if (i >= row_start[r + 1]) return;
+        const int c = __ldg(p.col_idx + i);
+        if (static_cast<unsigned>(c) >= static_cast<unsigned>(cols)) return;
+        const std::uint8_t *row_bytes = p.packed + (p.packed_row_ptr != nullptr ? __ldg(p.packed_row_ptr + r0 + r) : begin);
+        next_code = gm_load_code<BITS>(row_bytes, threadIdx.x);
+        next_base = __ldg(p.col_ptr + c);
+        next_col = c;
+    };
+    fetch(0);
+    for (int r = 0; r < block_rows; ++r) {
+        const int c0 = next_col;
+        const unsigned code0 = next_code;
+        const std::int64_t base0 = next_base;
+        fetch(r + 1);
+        const std::int32_t row = static_cast<std::int32_t>(r0 + r);
+        if (c0 >= 0) {
+            const std::int64_t pos = base0 + atomicAdd(&gm_head[c0], 1u);
+            p.row_idx[pos] = row;
+            p.codes[pos] = static_cast<std::uint8_t>(code0);
+        }
+        const std::int64_t begin = row_start[r], end = row_start[r + 1];
+        if (end - begin > kBuildThreads) { // the rest of a long row
+            const std::uint8_t *row_bytes = p.packed + (p.packed_row_ptr != nullptr ? __ldg(p.packed_row_ptr + r0 + r) : begin);
+            for (std::int64_t i = begin + kBuildThreads + threadIdx.x; i < end; i += kBuildThreads) {
+                const int c = __ldg(p.col_idx + i);
+                if (static_cast<unsigned>(c) >= static_cast<unsigned>(cols)) continue;
+                const std::int64_t pos = __ldg(p.col_ptr + c) + atomicAdd(&gm_head[c], 1u);
+                p.row_idx[pos] = row;
+                p.codes[pos] = static_cast<std::uint8_t>(gm_load_code<BITS>(row_bytes, i - begin));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+std::size_t fill_smem_bytes(std::int64_t cols) {
+    return static_cast<std::size_t>((cols + 1) & ~std::int64_t{1}) * 4u + static_cast<std::size_t>(kBlockRows + 1) * 8u;
+}
+
+} // namespace
+
+namespace {
+
+struct gather_params {
+    const std::int64_t *col_ptr;
+    const std::int32_t *row_idx;
+    const std::uint8_t *codes;
+    const float *scales;
+    const float *offsets;
+    const float *g;
+    float *out;
+    std::int64_t g_ld, out_ld, cols;
+    std::int64_t row_begin, row_end;
+    int policy;
+    int restrict_rows; // the launch covers a proper sub-range of the rows
+    int aligned;       // G rows can be read with one vector load per lane
+    float alpha, beta;
+    unsigned *queue;   // next gene to hand out
+};
+
+template<int VEC>
+__device__ __forceinline__ void gather_load(const float *src, bool aligned, float (&v)[VEC]) {
+    if constexpr (VEC == 1) {
+        v[0] = __ldg(src);
+    } else if constexpr (VEC == 2) {
+        if (aligned) {
+            const float2 t = __ldg(reinterpret_cast<const float2 *>(src));
+            v[0] = t.x; v[1] = t.y;
+        } else {
+            v[0] = __ldg(src); v[1] = __ldg(src + 1);
+        }
+    } else {
+        if (aligned) {
+            const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+            v[0] = __ldg(src); v[1] = __ldg(src + 1); v[2] = __ldg(src + 2); v[3] = __ldg(src + 3);
+        }
+    }
+}
+
+// first position in [lo, hi) whose row is >= bound
+__device__ __forceinline__ std::int64_t gather_lower_bound(const std::int32_t *row_idx, std::int64_t lo, std::int64_t hi,
+                                                           std::int64_t bound) {
+    while (lo < hi) {
+        const std::int64_t mid = lo + ((hi - lo) >> 1);
+        if (static_cast<std::int64_t>(__ldg(row_idx + mid)) < bound) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+// N == 32 * VEC; lane l owns the output columns [l * VEC, l * VEC + VEC).
+template<int VEC>
+__global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kernel(const gather_params p) {
+    __shared__ float part[kGatherWarps][32 * VEC];
+    __shared__ unsigned next_gene;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool row_policy = p.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+    const bool aligned = p.aligned != 0;
+    for (;;) {
+        if (threadIdx.x == 0) next_gene = atomicAdd(p.queue, 1u);
+        __syncthreads();
+        const std::int64_t gene = next_gene;
+        if (gene >= p.cols) return;
+        std::int64_t lo = __ldg(p.col_ptr + gene), hi = __ldg(p.col_ptr + gene + 1);
+        if (p.restrict_rows) {
+            lo = gather_lower_bound(p.row_idx, lo, hi, p.row_begin);
+            hi = gather_lower_bound(p.row_idx, lo, hi, p.row_end);
+        }
+        const float scale = p.scales != nullptr ? __ldg(p.scales + gene) : 1.0f;
+        const float gene_offset = (!row_policy && p.offsets != nullptr) ? __ldg(p.offsets + gene) : 0.0f;
+        float acc[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
+        const float *g_lane = p.g + lane * VEC;
+        for (std::int64_t chunk = lo + static_cast<std::int64_t>(warp) * kGatherChunk; chunk < hi;
+             chunk += static_cast<std::int64_t>(kGatherWarps) * kGatherChunk) {
+            const std::int64_t chunk_end = min(hi, chunk + kGatherChunk);
+            for (std::int64_t base = chunk; base < chunk_end; base += 32) {
+                const int count = static_cast<int>(min(static_cast<std::int64_t>(32), chunk_end - base));
+                int row = 0;
+                float value = 0.0f;
+                if (lane < count) {
+                    row = __ldg(p.row_idx + base + lane);
+                    const float code = static_cast<float>(__ldg(p.codes + base + lane));
+                    const float offset = row_policy ? (p.offsets != nullptr ? __ldg(p.offsets + row) : 0.0f) : gene_offset;
+                    value = fmaf(code, scale, offset);
+                }
+                if (count == 32) {
+#pragma unroll
+                    for (int j0 = 0; j0 < 32; j0 += 8) { // eight rows of G in flight, then their FMAs in order
+                        float gv[8][VEC], vv[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int r = __shfl_sync(0xffffffffu, row, j0 + u);
+                            vv[u] = __shfl_sync(0xffffffffu, value, j0 + u);
+                            gather_load<VEC>(g_lane + static_cast<std::int64_t>(r) * p.g_ld, aligned, gv[u]);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+#pragma unroll
+                            for (int k = 0; k < VEC; ++k) acc[k] = fmaf(vv[u], gv[u][k], acc[k]);
+                    }
+                } else {
+                    for (int j = 0; j < count; ++j) {
+                        const int r = __shfl_sync(0xffffffffu, row, j);
+                        const float v = __shfl_sync(0xffffffffu, value, j);
+                        float gv[VEC];
+                        gather_load<VEC>(g_lane + static_cast<std::int64_t>(r) * p.g_ld, aligned, gv);
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) acc[k] = fmaf(v, gv[k], acc[k]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) part[warp][lane * VEC + k] = acc[k];
+        __syncthreads();
+        if (threadIdx.x < 32 * VEC) {
+            float sum = part[0][threadIdx.x];
+#pragma unroll
+            for (int w = 1; w < kGatherWarps; ++w) sum = sum + part[w][threadIdx.x];
+            float *dst = p.out + gene * p.out_ld + threadIdx.x;
+            float result = p.alpha * sum;
+            if (p.beta != 0.0f) result = fmaf(p.beta, *dst, result);
+            *dst = result;
+        }
+    }
+}
+
+} // namespace
+
+bool qcsr_gene_major_shape_ok(std::int64_t rows, std::int64_t cols, int bits) {
+    return rows >= 0 && rows < (std::int64_t{1} << 31) && cols >= 1 && fill_smem_bytes(cols) <= 227u * 1024u &&
+           (bits == 8 || bits == 4);
+}
+
+std::uint64_t qcsr_gene_major_workspace_bytes(std::int64_t rows, std::int64_t cols) {
+    const std::uint64_t blocks = static_cast<std::uint64_t>((rows + kBlockRows - 1) / kBlockRows);
+    return 256u + blocks * static_cast<std::uint64_t>(cols) * 4u;
+}
+
+cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, std::int32_t *row_idx, std::uint8_t *codes,
+                                    void *workspace, std::uint64_t workspace_bytes, cudaStream_t stream) {
+    if (!qcsr_gene_major_shape_ok(x.rows, x.cols, x.bits))
+        return fail(CB200_STATUS_UNSUPPORTED, "gene-major copy: up to 2^31 - 1 rows, %lld genes (a counter per gene in shared memory), 8- or 4-bit codes",
+                    static_cast<long long>((227 * 1024 - (kBlockRows + 1) * 8) / 4));
+    if (x.bits == 4 && x.packed_row_ptr == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "4-bit codes need packed_row_ptr");
+    if (col_ptr == nullptr || (x.nnz > 0 && (row_idx == nullptr || codes == nullptr)) || x.row_ptr == nullptr)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "null array");
+    if (workspace == nullptr || workspace_bytes < qcsr_gene_major_workspace_bytes(x.rows, x.cols))
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "gene-major copy needs %llu workspace bytes",
+                    static_cast<unsigned long long>(qcsr_gene_major_workspace_bytes(x.rows, x.cols)));
+    gm_params p{};
+    p.row_ptr = x.row_ptr; p.packed_row_ptr = x.packed_row_ptr; p.col_idx = x.col_idx; p.packed = x.packed;
+    p.rows = x.rows; p.cols = x.cols; p.blocks = (x.rows + kBlockRows - 1) / kBlockRows;
+    p.status = static_cast<int *>(workspace);
+    p.counts = reinterpret_cast<std::uint32_t *>(static_cast<unsigned char *>(workspace) + 256);
+    p.col_ptr = col_ptr; p.row_idx = row_idx; p.codes = codes;
+    CB200_CUDA_OK(cudaMemsetAsync(workspace, 0, 256, stream));
+    if (p.blocks == 0) {
+        CB200_CUDA_OK(cudaMemsetAsync(col_ptr, 0, static_cast<std::size_t>(x.cols + 1) * 8u, stream));
+        return CB200_STATUS_SUCCESS;
+    }
+    const std::size_t count_smem = static_cast<std::size_t>(x.cols) * 4u, fill_smem = fill_smem_bytes(x.cols);
+    CB200_CUDA_OK(cudaFuncSetAttribute(gm_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(count_smem)));
+    gm_count_kernel<<<static_cast<unsigned>(p.blocks), kBuildThreads, count_smem, stream>>>(p);
+    gm_block_scan_kernel<<<static_cast<unsigned>((x.cols + 255) / 256), 256, 0, stream>>>(p);
+    gm_col_scan_kernel<<<1, 1024, 0, stream>>>(col_ptr, x.cols);
+    if (x.bits == 8) {
+        CB200_CUDA_OK(cudaFuncSetAttribute(gm_fill_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fill_smem)));
+        gm_fill_kernel<8><<<static_cast<unsigned>(p.blocks), kBuildThreads, fill_smem, stream>>>(p);
+    } else {
+        CB200_CUDA_OK(cudaFuncSetAttribute(gm_fill_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fill_smem)));
+        gm_fill_kernel<4><<<static_cast<unsigned>(p.blocks), kBuildThreads, fill_smem, stream>>>(p);
+    }
+    count_launch(4);
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status build_gene_major_layout(const qcsr_view &x, gene_major_layout *out) {
+    *out = gene_major_layout{};
+    if (!qcsr_gene_major_shape_ok(x.rows, x.cols, x.bits)) return fail(CB200_STATUS_UNSUPPORTED, "shape outside the gene-major copy");
+    const std::uint64_t ws_bytes = qcsr_gene_major_workspace_bytes(x.rows, x.cols);
+    void *ws = nullptr;
+    const std::size_t ptr_bytes = static_cast<std::size_t>(x.cols + 1) * 8u;
+    const std::size_t idx_bytes = static_cast<std::size_t>(std::max<std::int64_t>(x.nnz, 1)) * 4u;
+    const std::size_t code_bytes = static_cast<std::size_t>(std::max<std::int64_t>(x.nnz, 1));
+    cudaError_t err = cudaMalloc(&ws, ws_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->col_ptr), ptr_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->row_idx), idx_bytes);
+    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->codes), code_bytes);
+    cb200_status st = err == cudaSuccess ? CB200_STATUS_SUCCESS : fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err));
+    int status = 0;
+    if (st == CB200_STATUS_SUCCESS) st = launch_qcsr_gene_major(x, out->col_ptr, out->row_idx, out->codes, ws, ws_bytes, nullptr);
+    if (st == CB200_STATUS_SUCCESS) {
+        err = cudaMemcpy(&status, ws, sizeof(int), cudaMemcpyDeviceToHost); // synchronises
+        if (err != cudaSuccess) st = fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err));
+        else if (status != 0) st = fail(CB200_STATUS_INVALID_SHAPE, "a column index lies outside the matrix");
+    }
+    if (ws != nullptr) cudaFree(ws);
+    if (st != CB200_STATUS_SUCCESS) {
+        free_gene_major_layout(out);
+        return st;
+    }
+    out->bytes = ptr_bytes + idx_bytes + code_bytes;
+    out->src_row_ptr = x.row_ptr; out->src_col_idx = x.col_idx; out->src_packed = x.packed;
+    return CB200_STATUS_SUCCESS;
+}
+
+void free_gene_major_layout(gene_major_layout *layout) {
+    if (layout->col_ptr != nullptr) cudaFree(layout->col_ptr);
+    if (layout->row_idx != nullptr) cudaFree(layout->row_idx);
+    if (layout->codes != nullptr) cudaFree(layout->codes);
+    *layout = gene_major_layout{};
+}
+
+bool qcsr_transpose_gather_shape_ok(std::int64_t n) { return n == 32 || n == 64 || n == 128; }
+std::uint64_t qcsr_transpose_gather_workspace_bytes() { return 256u; }
+
+cb200_status launch_qcsr_transpose_gather(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                          std::int64_t row_end, const gene_major_layout &layout, void *workspace,
+                                          std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream) {
+    if (d.n == 0 || x.cols == 0) return CB200_STATUS_SUCCESS;
+    if (d.dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes an fp32 dense operand");
+    if (!qcsr_transpose_gather_shape_ok(d.n)) return fail(CB200_STATUS_UNSUPPORTED, "the order-fixed transpose covers N in {32, 64, 128}");
+    if (layout.col_ptr == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "no gene-major copy");
+    if (layout.src_row_ptr != x.row_ptr || layout.src_col_idx != x.col_idx || layout.src_packed != x.packed)
+        return fail(CB200_STATUS_STALE_STRUCTURE, "the gene-major copy was built from other arrays");
+    if (workspace == nullptr || workspace_bytes < qcsr_transpose_gather_workspace_bytes())
+        return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "the order-fixed transpose needs 256 workspace bytes");
+    gather_params p{};
+    p.col_ptr = layout.col_ptr; p.row_idx = layout.row_idx; p.codes = layout.codes;
+    p.scales = x.scales; p.offsets = x.offsets; p.g = static_cast<const float *>(d.dense); p.out = d.out;
+    p.g_ld = d.dense_ld; p.out_ld = d.out_ld; p.cols = x.cols;
+    p.row_begin = row_begin; p.row_end = std::max(row_begin, row_end);
+    p.policy = x.policy; p.restrict_rows = (row_begin > 0 || row_end < x.rows) ? 1 : 0;
+    const int vec = static_cast<int>(d.n / 32);
+    p.aligned = (reinterpret_cast<std::uintptr_t>(d.dense) % (4u * vec) == 0u) && ((d.dense_ld * 4) % (4 * vec) == 0) ? 1 : 0;
+    p.alpha = d.alpha; p.beta = d.beta;
+    p.queue = static_cast<unsigned *>(workspace);
+    CB200_CUDA_OK(cudaMemsetAsync(workspace, 0, 4, stream));
+    const unsigned grid = static_cast<unsigned>(std::min<std::int64_t>(x.cols, static_cast<std::int64_t>(sm_count) * 8));
+    if (vec == 1) qcsr_transpose_gather_kernel<1><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    else if (vec == 2) qcsr_transpose_gather_kernel<2><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    else qcsr_transpose_gather_kernel<4><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    count_launch();
+    CB200_CUDA_OK(cudaGetLastError());
+    return CB200_STATUS_SUCCESS;
+}
+
+} // namespace cb200
+
+extern "C" uint64_t cb200_qcsr_gene_major_workspace(int64_t rows, int64_t cols) {
+    if (!cb200::qcsr_gene_major_shape_ok(rows, cols, 8)) return 0;
+    return cb200::qcsr_gene_major_workspace_bytes(rows, cols);
+}
+
+extern "C" cb200_status cb200_qcsr_gene_major(const cb200_qcsr *x, int64_t *col_ptr, int32_t *row_idx, uint8_t *codes,
+                                              void *workspace, uint64_t workspace_bytes, int32_t device, void *stream) {
+    using namespace cb200;
+    clear_error();
+    if (x == nullptr || x->version != CB200_ABI_VERSION || x->size < sizeof(cb200_qcsr))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    const qcsr_view view{x->rows, x->cols, x->nnz, x->bits, x->policy, x->row_ptr, x->packed_row_ptr,
+                         x->col_idx, x->packed_values, x->scales, x->offsets};
+    return launch_qcsr_gene_major(view, col_ptr, row_idx, codes, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}

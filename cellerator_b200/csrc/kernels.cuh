@@ -117,6 +117,32 @@ cb200_status launch_qcsr_transpose(const qcsr_view &x, const dense_args &d, std:
                                    void *workspace, std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream);
 std::uint64_t qcsr_transpose_workspace_bytes(std::int64_t cols, std::int64_t n, int sm_count);
 
+// Gene-major copy (a CSC) of a matrix: cells ascend inside every gene; one code per byte (4-bit
+// sources are widened).  Built once at prepare time for the order-fixed transpose below.
+struct gene_major_layout {
+    std::int64_t *col_ptr = nullptr;  // cols + 1
+    std::int32_t *row_idx = nullptr;  // nnz
+    std::uint8_t *codes = nullptr;    // nnz
+    std::uint64_t bytes = 0;
+    const void *src_row_ptr = nullptr, *src_col_idx = nullptr, *src_packed = nullptr; // arrays it was built from
+};
+bool qcsr_gene_major_shape_ok(std::int64_t rows, std::int64_t cols, int bits);
+std::uint64_t qcsr_gene_major_workspace_bytes(std::int64_t rows, std::int64_t cols);
+// Enqueues the stable counting sort into caller arrays; the first word of `workspace` ends up
+// non-zero when a column index lies outside the matrix.
+cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, std::int32_t *row_idx, std::uint8_t *codes,
+                                    void *workspace, std::uint64_t workspace_bytes, cudaStream_t stream);
+// current device; allocates and synchronises
+cb200_status build_gene_major_layout(const qcsr_view &x, gene_major_layout *out);
+void free_gene_major_layout(gene_major_layout *layout);
+// Transpose with a fixed order of the fp32 sums (same bits on every run), N in {32, 64, 128}:
+// gathers rows of G gene by gene from the gene-major copy.
+bool qcsr_transpose_gather_shape_ok(std::int64_t n);
+std::uint64_t qcsr_transpose_gather_workspace_bytes();
+cb200_status launch_qcsr_transpose_gather(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                          std::int64_t row_end, const gene_major_layout &layout, void *workspace,
+                                          std::uint64_t workspace_bytes, int sm_count, cudaStream_t stream);
+
 struct qbell_view {
     std::int64_t rows, cols;
     int block_size, ell_cols;

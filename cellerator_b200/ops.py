@@ -310,15 +310,17 @@ def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = No
 
 
 def spmm_transpose(x: QuantizedCsr, g: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
-                   row_begin=0, row_end=0, multiply: int = 0):
+                   row_begin=0, row_end=0, multiply: int = 0, deterministic=False):
     """G' = alpha * deq(X)^T G + beta * G'.
 
-    multiply=capi.DTYPE_BF16 asks for tensor-core products (decoded values and G rounded to bf16)."""
+    multiply=capi.DTYPE_BF16 asks for tensor-core products (decoded values and G rounded to bf16);
+    deterministic=True for the gather schedule whose fp32 sums have a fixed order."""
     n = g.shape[1]
     if out is None:
         out = torch.empty(x.cols, n, dtype=torch.float32, device=x.device)
     op = PreparedSpmm(capi.PROJECTION_TRANSPOSE, x.rows, x.cols, n, x.nnz, x.bits, x.policy, g.dtype, x.device,
-                      multiply=multiply, device_matrix=x if multiply == capi.DTYPE_BF16 else None)
+                      multiply=multiply, device_matrix=x if (multiply == capi.DTYPE_BF16 or deterministic) else None,
+                      deterministic=deterministic)
     op.run(x, g, out, alpha=alpha, beta=beta, row_begin=row_begin, row_end=row_end)
     op.close()
     return out
@@ -417,6 +419,25 @@ def build_execution_csr(row_offsets, block_ids, local_ids, canonical_ids, featur
     e.device = device.index if device.index is not None else torch.cuda.current_device()
     capi.check(capi.lib().cb200_build_execution_csr(C.byref(e), C.c_void_p(_stream_handle(device))))
     return int(status.item()), out
+
+
+def qcsr_gene_major(x: "QuantizedCsr"):
+    """Gene-major copy (a CSC) of a device matrix (cb200_qcsr_gene_major): -> (col_ptr int64 [cols + 1],
+    row_idx int32 [nnz], codes uint8 [nnz]), the cells ascending inside every gene, one code per byte."""
+    lib = capi.lib()
+    need = int(lib.cb200_qcsr_gene_major_workspace(x.rows, x.cols))
+    device = x.device
+    work = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+    col_ptr = torch.empty(x.cols + 1, dtype=torch.int64, device=device)
+    row_idx = torch.empty(max(x.nnz, 1), dtype=torch.int32, device=device)
+    codes = torch.empty(max(x.nnz, 1), dtype=torch.uint8, device=device)
+    desc = x.desc()
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    capi.check(lib.cb200_qcsr_gene_major(C.byref(desc), col_ptr.data_ptr(), row_idx.data_ptr(), codes.data_ptr(),
+                                         work.data_ptr(), work.numel(), index, _stream_handle(device)))
+    if int(work[:4].view(torch.int32).item()) != 0:
+        raise ValueError("a column index lies outside the matrix")
+    return col_ptr, row_idx[:x.nnz], codes[:x.nnz]
 
 
 def pack_dense_operand(source: torch.Tensor, fperm: torch.Tensor, col_major=False, fb_offsets=None,

@@ -522,6 +522,28 @@ typedef struct cb200_execution_csr {
 
 cb200_status cb200_build_execution_csr(const cb200_execution_csr *view, void *stream);
 
+/* Gene-major copy (a CSC) of a quantized CSR matrix, built on the device: the CSR -> CSC transpose of
+ * the reference (count_transpose_targets + scatter_transpose,
+ * src/compute/matrix/convert/compressed.cu:146-178, reached through the compressed-matrix converters),
+ * for the quantized format.  The reference places entries at atomicAdd(heads + minor, 1), which leaves
+ * the order inside a gene to the scheduler; this build is a stable counting sort: inside every gene
+ * the cells ascend, and every run produces the same arrays.
+ *   col_ptr  device, cols + 1: first entry of each gene
+ *   row_idx  device, nnz: the cell of each entry
+ *   codes    device, nnz: one code per byte (4-bit sources are widened, the value is unchanged)
+ * Scales and offsets are shared with the source.  Limits: rows < 2^31; cols <= 56,062 (a 32-bit
+ * counter per gene in shared memory) -- outside them CB200_STATUS_UNSUPPORTED.  Enqueues on `stream`,
+ * allocates nothing; `workspace` (device) needs cb200_qcsr_gene_major_workspace(rows, cols) bytes
+ * (0 = shape outside the limits), and its first 32-bit word is 0 afterwards unless a column index lay
+ * outside the matrix (bit 0).
+ * cb200_spmm_prepare builds this copy itself for a transpose problem with deterministic = 1 and the
+ * device matrix at hand (schedule "gene_gather"): the sums then have a fixed order -- per gene, eight
+ * interleaved runs of 256-entry chunks added entry by entry with fp32 FMAs, the eight partial sums
+ * added in order -- and the output is the same bits on every run. */
+uint64_t cb200_qcsr_gene_major_workspace(int64_t rows, int64_t cols);
+cb200_status cb200_qcsr_gene_major(const cb200_qcsr *x, int64_t *col_ptr, int32_t *row_idx, uint8_t *codes,
+                                   void *workspace, uint64_t workspace_bytes, int32_t device, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Routing of the reference's public projection calls: cellerator_sparse_projection_forward /
  * _backward (include/Cellerator/abi.h:111-124, src/abi/abi.cu:278-396) for the quantized layouts,

@@ -241,6 +241,38 @@ class Oracle(_Base):
         self._fn("digest_f32", None)(_p(v, C.c_float), C.c_uint64(v.shape[0]), C.c_uint64(v.shape[1]),
                                      C.c_uint64(v.shape[1]), C.c_uint32(4), _p(out, C.c_uint64))
 
+    # ---- gene-major copy and the order-fixed transpose (restatement only: the reference's CSC
+    # transposer is device code, and its transpose kernel adds in atomic order) ----------------
+    def qcsr_gene_major(self, bits, cols, row_ptr, packed_row_ptr, col_idx, packed):
+        """-> (status, col_ptr, row_idx, codes): stable CSR -> CSC of the codes (see oracle.c)."""
+        row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        rows, nnz = len(row_ptr) - 1, int(row_ptr[-1])
+        col_ptr = np.zeros(cols + 1, dtype=np.int64)
+        row_idx = np.zeros(max(nnz, 1), dtype=np.int32)
+        codes = np.zeros(max(nnz, 1), dtype=np.uint8)
+        rc = self._fn("qcsr_gene_major")(
+            C.c_int(bits), C.c_int64(rows), C.c_int64(cols), _p(row_ptr, C.c_int64), _p(prp, C.c_int64),
+            _p(col_idx, C.c_int32), _p(packed, C.c_uint8), _p(col_ptr, C.c_int64), _p(row_idx, C.c_int32), _p(codes, C.c_uint8))
+        return rc, col_ptr, row_idx[:nnz], codes[:nnz]
+
+    def qcsr_transpose_ordered(self, policy, col_ptr, row_idx, codes, scales, offsets, g, row_begin, row_end,
+                               alpha=1.0, beta=0.0, out=None):
+        """fp32 result of the deterministic transpose schedule, bit for bit (see oracle.c)."""
+        col_ptr = _i64(col_ptr)
+        row_idx = np.ascontiguousarray(row_idx, dtype=np.int32)
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        scales, offsets, g = _f32(scales), _f32(offsets), _f32(g)
+        cols, n = len(col_ptr) - 1, g.shape[1]
+        out = np.zeros((cols, n), dtype=np.float32) if out is None else np.ascontiguousarray(out, dtype=np.float32).copy()
+        rc = self._fn("qcsr_transpose_ordered")(
+            C.c_int(policy), C.c_int64(cols), C.c_int64(n), _p(col_ptr, C.c_int64), _p(row_idx, C.c_int32),
+            _p(codes, C.c_uint8), _p(scales, C.c_float), _p(offsets, C.c_float), _p(g, C.c_float), C.c_int64(g.shape[1]),
+            C.c_int64(row_begin), C.c_int64(row_end), C.c_float(alpha), C.c_float(beta), _p(out, C.c_float), C.c_int64(n))
+        assert rc == 0, rc
+        return out
+
     def pack_csr(self, bits, policy, row_ptr, packed_row_ptr, col_idx, scales, offsets, values,
                  row_begin=0, row_end=None, value_base=0, total_bytes=None):
         row_ptr, prp = _i64(row_ptr), _i64(packed_row_ptr)

@@ -792,3 +792,74 @@ ORC_API int orc_build_execution_csr(uint32_t rows, uint32_t nnz, uint32_t featur
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* gene-major copy (CSC) and the order-fixed transpose                       */
+
+/* CSR -> CSC of the codes as a stable counting sort: what count_transpose_targets +
+ * scatter_transpose (src/compute/matrix/convert/compressed.cu:146-178) produce, with the one
+ * freedom those kernels leave -- the order of the cells inside a gene, decided there by the order in
+ * which atomicAdd(heads + minor, 1) happens to be served -- fixed to ascending cells.  Codes come out
+ * one per byte.  Returns 0, or 1 when a column index lies outside the matrix. */
+ORC_API int orc_qcsr_gene_major(int bits, int64_t rows, int64_t cols, const int64_t *row_ptr,
+                                const int64_t *packed_row_ptr, const int32_t *col_idx, const uint8_t *packed,
+                                int64_t *col_ptr, int32_t *row_idx, uint8_t *codes) {
+    for (int64_t c = 0; c <= cols; ++c) col_ptr[c] = 0;
+    for (int64_t i = row_ptr[0]; i < row_ptr[rows]; ++i) {
+        if (col_idx[i] < 0 || col_idx[i] >= cols) return 1;
+        col_ptr[col_idx[i] + 1] += 1; /* count_transpose_targets: ptr[minor + 1] += 1 */
+    }
+    for (int64_t c = 0; c < cols; ++c) col_ptr[c + 1] += col_ptr[c];
+    int64_t *heads = (int64_t *)malloc((size_t)(cols > 0 ? cols : 1) * sizeof(int64_t));
+    if (heads == NULL) return 2;
+    for (int64_t c = 0; c < cols; ++c) heads[c] = col_ptr[c];
+    for (int64_t r = 0; r < rows; ++r) {
+        const uint8_t *row_bytes = packed + (packed_row_ptr != NULL ? packed_row_ptr[r] : row_ptr[r]);
+        for (int64_t i = row_ptr[r]; i < row_ptr[r + 1]; ++i) {
+            const int64_t dst = heads[col_idx[i]]++; /* scatter_transpose, rows taken in order */
+            row_idx[dst] = (int32_t)r;
+            codes[dst] = (uint8_t)orc_unpack_code(bits, row_bytes, i - row_ptr[r]);
+        }
+    }
+    free(heads);
+    return 0;
+}
+
+/* G' = alpha * deq(X)^T G + beta * G' from the gene-major copy, in the order the deterministic
+ * device schedule defines (the reference's csr_spmm_bwd_rhs_kernel_ adds in atomic order and defines
+ * none): the entries of a gene inside [row_begin, row_end) are cut into chunks of 256; run w of
+ * eight takes the chunks w, w + 8, ... and adds them entry by entry with one fused multiply-add per
+ * output column, the value decoded with a fused multiply-add as on the device; the eight partial sums
+ * are added 0 + 1 + ... + 7; the output is alpha * sum, or fma(beta, old, alpha * sum). */
+ORC_API int orc_qcsr_transpose_ordered(int policy, int64_t cols, int64_t n, const int64_t *col_ptr,
+                                       const int32_t *row_idx, const uint8_t *codes, const float *scales,
+                                       const float *offsets, const float *g, int64_t g_ld, int64_t row_begin,
+                                       int64_t row_end, float alpha, float beta, float *out, int64_t out_ld) {
+    float *part = (float *)malloc((size_t)(8 * (n > 0 ? n : 1)) * sizeof(float));
+    if (part == NULL) return 2;
+    for (int64_t c = 0; c < cols; ++c) {
+        int64_t lo = col_ptr[c], hi = col_ptr[c + 1];
+        while (lo < hi && row_idx[lo] < row_begin) ++lo;
+        int64_t end = lo;
+        while (end < hi && row_idx[end] < row_end) ++end;
+        hi = end;
+        for (int64_t i = 0; i < 8 * n; ++i) part[i] = 0.0f;
+        const float scale = orc_scale_for(scales, c);
+        for (int64_t e = lo; e < hi; ++e) {
+            const int64_t run = ((e - lo) / 256) % 8;
+            const int64_t r = row_idx[e];
+            const float offset = policy == 2 ? (offsets != NULL ? offsets[r] : 0.0f) : (offsets != NULL ? offsets[c] : 0.0f);
+            const float value = fmaf((float)codes[e], scale, offset);
+            for (int64_t j = 0; j < n; ++j) part[run * n + j] = fmaf(value, g[r * g_ld + j], part[run * n + j]);
+        }
+        for (int64_t j = 0; j < n; ++j) {
+            float sum = part[j];
+            for (int w = 1; w < 8; ++w) sum = sum + part[w * n + j];
+            float result = alpha * sum;
+            if (beta != 0.0f) result = fmaf(beta, out[c * out_ld + j], result);
+            out[c * out_ld + j] = result;
+        }
+    }
+    free(part);
+    return 0;
+}
