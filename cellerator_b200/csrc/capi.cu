@@ -553,7 +553,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
                     (unsigned long long)prepared->workspace_bytes, (unsigned long long)launch->workspace_bytes);
     /* lifetimes.hh:160-172: the expected generation of a bound value plane must be the live one; here the
      * "live" values of a prepared copy are those it was built from */
-    if ((prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr) && pr.value_generation != 0u &&
+    if ((prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr || prepared->gene_major.col_ptr != nullptr) &&
+        pr.value_generation != 0u &&
         launch->value_generation != 0u && launch->value_generation != pr.value_generation)
         return fail(CB200_STATUS_STALE_VALUE, "the prepared operation keeps a copy of value generation %llu, the launch binds %llu",
                     (unsigned long long)pr.value_generation, (unsigned long long)launch->value_generation);

@@ -195,7 +195,7 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
     }
 }
 
-core::operation_status prepare_any(int projection_kind, bool composed, const core::operation_candidate &candidate,
+core::operation_status prepare_any(int projection_kind, bool composed, bool ordered, const core::operation_candidate &candidate,
                                    const core::operation_problem &problem, const core::structure_set_key &structures,
                                    const core::projection_key &projection, const core::numeric_policy &numeric,
                                    const core::prepare_policy &policy, core::prepared_operation *out) noexcept {
@@ -233,7 +233,12 @@ core::operation_status prepare_any(int projection_kind, bool composed, const cor
     p.structure_epoch = structures.structures[0].epoch.value;
     // the optional length-sorted row order is persistent preprocessing: only when the policy allows it
     p.host_row_ptr = policy.allow_persistent_preprocessing ? shape->host_row_ptr : nullptr;
-    p.deterministic = policy.deterministic ? 1 : 0;
+    // the ordered transpose always asks for the fixed order; it gathers from a gene-major copy that
+    // prepare builds from the device matrix of the catalog entry
+    if (ordered && shape->device_matrix == nullptr)
+        return status(core::operation_status_code::unsupported_problem,
+                      "the ordered transpose needs the device matrix in the projection's catalog entry");
+    p.deterministic = (policy.deterministic || ordered) ? 1 : 0;
     // bf16 products (tensor-core schedules) only when the request's numeric policy says so
     p.multiply = dtype_of(numeric.multiply);
     p.device_matrix = policy.allow_persistent_preprocessing ? shape->device_matrix : nullptr;
@@ -324,31 +329,37 @@ core::operation_status prepare_csr(const core::operation_candidate &c, const cor
                                    const core::structure_set_key &s, const core::projection_key &pj,
                                    const core::numeric_policy &n, const core::prepare_policy &po,
                                    core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_CSR, false, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_CSR, false, false, c, pr, s, pj, n, po, out);
 }
 core::operation_status prepare_csr_epilogue(const core::operation_candidate &c, const core::operation_problem &pr,
                                             const core::structure_set_key &s, const core::projection_key &pj,
                                             const core::numeric_policy &n, const core::prepare_policy &po,
                                             core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_CSR, true, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_CSR, true, false, c, pr, s, pj, n, po, out);
 }
 core::operation_status prepare_bell_epilogue(const core::operation_candidate &c, const core::operation_problem &pr,
                                              const core::structure_set_key &s, const core::projection_key &pj,
                                              const core::numeric_policy &n, const core::prepare_policy &po,
                                              core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, true, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, true, false, c, pr, s, pj, n, po, out);
 }
 core::operation_status prepare_transpose(const core::operation_candidate &c, const core::operation_problem &pr,
                                          const core::structure_set_key &s, const core::projection_key &pj,
                                          const core::numeric_policy &n, const core::prepare_policy &po,
                                          core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_TRANSPOSE, false, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_TRANSPOSE, false, false, c, pr, s, pj, n, po, out);
+}
+core::operation_status prepare_transpose_ordered(const core::operation_candidate &c, const core::operation_problem &pr,
+                                                 const core::structure_set_key &s, const core::projection_key &pj,
+                                                 const core::numeric_policy &n, const core::prepare_policy &po,
+                                                 core::prepared_operation *out) noexcept {
+    return prepare_any(CB200_PROJECTION_TRANSPOSE, false, true, c, pr, s, pj, n, po, out);
 }
 core::operation_status prepare_bell(const core::operation_candidate &c, const core::operation_problem &pr,
                                     const core::structure_set_key &s, const core::projection_key &pj,
                                     const core::numeric_policy &n, const core::prepare_policy &po,
                                     core::prepared_operation *out) noexcept {
-    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, false, c, pr, s, pj, n, po, out);
+    return prepare_any(CB200_PROJECTION_BLOCKED_ELL, false, false, c, pr, s, pj, n, po, out);
 }
 
 core::operation_candidate make_candidate(std::uint64_t id, const char *name, core::projection_kind projection,
@@ -396,6 +407,14 @@ core::operation_candidate quantized_csr_transpose_candidate() noexcept {
                           core::candidate_graph_capture, &supports_transpose, &prepare_transpose, 0u);
 }
 
+core::operation_candidate quantized_csr_transpose_ordered_candidate() noexcept {
+    // gathers gene by gene from a gene-major copy built at prepare time; the fp32 sums have a fixed
+    // order, so repeated runs are bitwise identical.  The copy is persistent preprocessing.
+    return make_candidate(0xcb200c5a00000006ull, "cb200.qcsr.transpose.ordered.sm100a", core::projection_kind::transpose_or_backward,
+                          core::candidate_deterministic | core::candidate_graph_capture | core::candidate_persistent_preprocessing,
+                          &supports_transpose, &prepare_transpose_ordered, 256u);
+}
+
 core::operation_candidate quantized_blocked_ell_candidate() noexcept {
     return make_candidate(0xcb200c5a00000003ull, "cb200.qbell.forward.sm100a", core::projection_kind::blocked_ell,
                           core::candidate_deterministic | core::candidate_graph_capture, &supports_bell, &prepare_bell, 0u);
@@ -416,7 +435,8 @@ core::operation_candidate quantized_blocked_ell_epilogue_candidate() noexcept {
 core::operation_status register_all(core::candidate_registry *registry) noexcept {
     const core::operation_candidate all[] = {quantized_csr_forward_candidate(), quantized_csr_transpose_candidate(),
                                              quantized_blocked_ell_candidate(), quantized_csr_forward_epilogue_candidate(),
-                                             quantized_blocked_ell_epilogue_candidate()};
+                                             quantized_blocked_ell_epilogue_candidate(),
+                                             quantized_csr_transpose_ordered_candidate()};
     for (const core::operation_candidate &c : all) {
         const core::operation_status s = core::register_candidate(registry, c);
         if (!s) return s;

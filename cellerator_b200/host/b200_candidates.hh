@@ -88,7 +88,13 @@ core::operation_candidate quantized_blocked_ell_candidate() noexcept;
 core::operation_candidate quantized_csr_forward_epilogue_candidate() noexcept;
 core::operation_candidate quantized_blocked_ell_epilogue_candidate() noexcept;
 
-// Registers the five candidates; returns the first failing status.
+// The transpose with a fixed order of its fp32 sums (bitwise identical runs): it carries
+// candidate_deterministic, so a deterministic prepare_policy selects it where the atomic-order
+// transpose is rejected (operation_core.cc:210-214), and candidate_persistent_preprocessing for the
+// gene-major copy it builds from the catalog entry's device matrix.
+core::operation_candidate quantized_csr_transpose_ordered_candidate() noexcept;
+
+// Registers the six candidates; returns the first failing status.
 core::operation_status register_all(core::candidate_registry *registry) noexcept;
 
 // Releases what prepare() attached to a prepared operation (the cb200_prepared handle and the

@@ -92,7 +92,7 @@ int main(int argc, char **argv) {
 
     // ---- registration and capability query (host only) ----------------------------------
     static core::candidate_registry registry;
-    CHECK(static_cast<bool>(host::register_all(&registry)) && registry.size == 5u, "register five candidates");
+    CHECK(static_cast<bool>(host::register_all(&registry)) && registry.size == 6u, "register six candidates");
     CHECK(core::register_candidate(&registry, host::quantized_csr_forward_candidate()).code ==
               core::operation_status_code::duplicate_candidate, "duplicate registration is rejected");
     const core::operation_candidate *fwd = core::find_candidate(registry, host::quantized_csr_forward_candidate().identity);
@@ -569,6 +569,49 @@ int main(int argc, char **argv) {
         CHECK(newer.code == core::operation_status_code::invalid_launch_bindings &&
                   newer.binding == ex::binding_validation_code::stale_value,
               "a launch with a newer value generation is refused by an operation that keeps a copy of the values");
+        // ---- the ordered transpose: a deterministic policy selects it, two runs agree in every bit ----
+        {
+            const core::operation_candidate *ord =
+                core::find_candidate(registry, host::quantized_csr_transpose_ordered_candidate().identity);
+            CHECK(ord != nullptr && (ord->capability_flags & core::candidate_deterministic) != 0u &&
+                      (ord->capability_flags & core::candidate_persistent_preprocessing) != 0u,
+                  "the ordered transpose claims determinism and persistent preprocessing");
+            core::prepare_policy det_only;
+            det_only.deterministic = true;
+            det_only.allow_persistent_preprocessing = false;
+            core::prepared_operation po{};
+            CHECK(core::prepare_candidate(*ord, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32), det_only, &po).code ==
+                      core::operation_status_code::capability_rejected,
+                  "without persistent preprocessing the ordered transpose is rejected");
+            core::prepare_policy det_pre = with_preprocessing;
+            det_pre.deterministic = true;
+            st = core::prepare_candidate(*ord, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32), det_pre, &po);
+            CHECK(static_cast<bool>(st), "prepare_candidate(ordered transpose, deterministic policy)");
+            if (!st) std::printf("  message: %s\n", st.message);
+            CHECK(std::strcmp(host::prepared_schedule(po), "gene_gather") == 0, "deterministic transpose -> gather schedule");
+            plane2.generation = {5u};
+            l2.values = &v2;
+            std::vector<float> first(K * N), second(K * N);
+            st = core::run_prepared_operation(po, l2);
+            CHECK(static_cast<bool>(st), "run_prepared_operation(ordered transpose)");
+            if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+            cudaStreamSynchronize(stream);
+            cudaMemcpy(first.data(), d_gt, first.size() * sizeof(float), cudaMemcpyDeviceToHost);
+            cudaMemset(d_gt, 0xff, first.size() * sizeof(float));
+            st = core::run_prepared_operation(po, l2);
+            cudaStreamSynchronize(stream);
+            cudaMemcpy(second.data(), d_gt, second.size() * sizeof(float), cudaMemcpyDeviceToHost);
+            CHECK(static_cast<bool>(st) && std::memcmp(first.data(), second.data(), first.size() * sizeof(float)) == 0,
+                  "ordered transpose: the second run repeats every bit of the first");
+            double worst_ordered = 0.0;
+            for (std::int64_t gene = 0; gene < K; ++gene)
+                for (std::int64_t c = 0; c < N; ++c)
+                    worst_ordered = std::max(worst_ordered, std::fabs(static_cast<double>(first[gene * N + c]) - ref[gene * N + c]) /
+                                                                (col_l1[gene] * gmax + 1e-30));
+            std::printf("  transpose (ordered) max |d| / (||column||_1 max|G|) = %.3e\n", worst_ordered);
+            CHECK(worst_ordered <= 1.0e-4, "ordered transpose within the fp32 bound of the reference referee's result");
+            host::release_prepared(&po);
+        }
         host::release_prepared(&pt);
         cudaFree(d_ws2);
     }
