@@ -212,24 +212,18 @@ struct gather_params {
     unsigned *queue;   // next gene to hand out
 };
 
-template<int VEC>
-__device__ __forceinline__ void gather_load(const float *src, bool aligned, float (&v)[VEC]) {
-    if constexpr (VEC == 1) {
-        v[0] = __ldg(src);
-    } else if constexpr (VEC == 2) {
-        if (aligned) {
-            const float2 t = __ldg(reinterpret_cast<const float2 *>(src));
-            v[0] = t.x; v[1] = t.y;
-        } else {
-            v[0] = __ldg(src); v[1] = __ldg(src + 1);
-        }
+// VEC consecutive floats of a row of G; ALIGNED: one vector load
+template<int VEC, bool ALIGNED>
+__device__ __forceinline__ void gather_load(const float *src, float (&v)[VEC]) {
+    if constexpr (VEC == 2 && ALIGNED) {
+        const float2 t = __ldg(reinterpret_cast<const float2 *>(src));
+        v[0] = t.x; v[1] = t.y;
+    } else if constexpr (VEC == 4 && ALIGNED) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else {
-        if (aligned) {
-            const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
-            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-        } else {
-            v[0] = __ldg(src); v[1] = __ldg(src + 1); v[2] = __ldg(src + 2); v[3] = __ldg(src + 3);
-        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = __ldg(src + k);
     }
 }
 
@@ -244,14 +238,16 @@ __device__ __forceinline__ std::int64_t gather_lower_bound(const std::int32_t *r
     return lo;
 }
 
-// N == 32 * VEC; lane l owns the output columns [l * VEC, l * VEC + VEC).
-template<int VEC>
+// N == 32 * VEC; lane l owns the output columns [l * VEC, l * VEC + VEC).  The inner loop is kept to
+// two shuffles, one 32 x 32 -> 64-bit multiply-add for the address, one load and VEC FMAs per entry:
+// the kernel issues an instruction in most cycles, so every instruction per entry counts.
+template<int VEC, bool ALIGNED>
 __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kernel(const gather_params p) {
     __shared__ float part[kGatherWarps][32 * VEC];
     __shared__ unsigned next_gene;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool row_policy = p.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
-    const bool aligned = p.aligned != 0;
+    const std::uint32_t g_row_bytes = static_cast<std::uint32_t>(p.g_ld) * 4u; // the launcher checks it fits
     for (;;) {
         if (threadIdx.x == 0) next_gene = atomicAdd(p.queue, 1u);
         __syncthreads();
@@ -267,7 +263,7 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
         float acc[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
-        const float *g_lane = p.g + lane * VEC;
+        const char *g_lane = reinterpret_cast<const char *>(p.g + lane * VEC);
         for (std::int64_t chunk = lo + static_cast<std::int64_t>(warp) * kGatherChunk; chunk < hi;
              chunk += static_cast<std::int64_t>(kGatherWarps) * kGatherChunk) {
             const std::int64_t chunk_end = min(hi, chunk + kGatherChunk);
@@ -289,7 +285,8 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
                         for (int u = 0; u < 8; ++u) {
                             const int r = __shfl_sync(0xffffffffu, row, j0 + u);
                             vv[u] = __shfl_sync(0xffffffffu, value, j0 + u);
-                            gather_load<VEC>(g_lane + static_cast<std::int64_t>(r) * p.g_ld, aligned, gv[u]);
+                            gather_load<VEC, ALIGNED>(
+                                reinterpret_cast<const float *>(g_lane + static_cast<std::uint64_t>(static_cast<std::uint32_t>(r)) * g_row_bytes), gv[u]);
                         }
 #pragma unroll
                         for (int u = 0; u < 8; ++u)
@@ -301,7 +298,8 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
                         const int r = __shfl_sync(0xffffffffu, row, j);
                         const float v = __shfl_sync(0xffffffffu, value, j);
                         float gv[VEC];
-                        gather_load<VEC>(g_lane + static_cast<std::int64_t>(r) * p.g_ld, aligned, gv);
+                        gather_load<VEC, ALIGNED>(
+                            reinterpret_cast<const float *>(g_lane + static_cast<std::uint64_t>(static_cast<std::uint32_t>(r)) * g_row_bytes), gv);
 #pragma unroll
                         for (int k = 0; k < VEC; ++k) acc[k] = fmaf(v, gv[k], acc[k]);
                     }
@@ -437,9 +435,13 @@ cb200_status launch_qcsr_transpose_gather(const qcsr_view &x, const dense_args &
     p.queue = static_cast<unsigned *>(workspace);
     CB200_CUDA_OK(cudaMemsetAsync(workspace, 0, 4, stream));
     const unsigned grid = static_cast<unsigned>(std::min<std::int64_t>(x.cols, static_cast<std::int64_t>(sm_count) * 8));
-    if (vec == 1) qcsr_transpose_gather_kernel<1><<<grid, kGatherWarps * 32, 0, stream>>>(p);
-    else if (vec == 2) qcsr_transpose_gather_kernel<2><<<grid, kGatherWarps * 32, 0, stream>>>(p);
-    else qcsr_transpose_gather_kernel<4><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    if (d.dense_ld < 0 || d.dense_ld >= (std::int64_t{1} << 30))
+        return fail(CB200_STATUS_UNSUPPORTED, "the order-fixed transpose takes rows of G below 4 GB");
+    if (vec == 1) qcsr_transpose_gather_kernel<1, true><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    else if (vec == 2 && p.aligned) qcsr_transpose_gather_kernel<2, true><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    else if (vec == 2) qcsr_transpose_gather_kernel<2, false><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    else if (p.aligned) qcsr_transpose_gather_kernel<4, true><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    else qcsr_transpose_gather_kernel<4, false><<<grid, kGatherWarps * 32, 0, stream>>>(p);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
