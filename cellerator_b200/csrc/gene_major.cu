@@ -227,6 +227,14 @@ __device__ __forceinline__ void gather_load(const float *src, float (&v)[VEC]) {
     }
 }
 
+// float of the low byte of a word, one conversion instruction (a cvt from .u8 reads the low 8 bits
+// of a wider source register)
+__device__ __forceinline__ float low_byte_to_float(unsigned word) {
+    float f;
+    asm("cvt.rn.f32.u8 %0, %1;" : "=f"(f) : "r"(word));
+    return f;
+}
+
 // first position in [lo, hi) whose row is >= bound
 __device__ __forceinline__ std::int64_t gather_lower_bound(const std::int32_t *row_idx, std::int64_t lo, std::int64_t hi,
                                                            std::int64_t bound) {
@@ -241,7 +249,11 @@ __device__ __forceinline__ std::int64_t gather_lower_bound(const std::int32_t *r
 // N == 32 * VEC; lane l owns the output columns [l * VEC, l * VEC + VEC).  The inner loop is kept to
 // two shuffles, one 32 x 32 -> 64-bit multiply-add for the address, one load and VEC FMAs per entry:
 // the kernel issues an instruction in most cycles, so every instruction per entry counts.
-template<int VEC, bool ALIGNED>
+// What bounds it then is the load/store unit's data pipe, which also carries the shuffles: 256 B of G
+// and two 128 B shuffles per entry at N = 64.  PACKED (per-gene offsets, cells below 2^24) halves the
+// shuffles: a lane hands out (cell << 8 | code) and every lane decodes the value itself -- the same
+// fused multiply-add, so the same bits.
+template<int VEC, bool ALIGNED, bool PACKED>
 __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kernel(const gather_params p) {
     __shared__ float part[kGatherWarps][32 * VEC];
     __shared__ unsigned next_gene;
@@ -273,9 +285,13 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
                 float value = 0.0f;
                 if (lane < count) {
                     row = __ldg(p.row_idx + base + lane);
-                    const float code = static_cast<float>(__ldg(p.codes + base + lane));
-                    const float offset = row_policy ? (p.offsets != nullptr ? __ldg(p.offsets + row) : 0.0f) : gene_offset;
-                    value = fmaf(code, scale, offset);
+                    const unsigned code = __ldg(p.codes + base + lane);
+                    if constexpr (PACKED) {
+                        row = static_cast<int>((static_cast<unsigned>(row) << 8) | code);
+                    } else {
+                        const float offset = row_policy ? (p.offsets != nullptr ? __ldg(p.offsets + row) : 0.0f) : gene_offset;
+                        value = fmaf(static_cast<float>(code), scale, offset);
+                    }
                 }
                 if (count == 32) {
 #pragma unroll
@@ -283,10 +299,15 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
                         float gv[8][VEC], vv[8];
 #pragma unroll
                         for (int u = 0; u < 8; ++u) {
-                            const int r = __shfl_sync(0xffffffffu, row, j0 + u);
-                            vv[u] = __shfl_sync(0xffffffffu, value, j0 + u);
+                            unsigned r = static_cast<unsigned>(__shfl_sync(0xffffffffu, row, j0 + u));
+                            if constexpr (PACKED) {
+                                vv[u] = fmaf(low_byte_to_float(r), scale, gene_offset);
+                                r >>= 8;
+                            } else {
+                                vv[u] = __shfl_sync(0xffffffffu, value, j0 + u);
+                            }
                             gather_load<VEC, ALIGNED>(
-                                reinterpret_cast<const float *>(g_lane + static_cast<std::uint64_t>(static_cast<std::uint32_t>(r)) * g_row_bytes), gv[u]);
+                                reinterpret_cast<const float *>(g_lane + static_cast<std::uint64_t>(r) * g_row_bytes), gv[u]);
                         }
 #pragma unroll
                         for (int u = 0; u < 8; ++u)
@@ -295,11 +316,17 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
                     }
                 } else {
                     for (int j = 0; j < count; ++j) {
-                        const int r = __shfl_sync(0xffffffffu, row, j);
-                        const float v = __shfl_sync(0xffffffffu, value, j);
+                        unsigned r = static_cast<unsigned>(__shfl_sync(0xffffffffu, row, j));
+                        float v;
+                        if constexpr (PACKED) {
+                            v = fmaf(low_byte_to_float(r), scale, gene_offset);
+                            r >>= 8;
+                        } else {
+                            v = __shfl_sync(0xffffffffu, value, j);
+                        }
                         float gv[VEC];
                         gather_load<VEC, ALIGNED>(
-                            reinterpret_cast<const float *>(g_lane + static_cast<std::uint64_t>(static_cast<std::uint32_t>(r)) * g_row_bytes), gv);
+                            reinterpret_cast<const float *>(g_lane + static_cast<std::uint64_t>(r) * g_row_bytes), gv);
 #pragma unroll
                         for (int k = 0; k < VEC; ++k) acc[k] = fmaf(v, gv[k], acc[k]);
                     }
@@ -437,11 +464,17 @@ cb200_status launch_qcsr_transpose_gather(const qcsr_view &x, const dense_args &
     const unsigned grid = static_cast<unsigned>(std::min<std::int64_t>(x.cols, static_cast<std::int64_t>(sm_count) * 8));
     if (d.dense_ld < 0 || d.dense_ld >= (std::int64_t{1} << 30))
         return fail(CB200_STATUS_UNSUPPORTED, "the order-fixed transpose takes rows of G below 4 GB");
-    if (vec == 1) qcsr_transpose_gather_kernel<1, true><<<grid, kGatherWarps * 32, 0, stream>>>(p);
-    else if (vec == 2 && p.aligned) qcsr_transpose_gather_kernel<2, true><<<grid, kGatherWarps * 32, 0, stream>>>(p);
-    else if (vec == 2) qcsr_transpose_gather_kernel<2, false><<<grid, kGatherWarps * 32, 0, stream>>>(p);
-    else if (p.aligned) qcsr_transpose_gather_kernel<4, true><<<grid, kGatherWarps * 32, 0, stream>>>(p);
-    else qcsr_transpose_gather_kernel<4, false><<<grid, kGatherWarps * 32, 0, stream>>>(p);
+    const bool packed = x.policy != CB200_DECODE_COLUMN_SCALE_ROW_OFFSET && x.rows <= (std::int64_t{1} << 24) && p.aligned;
+    const unsigned threads = kGatherWarps * 32;
+    if (packed) {
+        if (vec == 1) qcsr_transpose_gather_kernel<1, true, true><<<grid, threads, 0, stream>>>(p);
+        else if (vec == 2) qcsr_transpose_gather_kernel<2, true, true><<<grid, threads, 0, stream>>>(p);
+        else qcsr_transpose_gather_kernel<4, true, true><<<grid, threads, 0, stream>>>(p);
+    } else if (vec == 1) qcsr_transpose_gather_kernel<1, true, false><<<grid, threads, 0, stream>>>(p);
+    else if (vec == 2 && p.aligned) qcsr_transpose_gather_kernel<2, true, false><<<grid, threads, 0, stream>>>(p);
+    else if (vec == 2) qcsr_transpose_gather_kernel<2, false, false><<<grid, threads, 0, stream>>>(p);
+    else if (p.aligned) qcsr_transpose_gather_kernel<4, true, false><<<grid, threads, 0, stream>>>(p);
+    else qcsr_transpose_gather_kernel<4, false, false><<<grid, threads, 0, stream>>>(p);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
