@@ -232,7 +232,9 @@ cb200_status cb200_backend_query(int32_t projection, const cb200_numeric_policy 
         /* G is fp32 storage either way; bf16 products round both factors (tensor-core schedule) */
         out->supported = common && numeric->dense_storage == CB200_DTYPE_F32 &&
                          (numeric->multiply == CB200_DTYPE_F32 || numeric->multiply == CB200_DTYPE_BF16);
-        out->flags = CB200_CAP_GRAPH_CAPTURE; /* floating-point reductions: order not fixed */
+        /* floating-point reductions, order not fixed -- unless prepare is asked for determinism and
+         * handed the matrix, when it builds a gene-major copy and the sums have a fixed order */
+        out->flags = CB200_CAP_GRAPH_CAPTURE;
         break;
     case CB200_PROJECTION_BLOCKED_ELL:
         out->name = "cb200.qbell.forward.sm100a";
