@@ -6,8 +6,8 @@
 // per (stored entry, output column) over f16 values.  Here the codes are decoded in
 // registers, one warp owns a cell row and keeps that row of G in registers, and each lane
 // issues 128-bit vector reductions (red.global.add.v4.f32) into the gene row of G'.
-// The order of the floating-point sums is not fixed, so this projection never advertises
-// the deterministic capability.
+// The order of the floating-point sums is not fixed: a problem that asks for determinism is
+// served by the gather schedule over a gene-major copy instead (gene_major.cu).
 #include "kernels.cuh"
 
 #include <algorithm>

@@ -227,7 +227,8 @@ typedef struct cb200_spmm_problem {
     uint64_t structure_epoch; /* non-zero; a launch with another epoch is stale (launch_bindings.hh:261-275) */
     /* Optional host copy of row_ptr (m+1) used to choose the row schedule; NULL = default. */
     const int64_t *host_row_ptr;
-    int32_t deterministic; /* prepare_policy.deterministic, operation_core.hh:116-124 */
+    int32_t deterministic; /* prepare_policy.deterministic, operation_core.hh:116-124; a transpose needs
+                            * device_matrix for it (schedule "gene_gather"), else prepare is refused */
     /* numeric_policy.multiply of the request: 0 or CB200_DTYPE_F32 = exact fp32 products;
      * CB200_DTYPE_BF16 = decoded values may be rounded to bf16 and multiplied on the tensor cores
      * (CSR forward with bf16 W: schedules "tensor_windows" / "tensor_blocked"; transpose with the
@@ -531,8 +532,8 @@ cb200_status cb200_build_execution_csr(const cb200_execution_csr *view, void *st
  *   col_ptr  device, cols + 1: first entry of each gene
  *   row_idx  device, nnz: the cell of each entry
  *   codes    device, nnz: one code per byte (4-bit sources are widened, the value is unchanged)
- * Scales and offsets are shared with the source.  Limits: rows < 2^31; cols <= 56,062 (a 32-bit
- * counter per gene in shared memory) -- outside them CB200_STATUS_UNSUPPORTED.  Enqueues on `stream`,
+ * Scales and offsets are shared with the source.  Limits: rows < 2^31; cols <= 58,112 (a 32-bit
+ * counter per gene in shared memory); column indices ascend inside a row, as the format requires -- outside them CB200_STATUS_UNSUPPORTED.  Enqueues on `stream`,
  * allocates nothing; `workspace` (device) needs cb200_qcsr_gene_major_workspace(rows, cols) bytes
  * (0 = shape outside the limits), and its first 32-bit word is 0 afterwards unless a column index lay
  * outside the matrix (bit 0).

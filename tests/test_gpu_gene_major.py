@@ -38,9 +38,9 @@ def test_gene_major_copy_reports_a_bad_column_and_refuses_wide_matrices(cuda_dev
     c["col_idx"][-1] = 20
     with pytest.raises(ValueError):
         ops.qcsr_gene_major(to_dev(c, cuda_device))
-    assert capi.lib().cb200_qcsr_gene_major_workspace(10, 56062) > 0
-    assert capi.lib().cb200_qcsr_gene_major_workspace(10, 56063) == 0
-    wide = host_pack(oracle, random_csr(rng, rows=4, cols=56063, max_nnz=3, bits=8))
+    assert capi.lib().cb200_qcsr_gene_major_workspace(10, 58112) > 0
+    assert capi.lib().cb200_qcsr_gene_major_workspace(10, 58113) == 0
+    wide = host_pack(oracle, random_csr(rng, rows=4, cols=58113, max_nnz=3, bits=8))
     with pytest.raises(capi.Cb200Error):
         ops.qcsr_gene_major(to_dev(wide, cuda_device))
 

@@ -100,7 +100,7 @@ def test_bad_descriptors_are_rejected_before_any_device_call():
     assert L.cb200_spmm_prepare(C.byref(pr), C.byref(handle)) == capi.UNSUPPORTED
     pr.bits = 8
     pr.projection, pr.deterministic = capi.PROJECTION_TRANSPOSE, 1
-    assert L.cb200_spmm_prepare(C.byref(pr), C.byref(handle)) == capi.UNSUPPORTED          # not deterministic
+    assert L.cb200_spmm_prepare(C.byref(pr), C.byref(handle)) == capi.UNSUPPORTED          # deterministic transpose without the device matrix
     assert L.cb200_spmm_run(None, None) == capi.INVALID_ARGUMENT
 
 
