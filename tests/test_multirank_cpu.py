@@ -44,6 +44,20 @@ def _worker(rank, world, port, result_dir):
         # transpose: partial over my rows, then the all-reduce the GPU path issues
         part = torch.from_numpy(checker.qcsr_transpose(*args, g, 300, r0, r1))
         dist.all_reduce(part, op=dist.ReduceOp.SUM)
+        # deterministic transpose: fixed-order fp32 partial over my row range of the gene-major copy,
+        # summed by the same all-reduce; a second round repeats every bit
+        rc, col_ptr, row_idx, codes = checker.qcsr_gene_major(8, 300, h["row_ptr"], h["packed_row_ptr"], h["col_idx"], h["packed"])
+        assert rc == 0
+        rounds = []
+        for _ in range(2):
+            mine = torch.from_numpy(checker.qcsr_transpose_ordered(1, col_ptr, row_idx, codes, h["scales"], h["offsets"], g, r0, r1))
+            dist.all_reduce(mine, op=dist.ReduceOp.SUM)
+            rounds.append(mine.numpy().copy())
+        if rank == 0:
+            gt64 = checker.qcsr_transpose(*args, g, 300)
+            np.save(os.path.join(result_dir, "ordered.npy"),
+                    np.array([float(np.array_equal(rounds[0].view(np.uint32), rounds[1].view(np.uint32))),
+                              float(np.abs(rounds[0] - gt64).max() / (np.abs(gt64).max() + 1e-30))]))
         if rank == 0:
             y_ref = checker.qcsr_forward(*args, w, 300)
             gt_ref = checker.qcsr_transpose(*args, g, 300)
@@ -59,6 +73,8 @@ def test_row_sharding_and_allreduce_on_cpu_ranks(tmp_path, world):
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     assert bool(np.load(tmp_path / "fwd_ok.npy")[0])          # forward shards tile Y bit-exactly
     assert float(np.load(tmp_path / "tr_err.npy")[0]) < 1e-9   # double sums regrouped by shard
+    same_bits, rel_err = np.load(tmp_path / "ordered.npy")
+    assert same_bits == 1.0 and rel_err < 1e-5                 # fixed-order fp32 partials, summed across ranks
 
 
 def test_empty_trailing_shards():
