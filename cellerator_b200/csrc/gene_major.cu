@@ -28,6 +28,7 @@
 #include "kernels.cuh"
 
 #include <algorithm>
+#include <vector>
 
 namespace cb200 {
 namespace {
@@ -255,6 +256,7 @@ struct gather_params {
     int aligned;       // G rows can be read with one vector load per lane
     float alpha, beta;
     unsigned *queue;   // next gene to hand out
+    const std::int32_t *gene_order; // position in the queue -> gene (long genes first); null: natural order
 };
 
 // VEC consecutive floats of a row of G; ALIGNED: one vector load
@@ -308,8 +310,8 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
     for (;;) {
         if (threadIdx.x == 0) next_gene = atomicAdd(p.queue, 1u);
         __syncthreads();
-        const std::int64_t gene = next_gene;
-        if (gene >= p.cols) return;
+        if (next_gene >= p.cols) return;
+        const std::int64_t gene = p.gene_order != nullptr ? __ldg(p.gene_order + next_gene) : static_cast<std::int64_t>(next_gene);
         std::int64_t lo = __ldg(p.col_ptr + gene), hi = __ldg(p.col_ptr + gene + 1);
         if (p.restrict_rows) {
             lo = gather_lower_bound(p.row_idx, lo, hi, p.row_begin);
@@ -470,11 +472,25 @@ cb200_status build_gene_major_layout(const qcsr_view &x, gene_major_layout *out)
         else if (status != 0) st = fail(CB200_STATUS_INVALID_SHAPE, "a column index lies outside the matrix");
     }
     if (ws != nullptr) cudaFree(ws);
+    // genes by descending entry count: a gene is one CTA's work, so the long ones have to start first
+    if (st == CB200_STATUS_SUCCESS) {
+        std::vector<std::int64_t> ptr(static_cast<std::size_t>(x.cols) + 1u);
+        std::vector<std::int32_t> order(static_cast<std::size_t>(x.cols));
+        err = cudaMemcpy(ptr.data(), out->col_ptr, ptr_bytes, cudaMemcpyDeviceToHost);
+        for (std::int64_t c = 0; c < x.cols; ++c) order[static_cast<std::size_t>(c)] = static_cast<std::int32_t>(c);
+        std::stable_sort(order.begin(), order.end(), [&](std::int32_t a, std::int32_t b) {
+            return ptr[static_cast<std::size_t>(a) + 1u] - ptr[static_cast<std::size_t>(a)] >
+                   ptr[static_cast<std::size_t>(b) + 1u] - ptr[static_cast<std::size_t>(b)];
+        });
+        if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->gene_order), order.size() * sizeof(std::int32_t));
+        if (err == cudaSuccess) err = cudaMemcpy(out->gene_order, order.data(), order.size() * sizeof(std::int32_t), cudaMemcpyHostToDevice);
+        if (err != cudaSuccess) st = fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err));
+    }
     if (st != CB200_STATUS_SUCCESS) {
         free_gene_major_layout(out);
         return st;
     }
-    out->bytes = ptr_bytes + idx_bytes + code_bytes;
+    out->bytes = ptr_bytes + idx_bytes + code_bytes + static_cast<std::size_t>(x.cols) * sizeof(std::int32_t);
     out->src_row_ptr = x.row_ptr; out->src_col_idx = x.col_idx; out->src_packed = x.packed;
     return CB200_STATUS_SUCCESS;
 }
@@ -483,6 +499,7 @@ void free_gene_major_layout(gene_major_layout *layout) {
     if (layout->col_ptr != nullptr) cudaFree(layout->col_ptr);
     if (layout->row_idx != nullptr) cudaFree(layout->row_idx);
     if (layout->codes != nullptr) cudaFree(layout->codes);
+    if (layout->gene_order != nullptr) cudaFree(layout->gene_order);
     *layout = gene_major_layout{};
 }
 
@@ -510,6 +527,7 @@ cb200_status launch_qcsr_transpose_gather(const qcsr_view &x, const dense_args &
     p.aligned = (reinterpret_cast<std::uintptr_t>(d.dense) % (4u * vec) == 0u) && ((d.dense_ld * 4) % (4 * vec) == 0) ? 1 : 0;
     p.alpha = d.alpha; p.beta = d.beta;
     p.queue = static_cast<unsigned *>(workspace);
+    p.gene_order = layout.gene_order;
     CB200_CUDA_OK(cudaMemsetAsync(workspace, 0, 4, stream));
     const unsigned grid = static_cast<unsigned>(std::min<std::int64_t>(x.cols, static_cast<std::int64_t>(sm_count) * 8));
     if (d.dense_ld < 0 || d.dense_ld >= (std::int64_t{1} << 30))

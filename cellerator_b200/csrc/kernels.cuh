@@ -123,6 +123,7 @@ struct gene_major_layout {
     std::int64_t *col_ptr = nullptr;  // cols + 1
     std::int32_t *row_idx = nullptr;  // nnz
     std::uint8_t *codes = nullptr;    // nnz
+    std::int32_t *gene_order = nullptr; // cols: genes by descending entry count (the gather kernel starts the long ones first)
     std::uint64_t bytes = 0;
     const void *src_row_ptr = nullptr, *src_col_idx = nullptr, *src_packed = nullptr; // arrays it was built from
 };

@@ -151,3 +151,26 @@ def test_deterministic_transpose_at_scale_against_the_atomic_kernel(cuda_device)
     gmax = float(g.abs().max())
     assert torch.all((a - exact).abs() <= 1e-4 * (col_l1[:, None] * gmax).float() + 1e-30)
     op.close()
+
+
+def test_deterministic_transpose_skewed_genes(cuda_device, oracle):
+    """One gene present in every cell, the others rare: the long gene is handed out first (genes go to
+    CTAs in descending order of their entry count), the result is still the fixed-order one."""
+    rng = np.random.default_rng(123)
+    rows, cols, n = 7000, 60, 64
+    counts = rng.integers(0, 4, size=rows)
+    row_ptr = np.zeros(rows + 1, dtype=np.int64)
+    np.cumsum(counts + 1, out=row_ptr[1:])
+    others = np.array([g for g in range(cols) if g != 41])
+    col_idx = np.concatenate([np.sort(np.append(rng.choice(others, size=int(k), replace=False), 41)) for k in counts]).astype(np.int32)
+    c = dict(rows=rows, cols=cols, bits=8, policy=1, row_ptr=row_ptr, col_idx=col_idx,
+             scales=rng.uniform(0.01, 0.5, size=cols).astype(np.float32), offsets=rng.uniform(-1, 1, size=cols).astype(np.float32),
+             values=rng.uniform(-2.0, 40.0, size=len(col_idx)).astype(np.float32))
+    c = host_pack(oracle, c)
+    x = to_dev(c, cuda_device)
+    g, g_host = dense(rng, rows, n, torch.float32, cuda_device, std=1.0)
+    out = ops.spmm_transpose(x, g, deterministic=True).cpu().numpy()
+    rc, col_ptr, row_idx, codes = oracle.qcsr_gene_major(8, cols, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"])
+    assert rc == 0 and col_ptr[42] - col_ptr[41] == rows
+    want = oracle.qcsr_transpose_ordered(1, col_ptr, row_idx, codes, c["scales"], c["offsets"], g_host, 0, rows)
+    assert np.array_equal(bits_of(out), bits_of(want))
