@@ -273,8 +273,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
             (problem->device_matrix == nullptr || !qcsr_transpose_gather_shape_ok(problem->n) ||
              !qcsr_gene_major_shape_ok(problem->m, problem->k, problem->bits)))
             return fail(CB200_STATUS_UNSUPPORTED,
-                        "a deterministic transpose needs the device matrix at prepare time, N in {32, 64, 128} and a gene count "
-                        "whose counters fit shared memory; the other transpose kernels add in atomic order");
+                        "a deterministic transpose needs the device matrix at prepare time and N in {32, 64, 128}; the other "
+                        "transpose kernels add in atomic order");
     } else if (problem->projection == CB200_PROJECTION_CSR || problem->projection == CB200_PROJECTION_BLOCKED_ELL) {
         if (!supported_dense(problem->dense_dtype)) return fail(CB200_STATUS_UNSUPPORTED, "W must be fp32 or bf16");
     } else {

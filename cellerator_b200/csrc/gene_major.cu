@@ -7,7 +7,7 @@
 // the order of the cells inside a gene to the scheduler.  Here the placement is a stable counting
 // sort -- cells ascend inside every gene, the same arrays on every run -- in three steps:
 //   1. one CTA per block of 1,024 rows counts its entries per gene in shared memory and writes the
-//      counts row  counts[block][gene];
+//      counts row  counts[block][gene] (beyond 57,344 genes: one launch per range of that many);
 //   2. per gene, the counts are scanned over the blocks (the offset of a block inside the gene's
 //      segment) and the totals over the genes (col_ptr);
 //   3. the CTA of a block walks its rows in order; the entries of one row go to different genes
@@ -62,23 +62,24 @@ __device__ __forceinline__ unsigned gm_load_code(const std::uint8_t *row_bytes, 
     }
 }
 
-// step 1: counts[block][gene]
-__global__ void __launch_bounds__(kBuildThreads) gm_count_kernel(const gm_params p) {
+// step 1: counts[block][gene] for the genes [g0, g1): one launch per range of genes whose counters
+// fit shared memory (one launch up to 57,344 genes)
+__global__ void __launch_bounds__(kBuildThreads) gm_count_kernel(const gm_params p, int g0, int g1) {
     extern __shared__ std::uint32_t gm_hist[];
-    const int cols = static_cast<int>(p.cols);
-    for (int c = threadIdx.x; c < cols; c += kBuildThreads) gm_hist[c] = 0u;
+    const int span = g1 - g0;
+    for (int c = threadIdx.x; c < span; c += kBuildThreads) gm_hist[c] = 0u;
     __syncthreads();
     const std::int64_t r0 = static_cast<std::int64_t>(blockIdx.x) * kBlockRows;
     const std::int64_t r1 = min(p.rows, r0 + kBlockRows);
     const std::int64_t begin = __ldg(p.row_ptr + r0), end = __ldg(p.row_ptr + r1);
     for (std::int64_t i = begin + threadIdx.x; i < end; i += kBuildThreads) {
         const int c = __ldg(p.col_idx + i);
-        if (static_cast<unsigned>(c) < static_cast<unsigned>(cols)) atomicAdd(&gm_hist[c], 1u);
-        else atomicOr(p.status, 1); // a column outside the matrix: reported, entry left out
+        if (static_cast<unsigned>(c - g0) < static_cast<unsigned>(span)) atomicAdd(&gm_hist[c - g0], 1u);
+        else if (static_cast<unsigned>(c) >= static_cast<unsigned>(p.cols)) atomicOr(p.status, 1); // outside the matrix: reported, left out
     }
     __syncthreads();
-    std::uint32_t *row = p.counts + static_cast<std::int64_t>(blockIdx.x) * cols;
-    for (int c = threadIdx.x; c < cols; c += kBuildThreads) row[c] = gm_hist[c];
+    std::uint32_t *row = p.counts + static_cast<std::int64_t>(blockIdx.x) * p.cols + g0;
+    for (int c = threadIdx.x; c < span; c += kBuildThreads) row[c] = gm_hist[c];
 }
 
 // step 2a: per gene, exclusive scan of the counts over the blocks; the total goes to col_ptr[gene]
@@ -230,8 +231,7 @@ __global__ void __launch_bounds__(kBuildThreads) gm_fill_kernel(const gm_params 
 }
 
 
-// the counting pass keeps a counter per gene in shared memory: that bounds the gene count
-std::size_t count_smem_limit_genes() { return (227u * 1024u) / 4u; }
+constexpr int kCountGenes = 56 * 1024; // genes per launch of the counting pass: a 32-bit counter each in shared memory
 std::size_t fill_smem_bytes() {
     return static_cast<std::size_t>(kFillGenes + 2 * kBlockRows + 1) * 8u +
            static_cast<std::size_t>(kFillGenes + kBlockRows + 2 + kStageEntries) * 4u;
@@ -398,8 +398,7 @@ __global__ void __launch_bounds__(kGatherWarps * 32) qcsr_transpose_gather_kerne
 } // namespace
 
 bool qcsr_gene_major_shape_ok(std::int64_t rows, std::int64_t cols, int bits) {
-    return rows >= 0 && rows < (std::int64_t{1} << 31) && cols >= 1 &&
-           static_cast<std::uint64_t>(cols) <= count_smem_limit_genes() && (bits == 8 || bits == 4);
+    return rows >= 0 && rows < (std::int64_t{1} << 31) && cols >= 1 && cols < (std::int64_t{1} << 31) && (bits == 8 || bits == 4);
 }
 
 std::uint64_t qcsr_gene_major_workspace_bytes(std::int64_t rows, std::int64_t cols) {
@@ -410,8 +409,7 @@ std::uint64_t qcsr_gene_major_workspace_bytes(std::int64_t rows, std::int64_t co
 cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, std::int32_t *row_idx, std::uint8_t *codes,
                                     void *workspace, std::uint64_t workspace_bytes, cudaStream_t stream) {
     if (!qcsr_gene_major_shape_ok(x.rows, x.cols, x.bits))
-        return fail(CB200_STATUS_UNSUPPORTED, "gene-major copy: up to 2^31 - 1 rows, %lld genes (a counter per gene in shared memory), 8- or 4-bit codes",
-                    static_cast<long long>(count_smem_limit_genes()));
+        return fail(CB200_STATUS_UNSUPPORTED, "gene-major copy: up to 2^31 - 1 rows and genes, 8- or 4-bit codes");
     if (x.bits == 4 && x.packed_row_ptr == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "4-bit codes need packed_row_ptr");
     if (col_ptr == nullptr || (x.nnz > 0 && (row_idx == nullptr || codes == nullptr)) || x.row_ptr == nullptr)
         return fail(CB200_STATUS_INVALID_ARGUMENT, "null array");
@@ -429,10 +427,12 @@ cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, s
         CB200_CUDA_OK(cudaMemsetAsync(col_ptr, 0, static_cast<std::size_t>(x.cols + 1) * 8u, stream));
         return CB200_STATUS_SUCCESS;
     }
-    const std::size_t count_smem = static_cast<std::size_t>(x.cols) * 4u;
+    const std::size_t count_smem = static_cast<std::size_t>(std::min<std::int64_t>(x.cols, kCountGenes)) * 4u;
     const std::size_t fill_smem = fill_smem_bytes();
     CB200_CUDA_OK(cudaFuncSetAttribute(gm_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(count_smem)));
-    gm_count_kernel<<<static_cast<unsigned>(p.blocks), kBuildThreads, count_smem, stream>>>(p);
+    for (std::int64_t g0 = 0; g0 < x.cols; g0 += kCountGenes)
+        gm_count_kernel<<<static_cast<unsigned>(p.blocks), kBuildThreads, count_smem, stream>>>(
+            p, static_cast<int>(g0), static_cast<int>(std::min<std::int64_t>(x.cols, g0 + kCountGenes)));
     gm_block_scan_kernel<<<static_cast<unsigned>((x.cols + 255) / 256), 256, 0, stream>>>(p);
     gm_col_scan_kernel<<<1, 1024, 0, stream>>>(col_ptr, x.cols);
     if (x.bits == 8) {
@@ -446,7 +446,8 @@ cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, s
             gm_fill_kernel<4><<<static_cast<unsigned>(p.blocks), kBuildThreads, fill_smem, stream>>>(
                 p, static_cast<int>(g0), static_cast<int>(std::min<std::int64_t>(x.cols, g0 + kFillGenes)));
     }
-    count_launch(3 + static_cast<std::uint64_t>((x.cols + kFillGenes - 1) / kFillGenes));
+    count_launch(2 + static_cast<std::uint64_t>((x.cols + kCountGenes - 1) / kCountGenes) +
+                 static_cast<std::uint64_t>((x.cols + kFillGenes - 1) / kFillGenes));
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
 }

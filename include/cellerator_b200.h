@@ -532,8 +532,8 @@ cb200_status cb200_build_execution_csr(const cb200_execution_csr *view, void *st
  *   col_ptr  device, cols + 1: first entry of each gene
  *   row_idx  device, nnz: the cell of each entry
  *   codes    device, nnz: one code per byte (4-bit sources are widened, the value is unchanged)
- * Scales and offsets are shared with the source.  Limits: rows < 2^31; cols <= 58,112 (a 32-bit
- * counter per gene in shared memory); column indices ascend inside a row, as the format requires -- outside them CB200_STATUS_UNSUPPORTED.  Enqueues on `stream`,
+ * Scales and offsets are shared with the source.  Rows and genes below 2^31; column indices ascend
+ * inside a row, as the format requires.  Enqueues on `stream`,
  * allocates nothing; `workspace` (device) needs cb200_qcsr_gene_major_workspace(rows, cols) bytes
  * (0 = shape outside the limits), and its first 32-bit word is 0 afterwards unless a column index lay
  * outside the matrix (bit 0).
