@@ -13,7 +13,7 @@
 //   3. the CTA of a block walks its rows in order; the entries of one row go to different genes
 //      (column indices ascend strictly inside a row), so a row is placed in parallel and a barrier
 //      between rows keeps the cells of a gene in ascending order.  This pass runs once per range of
-//      4,096 genes, so that the segments being written stay in L2.
+//      1,024 genes, so that the segments being written stay in L2.
 // Codes are widened to one byte per entry in the copy (4-bit sources too): a gene's segment is
 // written by many CTAs at once and bytes need no read-modify-write.
 //
@@ -143,7 +143,7 @@ __device__ __forceinline__ std::int64_t gm_lower_bound(const std::int32_t *col_i
     return lo;
 }
 
-constexpr int kFillGenes = 4096;   // genes per launch of the placing pass
+constexpr int kFillGenes = 1024;   // genes per launch of the placing pass
 constexpr int kStageEntries = 8192; // entries staged in shared memory per group of rows (>= kFillGenes: a row fits)
 
 // step 3: place the entries of the genes [g0, g1), rows of a block in order.  One launch per gene
@@ -152,10 +152,10 @@ constexpr int kStageEntries = 8192; // entries staged in shared memory per group
 // The entries of a range are contiguous inside a row, because column indices ascend there.
 // A CTA stages the entries of as many rows as fit (warp per row, coalesced, many loads in flight) as
 // words (gene - g0) << 8 | code, then walks those rows in order out of shared memory with a barrier
-// between rows: the ordered walk has no global load on its critical path.  What remains is the rate
-// at which L2 takes scattered partial-sector writes (a 4 B cell and a 1 B code per entry, 3.6 G writes
-// for 1.8 G entries): 99 ms for 10^6 x 33,538 with 1.8 G entries, 161 ms before the gene ranges and
-// the staging.
+// between rows: the ordered walk has no global load on its critical path.  Measured on 10^6 x 33,538
+// with 1.8 G entries: 161 ms with every gene in one launch and the loads inside the walk, 99 ms with
+// ranges of 4,096 genes, 66 ms with 1,024 (the sectors being filled by the 296 resident CTAs then
+// fit L2: 19 MB), 110 ms with 512 (twice the launches, and a barrier per row in each).
 template<int BITS>
 __global__ void __launch_bounds__(kBuildThreads) gm_fill_kernel(const gm_params p, int g0, int g1) {
     extern __shared__ std::int64_t gm_fill_smem[];
