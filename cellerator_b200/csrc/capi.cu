@@ -331,7 +331,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
                 return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
             }
             if (problem->persistent_limit_bytes != 0u &&
-                static_cast<std::uint64_t>(problem->nnz) * 5u + static_cast<std::uint64_t>(problem->k + 1) * 8u >
+                static_cast<std::uint64_t>(problem->nnz) * 5u + static_cast<std::uint64_t>(problem->k + 1) * 12u >
                     problem->persistent_limit_bytes) {
                 delete p;
                 return fail(CB200_STATUS_UNSUPPORTED, "the gene-major copy of a deterministic transpose exceeds the persistent memory limit");
