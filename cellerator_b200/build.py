@@ -6,7 +6,9 @@
 Outputs (git-ignored, kept beside the sources so they travel with the tree):
     cellerator_b200/lib/libcellerator_b200.so       kernels + C ABI (include/cellerator_b200.h)
     cellerator_b200/lib/libcb200_synth.so           seeded workload generator used by bench/tests
-    cellerator_b200/lib/libcb200_cpmath.so          C++ operation-core backend over the C ABI
+    cellerator_b200/lib/libcb200_candidates.so      host/b200_candidates.cc, the C++ operation-core candidates over the
+                                                    C ABI; compiles against the Cellerator headers, so it is built only
+                                                    where CELLERATOR_REFERENCE names a Cellerator source tree
 """
 from __future__ import annotations
 
@@ -28,7 +30,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "-I", os.path.join(ROOT, "include")] + os.environ.get("CB200_NVCC_EXTRA", "").split()
 
-KERNEL_SOURCES = ["capi.cu", "qcsr_forward.cu", "qcsr_forward_tiled.cu", "qcsr_forward_mma.cu", "qcsr_forward_blocked.cu", "qcsr_forward_dense.cu", "qcsr_transpose.cu", "qcsr_transpose_blocked.cu", "bell_lowering.cu", "public_route.cu", "gene_major.cu", "qbell_forward.cu", "qbell_tcgen05.cu",
+KERNEL_SOURCES = ["capi.cu", "host_contract.cu", "fleet.cu", "host_stage.cu", "qcsr_forward.cu", "qcsr_forward_tiled.cu", "qcsr_forward_mma.cu", "qcsr_forward_blocked.cu", "qcsr_forward_dense.cu", "qcsr_transpose.cu", "qcsr_transpose_blocked.cu", "bell_lowering.cu", "public_route.cu", "gene_major.cu", "qbell_forward.cu", "qbell_tcgen05.cu",
                   "codec.cu"]
 SYNTH_SOURCES = ["synth.cu"]
 
@@ -66,11 +68,19 @@ def _compile(src: str, force: bool, extra: list[str]) -> str:
     return obj
 
 
+def reference_root() -> str | None:
+    """The Cellerator source tree the C++ host layer compiles against: the directory CELLERATOR_REFERENCE
+    names, else a checkout called `reference` beside this repository."""
+    for root in (os.environ.get("CELLERATOR_REFERENCE", ""), os.path.join(os.path.dirname(ROOT), "reference")):
+        if root and os.path.isdir(os.path.join(root, "include", "Cellerator")):
+            return os.path.abspath(root)
+    return None
+
+
 def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
     os.makedirs(LIB, exist_ok=True)
     os.makedirs(OBJ, exist_ok=True)
     targets = {k: [s for s in v if os.path.exists(s)] for k, v in TARGETS.items()}
-    cpmath = os.path.join(HOST, "cpmath_backend.cc")
     jobs = {}
     with cf.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
         for lib, srcs in targets.items():
@@ -84,18 +94,23 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
         path = os.path.join(LIB, lib)
         deps = [objs[s] for s in srcs]
         if force or _newer(path, deps):
-            _run([NVCC, *ARCH, "-shared", "-o", path, *deps])
+            _run([NVCC, *ARCH, "-shared", "-o", path, *deps, "-ldl"])  # dl: NCCL is bound at run time (fleet.cu)
         out[lib] = path
         if verbose:
             print("built", path)
-    if os.path.exists(cpmath):
-        path = os.path.join(LIB, "libcb200_cpmath.so")
-        deps = [cpmath] + _headers()
+    ref = reference_root()
+    candidates = os.path.join(HOST, "b200_candidates.cc")
+    if ref is not None and os.path.exists(candidates):
+        # the product's own C++ host layer: operation_candidate records over the C ABI
+        path = os.path.join(LIB, "libcb200_candidates.so")
+        deps = [candidates] + _headers()
         if force or _newer(path, deps + [out["libcellerator_b200.so"]]):
             cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-            _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(ROOT, "include"), "-I", HOST,
-                  "-o", path, cpmath, "-L", LIB, "-lcellerator_b200", "-Wl,-rpath,$ORIGIN"])
-        out["libcb200_cpmath.so"] = path
+            cuda_inc = os.path.join(os.path.dirname(os.path.dirname(NVCC)), "include")
+            _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(ref, "include"), "-I", cuda_inc,
+                  "-I", os.path.join(ROOT, "include"), "-I", HOST, "-o", path, candidates, "-L", LIB, "-lcellerator_b200",
+                  "-Wl,-rpath,$ORIGIN"])
+        out["libcb200_candidates.so"] = path
         if verbose:
             print("built", path)
     return out

@@ -13,10 +13,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libcellerator_b200.so")
 SYNTH_PATH = os.path.join(HERE, "lib", "libcb200_synth.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
+ALL_ROWS = -1      # cb200_launch.row_end: up to the last row
 
 SUCCESS, INVALID_ARGUMENT, INVALID_SHAPE, UNSUPPORTED, CUDA_ERROR, INTERNAL_ERROR, STALE_STRUCTURE, \
     INSUFFICIENT_WORKSPACE, INVALID_STREAM, SEALED = range(10)
+STALE_VALUE, COMM_NOT_READY, DEVICE_WAIT_TIMEOUT = 10, 11, 12
 
 DTYPE_U8, DTYPE_U4, DTYPE_F16, DTYPE_BF16, DTYPE_F32, DTYPE_F64 = 2, 32, 6, 7, 8, 9
 DECODE_PER_GENE_AFFINE, DECODE_COLUMN_SCALE_ROW_OFFSET = 1, 2
@@ -70,7 +72,9 @@ class SpmmProblem(C.Structure):
                 ("k", C.c_int64), ("n", C.c_int64), ("nnz", C.c_int64), ("bits", C.c_int32), ("policy", C.c_int32),
                 ("dense_dtype", C.c_int32), ("device", C.c_int32), ("structure_epoch", C.c_uint64),
                 ("host_row_ptr", C.c_void_p), ("deterministic", C.c_int32), ("multiply", C.c_int32),
-                ("device_matrix", C.POINTER(QCsr)), ("persistent_limit_bytes", C.c_uint64), ("value_generation", C.c_uint64)]
+                ("device_matrix", C.POINTER(QCsr)), ("persistent_limit_bytes", C.c_uint64), ("value_generation", C.c_uint64),
+                ("schedule_hint", C.c_char_p), ("persistent", C.c_void_p), ("persistent_bytes", C.c_uint64),
+                ("prepare_stream", C.c_void_p)]
 
 
 class Launch(C.Structure):
@@ -145,6 +149,57 @@ class DensePack(C.Structure):
                 ("packed_capacity_bytes", C.c_uint64), ("status_word", C.c_void_p), ("device", C.c_int32)]
 
 
+class FeatureOrderIdentity(C.Structure):
+    _fields_ = [("schema_version", C.c_uint32), ("kind", C.c_uint32), ("feature_count", C.c_uint32),
+                ("feature_axis_identity_version", C.c_uint32), ("feature_axis_identity", C.c_uint64),
+                ("packing_geometry_identity", C.c_uint64)]
+
+
+class ScalarValue(C.Structure):
+    _fields_ = [("type_code", C.c_uint32), ("reserved", C.c_uint32), ("bits", C.c_uint64)]
+
+
+class SpmmRequest(C.Structure):
+    _fields_ = [("schema_version", C.c_uint32), ("operation", C.c_uint32), ("m", C.c_uint64), ("k", C.c_uint64),
+                ("n", C.c_uint64), ("sparse_nnz", C.c_uint64), ("structure_schema_version", C.c_uint32),
+                ("structure_identity_version", C.c_uint32), ("structure_value", C.c_uint64),
+                ("transpose_sparse", C.c_uint32), ("transpose_dense", C.c_uint32), ("dense_rhs_layout", C.c_uint32),
+                ("output_layout", C.c_uint32), ("dense_rhs_leading_dimension", C.c_uint64),
+                ("output_leading_dimension", C.c_uint64), ("sparse_storage_type_code", C.c_uint32),
+                ("dense_storage_type_code", C.c_uint32), ("output_storage_type_code", C.c_uint32),
+                ("compute_type_code", C.c_uint32), ("accumulation_type_code", C.c_uint32), ("alpha", ScalarValue),
+                ("beta", ScalarValue), ("determinism", C.c_uint32), ("workspace_kind", C.c_uint32),
+                ("workspace_reserved", C.c_uint32), ("workspace_byte_limit", C.c_uint64), ("reuse_kind", C.c_uint32),
+                ("reuse_reserved", C.c_uint32), ("reuse_expected_run_count", C.c_uint64), ("epilogue_kind", C.c_uint32),
+                ("epilogue_bias_type_code", C.c_uint32), ("epilogue_bias_element_count", C.c_uint64),
+                ("sparse_feature_order", FeatureOrderIdentity), ("dense_feature_order", FeatureOrderIdentity)]
+
+
+# real::value_* type codes of the request contract (include/Cellerator/types.cuh:150-158)
+TYPE_F16, TYPE_F32, TYPE_F64, TYPE_BF16 = 3, 4, 5, 6
+
+
+class QBellHost(C.Structure):
+    _fields_ = [("rows", C.c_uint32), ("cols", C.c_uint32), ("nnz", C.c_uint32), ("block_size", C.c_uint32),
+                ("ell_cols", C.c_uint32), ("bits", C.c_uint32), ("row_stride_bytes", C.c_uint32),
+                ("decode_policy", C.c_uint32), ("flags", C.c_uint32), ("storage", C.c_void_p),
+                ("block_col_idx", C.c_void_p), ("packed_values", C.c_void_p), ("column_scales", C.c_void_p),
+                ("column_offsets", C.c_void_p), ("row_offsets", C.c_void_p)]
+
+
+class FleetOptions(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device_count", C.c_int32),
+                ("devices", C.POINTER(C.c_int32)), ("streams", C.POINTER(C.c_void_p)), ("enable_peer_access", C.c_int32),
+                ("world_size", C.c_int32), ("world_rank", C.c_int32), ("nccl_unique_id", C.c_void_p),
+                ("nccl_library", C.c_char_p)]
+
+
+class HostStageOptions(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32), ("k", C.c_int64), ("n", C.c_int64),
+                ("bits", C.c_int32), ("policy", C.c_int32), ("dense_dtype", C.c_int32), ("multiply", C.c_int32),
+                ("max_chunk_rows", C.c_int64), ("max_chunk_nnz", C.c_int64), ("chunk_buffers", C.c_int32)]
+
+
 class SessionOptions(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32),
                 ("owned_stream_count", C.c_uint32), ("external_stream_count", C.c_uint32),
@@ -170,6 +225,20 @@ EXPORTED_SYMBOLS = [
     "cb200_public_projection_scratch", "cb200_public_projection_forward", "cb200_public_projection_backward_rhs",
     "cb200_session_create", "cb200_session_reserve_persistent", "cb200_session_reserve_transient",
     "cb200_session_seal", "cb200_session_bind", "cb200_session_synchronize", "cb200_session_destroy",
+    "cb200_find_in_row", "cb200_get_code", "cb200_get_value", "cb200_get_values",
+    "cb200_spmm_persistent_requirement", "cb200_prepared_output_shape", "cb200_prepared_status",
+    "cb200_qcsr_forward_static_status", "cb200_public_projection_status",
+    "cb200_spmm_request_validate", "cb200_spmm_request_classify", "cb200_spmm_request_signature",
+    "cb200_spmm_request_from_problem",
+    "cb200_qbell_pack_aux", "cb200_qbell_unpack_aux", "cb200_qbell_row_bytes", "cb200_qbell_aligned_row_bytes",
+    "cb200_qbell_host_init", "cb200_qbell_host_bytes", "cb200_qbell_host_allocate", "cb200_qbell_host_pin",
+    "cb200_qbell_host_unpin", "cb200_qbell_host_clear", "cb200_qbell_host_view", "cb200_qbell_host_upload",
+    "cb200_fleet_unique_id", "cb200_fleet_create", "cb200_fleet_destroy", "cb200_fleet_slot_count",
+    "cb200_fleet_world_size", "cb200_fleet_device", "cb200_fleet_stream", "cb200_fleet_communicator_ready",
+    "cb200_fleet_request_scratch", "cb200_fleet_synchronize", "cb200_fleet_partition", "cb200_fleet_run_forward",
+    "cb200_fleet_run_transpose", "cb200_fleet_allreduce_sum_f32",
+    "cb200_host_stage_create", "cb200_host_stage_destroy", "cb200_host_stage_device_bytes", "cb200_host_forward",
+    "cb200_test_arm_wait_timeout", "cb200_test_disarm_wait_timeout",
 ]
 
 _lib = None
@@ -216,6 +285,74 @@ def lib() -> C.CDLL:
         L.cb200_spmm_run.argtypes = [C.c_void_p, C.POINTER(Launch)]
         L.cb200_qcsr_forward_static.argtypes = [C.POINTER(QCsr), C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
                                                 C.c_int64, C.c_float, C.c_float, C.c_int32, C.c_void_p]
+        L.cb200_find_in_row.restype = C.c_int64
+        L.cb200_find_in_row.argtypes = [C.POINTER(QCsr), C.c_int64, C.c_int64]
+        L.cb200_get_code.restype = C.c_uint32
+        L.cb200_get_code.argtypes = [C.POINTER(QCsr), C.c_int64, C.c_int64]
+        L.cb200_get_value.restype = C.c_float
+        L.cb200_get_value.argtypes = [C.POINTER(QCsr), C.c_int64, C.c_int64]
+        L.cb200_get_values.argtypes = [C.POINTER(QCsr), C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
+                                       C.c_int32, C.c_void_p]
+        L.cb200_spmm_persistent_requirement.argtypes = [C.POINTER(SpmmProblem), C.POINTER(C.c_uint64)]
+        L.cb200_prepared_output_shape.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        L.cb200_prepared_status.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+        L.cb200_qcsr_forward_static_status.argtypes = [C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]
+        L.cb200_public_projection_status.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]
+        L.cb200_spmm_request_validate.argtypes = [C.POINTER(SpmmRequest)]
+        L.cb200_spmm_request_classify.argtypes = [C.POINTER(SpmmRequest)]
+        L.cb200_spmm_request_signature.argtypes = [C.POINTER(SpmmRequest), C.POINTER(C.c_uint64 * 2)]
+        L.cb200_spmm_request_from_problem.argtypes = [C.POINTER(SpmmProblem), C.POINTER(Launch), C.c_uint64, C.c_uint64,
+                                                      C.POINTER(SpmmRequest)]
+        L.cb200_qbell_pack_aux.restype = C.c_uint64
+        L.cb200_qbell_pack_aux.argtypes = [C.c_uint32, C.c_uint32, C.c_uint64]
+        L.cb200_qbell_unpack_aux.restype = None
+        L.cb200_qbell_unpack_aux.argtypes = [C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint64),
+                                             C.POINTER(C.c_uint32)]
+        L.cb200_qbell_row_bytes.restype = C.c_uint32
+        L.cb200_qbell_row_bytes.argtypes = [C.c_uint32, C.c_uint32]
+        L.cb200_qbell_aligned_row_bytes.restype = C.c_uint32
+        L.cb200_qbell_aligned_row_bytes.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32]
+        L.cb200_qbell_host_init.restype = None
+        L.cb200_qbell_host_init.argtypes = [C.POINTER(QBellHost)] + [C.c_uint32] * 8
+        L.cb200_qbell_host_bytes.restype = C.c_uint64
+        L.cb200_qbell_host_bytes.argtypes = [C.POINTER(QBellHost)]
+        L.cb200_qbell_host_allocate.argtypes = [C.POINTER(QBellHost)]
+        L.cb200_qbell_host_pin.argtypes = [C.POINTER(QBellHost)]
+        L.cb200_qbell_host_unpin.restype = None
+        L.cb200_qbell_host_unpin.argtypes = [C.POINTER(QBellHost)]
+        L.cb200_qbell_host_clear.restype = None
+        L.cb200_qbell_host_clear.argtypes = [C.POINTER(QBellHost)]
+        L.cb200_qbell_host_view.argtypes = [C.POINTER(QBellHost), C.POINTER(QBell)]
+        L.cb200_qbell_host_upload.argtypes = [C.POINTER(QBellHost), C.c_void_p, C.c_uint64, C.c_int32, C.c_void_p,
+                                              C.POINTER(QBell)]
+        L.cb200_fleet_unique_id.argtypes = [C.c_char_p, C.c_void_p]
+        L.cb200_fleet_create.argtypes = [C.POINTER(FleetOptions), C.POINTER(C.c_void_p)]
+        L.cb200_fleet_destroy.restype = None
+        L.cb200_fleet_destroy.argtypes = [C.c_void_p]
+        for name in ("cb200_fleet_slot_count", "cb200_fleet_world_size", "cb200_fleet_communicator_ready"):
+            getattr(L, name).argtypes = [C.c_void_p]
+        L.cb200_fleet_device.argtypes = [C.c_void_p, C.c_uint32]
+        L.cb200_fleet_stream.restype = C.c_void_p
+        L.cb200_fleet_stream.argtypes = [C.c_void_p, C.c_uint32]
+        L.cb200_fleet_request_scratch.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.POINTER(C.c_void_p)]
+        L.cb200_fleet_synchronize.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint32]
+        L.cb200_fleet_partition.argtypes = [C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(CsrBlock)]
+        L.cb200_fleet_run_forward.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint32, C.POINTER(C.c_void_p),
+                                              C.POINTER(Launch)]
+        L.cb200_fleet_run_transpose.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint32, C.POINTER(C.c_void_p),
+                                                C.POINTER(Launch)]
+        L.cb200_fleet_allreduce_sum_f32.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint32, C.POINTER(C.c_void_p),
+                                                    C.POINTER(C.c_void_p), C.c_uint64]
+        L.cb200_host_stage_create.argtypes = [C.POINTER(HostStageOptions), C.POINTER(C.c_void_p)]
+        L.cb200_host_stage_destroy.restype = None
+        L.cb200_host_stage_destroy.argtypes = [C.c_void_p]
+        L.cb200_host_stage_device_bytes.restype = C.c_uint64
+        L.cb200_host_stage_device_bytes.argtypes = [C.c_void_p]
+        L.cb200_host_forward.argtypes = [C.c_void_p, C.POINTER(QCsr), C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                         C.c_float, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        L.cb200_test_arm_wait_timeout.restype = None
+        L.cb200_test_arm_wait_timeout.argtypes = [C.c_uint32]
+        L.cb200_test_disarm_wait_timeout.restype = None
         L.cb200_session_create.argtypes = [C.POINTER(SessionOptions), C.POINTER(C.c_void_p)]
         L.cb200_session_reserve_persistent.argtypes = [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]
         L.cb200_session_reserve_transient.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]

@@ -72,6 +72,9 @@ struct cb200_prepared {
     // ... or, for a transpose that has to be deterministic, the gene-major copy the gather kernel reads
     gene_major_layout gene_major;
     std::uint64_t persistent_bytes;
+    // the device memory all of the above lives in: the caller's block or this operation's own allocations
+    device_arena arena;
+    bool bell_cuda_cores; // Blocked-ELL: the caller asked for the CUDA-core kernel
 };
 
 struct cb200_session {
@@ -101,6 +104,8 @@ const char *cb200_status_string(cb200_status status) {
     case CB200_STATUS_INVALID_STREAM: return "invalid stream";
     case CB200_STATUS_SEALED: return "session sealed";
     case CB200_STATUS_STALE_VALUE: return "stale value generation";
+    case CB200_STATUS_COMM_NOT_READY: return "communicator not ready";
+    case CB200_STATUS_DEVICE_WAIT_TIMEOUT: return "a bounded device wait ran out";
     }
     return "unknown status";
 }
@@ -248,12 +253,35 @@ cb200_status cb200_backend_query(int32_t projection, const cb200_numeric_policy 
     return CB200_STATUS_SUCCESS;
 }
 
+} // extern "C"
+
 /* ---- prepared operation --------------------------------------------------------------- */
 
-cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepared **out) {
-    clear_error();
-    if (out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "prepare needs an output handle");
-    *out = nullptr;
+namespace {
+
+// What prepare will build for a problem, decided from the shape, the mean row length and the caller's
+// request alone (no device query), so that the bytes it needs can be told before the session is sealed.
+struct schedule_plan {
+    cb200_status status = CB200_STATUS_SUCCESS;
+    bool tiled = false;          // CSR forward: gene-tiled kernel (else warp per row)
+    bool tensor_windows = false; // CSR forward: tensor cores fed from the CSR arrays
+    bool blocked = false;        // window-blocked copy (forward or transpose)
+    bool blocked_lo = false;     // ... with the second array of baked words (split products)
+    bool split = false;          // fp32 products rebuilt from bf16 passes
+    bool dense_wanted = false;   // forward: decoded operand tiles instead of entry words, when they fit
+    bool dense_forced = false;   // ... asked for by name: the free-memory rule does not apply
+    bool gene_gather = false;    // transpose with a fixed order of the sums
+    bool row_order = false;      // length-sorted row order for the tiled kernels
+    bool bell_cuda_cores = false;
+    double mean_row_nnz = 0.0;
+};
+
+bool hint_is(const char *hint, const char *name) { return hint != nullptr && std::strcmp(hint, name) == 0; }
+bool hint_starts(const char *hint, const char *prefix) {
+    return hint != nullptr && std::strncmp(hint, prefix, std::strlen(prefix)) == 0;
+}
+
+cb200_status validate_problem(const cb200_spmm_problem *problem) {
     if (!valid_header(problem)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_spmm_problem header");
     if (problem->m < 0 || problem->k < 0 || problem->n < 0 || problem->nnz < 0)
         return fail(CB200_STATUS_INVALID_SHAPE, "negative dimension");
@@ -266,6 +294,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     if (problem->multiply == CB200_DTYPE_BF16 && problem->projection != CB200_PROJECTION_TRANSPOSE &&
         problem->dense_dtype != CB200_DTYPE_BF16)
         return fail(CB200_STATUS_UNSUPPORTED, "bf16 products on a forward projection need a bf16 dense operand");
+    if (problem->persistent != nullptr && (reinterpret_cast<std::uintptr_t>(problem->persistent) & 255u) != 0u)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "persistent memory must be 256-byte aligned");
     if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         if (problem->dense_dtype != CB200_DTYPE_F32) return fail(CB200_STATUS_UNSUPPORTED, "transpose takes fp32 G");
         // a fixed order of the sums needs the gene-major copy, which prepare builds from the matrix
@@ -280,29 +310,200 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
     } else {
         return fail(CB200_STATUS_UNSUPPORTED, "unknown projection %d", problem->projection);
     }
+    if (problem->device_matrix != nullptr && problem->projection != CB200_PROJECTION_BLOCKED_ELL) {
+        const cb200_qcsr &dm = *problem->device_matrix;
+        if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
+            dm.bits != problem->bits || dm.policy != problem->policy)
+            return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
+    }
+    return CB200_STATUS_SUCCESS;
+}
 
+schedule_plan plan_schedule(const cb200_spmm_problem &pr) {
+    schedule_plan plan;
+    const char *hint = (pr.schedule_hint != nullptr && pr.schedule_hint[0] != '\0') ? pr.schedule_hint : nullptr;
+    const std::uint64_t limit = pr.persistent_limit_bytes;
+    const std::uint64_t nnz = static_cast<std::uint64_t>(pr.nnz);
+    plan.mean_row_nnz = pr.m > 0 ? static_cast<double>(pr.nnz) / static_cast<double>(pr.m) : 0.0;
+    if (pr.projection == CB200_PROJECTION_BLOCKED_ELL) {
+        plan.bell_cuda_cores = hint_is(hint, "cuda_cores");
+        return plan;
+    }
+    if (pr.projection == CB200_PROJECTION_TRANSPOSE) {
+        // With the matrix at hand: the tensor-core kernel over the window-blocked copy.  bf16 products
+        // allowed: one pass (decoded values and G rounded to bf16).  fp32 products: three bf16 passes
+        // (hi*hi + hi*lo + lo*hi) rebuild each product to ~3 * 2^-17 relative, inside the 1e-4 bound of
+        // an fp32 G; that is not bit-equal to an fp32 multiply, and callers that need the fp32-FMA kernel
+        // do not hand the matrix to prepare.  The cost follows the dense area, so it needs density.
+        if (pr.deterministic) {
+            plan.gene_gather = true; // same bits on every run: gather gene by gene from a gene-major copy
+            if (limit != 0u && nnz * 5u + static_cast<std::uint64_t>(pr.k + 1) * 12u > limit) {
+                plan.status = fail(CB200_STATUS_UNSUPPORTED, "the gene-major copy of a deterministic transpose exceeds the persistent memory limit");
+            }
+            return plan;
+        }
+        bool blocked = pr.device_matrix != nullptr && qcsr_transpose_blocked_shape_ok(pr.m, pr.k, pr.n, pr.bits);
+        if (hint == nullptr) blocked = blocked && pr.m >= 16 * 256 && plan.mean_row_nnz >= 0.004 * static_cast<double>(pr.k);
+        else blocked = blocked && hint_starts(hint, "tensor_blocked");
+        if (blocked && limit != 0u && nnz * 4u > limit) blocked = false; // a word per entry has to fit under the caller's limit
+        plan.blocked = blocked;
+        plan.split = pr.multiply != CB200_DTYPE_BF16;
+        // decoded values in the entry words, positions of this kernel's gene-major tile; a second array with the
+        // next eight mantissa bits for the split passes when the limit has room
+        plan.blocked_lo = blocked && plan.split && (limit == 0u || nnz * 8u <= limit);
+        return plan;
+    }
+    // CSR forward.  Row schedule from the nnz/row distribution: the gene-tiled kernel pays a fixed cost per
+    // (row, gene tile) visit, so it needs enough stored entries per visit and enough row groups to fill the
+    // SMs; short or few rows go to the warp-per-row kernel.
+    const std::int64_t row_bytes = pr.n * (pr.dense_dtype == CB200_DTYPE_BF16 ? 2 : 4);
+    const bool shape_ok = (pr.n == 32 || pr.n == 64 || pr.n == 128) && row_bytes <= 256;
+    const double tile_genes = row_bytes > 0 ? 98304.0 / static_cast<double>(row_bytes) : 0.0;
+    const double per_visit = pr.k > 0 ? plan.mean_row_nnz * tile_genes / static_cast<double>(pr.k) : 0.0;
+    bool tiled = shape_ok && pr.m >= 16 * 128 && (per_visit >= 6.0 || tile_genes >= pr.k);
+    if (hint_is(hint, "warp_per_row")) tiled = false;
+    if (hint_is(hint, "gene_tiled")) tiled = shape_ok;
+    // bf16 products allowed: the tensor-core kernel, which treats 512-row x 64-gene windows as dense.  That
+    // pays once a window holds enough stored entries (density) and there are row groups for every SM;
+    // otherwise the exact kernels above run (they satisfy the policy too).
+    const bool tensor_ok = pr.multiply == CB200_DTYPE_BF16 && pr.dense_dtype == CB200_DTYPE_BF16 &&
+                           (pr.n == 32 || pr.n == 64 || pr.n == 128) && pr.k > 0;
+    bool tensor = tensor_ok && pr.m >= 512 && plan.mean_row_nnz >= 0.10 * static_cast<double>(pr.k);
+    if (hint != nullptr) tensor = tensor_ok && hint_is(hint, "tensor_windows");
+    if (tensor) tiled = true; // same length-sorted row order
+    // With the device-resident matrix at hand, prepare re-lays it once into the window-blocked copy
+    // (persistent preprocessing) and the tensor-core kernel streams that instead of the CSR arrays.  Its
+    // cost follows the dense area m x k, so it needs a minimum density to pay.  Two ways in: bf16 products
+    // allowed (one pass), or fp32 products requested, which the kernel rebuilds from bf16 pieces in two
+    // (bf16 W) or three (fp32 W) passes: not bit-equal to fp32 multiplies, but inside the 1e-4 bound;
+    // callers that need the fp32-FMA kernel do not hand the matrix to prepare.  Split passes cost 2-3x, so
+    // they need a denser matrix to beat the exact kernel.
+    const bool split = pr.multiply != CB200_DTYPE_BF16;
+    const bool blocked_ok = pr.device_matrix != nullptr && (tensor_ok || split) &&
+                            qcsr_blocked_shape_ok(pr.m, pr.k, pr.n, pr.bits, pr.dense_dtype);
+    const double min_density = !split ? 0.015 : (pr.dense_dtype == CB200_DTYPE_BF16 ? 0.04 : 0.06);
+    bool blocked = blocked_ok && pr.m >= 16 * 256 && plan.mean_row_nnz >= min_density * static_cast<double>(pr.k);
+    if (hint != nullptr) blocked = blocked_ok && (hint_starts(hint, "tensor_blocked") || (!split && hint_is(hint, "tensor_dense")));
+    if (blocked && limit != 0u && nnz * 4u > limit) blocked = false; // a word per entry
+    plan.split = split;
+    plan.blocked = blocked;
+    // the entry words hold the decoded values (no look-up at launch); the split-product schedules get a
+    // second array with the next eight mantissa bits when the limit has room for it
+    plan.blocked_lo = blocked && split && (limit == 0u || nnz * 8u <= limit);
+    if (blocked) {
+        tiled = false; // no length-sorted row order: the copy works in natural row order, and the exact
+        tensor = false; // kernel that serves unaligned row ranges runs in natural order too
+        // Dense enough, bf16 products, and room for rows x genes x 2 bytes: keep the decoded operand tiles
+        // instead of the entry words; a launch then streams them and decodes nothing.
+        const std::uint64_t tile_bytes = qcsr_dense_tile_bytes(pr.m, pr.k);
+        bool dense = !split && plan.mean_row_nnz >= 0.08 * static_cast<double>(pr.k);
+        if (hint != nullptr) dense = !split && hint_is(hint, "tensor_dense");
+        plan.dense_forced = dense && hint != nullptr;
+        if (limit != 0u && tile_bytes > limit) dense = false;
+        plan.dense_wanted = dense;
+    }
+    plan.tiled = tiled;
+    plan.tensor_windows = tensor;
+    // The tiled kernel gives each row to one lane group, so a CTA is as slow as its longest row.  With the
+    // row lengths at hand, order the rows by length once: every CTA then works on rows of nearly equal length.
+    plan.row_order = tiled && pr.host_row_ptr != nullptr && pr.m > 0 && pr.m <= 0x7fffffff;
+    return plan;
+}
+
+std::uint64_t plan_persistent_bytes(const cb200_spmm_problem &pr, const schedule_plan &plan) {
+    std::uint64_t bytes = 0;
+    if (plan.gene_gather) bytes += qcsr_gene_major_layout_bytes_bound(pr.m, pr.k, pr.nnz);
+    if (plan.blocked) bytes += qcsr_blocked_layout_bytes_bound(pr.m, pr.k, pr.nnz, plan.blocked_lo);
+    if (plan.dense_wanted) bytes += device_arena::rounded(qcsr_dense_tile_bytes(pr.m, pr.k));
+    if (plan.row_order) bytes += device_arena::rounded(static_cast<std::uint64_t>(pr.m) * sizeof(std::int32_t));
+    return bytes;
+}
+
+// cudaDeviceGetAttribute answers of a device, asked once (cudaGetDeviceProperties fills dozens of fields
+// and costs milliseconds; the routed public calls prepare on every projection)
+struct device_facts { int major = 0, sm_count = 0; };
+cb200_status facts_of(int device, device_facts *out) {
+    constexpr int kMax = 64;
+    static std::atomic<int> cached_major[kMax], cached_sms[kMax];
+    if (device >= 0 && device < kMax && cached_sms[device].load(std::memory_order_acquire) != 0) {
+        out->major = cached_major[device].load(std::memory_order_relaxed);
+        out->sm_count = cached_sms[device].load(std::memory_order_relaxed);
+        return CB200_STATUS_SUCCESS;
+    }
     int device_count = 0;
     CB200_CUDA_OK(cudaGetDeviceCount(&device_count));
-    if (problem->device < 0 || problem->device >= device_count)
-        return fail(CB200_STATUS_INVALID_STREAM, "device %d not present (%d visible)", problem->device, device_count);
-    cudaDeviceProp prop{};
-    CB200_CUDA_OK(cudaGetDeviceProperties(&prop, problem->device));
-    if (prop.major != 10)
-        return fail(CB200_STATUS_UNSUPPORTED, "this library is built for sm_100a only; device %d is sm_%d%d",
-                    problem->device, prop.major, prop.minor);
+    if (device < 0 || device >= device_count)
+        return fail(CB200_STATUS_INVALID_STREAM, "device %d not present (%d visible)", device, device_count);
+    CB200_CUDA_OK(cudaDeviceGetAttribute(&out->major, cudaDevAttrComputeCapabilityMajor, device));
+    CB200_CUDA_OK(cudaDeviceGetAttribute(&out->sm_count, cudaDevAttrMultiProcessorCount, device));
+    if (device < kMax) {
+        cached_major[device].store(out->major, std::memory_order_relaxed);
+        cached_sms[device].store(out->sm_count, std::memory_order_release);
+    }
+    return CB200_STATUS_SUCCESS;
+}
+
+} // namespace
+
+extern "C" {
+
+cb200_status cb200_spmm_persistent_requirement(const cb200_spmm_problem *problem, uint64_t *bytes) {
+    clear_error();
+    if (bytes == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "persistent_requirement needs an output");
+    *bytes = 0u;
+    const cb200_status valid = validate_problem(problem);
+    if (valid != CB200_STATUS_SUCCESS) return valid;
+    const schedule_plan plan = plan_schedule(*problem);
+    if (plan.status != CB200_STATUS_SUCCESS) return plan.status;
+    *bytes = plan_persistent_bytes(*problem, plan);
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepared **out) {
+    clear_error();
+    if (out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "prepare needs an output handle");
+    *out = nullptr;
+    const cb200_status valid = validate_problem(problem);
+    if (valid != CB200_STATUS_SUCCESS) return valid;
+    const schedule_plan plan = plan_schedule(*problem);
+    if (plan.status != CB200_STATUS_SUCCESS) return plan.status;
+
+    device_facts facts;
+    const cb200_status found = facts_of(problem->device, &facts);
+    if (found != CB200_STATUS_SUCCESS) return found;
+    if (facts.major != 10)
+        return fail(CB200_STATUS_UNSUPPORTED, "this library is built for sm_100a only; device %d has compute capability %d.x",
+                    problem->device, facts.major);
 
     cb200_prepared *p = new (std::nothrow) cb200_prepared{};
     if (p == nullptr) return fail(CB200_STATUS_INTERNAL_ERROR, "out of host memory");
     p->problem = *problem;
     p->problem.host_row_ptr = nullptr; /* borrowed for the analysis below only */
     p->problem.device_matrix = nullptr;
-    p->sm_count = prop.multiProcessorCount;
+    p->problem.schedule_hint = nullptr;
+    p->sm_count = facts.sm_count;
     p->schedule = fwd_schedule::warp_per_row;
     p->schedule_name = "warp_per_row";
     p->workspace_alignment = 256u;
     p->workspace_bytes = 0u;
-    p->mean_row_nnz = problem->m > 0 ? static_cast<double>(problem->nnz) / static_cast<double>(problem->m) : 0.0;
+    p->mean_row_nnz = plan.mean_row_nnz;
     p->max_row_nnz = p->mean_row_nnz;
+    p->bell_cuda_cores = plan.bell_cuda_cores;
+    p->arena.borrowed = problem->persistent != nullptr;
+    p->arena.base = static_cast<unsigned char *>(problem->persistent);
+    p->arena.capacity = problem->persistent != nullptr ? problem->persistent_bytes : 0u;
+    cudaStream_t stream = static_cast<cudaStream_t>(problem->prepare_stream);
+    const auto abandon = [&](cb200_status st) {
+        device_scope scope(problem->device);
+        p->arena.release_all();
+        delete p;
+        return st;
+    };
+    if (p->arena.borrowed && plan_persistent_bytes(*problem, plan) - (plan.dense_wanted ? device_arena::rounded(qcsr_dense_tile_bytes(problem->m, problem->k)) : 0u) >
+                                 p->arena.capacity)
+        return abandon(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "persistent memory of %llu bytes needed (cb200_spmm_persistent_requirement), %llu given",
+                            (unsigned long long)plan_persistent_bytes(*problem, plan), (unsigned long long)p->arena.capacity));
+
     if (problem->host_row_ptr != nullptr && problem->projection != CB200_PROJECTION_BLOCKED_ELL) {
         int64_t longest = 0;
         for (int64_t r = 0; r < problem->m; ++r) {
@@ -311,193 +512,82 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         }
         p->max_row_nnz = static_cast<double>(longest);
     }
+    device_scope scope(problem->device);
+    if (scope.status != cudaSuccess) return abandon(fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status)));
+
     if (problem->projection == CB200_PROJECTION_TRANSPOSE) {
         p->workspace_bytes = qcsr_transpose_workspace_bytes(problem->k, problem->n, p->sm_count);
         p->schedule_name = "vector_reductions";
-        // With the matrix at hand: the tensor-core kernel over the window-blocked copy.  bf16 products
-        // allowed: one pass (decoded values and G rounded to bf16).  fp32 products: three bf16 passes
-        // (hi*hi + hi*lo + lo*hi) rebuild each product to ~3 * 2^-17 relative, inside the 1e-4 bound of
-        // an fp32 G; that is not bit-equal to an fp32 multiply, and callers that need the fp32-FMA kernel
-        // do not hand the matrix to prepare.  The cost follows the dense area, so it needs density.
-        const char *force = std::getenv("CB200_TRANSPOSE_SCHEDULE");
-        bool blocked = problem->device_matrix != nullptr && !problem->deterministic &&
-                       qcsr_transpose_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits);
-        if (problem->deterministic) {
-            // same bits on every run: gather gene by gene from a gene-major copy, sums in a fixed order
-            const cb200_qcsr &dm = *problem->device_matrix;
-            if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
-                dm.bits != problem->bits || dm.policy != problem->policy) {
-                delete p;
-                return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
-            }
-            if (problem->persistent_limit_bytes != 0u &&
-                static_cast<std::uint64_t>(problem->nnz) * 5u + static_cast<std::uint64_t>(problem->k + 1) * 12u >
-                    problem->persistent_limit_bytes) {
-                delete p;
-                return fail(CB200_STATUS_UNSUPPORTED, "the gene-major copy of a deterministic transpose exceeds the persistent memory limit");
-            }
-            device_scope scope(problem->device);
-            cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
-                                                          : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            if (st == CB200_STATUS_SUCCESS) st = build_gene_major_layout(view_of(dm), &p->gene_major);
-            if (st != CB200_STATUS_SUCCESS) {
-                delete p;
-                return st;
-            }
+        if (plan.gene_gather) {
+            const cb200_status st = build_gene_major_layout(view_of(*problem->device_matrix), p->arena, stream, &p->gene_major);
+            if (st != CB200_STATUS_SUCCESS) return abandon(st);
             p->schedule_name = "gene_gather";
             p->workspace_bytes = qcsr_transpose_gather_workspace_bytes();
             p->persistent_bytes += p->gene_major.bytes;
         }
-        if (force == nullptr)
-            blocked = blocked && problem->m >= 16 * 256 && p->mean_row_nnz >= 0.004 * static_cast<double>(problem->k);
-        else
-            blocked = blocked && std::strcmp(force, "tensor_blocked") == 0;
-        // a word per entry has to fit under the caller's limit, as in the forward direction
-        if (blocked && problem->persistent_limit_bytes != 0u &&
-            static_cast<std::uint64_t>(problem->nnz) * 4u > problem->persistent_limit_bytes)
-            blocked = false;
-        if (blocked) {
-            const cb200_qcsr &dm = *problem->device_matrix;
-            if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
-                dm.bits != problem->bits || dm.policy != problem->policy) {
-                delete p;
-                return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
-            }
-            device_scope scope(problem->device);
-            cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
-                                                          : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            // decoded values in the entry words, positions of this kernel's gene-major tile; a second
-            // array with the next eight mantissa bits for the split passes when the limit has room
-            const bool t_split = problem->multiply != CB200_DTYPE_BF16;
-            const std::uint64_t t_limit = problem->persistent_limit_bytes;
-            const bool t_lo = t_split && (t_limit == 0u || static_cast<std::uint64_t>(problem->nnz) * 8u <= t_limit);
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !t_split || t_lo, t_lo, true, &p->blocked);
-            if (st != CB200_STATUS_SUCCESS) {
-                delete p;
-                return st;
-            }
+        if (plan.blocked) {
+            const cb200_status st = build_blocked_layout(view_of(*problem->device_matrix), !plan.split || plan.blocked_lo, plan.blocked_lo,
+                                                         true, p->arena, stream, &p->blocked);
+            if (st != CB200_STATUS_SUCCESS) return abandon(st);
             p->schedule_name = problem->multiply == CB200_DTYPE_BF16 ? "tensor_blocked" : "tensor_blocked_x3";
             p->workspace_bytes = qcsr_transpose_blocked_workspace_bytes(problem->m, problem->n);
             p->persistent_bytes += p->blocked.bytes;
         }
     }
     if (problem->projection == CB200_PROJECTION_BLOCKED_ELL && problem->dense_dtype == CB200_DTYPE_BF16 &&
-        (problem->n == 128 || problem->n == 256)) {
+        (problem->n == 128 || problem->n == 256) && !plan.bell_cuda_cores) {
         // the tensor-core kernel multiplies against W^T: room for that bf16 copy plus a status block
         p->workspace_bytes = qbell_tcgen05_workspace_bytes(problem->k, problem->n);
         p->schedule_name = "tcgen05_block_rows";
+    } else if (problem->projection == CB200_PROJECTION_BLOCKED_ELL) {
+        p->schedule_name = "cuda_cores";
     }
     if (problem->projection == CB200_PROJECTION_CSR) {
-        // Row schedule from the nnz/row distribution: the gene-tiled kernel pays a fixed cost per
-        // (row, gene tile) visit, so it needs enough stored entries per visit and enough row
-        // groups to fill the SMs; short or few rows go to the warp-per-row kernel.
-        const std::int64_t row_bytes = problem->n * (problem->dense_dtype == CB200_DTYPE_BF16 ? 2 : 4);
-        const bool shape_ok = (problem->n == 32 || problem->n == 64 || problem->n == 128) && row_bytes <= 256;
-        const double tile_genes = row_bytes > 0 ? 98304.0 / static_cast<double>(row_bytes) : 0.0;
-        const double per_visit = problem->k > 0 ? p->mean_row_nnz * tile_genes / static_cast<double>(problem->k) : 0.0;
-        const char *force = std::getenv("CB200_FWD_SCHEDULE");
-        bool tiled = shape_ok && problem->m >= 16 * 128 && (per_visit >= 6.0 || tile_genes >= problem->k);
-        if (force != nullptr && std::strcmp(force, "warp_per_row") == 0) tiled = false;
-        if (force != nullptr && std::strcmp(force, "gene_tiled") == 0) tiled = shape_ok;
-        if (tiled) {
+        if (plan.tiled) {
             p->schedule = fwd_schedule::gene_tiled;
             p->schedule_name = "gene_tiled";
         }
-        p->workspace_bytes = 256u; // status word of the tiled kernel
-        // bf16 products allowed: the tensor-core kernel, which treats 512-row x 64-gene windows as
-        // dense.  That pays once a window holds enough stored entries (density) and there are row
-        // groups for every SM; otherwise the exact kernels above run (they satisfy the policy too).
-        const bool tensor_ok = problem->multiply == CB200_DTYPE_BF16 && problem->dense_dtype == CB200_DTYPE_BF16 &&
-                               (problem->n == 32 || problem->n == 64 || problem->n == 128) && problem->k > 0;
-        bool tensor = tensor_ok && problem->m >= 512 && p->mean_row_nnz >= 0.10 * static_cast<double>(problem->k);
-        if (force != nullptr) tensor = tensor_ok && std::strcmp(force, "tensor_windows") == 0;
-        if (tensor) {
-            tiled = true; // same length-sorted row order
+        p->workspace_bytes = qcsr_tiled_workspace_bytes(); // status word of the tiled kernel
+        if (plan.tensor_windows) {
             p->schedule = fwd_schedule::tensor_windows;
             p->schedule_name = "tensor_windows";
             p->workspace_bytes = qcsr_mma_workspace_bytes(problem->k, problem->n);
         }
-        // With the device-resident matrix at hand, prepare re-lays it once into the window-blocked
-        // copy (persistent preprocessing) and the tensor-core kernel streams that instead of the CSR
-        // arrays.  Its cost follows the dense area m x k, so it needs a minimum density to pay.
-        // Two ways in: bf16 products allowed (one pass), or fp32 products requested, which the kernel
-        // rebuilds from bf16 pieces in two (bf16 W) or three (fp32 W) passes: not bit-equal to fp32
-        // multiplies, but inside the 1e-4 bound; callers that need the fp32-FMA kernel do not hand the
-        // matrix to prepare.  Split passes cost 2-3x, so they need a denser matrix to beat the exact kernel.
-        const bool split = problem->multiply != CB200_DTYPE_BF16;
-        const bool blocked_ok = problem->device_matrix != nullptr && (tensor_ok || split) &&
-                                qcsr_blocked_shape_ok(problem->m, problem->k, problem->n, problem->bits, problem->dense_dtype);
-        const double min_density = !split ? 0.015 : (problem->dense_dtype == CB200_DTYPE_BF16 ? 0.04 : 0.06);
-        bool blocked = blocked_ok && problem->m >= 16 * 256 && p->mean_row_nnz >= min_density * static_cast<double>(problem->k);
-        if (force != nullptr)
-            blocked = blocked_ok && (std::strcmp(force, "tensor_blocked") == 0 || (!split && std::strcmp(force, "tensor_dense") == 0));
-        const std::uint64_t limit = problem->persistent_limit_bytes;
-        if (blocked && limit != 0u && static_cast<std::uint64_t>(problem->nnz) * 4u > limit) blocked = false; // a word per entry
-        if (blocked) {
-            const cb200_qcsr &dm = *problem->device_matrix;
-            if (!valid_header(&dm) || dm.rows != problem->m || dm.cols != problem->k || dm.nnz != problem->nnz ||
-                dm.bits != problem->bits || dm.policy != problem->policy) {
-                delete p;
-                return fail(CB200_STATUS_INVALID_SHAPE, "the matrix handed to prepare disagrees with the problem");
-            }
-            device_scope scope(problem->device);
-            cb200_status st = scope.status == cudaSuccess ? CB200_STATUS_SUCCESS
-                                                          : fail(CB200_STATUS_CUDA_ERROR, "%s", cudaGetErrorString(scope.status));
-            // the entry words hold the decoded values (no look-up at launch); the split-product schedules
-            // get a second array with the next eight mantissa bits when the limit has room for it
-            const bool lo_words = split && (limit == 0u || static_cast<std::uint64_t>(problem->nnz) * 8u <= limit);
-            if (st == CB200_STATUS_SUCCESS) st = build_blocked_layout(view_of(dm), !split || lo_words, lo_words, false, &p->blocked);
-            if (st != CB200_STATUS_SUCCESS) {
-                delete p;
-                return st;
-            }
-            tiled = false; // no length-sorted row order: the copy works in natural row order, and the
-                           // exact kernel that serves unaligned row ranges runs in natural order too
+        if (plan.blocked) {
+            const qcsr_view dm = view_of(*problem->device_matrix);
+            cb200_status st = build_blocked_layout(dm, !plan.split || plan.blocked_lo, plan.blocked_lo, false, p->arena, stream, &p->blocked);
+            if (st != CB200_STATUS_SUCCESS) return abandon(st);
             p->schedule = fwd_schedule::tensor_blocked;
-            p->schedule_name = !split ? "tensor_blocked"
-                                      : (problem->dense_dtype == CB200_DTYPE_BF16 ? "tensor_blocked_x2" : "tensor_blocked_x3");
+            p->schedule_name = !plan.split ? "tensor_blocked"
+                                           : (problem->dense_dtype == CB200_DTYPE_BF16 ? "tensor_blocked_x2" : "tensor_blocked_x3");
             p->workspace_bytes = std::max<std::uint64_t>(qcsr_blocked_workspace_bytes(problem->k, problem->n), 256u);
-            // Dense enough, bf16 products, and room for rows x genes x 2 bytes: keep the decoded operand
-            // tiles instead of the entry words; a launch then streams them and decodes nothing.
-            const std::uint64_t tile_bytes = qcsr_dense_tile_bytes(problem->m, problem->k);
-            std::size_t free_bytes = 0, total_bytes = 0;
-            bool dense = !split && p->mean_row_nnz >= 0.08 * static_cast<double>(problem->k) &&
-                         cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess && tile_bytes <= free_bytes / 2u;
-            if (force != nullptr) dense = !split && std::strcmp(force, "tensor_dense") == 0;
-            if (limit != 0u && tile_bytes > limit) dense = false;
+            bool dense = plan.dense_wanted;
+            if (dense && !plan.dense_forced && !p->arena.borrowed) {
+                // own allocations: the tiles may take half of what the device has free, no more
+                std::size_t free_bytes = 0, total_bytes = 0;
+                dense = cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess && qcsr_dense_tile_bytes(problem->m, problem->k) <= free_bytes / 2u;
+            }
             if (dense) {
                 bool built = false;
-                st = densify_blocked_layout(view_of(dm), &p->blocked, &built);
-                if (st != CB200_STATUS_SUCCESS) {
-                    free_blocked_layout(&p->blocked);
-                    delete p;
-                    return st;
-                }
+                st = densify_blocked_layout(dm, &p->blocked, p->arena, stream, &built);
+                if (st != CB200_STATUS_SUCCESS) return abandon(st);
                 if (built) p->schedule_name = "tensor_dense";
             }
             p->persistent_bytes += p->blocked.bytes;
         }
-        // The tiled kernel gives each row to one lane group, so a CTA is as slow as its longest row.
-        // With the row lengths at hand, order the rows by length once (persistent preprocessing):
-        // every CTA then works on rows of nearly equal length.
-        if (tiled && problem->host_row_ptr != nullptr && problem->m > 0 && problem->m <= 0x7fffffff) {
+        if (plan.row_order) {
             std::vector<std::int32_t> order(static_cast<std::size_t>(problem->m));
             for (std::int64_t r = 0; r < problem->m; ++r) order[static_cast<std::size_t>(r)] = static_cast<std::int32_t>(r);
             const std::int64_t *rp = problem->host_row_ptr;
             std::stable_sort(order.begin(), order.end(), [rp](std::int32_t a, std::int32_t b) {
                 return rp[a + 1] - rp[a] > rp[b + 1] - rp[b];
             });
-            device_scope scope(problem->device);
             const std::size_t bytes = order.size() * sizeof(std::int32_t);
-            cudaError_t err = scope.status;
-            if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&p->row_order), bytes);
-            if (err == cudaSuccess) err = cudaMemcpy(p->row_order, order.data(), bytes, cudaMemcpyHostToDevice);
-            if (err != cudaSuccess) {
-                if (p->row_order != nullptr) cudaFree(p->row_order);
-                free_blocked_layout(&p->blocked);
-                delete p;
-                return fail(CB200_STATUS_CUDA_ERROR, "row order upload: %s", cudaGetErrorString(err));
-            }
+            p->row_order = static_cast<std::int32_t *>(p->arena.take(bytes));
+            if (p->row_order == nullptr) return abandon(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "no device memory for the row order"));
+            cudaError_t err = cudaMemcpyAsync(p->row_order, order.data(), bytes, cudaMemcpyHostToDevice, stream);
+            if (err == cudaSuccess) err = cudaStreamSynchronize(stream); // `order` leaves scope
+            if (err != cudaSuccess) return abandon(fail(CB200_STATUS_CUDA_ERROR, "row order upload: %s", cudaGetErrorString(err)));
             p->persistent_bytes += bytes;
         }
     }
@@ -507,12 +597,9 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
 
 void cb200_prepared_destroy(cb200_prepared *prepared) {
     if (prepared == nullptr) return;
-    if (prepared->row_order != nullptr || prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr ||
-        prepared->gene_major.col_ptr != nullptr) {
+    if (prepared->arena.owned_count != 0) {
         device_scope scope(prepared->problem.device);
-        if (prepared->row_order != nullptr) cudaFree(prepared->row_order);
-        free_blocked_layout(&prepared->blocked);
-        free_gene_major_layout(&prepared->gene_major);
+        prepared->arena.release_all();
     }
     delete prepared;
 }
@@ -531,6 +618,15 @@ const char *cb200_prepared_schedule(const cb200_prepared *prepared) {
 
 uint64_t cb200_prepared_persistent_bytes(const cb200_prepared *prepared) {
     return prepared != nullptr ? prepared->persistent_bytes : 0u;
+}
+
+cb200_status cb200_prepared_output_shape(const cb200_prepared *prepared, uint64_t *rows, uint64_t *columns) {
+    clear_error();
+    if (prepared == nullptr || rows == nullptr || columns == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "output_shape needs a prepared operation and outputs");
+    const cb200_spmm_problem &pr = prepared->problem;
+    *rows = static_cast<uint64_t>(pr.projection == CB200_PROJECTION_TRANSPOSE ? pr.k : pr.m);
+    *columns = static_cast<uint64_t>(pr.n);
+    return CB200_STATUS_SUCCESS;
 }
 
 cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch) {
@@ -584,7 +680,7 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     CB200_CUDA_OK(scope.status);
 
     int64_t row_begin = launch->row_begin, row_end = launch->row_end;
-    if (row_begin == 0 && row_end == 0) row_end = pr.m;
+    if (row_end == CB200_ALL_ROWS) row_end = pr.m;
     if (row_begin < 0 || row_end > pr.m || row_begin > row_end)
         return fail(CB200_STATUS_INVALID_SHAPE, "row range [%lld,%lld) outside 0..%lld", (long long)row_begin,
                     (long long)row_end, (long long)pr.m);
@@ -597,7 +693,7 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
         if (b.block_col_idx == nullptr || b.packed_values == nullptr)
             return fail(CB200_STATUS_INVALID_ARGUMENT, "Blocked-ELL matrix has null arrays");
         return launch_qbell_forward(view_of(b), d, row_begin, row_end, launch->workspace, launch->workspace_bytes,
-                                    prepared->sm_count, stream);
+                                    prepared->sm_count, prepared->bell_cuda_cores, stream);
     }
     if (!valid_header(launch->csr)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
     const cb200_qcsr &x = *launch->csr;
@@ -614,6 +710,22 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
     return launch_qcsr_forward(view_of(x), d, row_begin, row_end, prepared->schedule, prepared->row_order, &prepared->blocked,
                                pr.multiply != CB200_DTYPE_BF16, launch->workspace, launch->workspace_bytes, prepared->sm_count,
                                stream);
+}
+
+cb200_status cb200_prepared_status(const cb200_prepared *prepared, const void *workspace, void *stream, int32_t *host_word) {
+    clear_error();
+    if (prepared == nullptr || host_word == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "status needs a prepared operation and an output");
+    *host_word = 0;
+    if (prepared->workspace_bytes == 0u) return CB200_STATUS_SUCCESS; // this schedule waits on nothing
+    if (workspace == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "status needs the workspace of the launch");
+    device_scope scope(prepared->problem.device);
+    CB200_CUDA_OK(scope.status);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CB200_CUDA_OK(cudaMemcpyAsync(host_word, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CB200_CUDA_OK(cudaStreamSynchronize(s));
+    if (*host_word != 0)
+        return fail(CB200_STATUS_DEVICE_WAIT_TIMEOUT, "a kernel of the last launch gave up a bounded wait (status word %d): its output is not valid", *host_word);
+    return CB200_STATUS_SUCCESS;
 }
 
 /* ---- session ------------------------------------------------------------------------------ */

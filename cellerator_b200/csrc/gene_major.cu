@@ -452,56 +452,59 @@ cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, s
     return CB200_STATUS_SUCCESS;
 }
 
-cb200_status build_gene_major_layout(const qcsr_view &x, gene_major_layout *out) {
+std::uint64_t qcsr_gene_major_layout_bytes_bound(std::int64_t rows, std::int64_t cols, std::int64_t nnz) {
+    const std::uint64_t entries = static_cast<std::uint64_t>(std::max<std::int64_t>(nnz, 1));
+    return device_arena::rounded(qcsr_gene_major_workspace_bytes(rows, cols)) + device_arena::rounded(static_cast<std::uint64_t>(cols + 1) * 8u) +
+           device_arena::rounded(entries * 4u) + device_arena::rounded(entries) + device_arena::rounded(static_cast<std::uint64_t>(cols) * 4u);
+}
+
+cb200_status build_gene_major_layout(const qcsr_view &x, device_arena &arena, cudaStream_t stream, gene_major_layout *out) {
     *out = gene_major_layout{};
     if (!qcsr_gene_major_shape_ok(x.rows, x.cols, x.bits)) return fail(CB200_STATUS_UNSUPPORTED, "shape outside the gene-major copy");
     const std::uint64_t ws_bytes = qcsr_gene_major_workspace_bytes(x.rows, x.cols);
-    void *ws = nullptr;
     const std::size_t ptr_bytes = static_cast<std::size_t>(x.cols + 1) * 8u;
     const std::size_t idx_bytes = static_cast<std::size_t>(std::max<std::int64_t>(x.nnz, 1)) * 4u;
     const std::size_t code_bytes = static_cast<std::size_t>(std::max<std::int64_t>(x.nnz, 1));
-    cudaError_t err = cudaMalloc(&ws, ws_bytes);
-    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->col_ptr), ptr_bytes);
-    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->row_idx), idx_bytes);
-    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->codes), code_bytes);
-    cb200_status st = err == cudaSuccess ? CB200_STATUS_SUCCESS : fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err));
-    int status = 0;
-    if (st == CB200_STATUS_SUCCESS) st = launch_qcsr_gene_major(x, out->col_ptr, out->row_idx, out->codes, ws, ws_bytes, nullptr);
-    if (st == CB200_STATUS_SUCCESS) {
-        err = cudaMemcpy(&status, ws, sizeof(int), cudaMemcpyDeviceToHost); // synchronises
-        if (err != cudaSuccess) st = fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err));
-        else if (status != 0) st = fail(CB200_STATUS_INVALID_SHAPE, "a column index lies outside the matrix");
-    }
-    if (ws != nullptr) cudaFree(ws);
-    // genes by descending entry count: a gene is one CTA's work, so the long ones have to start first
-    if (st == CB200_STATUS_SUCCESS) {
-        std::vector<std::int64_t> ptr(static_cast<std::size_t>(x.cols) + 1u);
-        std::vector<std::int32_t> order(static_cast<std::size_t>(x.cols));
-        err = cudaMemcpy(ptr.data(), out->col_ptr, ptr_bytes, cudaMemcpyDeviceToHost);
-        for (std::int64_t c = 0; c < x.cols; ++c) order[static_cast<std::size_t>(c)] = static_cast<std::int32_t>(c);
-        std::stable_sort(order.begin(), order.end(), [&](std::int32_t a, std::int32_t b) {
-            return ptr[static_cast<std::size_t>(a) + 1u] - ptr[static_cast<std::size_t>(a)] >
-                   ptr[static_cast<std::size_t>(b) + 1u] - ptr[static_cast<std::size_t>(b)];
-        });
-        if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->gene_order), order.size() * sizeof(std::int32_t));
-        if (err == cudaSuccess) err = cudaMemcpy(out->gene_order, order.data(), order.size() * sizeof(std::int32_t), cudaMemcpyHostToDevice);
-        if (err != cudaSuccess) st = fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err));
-    }
-    if (st != CB200_STATUS_SUCCESS) {
-        free_gene_major_layout(out);
+    const std::size_t order_bytes = static_cast<std::size_t>(std::max<std::int64_t>(x.cols, 1)) * sizeof(std::int32_t);
+    void *ws = arena.take(ws_bytes);
+    out->col_ptr = static_cast<std::int64_t *>(arena.take(ptr_bytes));
+    out->row_idx = static_cast<std::int32_t *>(arena.take(idx_bytes));
+    out->codes = static_cast<std::uint8_t *>(arena.take(code_bytes));
+    out->gene_order = static_cast<std::int32_t *>(arena.take(order_bytes));
+    const auto give_up = [&](cb200_status st) {
+        arena.give_back(out->gene_order, order_bytes);
+        arena.give_back(out->codes, code_bytes);
+        arena.give_back(out->row_idx, idx_bytes);
+        arena.give_back(out->col_ptr, ptr_bytes);
+        arena.give_back(ws, ws_bytes);
+        *out = gene_major_layout{};
         return st;
-    }
+    };
+    if (ws == nullptr || out->col_ptr == nullptr || out->row_idx == nullptr || out->codes == nullptr || out->gene_order == nullptr)
+        return give_up(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "no device memory for the gene-major copy"));
+    cb200_status st = launch_qcsr_gene_major(x, out->col_ptr, out->row_idx, out->codes, ws, ws_bytes, stream);
+    if (st != CB200_STATUS_SUCCESS) return give_up(st);
+    int status = 0;
+    std::vector<std::int64_t> ptr(static_cast<std::size_t>(x.cols) + 1u);
+    cudaError_t err = cudaMemcpyAsync(&status, ws, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(ptr.data(), out->col_ptr, ptr_bytes, cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) return give_up(fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err)));
+    if (status != 0) return give_up(fail(CB200_STATUS_INVALID_SHAPE, "a column index lies outside the matrix"));
+    // genes by descending entry count: a gene is one CTA's work, so the long ones have to start first
+    std::vector<std::int32_t> order(static_cast<std::size_t>(x.cols));
+    for (std::int64_t c = 0; c < x.cols; ++c) order[static_cast<std::size_t>(c)] = static_cast<std::int32_t>(c);
+    std::stable_sort(order.begin(), order.end(), [&](std::int32_t a, std::int32_t b) {
+        return ptr[static_cast<std::size_t>(a) + 1u] - ptr[static_cast<std::size_t>(a)] >
+               ptr[static_cast<std::size_t>(b) + 1u] - ptr[static_cast<std::size_t>(b)];
+    });
+    err = cudaMemcpyAsync(out->gene_order, order.data(), order.size() * sizeof(std::int32_t), cudaMemcpyHostToDevice, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) return give_up(fail(CB200_STATUS_CUDA_ERROR, "gene-major copy: %s", cudaGetErrorString(err)));
+    arena.give_back(ws, ws_bytes);
     out->bytes = ptr_bytes + idx_bytes + code_bytes + static_cast<std::size_t>(x.cols) * sizeof(std::int32_t);
     out->src_row_ptr = x.row_ptr; out->src_col_idx = x.col_idx; out->src_packed = x.packed;
     return CB200_STATUS_SUCCESS;
-}
-
-void free_gene_major_layout(gene_major_layout *layout) {
-    if (layout->col_ptr != nullptr) cudaFree(layout->col_ptr);
-    if (layout->row_idx != nullptr) cudaFree(layout->row_idx);
-    if (layout->codes != nullptr) cudaFree(layout->codes);
-    if (layout->gene_order != nullptr) cudaFree(layout->gene_order);
-    *layout = gene_major_layout{};
 }
 
 bool qcsr_transpose_gather_shape_ok(std::int64_t n) { return n == 32 || n == 64 || n == 128; }

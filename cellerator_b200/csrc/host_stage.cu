@@ -1,0 +1,263 @@
+// Forward projection of a quantized CSR matrix that lives in HOST memory: the row range is cut into
+// chunks that travel host -> device -> host through a small ring of device buffers, so that the copy
+// in, the multiply and the copy out of neighbouring chunks overlap and the device never holds more
+// than `chunk_buffers` chunks.  The reference's callers do the same by hand before every projection
+// (operands are copied in, the projection runs, the result is copied out: src/abi/abi.cu:278-340);
+// here it is one call of the C ABI.
+//
+// Streams: one for host -> device copies, one for the kernels, one for device -> host copies, tied by
+// events per ring buffer.  A chunk's row pointers arrive with their absolute offsets and are rebased on
+// the device (one small kernel), so the chunk is a matrix of its own for the projection kernel.  The
+// kernels are the CSR schedules that read codes and indices at launch (gene-tiled where the shape allows,
+// else warp per row): the values arrive with the call, so nothing prepared from them can be used.
+#include "kernels.cuh"
+
+#include <algorithm>
+#include <cstring>
+#include <new>
+#include <vector>
+
+using namespace cb200;
+
+namespace {
+
+constexpr int kMaxBuffers = 4;
+
+__global__ void __launch_bounds__(256) rebase_kernel(std::int64_t *ptr, std::int64_t count, std::int64_t base) {
+    const std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) ptr[i] -= base;
+}
+
+struct chunk_buffer {
+    std::int64_t *row_ptr = nullptr;
+    std::int64_t *packed_row_ptr = nullptr; // 4-bit codes only
+    std::int32_t *col_idx = nullptr;
+    std::uint8_t *packed = nullptr;
+    float *row_offsets = nullptr;           // row-offset policy only
+    float *y = nullptr;
+    void *workspace = nullptr;
+    cudaEvent_t copied_in = nullptr, computed = nullptr, copied_out = nullptr;
+};
+
+} // namespace
+
+struct cb200_host_stage {
+    cb200_host_stage_options o{};
+    int sm_count = 0;
+    fwd_schedule schedule = fwd_schedule::warp_per_row;
+    cudaStream_t h2d = nullptr, compute = nullptr, d2h = nullptr;
+    void *w = nullptr;
+    float *scales = nullptr, *offsets = nullptr;
+    cudaEvent_t shared_in = nullptr;
+    chunk_buffer ring[kMaxBuffers];
+    std::uint64_t device_bytes = 0;
+    std::uint64_t workspace_bytes = 0;
+};
+
+namespace {
+
+template<typename T>
+cudaError_t device_alloc(T **p, std::uint64_t count, std::uint64_t *total) {
+    const std::uint64_t bytes = std::max<std::uint64_t>(count, 1u) * sizeof(T);
+    *total += bytes;
+    return cudaMalloc(reinterpret_cast<void **>(p), bytes);
+}
+
+} // namespace
+
+extern "C" {
+
+void cb200_host_stage_destroy(cb200_host_stage *s) {
+    if (s == nullptr) return;
+    device_scope scope(s->o.device);
+    for (cudaStream_t st : {s->h2d, s->compute, s->d2h})
+        if (st != nullptr) cudaStreamSynchronize(st);
+    for (chunk_buffer &b : s->ring) {
+        cudaFree(b.row_ptr); cudaFree(b.packed_row_ptr); cudaFree(b.col_idx); cudaFree(b.packed);
+        cudaFree(b.row_offsets); cudaFree(b.y); cudaFree(b.workspace);
+        for (cudaEvent_t e : {b.copied_in, b.computed, b.copied_out})
+            if (e != nullptr) cudaEventDestroy(e);
+    }
+    cudaFree(s->w); cudaFree(s->scales); cudaFree(s->offsets);
+    if (s->shared_in != nullptr) cudaEventDestroy(s->shared_in);
+    for (cudaStream_t st : {s->h2d, s->compute, s->d2h})
+        if (st != nullptr) cudaStreamDestroy(st);
+    delete s;
+}
+
+cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_host_stage **out) {
+    clear_error();
+    if (out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "host_stage_create needs an output handle");
+    *out = nullptr;
+    if (o == nullptr || o->version != CB200_ABI_VERSION || o->size < sizeof(cb200_host_stage_options))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_host_stage_options header");
+    if (o->k <= 0 || o->n <= 0 || o->max_chunk_rows <= 0 || o->max_chunk_nnz <= 0 || o->max_chunk_rows > 0x7fffffffll)
+        return fail(CB200_STATUS_INVALID_SHAPE, "a stage needs positive k, n and chunk capacities");
+    if (o->bits != 8 && o->bits != 4) return fail(CB200_STATUS_UNSUPPORTED, "bits must be 4 or 8, got %d", o->bits);
+    if (o->policy != CB200_DECODE_PER_GENE_AFFINE && o->policy != CB200_DECODE_COLUMN_SCALE_ROW_OFFSET)
+        return fail(CB200_STATUS_UNSUPPORTED, "unknown decode policy %d", o->policy);
+    if (o->dense_dtype != CB200_DTYPE_F32 && o->dense_dtype != CB200_DTYPE_BF16) return fail(CB200_STATUS_UNSUPPORTED, "W must be fp32 or bf16");
+    if (o->chunk_buffers < 2 || o->chunk_buffers > kMaxBuffers) return fail(CB200_STATUS_INVALID_ARGUMENT, "2..%d chunk buffers", kMaxBuffers);
+    int visible = 0, major = 0;
+    CB200_CUDA_OK(cudaGetDeviceCount(&visible));
+    if (o->device < 0 || o->device >= visible) return fail(CB200_STATUS_INVALID_STREAM, "device %d not present (%d visible)", o->device, visible);
+    CB200_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, o->device));
+    if (major != 10) return fail(CB200_STATUS_UNSUPPORTED, "this library is built for sm_100a only");
+    device_scope scope(o->device);
+    CB200_CUDA_OK(scope.status);
+    cb200_host_stage *s = new (std::nothrow) cb200_host_stage{};
+    if (s == nullptr) return fail(CB200_STATUS_INTERNAL_ERROR, "out of host memory");
+    s->o = *o;
+    cudaError_t err = cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, o->device);
+    const std::uint64_t elem = o->dense_dtype == CB200_DTYPE_BF16 ? 2u : 4u;
+    // the gene-tiled kernel where the shape allows it (its fixed cost per visit needs rows of some length,
+    // which a chunk of a single-cell matrix has); else one warp per row
+    const std::int64_t row_bytes = o->n * static_cast<std::int64_t>(elem);
+    const bool tiled_shape = (o->n == 32 || o->n == 64 || o->n == 128) && row_bytes <= 256;
+    const double mean = static_cast<double>(o->max_chunk_nnz) / static_cast<double>(o->max_chunk_rows);
+    const double per_visit = mean * (98304.0 / static_cast<double>(row_bytes)) / static_cast<double>(o->k);
+    s->schedule = tiled_shape && per_visit >= 6.0 ? fwd_schedule::gene_tiled : fwd_schedule::warp_per_row;
+    s->workspace_bytes = qcsr_tiled_workspace_bytes();
+    for (cudaStream_t *st : {&s->h2d, &s->compute, &s->d2h})
+        if (err == cudaSuccess) err = cudaStreamCreateWithFlags(st, cudaStreamNonBlocking);
+    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&s->shared_in, cudaEventDisableTiming);
+    unsigned char *w_bytes = nullptr;
+    if (err == cudaSuccess) err = device_alloc(&w_bytes, static_cast<std::uint64_t>(o->k) * o->n * elem, &s->device_bytes);
+    s->w = w_bytes;
+    if (err == cudaSuccess) err = device_alloc(&s->scales, o->k, &s->device_bytes);
+    if (err == cudaSuccess && o->policy == CB200_DECODE_PER_GENE_AFFINE) err = device_alloc(&s->offsets, o->k, &s->device_bytes);
+    for (int b = 0; b < o->chunk_buffers && err == cudaSuccess; ++b) {
+        chunk_buffer &c = s->ring[b];
+        err = device_alloc(&c.row_ptr, o->max_chunk_rows + 1, &s->device_bytes);
+        if (err == cudaSuccess && o->bits == 4) err = device_alloc(&c.packed_row_ptr, o->max_chunk_rows + 1, &s->device_bytes);
+        if (err == cudaSuccess) err = device_alloc(&c.col_idx, o->max_chunk_nnz, &s->device_bytes);
+        // 4-bit rows are padded to whole bytes: at most one byte per row on top of nnz / 2
+        const std::uint64_t code_bytes = o->bits == 8 ? static_cast<std::uint64_t>(o->max_chunk_nnz)
+                                                      : static_cast<std::uint64_t>(o->max_chunk_nnz) / 2u + static_cast<std::uint64_t>(o->max_chunk_rows);
+        if (err == cudaSuccess) err = device_alloc(&c.packed, code_bytes + 16u, &s->device_bytes);
+        if (err == cudaSuccess && o->policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET) err = device_alloc(&c.row_offsets, o->max_chunk_rows, &s->device_bytes);
+        if (err == cudaSuccess) err = device_alloc(&c.y, static_cast<std::uint64_t>(o->max_chunk_rows) * o->n, &s->device_bytes);
+        unsigned char *ws = nullptr;
+        if (err == cudaSuccess) err = device_alloc(&ws, s->workspace_bytes, &s->device_bytes);
+        c.workspace = ws;
+        for (cudaEvent_t *e : {&c.copied_in, &c.computed, &c.copied_out})
+            if (err == cudaSuccess) err = cudaEventCreateWithFlags(e, cudaEventDisableTiming);
+    }
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        cb200_host_stage_destroy(s);
+        return fail(CB200_STATUS_CUDA_ERROR, "host stage: %s", cudaGetErrorString(err));
+    }
+    *out = s;
+    return CB200_STATUS_SUCCESS;
+}
+
+uint64_t cb200_host_stage_device_bytes(const cb200_host_stage *s) { return s != nullptr ? s->device_bytes : 0u; }
+
+cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const void *w, int64_t w_ld, float *y, int64_t y_ld,
+                                float alpha, uint64_t *h2d_bytes, uint64_t *d2h_bytes) {
+    clear_error();
+    if (s == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "null host stage");
+    if (x == nullptr || x->version != CB200_ABI_VERSION || x->size < sizeof(cb200_qcsr)) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cb200_qcsr header");
+    const cb200_host_stage_options &o = s->o;
+    if (x->cols != o.k || x->bits != o.bits || x->policy != o.policy) return fail(CB200_STATUS_INVALID_SHAPE, "the matrix disagrees with the stage");
+    if (x->rows < 0 || w_ld != o.n || y_ld < o.n) return fail(CB200_STATUS_INVALID_SHAPE, "W must be contiguous (ld == n) and y_ld >= n");
+    if (x->row_ptr == nullptr || w == nullptr || (x->rows != 0 && y == nullptr) || x->scales == nullptr ||
+        (x->nnz != 0 && (x->col_idx == nullptr || x->packed_values == nullptr)) || (o.bits == 4 && x->packed_row_ptr == nullptr))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "the host matrix has null arrays (scales are required; 4-bit codes need packed_row_ptr)");
+    const bool row_policy = o.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+    const std::int64_t *rp = x->row_ptr;
+    const std::int64_t *prp = o.bits == 8 ? x->row_ptr : x->packed_row_ptr;
+    // chunk plan: as many rows as fit the buffers, at least one
+    std::vector<std::int64_t> bounds{0};
+    for (std::int64_t r = 0; r < x->rows;) {
+        std::int64_t hi = std::min<std::int64_t>(x->rows, r + o.max_chunk_rows);
+        // largest end with rp[end] - rp[r] <= max_chunk_nnz (row pointers ascend)
+        const std::int64_t *cut = std::upper_bound(rp + r, rp + hi + 1, rp[r] + o.max_chunk_nnz);
+        hi = std::min<std::int64_t>(hi, static_cast<std::int64_t>(cut - rp) - 1);
+        if (hi <= r) return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "row %lld holds %lld entries, a chunk buffer %lld", (long long)r,
+                                 (long long)(rp[r + 1] - rp[r]), (long long)o.max_chunk_nnz);
+        bounds.push_back(hi);
+        r = hi;
+    }
+    device_scope scope(o.device);
+    CB200_CUDA_OK(scope.status);
+    const std::uint64_t elem = o.dense_dtype == CB200_DTYPE_BF16 ? 2u : 4u;
+    std::uint64_t in_bytes = 0, out_bytes = 0;
+    // operands every chunk shares
+    const std::uint64_t w_bytes = static_cast<std::uint64_t>(o.k) * o.n * elem;
+    CB200_CUDA_OK(cudaMemcpyAsync(s->w, w, w_bytes, cudaMemcpyHostToDevice, s->h2d));
+    CB200_CUDA_OK(cudaMemcpyAsync(s->scales, x->scales, static_cast<std::uint64_t>(o.k) * 4u, cudaMemcpyHostToDevice, s->h2d));
+    in_bytes += w_bytes + static_cast<std::uint64_t>(o.k) * 4u;
+    if (!row_policy && x->offsets != nullptr) {
+        CB200_CUDA_OK(cudaMemcpyAsync(s->offsets, x->offsets, static_cast<std::uint64_t>(o.k) * 4u, cudaMemcpyHostToDevice, s->h2d));
+        in_bytes += static_cast<std::uint64_t>(o.k) * 4u;
+    }
+    CB200_CUDA_OK(cudaEventRecord(s->shared_in, s->h2d));
+    CB200_CUDA_OK(cudaStreamWaitEvent(s->compute, s->shared_in, 0));
+
+    const int buffers = o.chunk_buffers;
+    for (std::size_t c = 0; c + 1 < bounds.size(); ++c) {
+        chunk_buffer &b = s->ring[c % static_cast<std::size_t>(buffers)];
+        const std::int64_t r0 = bounds[c], r1 = bounds[c + 1], rows = r1 - r0;
+        const std::int64_t n0 = rp[r0], nnz = rp[r1] - n0, p0 = prp[r0], code_bytes = prp[r1] - p0;
+        // ---- in: one copy per array, once the buffer's previous chunk has been multiplied
+        if (c >= static_cast<std::size_t>(buffers)) CB200_CUDA_OK(cudaStreamWaitEvent(s->h2d, b.computed, 0));
+        CB200_CUDA_OK(cudaMemcpyAsync(b.row_ptr, rp + r0, static_cast<std::uint64_t>(rows + 1) * 8u, cudaMemcpyHostToDevice, s->h2d));
+        in_bytes += static_cast<std::uint64_t>(rows + 1) * 8u;
+        if (o.bits == 4) {
+            CB200_CUDA_OK(cudaMemcpyAsync(b.packed_row_ptr, prp + r0, static_cast<std::uint64_t>(rows + 1) * 8u, cudaMemcpyHostToDevice, s->h2d));
+            in_bytes += static_cast<std::uint64_t>(rows + 1) * 8u;
+        }
+        if (nnz > 0) {
+            CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx, x->col_idx + n0, static_cast<std::uint64_t>(nnz) * 4u, cudaMemcpyHostToDevice, s->h2d));
+            CB200_CUDA_OK(cudaMemcpyAsync(b.packed, x->packed_values + p0, static_cast<std::uint64_t>(code_bytes), cudaMemcpyHostToDevice, s->h2d));
+            in_bytes += static_cast<std::uint64_t>(nnz) * 4u + static_cast<std::uint64_t>(code_bytes);
+        }
+        if (row_policy && x->offsets != nullptr) {
+            CB200_CUDA_OK(cudaMemcpyAsync(b.row_offsets, x->offsets + r0, static_cast<std::uint64_t>(rows) * 4u, cudaMemcpyHostToDevice, s->h2d));
+            in_bytes += static_cast<std::uint64_t>(rows) * 4u;
+        }
+        CB200_CUDA_OK(cudaEventRecord(b.copied_in, s->h2d));
+        // ---- multiply, once the chunk is in and the buffer's previous result is out
+        CB200_CUDA_OK(cudaStreamWaitEvent(s->compute, b.copied_in, 0));
+        if (c >= static_cast<std::size_t>(buffers)) CB200_CUDA_OK(cudaStreamWaitEvent(s->compute, b.copied_out, 0));
+        const unsigned grid = static_cast<unsigned>((rows + 1 + 255) / 256);
+        rebase_kernel<<<grid, 256, 0, s->compute>>>(b.row_ptr, rows + 1, n0);
+        if (o.bits == 4) rebase_kernel<<<grid, 256, 0, s->compute>>>(b.packed_row_ptr, rows + 1, p0);
+        count_launch(o.bits == 4 ? 2 : 1);
+        CB200_CUDA_OK(cudaGetLastError());
+        const qcsr_view view{rows, o.k, nnz, o.bits, o.policy, b.row_ptr, o.bits == 4 ? b.packed_row_ptr : nullptr, b.col_idx, b.packed,
+                             s->scales, row_policy ? (x->offsets != nullptr ? b.row_offsets : nullptr) : (x->offsets != nullptr ? s->offsets : nullptr)};
+        const dense_args d{s->w, o.n, o.dense_dtype, b.y, o.n, o.n, alpha, 0.0f};
+        const cb200_status st = launch_qcsr_forward(view, d, 0, rows, s->schedule, nullptr, nullptr, false, b.workspace, s->workspace_bytes,
+                                                    s->sm_count, s->compute);
+        if (st != CB200_STATUS_SUCCESS) return st;
+        CB200_CUDA_OK(cudaEventRecord(b.computed, s->compute));
+        // ---- out
+        CB200_CUDA_OK(cudaStreamWaitEvent(s->d2h, b.computed, 0));
+        if (y_ld == o.n) {
+            CB200_CUDA_OK(cudaMemcpyAsync(y + r0 * y_ld, b.y, static_cast<std::uint64_t>(rows) * o.n * 4u, cudaMemcpyDeviceToHost, s->d2h));
+        } else {
+            CB200_CUDA_OK(cudaMemcpy2DAsync(y + r0 * y_ld, static_cast<std::size_t>(y_ld) * 4u, b.y, static_cast<std::size_t>(o.n) * 4u,
+                                            static_cast<std::size_t>(o.n) * 4u, static_cast<std::size_t>(rows), cudaMemcpyDeviceToHost, s->d2h));
+        }
+        out_bytes += static_cast<std::uint64_t>(rows) * o.n * 4u;
+        CB200_CUDA_OK(cudaEventRecord(b.copied_out, s->d2h));
+    }
+    CB200_CUDA_OK(cudaStreamSynchronize(s->d2h));
+    CB200_CUDA_OK(cudaStreamSynchronize(s->compute));
+    CB200_CUDA_OK(cudaStreamSynchronize(s->h2d));
+    // the kernels' bounded waits: a status word per ring buffer, all of them zero unless a wait ran out
+    const std::size_t used = std::min<std::size_t>(bounds.size() - 1u, static_cast<std::size_t>(buffers));
+    for (std::size_t b = 0; b < used; ++b) {
+        int word = 0;
+        CB200_CUDA_OK(cudaMemcpy(&word, s->ring[b].workspace, sizeof(int), cudaMemcpyDeviceToHost));
+        if (word != 0) return fail(CB200_STATUS_DEVICE_WAIT_TIMEOUT, "a kernel of the call gave up a bounded wait: y is not valid");
+    }
+    if (h2d_bytes != nullptr) *h2d_bytes = in_bytes;
+    if (d2h_bytes != nullptr) *d2h_bytes = out_bytes;
+    return CB200_STATUS_SUCCESS;
+}
+
+} // extern "C"

@@ -31,9 +31,60 @@ struct dense_args {
 
 enum class fwd_schedule : int { warp_per_row = 0, gene_tiled = 1, tensor_windows = 2, tensor_blocked = 3 };
 
+// Device memory a prepared operation keeps.  Two modes: pieces carved out of a block the caller owns (a
+// session's persistent reservation: nothing is allocated or freed here), or pieces allocated one by one
+// with cudaMalloc and freed when the operation is destroyed.  Pieces are 256-byte aligned.
+struct device_arena {
+    unsigned char *base = nullptr;
+    std::uint64_t capacity = 0, used = 0;
+    bool borrowed = false;
+    static constexpr int kMaxOwned = 24;
+    void *owned[kMaxOwned] = {};
+    int owned_count = 0;
+
+    static std::uint64_t rounded(std::uint64_t bytes) { return (bytes + 255u) & ~static_cast<std::uint64_t>(255u); }
+    // nullptr: the borrowed block has no room left, or the allocation failed (the CUDA error is cleared)
+    void *take(std::uint64_t bytes) {
+        const std::uint64_t need = rounded(bytes == 0u ? 1u : bytes);
+        if (borrowed) {
+            if (need > capacity - used) return nullptr;
+            void *p = base + used;
+            used += need;
+            return p;
+        }
+        if (owned_count == kMaxOwned) return nullptr;
+        void *p = nullptr;
+        if (cudaMalloc(&p, need) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        owned[owned_count++] = p;
+        used += need;
+        return p;
+    }
+    // A piece that is no longer needed: freed at once when owned; borrowed memory stays with its owner.
+    void give_back(void *p, std::uint64_t bytes) {
+        if (p == nullptr || borrowed) return;
+        for (int i = 0; i < owned_count; ++i) {
+            if (owned[i] != p) continue;
+            cudaFree(p);
+            owned[i] = owned[--owned_count];
+            used -= rounded(bytes == 0u ? 1u : bytes);
+            return;
+        }
+    }
+    void release_all() {
+        for (int i = 0; i < owned_count; ++i) cudaFree(owned[i]);
+        owned_count = 0;
+        used = 0;
+    }
+};
+
 // Gene-tiled kernel (W staged through shared memory); *taken is false when the shape is outside
 // what it covers, and the caller then runs the warp-per-row kernel.
 bool qcsr_forward_tiled_supported(const qcsr_view &x, const dense_args &d);
+// global scratch the tiled kernel needs, whatever the matrix: one status block (first word = status)
+constexpr std::uint64_t qcsr_tiled_workspace_bytes() { return 256u; }
 cb200_status launch_qcsr_forward_tiled(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                        std::int64_t row_end, int *status_word, const std::int32_t *row_order,
                                        int sm_count, cudaStream_t stream, bool *taken);
@@ -73,15 +124,19 @@ struct blocked_layout {
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
-// current device; allocates and synchronises.  bake: decoded values in the entry words (forward, bf16 products only)
+// Current device; memory from `arena`, kernels on `stream`, which is waited for.
+// bake: decoded values in the entry words (forward, bf16 products only)
 // bake_lo (needs bake): also the array of the next eight mantissa bits (split-product schedules)
 // gene_major (needs bake): byte positions of the transpose kernel's tile in the baked words
-cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, bool gene_major, blocked_layout *out);
-void free_blocked_layout(blocked_layout *layout);
-// Dense operand tiles from the window-blocked copy (decoded values of `x` baked in; the entry words
-// are freed).  *built stays false, the copy untouched, when the device has no room.  Synchronises.
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, bool gene_major, device_arena &arena,
+                                  cudaStream_t stream, blocked_layout *out);
+// upper bound of what build_blocked_layout takes from the arena (scratch of the build included)
+std::uint64_t qcsr_blocked_layout_bytes_bound(std::int64_t rows, std::int64_t cols, std::int64_t nnz, bool bake_lo);
+// Dense operand tiles from the window-blocked copy (decoded values of `x` baked in; the entry words go
+// back to the arena).  *built stays false, the copy untouched, when the arena has no room.  Waits for `stream`.
 std::uint64_t qcsr_dense_tile_bytes(std::int64_t rows, std::int64_t cols);
-cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, bool *built);
+cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, device_arena &arena, cudaStream_t stream,
+                                    bool *built);
 // *taken as for the blocked launch below; the tiles hold bf16(value): one pass of bf16 products only
 cb200_status launch_qcsr_forward_dense(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                        std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
@@ -133,9 +188,9 @@ std::uint64_t qcsr_gene_major_workspace_bytes(std::int64_t rows, std::int64_t co
 // non-zero when a column index lies outside the matrix.
 cb200_status launch_qcsr_gene_major(const qcsr_view &x, std::int64_t *col_ptr, std::int32_t *row_idx, std::uint8_t *codes,
                                     void *workspace, std::uint64_t workspace_bytes, cudaStream_t stream);
-// current device; allocates and synchronises
-cb200_status build_gene_major_layout(const qcsr_view &x, gene_major_layout *out);
-void free_gene_major_layout(gene_major_layout *layout);
+// current device; memory from `arena`, kernels and copies on `stream`, which is waited for
+cb200_status build_gene_major_layout(const qcsr_view &x, device_arena &arena, cudaStream_t stream, gene_major_layout *out);
+std::uint64_t qcsr_gene_major_layout_bytes_bound(std::int64_t rows, std::int64_t cols, std::int64_t nnz);
 // Transpose with a fixed order of the fp32 sums (same bits on every run), N in {32, 64, 128}:
 // gathers rows of G gene by gene from the gene-major copy.
 bool qcsr_transpose_gather_shape_ok(std::int64_t n);
@@ -157,9 +212,10 @@ struct qbell_view {
 
 // `workspace` (optional) holds the transposed bf16 copy of W that the tensor-core kernel needs;
 // without it (or for shapes that kernel does not cover) the CUDA-core kernel runs.
+// cuda_cores_only: the caller asked for the CUDA-core kernel (schedule hint "cuda_cores")
 cb200_status launch_qbell_forward(const qbell_view &x, const dense_args &d, std::int64_t row_begin,
                                   std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes, int sm_count,
-                                  cudaStream_t stream);
+                                  bool cuda_cores_only, cudaStream_t stream);
 std::uint64_t qbell_tcgen05_workspace_bytes(std::int64_t cols, std::int64_t n);
 
 cb200_status launch_quantize_rows(const qcsr_view &x, std::int64_t row_begin, std::int64_t row_end,

@@ -67,6 +67,10 @@ cb200_status route(const cb200_public_layout *l, int32_t projection, const float
     if (dense_ld < n || out_ld < n) return fail(CB200_STATUS_INVALID_SHAPE, "leading dimension smaller than the column count");
     if (reinterpret_cast<std::uintptr_t>(scratch) % 256u != 0u) return fail(CB200_STATUS_INVALID_ARGUMENT, "scratch must be 256-byte aligned");
     scratch_cursor cur{static_cast<unsigned char *>(scratch), scratch_bytes};
+    // the first 256 bytes of the scratch are the kernels' status block (first word = status), so that
+    // cb200_public_projection_status finds it without knowing the layout; the widened offsets follow
+    void *status_block = cur.take(256u);
+    if (status_block == nullptr) return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "scratch too small for the status block (256 bytes)");
 
     cb200_spmm_problem pr{};
     pr.version = CB200_ABI_VERSION;
@@ -117,7 +121,8 @@ cb200_status route(const cb200_public_layout *l, int32_t projection, const float
     std::uint64_t need = 0;
     std::uint32_t align = 256;
     cb200_prepared_workspace(prepared, &need, &align);
-    void *ws = need != 0u ? cur.take(need) : nullptr;
+    // the exact fp32 schedules these calls select need the status block only
+    void *ws = need == 0u ? nullptr : (need <= 256u ? status_block : cur.take(need));
     if (need != 0u && ws == nullptr) {
         cb200_prepared_destroy(prepared);
         return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "scratch too small for the kernel workspace (%llu more bytes)",
@@ -125,7 +130,13 @@ cb200_status route(const cb200_public_layout *l, int32_t projection, const float
     }
     ln.dense = dense; ln.dense_ld = dense_ld; ln.out = out; ln.out_ld = out_ld;
     ln.alpha = 1.0f; ln.beta = 0.0f; ln.structure_epoch = 1u; ln.stream = stream; ln.device = device;
+    ln.row_begin = 0; ln.row_end = CB200_ALL_ROWS;
     ln.workspace_device = device; ln.workspace = ws; ln.workspace_bytes = need;
+    if (need == 0u) { // a schedule without waits: the status block still reads 0 afterwards
+        device_scope scope(device);
+        CB200_CUDA_OK(scope.status);
+        CB200_CUDA_OK(cudaMemsetAsync(status_block, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+    }
     st = cb200_spmm_run(prepared, &ln);
     cb200_prepared_destroy(prepared);
     return st;
@@ -164,4 +175,19 @@ extern "C" cb200_status cb200_public_projection_backward_rhs(const cb200_public_
     clear_error();
     return route(layout, CB200_PROJECTION_TRANSPOSE, grad_out, grad_out_ld, out_cols, grad_rhs, grad_rhs_ld, device, stream,
                  scratch, scratch_bytes);
+}
+
+extern "C" cb200_status cb200_public_projection_status(const void *scratch, int32_t device, void *stream, int32_t *host_word) {
+    using namespace cb200;
+    clear_error();
+    if (scratch == nullptr || host_word == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "status needs the scratch of the call and an output");
+    *host_word = 0;
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CB200_CUDA_OK(cudaMemcpyAsync(host_word, scratch, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CB200_CUDA_OK(cudaStreamSynchronize(s));
+    if (*host_word != 0)
+        return fail(CB200_STATUS_DEVICE_WAIT_TIMEOUT, "a kernel of the last routed projection gave up a bounded wait: its output is not valid");
+    return CB200_STATUS_SUCCESS;
 }

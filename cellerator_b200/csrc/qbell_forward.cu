@@ -181,18 +181,14 @@ cb200_status dispatch(const bell_params &p, bool vector_ok, cudaStream_t stream)
 
 cb200_status launch_qbell_forward(const qbell_view &x, const dense_args &d, std::int64_t row_begin,
                                   std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes, int sm_count,
-                                  cudaStream_t stream) {
+                                  bool cuda_cores_only, cudaStream_t stream) {
     if (row_end <= row_begin || d.n == 0) return CB200_STATUS_SUCCESS;
     if (x.block_size <= 0 || x.ell_cols < 0 || x.ell_cols % x.block_size != 0)
         return fail(CB200_STATUS_INVALID_SHAPE, "ell_cols must be a multiple of block_size");
     if (x.bits != 8 && x.bits != 4) return fail(CB200_STATUS_UNSUPPORTED, "Blocked-ELL supports 8-bit and 4-bit codes");
 
     bool taken = false;
-    static const bool tensor_path = [] {
-        const char *e = std::getenv("CB200_BELL_TENSOR");
-        return e == nullptr || e[0] != '0';
-    }();
-    const cb200_status tc = tensor_path ? launch_qbell_tcgen05(x, d, row_begin, row_end, workspace, workspace_bytes, sm_count,
+    const cb200_status tc = !cuda_cores_only ? launch_qbell_tcgen05(x, d, row_begin, row_end, workspace, workspace_bytes, sm_count,
                                                                stream, &taken)
                                         : CB200_STATUS_SUCCESS;
     if (tc != CB200_STATUS_SUCCESS || taken) return tc;

@@ -209,11 +209,7 @@ __global__ void __launch_bounds__(256) qcsr_fwd_generic_kernel(const fwd_params 
 template<int BITS, typename WT>
 cb200_status dispatch_n(const fwd_params &p, bool vector_ok, cudaStream_t stream) {
     const std::int64_t rows = p.row_end - p.row_begin;
-    static const int threads = [] {
-        const char *e = std::getenv("CB200_FWD_THREADS");
-        const int t = e != nullptr ? std::atoi(e) : 0;
-        return (t >= 32 && t <= 256 && t % 32 == 0) ? t : 128;
-    }();
+    constexpr int threads = 128; // four rows per CTA (64 to 256 threads measured within 2 % of each other)
     const unsigned grid = static_cast<unsigned>((rows + (threads / 32) - 1) / (threads / 32));
     if (vector_ok && p.n % 8 == 0) {
         switch (p.n / 8) {

@@ -187,7 +187,12 @@ struct blocked_params {
     int epilogue;
     int *status;
     int value_part; // 0: the tile holds hi = bf16(value); 1: lo = bf16(value - hi)
+    int poll_limit; // polls a bounded wait makes before it gives up (kPollLimit; less under the test hook)
+    int withhold_w; // test hook: the W loader issues no copies, so the waits for W run out
 };
+
+// Test hook (cb200_test_arm_wait_timeout): read at launch time by the two-group kernel's launcher.
+std::atomic<int> g_test_poll_limit{0}; // 0 = not armed
 
 template<int NC, int CS, bool BAKED>
 __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blocked_params p) {
@@ -502,12 +507,14 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     std::uint64_t *c_empty = c_full + CHUNKS;     // [CHUNKS] scatter group -> chunk loader (one arrival per warp)
     std::uint64_t *acc_full = c_empty + CHUNKS;   // MMA commit -> epilogue warps
     std::uint64_t *acc_empty = acc_full + 1;      // epilogue warps -> MMA
-    volatile int *chunk_meta = reinterpret_cast<volatile int *>(acc_empty + 1); // [CHUNKS] (entries << 1) | last chunk of its window
+    std::uint64_t *mma_drain = acc_empty + 1;     // MMA commit -> MMA warp, used once, after an abort
+    volatile int *chunk_meta = reinterpret_cast<volatile int *>(mma_drain + 1); // [CHUNKS] (entries << 1) | last chunk of its window
     std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + CHUNKS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int limit = p.poll_limit;
     const std::uint32_t smem0 = smem_addr(smem);
     const std::uint32_t wstage0 = smem0 + 2 * kABufBytes;
     const std::uint32_t chunk0 = wstage0 + STAGES * WREC;
@@ -527,6 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
         }
         bar_init(smem_addr(acc_full), 1);
         bar_init(smem_addr(acc_empty), kEpilogueWarps);
+        bar_init(smem_addr(mma_drain), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -554,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
             const std::int64_t row = (first_group + gi * gridDim.x) * kRows + tid;
             for (int w = 0; w < p.windows; ++w, ++q) {
                 if (static_cast<int>(q & 1) != grp) continue;
-                bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
+                bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag, limit);
 #pragma unroll
                 for (int k = 0; k < kABufBytes / (kGroupThreads * 16); ++k)
                     *reinterpret_cast<uint4 *>(tile + k * (kGroupThreads * 16) + gtid * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -565,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 int guard = 0;
                 while (!last && ++guard < (1 << 20)) {
                     const int cs = grp * kRing2 + static_cast<int>(qc % kRing2);
-                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing2) & 1), abort_flag);
+                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing2) & 1), abort_flag, limit);
                     const int meta = chunk_meta[cs];
                     const int count = *abort_flag != 0 ? 0 : (meta >> 1);
                     last = (meta & 1) != 0 || *abort_flag != 0;
@@ -590,7 +598,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
 
             // ---- thread t < 256 (group 0) writes row t of the row group: TMEM lane = row within the sub-block
             if (grp != 0) continue;
-            bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(gi & 1), abort_flag);
+            bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(gi & 1), abort_flag, limit);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int h = 0; h < NC / 32; ++h) {
@@ -609,14 +617,15 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
         // ================= MMA issuer =================
         long long q = 0;
         for (std::int64_t g = 0; g < my_groups; ++g) {
-            bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((g & 1) ^ 1), abort_flag);
+            bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((g & 1) ^ 1), abort_flag, limit);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int w = 0; w < p.windows; ++w, ++q) {
                 const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
                 const int s = static_cast<int>(q % STAGES);
-                bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag);
-                bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag);
+                bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag, limit);
+                bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag, limit);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (*abort_flag != 0) break; // a wait ran out: nothing more is multiplied
                 if (lane == 0) {
                     const std::uint32_t a_tile = smem0 + b * kABufBytes;
                     const std::uint32_t b_tile = wstage0 + s * WREC;
@@ -635,28 +644,42 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 }
                 __syncwarp();
             }
+            if (*abort_flag != 0) break;
         }
+        // after an abort: the MMAs already issued finish before the CTA frees its TMEM and shared memory
+        if (*abort_flag != 0 && lane == 0) {
+            mma_commit(smem_addr(mma_drain));
+            bar_wait_drain(smem_addr(mma_drain), 0u, limit);
+        }
+        __syncwarp();
     } else if (warp == kProducerWarps + 1) {
         // ================= W loader =================
-        if (lane == 0) {
+        if (lane == 0 && p.withhold_w == 0) {
             const long long total = my_groups * p.windows;
-            for (long long q = 0; q < total; ++q) {
+            long long q = 0;
+            for (; q < total; ++q) {
                 const int s = static_cast<int>(q % STAGES);
-                bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag);
+                bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag, limit);
+                if (*abort_flag != 0) break; // no new copies once a wait of the CTA has run out
                 bar_arrive_expect_tx(smem_addr(w_full + s), WREC);
                 bulk_copy_g2s(wstage0 + s * WREC, p.records + static_cast<std::size_t>(q % p.windows) * REC, WREC, smem_addr(w_full + s));
             }
+            // after an abort: let the copies still in flight land (the last one issued into each stage)
+            if (*abort_flag != 0)
+                for (long long last = q - 1; last >= 0 && last > q - 1 - STAGES; --last)
+                    bar_wait_drain(smem_addr(w_full + static_cast<int>(last % STAGES)), static_cast<std::uint32_t>((last / STAGES) & 1), limit);
         }
     } else if (warp == kProducerWarps + 2) {
         // ================= entry chunks: window q goes to the ring of scatter group q & 1 =================
         long long q = 0;
         long long qc0 = 0, qc1 = 0; // chunks issued into each ring
-        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
+        int stop = 0;
+        for (std::int64_t gi = 0; gi < my_groups && stop == 0; ++gi) {
             const std::int64_t seg0 = (first_group + gi * gridDim.x) * p.windows;
-            for (int wbase = 0; wbase < p.windows; wbase += 31) {
+            for (int wbase = 0; wbase < p.windows && stop == 0; wbase += 31) {
                 const int span = min(31, p.windows - wbase); // segment bounds of up to 31 windows in one coalesced read
                 const std::int64_t bound = lane <= span ? __ldg(p.seg_ptr + seg0 + wbase + lane) : 0;
-                for (int j = 0; j < span; ++j, ++q) {
+                for (int j = 0; j < span && stop == 0; ++j, ++q) {
                     const std::int64_t lo = __shfl_sync(0xffffffffu, bound, j), hi = __shfl_sync(0xffffffffu, bound, j + 1);
                     const int ring = static_cast<int>(q & 1);
                     std::int64_t at = lo;
@@ -665,7 +688,13 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                         const long long mine = ring == 0 ? qc0 : qc1;
                         if (lane == 0) {
                             const int cs = ring * kRing2 + static_cast<int>(mine % kRing2);
-                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((mine / kRing2) & 1) ^ 1), abort_flag);
+                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((mine / kRing2) & 1) ^ 1), abort_flag, limit);
+                            if (*abort_flag != 0) stop = 1; // no new copies once a wait of the CTA has run out
+                        }
+                        stop = __shfl_sync(0xffffffffu, stop, 0);
+                        if (stop != 0) break;
+                        if (lane == 0) {
+                            const int cs = ring * kRing2 + static_cast<int>(mine % kRing2);
                             chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
                             if (count > 0) {
                                 bar_arrive_expect_tx(smem_addr(c_full + cs), static_cast<std::uint32_t>(count) * 4u);
@@ -682,6 +711,16 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 }
             }
         }
+        // after an abort: let the chunk copies still in flight land (the last one issued into each stage of both rings)
+        if (stop != 0 && lane == 0) {
+            for (int ring = 0; ring < 2; ++ring) {
+                const long long issued = ring == 0 ? qc0 : qc1;
+                for (long long last = issued - 1; last >= 0 && last > issued - 1 - kRing2; --last)
+                    bar_wait_drain(smem_addr(c_full + ring * kRing2 + static_cast<int>(last % kRing2)),
+                                   static_cast<std::uint32_t>((last / kRing2) & 1), limit);
+            }
+        }
+        __syncwarp();
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -696,7 +735,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
 template<int NC>
 cb200_status launch_blocked2(const blocked_params &p, int sm_count, cudaStream_t stream) {
     constexpr std::size_t smem = 2 * kABufBytes + w2_stages(NC) * NC * kWin * 2 + 2 * kRing2 * kChunk2Bytes +
-                                 (6 + 2 * w2_stages(NC) + 4 * kRing2) * sizeof(std::uint64_t) + 2 * kRing2 * 4 + 24;
+                                 (7 + 2 * w2_stages(NC) + 4 * kRing2) * sizeof(std::uint64_t) + 2 * kRing2 * 4 + 24;
     static_assert(smem <= 232448, "shared memory budget");
     CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked2_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const std::int64_t groups = p.group_end - p.group_begin;
@@ -722,17 +761,19 @@ bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n,
     return groups * windows < (static_cast<std::int64_t>(1) << 31);
 }
 
-void free_blocked_layout(blocked_layout *layout) {
-    if (layout == nullptr) return;
-    if (layout->entries != nullptr) cudaFree(layout->entries);
-    if (layout->entries_lo != nullptr) cudaFree(layout->entries_lo);
-    if (layout->seg_ptr != nullptr) cudaFree(layout->seg_ptr);
-    if (layout->dense_tiles != nullptr) cudaFree(layout->dense_tiles);
-    *layout = blocked_layout{};
+std::uint64_t qcsr_blocked_layout_bytes_bound(std::int64_t rows, std::int64_t cols, std::int64_t nnz, bool bake_lo) {
+    const std::uint64_t groups = static_cast<std::uint64_t>((rows + kRows - 1) / kRows);
+    const std::uint64_t segments = groups * static_cast<std::uint64_t>((cols + kWin - 1) / kWin);
+    // a segment is padded to a multiple of four words: at most three more per segment
+    const std::uint64_t words = static_cast<std::uint64_t>(nnz) + 3u * segments;
+    return device_arena::rounded(segments * sizeof(unsigned)) + device_arena::rounded(segments * sizeof(unsigned long long)) +
+           device_arena::rounded((segments + 1u) * sizeof(std::int64_t)) + (bake_lo ? 2u : 1u) * device_arena::rounded(words * 4u);
 }
 
-// Builds the window-blocked copy of `x` on the current device; synchronises.
-cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, bool gene_major, blocked_layout *out) {
+// Builds the window-blocked copy of `x` on the current device: memory from `arena`, kernels on `stream`,
+// which is waited for (the size of the copy is read back before its arrays are taken).
+cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, bool gene_major, device_arena &arena,
+                                  cudaStream_t stream, blocked_layout *out) {
     *out = blocked_layout{};
     if (x.row_ptr == nullptr || (x.nnz != 0 && (x.col_idx == nullptr || x.packed == nullptr)))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "the matrix handed to prepare has null arrays");
@@ -741,48 +782,61 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     const int windows = static_cast<int>((x.cols + kWin - 1) / kWin);
     const std::int64_t segments = groups * windows;
     const int bake_mode = !bake ? 0 : (x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET ? 2 : 1);
-    unsigned *counts = nullptr;
-    unsigned long long *cursor = nullptr;
-    cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&counts), static_cast<std::size_t>(segments) * sizeof(unsigned));
-    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&cursor), static_cast<std::size_t>(segments) * sizeof(unsigned long long));
-    if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void **>(&out->seg_ptr), static_cast<std::size_t>(segments + 1) * sizeof(std::int64_t));
-    if (err == cudaSuccess) err = cudaMemset(counts, 0, static_cast<std::size_t>(segments) * sizeof(unsigned));
+    const std::uint64_t count_bytes = static_cast<std::uint64_t>(segments) * sizeof(unsigned);
+    const std::uint64_t cursor_bytes = static_cast<std::uint64_t>(segments) * sizeof(unsigned long long);
+    const std::uint64_t seg_bytes = static_cast<std::uint64_t>(segments + 1) * sizeof(std::int64_t);
+    unsigned *counts = static_cast<unsigned *>(arena.take(count_bytes));
+    unsigned long long *cursor = static_cast<unsigned long long *>(arena.take(cursor_bytes));
+    out->seg_ptr = static_cast<std::int64_t *>(arena.take(seg_bytes));
+    std::uint64_t word_bytes = 0;
+    const auto give_up = [&](cb200_status st) {
+        arena.give_back(out->entries_lo, word_bytes);
+        arena.give_back(out->entries, word_bytes);
+        arena.give_back(out->seg_ptr, seg_bytes);
+        arena.give_back(cursor, cursor_bytes);
+        arena.give_back(counts, count_bytes);
+        *out = blocked_layout{};
+        return st;
+    };
+    if (counts == nullptr || cursor == nullptr || out->seg_ptr == nullptr)
+        return give_up(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "no device memory for the segment table of the window-blocked copy"));
+    cudaError_t err = cudaMemsetAsync(counts, 0, count_bytes, stream);
     const unsigned grid = static_cast<unsigned>((x.rows + 7) / 8); // one warp per row, 8 rows per block
     std::int64_t total = 0;
     if (err == cudaSuccess) {
         if (x.bits == 8)
-            blocked_pass_kernel<8, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
+            blocked_pass_kernel<8, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
         else
-            blocked_pass_kernel<4, false><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
+            blocked_pass_kernel<4, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
         count_launch();
-        segment_scan_kernel<<<1, 1024>>>(counts, segments, out->seg_ptr, cursor);
+        segment_scan_kernel<<<1, 1024, 0, stream>>>(counts, segments, out->seg_ptr, cursor);
         count_launch();
         err = cudaGetLastError();
     }
-    if (err == cudaSuccess) err = cudaMemcpy(&total, out->seg_ptr + segments, sizeof(total), cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(&total, out->seg_ptr + segments, sizeof(total), cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
     if (err == cudaSuccess && total > 0) {
-        err = cudaMalloc(reinterpret_cast<void **>(&out->entries), static_cast<std::size_t>(total) * sizeof(std::uint32_t));
-        if (err == cudaSuccess) err = cudaMemset(out->entries, 0x80, static_cast<std::size_t>(total) * sizeof(std::uint32_t)); // padding = invalid
-        if (err == cudaSuccess && bake && bake_lo) {
-            err = cudaMalloc(reinterpret_cast<void **>(&out->entries_lo), static_cast<std::size_t>(total) * sizeof(std::uint32_t));
-            if (err == cudaSuccess) err = cudaMemset(out->entries_lo, 0x80, static_cast<std::size_t>(total) * sizeof(std::uint32_t));
-        }
+        word_bytes = static_cast<std::uint64_t>(total) * sizeof(std::uint32_t);
+        out->entries = static_cast<std::uint32_t *>(arena.take(word_bytes));
+        if (bake && bake_lo) out->entries_lo = static_cast<std::uint32_t *>(arena.take(word_bytes));
+        if (out->entries == nullptr || (bake && bake_lo && out->entries_lo == nullptr))
+            return give_up(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "no device memory for the %lld entry words of the window-blocked copy",
+                                static_cast<long long>(total)));
+        err = cudaMemsetAsync(out->entries, 0x80, word_bytes, stream); // padding = invalid
+        if (err == cudaSuccess && out->entries_lo != nullptr) err = cudaMemsetAsync(out->entries_lo, 0x80, word_bytes, stream);
         if (err == cudaSuccess) {
             if (x.bits == 8)
-                blocked_pass_kernel<8, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
+                blocked_pass_kernel<8, true><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
             else
-                blocked_pass_kernel<4, true><<<grid, 256>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
+                blocked_pass_kernel<4, true><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
             count_launch();
             err = cudaGetLastError();
         }
     }
-    if (err == cudaSuccess) err = cudaDeviceSynchronize();
-    if (counts != nullptr) cudaFree(counts);
-    if (cursor != nullptr) cudaFree(cursor);
-    if (err != cudaSuccess) {
-        free_blocked_layout(out);
-        return fail(CB200_STATUS_CUDA_ERROR, "building the window-blocked copy: %s", cudaGetErrorString(err));
-    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) return give_up(fail(CB200_STATUS_CUDA_ERROR, "building the window-blocked copy: %s", cudaGetErrorString(err)));
+    arena.give_back(cursor, cursor_bytes);
+    arena.give_back(counts, count_bytes);
     out->groups = groups;
     out->windows = windows;
     out->total_entries = total;
@@ -832,6 +886,12 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     p.records = records; p.y = d.out; p.y_ld = d.out_ld; p.row_end = row_end;
     p.group_begin = row_begin / kRows; p.group_end = (row_end + kRows - 1) / kRows; p.windows = layout.windows;
     p.alpha = d.alpha; p.status = status;
+    p.poll_limit = kPollLimit;
+    p.withhold_w = 0;
+    if (const int armed = g_test_poll_limit.load(std::memory_order_relaxed)) { // test hook: see cb200_test_arm_wait_timeout
+        p.poll_limit = armed;
+        p.withhold_w = 1;
+    }
     *taken = true;
     // One pass multiplies bf16(value) with bf16 W.  With split products the fp32 product is rebuilt
     // from bf16 pieces, value = hi + lo and (fp32 W) W = hi + lo:  bf16 W: hi*w + lo*w (two passes, exact
@@ -865,13 +925,9 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
         p.bias = d.bias;
         p.epilogue = i + 1 == pass_count ? d.epilogue : CB200_EPILOGUE_NONE;
         cb200_status st;
-        static const bool two_groups_enabled = [] {
-            const char *e = std::getenv("CB200_SCATTER_GROUPS");
-            return e == nullptr || std::atoi(e) != 1;
-        }();
         const bool long_segments = layout.total_entries > static_cast<std::int64_t>(kChunkEntries) * layout.groups * layout.windows;
         // two scatter groups pay when a window is a chunk or two; long segments keep one group and deeper chunks
-        const bool two_groups = layout.baked && two_groups_enabled && !long_segments;
+        const bool two_groups = layout.baked && !long_segments;
         switch (d.n) {
         case 32: st = two_groups ? launch_blocked2<32>(p, sm_count, stream) : launch_one<32>(p, long_segments, layout.baked, sm_count, stream); break;
         case 64: st = two_groups ? launch_blocked2<64>(p, sm_count, stream) : launch_one<64>(p, long_segments, layout.baked, sm_count, stream); break;
@@ -883,3 +939,9 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
 }
 
 } // namespace cb200
+
+extern "C" void cb200_test_arm_wait_timeout(uint32_t poll_limit) {
+    const uint32_t clamped = poll_limit < 64u ? 64u : (poll_limit > static_cast<uint32_t>(cb200::kPollLimit) ? static_cast<uint32_t>(cb200::kPollLimit) : poll_limit);
+    cb200::g_test_poll_limit.store(static_cast<int>(clamped), std::memory_order_relaxed);
+}
+extern "C" void cb200_test_disarm_wait_timeout(void) { cb200::g_test_poll_limit.store(0, std::memory_order_relaxed); }

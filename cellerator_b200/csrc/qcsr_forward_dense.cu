@@ -262,35 +262,33 @@ std::uint64_t qcsr_dense_tile_bytes(std::int64_t rows, std::int64_t cols) {
 }
 
 // Turns the window-blocked copy into dense operand tiles (decoded bf16 values, scales and offsets of
-// `x` baked in); frees the entry words.  *built is false, with the copy left as it was, when the
-// device has no room for the tiles.  Synchronises.
-cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, bool *built) {
+// `x` baked in); the entry words go back to the arena.  *built is false, with the copy left as it was,
+// when the arena has no room for the tiles.  Waits for `stream`.
+cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, device_arena &arena, cudaStream_t stream,
+                                    bool *built) {
     *built = false;
     if (layout == nullptr || layout->seg_ptr == nullptr) return CB200_STATUS_SUCCESS;
     const std::int64_t segments = layout->groups * layout->windows;
     const std::uint64_t bytes = static_cast<std::uint64_t>(segments) * kABufBytes;
-    unsigned char *tiles = nullptr;
-    if (cudaMalloc(reinterpret_cast<void **>(&tiles), bytes) != cudaSuccess) {
-        cudaGetLastError(); // out of memory is not an error of the prepare: the blocked copy stays
-        return CB200_STATUS_SUCCESS;
-    }
+    unsigned char *tiles = static_cast<unsigned char *>(arena.take(bytes));
+    if (tiles == nullptr) return CB200_STATUS_SUCCESS; // out of memory is not an error of the prepare: the blocked copy stays
     const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
     cudaError_t err = cudaFuncSetAttribute(densify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kABufBytes);
     if (err == cudaSuccess && segments > 0) {
-        densify_kernel<<<static_cast<unsigned>(segments), 512, kABufBytes>>>(layout->entries, layout->seg_ptr, x.scales,
-                                                                             row_policy ? nullptr : x.offsets,
-                                                                             row_policy ? x.offsets : nullptr, x.rows, x.cols,
-                                                                             layout->windows, layout->baked ? 1 : 0, tiles);
+        densify_kernel<<<static_cast<unsigned>(segments), 512, kABufBytes, stream>>>(layout->entries, layout->seg_ptr, x.scales,
+                                                                                     row_policy ? nullptr : x.offsets,
+                                                                                     row_policy ? x.offsets : nullptr, x.rows, x.cols,
+                                                                                     layout->windows, layout->baked ? 1 : 0, tiles);
         count_launch();
         err = cudaGetLastError();
     }
-    if (err == cudaSuccess) err = cudaDeviceSynchronize();
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
     if (err != cudaSuccess) {
-        cudaFree(tiles);
+        arena.give_back(tiles, bytes);
         return fail(CB200_STATUS_CUDA_ERROR, "building the dense operand tiles: %s", cudaGetErrorString(err));
     }
-    if (layout->entries != nullptr) cudaFree(layout->entries);
-    cudaFree(layout->seg_ptr);
+    arena.give_back(layout->entries, static_cast<std::uint64_t>(layout->total_entries) * 4u);
+    arena.give_back(layout->seg_ptr, static_cast<std::uint64_t>(segments + 1) * 8u);
     layout->entries = nullptr;
     layout->seg_ptr = nullptr;
     layout->total_entries = 0;

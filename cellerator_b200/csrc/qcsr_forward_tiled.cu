@@ -337,10 +337,12 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_tiled_kernel(const tiled
             // ---- wait for the tile's bytes (bounded)
             {
                 const std::uint32_t parity = static_cast<std::uint32_t>((q >> 1) & 1);
+                // once any wait of the CTA has run out, later tiles do not wait again: the kernel finishes
+                // promptly with memory-safe indices and reports status 1
                 int spins = 0;
-                while (!mbar_try_wait(bar0 + 8 * b, parity)) {
+                while (*static_cast<volatile int *>(abort_flag) == 0 && !mbar_try_wait(bar0 + 8 * b, parity)) {
                     if (++spins > (1 << 22)) {
-                        *abort_flag = 1;
+                        *static_cast<volatile int *>(abort_flag) = 1;
                         break;
                     }
                 }
@@ -595,7 +597,8 @@ extern "C" cb200_status cb200_qcsr_forward_static(const cb200_qcsr *x, const voi
     if (static_cast<const void *>(y) == w) return fail(CB200_STATUS_INVALID_ARGUMENT, "output aliases the dense input");
     if (x->rows < 0 || x->cols < 0 || n <= 0 || y_ld < n) return fail(CB200_STATUS_INVALID_SHAPE, "bad shape");
     // scratch this kernel needs for this problem against what the fixed array holds
-    const std::size_t needed = 256; // one status block, whatever the matrix size
+    const std::size_t needed = qcsr_tiled_workspace_bytes(); // one status block, whatever the matrix size
+    static_assert(kStaticScratchBytes >= qcsr_tiled_workspace_bytes(), "the built-in array must hold the tiled kernel's scratch");
     if (needed > kStaticScratchBytes)
         return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "needs %zu bytes of scratch, the built-in array holds %zu", needed,
                     kStaticScratchBytes);
@@ -621,5 +624,26 @@ extern "C" cb200_status cb200_qcsr_forward_static(const cb200_qcsr *x, const voi
                                                       static_cast<cudaStream_t>(stream), &taken);
     if (st != CB200_STATUS_SUCCESS) return st;
     if (!taken) return fail(CB200_STATUS_INTERNAL_ERROR, "tiled kernel declined a shape it reports as supported");
+    return CB200_STATUS_SUCCESS;
+}
+
+extern "C" cb200_status cb200_qcsr_forward_static_status(int32_t device, void *stream, int32_t *host_word) {
+    using namespace cb200;
+    clear_error();
+    if (host_word == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "status needs an output");
+    *host_word = 0;
+    if (device < 0 || device >= kStaticMaxDevices)
+        return fail(CB200_STATUS_INVALID_STREAM, "device ordinal %d outside 0..%d", device, kStaticMaxDevices - 1);
+    // the address cached by the first static call on this device; nothing is looked up or allocated here
+    void *scratch = g_static_scratch_address[device].load(std::memory_order_acquire);
+    if (scratch == nullptr)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "no cb200_qcsr_forward_static call has run on device %d yet", device);
+    device_scope scope(device);
+    CB200_CUDA_OK(scope.status);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CB200_CUDA_OK(cudaMemcpyAsync(host_word, scratch, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CB200_CUDA_OK(cudaStreamSynchronize(s));
+    if (*host_word != 0)
+        return fail(CB200_STATUS_DEVICE_WAIT_TIMEOUT, "the last static forward call on device %d gave up a bounded wait: its output is not valid", device);
     return CB200_STATUS_SUCCESS;
 }

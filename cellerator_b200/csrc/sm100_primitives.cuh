@@ -28,15 +28,23 @@ __device__ __forceinline__ bool bar_try_wait(std::uint32_t bar, std::uint32_t pa
     return ok != 0u;
 }
 // Bounded wait.  Once any wait of the CTA has timed out (`*abort_flag` set) waits return at once.
-__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag) {
+constexpr int kPollLimit = 1 << 22;
+__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag, int limit = kPollLimit) {
     int spins = 0;
     while (!bar_try_wait(bar, parity)) {
         if (*abort_flag != 0) return;
-        if (++spins > (1 << 22)) {
+        if (++spins > limit) {
             *abort_flag = 1;
             return;
         }
     }
+}
+// Bounded wait that does not look at the abort flag: what a role uses, after the CTA has aborted, to let the
+// copies or MMAs it still has in flight finish before the CTA gives up its shared memory and TMEM.
+__device__ __forceinline__ bool bar_wait_drain(std::uint32_t bar, std::uint32_t parity, int limit = kPollLimit) {
+    for (int spins = 0; spins <= limit; ++spins)
+        if (bar_try_wait(bar, parity)) return true;
+    return false;
 }
 // One contiguous global -> shared copy by the copy engine (this GPU's own memory, no multicast).
 __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes, std::uint32_t bar) {

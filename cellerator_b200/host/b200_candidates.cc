@@ -174,6 +174,8 @@ core::operation_status run(const core::prepared_operation &prepared, const ex::l
         l.bias = static_cast<const float *>(launch.inputs[2].storage.dense.data);
     }
     l.structure_epoch = launch.structures[0].epoch.value;
+    l.row_begin = 0; // the operation core binds whole operands; shards are separate structures
+    l.row_end = CB200_ALL_ROWS;
     l.stream = launch.stream.stream;
     l.device = launch.stream.device_ordinal;
     l.workspace = launch.workspace.data;
@@ -244,6 +246,11 @@ core::operation_status prepare_any(int projection_kind, bool composed, bool orde
     p.device_matrix = policy.allow_persistent_preprocessing ? shape->device_matrix : nullptr;
     p.persistent_limit_bytes = policy.persistent_memory_limit;
     p.value_generation = p.device_matrix != nullptr ? shape->device_matrix_generation.value : 0u;
+    p.schedule_hint = shape->schedule_hint;
+    // persistent memory the session reserved for this operation (borrowed, OPERATION_CORE.md:17-25), and its stream
+    p.persistent = shape->persistent;
+    p.persistent_bytes = shape->persistent_bytes;
+    p.prepare_stream = shape->prepare_stream;
 
     auto *state = new (std::nothrow) prepared_state;
     if (state == nullptr) return status(core::operation_status_code::preparation_failed, "out of host memory");

@@ -59,6 +59,15 @@ struct projection_catalog_entry {
     // prepare builds from them is only valid for that generation: a launch binding another one is refused
     // as a stale value (the reference does not freeze values in prepared state, lifetimes.hh:80-81)
     ex::value_generation device_matrix_generation{};
+    // optional: one schedule by name (cb200_spmm_problem.schedule_hint): how a planner that keeps one candidate
+    // per schedule pins its choice; null lets prepare choose
+    const char *schedule_hint = nullptr;
+    // optional: persistent memory of the execution session (reserve_persistent before seal_session,
+    // include/Cellerator/runtime/session.cuh:141) that prepare builds its copies in instead of allocating,
+    // sized by cb200_spmm_persistent_requirement, and the stream prepare works on
+    void *persistent = nullptr;
+    std::uint64_t persistent_bytes = 0u;
+    void *prepare_stream = nullptr;
     // how the result meets the destination (output_effect_contract, launch_bindings.hh:19-33): overwrite
     // (out = product), accumulate (out += product; the destination must be initialised) or
     // affine_accumulate (out = alpha * product + beta * out, alpha and beta bound per launch as f32 or

@@ -201,12 +201,18 @@ def backend_query(projection: int, sparse=capi.DTYPE_U8, dense=capi.DTYPE_BF16, 
             "transient_bytes": cap.transient_bytes, "name": (cap.name or b"").decode()}
 
 
+# Schedule requested for every operation of a projection kind that names none itself (cb200_spmm_problem.
+# schedule_hint): how a test pins one kernel for all the operations it prepares.  Empty by default.
+SCHEDULE_REQUEST: dict[int, str | None] = {}
+
+
 class PreparedSpmm:
     """prepare once, run many times (cb200_spmm_prepare / cb200_spmm_run)."""
 
     def __init__(self, projection: int, m: int, k: int, n: int, nnz: int, bits: int, policy: int, dense_dtype,
                  device, structure_epoch: int = 1, host_row_ptr: np.ndarray | None = None, deterministic=False,
-                 multiply: int = 0, device_matrix=None, persistent_limit_bytes: int = 0, value_generation: int = 0):
+                 multiply: int = 0, device_matrix=None, persistent_limit_bytes: int = 0, value_generation: int = 0,
+                 schedule: str | None = None, persistent: torch.Tensor | None = None, prepare_stream: int | None = None):
         self.device = torch.device(device)
         pr = capi.header(capi.SpmmProblem())
         pr.projection, pr.m, pr.k, pr.n, pr.nnz, pr.bits, pr.policy = projection, m, k, n, nnz, bits, policy
@@ -225,6 +231,14 @@ class PreparedSpmm:
             pr.device_matrix = C.pointer(self._matrix_desc)
         pr.persistent_limit_bytes = persistent_limit_bytes  # 0: no limit on what prepare may keep on the device
         pr.value_generation = value_generation              # generation of the values device_matrix holds (0: not tracked)
+        if schedule is None:
+            schedule = SCHEDULE_REQUEST.get(projection)
+        self._hint = schedule.encode() if schedule else None
+        pr.schedule_hint = self._hint                       # one schedule by name; None lets prepare choose
+        self._persistent = persistent                       # caller-owned block prepare builds its copies in
+        if persistent is not None:
+            pr.persistent, pr.persistent_bytes = persistent.data_ptr(), persistent.numel() * persistent.element_size()
+        pr.prepare_stream = prepare_stream
         self.problem = pr
         self.handle = C.c_void_p()
         capi.check(capi.lib().cb200_spmm_prepare(C.byref(pr), C.byref(self.handle)))
@@ -244,7 +258,41 @@ class PreparedSpmm:
         """Device bytes the prepared operation owns (row order, window-blocked copy)."""
         return int(capi.lib().cb200_prepared_persistent_bytes(self.handle))
 
-    def make_launch(self, x, dense: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0, row_begin=0, row_end=0,
+    def status(self, stream: int | None = None) -> int:
+        """Status word of the launches that used this operation's workspace (cb200_prepared_status): 0, or
+        raises Cb200Error(DEVICE_WAIT_TIMEOUT) when a kernel gave up a bounded wait.  Waits for the stream."""
+        word = C.c_int32(-1)
+        ws = None if self.workspace is None else C.c_void_p(self.workspace.data_ptr())
+        capi.check(capi.lib().cb200_prepared_status(self.handle, ws, C.c_void_p(_stream_handle(self.device) if stream is None else stream),
+                                                    C.byref(word)))
+        return int(word.value)
+
+    @staticmethod
+    def persistent_requirement(projection, m, k, n, nnz, bits, policy, dense_dtype, device_index, multiply=0,
+                               device_matrix=None, deterministic=False, persistent_limit_bytes=0, host_row_ptr=None,
+                               schedule: str | None = None) -> int:
+        """cb200_spmm_persistent_requirement: bytes a session reserves for the operation before sealing."""
+        pr = capi.header(capi.SpmmProblem())
+        pr.projection, pr.m, pr.k, pr.n, pr.nnz, pr.bits, pr.policy = projection, m, k, n, nnz, bits, policy
+        pr.dense_dtype = _TORCH_DENSE[dense_dtype] if isinstance(dense_dtype, torch.dtype) else dense_dtype
+        pr.device, pr.structure_epoch, pr.multiply, pr.deterministic = device_index, 1, multiply, int(deterministic)
+        pr.persistent_limit_bytes = persistent_limit_bytes
+        keep = None
+        if device_matrix is not None:
+            keep = device_matrix.desc()
+            pr.device_matrix = C.pointer(keep)
+        hrp = None
+        if host_row_ptr is not None:
+            hrp = np.ascontiguousarray(host_row_ptr, dtype=np.int64)
+            pr.host_row_ptr = hrp.ctypes.data
+        hint = schedule.encode() if schedule else None
+        pr.schedule_hint = hint
+        need = C.c_uint64()
+        capi.check(capi.lib().cb200_spmm_persistent_requirement(C.byref(pr), C.byref(need)))
+        del keep, hrp, hint
+        return int(need.value)
+
+    def make_launch(self, x, dense: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0, row_begin=0, row_end=capi.ALL_ROWS,
                     stream: int | None = None, epoch: int | None = None, epilogue: str | int = 0,
                     bias: torch.Tensor | None = None, value_generation: int = 0) -> capi.Launch:
         ln = capi.header(capi.Launch())
@@ -293,7 +341,7 @@ class PreparedSpmm:
 
 
 def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
-                 multiply: int = 0, epilogue: str | int = 0, bias: torch.Tensor | None = None):
+                 multiply: int = 0, epilogue: str | int = 0, bias: torch.Tensor | None = None, schedule: str | None = None):
     """Y = act(alpha * deq(X) W + beta * Y + bias) (one-shot convenience: prepare + run).
 
     epilogue names one of capi.EPILOGUE ("none", "bias", "relu", "gelu_erf", "gelu_tanh", "bias_relu", ...).
@@ -303,14 +351,14 @@ def spmm_forward(x: QuantizedCsr, w: torch.Tensor, out: torch.Tensor | None = No
     if out is None:
         out = torch.empty(x.rows, n, dtype=torch.float32, device=x.device)
     op = PreparedSpmm(capi.PROJECTION_CSR, x.rows, x.cols, n, x.nnz, x.bits, x.policy, w.dtype, x.device,
-                      host_row_ptr=x.host_row_ptr, multiply=multiply)
+                      host_row_ptr=x.host_row_ptr, multiply=multiply, schedule=schedule)
     op.run(x, w, out, alpha=alpha, beta=beta, epilogue=epilogue, bias=bias)
     op.close()
     return out
 
 
 def spmm_transpose(x: QuantizedCsr, g: torch.Tensor, out: torch.Tensor | None = None, alpha=1.0, beta=0.0,
-                   row_begin=0, row_end=0, multiply: int = 0, deterministic=False):
+                   row_begin=0, row_end=capi.ALL_ROWS, multiply: int = 0, deterministic=False):
     """G' = alpha * deq(X)^T G + beta * G'.
 
     multiply=capi.DTYPE_BF16 asks for tensor-core products (decoded values and G rounded to bf16);

@@ -30,7 +30,7 @@ extern "C" {
 #pragma GCC visibility push(default)
 #endif
 
-#define CB200_ABI_VERSION 1u
+#define CB200_ABI_VERSION 2u
 
 /* include/Cellerator/abi.h:14-21 (cellerator_status), extended with the operation-core
  * outcomes of operation_core.hh:118-131 that can cross this boundary. */
@@ -45,7 +45,13 @@ typedef enum cb200_status {
     CB200_STATUS_INSUFFICIENT_WORKSPACE = 7,
     CB200_STATUS_INVALID_STREAM = 8,
     CB200_STATUS_SEALED = 9,
-    CB200_STATUS_STALE_VALUE = 10 /* lifetime_validation_code::stale_value_generation, lifetimes.hh:88-94 */
+    CB200_STATUS_STALE_VALUE = 10, /* lifetime_validation_code::stale_value_generation, lifetimes.hh:88-94 */
+    /* a collective was asked for and the fleet's NCCL communicator is not ready (nccl_communicator.ready,
+     * include/Cellerator/dist/nccl_communicator.cuh:12-22); nothing falls back to another path */
+    CB200_STATUS_COMM_NOT_READY = 11,
+    /* a status query found the device status word of a launch set: a bounded wait inside a kernel ran out
+     * and the launch's output is not valid */
+    CB200_STATUS_DEVICE_WAIT_TIMEOUT = 12
 } cb200_status;
 
 /* execution::numeric_type, include/Cellerator/execution/operands.hh:9-20 (same values) */
@@ -129,6 +135,20 @@ int64_t cb200_build_uniform_block_row_ptr(int64_t rows, int64_t rows_per_block, 
 cb200_status cb200_get_block(int64_t rows, const int64_t *row_ptr, const int64_t *packed_row_ptr,
                              const int64_t *block_row_ptr, int64_t block_count, int64_t block_index,
                              cb200_csr_block *out);
+
+/* Element look-up on a matrix whose arrays are HOST pointers: find_in_row / get_code / get_value,
+ * include/Cellerator/quantized/access.cuh:47-79,133-153.  find_in_row scans the row from its start
+ * and returns the index of the first entry of `column` in col_idx, -1 when the row holds none or an
+ * argument is out of range.  get_code returns code `local_index` of the row's packed bytes.
+ * get_value is the decoded value of (row, column), 0 where nothing is stored or the pair lies
+ * outside the matrix (the reference's rule). */
+int64_t cb200_find_in_row(const cb200_qcsr *m, int64_t row, int64_t column);
+uint32_t cb200_get_code(const cb200_qcsr *m, int64_t row, int64_t local_index);
+float cb200_get_value(const cb200_qcsr *m, int64_t row, int64_t column);
+/* The same look-up for `count` (row, column) pairs of a DEVICE-resident matrix; rows, columns, values
+ * and codes (optional, -1 where nothing is stored) are device arrays.  Enqueues on `stream`. */
+cb200_status cb200_get_values(const cb200_qcsr *m, const int64_t *rows, const int32_t *columns, int64_t count,
+                              float *values, int32_t *codes, int32_t device, void *stream);
 
 /* Device codec over rows [row_begin,row_end) of a device-resident matrix.
  * launch_quantize_block / launch_dequantize_block, portable_backend.cuh:23-61 with
@@ -265,11 +285,34 @@ typedef struct cb200_spmm_problem {
      * does, so a launch that names another generation (cb200_launch.value_generation) is refused with
      * CB200_STATUS_STALE_VALUE instead of multiplying stale values. */
     uint64_t value_generation;
+    /* Optional request for one schedule by the name cb200_prepared_schedule reports ("gene_tiled",
+     * "warp_per_row", "tensor_windows", "tensor_blocked", "tensor_dense"; transpose: "tensor_blocked",
+     * "vector_reductions"; Blocked-ELL: "cuda_cores"); NULL or "" lets prepare choose from the shape and
+     * the row statistics.  A request the shape or the policy cannot serve is not an error: prepare
+     * keeps its own choice, and cb200_prepared_schedule tells which schedule runs.  This is the
+     * planner's lever (one candidate per schedule); nothing in the library reads the environment. */
+    const char *schedule_hint;
+    /* Session-owned persistent memory (prepared_operation.persistent is borrowed, OPERATION_CORE.md:17-25;
+     * the session reserves it before sealing, src/runtime/session_setup.cu.inc:111-140).  With
+     * persistent != NULL prepare places everything it keeps on the device inside
+     * [persistent, persistent + persistent_bytes), 256-byte aligned, and calls no cudaMalloc; the
+     * block must hold cb200_spmm_persistent_requirement(problem) bytes and must outlive the prepared
+     * operation, whose destroy call does not free it.  NULL: prepare allocates and destroy frees. */
+    void *persistent;
+    uint64_t persistent_bytes;
+    /* Stream prepare enqueues its kernels and copies on (cudaStream_t; NULL = the device's default
+     * stream).  Prepare waits for that stream before it returns, and for nothing else. */
+    void *prepare_stream;
 } cb200_spmm_problem;
 
 typedef struct cb200_prepared cb200_prepared;
 
 cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepared **out);
+/* Upper bound of the device bytes cb200_spmm_prepare would keep for this problem (0 when it keeps
+ * nothing): what a session reserves as persistent memory before sealing and hands over in
+ * cb200_spmm_problem.persistent.  Pure host arithmetic on the shape; the bound covers the padding of
+ * the window-blocked copy, so prepare never needs more. */
+cb200_status cb200_spmm_persistent_requirement(const cb200_spmm_problem *problem, uint64_t *bytes);
 void cb200_prepared_destroy(cb200_prepared *prepared);
 /* workspace_requirement, launch_bindings.hh:67-71 */
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
@@ -281,8 +324,17 @@ const char *cb200_prepared_schedule(const cb200_prepared *prepared);
 /* device bytes the prepared operation owns (row order, window-blocked copy): prepared_operation.persistent.bytes,
  * operation_core.hh:126-129,167-181; freed by cb200_prepared_destroy */
 uint64_t cb200_prepared_persistent_bytes(const cb200_prepared *prepared);
+/* rows x columns of the output a launch of this operation writes: m x n (forward, Blocked-ELL), k x n (transpose) */
+cb200_status cb200_prepared_output_shape(const cb200_prepared *prepared, uint64_t *rows, uint64_t *columns);
 
-/* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch. */
+#define CB200_ALL_ROWS (-1)
+
+/* launch_bindings, launch_bindings.hh:90-102: everything that changes per launch.
+ *
+ * Status word.  The kernels wait on barriers with a bound; when a bound runs out the launch ends early,
+ * its output is not valid, and the first 32-bit word of `workspace` is non-zero afterwards.  Every launch
+ * clears that word on its stream first.  cb200_spmm_run cannot report it (it returns before the kernels
+ * run): read it with cb200_prepared_status once the stream has passed the launch. */
 typedef struct cb200_launch {
     uint32_t version;
     size_t size;
@@ -296,7 +348,8 @@ typedef struct cb200_launch {
     float beta;
     uint64_t structure_epoch;
     int64_t row_begin;       /* rows [row_begin,row_end) of X; out rows are indexed by absolute row */
-    int64_t row_end;         /* 0,0 = all rows */
+    int64_t row_end;         /* CB200_ALL_ROWS (-1) = up to the last row; [r,r) is an empty shard: a forward
+                              * launch then writes nothing, a transpose scales G' by beta */
     void *stream;            /* stream_context, launch_bindings.hh:55-59 */
     int32_t device;
     int32_t workspace_device;
@@ -316,6 +369,14 @@ typedef struct cb200_launch {
 } cb200_launch;
 
 cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *launch);
+/* Reads the status word of the launches that used `workspace` (the transient_workspace of
+ * launch_bindings.hh:61-65): copies it to *host_word in stream order and waits for `stream`.  Returns
+ * CB200_STATUS_SUCCESS when the word is 0, CB200_STATUS_DEVICE_WAIT_TIMEOUT when a kernel gave up a
+ * bounded wait (the output of that launch is not valid; the context stays usable).  A binding calls
+ * it where it would synchronise anyway: after the last launch of a step, before results are used.
+ * A prepared operation whose schedule needs no workspace reports 0. */
+cb200_status cb200_prepared_status(const cb200_prepared *prepared, const void *workspace, void *stream,
+                                   int32_t *host_word);
 
 /* Number of kernel launches this library has enqueued since it was loaded (all threads). */
 uint64_t cb200_kernel_launch_count(void);
@@ -347,6 +408,11 @@ uint64_t cb200_kernel_launch_count(void);
  * w_dtype is CB200_DTYPE_BF16 or CB200_DTYPE_F32; x, w, y are device pointers on `device`. */
 cb200_status cb200_qcsr_forward_static(const cb200_qcsr *x, const void *w, int32_t w_dtype, int64_t n, float *y,
                                        int64_t y_ld, float alpha, float beta, int32_t device, void *stream);
+/* Status word of the last cb200_qcsr_forward_static call on `device` (it lives in the library's own
+ * array, which the caller cannot read): copied in stream order, then `stream` is waited for.  Same
+ * return convention as cb200_prepared_status; allocates nothing.  Before the first static call on the
+ * device there is nothing to read and the call returns CB200_STATUS_INVALID_ARGUMENT. */
+cb200_status cb200_qcsr_forward_static_status(int32_t device, void *stream, int32_t *host_word);
 
 /* ------------------------------------------------------------------------------------ */
 /* Runtime session.  runtime::execution_session, include/Cellerator/runtime/session.cuh:106-177:
@@ -584,6 +650,223 @@ cb200_status cb200_public_projection_forward(const cb200_public_layout *layout, 
 cb200_status cb200_public_projection_backward_rhs(const cb200_public_layout *layout, const float *grad_out,
                                                   int64_t grad_out_ld, int64_t out_cols, float *grad_rhs, int64_t grad_rhs_ld,
                                                   int32_t device, void *stream, void *scratch, uint64_t scratch_bytes);
+
+
+/* Status word of the last routed projection call that used `scratch` (its first 32-bit word, see
+ * cb200_launch): same convention as cb200_prepared_status. */
+cb200_status cb200_public_projection_status(const void *scratch, int32_t device, void *stream, int32_t *host_word);
+
+/* ------------------------------------------------------------------------------------------
+ * The backend-neutral SpMM request and its 128-bit signature: spmm_request, validate_spmm_request,
+ * classify_trivial_operation and make_operation_signature
+ * (include/Cellerator/compute/math/operation.hh:136-221, src/compute/math/operation.cc:119-292,
+ * src/compute/math/operation_signature.cc:30-68).  The signature is the key of the reference's plan
+ * cache; it never depends on a live address.  Field meanings and enum values are the reference's:
+ * type codes are real::value_* of include/Cellerator/types.cuh:150-158 (f16 3, f32 4, f64 5, bf16 6,
+ * fp8 7 / 8), layouts 1 row-major / 2 column-major, workspace kinds 1..3, reuse kinds 1..3,
+ * feature-order kinds 1 canonical / 2 packed, epilogue kinds as cb200_epilogue. */
+typedef struct cb200_feature_order_identity { /* operation.hh:87-94 */
+    uint32_t schema_version; /* 1 */
+    uint32_t kind;
+    uint32_t feature_count;
+    uint32_t feature_axis_identity_version;
+    uint64_t feature_axis_identity;
+    uint64_t packing_geometry_identity;
+} cb200_feature_order_identity;
+
+typedef struct cb200_scalar_value { /* operation.hh:104-108 */
+    uint32_t type_code;
+    uint32_t reserved;
+    uint64_t bits;
+} cb200_scalar_value;
+
+typedef struct cb200_spmm_request { /* operation.hh:136-164 */
+    uint32_t schema_version; /* 1 */
+    uint32_t operation;      /* 1 = spmm */
+    uint64_t m, k, n, sparse_nnz;
+    uint32_t structure_schema_version; /* sparse_structure_identity, operation.hh:98-102 */
+    uint32_t structure_identity_version;
+    uint64_t structure_value;
+    uint32_t transpose_sparse, transpose_dense;   /* 0 none, 1 transpose */
+    uint32_t dense_rhs_layout, output_layout;
+    uint64_t dense_rhs_leading_dimension, output_leading_dimension;
+    uint32_t sparse_storage_type_code, dense_storage_type_code, output_storage_type_code;
+    uint32_t compute_type_code, accumulation_type_code;
+    cb200_scalar_value alpha, beta;
+    uint32_t determinism;    /* 0 allow non-deterministic, 1 deterministic */
+    uint32_t workspace_kind, workspace_reserved;
+    uint64_t workspace_byte_limit;
+    uint32_t reuse_kind, reuse_reserved;
+    uint64_t reuse_expected_run_count;
+    uint32_t epilogue_kind, epilogue_bias_type_code;
+    uint64_t epilogue_bias_element_count;
+    cb200_feature_order_identity sparse_feature_order, dense_feature_order;
+} cb200_spmm_request;
+
+/* request_validation_code, operation.hh:63-80 (same values); 0 = ok */
+int32_t cb200_spmm_request_validate(const cb200_spmm_request *request);
+/* trivial_operation_kind, operation.hh:195-199: 0 none, 1 no output, 2 epilogue only */
+int32_t cb200_spmm_request_classify(const cb200_spmm_request *request);
+/* make_operation_signature: signature[0] = low, signature[1] = high */
+cb200_status cb200_spmm_request_signature(const cb200_spmm_request *request, uint64_t signature[2]);
+/* The request a prepared problem and one of its launches stand for (shapes, transposes, leading
+ * dimensions, type codes, alpha / beta, determinism, epilogue), with the identities the caller owns
+ * passed through: fills *request so that it validates and can be signed.  reuse: persistent. */
+cb200_status cb200_spmm_request_from_problem(const cb200_spmm_problem *problem, const cb200_launch *launch,
+                                             uint64_t structure_identity, uint64_t feature_axis_identity,
+                                             cb200_spmm_request *request);
+
+/* ------------------------------------------------------------------------------------------
+ * Host container of a quantized Blocked-ELL matrix: matrix::quantized_blocked_ell,
+ * include/Cellerator/matrix/quantized_blocked_ell.cuh:27-220.  One malloc slab holds, in this order,
+ * block_col_idx, the packed codes, column scales, column offsets and row offsets; pin registers the
+ * slab with the CUDA driver (cudaHostRegisterPortable) so that copies from it run asynchronously. */
+enum { CB200_QBELL_HOST_REGISTERED = 1u << 0 };
+typedef struct cb200_qbell_host {
+    uint32_t rows, cols, nnz, block_size, ell_cols, bits, row_stride_bytes, decode_policy, flags;
+    void *storage;
+    uint32_t *block_col_idx;
+    uint8_t *packed_values;
+    float *column_scales;
+    float *column_offsets;
+    float *row_offsets;
+} cb200_qbell_host;
+
+/* aux word of the container's serialised header, quantized_blocked_ell.cuh:27-48:
+ * (ell_width << 24) | (bits << 16) | block_size */
+uint64_t cb200_qbell_pack_aux(uint32_t bits, uint32_t block_size, uint64_t ell_width);
+void cb200_qbell_unpack_aux(uint64_t aux, uint32_t *bits, uint32_t *block_size, uint64_t *ell_width, uint32_t *ell_cols);
+/* quantized_blocked_ell_row_bytes / _aligned_row_bytes (quantized_blocked_ell.cuh:50-66); alignment <= 1: no padding */
+uint32_t cb200_qbell_row_bytes(uint32_t bits, uint32_t ell_cols);
+uint32_t cb200_qbell_aligned_row_bytes(uint32_t bits, uint32_t ell_cols, uint32_t alignment);
+/* init: row_stride_bytes 0 = aligned_row_bytes(bits, ell_cols, 16) */
+void cb200_qbell_host_init(cb200_qbell_host *m, uint32_t rows, uint32_t cols, uint32_t nnz, uint32_t block_size,
+                           uint32_t ell_cols, uint32_t bits, uint32_t decode_policy, uint32_t row_stride_bytes);
+uint64_t cb200_qbell_host_bytes(const cb200_qbell_host *m); /* sizeof(*m) + the slab */
+int32_t cb200_qbell_host_allocate(cb200_qbell_host *m);     /* 1 ok, 0 out of memory; frees what it held */
+int32_t cb200_qbell_host_pin(cb200_qbell_host *m);          /* 1 registered (or nothing to register), 0 refused */
+void cb200_qbell_host_unpin(cb200_qbell_host *m);
+void cb200_qbell_host_clear(cb200_qbell_host *m);
+/* the container as a cb200_qbell whose arrays are the slab's HOST pointers (offsets follow decode_policy) */
+cb200_status cb200_qbell_host_view(const cb200_qbell_host *m, cb200_qbell *view);
+/* Copies the slab to `device_storage` (device memory of cb200_qbell_host_bytes(m) - sizeof(*m) bytes, 256-byte
+ * aligned) with one cudaMemcpyAsync on `stream` and fills *device_view with the device addresses of the
+ * five arrays, which keep the slab's offsets. */
+cb200_status cb200_qbell_host_upload(const cb200_qbell_host *m, void *device_storage, uint64_t device_bytes,
+                                     int32_t device, void *stream, cb200_qbell *device_view);
+
+/* ------------------------------------------------------------------------------------------
+ * Multi-GPU layer.  fleet_context (src/compute/runtime/runtime.hh:47-87, runtime.cu:96-199): the
+ * devices of one process as numbered slots, one stream per slot, peer access, grow-only scratch per
+ * slot, and the NCCL communicator (nccl_communicator, init_local_nccl_communicator /
+ * init_ranked_nccl_communicator, communicator_allreduce:
+ * include/Cellerator/dist/nccl_communicator.cuh:12-22,109-156,290-315).  Two ways to build one:
+ *   - one process, several GPUs (the reference's default): slots = devices[], communicator from
+ *     ncclCommInitAll over them; world_size is the slot count;
+ *   - one process per GPU: one slot, world_size / world_rank of the job and the 128-byte NCCL unique id
+ *     that rank 0 made with cb200_fleet_unique_id and the launcher distributed (ncclCommInitRank).
+ * NCCL is loaded at run time (dlopen of libnccl.so.2, or of options.nccl_library): a process that
+ * already holds a copy shares it.  When the library or the communicator cannot be had the fleet is
+ * still created, cb200_fleet_communicator_ready reports 0, and every call that needs a collective
+ * returns CB200_STATUS_COMM_NOT_READY: nothing falls back to peer copies behind the caller's back
+ * (the reference's reduce does, src/compute/runtime/reduce.cu:228-294).  No lock anywhere: one thread
+ * drives a fleet, as in the reference. */
+typedef struct cb200_fleet cb200_fleet;
+
+typedef struct cb200_fleet_options {
+    uint32_t version;
+    size_t size;
+    int32_t device_count;       /* local slots, 1..16 */
+    const int32_t *devices;     /* CUDA ordinals; NULL = 0 .. device_count-1 */
+    void *const *streams;       /* optional caller streams, one per slot; NULL = the fleet creates non-blocking ones */
+    int32_t enable_peer_access; /* cudaDeviceEnablePeerAccess between the slots (discover_fleet's default) */
+    int32_t world_size;         /* 0 = device_count (single process) */
+    int32_t world_rank;         /* rank of slot 0; slot i has rank world_rank + i */
+    const void *nccl_unique_id; /* 128 bytes; NULL with world_size == device_count: ncclCommInitAll */
+    const char *nccl_library;   /* NULL = "libnccl.so.2" */
+} cb200_fleet_options;
+
+/* ncclGetUniqueId: 128 bytes for the launcher to hand to every rank */
+cb200_status cb200_fleet_unique_id(const char *nccl_library, void *unique_id_128);
+cb200_status cb200_fleet_create(const cb200_fleet_options *options, cb200_fleet **out);
+void cb200_fleet_destroy(cb200_fleet *fleet);
+int32_t cb200_fleet_slot_count(const cb200_fleet *fleet);
+int32_t cb200_fleet_world_size(const cb200_fleet *fleet);
+int32_t cb200_fleet_device(const cb200_fleet *fleet, uint32_t slot);           /* fleet_device_id; -1 = no such slot */
+void *cb200_fleet_stream(const cb200_fleet *fleet, uint32_t slot);             /* fleet_stream */
+int32_t cb200_fleet_communicator_ready(const cb200_fleet *fleet);              /* nccl_communicator.ready */
+/* request_fleet_scratch, runtime.cu: device memory of the slot, at least `bytes`, kept until destroy; grows by
+ * reallocation (contents are not kept), so ask for the largest size before the first launch */
+cb200_status cb200_fleet_request_scratch(cb200_fleet *fleet, uint32_t slot, uint64_t bytes, void **scratch);
+cb200_status cb200_fleet_synchronize(cb200_fleet *fleet, const uint32_t *slots, uint32_t slot_count); /* synchronize_slots */
+
+/* Row ranges of `parts` shards: the reference's uniform rule (build_uniform_block_row_ptr with
+ * rows_per_block = ceil(rows / parts), layout.cuh:131-157) read back through get_block
+ * (access.cuh:7-44), padded with empty trailing shards when rows do not fill every part, so that
+ * shard i belongs to rank i.  row_ptr / packed_row_ptr are HOST arrays (packed_row_ptr NULL: equal to
+ * row_ptr, the 8-bit case).  blocks has `parts` entries. */
+cb200_status cb200_fleet_partition(int64_t rows, int32_t parts, const int64_t *row_ptr, const int64_t *packed_row_ptr,
+                                   cb200_csr_block *blocks);
+
+/* dist::launch_csr_spmm_fwd_f16_f32 (src/compute/sparse/project/project.cu:321-341): the forward
+ * projection of every listed slot, each on its slot's device and stream (launches[i].device and
+ * .stream are overwritten with the slot's), no collective, no host synchronisation. */
+cb200_status cb200_fleet_run_forward(cb200_fleet *fleet, const uint32_t *slots, uint32_t slot_count,
+                                     cb200_prepared *const *prepared, cb200_launch *launches);
+/* dist::launch_csr_spmm_bwd_rhs_f16_f32 + dist::reduce_sum_to_leader_f32
+ * (src/compute/sparse/ops/kernels/dist_sparse.cu:24-32,177-197, src/compute/runtime/reduce.cu:147-294):
+ * every listed slot computes its k x n partial of G' into launches[i].out, then ONE
+ * ncclAllReduce(float32, sum) per slot over k*n floats (out_ld must equal n), in place, grouped, on the
+ * slots' streams, so that every rank of the job ends with the sum.  Stream order carries the dependency:
+ * no host synchronisation before the collective (the reference has one, reduce.cu:164).  A job of one
+ * rank needs no communicator.  Otherwise a communicator that is not ready -> CB200_STATUS_COMM_NOT_READY
+ * before any kernel is enqueued. */
+cb200_status cb200_fleet_run_transpose(cb200_fleet *fleet, const uint32_t *slots, uint32_t slot_count,
+                                       cb200_prepared *const *prepared, cb200_launch *launches);
+/* reduce_sum_to_leader_f32 as an all-reduce: outs[i] = sum over the job's ranks of partials[i]
+ * (count floats, device pointers of the slots; outs[i] may equal partials[i]). */
+cb200_status cb200_fleet_allreduce_sum_f32(cb200_fleet *fleet, const uint32_t *slots, uint32_t slot_count,
+                                           const float *const *partials, float *const *outs, uint64_t count);
+
+/* ------------------------------------------------------------------------------------------
+ * Forward projection from HOST buffers: the call of a caller whose matrix lives in host memory
+ * (the reference's models and the public ABI copy their operands in before every projection,
+ * src/abi/abi.cu:278-340).  The stage owns device buffers for `chunk_count` row chunks in flight and
+ * three streams; a run cuts the row range into chunks of about rows / chunks_per_run rows, copies
+ * chunk i+1 in (one cudaMemcpyAsync per array) while chunk i is multiplied and chunk i-1's rows of Y
+ * are copied out.  Everything crosses PCIe inside the call; pinned host memory makes the copies
+ * asynchronous.  The operation behind it is prepared without the matrix (CSR schedules that read the
+ * arrays at launch), because the values arrive with the call. */
+typedef struct cb200_host_stage cb200_host_stage;
+
+typedef struct cb200_host_stage_options {
+    uint32_t version;
+    size_t size;
+    int32_t device;
+    int64_t k, n;
+    int32_t bits, policy, dense_dtype, multiply;
+    int64_t max_chunk_rows;   /* rows one device chunk buffer holds */
+    int64_t max_chunk_nnz;    /* stored entries one device chunk buffer holds */
+    int32_t chunk_buffers;    /* chunks in flight, 2..4 */
+} cb200_host_stage_options;
+
+cb200_status cb200_host_stage_create(const cb200_host_stage_options *options, cb200_host_stage **out);
+void cb200_host_stage_destroy(cb200_host_stage *stage);
+uint64_t cb200_host_stage_device_bytes(const cb200_host_stage *stage);
+/* x: HOST arrays (row_ptr, col_idx, packed_values, packed_row_ptr for 4-bit codes, scales, offsets);
+ * w: k x n HOST (dense_dtype), y: rows x n HOST fp32.  Returns after the last copy has landed in y
+ * (it waits for its own streams).  h2d_bytes / d2h_bytes (optional) receive the bytes moved. */
+cb200_status cb200_host_forward(cb200_host_stage *stage, const cb200_qcsr *x, const void *w, int64_t w_ld, float *y,
+                                int64_t y_ld, float alpha, uint64_t *h2d_bytes, uint64_t *d2h_bytes);
+
+/* ------------------------------------------------------------------------------------------
+ * Test hook (no counterpart in the reference).  Makes the bounded waits of the tensor-core forward
+ * kernel over the window-blocked copy observable: while armed, that kernel's W loader issues no
+ * copies and every wait of the launch gives up after `poll_limit` polls, so the launch ends within
+ * microseconds with the status word set, its TMEM freed and its output invalid.  The next launch after
+ * cb200_test_disarm_wait_timeout is a normal one.  poll_limit is clamped to [64, 2^22]. */
+void cb200_test_arm_wait_timeout(uint32_t poll_limit);
+void cb200_test_disarm_wait_timeout(void);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

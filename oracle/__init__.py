@@ -25,17 +25,32 @@ EPILOGUE = {"none": 0, "bias": 1, "relu": 2, "gelu_erf": 3, "gelu_tanh": 4, "bia
             "bias_gelu_erf": 6, "bias_gelu_tanh": 7}
 
 
+def reference_root() -> str | None:
+    """The Cellerator source tree to compile the reference from: the directory CELLERATOR_REFERENCE names, else
+    a checkout called `reference` beside this repository.  None when neither holds the Cellerator headers."""
+    beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    for root in (os.environ.get("CELLERATOR_REFERENCE", ""), beside):
+        if root and os.path.isdir(os.path.join(root, "include", "Cellerator")):
+            return os.path.abspath(root)
+    return None
+
+
 def build(ref: bool | None = None) -> None:
     """Compile liboracle.so, and the reference shim when the reference tree is present."""
     targets = ["all"]
+    root = reference_root()
     if ref is None:
-        ref = os.path.isdir(os.environ.get("CB200_REFERENCE", "/root/reference"))
+        ref = root is not None
+    env = dict(os.environ)
     if ref:
+        if root is None:
+            raise FileNotFoundError("no Cellerator source tree: set CELLERATOR_REFERENCE")
+        env["REFERENCE"] = root
         targets.append("ref")
         product = os.path.join(os.path.dirname(_HERE), "cellerator_b200", "lib", "libcellerator_b200.so")
         if os.path.exists(product):
-            targets.append("conformance")   # the reference's operation core driving the backend
-    subprocess.run(["make", "-C", _HERE, *targets], check=True, capture_output=True)
+            targets.append("conformance")   # the reference's operation core and planner driving the backend
+    subprocess.run(["make", "-C", _HERE, *targets], check=True, capture_output=True, env=env)
 
 
 def _p(a, ctype):
@@ -237,6 +252,14 @@ class Oracle(_Base):
             build(ref=False)
         super().__init__(ORACLE_LIB)
 
+    def request_contract(self, fields):
+        """fields: the 48 values of a spmm_request in declaration order -> (validation code, trivial kind, low, high)"""
+        f = np.ascontiguousarray(fields, dtype=np.uint64)
+        assert f.size == 48
+        out = np.zeros(4, dtype=np.uint64)
+        self._fn("request_contract", None)(_p(f, C.c_uint64), _p(out, C.c_uint64))
+        return tuple(int(v) for v in out)
+
     def _digest(self, v, out):
         self._fn("digest_f32", None)(_p(v, C.c_float), C.c_uint64(v.shape[0]), C.c_uint64(v.shape[1]),
                                      C.c_uint64(v.shape[1]), C.c_uint32(4), _p(out, C.c_uint64))
@@ -391,6 +414,14 @@ class Reference(_Base):
     @staticmethod
     def available():
         return os.path.exists(REF_LIB)
+
+    def request_contract(self, fields):
+        """fields: the 48 values of a spmm_request in declaration order -> (validation code, trivial kind, low, high)"""
+        f = np.ascontiguousarray(fields, dtype=np.uint64)
+        assert f.size == 48
+        out = np.zeros(4, dtype=np.uint64)
+        self._fn("request_contract", None)(_p(f, C.c_uint64), _p(out, C.c_uint64))
+        return tuple(int(v) for v in out)
 
     def _digest(self, v, out):
         self._fn("digest_f32", None)(_p(v, C.c_float), C.c_uint64(v.shape[0]), C.c_uint64(v.shape[1]),

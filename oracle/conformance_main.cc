@@ -516,14 +516,13 @@ int main(int argc, char **argv) {
         ts.projection_kind = CB200_PROJECTION_TRANSPOSE;
         ts.device_matrix = &dm;
         ts.device_matrix_generation = {5u}; // the generation of `plane`
+        ts.schedule_hint = "tensor_blocked"; // the matrix is far below the size prepare would pick it for
         host::register_projection(ts);
-        setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked", 1); // the matrix is far below the size prepare would pick it for
         core::prepared_operation pt{};
         core::prepare_policy with_preprocessing;
         with_preprocessing.allow_persistent_preprocessing = true;
         st = core::prepare_candidate(*tr, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32),
                                      with_preprocessing, &pt);
-        unsetenv("CB200_TRANSPOSE_SCHEDULE");
         CHECK(static_cast<bool>(st), "prepare_candidate(transpose, matrix handed to prepare)");
         if (!st) std::printf("  message: %s\n", st.message);
         CHECK(std::strcmp(host::prepared_schedule(pt), "tensor_blocked_x3") == 0, "fp32 products + matrix at prepare -> split-product tensor schedule");

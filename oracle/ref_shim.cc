@@ -240,8 +240,41 @@ int ref_spmm_reference(std::uint64_t m, std::uint64_t k, std::uint64_t n, int tr
     return static_cast<int>(status.code);
 }
 
-// make_operation_signature of the request used by tests/math_operation_contract_test.cc is
-// checked by the reference's own test; here only the digest helper is exported.
+// The reference's request contract on a request handed over as 48 unsigned 64-bit fields in the
+// declaration order of spmm_request (operation.hh:136-164; 32-bit fields widened, the two scalar and the
+// two reserved words included as they lie): out[0] = validate_spmm_request code, out[1] =
+// classify_trivial_operation kind, out[2], out[3] = make_operation_signature low, high.
+void ref_request_contract(const std::uint64_t *f, std::uint64_t out[4]) {
+    cm::spmm_request r;
+    int i = 0;
+    const auto u32 = [&]() { return static_cast<cm::u32>(f[i++]); };
+    const auto u64 = [&]() { return f[i++]; };
+    r.schema_version = u32(); r.operation = static_cast<cm::operation_kind>(u32());
+    r.m = u64(); r.k = u64(); r.n = u64(); r.sparse_nnz = u64();
+    r.sparse_structure.schema_version = u32(); r.sparse_structure.identity_version = u32(); r.sparse_structure.value = u64();
+    r.transpose_sparse = static_cast<cm::transpose_kind>(u32()); r.transpose_dense = static_cast<cm::transpose_kind>(u32());
+    r.dense_rhs_layout = static_cast<cm::dense_layout_kind>(u32()); r.output_layout = static_cast<cm::dense_layout_kind>(u32());
+    r.dense_rhs_leading_dimension = u64(); r.output_leading_dimension = u64();
+    r.sparse_storage_type_code = u32(); r.dense_storage_type_code = u32(); r.output_storage_type_code = u32();
+    r.compute_type_code = u32(); r.accumulation_type_code = u32();
+    r.alpha.type_code = u32(); r.alpha.reserved = u32(); r.alpha.bits = u64();
+    r.beta.type_code = u32(); r.beta.reserved = u32(); r.beta.bits = u64();
+    r.determinism = static_cast<cm::determinism_requirement>(u32());
+    r.workspace.kind = static_cast<cm::workspace_policy_kind>(u32()); r.workspace.reserved = u32(); r.workspace.byte_limit = u64();
+    r.reuse.kind = static_cast<cm::expected_reuse_kind>(u32()); r.reuse.reserved = u32(); r.reuse.expected_run_count = u64();
+    r.epilogue.kind = static_cast<cm::epilogue_kind>(u32()); r.epilogue.bias_type_code = u32(); r.epilogue.bias_element_count = u64();
+    for (cm::feature_order_identity *o : {&r.sparse_feature_order, &r.dense_feature_order}) {
+        o->schema_version = u32(); o->kind = static_cast<cm::feature_order_kind>(u32()); o->feature_count = u32();
+        o->feature_axis_identity_version = u32(); o->feature_axis_identity = u64(); o->packing_geometry_identity = u64();
+    }
+    const cm::operation_signature sig = cm::make_operation_signature(r);
+    out[0] = static_cast<std::uint64_t>(cm::validate_spmm_request(r).code);
+    out[1] = static_cast<std::uint64_t>(cm::classify_trivial_operation(r));
+    out[2] = sig.low;
+    out[3] = sig.high;
+}
+
+// digest helper of the referee
 void ref_digest_f32(const float *values, std::uint64_t rows, std::uint64_t columns, std::uint64_t ld,
                     std::uint64_t out[2]) {
     const cm::logical_dense_view view{values, rows, columns, ld, cm::dense_layout_kind::row_major,

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the UNMODIFIED reference sources.
 
-Run on a machine that has the Cellerator tree (the Makefile's REFERENCE, or CB200_REFERENCE):
+Run on a machine that has the Cellerator tree (CELLERATOR_REFERENCE, or a checkout called `reference` beside this repository):
 
     make -C oracle ref && python tests/golden/make_golden.py
 

@@ -54,7 +54,7 @@ FORWARD_CASES = [
 
 @pytest.mark.parametrize("schedule,dtype,n,multiply,hand_matrix,tol", FORWARD_CASES)
 def test_forward_epilogues(cuda_device, oracle, monkeypatch, schedule, dtype, n, multiply, hand_matrix, tol):
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule.split("_x")[0])
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule.split("_x")[0])
     rng = np.random.default_rng(len(schedule) * 131 + n)
     rows, cols, bits, policy = 2 * 1024 + 77, 900, 8, 1
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=280, bits=bits, policy=policy))

@@ -161,7 +161,7 @@ def test_gene_tiled_schedule(cuda_device, oracle, monkeypatch, bits, dtype, n, p
     """The shared-memory-staged kernel, forced on a small matrix that still spans several gene
     tiles, several row groups per CTA and a ragged last group; bit-identical across row ranges
     and to a second run, and the bounded-wait status word stays 0."""
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", "gene_tiled")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "gene_tiled")
     rng = np.random.default_rng(31 * bits + n + policy)
     rows, cols = 128 * 3 + 37, 4100
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=700, bits=bits, policy=policy))
@@ -184,7 +184,7 @@ def test_gene_tiled_schedule(cuda_device, oracle, monkeypatch, bits, dtype, n, p
     y1 = op.run(x, w, y0.clone(), alpha=2.0, beta=0.5)
     assert torch.allclose(y1, 2.0 * y + 0.5 * y0, rtol=1e-5, atol=1e-6)
     # the warp-per-row kernel agrees to rounding (different summation order)
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", "warp_per_row")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "warp_per_row")
     op2 = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, bits, policy, w.dtype, cuda_device)
     assert op2.schedule == "warp_per_row"
     y2 = op2.run(x, w, torch.empty_like(y))

@@ -42,7 +42,7 @@ BLOCKED = ("tensor_blocked", "tensor_dense")          # schedules that need the 
 def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits, n, policy):
     """Forced on a small matrix: several row groups (ragged last one, empty rows), a ragged last
     gene window, row starts at every alignment; row ranges, alpha/beta, determinism."""
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule)
     rng = np.random.default_rng(77 * bits + n + policy)
     rows, cols = 512 * 2 + 171, 1000
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=300, bits=bits, policy=policy))
@@ -152,9 +152,9 @@ def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule
     # 4,000-gene one the dense tiles; the other combinations are forced
     own = {8: "tensor_blocked", 4: "tensor_dense"}[bits]
     if schedule != own:
-        monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)
+        monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule)
     op = prepared(x, n, w1, cuda_device, blocked=schedule in BLOCKED)
-    monkeypatch.delenv("CB200_FWD_SCHEDULE", raising=False)
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, None)
     assert op.schedule == schedule
     y1 = op.run(x, w1, torch.empty(x.rows, n, device=cuda_device))
     torch.cuda.synchronize()
@@ -208,7 +208,7 @@ def test_split_products_meet_the_fp32_bound(cuda_device, oracle, monkeypatch, dt
     product from bf16 pieces (two passes for a bf16 W, three for an fp32 W) and meets the bound of
     the exact kernels, 1e-4 * ||row||_1 * max|W|; repeatable, alpha / beta, row ranges."""
     from gpu_util import assert_forward_close
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", "tensor_blocked")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "tensor_blocked")
     rng = np.random.default_rng(5 * bits + n + policy)
     rows, cols = 256 * 3 + 99, 900
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=260, bits=bits, policy=policy))
@@ -240,7 +240,7 @@ def test_split_products_meet_the_fp32_bound(cuda_device, oracle, monkeypatch, dt
 def test_value_generation_is_checked_by_operations_that_keep_values(cuda_device, oracle, monkeypatch):
     """The reference does not freeze values in prepared state; an operation that keeps a copy of them
     (window-blocked copy, dense tiles) refuses a launch that names another value generation."""
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", "tensor_blocked")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "tensor_blocked")
     rng = np.random.default_rng(2)
     c = host_pack(oracle, random_csr(rng, rows=600, cols=400, max_nnz=100, bits=8, policy=1))
     x = to_dev(c, cuda_device)
@@ -252,7 +252,7 @@ def test_value_generation_is_checked_by_operations_that_keep_values(cuda_device,
     with pytest.raises(capi.Cb200Error, match="value generation"):
         op.run(x, w, y, value_generation=8)
     op.close()
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", "gene_tiled")      # reads the codes at launch: any generation
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "gene_tiled")      # reads the codes at launch: any generation
     exact = ops.PreparedSpmm(capi.PROJECTION_CSR, 600, 400, 64, x.nnz, 8, 1, w.dtype, cuda_device, value_generation=7)
     exact.run(x, w, y, value_generation=8)
     exact.close()

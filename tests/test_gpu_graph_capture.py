@@ -35,7 +35,7 @@ def capture_and_replay(op, x, d, out, stream, **kw):
 
 @pytest.mark.parametrize("schedule,multiply", [("warp_per_row", 0), ("gene_tiled", 0), ("tensor_blocked", capi.DTYPE_BF16)])
 def test_forward_schedules_are_capturable(cuda_device, oracle, monkeypatch, schedule, multiply):
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", schedule)
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule)
     rng = np.random.default_rng(len(schedule))
     rows, cols, n = 256 * 20, 700, 64
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=90, bits=8))
@@ -54,7 +54,7 @@ def test_forward_schedules_are_capturable(cuda_device, oracle, monkeypatch, sche
 @pytest.mark.parametrize("mode", ["vector_reductions", "tensor_blocked", "gene_gather"])
 def test_transpose_schedules_are_capturable(cuda_device, oracle, monkeypatch, mode):
     if mode == "tensor_blocked":
-        monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+        monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_TRANSPOSE, "tensor_blocked")
     rng = np.random.default_rng(len(mode))
     rows, cols, n = 256 * 6, 500, 64
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=80, bits=8))

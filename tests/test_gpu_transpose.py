@@ -124,7 +124,7 @@ def test_tensor_transpose_parity(cuda_device, oracle, monkeypatch, bits, n, poli
     """The tcgen05 schedule over the window-blocked copy, forced on a small matrix: several row
     groups, more than one set of eight gene windows with a ragged last set and a ragged last window,
     row ranges (rows outside the range contribute nothing), alpha / beta."""
-    monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_TRANSPOSE, "tensor_blocked")
     rng = np.random.default_rng(91 * bits + n + policy)
     rows, cols = 256 * 5, 1300
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=200, bits=bits, policy=policy))
@@ -191,7 +191,7 @@ def test_tensor_transpose_split_products_meet_the_fp32_bound(cuda_device, oracle
     """fp32 products requested and the matrix handed to prepare: three bf16 passes (hi*hi + hi*lo +
     lo*hi) rebuild each product; the result meets the fp32 bound 1e-4 * ||gene column||_1 * max|G|
     with a wide margin, also on a row range and with alpha / beta."""
-    monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_TRANSPOSE, "tensor_blocked")
     rng = np.random.default_rng(17 * bits + policy)
     rows, cols, n = 256 * 4, 1100, 64
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=220, bits=bits, policy=policy))
@@ -224,7 +224,7 @@ def test_tensor_transpose_respects_the_memory_limit(cuda_device, oracle, monkeyp
     """persistent_limit_bytes with room for one word per entry but not two: the split passes decode
     the code words at launch and still meet the fp32 bound; below one word per entry the exact
     kernel runs.  The limit is prepare_policy.persistent_memory_limit of the reference."""
-    monkeypatch.setenv("CB200_TRANSPOSE_SCHEDULE", "tensor_blocked")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_TRANSPOSE, "tensor_blocked")
     rng = np.random.default_rng(91)
     rows, cols, n = 256 * 3, 900, 64
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=200, bits=8, policy=1))

@@ -31,7 +31,7 @@ def forward_static(x, w, y, alpha=1.0, beta=0.0):
 
 @pytest.mark.parametrize("bits,dtype,n", [(8, torch.bfloat16, 64), (4, torch.bfloat16, 128), (8, torch.float32, 32)])
 def test_static_scratch_entry_matches_prepared_entry_twice(cuda_device, oracle, monkeypatch, bits, dtype, n):
-    monkeypatch.setenv("CB200_FWD_SCHEDULE", "gene_tiled")
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "gene_tiled")
     rng = np.random.default_rng(900 + bits + n)
     rows, cols = 128 * 2 + 19, 2600
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=500, bits=bits, policy=1))
