@@ -530,9 +530,11 @@ cb200_status launch_qcsr_transpose_gather(const qcsr_view &x, const dense_args &
     const int vec = static_cast<int>(d.n / 32);
     p.aligned = (reinterpret_cast<std::uintptr_t>(d.dense) % (4u * vec) == 0u) && ((d.dense_ld * 4) % (4 * vec) == 0) ? 1 : 0;
     p.alpha = d.alpha; p.beta = d.beta;
-    p.queue = static_cast<unsigned *>(workspace);
+    // word 0 of the workspace is the status word every schedule keeps there (this kernel waits on nothing, so it
+    // stays 0); the gene queue is the word at byte 64
+    p.queue = static_cast<unsigned *>(workspace) + 16;
     p.gene_order = layout.gene_order;
-    CB200_CUDA_OK(cudaMemsetAsync(workspace, 0, 4, stream));
+    CB200_CUDA_OK(cudaMemsetAsync(workspace, 0, 128, stream));
     const unsigned grid = static_cast<unsigned>(std::min<std::int64_t>(x.cols, static_cast<std::int64_t>(sm_count) * 8));
     if (d.dense_ld < 0 || d.dense_ld >= (std::int64_t{1} << 30))
         return fail(CB200_STATUS_UNSUPPORTED, "the order-fixed transpose takes rows of G below 4 GB");

@@ -487,7 +487,10 @@ __host__ __device__ constexpr int w2_stages(int n) {
                : (232448 - 2 * kABufBytes - 2 * kRing2 * kChunk2Bytes - 1024) / (n * kWin * 2);
 }
 
-template<int NC>
+// TEST_HOOK: the instantiation cb200_test_arm_wait_timeout selects.  It differs in two places only: the poll limit
+// of the waits comes from the launch (a few thousand instead of 2^22) and the W loader issues no copies, so
+// that the waits for W run out.  Everything that happens after a wait has run out is common code.
+template<int NC, bool TEST_HOOK>
 __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const blocked_params p) {
     constexpr int REC = record_bytes(NC);   // distance of the W records in global memory
     constexpr int WREC = NC * kWin * 2;     // the W part of a record (the decode table is not needed)
@@ -514,7 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int limit = p.poll_limit;
+    const int limit = TEST_HOOK ? p.poll_limit : kPollLimit;
     const std::uint32_t smem0 = smem_addr(smem);
     const std::uint32_t wstage0 = smem0 + 2 * kABufBytes;
     const std::uint32_t chunk0 = wstage0 + STAGES * WREC;
@@ -616,6 +619,10 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     } else if (warp == kProducerWarps) {
         // ================= MMA issuer =================
         long long q = 0;
+        // The issue path is kept as short as it can be: a vote and a branch per window to stop early after a wait
+        // has run out cost 0.7 ms of 6.3 on the 1M x 33,538 matrix.  After an abort the remaining windows are
+        // therefore still issued (on stale tiles, into this CTA's own TMEM; the waits return at once) and only
+        // the end of the role looks at the flag.
         for (std::int64_t g = 0; g < my_groups; ++g) {
             bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((g & 1) ^ 1), abort_flag, limit);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -625,7 +632,6 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag, limit);
                 bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag, limit);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (*abort_flag != 0) break; // a wait ran out: nothing more is multiplied
                 if (lane == 0) {
                     const std::uint32_t a_tile = smem0 + b * kABufBytes;
                     const std::uint32_t b_tile = wstage0 + s * WREC;
@@ -644,28 +650,27 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 }
                 __syncwarp();
             }
-            if (*abort_flag != 0) break;
         }
         // after an abort: the MMAs already issued finish before the CTA frees its TMEM and shared memory
-        if (*abort_flag != 0 && lane == 0) {
+        if (lane == 0 && *abort_flag != 0) {
             mma_commit(smem_addr(mma_drain));
             bar_wait_drain(smem_addr(mma_drain), 0u, limit);
         }
         __syncwarp();
     } else if (warp == kProducerWarps + 1) {
         // ================= W loader =================
-        if (lane == 0 && p.withhold_w == 0) {
+        if (lane == 0 && !(TEST_HOOK && p.withhold_w != 0)) {
             const long long total = my_groups * p.windows;
             long long q = 0;
             for (; q < total; ++q) {
                 const int s = static_cast<int>(q % STAGES);
-                bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag, limit);
-                if (*abort_flag != 0) break; // no new copies once a wait of the CTA has run out
+                // no new copies once a wait of the CTA has run out
+                if (bar_wait(smem_addr(w_empty + s), static_cast<std::uint32_t>(((q / STAGES) & 1) ^ 1), abort_flag, limit)) break;
                 bar_arrive_expect_tx(smem_addr(w_full + s), WREC);
                 bulk_copy_g2s(wstage0 + s * WREC, p.records + static_cast<std::size_t>(q % p.windows) * REC, WREC, smem_addr(w_full + s));
             }
             // after an abort: let the copies still in flight land (the last one issued into each stage)
-            if (*abort_flag != 0)
+            if (q < total)
                 for (long long last = q - 1; last >= 0 && last > q - 1 - STAGES; --last)
                     bar_wait_drain(smem_addr(w_full + static_cast<int>(last % STAGES)), static_cast<std::uint32_t>((last / STAGES) & 1), limit);
         }
@@ -673,27 +678,24 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
         // ================= entry chunks: window q goes to the ring of scatter group q & 1 =================
         long long q = 0;
         long long qc0 = 0, qc1 = 0; // chunks issued into each ring
-        int stop = 0;
-        for (std::int64_t gi = 0; gi < my_groups && stop == 0; ++gi) {
+        bool dead = false; // lane 0: a wait was given up, no copy is issued any more (the loops run out empty)
+        for (std::int64_t gi = 0; gi < my_groups; ++gi) {
             const std::int64_t seg0 = (first_group + gi * gridDim.x) * p.windows;
-            for (int wbase = 0; wbase < p.windows && stop == 0; wbase += 31) {
+            for (int wbase = 0; wbase < p.windows; wbase += 31) {
                 const int span = min(31, p.windows - wbase); // segment bounds of up to 31 windows in one coalesced read
                 const std::int64_t bound = lane <= span ? __ldg(p.seg_ptr + seg0 + wbase + lane) : 0;
-                for (int j = 0; j < span && stop == 0; ++j, ++q) {
+                for (int j = 0; j < span; ++j, ++q) {
                     const std::int64_t lo = __shfl_sync(0xffffffffu, bound, j), hi = __shfl_sync(0xffffffffu, bound, j + 1);
                     const int ring = static_cast<int>(q & 1);
                     std::int64_t at = lo;
                     do {
                         const int count = static_cast<int>(min(static_cast<std::int64_t>(kChunk2Entries), hi - at));
                         const long long mine = ring == 0 ? qc0 : qc1;
-                        if (lane == 0) {
+                        if (lane == 0 && !dead) {
                             const int cs = ring * kRing2 + static_cast<int>(mine % kRing2);
-                            bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((mine / kRing2) & 1) ^ 1), abort_flag, limit);
-                            if (*abort_flag != 0) stop = 1; // no new copies once a wait of the CTA has run out
+                            dead = bar_wait(smem_addr(c_empty + cs), static_cast<std::uint32_t>(((mine / kRing2) & 1) ^ 1), abort_flag, limit);
                         }
-                        stop = __shfl_sync(0xffffffffu, stop, 0);
-                        if (stop != 0) break;
-                        if (lane == 0) {
+                        if (lane == 0 && !dead) {
                             const int cs = ring * kRing2 + static_cast<int>(mine % kRing2);
                             chunk_meta[cs] = (count << 1) | (at + count >= hi ? 1 : 0);
                             if (count > 0) {
@@ -705,14 +707,16 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                             }
                         }
                         at += count;
-                        if (ring == 0) ++qc0;
-                        else ++qc1;
+                        if (!dead) { // lane 0's counters stop with its last issued chunk (the drain below needs them)
+                            if (ring == 0) ++qc0;
+                            else ++qc1;
+                        }
                     } while (at < hi);
                 }
             }
         }
         // after an abort: let the chunk copies still in flight land (the last one issued into each stage of both rings)
-        if (stop != 0 && lane == 0) {
+        if (dead && lane == 0) {
             for (int ring = 0; ring < 2; ++ring) {
                 const long long issued = ring == 0 ? qc0 : qc1;
                 for (long long last = issued - 1; last >= 0 && last > issued - 1 - kRing2; --last)
@@ -732,18 +736,22 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-template<int NC>
-cb200_status launch_blocked2(const blocked_params &p, int sm_count, cudaStream_t stream) {
+template<int NC, bool TEST_HOOK>
+cb200_status launch_blocked2_as(const blocked_params &p, int sm_count, cudaStream_t stream) {
     constexpr std::size_t smem = 2 * kABufBytes + w2_stages(NC) * NC * kWin * 2 + 2 * kRing2 * kChunk2Bytes +
                                  (7 + 2 * w2_stages(NC) + 4 * kRing2) * sizeof(std::uint64_t) + 2 * kRing2 * 4 + 24;
     static_assert(smem <= 232448, "shared memory budget");
-    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked2_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked2_kernel<NC, TEST_HOOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const std::int64_t groups = p.group_end - p.group_begin;
     const unsigned grid = static_cast<unsigned>(groups < sm_count ? groups : sm_count);
-    qcsr_fwd_blocked2_kernel<NC><<<grid, kThreads, smem, stream>>>(p);
+    qcsr_fwd_blocked2_kernel<NC, TEST_HOOK><<<grid, kThreads, smem, stream>>>(p);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
+}
+template<int NC>
+cb200_status launch_blocked2(const blocked_params &p, int sm_count, cudaStream_t stream) {
+    return p.withhold_w != 0 ? launch_blocked2_as<NC, true>(p, sm_count, stream) : launch_blocked2_as<NC, false>(p, sm_count, stream);
 }
 } // namespace
 

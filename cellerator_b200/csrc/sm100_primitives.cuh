@@ -28,16 +28,19 @@ __device__ __forceinline__ bool bar_try_wait(std::uint32_t bar, std::uint32_t pa
     return ok != 0u;
 }
 // Bounded wait.  Once any wait of the CTA has timed out (`*abort_flag` set) waits return at once.
+// Returns true when the wait was given up (its own bound ran out, or another wait's did): the flag is
+// looked at only while the barrier is not ready, so a wait that succeeds at once costs nothing extra.
 constexpr int kPollLimit = 1 << 22;
-__device__ __forceinline__ void bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag, int limit = kPollLimit) {
+__device__ __forceinline__ bool bar_wait(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag, int limit = kPollLimit) {
     int spins = 0;
     while (!bar_try_wait(bar, parity)) {
-        if (*abort_flag != 0) return;
+        if (*abort_flag != 0) return true;
         if (++spins > limit) {
             *abort_flag = 1;
-            return;
+            return true;
         }
     }
+    return false;
 }
 // Bounded wait that does not look at the abort flag: what a role uses, after the CTA has aborted, to let the
 // copies or MMAs it still has in flight finish before the CTA gives up its shared memory and TMEM.

@@ -109,3 +109,37 @@ def test_device_generated_bell_matches_oracle(cuda_device, oracle):
     dec = ops.dequantize_bell(x).cpu().numpy()
     frac = float((dec != 0).mean())
     assert 0.5 < frac < 0.7            # about 60 % of the slots of present blocks are non-zero
+
+
+def test_bell_configuration_at_one_eighth_scale(cuda_device, oracle):
+    """The Blocked-ELL configuration's genes, block geometry and N = 256 on 1/8 of a GPU's shard (31,232 cells,
+    976 block rows), device-generated: block rows sampled at the start, the middle and the end against the
+    reference's decode + double-precision referee, repeat runs bit-identical, shards equal to the whole."""
+    cfg = dict(synth.CONFIGS["c5_bell"])
+    bs = cfg["block_size"]
+    cfg["rows"] = cfg["rows"] // 8 // 8 // bs * bs
+    x = synth.make_qbell_device(**cfg, device=cuda_device, seed=0)
+    rng = np.random.default_rng(6)
+    w, w_host = dense(rng, x.cols, cfg["n"], torch.bfloat16, cuda_device)
+    op = ops.PreparedSpmm(capi.PROJECTION_BLOCKED_ELL, x.rows, x.cols, cfg["n"], x.rows * x.ell_cols, x.bits, x.policy, w.dtype, cuda_device)
+    assert op.schedule == "tcgen05_block_rows"
+    y = op.run(x, w, torch.full((x.rows, cfg["n"]), float("nan"), device=cuda_device))
+    assert op.status() == 0
+    assert torch.equal(y, op.run(x, w, torch.empty_like(y)))
+    bci = x.block_col_idx.cpu().numpy().view(np.uint32).reshape(-1, cfg["ell_blocks"])
+    packed = x.packed.cpu().numpy().reshape(x.rows, x.row_stride_bytes)
+    wmax = float(np.abs(w_host).max())
+    block_rows = x.rows // bs
+    for b0 in (0, block_rows // 2 - 1, block_rows - 3):
+        r0, r1 = b0 * bs, (b0 + 3) * bs
+        h = dict(rows=r1 - r0, cols=x.cols, block_size=bs, ell_cols=x.ell_cols, row_stride_bytes=x.row_stride_bytes, bits=x.bits,
+                 policy=x.policy, block_col_idx=bci[b0:b0 + 3].ravel().copy(), packed=packed[r0:r1].ravel().copy(),
+                 scales=x.scales.cpu().numpy(), offsets=x.offsets.cpu().numpy())
+        ref, l1 = bell_reference(oracle, h, w_host)
+        assert_bell_close(y[r0:r1].cpu().numpy(), ref, l1, wmax, bf16_multiply=True)
+    out = torch.empty_like(y)
+    cut = (block_rows // 3) * bs
+    op.run(x, w, out, row_begin=0, row_end=cut)
+    op.run(x, w, out, row_begin=cut, row_end=x.rows)
+    assert torch.equal(out, y)
+    op.close()

@@ -18,12 +18,22 @@ from gpu_util import dense, host_pack, row_l1, to_dev
 pytestmark = pytest.mark.gpu
 
 
-def assert_tensor_close(y, ref, l1, wmax):
+def assert_tensor_close(y, ref, l1, wmax, relative=False):
+    """bf16 products against the oracle: the absolute bound 1e-2 * ||row||_1 * max|W|; with relative=True also the
+    contract's "1e-2 relative for bf16 W" as the exact kernels are held to it (tests/gpu_util.py): |d| /
+    max(|y_ref|, floor) <= 1e-2 with the floor 1e-2 * ||row||_1 * max|W|.  That second form is asked of the
+    benchmark configurations, whose rows hold hundreds of entries; a row of a handful of entries that cancel can
+    sit at 2^-9 * ||row||_1 * max|W| = 0.2 of that floor with every product rounded correctly.
+    Returns the observed maximum of the relative error."""
     err = np.abs(np.asarray(y, dtype=np.float64) - ref)
     scale = l1[:, None] * wmax + 1e-30
     assert np.all(err <= 1e-2 * scale), f"max err/scale {np.max(err / scale):.3e}"
     # the rounding is unbiased: the typical error is far below the bound
     assert np.median(err / scale) < 1e-3
+    rel = err / np.maximum(np.abs(ref), 1e-2 * scale)
+    worst = float(np.max(rel, initial=0.0))
+    assert not relative or worst <= 1e-2, f"max relative error {worst:.3e}"
+    return worst
 
 
 def prepared(x, n, w, device, blocked=False, **kw):
@@ -196,7 +206,8 @@ def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule
         ref = oracle.qcsr_forward(bits, 1, sub["row_ptr"], sub["packed_row_ptr"], sub["col_idx"], sub["packed"],
                                   sub["scales"], sub["offsets"], w_host, x.cols)
         l1s, _ = row_l1(oracle, sub)
-        assert_tensor_close(y1[r0:r1].cpu().numpy(), ref, l1s, wmax)
+        worst = assert_tensor_close(y1[r0:r1].cpu().numpy(), ref, l1s, wmax, relative=True)
+        print(f"{schedule} bits={bits} n={n} rows [{r0},{r1}): max relative error {worst:.3e} (bound 1e-2)")
     op.close()
     exact.close()
 

@@ -248,3 +248,53 @@ def test_tensor_transpose_respects_the_memory_limit(cuda_device, oracle, monkeyp
     out = none.run(x, g, torch.full((cols, n), float("nan"), device=cuda_device))
     assert_transpose_close(out.cpu().numpy(), ref, cl1, gmax)
     none.close()
+
+
+def _row_range_on_host(x, r0, r1):
+    """Rows [r0, r1) of a device matrix as a host matrix of its own (offsets rebased to 0)."""
+    rp = x.host_row_ptr
+    lo, hi = int(rp[r0]), int(rp[r1])
+    sub = dict(rows=r1 - r0, cols=x.cols, bits=x.bits, policy=x.policy, row_ptr=rp[r0:r1 + 1] - lo,
+               col_idx=x.col_idx[lo:hi].cpu().numpy(), scales=x.scales.cpu().numpy(), offsets=x.offsets.cpu().numpy())
+    if x.bits == 8:
+        sub["packed"], sub["packed_row_ptr"] = x.packed[lo:hi].cpu().numpy(), sub["row_ptr"]
+    else:
+        prp = x.packed_row_ptr[r0:r1 + 1].cpu().numpy()
+        sub["packed"], sub["packed_row_ptr"] = x.packed[int(prp[0]):int(prp[-1])].cpu().numpy(), prp - prp[0]
+    return sub
+
+
+@pytest.mark.parametrize("schedule", ["tensor_blocked_x3", "tensor_blocked", "gene_gather", "vector_reductions"])
+def test_transpose_schedules_against_the_oracle_at_scale(cuda_device, oracle, schedule):
+    """Genes as in the benchmark configuration, 1/8 of its cells, the schedule prepare chooses for each kind of
+    request: row-range partials over 2,048 cells at the start and in the middle of the matrix against the
+    oracle's double-precision partial of the same rows: 1e-4 * ||gene column||_1 * max|G| for fp32 products
+    (exact, split, ordered), 1e-2 for the single bf16 pass."""
+    cfg = dict(synth.CONFIGS["c2_forward"])
+    cfg["rows"] //= 8
+    x = synth.make_qcsr_device(**cfg, device=cuda_device, seed=0)
+    n = 64
+    g = torch.randn(x.rows, n, device=cuda_device)
+    kw = {"tensor_blocked_x3": dict(device_matrix=x), "tensor_blocked": dict(device_matrix=x, multiply=capi.DTYPE_BF16),
+          "gene_gather": dict(device_matrix=x, deterministic=True), "vector_reductions": {}}[schedule]
+    op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, x.rows, x.cols, n, x.nnz, x.bits, x.policy, g.dtype, cuda_device, **kw)
+    assert op.schedule == schedule
+    mid = x.rows // 2 + 77                                         # inside a 256-row group
+    for r0 in (0, mid):
+        r1 = r0 + 2048
+        part = op.run(x, g, torch.full((x.cols, n), float("nan"), device=cuda_device), row_begin=r0, row_end=r1)
+        assert op.status() == 0
+        sub = _row_range_on_host(x, r0, r1)
+        g_host = g[r0:r1].cpu().numpy()
+        ref = oracle.qcsr_transpose(sub["bits"], sub["policy"], sub["row_ptr"], sub["packed_row_ptr"], sub["col_idx"], sub["packed"],
+                                    sub["scales"], sub["offsets"], g_host, x.cols)
+        cl1 = col_l1_of(oracle, sub)
+        gmax = float(np.abs(g_host).max())
+        got = part.cpu().numpy()
+        if schedule == "tensor_blocked":
+            assert_tensor_transpose_close(got, ref, cl1, gmax)
+        else:
+            assert_transpose_close(got, ref, cl1, gmax)
+        worst = np.max(np.abs(got.astype(np.float64) - ref) / (cl1[:, None] * gmax + 1e-30))
+        print(f"{schedule} rows [{r0},{r1}): max |d| / (||column||_1 max|G|) = {worst:.3e}")
+    op.close()

@@ -29,17 +29,25 @@ def forward_static(x, w, y, alpha=1.0, beta=0.0):
                                                 torch.cuda.current_stream(dev).cuda_stream)
 
 
-@pytest.mark.parametrize("bits,dtype,n", [(8, torch.bfloat16, 64), (4, torch.bfloat16, 128), (8, torch.float32, 32)])
-def test_static_scratch_entry_matches_prepared_entry_twice(cuda_device, oracle, monkeypatch, bits, dtype, n):
+def static_status(device):
+    """cb200_qcsr_forward_static_status: the status word of the last static call (it lives in the library's array)."""
+    word = C.c_int32(-1)
+    st = capi.lib().cb200_qcsr_forward_static_status(device.index, torch.cuda.current_stream(device).cuda_stream, C.byref(word))
+    return st, word.value
+
+
+@pytest.mark.parametrize("bits,dtype,n,policy", [(8, torch.bfloat16, 64, 1), (4, torch.bfloat16, 128, 1), (8, torch.float32, 32, 1),
+                                                 (8, torch.bfloat16, 64, 2), (4, torch.float32, 64, 2)])
+def test_static_scratch_entry_matches_prepared_entry_twice(cuda_device, oracle, monkeypatch, bits, dtype, n, policy):
     monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "gene_tiled")
-    rng = np.random.default_rng(900 + bits + n)
+    rng = np.random.default_rng(900 + bits + n + policy)
     rows, cols = 128 * 2 + 19, 2600
-    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=500, bits=bits, policy=1))
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=500, bits=bits, policy=policy))
     x = to_dev(c, cuda_device)
     w, w_host = dense(rng, cols, n, dtype, cuda_device)
 
     # the existing entry point: prepared operation + caller workspace
-    op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, bits, 1, w.dtype, cuda_device,
+    op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cols, n, x.nnz, bits, policy, w.dtype, cuda_device,
                           host_row_ptr=x.host_row_ptr)
     assert op.schedule == "gene_tiled"
     expected = op.run(x, w, torch.empty(rows, n, device=cuda_device))
@@ -55,8 +63,10 @@ def test_static_scratch_entry_matches_prepared_entry_twice(cuda_device, oracle, 
     torch.cuda.synchronize(cuda_device)
     free_after, _ = torch.cuda.mem_get_info(cuda_device)
     assert free_after == free_before
+    assert static_status(cuda_device) == (capi.SUCCESS, 0)       # no bounded wait ran out; the reader allocates nothing either
+    assert torch.cuda.mem_get_info(cuda_device)[0] == free_before
 
-    ref = oracle.qcsr_forward(bits, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
+    ref = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
                               c["offsets"], w_host, cols)
     l1, _ = row_l1(oracle, c)
     for got in (first, second):
