@@ -200,6 +200,24 @@ class HostStageOptions(C.Structure):
                 ("max_chunk_rows", C.c_int64), ("max_chunk_nnz", C.c_int64), ("chunk_buffers", C.c_int32)]
 
 
+class AllocationAccounting(C.Structure):
+    _fields_ = [("current_bytes", C.c_uint64), ("high_water_bytes", C.c_uint64), ("allocation_count", C.c_uint64)]
+
+
+class SessionAccounting(C.Structure):
+    _fields_ = [("structure", AllocationAccounting), ("plan", AllocationAccounting), ("graph_stable", AllocationAccounting),
+                ("transient", AllocationAccounting), ("device_query_count", C.c_uint64), ("handle_prepare_count", C.c_uint64),
+                ("launch_bind_count", C.c_uint64), ("synchronization_count", C.c_uint64)]
+
+
+class SessionCacheEntry(C.Structure):
+    _fields_ = [("key_high", C.c_uint64), ("key_low", C.c_uint64), ("state", C.c_void_p), ("structure_epoch", C.c_uint64),
+                ("generation", C.c_uint64)]
+
+
+LIFETIME_STRUCTURE, LIFETIME_PLAN, LIFETIME_GRAPH_STABLE = 0, 1, 2
+
+
 class SessionOptions(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32),
                 ("owned_stream_count", C.c_uint32), ("external_stream_count", C.c_uint32),
@@ -239,6 +257,8 @@ EXPORTED_SYMBOLS = [
     "cb200_fleet_run_transpose", "cb200_fleet_allreduce_sum_f32",
     "cb200_host_stage_create", "cb200_host_stage_destroy", "cb200_host_stage_device_bytes", "cb200_host_forward",
     "cb200_test_arm_wait_timeout", "cb200_test_disarm_wait_timeout",
+    "cb200_session_reserve_persistent_as", "cb200_session_prepare_stream_libraries", "cb200_session_get_accounting",
+    "cb200_session_graph_stable_address", "cb200_session_cache_insert", "cb200_session_cache_find",
 ]
 
 _lib = None
@@ -355,6 +375,13 @@ def lib() -> C.CDLL:
         L.cb200_test_disarm_wait_timeout.restype = None
         L.cb200_session_create.argtypes = [C.POINTER(SessionOptions), C.POINTER(C.c_void_p)]
         L.cb200_session_reserve_persistent.argtypes = [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]
+        L.cb200_session_reserve_persistent_as.argtypes = [C.c_void_p, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p)]
+        L.cb200_session_prepare_stream_libraries.argtypes = [C.c_void_p, C.c_uint32]
+        L.cb200_session_get_accounting.argtypes = [C.c_void_p, C.POINTER(SessionAccounting)]
+        L.cb200_session_graph_stable_address.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+        L.cb200_session_cache_insert.argtypes = [C.c_void_p, C.c_int32, C.POINTER(SessionCacheEntry)]
+        L.cb200_session_cache_find.argtypes = [C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64]
+        L.cb200_session_cache_find.restype = C.POINTER(SessionCacheEntry)
         L.cb200_session_reserve_transient.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]
         L.cb200_session_seal.argtypes = [C.c_void_p]
         L.cb200_session_bind.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]

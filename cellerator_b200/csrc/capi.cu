@@ -86,8 +86,21 @@ struct cb200_session {
     void *transient[8];
     std::uint64_t transient_bytes[8];
     void *persistent[64];
+    std::uint64_t persistent_bytes[64];
+    int persistent_lifetime[64];
     std::uint32_t persistent_count;
+    cb200_session_accounting accounting;
+    cb200_session_cache_entry caches[3][64];
+    std::uint32_t cache_size[3];
 };
+
+namespace {
+void account(cb200_allocation_accounting *a, std::uint64_t bytes) {
+    a->current_bytes += bytes;
+    if (a->current_bytes > a->high_water_bytes) a->high_water_bytes = a->current_bytes;
+    ++a->allocation_count;
+}
+} // namespace
 
 extern "C" {
 
@@ -763,17 +776,78 @@ cb200_status cb200_session_create(const cb200_session_options *options, cb200_se
 }
 
 cb200_status cb200_session_reserve_persistent(cb200_session *s, uint64_t bytes, void **allocation) {
+    return cb200_session_reserve_persistent_as(s, CB200_LIFETIME_STRUCTURE, bytes, allocation);
+}
+
+cb200_status cb200_session_reserve_persistent_as(cb200_session *s, int32_t lifetime, uint64_t bytes, void **allocation) {
     clear_error();
     if (s == nullptr || allocation == nullptr || bytes == 0u) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad reserve arguments");
+    if (lifetime < CB200_LIFETIME_STRUCTURE || lifetime > CB200_LIFETIME_GRAPH_STABLE)
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "unknown persistent lifetime %d", lifetime);
     if (s->sealed) return fail(CB200_STATUS_SEALED, "session is sealed; nothing can grow");
     if (s->persistent_count == 64u) return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "64 persistent allocations at most");
     device_scope scope(s->device);
     CB200_CUDA_OK(scope.status);
     void *ptr = nullptr;
     CB200_CUDA_OK(cudaMalloc(&ptr, bytes));
-    s->persistent[s->persistent_count++] = ptr;
+    s->persistent[s->persistent_count] = ptr;
+    s->persistent_bytes[s->persistent_count] = bytes;
+    s->persistent_lifetime[s->persistent_count++] = lifetime;
+    account(lifetime == CB200_LIFETIME_STRUCTURE ? &s->accounting.structure
+                                                 : (lifetime == CB200_LIFETIME_PLAN ? &s->accounting.plan : &s->accounting.graph_stable),
+            bytes);
     *allocation = ptr;
     return CB200_STATUS_SUCCESS;
+}
+
+cb200_status cb200_session_prepare_stream_libraries(cb200_session *s, uint32_t stream_index) {
+    clear_error();
+    if (s == nullptr || stream_index >= s->stream_count) return fail(CB200_STATUS_INVALID_ARGUMENT, "bad stream index");
+    if (s->sealed) return fail(CB200_STATUS_SEALED, "session is sealed; nothing can grow");
+    ++s->accounting.handle_prepare_count; // no library handle behind it: the kernels are this library's own
+    return CB200_STATUS_SUCCESS;
+}
+
+cb200_status cb200_session_get_accounting(const cb200_session *s, cb200_session_accounting *out) {
+    clear_error();
+    if (s == nullptr || out == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "accounting needs a session and an output");
+    *out = s->accounting;
+    return CB200_STATUS_SUCCESS;
+}
+
+int32_t cb200_session_graph_stable_address(const cb200_session *s, const void *address, uint64_t bytes) {
+    if (s == nullptr || address == nullptr) return 0;
+    const std::uintptr_t lo = reinterpret_cast<std::uintptr_t>(address);
+    for (std::uint32_t i = 0; i < s->persistent_count; ++i) {
+        if (s->persistent_lifetime[i] != CB200_LIFETIME_GRAPH_STABLE) continue;
+        const std::uintptr_t base = reinterpret_cast<std::uintptr_t>(s->persistent[i]);
+        if (lo >= base && bytes <= s->persistent_bytes[i] && lo - base <= s->persistent_bytes[i] - bytes) return 1;
+    }
+    return 0;
+}
+
+cb200_status cb200_session_cache_insert(cb200_session *s, int32_t kind, const cb200_session_cache_entry *entry) {
+    clear_error();
+    if (s == nullptr || entry == nullptr || kind < CB200_CACHE_PLAN || kind > CB200_CACHE_ORDER_TRANSFORM || entry->state == nullptr ||
+        (entry->key_high == 0u && entry->key_low == 0u))
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "bad cache entry");
+    cb200_session_cache_entry *cache = s->caches[kind];
+    for (std::uint32_t i = 0; i < s->cache_size[kind]; ++i) {
+        if (cache[i].key_high == entry->key_high && cache[i].key_low == entry->key_low) {
+            cache[i] = *entry;
+            return CB200_STATUS_SUCCESS;
+        }
+    }
+    if (s->cache_size[kind] == 64u) return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "the session cache holds 64 entries");
+    cache[s->cache_size[kind]++] = *entry;
+    return CB200_STATUS_SUCCESS;
+}
+
+const cb200_session_cache_entry *cb200_session_cache_find(const cb200_session *s, int32_t kind, uint64_t key_high, uint64_t key_low) {
+    if (s == nullptr || kind < CB200_CACHE_PLAN || kind > CB200_CACHE_ORDER_TRANSFORM) return nullptr;
+    for (std::uint32_t i = 0; i < s->cache_size[kind]; ++i)
+        if (s->caches[kind][i].key_high == key_high && s->caches[kind][i].key_low == key_low) return &s->caches[kind][i];
+    return nullptr;
 }
 
 cb200_status cb200_session_reserve_transient(cb200_session *s, uint32_t stream_index, uint64_t bytes) {
@@ -785,9 +859,13 @@ cb200_status cb200_session_reserve_transient(cb200_session *s, uint32_t stream_i
     CB200_CUDA_OK(scope.status);
     void *ptr = nullptr;
     CB200_CUDA_OK(cudaMalloc(&ptr, bytes));
-    if (s->transient[stream_index] != nullptr) cudaFree(s->transient[stream_index]);
+    if (s->transient[stream_index] != nullptr) {
+        cudaFree(s->transient[stream_index]);
+        s->accounting.transient.current_bytes -= s->transient_bytes[stream_index];
+    }
     s->transient[stream_index] = ptr;
     s->transient_bytes[stream_index] = bytes;
+    account(&s->accounting.transient, bytes);
     return CB200_STATUS_SUCCESS;
 }
 
@@ -805,6 +883,7 @@ cb200_launch_binding cb200_session_bind(cb200_session *s, uint32_t stream_index,
     if (s == nullptr || stream_index >= s->stream_count) return b;
     if (!s->sealed) { b.status = CB200_STATUS_SEALED; return b; } /* bind only works on a sealed session */
     if (required_workspace_bytes > s->transient_bytes[stream_index]) { b.status = CB200_STATUS_INSUFFICIENT_WORKSPACE; return b; }
+    ++s->accounting.launch_bind_count; // host bookkeeping only: no CUDA call, allocation or synchronisation here
     b.status = CB200_STATUS_SUCCESS;
     b.device = s->device;
     b.stream = s->streams[stream_index];
@@ -819,6 +898,7 @@ cb200_status cb200_session_synchronize(cb200_session *s) {
     device_scope scope(s->device);
     CB200_CUDA_OK(scope.status);
     for (std::uint32_t i = 0; i < s->stream_count; ++i) CB200_CUDA_OK(cudaStreamSynchronize(s->streams[i]));
+    ++s->accounting.synchronization_count;
     return CB200_STATUS_SUCCESS;
 }
 

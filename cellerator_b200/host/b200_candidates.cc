@@ -246,7 +246,8 @@ core::operation_status prepare_any(int projection_kind, bool composed, bool orde
     p.device_matrix = policy.allow_persistent_preprocessing ? shape->device_matrix : nullptr;
     p.persistent_limit_bytes = policy.persistent_memory_limit;
     p.value_generation = p.device_matrix != nullptr ? shape->device_matrix_generation.value : 0u;
-    p.schedule_hint = shape->schedule_hint;
+    // the planner's choice travels as the projection's variant; the catalog entry may pin one as well
+    p.schedule_hint = projection.variant != schedule_backend_choice ? schedule_name(projection.variant) : shape->schedule_hint;
     // persistent memory the session reserved for this operation (borrowed, OPERATION_CORE.md:17-25), and its stream
     p.persistent = shape->persistent;
     p.persistent_bytes = shape->persistent_bytes;
@@ -489,6 +490,61 @@ const char *prepared_schedule(const core::prepared_operation &prepared) noexcept
     record.analytical.transient_bytes = candidate.transient_bytes;
     record.flags = pl::planner_candidate_correct | pl::planner_candidate_graph_capture |
                    ((candidate.capability_flags & core::candidate_deterministic) ? pl::planner_candidate_deterministic : 0u);
+    return record;
+}
+
+const char *schedule_name(std::uint32_t variant) noexcept {
+    static const char *const names[schedule_variant_count] = {"", "warp_per_row", "gene_tiled", "tensor_windows", "tensor_blocked",
+                                                               "tensor_dense", "vector_reductions", "gene_gather",
+                                                               "tcgen05_block_rows", "cuda_cores"};
+    return variant < schedule_variant_count ? names[variant] : "";
+}
+
+::cellerator::planner::planner_candidate make_schedule_candidate(const core::operation_candidate &candidate,
+                                                                 const core::projection_key &projection,
+                                                                 const projection_catalog_entry &shape, std::uint32_t variant,
+                                                                 std::int32_t multiply, double hbm_bytes_per_ns) noexcept {
+    namespace pl = ::cellerator::planner;
+    const bool transpose = shape.projection_kind == CB200_PROJECTION_TRANSPOSE;
+    const bool split = multiply != CB200_DTYPE_BF16;
+    // Fraction of the measured HBM copy bandwidth each schedule reached on B200 on the benchmark configurations
+    // (1M x 33,538 cells x genes at 5.4 % density; 500k x 4,000 at 17 % for the dense tiles; 250k x 8,192 Blocked-ELL).
+    double fraction = 0.05;
+    switch (variant) {
+    case schedule_warp_per_row: fraction = 0.05; break;
+    case schedule_gene_tiled: fraction = 0.070; break;
+    case schedule_tensor_windows: fraction = 0.062; break;
+    case schedule_tensor_blocked:
+        fraction = transpose ? (split ? 0.078 : 0.226) : (split ? (shape.dense_dtype == CB200_DTYPE_BF16 ? 0.112 : 0.075) : 0.224);
+        break;
+    case schedule_tensor_dense: fraction = 0.395; break;
+    case schedule_vector_reductions: fraction = 0.013; break;
+    case schedule_gene_gather: fraction = 0.047; break;
+    case schedule_tcgen05_block_rows: fraction = 0.188; break;
+    case schedule_cuda_cores: fraction = 0.013; break;
+    default: break;
+    }
+    pl::planner_candidate record = make_planner_candidate(candidate, projection, shape, hbm_bytes_per_ns, fraction);
+    record.projection.variant = variant;
+    // what prepare would keep on the device for this schedule, from the backend itself (host arithmetic only)
+    cb200_spmm_problem p{};
+    p.version = CB200_ABI_VERSION;
+    p.size = sizeof p;
+    p.projection = shape.projection_kind;
+    p.m = shape.m; p.k = shape.k; p.n = shape.n; p.nnz = shape.nnz;
+    p.bits = shape.bits; p.policy = shape.decode_policy; p.dense_dtype = shape.dense_dtype; p.device = shape.device;
+    p.structure_epoch = 1u;
+    p.host_row_ptr = shape.host_row_ptr;
+    p.deterministic = variant == schedule_gene_gather ? 1 : 0;
+    p.multiply = multiply;
+    p.device_matrix = shape.device_matrix;
+    p.schedule_hint = schedule_name(variant);
+    std::uint64_t persistent = 0u;
+    if (cb200_spmm_persistent_requirement(&p, &persistent) != CB200_STATUS_SUCCESS) persistent = 0u;
+    record.analytical.persistent_bytes = persistent;
+    // building the copies: measured 18 ms of kernels for the 7.2 GB window-blocked copy of the 1M x 33,538 matrix
+    // (two passes over the matrix with an atomic per run of entries), i.e. 0.06 of the copy bandwidth per byte kept
+    record.analytical.backend_prepare_ns = 2.0e4 + static_cast<double>(persistent) / (hbm_bytes_per_ns * 0.06);
     return record;
 }
 

@@ -114,6 +114,36 @@ void release_prepared(core::prepared_operation *prepared) noexcept;
 // prepared operation is not one of this library's.
 const char *prepared_schedule(const core::prepared_operation &prepared) noexcept;
 
+// Kernel schedules as projection variants.  projection_key.variant (operation_core.hh:94-100) tells two physical
+// forms of one projection apart, and the planner caches its winner by (candidate identity, projection identity,
+// variant) (end_to_end_planner.cc find_candidate_index).  Variant 0 leaves the choice to the backend's prepare;
+// the others name one schedule, which prepare() passes on as cb200_spmm_problem.schedule_hint.
+enum schedule_variant : std::uint32_t {
+    schedule_backend_choice = 0u,
+    schedule_warp_per_row = 1u,
+    schedule_gene_tiled = 2u,
+    schedule_tensor_windows = 3u,
+    schedule_tensor_blocked = 4u,     // forward: one bf16 pass, or split passes when fp32 products are asked for; transpose alike
+    schedule_tensor_dense = 5u,
+    schedule_vector_reductions = 6u,  // transpose, fp32 FMA + vector reductions
+    schedule_gene_gather = 7u,        // transpose, fixed order of the sums
+    schedule_tcgen05_block_rows = 8u, // Blocked-ELL
+    schedule_cuda_cores = 9u,
+    schedule_variant_count = 10u
+};
+const char *schedule_name(std::uint32_t variant) noexcept; // "" for the backend's choice or an unknown variant
+
+// One planner_candidate per (operation candidate, schedule): identity and operation are the candidate's, the
+// projection key carries the schedule as its variant, the analytical phase costs come from the algorithmic
+// bytes of the shape, the fraction of the HBM roofline the schedule was measured at on B200 (kernel_ns), the
+// bytes cb200_spmm_persistent_requirement reports for it (persistent_bytes, and the prepare time of building
+// them), and the workspace of the schedule (transient_bytes).  `multiply` is the request's numeric_policy.multiply
+// as a cb200_dtype: it decides between the one-pass and the split-product forms of the tensor schedules.
+::cellerator::planner::planner_candidate make_schedule_candidate(const core::operation_candidate &candidate,
+                                                                 const core::projection_key &projection,
+                                                                 const projection_catalog_entry &shape, std::uint32_t variant,
+                                                                 std::int32_t multiply, double hbm_bytes_per_ns) noexcept;
+
 // planner_candidate record (end_to_end_planner.hh:118-126) with analytical phase costs from a
 // bandwidth model: kernel time = algorithmic bytes / `hbm_bytes_per_ns`, scaled by the fraction
 // of the roofline the kernel reaches.

@@ -437,8 +437,45 @@ typedef struct cb200_launch_binding { /* launch_runtime_binding, session.cuh:122
     uint64_t workspace_bytes;
 } cb200_launch_binding;
 
+/* persistent_lifetime, session.cuh:28-32: what a persistent reservation is tied to */
+typedef enum cb200_persistent_lifetime {
+    CB200_LIFETIME_STRUCTURE = 0,   /* lives as long as the structure (a window-blocked or gene-major copy) */
+    CB200_LIFETIME_PLAN = 1,        /* lives as long as a prepared plan */
+    CB200_LIFETIME_GRAPH_STABLE = 2 /* addresses that captured graphs hold */
+} cb200_persistent_lifetime;
+
+/* session_accounting, session.cuh:72-90: bytes and counts per class since the session was created */
+typedef struct cb200_allocation_accounting {
+    uint64_t current_bytes, high_water_bytes, allocation_count;
+} cb200_allocation_accounting;
+typedef struct cb200_session_accounting {
+    cb200_allocation_accounting structure, plan, graph_stable, transient;
+    uint64_t device_query_count, handle_prepare_count, launch_bind_count, synchronization_count;
+} cb200_session_accounting;
+
+/* session_cache_kind / session_cache_key / session_cache_entry, session.cuh:34-61: three fixed caches of 64 entries */
+typedef enum cb200_session_cache_kind { CB200_CACHE_PLAN = 0, CB200_CACHE_PROJECTION = 1, CB200_CACHE_ORDER_TRANSFORM = 2 } cb200_session_cache_kind;
+typedef struct cb200_session_cache_entry {
+    uint64_t key_high, key_low;
+    void *state;
+    uint64_t structure_epoch, generation;
+} cb200_session_cache_entry;
+
 cb200_status cb200_session_create(const cb200_session_options *options, cb200_session **out);
+/* reserve_persistent with lifetime CB200_LIFETIME_STRUCTURE */
 cb200_status cb200_session_reserve_persistent(cb200_session *s, uint64_t bytes, void **allocation);
+/* reserve_persistent, session_setup.cu.inc:111-140: one device allocation per call, at most 64, none after sealing */
+cb200_status cb200_session_reserve_persistent_as(cb200_session *s, int32_t lifetime, uint64_t bytes, void **allocation);
+/* prepare_stream_libraries: this backend uses no cuBLAS / cuSPARSE handle, so nothing is created; the call is
+ * counted (handle_prepare_count) and refused after sealing, like the reference's */
+cb200_status cb200_session_prepare_stream_libraries(cb200_session *s, uint32_t stream_index);
+cb200_status cb200_session_get_accounting(const cb200_session *s, cb200_session_accounting *out);
+/* graph_stable_address: 1 when [address, address + bytes) lies inside a graph-stable reservation */
+int32_t cb200_session_graph_stable_address(const cb200_session *s, const void *address, uint64_t bytes);
+/* insert_session_cache / find_session_cache: an entry with the same key is replaced; a full cache -> INSUFFICIENT_WORKSPACE;
+ * find returns NULL when the key is absent */
+cb200_status cb200_session_cache_insert(cb200_session *s, int32_t kind, const cb200_session_cache_entry *entry);
+const cb200_session_cache_entry *cb200_session_cache_find(const cb200_session *s, int32_t kind, uint64_t key_high, uint64_t key_low);
 cb200_status cb200_session_reserve_transient(cb200_session *s, uint32_t stream_index, uint64_t bytes);
 cb200_status cb200_session_seal(cb200_session *s);
 cb200_launch_binding cb200_session_bind(cb200_session *s, uint32_t stream_index, uint64_t required_workspace_bytes);

@@ -84,6 +84,121 @@ static problem_ids make_ids(std::uint32_t salt, core::projection_kind kind, std:
     return ids;
 }
 
+// plan_end_to_end (src/planner/end_to_end_planner.cc:268-518) over one planner_candidate per (operation candidate,
+// schedule) at the benchmark configuration's shape: the reference's own rejection rules and analytical ranking
+// decide.  No device is touched: the records come from host arithmetic on the shape.
+static void planner_leg(const core::candidate_registry &registry) {
+    namespace pl = ::cellerator::planner;
+    const core::operation_candidate *fwd = core::find_candidate(registry, host::quantized_csr_forward_candidate().identity);
+    const core::operation_candidate *tr = core::find_candidate(registry, host::quantized_csr_transpose_candidate().identity);
+    const core::operation_candidate *ord = core::find_candidate(registry, host::quantized_csr_transpose_ordered_candidate().identity);
+    CHECK(fwd != nullptr && tr != nullptr && ord != nullptr, "planner: the candidates are registered");
+    if (fwd == nullptr || tr == nullptr || ord == nullptr) return;
+    // 1,000,000 cells x 33,538 genes, 1.8e9 stored entries, N = 64: the matrix is described, not allocated
+    cb200_qcsr dm{};
+    dm.version = CB200_ABI_VERSION; dm.size = sizeof dm; dm.rows = 1000000; dm.cols = 33538; dm.nnz = 1797264673ll; dm.bits = 8;
+    dm.policy = CB200_DECODE_PER_GENE_AFFINE;
+    const auto request_for = [&](const problem_ids &ids, const pl::planner_candidate *candidates, std::uint32_t count) {
+        pl::planner_request r{};
+        r.problem = ids.problem;
+        r.keys.problem.identity = ids.problem.operation;
+        pl::make_persistent_structure_set_key(ids.structures, &r.keys.structures);
+        r.keys.geometry = {{1u, 1u}, {2u, 1u}, {3u, 1u}, {4u, 1u}, {5u, 1u}, {6u, 1u}};
+        r.keys.device = {0x10deu, 10u, 0u, 1u};
+        r.keys.build = {12090u, 1u, 580u, 2u};
+        r.keys.policy.structure_reuse = 1000u;
+        r.keys.policy.projection_reuse = 1000u;
+        r.candidates = candidates;
+        r.candidate_count = count;
+        r.current_evidence_revision = 1u;
+        return r;
+    };
+    const auto variant_of = [](const pl::planner_result &res) { return res.selected != nullptr ? res.selected->projection.variant : 0xffffffffu; };
+
+    // ---- forward, bf16 W, bf16 products allowed, the matrix at hand
+    problem_ids f = make_ids(30u, core::projection_kind::csr, static_cast<std::uint64_t>(dm.nnz));
+    host::projection_catalog_entry fs{};
+    fs.projection = f.projection.runtime; fs.projection_kind = CB200_PROJECTION_CSR;
+    fs.m = dm.rows; fs.k = dm.cols; fs.n = 64; fs.nnz = dm.nnz; fs.bits = 8; fs.dense_dtype = CB200_DTYPE_BF16; fs.device_matrix = &dm;
+    const pl::planner_candidate forward[3] = {
+        host::make_schedule_candidate(*fwd, f.projection, fs, host::schedule_gene_tiled, CB200_DTYPE_BF16, 6553.9),
+        host::make_schedule_candidate(*fwd, f.projection, fs, host::schedule_tensor_blocked, CB200_DTYPE_BF16, 6553.9),
+        host::make_schedule_candidate(*fwd, f.projection, fs, host::schedule_warp_per_row, CB200_DTYPE_BF16, 6553.9)};
+    CHECK(forward[1].analytical.persistent_bytes > 7000000000ull && forward[1].analytical.persistent_bytes < 7400000000ull &&
+              forward[0].analytical.persistent_bytes == 0u,
+          "planner: the window-blocked schedule declares its persistent copy (one word per entry), the exact ones none");
+    pl::planner_result res{};
+    pl::planner_request req = request_for(f, forward, 3u);
+    pl::planner_status st = pl::plan_end_to_end(req, &res);
+    CHECK(static_cast<bool>(st) && res.legal_count == 3u && res.source == pl::selection_source::analytical && res.tuning_skipped &&
+              variant_of(res) == host::schedule_tensor_blocked,
+          "planner: the tensor-core schedule over the window-blocked copy wins the forward projection on analytical cost");
+    if (!st) std::printf("  message: %s\n", st.message);
+    // the prepare of the copy is amortised: a one-shot request pays all of it, and the exact kernel wins
+    req.keys.policy.structure_reuse = req.keys.policy.projection_reuse = 1u;
+    st = pl::plan_end_to_end(req, &res);
+    CHECK(static_cast<bool>(st) && variant_of(res) == host::schedule_gene_tiled, "planner: a one-shot request does not pay for the copy");
+    req.keys.policy.structure_reuse = req.keys.policy.projection_reuse = 1000u;
+    // persistent-memory limit below the copy: rejected as persistent_memory, the exact gene-tiled kernel is next
+    req.policy.maximum_persistent_bytes = 1ull << 30;
+    st = pl::plan_end_to_end(req, &res);
+    CHECK(static_cast<bool>(st) && res.legal_count == 2u && res.diagnostics[1].rejection == pl::candidate_rejection::persistent_memory &&
+              variant_of(res) == host::schedule_gene_tiled,
+          "planner: the persistent-memory limit rejects the window-blocked copy and the gene-tiled kernel is selected");
+    // an empirical pass: the measurement hook confirms the analytical order with measured times
+    req.policy.maximum_persistent_bytes = 0u;
+    struct measured_times { int calls; };
+    measured_times ctx{0};
+    req.measurement.context = &ctx;
+    req.measurement.measure = [](void *c, const pl::planner_candidate &cand, pl::measured_candidate *m) noexcept -> bool {
+        ++static_cast<measured_times *>(c)->calls;
+        m->correct = true;
+        m->sample_count = 20u;
+        m->spread_percent = 0.3;
+        m->phases = cand.analytical;
+        // measured on B200, ms per launch: tensor_blocked 6.31, gene_tiled 20.3, warp_per_row 28.5
+        m->phases.kernel_ns = cand.projection.variant == host::schedule_tensor_blocked ? 6.31e6
+                              : cand.projection.variant == host::schedule_gene_tiled ? 20.3e6 : 28.5e6;
+        return true;
+    };
+    st = pl::plan_end_to_end(req, &res);
+    CHECK(static_cast<bool>(st) && res.source == pl::selection_source::empirical && ctx.calls == 3 && res.measurement_count == 3u &&
+              variant_of(res) == host::schedule_tensor_blocked && res.confidence > 0.8,
+          "planner: bounded tuning measures the shortlist and keeps the tensor-core schedule");
+
+    // ---- transpose, fp32 G: the atomic-order schedules are not deterministic, the ordered gather is
+    problem_ids t = make_ids(31u, core::projection_kind::transpose_or_backward, static_cast<std::uint64_t>(dm.nnz));
+    host::projection_catalog_entry ts = fs;
+    ts.projection = t.projection.runtime; ts.projection_kind = CB200_PROJECTION_TRANSPOSE; ts.dense_dtype = CB200_DTYPE_F32;
+    const pl::planner_candidate transposes[3] = {
+        host::make_schedule_candidate(*tr, t.projection, ts, host::schedule_vector_reductions, CB200_DTYPE_F32, 6553.9),
+        host::make_schedule_candidate(*tr, t.projection, ts, host::schedule_tensor_blocked, CB200_DTYPE_F32, 6553.9),
+        host::make_schedule_candidate(*ord, t.projection, ts, host::schedule_gene_gather, CB200_DTYPE_F32, 6553.9)};
+    CHECK((transposes[0].flags & pl::planner_candidate_deterministic) == 0u && (transposes[2].flags & pl::planner_candidate_deterministic) != 0u,
+          "planner: only the ordered transpose is flagged deterministic");
+    CHECK(transposes[1].analytical.persistent_bytes > 14000000000ull && transposes[2].analytical.persistent_bytes > 8900000000ull,
+          "planner: split-product words (8 B per entry) and the gene-major copy (5 B per entry) are declared");
+    pl::planner_request treq = request_for(t, transposes, 3u);
+    st = pl::plan_end_to_end(treq, &res);
+    CHECK(static_cast<bool>(st) && res.legal_count == 3u && variant_of(res) == host::schedule_tensor_blocked,
+          "planner: the split-product tensor schedule wins the transpose on analytical cost");
+    treq.policy.deterministic = true;
+    st = pl::plan_end_to_end(treq, &res);
+    CHECK(static_cast<bool>(st) && res.legal_count == 1u && res.diagnostics[0].rejection == pl::candidate_rejection::nondeterministic &&
+              res.diagnostics[1].rejection == pl::candidate_rejection::nondeterministic && variant_of(res) == host::schedule_gene_gather,
+          "planner: a deterministic policy rejects the atomic-order transposes and selects the ordered gather");
+    treq.policy.maximum_persistent_bytes = 1ull << 30; // ... which needs its gene-major copy
+    st = pl::plan_end_to_end(treq, &res);
+    CHECK(st.code == pl::planner_status_code::no_legal_candidate, "planner: deterministic and no room for the gene-major copy -> no legal candidate");
+    // a record whose projection kind is not its operation's is malformed (end_to_end_planner.cc:81-96)
+    pl::planner_candidate wrong = forward[0];
+    wrong.projection.kind = core::projection_kind::transpose_or_backward;
+    pl::planner_request wreq = request_for(f, &wrong, 1u);
+    st = pl::plan_end_to_end(wreq, &res);
+    CHECK(st.code == pl::planner_status_code::no_legal_candidate && res.diagnostics[0].rejection == pl::candidate_rejection::malformed,
+          "planner: a record with the wrong projection kind is rejected as malformed");
+}
+
 int main(int argc, char **argv) {
     const bool host_only_requested = argc > 1 && std::strcmp(argv[1], "--host-only") == 0;
     int device_count = 0;
@@ -159,6 +274,9 @@ int main(int argc, char **argv) {
                                       policy_u8(ex::numeric_type::f32), {}, &prepared).code ==
                   core::operation_status_code::unsupported_projection, "unknown projection handle is rejected");
     }
+    // ---- the reference's planner ranks the backend's schedules (host only) -----------------------------
+    planner_leg(registry);
+
     if (!have_device) {
         const core::operation_status s = core::prepare_candidate(*fwd, ids.problem, ids.structures, ids.projection,
                                                                  policy_u8(ex::numeric_type::f32), {}, &prepared);
@@ -517,6 +635,30 @@ int main(int argc, char **argv) {
         ts.device_matrix = &dm;
         ts.device_matrix_generation = {5u}; // the generation of `plane`
         ts.schedule_hint = "tensor_blocked"; // the matrix is far below the size prepare would pick it for
+        // the copy lives in memory the execution session reserved before sealing (prepared state borrows it,
+        // OPERATION_CORE.md:17-25): sized by the backend, handed over through the catalog entry
+        cb200_spmm_problem sizing{};
+        sizing.version = CB200_ABI_VERSION; sizing.size = sizeof sizing; sizing.projection = CB200_PROJECTION_TRANSPOSE;
+        sizing.m = M; sizing.k = K; sizing.n = N; sizing.nnz = nnz; sizing.bits = 8; sizing.policy = CB200_DECODE_PER_GENE_AFFINE;
+        sizing.dense_dtype = CB200_DTYPE_F32; sizing.structure_epoch = 3u; sizing.multiply = CB200_DTYPE_F32; sizing.device_matrix = &dm;
+        sizing.schedule_hint = "tensor_blocked";
+        std::uint64_t persistent_need = 0u;
+        CHECK(cb200_spmm_persistent_requirement(&sizing, &persistent_need) == CB200_STATUS_SUCCESS && persistent_need >= static_cast<std::uint64_t>(nnz) * 8u,
+              "the backend sizes the persistent memory of the split-product transpose (two words per entry)");
+        cb200_session_options sopt{};
+        sopt.version = CB200_ABI_VERSION; sopt.size = sizeof sopt; sopt.device = 0; sopt.owned_stream_count = 1u;
+        cb200_session *session = nullptr;
+        void *session_block = nullptr;
+        CHECK(cb200_session_create(&sopt, &session) == CB200_STATUS_SUCCESS &&
+                  cb200_session_reserve_persistent_as(session, CB200_LIFETIME_STRUCTURE, persistent_need, &session_block) == CB200_STATUS_SUCCESS &&
+                  cb200_session_seal(session) == CB200_STATUS_SUCCESS,
+              "session: reserve the persistent block, then seal");
+        const cb200_launch_binding bound = cb200_session_bind(session, 0u, 0u);
+        ts.persistent = session_block;
+        ts.persistent_bytes = persistent_need;
+        ts.prepare_stream = bound.stream;
+        std::size_t free_before = 0, free_after = 0, total_mem = 0;
+        cudaMemGetInfo(&free_before, &total_mem);
         host::register_projection(ts);
         core::prepared_operation pt{};
         core::prepare_policy with_preprocessing;
@@ -526,6 +668,8 @@ int main(int argc, char **argv) {
         CHECK(static_cast<bool>(st), "prepare_candidate(transpose, matrix handed to prepare)");
         if (!st) std::printf("  message: %s\n", st.message);
         CHECK(std::strcmp(host::prepared_schedule(pt), "tensor_blocked_x3") == 0, "fp32 products + matrix at prepare -> split-product tensor schedule");
+        cudaMemGetInfo(&free_after, &total_mem);
+        CHECK(free_after == free_before, "prepare built its copy inside the session's block: no device memory was allocated");
         CHECK(pt.binding_contract.workspace.minimum_bytes > 4096u, "the schedule reports its workspace (bf16 records of G)");
         void *d_ws2 = nullptr;
         const std::size_t ws2 = static_cast<std::size_t>(pt.binding_contract.workspace.minimum_bytes);
@@ -584,6 +728,10 @@ int main(int argc, char **argv) {
                   "without persistent preprocessing the ordered transpose is rejected");
             core::prepare_policy det_pre = with_preprocessing;
             det_pre.deterministic = true;
+            ts.persistent = nullptr; // the session's block holds the split-product copy: this operation allocates its own
+            ts.persistent_bytes = 0u;
+            ts.schedule_hint = nullptr;
+            host::register_projection(ts);
             st = core::prepare_candidate(*ord, t.problem, t.structures, t.projection, policy_u8(ex::numeric_type::f32), det_pre, &po);
             CHECK(static_cast<bool>(st), "prepare_candidate(ordered transpose, deterministic policy)");
             if (!st) std::printf("  message: %s\n", st.message);
@@ -613,16 +761,9 @@ int main(int argc, char **argv) {
         }
         host::release_prepared(&pt);
         cudaFree(d_ws2);
+        cb200_session_destroy(session); // the owner of the block outlived the prepared operations built in it
     }
 
-    // ---- planner record ---------------------------------------------------------------------------
-    {
-        const auto rec = host::make_planner_candidate(*fwd, ids.projection, shape, 6553.9, 0.07);
-        CHECK(core::same_stable_id(rec.identity, fwd->identity) && rec.operation == fwd &&
-                  rec.projection.kind == fwd->projection && std::isfinite(rec.analytical.kernel_ns) &&
-                  rec.analytical.kernel_ns > 0.0 && (rec.flags & ::cellerator::planner::planner_candidate_correct) != 0u,
-              "planner_candidate record is well formed");
-    }
     std::printf("%s: %d failure(s)\n", g_failures ? "FAILED" : "OK", g_failures);
     return g_failures ? 1 : 0;
 }

@@ -93,3 +93,51 @@ def test_session_reserve_seal_bind(cuda_device, problem):
     capi.check(L.cb200_session_synchronize(sess))
     assert np.allclose(out.cpu().numpy(), ref, rtol=1e-4, atol=1e-5)
     L.cb200_session_destroy(sess)
+
+
+def test_session_lifetimes_accounting_and_caches(cuda_device):
+    """persistent_lifetime classes, session_accounting and the fixed caches of the reference's execution_session
+    (include/Cellerator/runtime/session.cuh:28-90,147-177)."""
+    L = capi.lib()
+    opts = capi.header(capi.SessionOptions())
+    opts.device, opts.owned_stream_count = cuda_device.index, 2
+    sess = C.c_void_p()
+    capi.check(L.cb200_session_create(C.byref(opts), C.byref(sess)))
+    try:
+        a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        capi.check(L.cb200_session_reserve_persistent_as(sess, capi.LIFETIME_STRUCTURE, 1 << 20, C.byref(a)))
+        capi.check(L.cb200_session_reserve_persistent_as(sess, capi.LIFETIME_PLAN, 1 << 16, C.byref(b)))
+        capi.check(L.cb200_session_reserve_persistent_as(sess, capi.LIFETIME_GRAPH_STABLE, 4096, C.byref(c)))
+        assert L.cb200_session_reserve_persistent_as(sess, 7, 16, C.byref(c)) == capi.INVALID_ARGUMENT
+        capi.check(L.cb200_session_reserve_transient(sess, 0, 1 << 12))
+        capi.check(L.cb200_session_reserve_transient(sess, 0, 1 << 14))       # grows: the old block is replaced
+        capi.check(L.cb200_session_prepare_stream_libraries(sess, 1))
+        assert L.cb200_session_prepare_stream_libraries(sess, 9) == capi.INVALID_ARGUMENT
+        assert L.cb200_session_graph_stable_address(sess, c, 4096) == 1
+        assert L.cb200_session_graph_stable_address(sess, C.c_void_p(c.value + 4000), 200) == 0     # runs past the reservation
+        assert L.cb200_session_graph_stable_address(sess, a, 16) == 0                                # structure memory is not graph-stable
+        entry = capi.SessionCacheEntry(0xabc, 0xdef, a, 3, 5)
+        capi.check(L.cb200_session_cache_insert(sess, 1, C.byref(entry)))
+        entry.generation = 6
+        capi.check(L.cb200_session_cache_insert(sess, 1, C.byref(entry)))    # same key: replaced
+        found = L.cb200_session_cache_find(sess, 1, 0xabc, 0xdef)
+        assert found and found.contents.generation == 6 and found.contents.state == a.value
+        assert not L.cb200_session_cache_find(sess, 0, 0xabc, 0xdef)         # another cache kind
+        for i in range(63):
+            e = capi.SessionCacheEntry(1, 100 + i, a, 1, 1)
+            capi.check(L.cb200_session_cache_insert(sess, 1, C.byref(e)))
+        e = capi.SessionCacheEntry(1, 999, a, 1, 1)
+        assert L.cb200_session_cache_insert(sess, 1, C.byref(e)) == capi.INSUFFICIENT_WORKSPACE      # 64 entries
+        capi.check(L.cb200_session_seal(sess))
+        assert L.cb200_session_prepare_stream_libraries(sess, 0) == capi.SEALED
+        for _ in range(3):
+            assert L.cb200_session_bind(sess, 0, 1 << 14).status == capi.SUCCESS
+        capi.check(L.cb200_session_synchronize(sess))
+        acc = capi.SessionAccounting()
+        capi.check(L.cb200_session_get_accounting(sess, C.byref(acc)))
+        assert (acc.structure.current_bytes, acc.plan.current_bytes, acc.graph_stable.current_bytes) == (1 << 20, 1 << 16, 4096)
+        assert acc.structure.allocation_count == acc.plan.allocation_count == acc.graph_stable.allocation_count == 1
+        assert acc.transient.current_bytes == 1 << 14 and acc.transient.high_water_bytes == 1 << 14 and acc.transient.allocation_count == 2
+        assert (acc.handle_prepare_count, acc.launch_bind_count, acc.synchronization_count) == (1, 3, 1)
+    finally:
+        L.cb200_session_destroy(sess)
