@@ -8,6 +8,7 @@
 #include "sm100_primitives.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace cb200 {
 namespace {
@@ -74,17 +75,54 @@ __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
     d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
     return d;
 }
+// fp16 operands.  The decoded values and W are rounded to 16 bits before the tensor cores multiply them.  bf16
+// keeps 8 significant bits; fp16 keeps 11, which makes every product eight times more exact, but has a narrow
+// exponent range.  So an fp16 operand is stored times a power of two that brings its largest magnitude into
+// [2^14, 2^15), and the result is divided by the two factors again (exactly: they are powers of two).  Entries
+// more than 2^-29 below the largest lose bits to fp16's subnormal range, an absolute error below 2^-40 of the
+// largest magnitude.  The factor of W is found on the device at every launch (absmax_kernel), the factor of the
+// decoded values at prepare time.
+__host__ __device__ __forceinline__ float operand_scale(float absmax) {
+    if (!(absmax > 0.0f) || !(absmax < 3.0e38f)) return 1.0f; // zero, infinite or NaN: leave the operand as it is
+    int e = 0;
+    frexpf(absmax, &e); // absmax = m * 2^e, m in [0.5, 1)
+    e = e < -100 ? -100 : (e > 100 ? 100 : e);
+    return ldexpf(1.0f, 15 - e);
+}
+// Largest magnitude of a dense operand as the bits of a float in *out_bits (zeroed by the caller before).
+template<typename WT>
+__global__ void __launch_bounds__(256) absmax_kernel(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits) {
+    float m = 0.0f;
+    const std::int64_t total = rows * n;
+    for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+        const std::int64_t r = i / n;
+        const int c = static_cast<int>(i - r * n);
+        float v;
+        if constexpr (sizeof(WT) == 2) v = __bfloat162float(w[r * ld + c]);
+        else v = w[r * ld + c];
+        m = fmaxf(m, fabsf(v)); // NaN entries are ignored here; they still reach the product
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(out_bits, __float_as_uint(m)); // non-negative floats order like their bits
+}
+
 // W [genes][n] (leading dimension ld) -> one record per window of 128 genes: the n x 128 slice of
 // W^T in operand layout (byte offset of (column c, gene e) = (c/8)*2048 + (e/8)*128 + (c%8)*16 +
 // (e%8)*2, zero for genes >= cols) followed by 128 x {scale, zero-point}.  part 0 writes
 // hi = bf16(w) (w itself for a bf16 W); part 1 writes lo = bf16(w - hi), the next 8 mantissa bits.
+// With absmax_bits != null the record holds fp16 instead: hi = fp16(w * s), lo = fp16(w * s - hi), s =
+// operand_scale(largest |w|).
 template<typename WT>
 __global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int64_t ld, std::int64_t cols, int n, int part,
                                                            const float *scales, const float *offsets, int per_gene_offsets,
-                                                           unsigned char *records) {
+                                                           unsigned char *records, const unsigned *absmax_bits = nullptr) {
     const std::int64_t window = blockIdx.x;
     unsigned char *rec = records + window * record_bytes(n);
     __nv_bfloat16 *wt = reinterpret_cast<__nv_bfloat16 *>(rec);
+    const bool fp16 = absmax_bits != nullptr;
+    const float ws = fp16 ? operand_scale(__uint_as_float(*absmax_bits)) : 1.0f;
     for (int i = threadIdx.x; i < n * kWin; i += blockDim.x) {
         const int e = i / n, c = i % n; // consecutive threads read consecutive columns of one gene
         const std::int64_t gene = window * kWin + e;
@@ -93,9 +131,17 @@ __global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int
             if constexpr (sizeof(WT) == 2) value = __bfloat162float(w[gene * ld + c]);
             else value = w[gene * ld + c];
         }
+        const int at = ((c >> 3) * kRowGroupBytes + (e >> 3) * 128 + (c & 7) * 16 + (e & 7) * 2) >> 1;
+        if (fp16) {
+            const float scaled = value * ws;
+            __half h = __float2half_rn(scaled);
+            if (part != 0) h = __float2half_rn(scaled - __half2float(h));
+            reinterpret_cast<__half *>(rec)[at] = h;
+            continue;
+        }
         __nv_bfloat16 v = __float2bfloat16_rn(value);
         if (part != 0) v = __float2bfloat16_rn(value - __bfloat162float(v));
-        wt[((c >> 3) * kRowGroupBytes + (e >> 3) * 128 + (c & 7) * 16 + (e & 7) * 2) >> 1] = v;
+        wt[at] = v;
     }
     float2 *table = reinterpret_cast<float2 *>(rec + n * kWin * 2);
     for (int e = threadIdx.x; e < kWin; e += blockDim.x) {

@@ -121,6 +121,11 @@ struct blocked_layout {
     // the baked words hold byte positions in the transpose kernel's gene-major tile, not the forward one
     bool baked_gene_major = false;
     const void *src_scales = nullptr, *src_offsets = nullptr; // baked into the entries / the tiles
+    // the baked words (and the dense tiles made from them) hold fp16(value * value_scale) instead of bf16(value):
+    // 11 significant bits instead of 8; value_scale is a power of two chosen at prepare from the largest decoded
+    // magnitude the scales and offsets allow (forward operations; the transpose keeps bf16)
+    bool half_values = false;
+    float value_scale = 1.0f;
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);

@@ -54,6 +54,9 @@
 // the tensor pipe's (about a quarter busy) nor at HBM's.
 #include "blocked_tile.cuh"
 
+#include <algorithm>
+#include <cstring>
+
 namespace cb200 {
 namespace {
 
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                                                            std::int64_t rows, std::int64_t cols, int windows,
                                                            unsigned *counts, unsigned long long *cursor, std::uint32_t *entries,
                                                            int bake, const float *scales, const float *offsets,
-                                                           std::uint32_t *entries_lo, int gene_major) {
+                                                           std::uint32_t *entries_lo, int gene_major, float half_scale) {
     const int lane = threadIdx.x & 31;
     const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= rows) return; // warp-uniform
@@ -125,12 +128,21 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                     const float scale = scales != nullptr ? scales[gene] : 1.0f;
                     const float add = offsets != nullptr ? offsets[bake == 2 ? r : gene] : 0.0f;
                     const float value = fmaf(static_cast<float>(code), scale, add);
-                    const __nv_bfloat16 v = __float2bfloat16_rn(value);
                     const std::uint32_t position = ((gene_major != 0 ? tile_offset_gene_major(rl, gl) : tile_offset(rl, gl)) >> 1) << 16;
-                    word = static_cast<std::uint32_t>(__bfloat16_as_ushort(v)) | position;
-                    if (entries_lo != nullptr) // the next eight mantissa bits, for the split-product passes
-                        entries_lo[place + static_cast<unsigned>(lane - start)] =
-                            static_cast<std::uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(value - __bfloat162float(v)))) | position;
+                    if (half_scale != 0.0f) { // fp16(value * 2^k): 11 significant bits; the launch divides the result by 2^k again
+                        const float scaled = value * half_scale;
+                        const __half h = __float2half_rn(scaled);
+                        word = static_cast<std::uint32_t>(__half_as_ushort(h)) | position;
+                        if (entries_lo != nullptr) // the next eleven bits, for the split-product passes
+                            entries_lo[place + static_cast<unsigned>(lane - start)] =
+                                static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(scaled - __half2float(h)))) | position;
+                    } else {
+                        const __nv_bfloat16 v = __float2bfloat16_rn(value);
+                        word = static_cast<std::uint32_t>(__bfloat16_as_ushort(v)) | position;
+                        if (entries_lo != nullptr) // the next eight mantissa bits, for the split-product passes
+                            entries_lo[place + static_cast<unsigned>(lane - start)] =
+                                static_cast<std::uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(value - __bfloat162float(v)))) | position;
+                    }
                 } else {
                     word = code | (static_cast<std::uint32_t>(gl) << 8) | ((tile_offset(rl, gl) >> 1) << 15);
                 }
@@ -169,6 +181,26 @@ __global__ void __launch_bounds__(1024) segment_scan_kernel(const unsigned *coun
     if (threadIdx.x == 1023) seg_ptr[segments] = at; // the last slice (possibly empty) ends at the total
 }
 
+// Largest magnitude a decoded value can take, from the metadata alone: max over genes of |scale| * max code
+// (+ |offset| of the gene) in bound[0], max over rows of |row offset| in bound[1] (row-offset policy), as the
+// bits of non-negative floats.  The caller zeroes both words.
+__global__ void __launch_bounds__(256) value_bound_kernel(const float *scales, const float *gene_offsets, std::int64_t genes,
+                                                          const float *row_offsets, std::int64_t rows, float max_code, unsigned *bound) {
+    const std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    float a = 0.0f, b = 0.0f;
+    if (i < genes) a = fabsf(scales != nullptr ? scales[i] : 1.0f) * max_code + (gene_offsets != nullptr ? fabsf(gene_offsets[i]) : 0.0f);
+    if (row_offsets != nullptr && i < rows) b = fabsf(row_offsets[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (a > 0.0f) atomicMax(bound, __float_as_uint(a));
+        if (b > 0.0f) atomicMax(bound + 1, __float_as_uint(b));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // run time
 
@@ -187,6 +219,9 @@ struct blocked_params {
     int epilogue;
     int *status;
     int value_part; // 0: the tile holds hi = bf16(value); 1: lo = bf16(value - hi)
+    std::uint32_t idesc;       // instruction descriptor: bf16 or fp16 operands
+    float result_scale;        // 1 / (the power of two fp16 values were stored times); 1 for bf16 words
+    const unsigned *w_absmax;  // fp16 operands: largest |W| of this launch as float bits (its factor is undone too); else null
     int poll_limit; // polls a bounded wait makes before it gives up (kPollLimit; less under the test hook)
     int withhold_w; // test hook: the W loader issues no copies, so the waits for W run out
 };
@@ -199,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
     constexpr int REC = record_bytes(NC);
     constexpr int STAGES = w_stages(NC, CS);
     constexpr int kTmemCols = kSubBlocks * NC < 32 ? 32 : kSubBlocks * NC; // one accumulator per row sub-block
-    constexpr std::uint32_t IDESC = instr_desc(NC);
+    const std::uint32_t IDESC = p.idesc;
     extern __shared__ __align__(1024) unsigned char smem[];
     // [2][A tile] | [STAGES][W record] | [CS][entry chunk] | row offsets | barriers | chunk meta | tmem | abort
     unsigned char *chunk_base = smem + 2 * kABufBytes + STAGES * REC;
@@ -258,6 +293,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
     if (warp < kProducerWarps) {
         // ================= zero, scatter, epilogue =================
         const int sub = tid >> 7;
+        // fp16 operands were stored times powers of two: the result is divided by both again
+        const float alpha = p.alpha * p.result_scale / (p.w_absmax != nullptr ? operand_scale(__uint_as_float(__ldg(p.w_absmax))) : 1.0f);
         const bool use_row_offset = p.row_offsets != nullptr;
         long long q = 0;  // windows done by this CTA
         long long qc = 0; // chunks done by this CTA
@@ -338,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                 tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
                 if (row < p.row_end) {
                     float *out = p.y + row * p.y_ld + h * 32;
-                    store_row32(out, v, p.alpha, p.beta, p.bias, h * 32, p.epilogue);
+                    store_row32(out, v, alpha, p.beta, p.bias, h * 32, p.epilogue);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -497,7 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     constexpr int STAGES = w2_stages(NC);
     constexpr int CHUNKS = 2 * kRing2;
     constexpr int kTmemCols = kSubBlocks * NC < 32 ? 32 : kSubBlocks * NC;
-    constexpr std::uint32_t IDESC = instr_desc(NC);
+    const std::uint32_t IDESC = p.idesc;
     extern __shared__ __align__(1024) unsigned char smem[];
     // [2][A tile] | [STAGES][W window] | [2][kRing2][entry chunk] | barriers | chunk meta | tmem | abort | scratch
     unsigned char *chunk_base = smem + 2 * kABufBytes + STAGES * WREC;
@@ -558,6 +595,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
         // ================= two scatter groups; group 0 also writes Y =================
         const int grp = warp / kGroupWarps, gtid = tid - grp * kGroupThreads;
         const int sub = tid >> 7;
+        // fp16 operands were stored times powers of two: the result is divided by both again
+        const float alpha = p.alpha * p.result_scale / (p.w_absmax != nullptr ? operand_scale(__uint_as_float(__ldg(p.w_absmax))) : 1.0f);
         unsigned char *tile = smem + grp * kABufBytes;
         long long q = 0;  // windows of this CTA, both groups count all of them
         long long qc = 0; // chunks this group has consumed
@@ -609,7 +648,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
                 if (row < p.row_end) {
                     float *out = p.y + row * p.y_ld + h * 32;
-                    store_row32(out, v, p.alpha, p.beta, p.bias, h * 32, p.epilogue);
+                    store_row32(out, v, alpha, p.beta, p.bias, h * 32, p.epilogue);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -774,7 +813,7 @@ std::uint64_t qcsr_blocked_layout_bytes_bound(std::int64_t rows, std::int64_t co
     const std::uint64_t segments = groups * static_cast<std::uint64_t>((cols + kWin - 1) / kWin);
     // a segment is padded to a multiple of four words: at most three more per segment
     const std::uint64_t words = static_cast<std::uint64_t>(nnz) + 3u * segments;
-    return device_arena::rounded(segments * sizeof(unsigned)) + device_arena::rounded(segments * sizeof(unsigned long long)) +
+    return device_arena::rounded((segments + 2u) * sizeof(unsigned)) + device_arena::rounded(segments * sizeof(unsigned long long)) +
            device_arena::rounded((segments + 1u) * sizeof(std::int64_t)) + (bake_lo ? 2u : 1u) * device_arena::rounded(words * 4u);
 }
 
@@ -790,7 +829,9 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     const int windows = static_cast<int>((x.cols + kWin - 1) / kWin);
     const std::int64_t segments = groups * windows;
     const int bake_mode = !bake ? 0 : (x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET ? 2 : 1);
-    const std::uint64_t count_bytes = static_cast<std::uint64_t>(segments) * sizeof(unsigned);
+    const bool half_values = bake && !gene_major; // forward operations bake fp16 values; the transpose keeps bf16
+    // two words behind the segment counters for the bound of the decoded magnitudes
+    const std::uint64_t count_bytes = static_cast<std::uint64_t>(segments + 2) * sizeof(unsigned);
     const std::uint64_t cursor_bytes = static_cast<std::uint64_t>(segments) * sizeof(unsigned long long);
     const std::uint64_t seg_bytes = static_cast<std::uint64_t>(segments + 1) * sizeof(std::int64_t);
     unsigned *counts = static_cast<unsigned *>(arena.take(count_bytes));
@@ -811,18 +852,34 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     cudaError_t err = cudaMemsetAsync(counts, 0, count_bytes, stream);
     const unsigned grid = static_cast<unsigned>((x.rows + 7) / 8); // one warp per row, 8 rows per block
     std::int64_t total = 0;
+    unsigned bound_bits[2] = {0u, 0u};
+    if (err == cudaSuccess && half_values) {
+        const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+        const std::int64_t span = std::max<std::int64_t>(x.cols, row_policy ? x.rows : 0);
+        value_bound_kernel<<<static_cast<unsigned>((span + 255) / 256), 256, 0, stream>>>(
+            x.scales, row_policy ? nullptr : x.offsets, x.cols, row_policy ? x.offsets : nullptr, x.rows,
+            static_cast<float>((1 << x.bits) - 1), counts + segments);
+        count_launch();
+        err = cudaGetLastError();
+    }
     if (err == cudaSuccess) {
         if (x.bits == 8)
-            blocked_pass_kernel<8, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
+            blocked_pass_kernel<8, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0, 0.0f);
         else
-            blocked_pass_kernel<4, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
+            blocked_pass_kernel<4, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0, 0.0f);
         count_launch();
         segment_scan_kernel<<<1, 1024, 0, stream>>>(counts, segments, out->seg_ptr, cursor);
         count_launch();
         err = cudaGetLastError();
     }
     if (err == cudaSuccess) err = cudaMemcpyAsync(&total, out->seg_ptr + segments, sizeof(total), cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess && half_values)
+        err = cudaMemcpyAsync(bound_bits, counts + segments, sizeof(bound_bits), cudaMemcpyDeviceToHost, stream);
     if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    float bound = 0.0f, row_bound = 0.0f;
+    std::memcpy(&bound, &bound_bits[0], sizeof(float));
+    std::memcpy(&row_bound, &bound_bits[1], sizeof(float));
+    const float half_scale = half_values ? operand_scale(bound + row_bound) : 0.0f;
     if (err == cudaSuccess && total > 0) {
         word_bytes = static_cast<std::uint64_t>(total) * sizeof(std::uint32_t);
         out->entries = static_cast<std::uint32_t *>(arena.take(word_bytes));
@@ -834,9 +891,9 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
         if (err == cudaSuccess && out->entries_lo != nullptr) err = cudaMemsetAsync(out->entries_lo, 0x80, word_bytes, stream);
         if (err == cudaSuccess) {
             if (x.bits == 8)
-                blocked_pass_kernel<8, true><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
+                blocked_pass_kernel<8, true><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0, half_scale);
             else
-                blocked_pass_kernel<4, true><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0);
+                blocked_pass_kernel<4, true><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, nullptr, cursor, out->entries, bake_mode, x.scales, x.offsets, out->entries_lo, gene_major ? 1 : 0, half_scale);
             count_launch();
             err = cudaGetLastError();
         }
@@ -856,6 +913,8 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     out->baked_gene_major = bake && gene_major;
     out->src_scales = x.scales;
     out->src_offsets = x.offsets;
+    out->half_values = half_values;
+    out->value_scale = half_values ? half_scale : 1.0f;
     return CB200_STATUS_SUCCESS;
 }
 
@@ -884,9 +943,19 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     if (layout.baked && split_products && layout.entries_lo == nullptr) return CB200_STATUS_SUCCESS; // no lo words: another kernel runs
 
     int *status = static_cast<int *>(workspace);
+    unsigned *w_absmax = reinterpret_cast<unsigned *>(workspace) + 1; // fp16 operands: float bits of the largest |W|
     unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
     const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
-    CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    const bool half = layout.baked && layout.half_values;
+    CB200_CUDA_OK(cudaMemsetAsync(status, 0, 2 * sizeof(int), stream));
+    if (half) {
+        const std::int64_t elements = x.cols * d.n;
+        const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((elements + 1023) / 1024, 4 * static_cast<std::int64_t>(sm_count)));
+        if (w_bf16) absmax_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), w_absmax);
+        else absmax_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), w_absmax);
+        count_launch();
+        CB200_CUDA_OK(cudaGetLastError());
+    }
 
     blocked_params p{};
     p.entries = layout.entries; p.seg_ptr = layout.seg_ptr;
@@ -894,6 +963,9 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     p.records = records; p.y = d.out; p.y_ld = d.out_ld; p.row_end = row_end;
     p.group_begin = row_begin / kRows; p.group_end = (row_end + kRows - 1) / kRows; p.windows = layout.windows;
     p.alpha = d.alpha; p.status = status;
+    p.idesc = instr_desc(static_cast<int>(d.n), half);
+    p.result_scale = half ? 1.0f / layout.value_scale : 1.0f;
+    p.w_absmax = half ? w_absmax : nullptr;
     p.poll_limit = kPollLimit;
     p.withhold_w = 0;
     if (const int armed = g_test_poll_limit.load(std::memory_order_relaxed)) { // test hook: see cb200_test_arm_wait_timeout
@@ -918,11 +990,11 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
             if (w_bf16)
                 pack_windows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld,
                                                                               x.cols, static_cast<int>(d.n), passes[i].w_part, x.scales,
-                                                                              x.offsets, row_policy ? 0 : 1, records);
+                                                                              x.offsets, row_policy ? 0 : 1, records, half ? w_absmax : nullptr);
             else
                 pack_windows_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float *>(d.dense), d.dense_ld, x.cols,
                                                                       static_cast<int>(d.n), passes[i].w_part, x.scales, x.offsets,
-                                                                      row_policy ? 0 : 1, records);
+                                                                      row_policy ? 0 : 1, records, half ? w_absmax : nullptr);
             count_launch();
             CB200_CUDA_OK(cudaGetLastError());
             packed_part = passes[i].w_part;

@@ -7,6 +7,8 @@
 // has room for one (persistent_kernel_state, operation_core.hh:126-129).
 #include "blocked_tile.cuh"
 
+#include <algorithm>
+
 namespace cb200 {
 namespace {
 
@@ -90,6 +92,9 @@ struct dense_params {
     const float *bias;
     int epilogue;
     int *status;
+    std::uint32_t idesc;       // bf16 or fp16 operands
+    float result_scale;        // fp16 tiles: 1 / (the power of two the values were stored times)
+    const unsigned *w_absmax;  // fp16 operands: largest |W| of this launch as float bits; else null
 };
 
 template<int NC>
@@ -100,7 +105,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) qcsr_fwd_dense_kernel(const 
     constexpr int REC = record_bytes(NC);     // distance of the windows' records in global memory
     constexpr int kAccCols = kSubBlocks * NC; // one accumulator set: a group's rows x N
     constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
-    constexpr std::uint32_t IDESC = instr_desc(NC);
+    const std::uint32_t IDESC = p.idesc;
     static_assert(SA >= 2, "the half-stage ring needs two stages");
     extern __shared__ __align__(1024) unsigned char smem[];
     // [SA][half-stage] | [SB][W window] | barriers | tmem slot | abort
@@ -161,7 +166,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) qcsr_fwd_dense_kernel(const 
                 tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + ab * kAccCols + sub * NC + h * 32, v);
                 if (row < p.row_end) {
                     float *out = p.y + row * p.y_ld + h * 32;
-                    store_row32(out, v, p.alpha, p.beta, p.bias, h * 32, p.epilogue);
+                    store_row32(out, v, p.alpha * p.result_scale / (p.w_absmax != nullptr ? operand_scale(__uint_as_float(__ldg(p.w_absmax))) : 1.0f), p.beta, p.bias, h * 32, p.epilogue);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -294,7 +299,7 @@ cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, 
     layout->total_entries = 0;
     layout->dense_tiles = tiles;
     layout->bytes = bytes;
-    layout->baked = false;
+    layout->baked = false; // half_values / value_scale stay: the tiles hold what the baked words held
     layout->src_scales = x.scales;
     layout->src_offsets = x.offsets;
     *built = true;
@@ -314,16 +319,29 @@ cb200_status launch_qcsr_forward_dense(const qcsr_view &x, const dense_args &d, 
         x.scales != layout.src_scales || x.offsets != layout.src_offsets)
         return fail(CB200_STATUS_STALE_STRUCTURE, "the launch's matrix is not the one the dense operand tiles were built from");
     int *status = static_cast<int *>(workspace);
+    unsigned *w_absmax = reinterpret_cast<unsigned *>(workspace) + 1; // fp16 operands: float bits of the largest |W|
     unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
-    CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    const bool half = layout.half_values;
+    CB200_CUDA_OK(cudaMemsetAsync(status, 0, 2 * sizeof(int), stream));
+    if (half) {
+        const std::int64_t elements = x.cols * d.n;
+        const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((elements + 1023) / 1024, 4 * static_cast<std::int64_t>(sm_count)));
+        absmax_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), w_absmax);
+        count_launch();
+        CB200_CUDA_OK(cudaGetLastError());
+    }
     pack_windows_kernel<__nv_bfloat16><<<static_cast<unsigned>(layout.windows), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), 0, nullptr, nullptr, 0, records);
+        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), 0, nullptr, nullptr, 0, records,
+        half ? w_absmax : nullptr);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     dense_params p{};
     p.tiles = layout.dense_tiles; p.records = records; p.y = d.out; p.y_ld = d.out_ld; p.row_end = row_end;
     p.group_begin = row_begin / kRows; p.group_end = (row_end + kRows - 1) / kRows; p.windows = layout.windows;
     p.alpha = d.alpha; p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue; p.status = status;
+    p.idesc = instr_desc(static_cast<int>(d.n), half);
+    p.result_scale = half ? 1.0f / layout.value_scale : 1.0f;
+    p.w_absmax = half ? w_absmax : nullptr;
     *taken = true;
     switch (d.n) {
     case 32: return launch_dense<32>(p, sm_count, stream);

@@ -70,9 +70,11 @@ __device__ __forceinline__ std::uint64_t smem_desc_sw128(std::uint32_t addr) {
     d |= static_cast<std::uint64_t>(2) << 61; // 128-byte swizzle
     return d;
 }
-// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, M = 128.
-__host__ __device__ constexpr std::uint32_t instr_desc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((static_cast<std::uint32_t>(n) >> 3) << 17) | ((128u >> 4) << 24);
+// kind::f16 instruction descriptor: D fp32, A and B both bf16 (format 1) or both fp16 (format 0), both K-major,
+// M = 128.
+__host__ __device__ constexpr std::uint32_t instr_desc(int n, bool fp16_operands = false) {
+    return (1u << 4) | ((fp16_operands ? 0u : 1u) << 7) | ((fp16_operands ? 0u : 1u) << 10) |
+           ((static_cast<std::uint32_t>(n) >> 3) << 17) | ((128u >> 4) << 24);
 }
 __device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b, std::uint32_t idesc,
                                          bool accumulate) {
