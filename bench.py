@@ -515,7 +515,7 @@ def measure_workload(name, args, device, rank, world, steps, warmup, fleet, mult
                            "useful_tflops": wl["flops"] / (kernel_ms * 1e-3) / 1e12}
     rec["frac"] = rec["roofline"]["frac"]
     if check and rank == 0:
-        bf16_products = op.schedule in ("tensor_windows", "tensor_blocked", "tensor_dense", "tcgen05_block_rows")
+        bf16_products = op.schedule in ("tensor_windows", "tensor_blocked", "tensor_dense", "tensor_codes", "tcgen05_block_rows")
         rec["parity_check"] = parity_of_what_ran(wl, op, bf16_products)
     return rec, wl
 
@@ -680,7 +680,9 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"],
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": f"u{main['bits']} codes -> " + ("bf16 products (tcgen05), f32 accumulate"
-                                                 if schedule in ("tensor_windows", "tensor_blocked", "tensor_dense", "tcgen05_block_rows")
+                                                 if schedule in ("tensor_windows", "tcgen05_block_rows")
+                                                 else "fp16 products (tcgen05), f32 accumulate"
+                                                 if schedule in ("tensor_blocked", "tensor_dense", "tensor_codes")
                                                  else "split bf16 products (tcgen05, %s passes), f32 accumulate" % schedule[-1]
                                                  if schedule in ("tensor_blocked_x2", "tensor_blocked_x3")
                                                  else "f32 products, f32 accumulate"),
@@ -690,9 +692,12 @@ def run_ours(args):
                    "dense": "bf16" if args.workload != "c3_transpose" else "f32",
                    "parallelism": f"row-sharded x{world}" + (" + NCCL allreduce (cb200_fleet_run_transpose)" if args.workload == "c3_transpose" and world > 1 else ""),
                    "l2": "inputs larger than L2 (126 MB); no flush needed", "schedule": schedule,
-                   "dequantisation": ("at prepare: the timed kernel streams {bf16 decoded value, tile position} words that prepare "
+                   "dequantisation": ("at prepare: the timed kernel streams {fp16 decoded value, tile position} words that prepare "
                                       "wrote from the codes, scales and offsets; a change of any of them needs a new prepare"
-                                      if baked else "at launch: codes, scales and offsets are read by the timed kernel"),
+                                      if baked else
+                                      "at launch, in registers: the timed kernel streams dense tiles of codes (a byte per slot) that "
+                                      "prepare laid out; scales and offsets are read at every launch"
+                                      if schedule == "tensor_codes" else "at launch: codes, scales and offsets are read by the timed kernel"),
                    "prepare_ms_once": main["prepare_ms_once"], "persistent_bytes": main["persistent_bytes"]},
         "step_ms": main["step_ms"], "value_at_median": main["value_at_median"],
         "gpu_launches": main["gpu_launches"],

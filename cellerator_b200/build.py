@@ -30,7 +30,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "-I", os.path.join(ROOT, "include")] + os.environ.get("CB200_NVCC_EXTRA", "").split()
 
-KERNEL_SOURCES = ["capi.cu", "host_contract.cu", "fleet.cu", "host_stage.cu", "qcsr_forward.cu", "qcsr_forward_tiled.cu", "qcsr_forward_mma.cu", "qcsr_forward_blocked.cu", "qcsr_forward_dense.cu", "qcsr_transpose.cu", "qcsr_transpose_blocked.cu", "bell_lowering.cu", "public_route.cu", "gene_major.cu", "qbell_forward.cu", "qbell_tcgen05.cu",
+KERNEL_SOURCES = ["capi.cu", "host_contract.cu", "fleet.cu", "host_stage.cu", "qcsr_forward.cu", "qcsr_forward_tiled.cu", "qcsr_forward_mma.cu", "qcsr_forward_blocked.cu", "qcsr_forward_dense.cu", "qcsr_forward_codes.cu", "qcsr_transpose.cu", "qcsr_transpose_blocked.cu", "bell_lowering.cu", "public_route.cu", "gene_major.cu", "qbell_forward.cu", "qbell_tcgen05.cu",
                   "codec.cu"]
 SYNTH_SOURCES = ["synth.cu"]
 

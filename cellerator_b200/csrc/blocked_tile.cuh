@@ -91,11 +91,11 @@ __host__ __device__ __forceinline__ float operand_scale(float absmax) {
 }
 // Largest magnitude of a dense operand as the bits of a float in *out_bits (zeroed by the caller before).
 template<typename WT>
-__global__ void __launch_bounds__(256) absmax_kernel(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits) {
+__device__ __forceinline__ void absmax_body(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits, unsigned block, unsigned blocks) {
     float m = 0.0f;
     const std::int64_t total = rows * n;
-    for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+    for (std::int64_t i = static_cast<std::int64_t>(block) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<std::int64_t>(blocks) * blockDim.x) {
         const std::int64_t r = i / n;
         const int c = static_cast<int>(i - r * n);
         float v;
@@ -107,13 +107,43 @@ __global__ void __launch_bounds__(256) absmax_kernel(const WT *w, std::int64_t l
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(out_bits, __float_as_uint(m)); // non-negative floats order like their bits
 }
+template<typename WT>
+__global__ void __launch_bounds__(256) absmax_kernel(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits) {
+    absmax_body(w, ld, rows, n, out_bits, blockIdx.x, gridDim.x);
+}
+
+// Largest magnitude a decoded value can take, from the metadata alone: max over genes of |scale| * max code
+// (+ |offset| of the gene) in bound[0], max over rows of |row offset| in bound[1] (row-offset policy), as the
+// bits of non-negative floats.  The caller zeroes both words.
+__device__ __forceinline__ void value_bound_body(const float *scales, const float *gene_offsets, std::int64_t genes, const float *row_offsets,
+                                                 std::int64_t rows, float max_code, unsigned *bound, unsigned block) {
+    const std::int64_t i = static_cast<std::int64_t>(block) * blockDim.x + threadIdx.x;
+    float a = 0.0f, b = 0.0f;
+    if (i < genes) a = fabsf(scales != nullptr ? scales[i] : 1.0f) * max_code + (gene_offsets != nullptr ? fabsf(gene_offsets[i]) : 0.0f);
+    if (row_offsets != nullptr && i < rows) b = fabsf(row_offsets[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (a > 0.0f) atomicMax(bound, __float_as_uint(a));
+        if (b > 0.0f) atomicMax(bound + 1, __float_as_uint(b));
+    }
+}
+__global__ void __launch_bounds__(256) value_bound_kernel(const float *scales, const float *gene_offsets, std::int64_t genes,
+                                                          const float *row_offsets, std::int64_t rows, float max_code, unsigned *bound) {
+    value_bound_body(scales, gene_offsets, genes, row_offsets, rows, max_code, bound, blockIdx.x);
+}
 
 // W [genes][n] (leading dimension ld) -> one record per window of 128 genes: the n x 128 slice of
 // W^T in operand layout (byte offset of (column c, gene e) = (c/8)*2048 + (e/8)*128 + (c%8)*16 +
 // (e%8)*2, zero for genes >= cols) followed by 128 x {scale, zero-point}.  part 0 writes
 // hi = bf16(w) (w itself for a bf16 W); part 1 writes lo = bf16(w - hi), the next 8 mantissa bits.
 // With absmax_bits != null the record holds fp16 instead: hi = fp16(w * s), lo = fp16(w * s - hi), s =
-// operand_scale(largest |w|).
+// operand_scale(largest |w|).  The grid is (windows, column groups): block (w, g) lays out columns [g, g + 1) * n /
+// gridDim.y of window w; the blocks of group 0 also write the window's table.
+constexpr int kPackColumns = 16; // columns of W per block of the packing kernel
 template<typename WT>
 __global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int64_t ld, std::int64_t cols, int n, int part,
                                                            const float *scales, const float *offsets, int per_gene_offsets,
@@ -123,8 +153,9 @@ __global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int
     __nv_bfloat16 *wt = reinterpret_cast<__nv_bfloat16 *>(rec);
     const bool fp16 = absmax_bits != nullptr;
     const float ws = fp16 ? operand_scale(__uint_as_float(*absmax_bits)) : 1.0f;
-    for (int i = threadIdx.x; i < n * kWin; i += blockDim.x) {
-        const int e = i / n, c = i % n; // consecutive threads read consecutive columns of one gene
+    const int group_cols = n / static_cast<int>(gridDim.y), c_first = static_cast<int>(blockIdx.y) * group_cols;
+    for (int i = threadIdx.x; i < group_cols * kWin; i += blockDim.x) {
+        const int e = i / group_cols, c = c_first + i % group_cols; // consecutive threads read consecutive columns of one gene
         const std::int64_t gene = window * kWin + e;
         float value = 0.0f;
         if (gene < cols) {
@@ -143,6 +174,7 @@ __global__ void __launch_bounds__(256) pack_windows_kernel(const WT *w, std::int
         if (part != 0) v = __float2bfloat16_rn(value - __bfloat162float(v));
         wt[at] = v;
     }
+    if (blockIdx.y != 0) return;
     float2 *table = reinterpret_cast<float2 *>(rec + n * kWin * 2);
     for (int e = threadIdx.x; e < kWin; e += blockDim.x) {
         const std::int64_t gene = window * kWin + e;

@@ -283,6 +283,7 @@ struct schedule_plan {
     bool split = false;          // fp32 products rebuilt from bf16 passes
     bool dense_wanted = false;   // forward: decoded operand tiles instead of entry words, when they fit
     bool dense_forced = false;   // ... asked for by name: the free-memory rule does not apply
+    bool codes_wanted = false;   // forward, 4-bit codes: tiles of codes (a byte per slot) instead of decoded tiles
     bool gene_gather = false;    // transpose with a fixed order of the sums
     bool row_order = false;      // length-sorted row order for the tiled kernels
     bool bell_cuda_cores = false;
@@ -396,7 +397,8 @@ schedule_plan plan_schedule(const cb200_spmm_problem &pr) {
                             qcsr_blocked_shape_ok(pr.m, pr.k, pr.n, pr.bits, pr.dense_dtype);
     const double min_density = !split ? 0.015 : (pr.dense_dtype == CB200_DTYPE_BF16 ? 0.04 : 0.06);
     bool blocked = blocked_ok && pr.m >= 16 * 256 && plan.mean_row_nnz >= min_density * static_cast<double>(pr.k);
-    if (hint != nullptr) blocked = blocked_ok && (hint_starts(hint, "tensor_blocked") || (!split && hint_is(hint, "tensor_dense")));
+    if (hint != nullptr)
+        blocked = blocked_ok && (hint_starts(hint, "tensor_blocked") || (!split && (hint_is(hint, "tensor_dense") || hint_is(hint, "tensor_codes"))));
     if (blocked && limit != 0u && nnz * 4u > limit) blocked = false; // a word per entry
     plan.split = split;
     plan.blocked = blocked;
@@ -414,6 +416,17 @@ schedule_plan plan_schedule(const cb200_spmm_problem &pr) {
         plan.dense_forced = dense && hint != nullptr;
         if (limit != 0u && tile_bytes > limit) dense = false;
         plan.dense_wanted = dense;
+        // 4-bit codes with per-gene zero-points: keep tiles of CODES instead (one byte per slot, half the decoded
+        // tiles; scale and zero-point applied at launch).  Preferred to the decoded tiles wherever both would be built.
+        const bool codes_ok = !split && qcsr_codes_shape_ok(pr.m, pr.k, pr.n, pr.bits, pr.policy, pr.dense_dtype);
+        bool codes = codes_ok && plan.mean_row_nnz >= 0.08 * static_cast<double>(pr.k);
+        if (hint != nullptr) codes = codes_ok && hint_is(hint, "tensor_codes");
+        if (limit != 0u && qcsr_code_tile_bytes(pr.m, pr.k) > limit) codes = false;
+        if (codes) {
+            plan.codes_wanted = true;
+            plan.dense_wanted = false;
+            plan.dense_forced = hint != nullptr;
+        }
     }
     plan.tiled = tiled;
     plan.tensor_windows = tensor;
@@ -428,6 +441,7 @@ std::uint64_t plan_persistent_bytes(const cb200_spmm_problem &pr, const schedule
     if (plan.gene_gather) bytes += qcsr_gene_major_layout_bytes_bound(pr.m, pr.k, pr.nnz);
     if (plan.blocked) bytes += qcsr_blocked_layout_bytes_bound(pr.m, pr.k, pr.nnz, plan.blocked_lo);
     if (plan.dense_wanted) bytes += device_arena::rounded(qcsr_dense_tile_bytes(pr.m, pr.k));
+    if (plan.codes_wanted) bytes += device_arena::rounded(qcsr_code_tile_bytes(pr.m, pr.k));
     if (plan.row_order) bytes += device_arena::rounded(static_cast<std::uint64_t>(pr.m) * sizeof(std::int32_t));
     return bytes;
 }
@@ -512,7 +526,8 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         delete p;
         return st;
     };
-    if (p->arena.borrowed && plan_persistent_bytes(*problem, plan) - (plan.dense_wanted ? device_arena::rounded(qcsr_dense_tile_bytes(problem->m, problem->k)) : 0u) >
+    if (p->arena.borrowed && plan_persistent_bytes(*problem, plan) - (plan.dense_wanted ? device_arena::rounded(qcsr_dense_tile_bytes(problem->m, problem->k)) : 0u) -
+                                     (plan.codes_wanted ? device_arena::rounded(qcsr_code_tile_bytes(problem->m, problem->k)) : 0u) >
                                  p->arena.capacity)
         return abandon(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "persistent memory of %llu bytes needed (cb200_spmm_persistent_requirement), %llu given",
                             (unsigned long long)plan_persistent_bytes(*problem, plan), (unsigned long long)p->arena.capacity));
@@ -568,12 +583,29 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
         }
         if (plan.blocked) {
             const qcsr_view dm = view_of(*problem->device_matrix);
-            cb200_status st = build_blocked_layout(dm, !plan.split || plan.blocked_lo, plan.blocked_lo, false, p->arena, stream, &p->blocked);
+            // code tiles are made from code words; everything else from baked (decoded) words where it can be
+            bool codes = plan.codes_wanted;
+            if (codes && !plan.dense_forced && !p->arena.borrowed) {
+                std::size_t free_bytes = 0, total_bytes = 0;
+                codes = cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess &&
+                        qcsr_code_tile_bytes(problem->m, problem->k) + static_cast<std::uint64_t>(problem->nnz) * 4u <= free_bytes / 2u;
+            }
+            cb200_status st = build_blocked_layout(dm, !codes && (!plan.split || plan.blocked_lo), !codes && plan.blocked_lo, false, p->arena,
+                                                   stream, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) return abandon(st);
             p->schedule = fwd_schedule::tensor_blocked;
             p->schedule_name = !plan.split ? "tensor_blocked"
                                            : (problem->dense_dtype == CB200_DTYPE_BF16 ? "tensor_blocked_x2" : "tensor_blocked_x3");
             p->workspace_bytes = std::max<std::uint64_t>(qcsr_blocked_workspace_bytes(problem->k, problem->n), 256u);
+            if (codes) {
+                bool built = false;
+                st = bytify_blocked_layout(&p->blocked, p->arena, stream, &built);
+                if (st != CB200_STATUS_SUCCESS) return abandon(st);
+                if (built) {
+                    p->schedule_name = "tensor_codes";
+                    p->workspace_bytes = std::max<std::uint64_t>(p->workspace_bytes, qcsr_codes_workspace_bytes(problem->k, problem->n));
+                }
+            }
             bool dense = plan.dense_wanted;
             if (dense && !plan.dense_forced && !p->arena.borrowed) {
                 // own allocations: the tiles may take half of what the device has free, no more
@@ -664,7 +696,8 @@ cb200_status cb200_spmm_run(const cb200_prepared *prepared, const cb200_launch *
                     (unsigned long long)prepared->workspace_bytes, (unsigned long long)launch->workspace_bytes);
     /* lifetimes.hh:160-172: the expected generation of a bound value plane must be the live one; here the
      * "live" values of a prepared copy are those it was built from */
-    if ((prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr || prepared->gene_major.col_ptr != nullptr) &&
+    if ((prepared->blocked.seg_ptr != nullptr || prepared->blocked.dense_tiles != nullptr || prepared->blocked.code_tiles != nullptr ||
+         prepared->gene_major.col_ptr != nullptr) &&
         pr.value_generation != 0u &&
         launch->value_generation != 0u && launch->value_generation != pr.value_generation)
         return fail(CB200_STATUS_STALE_VALUE, "the prepared operation keeps a copy of value generation %llu, the launch binds %llu",

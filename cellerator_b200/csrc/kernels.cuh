@@ -126,6 +126,10 @@ struct blocked_layout {
     // magnitude the scales and offsets allow (forward operations; the transpose keeps bf16)
     bool half_values = false;
     float value_scale = 1.0f;
+    // Code tiles (forward, 4-bit codes, schedule "tensor_codes"): per (group, half window of 64 genes) a 16 KB stage
+    // with one byte per (cell, gene), 0 = nothing stored, else code + 1.  When set, entries / seg_ptr are gone.
+    // Scales and offsets are NOT in it: they are applied at launch.
+    unsigned char *code_tiles = nullptr;
 };
 bool qcsr_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int dense_dtype);
 std::uint64_t qcsr_blocked_workspace_bytes(std::int64_t cols, std::int64_t n);
@@ -142,6 +146,14 @@ std::uint64_t qcsr_blocked_layout_bytes_bound(std::int64_t rows, std::int64_t co
 std::uint64_t qcsr_dense_tile_bytes(std::int64_t rows, std::int64_t cols);
 cb200_status densify_blocked_layout(const qcsr_view &x, blocked_layout *layout, device_arena &arena, cudaStream_t stream,
                                     bool *built);
+// Code tiles from the window-blocked copy built with code words (bake == false); the entry words go back to the arena.
+bool qcsr_codes_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int policy, int dense_dtype);
+std::uint64_t qcsr_code_tile_bytes(std::int64_t rows, std::int64_t cols);
+std::uint64_t qcsr_codes_workspace_bytes(std::int64_t cols, std::int64_t n);
+cb200_status bytify_blocked_layout(blocked_layout *layout, device_arena &arena, cudaStream_t stream, bool *built);
+cb200_status launch_qcsr_forward_codes(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
+                                       std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
+                                       const blocked_layout &layout, int sm_count, cudaStream_t stream, bool *taken);
 // *taken as for the blocked launch below; the tiles hold bf16(value): one pass of bf16 products only
 cb200_status launch_qcsr_forward_dense(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                        std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,

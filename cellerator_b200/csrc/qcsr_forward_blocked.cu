@@ -181,26 +181,6 @@ __global__ void __launch_bounds__(1024) segment_scan_kernel(const unsigned *coun
     if (threadIdx.x == 1023) seg_ptr[segments] = at; // the last slice (possibly empty) ends at the total
 }
 
-// Largest magnitude a decoded value can take, from the metadata alone: max over genes of |scale| * max code
-// (+ |offset| of the gene) in bound[0], max over rows of |row offset| in bound[1] (row-offset policy), as the
-// bits of non-negative floats.  The caller zeroes both words.
-__global__ void __launch_bounds__(256) value_bound_kernel(const float *scales, const float *gene_offsets, std::int64_t genes,
-                                                          const float *row_offsets, std::int64_t rows, float max_code, unsigned *bound) {
-    const std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    float a = 0.0f, b = 0.0f;
-    if (i < genes) a = fabsf(scales != nullptr ? scales[i] : 1.0f) * max_code + (gene_offsets != nullptr ? fabsf(gene_offsets[i]) : 0.0f);
-    if (row_offsets != nullptr && i < rows) b = fabsf(row_offsets[i]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
-    }
-    if ((threadIdx.x & 31) == 0) {
-        if (a > 0.0f) atomicMax(bound, __float_as_uint(a));
-        if (b > 0.0f) atomicMax(bound + 1, __float_as_uint(b));
-    }
-}
-
 // ---------------------------------------------------------------------------------------------
 // run time
 
@@ -925,6 +905,10 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
                                          cudaStream_t stream, bool *taken) {
     *taken = false;
     if (row_end <= row_begin) return CB200_STATUS_SUCCESS;
+    if (layout.code_tiles != nullptr) {
+        if (split_products) return CB200_STATUS_SUCCESS; // one 16-bit pass only
+        return launch_qcsr_forward_codes(x, d, row_begin, row_end, workspace, workspace_bytes, layout, sm_count, stream, taken);
+    }
     if (layout.dense_tiles != nullptr) {
         if (split_products) return CB200_STATUS_SUCCESS; // the tiles hold bf16(value) only
         return launch_qcsr_forward_dense(x, d, row_begin, row_end, workspace, workspace_bytes, layout, sm_count, stream, taken);
@@ -986,7 +970,7 @@ cb200_status launch_qcsr_forward_blocked(const qcsr_view &x, const dense_args &d
     int packed_part = -1;
     for (int i = 0; i < pass_count; ++i) {
         if (passes[i].w_part != packed_part) {
-            const unsigned grid = static_cast<unsigned>(layout.windows);
+            const dim3 grid(static_cast<unsigned>(layout.windows), static_cast<unsigned>(d.n / kPackColumns));
             if (w_bf16)
                 pack_windows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld,
                                                                               x.cols, static_cast<int>(d.n), passes[i].w_part, x.scales,

@@ -330,7 +330,7 @@ cb200_status launch_qcsr_forward_dense(const qcsr_view &x, const dense_args &d, 
         count_launch();
         CB200_CUDA_OK(cudaGetLastError());
     }
-    pack_windows_kernel<__nv_bfloat16><<<static_cast<unsigned>(layout.windows), 256, 0, stream>>>(
+    pack_windows_kernel<__nv_bfloat16><<<dim3(static_cast<unsigned>(layout.windows), static_cast<unsigned>(d.n / kPackColumns)), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), 0, nullptr, nullptr, 0, records,
         half ? w_absmax : nullptr);
     count_launch();

@@ -42,6 +42,20 @@ __device__ __forceinline__ bool bar_wait(std::uint32_t bar, std::uint32_t parity
     }
     return false;
 }
+// The same for a barrier that is normally microseconds away (a ring with slack, a whole row group of MMAs): the
+// warp sleeps `ns` between polls, which leaves the issue slots of its scheduler to the warps that are working.
+__device__ __forceinline__ bool bar_wait_sleeping(std::uint32_t bar, std::uint32_t parity, volatile int *abort_flag, unsigned ns) {
+    int spins = 0;
+    while (!bar_try_wait(bar, parity)) {
+        if (*abort_flag != 0) return true;
+        if (++spins > kPollLimit / 4) {
+            *abort_flag = 1;
+            return true;
+        }
+        __nanosleep(ns);
+    }
+    return false;
+}
 // Bounded wait that does not look at the abort flag: what a role uses, after the CTA has aborted, to let the
 // copies or MMAs it still has in flight finish before the CTA gives up its shared memory and TMEM.
 __device__ __forceinline__ bool bar_wait_drain(std::uint32_t bar, std::uint32_t parity, int limit = kPollLimit) {

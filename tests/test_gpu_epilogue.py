@@ -47,6 +47,7 @@ FORWARD_CASES = [
     ("tensor_windows", torch.bfloat16, 64, capi.DTYPE_BF16, False, 1e-2),
     ("tensor_blocked", torch.bfloat16, 128, capi.DTYPE_BF16, True, 1e-2),
     ("tensor_dense", torch.bfloat16, 64, capi.DTYPE_BF16, True, 1e-2),
+    ("tensor_codes", torch.bfloat16, 128, capi.DTYPE_BF16, True, 1e-2),   # 4-bit codes
     ("tensor_blocked_x2", torch.bfloat16, 64, 0, True, 1e-4),     # the epilogue runs once, on the last pass
     ("tensor_blocked_x3", torch.float32, 32, 0, True, 1e-4),
 ]
@@ -56,7 +57,7 @@ FORWARD_CASES = [
 def test_forward_epilogues(cuda_device, oracle, monkeypatch, schedule, dtype, n, multiply, hand_matrix, tol):
     monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule.split("_x")[0])
     rng = np.random.default_rng(len(schedule) * 131 + n)
-    rows, cols, bits, policy = 2 * 1024 + 77, 900, 8, 1
+    rows, cols, bits, policy = 2 * 1024 + 77, 900, 4 if schedule == "tensor_codes" else 8, 1
     c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=280, bits=bits, policy=policy))
     x = to_dev(c, cuda_device)
     w, w_host = dense(rng, cols, n, dtype, cuda_device, std=0.05)

@@ -42,16 +42,18 @@ def prepared(x, n, w, device, blocked=False, **kw):
                             device_matrix=x if blocked else None, **kw)
 
 
-BLOCKED = ("tensor_blocked", "tensor_dense")          # schedules that need the matrix at prepare
+BLOCKED = ("tensor_blocked", "tensor_dense", "tensor_codes")          # schedules that need the matrix at prepare
 
 
-@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked", "tensor_dense"])
+@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked", "tensor_dense", "tensor_codes"])
 @pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("n", [32, 64, 128])
 @pytest.mark.parametrize("policy", [1, 2])
 def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits, n, policy):
     """Forced on a small matrix: several row groups (ragged last one, empty rows), a ragged last
     gene window, row starts at every alignment; row ranges, alpha/beta, determinism."""
+    if schedule == "tensor_codes" and (bits != 4 or policy != 1):
+        pytest.skip("code tiles hold 4-bit codes with per-gene zero-points")
     monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule)
     rng = np.random.default_rng(77 * bits + n + policy)
     rows, cols = 512 * 2 + 171, 1000
@@ -64,6 +66,8 @@ def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits
         assert 4 * x.nnz <= op.persistent_bytes <= 4 * x.nnz + 64 * ((rows + 255) // 256) * ((cols + 127) // 128) + 4 * rows
     if schedule == "tensor_dense":                                      # one 64 KB tile per 256 rows x 128 genes
         assert op.persistent_bytes == 65536 * ((rows + 255) // 256) * ((cols + 127) // 128)
+    if schedule == "tensor_codes":                                      # a byte per slot: half of that
+        assert op.persistent_bytes == 32768 * ((rows + 255) // 256) * ((cols + 127) // 128)
     y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
     torch.cuda.synchronize()
     assert int(op.workspace[:4].view(torch.int32).item()) == 0          # no bounded wait ran out
@@ -94,6 +98,16 @@ def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits
     y0 = torch.from_numpy(rng.normal(size=(rows, n)).astype(np.float32)).to(cuda_device)
     y1 = op.run(x, w, y0.clone(), alpha=2.0, beta=0.5)
     assert torch.allclose(y1, 2.0 * y + 0.5 * y0, rtol=1e-5, atol=1e-6)
+    if schedule == "tensor_codes":
+        # the tiles hold codes: scale and zero-point are read at launch, so new ones need no new prepare
+        c2 = dict(c, scales=(c["scales"] * 1.7).astype(np.float32), offsets=(c["offsets"] - 0.3).astype(np.float32))
+        x.scales.copy_(torch.from_numpy(c2["scales"]))
+        x.offsets.copy_(torch.from_numpy(c2["offsets"]))
+        y2 = op.run(x, w, torch.empty_like(y))
+        ref2 = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c2["scales"],
+                                   c2["offsets"], w_host, cols)
+        l1b, _ = row_l1(oracle, c2)
+        assert_tensor_close(y2.cpu().numpy(), ref2, l1b, wmax)
     op.close()
 
 
@@ -148,19 +162,21 @@ def test_dense_tiles_respect_the_memory_limit(cuda_device, oracle, monkeypatch):
         o.close()
 
 
-@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked", "tensor_dense"])
+@pytest.mark.parametrize("schedule", ["tensor_windows", "tensor_blocked", "tensor_dense", "tensor_codes"])
 @pytest.mark.parametrize("bits,n", [(8, 64), (4, 128)])
 def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule, bits, n):
     """Genes as in the benchmark configuration, 1/8 of its cells, device-generated: agreement with
     the exact schedule on every row, row-partition invariance, sampled rows against the oracle."""
+    if schedule == "tensor_codes" and bits != 4:
+        pytest.skip("code tiles hold 4-bit codes")
     cfg = dict(synth.CONFIGS["c2_forward" if bits == 8 else "c4_4bit"])
     cfg["rows"] //= 8
     x = synth.make_qcsr_device(**{**cfg, "bits": bits}, device=cuda_device, seed=0)
     rng = np.random.default_rng(9)
     w1, w_host = dense(rng, x.cols, n, torch.bfloat16, cuda_device)
     # prepare's own choice: the 5 %-dense 33,538-gene matrix keeps the window-blocked copy, the 17 %-dense
-    # 4,000-gene one the dense tiles; the other combinations are forced
-    own = {8: "tensor_blocked", 4: "tensor_dense"}[bits]
+    # 4,000-gene one (4-bit codes) the code tiles; the other combinations are forced
+    own = {8: "tensor_blocked", 4: "tensor_codes"}[bits]
     if schedule != own:
         monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule)
     op = prepared(x, n, w1, cuda_device, blocked=schedule in BLOCKED)
