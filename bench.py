@@ -41,6 +41,7 @@ NCU_DRAM_BYTES_PER_NNZ = {
     ("c2_forward", "gene_tiled"): 5.32,       # profiles/qcsr_fwd_tiled__c2_75776_rows.md
     ("c2_forward", "warp_per_row"): 5.21,     # profiles/qcsr_fwd_warp_row__c2_60k_rows.md
     ("c4_4bit", "tensor_dense"): 12.8,        # profiles/qcsr_fwd_dense__c4_131072_rows.md
+    ("c4_4bit", "tensor_codes"): 6.6,         # profiles/qcsr_fwd_codes__c4_131072_rows.md
 }
 
 

@@ -496,7 +496,7 @@ const char *prepared_schedule(const core::prepared_operation &prepared) noexcept
 const char *schedule_name(std::uint32_t variant) noexcept {
     static const char *const names[schedule_variant_count] = {"", "warp_per_row", "gene_tiled", "tensor_windows", "tensor_blocked",
                                                                "tensor_dense", "vector_reductions", "gene_gather",
-                                                               "tcgen05_block_rows", "cuda_cores"};
+                                                               "tcgen05_block_rows", "cuda_cores", "tensor_codes"};
     return variant < schedule_variant_count ? names[variant] : "";
 }
 
@@ -508,7 +508,7 @@ const char *schedule_name(std::uint32_t variant) noexcept {
     const bool transpose = shape.projection_kind == CB200_PROJECTION_TRANSPOSE;
     const bool split = multiply != CB200_DTYPE_BF16;
     // Fraction of the measured HBM copy bandwidth each schedule reached on B200 on the benchmark configurations
-    // (1M x 33,538 cells x genes at 5.4 % density; 500k x 4,000 at 17 % for the dense tiles; 250k x 8,192 Blocked-ELL).
+    // (1M x 33,538 cells x genes at 5.4 % density; 500k x 4,000 at 17 % for the dense and the code tiles; 250k x 8,192 Blocked-ELL).
     double fraction = 0.05;
     switch (variant) {
     case schedule_warp_per_row: fraction = 0.05; break;
@@ -518,6 +518,7 @@ const char *schedule_name(std::uint32_t variant) noexcept {
         fraction = transpose ? (split ? 0.078 : 0.226) : (split ? (shape.dense_dtype == CB200_DTYPE_BF16 ? 0.112 : 0.075) : 0.224);
         break;
     case schedule_tensor_dense: fraction = 0.395; break;
+    case schedule_tensor_codes: fraction = 0.449; break;
     case schedule_vector_reductions: fraction = 0.013; break;
     case schedule_gene_gather: fraction = 0.047; break;
     case schedule_tcgen05_block_rows: fraction = 0.188; break;

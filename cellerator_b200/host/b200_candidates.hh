@@ -129,7 +129,8 @@ enum schedule_variant : std::uint32_t {
     schedule_gene_gather = 7u,        // transpose, fixed order of the sums
     schedule_tcgen05_block_rows = 8u, // Blocked-ELL
     schedule_cuda_cores = 9u,
-    schedule_variant_count = 10u
+    schedule_tensor_codes = 10u,      // forward, 4-bit codes on dense matrices: tiles of codes, decoded at launch
+    schedule_variant_count = 11u
 };
 const char *schedule_name(std::uint32_t variant) noexcept; // "" for the backend's choice or an unknown variant
 

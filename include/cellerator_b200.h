@@ -273,7 +273,12 @@ typedef struct cb200_spmm_problem {
      * rounded up to 256 x 128 tiles; codes, scales and offsets are baked in, so a change of any of
      * them needs a new prepare).  A launch then streams the tiles into the tensor cores and does no
      * decoding.  Taken only when the tiles fit persistent_limit_bytes and half of the free device
-     * memory; otherwise "tensor_blocked" stays. */
+     * memory; otherwise "tensor_blocked" stays.
+     *
+     * The same with 4-bit codes and per-gene zero-points: prepare keeps dense tiles of CODES instead
+     * (schedule "tensor_codes": rows x genes bytes, a byte per slot; 0 = nothing stored, code + 1 otherwise).
+     * The matrix stays quantized: a launch decodes in registers with the scales and offsets it is given, so
+     * only changed codes (a new structure or value generation) need a new prepare. */
     const cb200_qcsr *device_matrix;
     /* prepare_policy.persistent_memory_limit (operation_core.hh:116-124): device bytes the prepared
      * operation may keep; 0 = no limit.  A copy that would exceed it is not built (the schedule
@@ -286,7 +291,7 @@ typedef struct cb200_spmm_problem {
      * CB200_STATUS_STALE_VALUE instead of multiplying stale values. */
     uint64_t value_generation;
     /* Optional request for one schedule by the name cb200_prepared_schedule reports ("gene_tiled",
-     * "warp_per_row", "tensor_windows", "tensor_blocked", "tensor_dense"; transpose: "tensor_blocked",
+     * "warp_per_row", "tensor_windows", "tensor_blocked", "tensor_dense", "tensor_codes"; transpose: "tensor_blocked",
      * "vector_reductions"; Blocked-ELL: "cuda_cores"); NULL or "" lets prepare choose from the shape and
      * the row statistics.  A request the shape or the policy cannot serve is not an error: prepare
      * keeps its own choice, and cb200_prepared_schedule tells which schedule runs.  This is the
@@ -317,7 +322,7 @@ void cb200_prepared_destroy(cb200_prepared *prepared);
 /* workspace_requirement, launch_bindings.hh:67-71 */
 cb200_status cb200_prepared_workspace(const cb200_prepared *prepared, uint64_t *minimum_bytes, uint32_t *alignment);
 /* kernel choice made at prepare time, as text: "warp_per_row", "gene_tiled" (exact fp32 products);
- * "tensor_windows", "tensor_blocked", "tensor_dense" (CSR, bf16 products on tcgen05);
+ * "tensor_windows", "tensor_blocked", "tensor_dense", "tensor_codes" (CSR, 16-bit products on tcgen05);
  * "tensor_blocked_x2" / "_x3" (fp32 products from bf16 passes); "tcgen05_block_rows" (Blocked-ELL);
  * transpose: "vector_reductions" (exact) or "tensor_blocked" */
 const char *cb200_prepared_schedule(const cb200_prepared *prepared);
