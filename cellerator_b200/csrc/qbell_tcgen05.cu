@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
     extern __shared__ __align__(1024) unsigned char smem[];
     // [kStages][A 16 KB | B 2 KB] | staged codes [2] | staged scales/offsets [2] | barriers | tmem base | flags
     std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(smem + kStages * kStageBytes + 2 * kCodesStageBytes + 2 * kMetaStageBytes);
-    std::uint64_t *full_bar = bars;                  // [kStages]  producers -> MMA      (128 arrivals)
+    std::uint64_t *full_bar = bars;                  // [kStages]  producers -> MMA      (one arrival per warp)
     std::uint64_t *empty_bar = bars + kStages;       // [kStages]  MMA commit -> producers (1 arrival)
     std::uint64_t *acc_full = bars + 2 * kStages;    // [2]        MMA commit -> epilogue  (1 arrival)
     std::uint64_t *acc_empty = bars + 2 * kStages + 2; // [2]      epilogue -> MMA        (128 arrivals)
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            bar_init(smem_addr(full_bar + s), kProducerThreads);
+            bar_init(smem_addr(full_bar + s), kProducerThreads / 32); // one arrival per producer warp
             bar_init(smem_addr(empty_bar + s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -177,7 +177,14 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
     if (warp >= 4 && warp < 8) {
         // ================= producers =================
         const int pt = tid - 128;          // 0..127
-        const int cell = pt >> 2, chunk = pt & 3; // B tile: cell within the block row, 8-gene chunk
+        // B tile: cell within the block row, 8-gene chunk.  A warp takes 16 cells x 2 neighbouring chunks.  The two lanes
+        // of a pair READ the two halves of one 16-byte piece of a cell's staged codes (the pieces of a row are permuted by
+        // cell mod 8 when they are staged, so the eight cells of a half warp read eight different bank groups).  The odd
+        // lanes then swap their codes with the odd lane eight further on, so that a quarter warp DECODES AND STORES cells
+        // c .. c + 3 of one chunk and cells c + 4 .. c + 7 of the next: eight different bank groups of the B tile.
+        const int pair = (pt & 31) >> 1, parity = pt & 1, cell_base = ((pt >> 5) & 1) * 16;
+        const int load_cell = cell_base + pair;
+        const int cell = cell_base + (parity != 0 ? (pair ^ 4) : pair), chunk = (pt >> 6) * 2 + parity;
         const std::uint32_t codes_stage = smem0 + kStages * kStageBytes;          // [2][32 cells][512 B]
         const std::uint32_t meta_stage = codes_stage + 2 * kCodesStageBytes;       // [2][16 slots][32 scales | 32 offsets]
         const int row_bytes = p.width * 32 * BITS / 8;
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                 const int c_cell = i / chunks_per_row, c = i % chunks_per_row;
                 const std::int64_t row = br * 32 + c_cell;
                 if (row >= p.row_begin && row < p.row_end)
-                    cp_async_16(codes_stage + buf * kCodesStageBytes + c_cell * 512 + c * 16, p.packed + row * p.row_stride + c * 16);
+                    cp_async_16(codes_stage + buf * kCodesStageBytes + c_cell * 512 + ((c ^ (c_cell & 7)) << 4), p.packed + row * p.row_stride + c * 16);
             }
             for (int i = pt; i < p.width * 16; i += kProducerThreads) {
                 const int slot = i >> 4, q = i & 15;
@@ -222,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
             asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
             if (br + step < p.block_row_end) prefetch_block_row(br + step, buf ^ 1);
             cp_async_commit();
-            const std::uint32_t my_codes = codes_stage + buf * kCodesStageBytes + cell * 512;
+            const std::uint32_t my_codes = codes_stage + buf * kCodesStageBytes + load_cell * 512;
             const std::uint32_t my_meta = meta_stage + buf * kMetaStageBytes + chunk * 32;
             for (int slot = 0; slot < p.width; ++slot) {
                 const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
@@ -239,21 +246,30 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                 // ---- B: decode 8 codes of (cell, genes chunk) to bf16, from the staged copies
                 const std::int64_t gene0 = static_cast<std::int64_t>(bc) * 32 + chunk * 8;
                 __nv_bfloat162 out[4];
+                // every lane reads and swaps (rows outside the launch hold stale bytes that are never decoded)
+                std::uint32_t lo = 0, hi = 0;
+                if constexpr (BITS == 8)
+                    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(my_codes + (((slot * 2 + (chunk >> 1)) ^ (load_cell & 7)) << 4) + (chunk & 1) * 8));
+                else
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(lo) : "r"(my_codes + ((slot ^ (load_cell & 7)) << 4) + chunk * 4));
+                {
+                    const std::uint32_t lo_far = __shfl_xor_sync(0xffffffffu, lo, 8), hi_far = __shfl_xor_sync(0xffffffffu, hi, 8);
+                    if (parity != 0) {
+                        lo = lo_far;
+                        hi = hi_far;
+                    }
+                }
                 if (cell_valid) {
                     unsigned code[8];
                     if constexpr (BITS == 8) {
-                        std::uint32_t lo, hi;
-                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(my_codes + slot * 32 + chunk * 8));
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             code[e] = (lo >> (8 * e)) & 0xffu;
                             code[4 + e] = (hi >> (8 * e)) & 0xffu;
                         }
                     } else {
-                        std::uint32_t raw;
-                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(my_codes + slot * 16 + chunk * 4));
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) code[e] = (raw >> (4 * e)) & 0xfu;
+                        for (int e = 0; e < 8; ++e) code[e] = (lo >> (4 * e)) & 0xfu;
                     }
                     float sc[8], of[8];
                     if (p.scales != nullptr) {
@@ -286,7 +302,8 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                                  : "memory");
                 }
                 fence_async_proxy();                      // the B tile was written with ordinary stores
-                bar_arrive(smem_addr(full_bar + stage));
+                __syncwarp();
+                if (lane == 0) bar_arrive(smem_addr(full_bar + stage));
                 ++item;
             }
         }
