@@ -498,6 +498,7 @@ constexpr int kGroupThreads = kGroupWarps * 32;
 constexpr int kChunk2Entries = 2048;
 constexpr int kChunk2Bytes = kChunk2Entries * 4;
 constexpr int kRing2 = 2; // chunk stages per scatter group
+constexpr int kThreads2 = kProducerThreads + 32 * (kSubBlocks + 2); // + an MMA warp per sub-block + W loader warp + chunk loader warp
 __host__ __device__ constexpr int w2_stages(int n) {
     return (232448 - 2 * kABufBytes - 2 * kRing2 * kChunk2Bytes - 1024) / (n * kWin * 2) >= kMaxWStages
                ? kMaxWStages
@@ -508,7 +509,7 @@ __host__ __device__ constexpr int w2_stages(int n) {
 // of the waits comes from the launch (a few thousand instead of 2^22) and the W loader issues no copies, so
 // that the waits for W run out.  Everything that happens after a wait has run out is common code.
 template<int NC, bool TEST_HOOK>
-__global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const blocked_params p) {
+__global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const blocked_params p) {
     constexpr int REC = record_bytes(NC);   // distance of the W records in global memory
     constexpr int WREC = NC * kWin * 2;     // the W part of a record (the decode table is not needed)
     constexpr int STAGES = w2_stages(NC);
@@ -527,8 +528,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     std::uint64_t *c_empty = c_full + CHUNKS;     // [CHUNKS] scatter group -> chunk loader (one arrival per warp)
     std::uint64_t *acc_full = c_empty + CHUNKS;   // MMA commit -> epilogue warps
     std::uint64_t *acc_empty = acc_full + 1;      // epilogue warps -> MMA
-    std::uint64_t *mma_drain = acc_empty + 1;     // MMA commit -> MMA warp, used once, after an abort
-    volatile int *chunk_meta = reinterpret_cast<volatile int *>(mma_drain + 1); // [CHUNKS] (entries << 1) | last chunk of its window
+    std::uint64_t *mma_drain = acc_empty + 1;     // [2] MMA commit -> the MMA warp itself, used once, after an abort
+    volatile int *chunk_meta = reinterpret_cast<volatile int *>(mma_drain + 2); // [CHUNKS] (entries << 1) | last chunk of its window
     std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(const_cast<int *>(chunk_meta) + CHUNKS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     unsigned char *scratch_slot = reinterpret_cast<unsigned char *>(tmem_slot + 2);
@@ -542,19 +543,20 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
             bar_init(smem_addr(a_full + b), kGroupWarps);
-            bar_init(smem_addr(a_empty + b), 1);
+            bar_init(smem_addr(a_empty + b), kSubBlocks); // one commit per MMA warp
         }
         for (int s = 0; s < STAGES; ++s) {
             bar_init(smem_addr(w_full + s), 1);
-            bar_init(smem_addr(w_empty + s), 1);
+            bar_init(smem_addr(w_empty + s), kSubBlocks);
         }
         for (int s = 0; s < CHUNKS; ++s) {
             bar_init(smem_addr(c_full + s), 1);
             bar_init(smem_addr(c_empty + s), kGroupWarps);
         }
-        bar_init(smem_addr(acc_full), 1);
+        bar_init(smem_addr(acc_full), kSubBlocks);
         bar_init(smem_addr(acc_empty), kEpilogueWarps);
         bar_init(smem_addr(mma_drain), 1);
+        bar_init(smem_addr(mma_drain + 1), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -584,6 +586,27 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
             const std::int64_t row = (first_group + gi * gridDim.x) * kRows + tid;
             for (int w = 0; w < p.windows; ++w, ++q) {
                 if (static_cast<int>(q & 1) != grp) continue;
+                // The window's first chunk (all of it for all but the densest matrices) goes into registers while the tile
+                // is still being read by the previous window's MMAs: between the tile's release and its hand-over there
+                // are then only stores.
+                bool last;
+                uint4 held[kChunk2Entries / (kGroupThreads * 4)];
+                {
+                    const int cs = grp * kRing2 + static_cast<int>(qc % kRing2);
+                    bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing2) & 1), abort_flag, limit);
+                    const int meta = chunk_meta[cs];
+                    const int count = *abort_flag != 0 ? 0 : (meta >> 1);
+                    last = (meta & 1) != 0 || *abort_flag != 0;
+                    const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunk2Bytes);
+#pragma unroll
+                    for (int k = 0; k < kChunk2Entries / (kGroupThreads * 4); ++k) { // segments are padded to multiples of 4
+                        const int i = (k * kGroupThreads + gtid) * 4;
+                        held[k] = i < count ? chunk[i >> 2] : make_uint4(kInvalidEntry, kInvalidEntry, kInvalidEntry, kInvalidEntry);
+                    }
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
+                    ++qc;
+                }
                 bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag, limit);
 #pragma unroll
                 for (int k = 0; k < kABufBytes / (kGroupThreads * 16); ++k)
@@ -591,20 +614,28 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 // the whole tile is zero before anyone of the group scatters (named barrier 1 or 2)
                 if (grp == 0) asm volatile("bar.sync 1, %0;" ::"n"(kGroupThreads) : "memory");
                 else asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory");
-                bool last = false;
+#pragma unroll
+                for (int k = 0; k < kChunk2Entries / (kGroupThreads * 4); ++k) {
+                    const std::uint32_t e[4] = {held[k].x, held[k].y, held[k].z, held[k].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { // padding words (top bit set) go to a scratch slot instead of branching
+                        unsigned char *dst = static_cast<int>(e[j]) >= 0 ? tile + (((e[j] >> 16) & 0x7fffu) << 1) : scratch_slot;
+                        *reinterpret_cast<unsigned short *>(dst) = static_cast<unsigned short>(e[j] & 0xffffu);
+                    }
+                }
                 int guard = 0;
-                while (!last && ++guard < (1 << 20)) {
+                while (!last && ++guard < (1 << 20)) { // further chunks of a long segment: scattered from shared memory
                     const int cs = grp * kRing2 + static_cast<int>(qc % kRing2);
                     bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing2) & 1), abort_flag, limit);
                     const int meta = chunk_meta[cs];
                     const int count = *abort_flag != 0 ? 0 : (meta >> 1);
                     last = (meta & 1) != 0 || *abort_flag != 0;
                     const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunk2Bytes);
-                    for (int i = gtid * 4; i < count; i += kGroupThreads * 4) { // segments are padded to multiples of 4
+                    for (int i = gtid * 4; i < count; i += kGroupThreads * 4) {
                         const uint4 e4 = chunk[i >> 2];
                         const std::uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) { // padding words (top bit set) go to a scratch slot instead of branching
+                        for (int k = 0; k < 4; ++k) {
                             unsigned char *dst = static_cast<int>(e[k]) >= 0 ? tile + (((e[k] >> 16) & 0x7fffu) << 1) : scratch_slot;
                             *reinterpret_cast<unsigned short *>(dst) = static_cast<unsigned short>(e[k] & 0xffffu);
                         }
@@ -635,13 +666,18 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
             __syncwarp();
             if (lane == 0) bar_arrive(smem_addr(acc_empty));
         }
-    } else if (warp == kProducerWarps) {
-        // ================= MMA issuer =================
-        long long q = 0;
+    } else if (warp < kProducerWarps + kSubBlocks) {
+        // ================= MMA issuers: one warp per 128-row sub-block of the tile =================
+        // One issuing thread is held to the rate at which the MMAs read their operands (the issue of a window's sixteen
+        // MMAs takes about as long as their execution) and then spends half as long again on commits, waits and
+        // loop overhead while the tensor pipe runs dry.  Each sub-block has its own accumulator columns, so two threads can
+        // issue a window's MMAs side by side: each issues eight, and both commit to the tile's and the W stage's barriers.
         // The issue path is kept as short as it can be: a vote and a branch per window to stop early after a wait
         // has run out cost 0.7 ms of 6.3 on the 1M x 33,538 matrix.  After an abort the remaining windows are
         // therefore still issued (on stale tiles, into this CTA's own TMEM; the waits return at once) and only
         // the end of the role looks at the flag.
+        const int sb = warp - kProducerWarps;
+        long long q = 0;
         for (std::int64_t g = 0; g < my_groups; ++g) {
             bar_wait(smem_addr(acc_empty), static_cast<std::uint32_t>((g & 1) ^ 1), abort_flag, limit);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -652,17 +688,12 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag, limit);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (lane == 0) {
-                    const std::uint32_t a_tile = smem0 + b * kABufBytes;
+                    const std::uint32_t a_tile = smem0 + b * kABufBytes + sb * kSubBlockBytes;
                     const std::uint32_t b_tile = wstage0 + s * WREC;
 #pragma unroll
-                    for (int kk = 0; kk < kWin / 16; ++kk) {
-                        const std::uint64_t db = smem_desc(b_tile + kk * 256);
-#pragma unroll
-                        for (int sb = 0; sb < kSubBlocks; ++sb)
-                            mma_bf16(tmem_base + sb * NC,
-                                     smem_desc_sw128(a_tile + sb * kSubBlockBytes + (kk >> 2) * kHalfBytes + (kk & 3) * 32), db, IDESC,
-                                     w > 0 || kk > 0);
-                    }
+                    for (int kk = 0; kk < kWin / 16; ++kk)
+                        mma_bf16(tmem_base + sb * NC, smem_desc_sw128(a_tile + (kk >> 2) * kHalfBytes + (kk & 3) * 32), smem_desc(b_tile + kk * 256),
+                                 IDESC, w > 0 || kk > 0);
                     mma_commit(smem_addr(a_empty + b));
                     mma_commit(smem_addr(w_empty + s));
                     if (w == p.windows - 1) mma_commit(smem_addr(acc_full));
@@ -672,11 +703,11 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
         }
         // after an abort: the MMAs already issued finish before the CTA frees its TMEM and shared memory
         if (lane == 0 && *abort_flag != 0) {
-            mma_commit(smem_addr(mma_drain));
-            bar_wait_drain(smem_addr(mma_drain), 0u, limit);
+            mma_commit(smem_addr(mma_drain + sb));
+            bar_wait_drain(smem_addr(mma_drain + sb), 0u, limit);
         }
         __syncwarp();
-    } else if (warp == kProducerWarps + 1) {
+    } else if (warp == kProducerWarps + kSubBlocks) {
         // ================= W loader =================
         if (lane == 0 && !(TEST_HOOK && p.withhold_w != 0)) {
             const long long total = my_groups * p.windows;
@@ -693,7 +724,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
                 for (long long last = q - 1; last >= 0 && last > q - 1 - STAGES; --last)
                     bar_wait_drain(smem_addr(w_full + static_cast<int>(last % STAGES)), static_cast<std::uint32_t>((last / STAGES) & 1), limit);
         }
-    } else if (warp == kProducerWarps + 2) {
+    } else if (warp == kProducerWarps + kSubBlocks + 1) {
         // ================= entry chunks: window q goes to the ring of scatter group q & 1 =================
         long long q = 0;
         long long qc0 = 0, qc1 = 0; // chunks issued into each ring
@@ -758,12 +789,12 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked2_kernel(const bl
 template<int NC, bool TEST_HOOK>
 cb200_status launch_blocked2_as(const blocked_params &p, int sm_count, cudaStream_t stream) {
     constexpr std::size_t smem = 2 * kABufBytes + w2_stages(NC) * NC * kWin * 2 + 2 * kRing2 * kChunk2Bytes +
-                                 (7 + 2 * w2_stages(NC) + 4 * kRing2) * sizeof(std::uint64_t) + 2 * kRing2 * 4 + 24;
+                                 (8 + 2 * w2_stages(NC) + 4 * kRing2) * sizeof(std::uint64_t) + 2 * kRing2 * 4 + 24;
     static_assert(smem <= 232448, "shared memory budget");
     CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_blocked2_kernel<NC, TEST_HOOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const std::int64_t groups = p.group_end - p.group_begin;
     const unsigned grid = static_cast<unsigned>(groups < sm_count ? groups : sm_count);
-    qcsr_fwd_blocked2_kernel<NC, TEST_HOOK><<<grid, kThreads, smem, stream>>>(p);
+    qcsr_fwd_blocked2_kernel<NC, TEST_HOOK><<<grid, kThreads2, smem, stream>>>(p);
     count_launch();
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
