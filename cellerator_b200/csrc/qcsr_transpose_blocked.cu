@@ -16,9 +16,10 @@
 // swizzle), and sixteen 128 x N x 16 tcgen05 MMAs multiply it with the group's rows of G.  G is
 // converted to bf16 once per launch into one 256 x N record per group, already in the K-major
 // core-matrix operand layout (rows outside the launch's row range are written as zero, which is how a
-// partial row range is honoured).  A CTA keeps the fp32 accumulators of eight windows (1,024 genes)
-// in TMEM (8 x N columns x 128 lanes) while it walks a run of groups, so the group's G record is
-// fetched once per eight windows; at the end of the run the accumulators are added into G' with
+// partial row range is honoured).  A CTA keeps the fp32 accumulators of a set of windows (four at N = 64,
+// eight at N = 32; two accumulators per window, one per MMA-issuing warp, 512 TMEM columns in all) while
+// it walks a run of groups, so the group's G record is fetched once per set; at the end of the run the
+// two accumulators of a window are added and the sums go into G' with
 // vector reductions (the (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so
 // several CTAs contribute to the same genes; G' is first scaled by beta by a small kernel).
 //
@@ -28,11 +29,13 @@
 // matrix, 6.25 against 7.93 for one bf16 pass).  Code words {code, gene, forward-tile position} are
 // still decoded here when the caller's memory limit left no room for the second array.
 //
-// Structure of a CTA (608 threads, one CTA per SM): warps 0-15 zero, decode and scatter -- as two
+// Structure of a CTA (640 threads, one CTA per SM): warps 0-15 zero, decode and scatter -- as two
 // groups of eight warps on alternate tiles, each with its own tile buffer and 8 KB chunk stage, so
 // that the per-tile chains of waits overlap (23.6 ms against 24.4 for the three split passes on the
-// 1M x 33,538 matrix) -- and read the accumulators back at the end of a run; warp 16 issues the MMAs;
-// warp 17 feeds the G ring (2 stages of 32 KB); warp 18 deals the entry chunks.  Every barrier wait is bounded; on a
+// 1M x 33,538 matrix); baked words are fetched into registers before the tile is released, so that only
+// stores lie between release and hand-over -- and read the accumulators back at the end of a run; warps 16
+// and 17 issue the MMAs, the first and the second eight K steps of every tile (15.7 ms against 17.5 with one
+// issuing warp); warp 18 feeds the G ring (2 stages of 32 KB); warp 19 deals the entry chunks.  Every barrier wait is bounded; on a
 // time-out a status word is raised, waits stop blocking, and the kernel runs to completion and frees
 // its TMEM.  A non-zero status means G' is not valid.
 #include "kernels.cuh"
@@ -46,11 +49,14 @@ namespace {
 
 constexpr int kWin = 128;                     // genes per window (as in the blocked copy)
 constexpr int kRows = 256;                    // cells per group (as in the blocked copy)
-constexpr int kSetWindows = 8;                // windows whose accumulators a CTA holds in TMEM
+// windows whose accumulators a CTA holds in TMEM: two sets of N columns per window (one per MMA-issuing warp, which
+// take the first and the second half of a tile's K steps), 512 columns in all
+__host__ __device__ constexpr int set_windows(int n) { return 256 / n; }
+constexpr int kIssuers = 2;
 constexpr int kProducerWarps = 16;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kChunkLoaders = 1;
-constexpr int kThreads = kProducerThreads + 32 * (2 + kChunkLoaders);
+constexpr int kThreads = kProducerThreads + 32 * (kIssuers + 1 + kChunkLoaders);
 constexpr int kTileBytes = kWin * kRows * 2;  // 64 KB: [cell quarter][gene][64 cells]
 constexpr int kQuarterBytes = kWin * 128;     // 16 KB: 128 genes x 64 cells
 constexpr int kGStages = 2;
@@ -127,7 +133,8 @@ __global__ void __launch_bounds__(256) pack_g_kernel(const float *g, std::int64_
 template<int NC, bool BAKED>
 __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(const tb_params p) {
     constexpr int GREC = g_record_bytes(NC);
-    constexpr int kTmemCols = kSetWindows * NC; // 512 (N = 64) or 256 (N = 32)
+    constexpr int kSetWindows = set_windows(NC);
+    constexpr int kTmemCols = kSetWindows * kIssuers * NC; // 512
     constexpr std::uint32_t IDESC = instr_desc(NC);
     extern __shared__ __align__(1024) unsigned char smem[];
     // [2][tile] | [kGStages][G record] | [kChunkStages][entry chunk] | tables | row offsets | barriers | ...
@@ -156,17 +163,17 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
             bar_init(smem_addr(a_full + b), kGroupWarps);
-            bar_init(smem_addr(a_empty + b), 1);
+            bar_init(smem_addr(a_empty + b), kIssuers); // one commit per MMA warp
         }
         for (int s = 0; s < kGStages; ++s) {
             bar_init(smem_addr(g_full + s), 1);
-            bar_init(smem_addr(g_empty + s), 1);
+            bar_init(smem_addr(g_empty + s), kIssuers);
         }
         for (int s = 0; s < kChunkStages; ++s) {
             bar_init(smem_addr(c_full + s), 1);
             bar_init(smem_addr(c_empty + s), kGroupWarps);
         }
-        bar_init(smem_addr(acc_full), 1);
+        bar_init(smem_addr(acc_full), kIssuers);
         bar_init(smem_addr(acc_empty), kProducerWarps);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -223,6 +230,27 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                 }
                 for (int wl = 0; wl < nwin; ++wl, ++q) {
                     if (static_cast<int>(q & 1) != grp) continue;
+                    // Baked words: the tile's first chunk (all of it for all but the densest matrices) goes into registers
+                    // while the tile is still being read by the MMAs of the group's previous tile; between the tile's release
+                    // and its hand-over there are then only stores.
+                    bool last = false;
+                    uint4 held[kChunkEntries / (kGroupThreads * 4)];
+                    if constexpr (BAKED) {
+                        const int cs = grp * kRing + static_cast<int>(qc % kRing);
+                        bar_wait(smem_addr(c_full + cs), static_cast<std::uint32_t>((qc / kRing) & 1), abort_flag);
+                        const int meta = chunk_meta[cs];
+                        const int n_entries = *abort_flag != 0 ? 0 : (meta >> 1);
+                        last = (meta & 1) != 0 || *abort_flag != 0;
+                        const uint4 *chunk = reinterpret_cast<const uint4 *>(chunk_base + cs * kChunkBytes);
+#pragma unroll
+                        for (int k = 0; k < kChunkEntries / (kGroupThreads * 4); ++k) { // segments are padded to multiples of 4
+                            const int i = (k * kGroupThreads + gtid) * 4;
+                            held[k] = i < n_entries ? chunk[i >> 2] : make_uint4(0x80000000u, 0x80000000u, 0x80000000u, 0x80000000u);
+                        }
+                        __syncwarp();
+                        if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
+                        ++qc;
+                    }
                     bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
 #pragma unroll
                     for (int k = 0; k < kTileBytes / (kGroupThreads * 16); ++k)
@@ -230,8 +258,18 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                     // the whole tile is zero before anyone of the group scatters (named barrier 2 or 3)
                     if (grp == 0) asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory");
                     else asm volatile("bar.sync 3, %0;" ::"n"(kGroupThreads) : "memory");
+                    if constexpr (BAKED) {
+#pragma unroll
+                        for (int k = 0; k < kChunkEntries / (kGroupThreads * 4); ++k) {
+                            const std::uint32_t e[4] = {held[k].x, held[k].y, held[k].z, held[k].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) { // padding words (top bit set) go to a scratch slot
+                                unsigned char *dst = static_cast<int>(e[j]) >= 0 ? tile + (((e[j] >> 16) & 0x7fffu) << 1) : scratch_slot;
+                                *reinterpret_cast<unsigned short *>(dst) = static_cast<unsigned short>(e[j] & 0xffffu);
+                            }
+                        }
+                    }
                     const float2 *wtable = table + wl * kWin;
-                    bool last = false;
                     int guard = 0;
                     while (!last && ++guard < (1 << 20)) {
                         const int cs = grp * kRing + static_cast<int>(qc % kRing);
@@ -283,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                 }
             }
             // ---- end of the run: add the accumulators into G'.  TMEM lane = gene within the window;
-            //      a warp reads the lane quarter its number allows, for two of the eight windows.
+            //      a warp reads the lane quarter its number allows, for every fourth window of the set.
             bar_wait(smem_addr(acc_full), static_cast<std::uint32_t>(run & 1), abort_flag);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quarter = warp & 3;
@@ -292,8 +330,11 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                 const std::int64_t gene = (set * kSetWindows + wl) * kWin + quarter * 32 + lane;
 #pragma unroll
                 for (int h = 0; h < NC / 32; ++h) {
-                    float v[32];
-                    tmem_ld32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + wl * NC + h * 32, v);
+                    float v[32], second[32]; // the two halves of the K steps were accumulated apart
+                    tmem_ld32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + wl * kIssuers * NC + h * 32, v);
+                    tmem_ld32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + (wl * kIssuers + 1) * NC + h * 32, second);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] += second[c];
                     if (gene < p.cols && *abort_flag == 0) {
                         float *out = p.out + gene * p.out_ld + h * 32;
 #pragma unroll
@@ -308,8 +349,11 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
             if (lane == 0) bar_arrive(smem_addr(acc_empty));
             u += count;
         }
-    } else if (warp == kProducerWarps) {
-        // ================= MMA issuer =================
+    } else if (warp < kProducerWarps + kIssuers) {
+        // ================= MMA issuers: warp kh issues the K steps [8 kh, 8 kh + 8) of every tile into its own accumulators.
+        // One issuing thread is held to the rate at which the MMAs read their operands and then spends half as long again
+        // on commits, waits and loop overhead while the tensor pipe runs dry; two threads halve the issue time of a tile. ==
+        const int kh = warp - kProducerWarps;
         long long q = 0, qg = 0;
         int run = 0;
         for (std::int64_t u = u0; u < u1; ++run) {
@@ -329,9 +373,11 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                         const std::uint32_t a_tile = smem0 + b * kTileBytes;
                         const std::uint32_t g_rec = grec0 + gs * GREC;
 #pragma unroll
-                        for (int kk = 0; kk < kRows / 16; ++kk)
-                            mma_bf16(tmem_base + wl * NC, smem_desc_sw128(a_tile + (kk >> 2) * kQuarterBytes + (kk & 3) * 32),
-                                     smem_desc_g(g_rec + kk * 256), IDESC, gi > 0 || kk > 0);
+                        for (int k8 = 0; k8 < kRows / 16 / kIssuers; ++k8) {
+                            const int kk = kh * (kRows / 16 / kIssuers) + k8;
+                            mma_bf16(tmem_base + (wl * kIssuers + kh) * NC, smem_desc_sw128(a_tile + (kk >> 2) * kQuarterBytes + (kk & 3) * 32),
+                                     smem_desc_g(g_rec + kk * 256), IDESC, gi > 0 || k8 > 0);
+                        }
                         mma_commit(smem_addr(a_empty + b));
                         if (wl == nwin - 1) mma_commit(smem_addr(g_empty + gs));
                         if (wl == nwin - 1 && gi == count - 1) mma_commit(smem_addr(acc_full));
@@ -342,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
             u += count;
         }
     } else {
-        const int role = warp - kProducerWarps - 1; // 0: G records, 1..kChunkLoaders: entry chunks
+        const int role = warp - kProducerWarps - kIssuers; // 0: G records, 1..kChunkLoaders: entry chunks
         if (role == 0) {
             if (lane == 0) {
                 long long qg = 0;
@@ -399,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
 }
 
 template<int NC> constexpr std::size_t tb_smem_bytes() {
-    return 2 * kTileBytes + kGStages * g_record_bytes(NC) + kChunkStages * kChunkBytes + kSetWindows * kWin * 8 + kRows * 4 +
+    return 2 * kTileBytes + kGStages * g_record_bytes(NC) + kChunkStages * kChunkBytes + set_windows(NC) * kWin * 8 + kRows * 4 +
            (6 + 2 * kGStages + 2 * kChunkStages) * sizeof(std::uint64_t) + (kChunkStages + 1) * 4 + 16;
 }
 
@@ -409,7 +455,7 @@ cb200_status launch_one(const tb_params &p, int sm_count, cudaStream_t stream) {
     static_assert(smem <= 232448, "shared memory budget");
     CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_transpose_blocked_kernel<NC, BAKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
-    const std::int64_t sets = (p.windows + kSetWindows - 1) / kSetWindows;
+    const std::int64_t sets = (p.windows + set_windows(NC) - 1) / set_windows(NC);
     const std::int64_t units = sets * p.group_count;
     const unsigned grid = static_cast<unsigned>(units < sm_count ? units : sm_count);
     qcsr_transpose_blocked_kernel<NC, BAKED><<<grid, kThreads, smem, stream>>>(p);
