@@ -29,8 +29,9 @@
 // and row groups dealt round-robin:
 //   qcsr_fwd_blocked_kernel   one scatter group: code words (split-product schedules under a memory
 //                             limit), and baked words whose segments span several chunks;
-//   qcsr_fwd_blocked2_kernel  baked words, two scatter groups on alternate windows: every pass of the
-//                             default schedules (6.30 ms per pass on the 1M x 33,538 matrix);
+//   qcsr_fwd_blocked2_kernel  baked words, two scatter groups on alternate windows, an MMA-issuing warp per row
+//                             sub-block: every pass of the default schedules (5.04 ms per pass on the
+//                             1M x 33,538 matrix; 640 threads);
 //   qcsr_fwd_dense_kernel     no scatter at all: prepare kept the operand tiles ("tensor_dense").
 //
 // Structure of a CTA of the first kernel (608 threads):
@@ -51,7 +52,8 @@
 // What bounds it.  Per window the shared memory moves ~64 KB of zeroes, ~20 KB of entries, tables and
 // scattered values, ~24 KB of copies coming in and 96 KB of MMA operand reads (the A tile once, the
 // W slice once per row sub-block): the kernel runs at the shared-memory bandwidth of the SM, not at
-// the tensor pipe's (about a quarter busy) nor at HBM's.
+// the tensor pipe's nor at HBM's: the MMAs are held to the rate at which they read their operands (one
+// 128 x 64 x 16 MMA per 43-47 cycles), which fills 55 % of a window's time in the two-group kernel.
 #include "blocked_tile.cuh"
 
 #include <algorithm>

@@ -14,20 +14,20 @@
 // offsets need no new prepare; only new codes (a new structure or value generation) do.  Against the decoded
 // tiles of "tensor_dense" (2 bytes per slot, values baked in) a launch moves half the bytes.
 //
-// A CTA (864 threads, one per SM, row groups dealt round-robin).  Shared memory holds only what the copy engine
+// A CTA (896 threads, one per SM, row groups dealt round-robin).  Shared memory holds only what the copy engine
 // brings: the decoded operand never touches it.  The decode warps write it into TENSOR MEMORY (tcgen05.st), next to
 // the accumulators, and the MMA reads its A operand from there; shared-memory bandwidth, which bounds a kernel that
 // stores decoded tiles to shared memory and lets the MMA read them back (16 KB in, 32 KB stored, 32 KB read per
 // half window), is left to the copies and the W operand.
 //   warps 0-7    write Y: thread t owns row t of the group (TMEM lane = row within the 128-row sub-block); the
 //                accumulators (256 columns) are handed back as soon as they are in registers;
-//   warp 8       one thread issues the MMAs: per window two row sub-blocks x eight K = 16 steps, A from tensor
+//   warps 8-9    one thread each issues the MMAs of one row sub-block: per window eight K = 16 steps, A from tensor
 //                memory (row = lane, two fp16 per 32-bit column), B = the window's slice of W from shared memory;
-//   warp 9       one thread feeds the W ring with bulk async copies (W re-laid per window into the operand
+//   warp 10      one thread feeds the W ring with bulk async copies (W re-laid per window into the operand
 //                layout, fp16, by a small kernel before this one);
-//   warp 10      one thread feeds the ring of code stages with bulk async copies (16 KB of codes and the half
+//   warp 11      one thread feeds the ring of code stages with bulk async copies (16 KB of codes and the half
 //                window's 256 bytes of {scale, zero-point} pairs behind them);
-//   warps 11-26  decode: a warp may write the 32 tensor-memory lanes (warp mod 4), so it owns those rows of both
+//   warps 12-27  decode: a warp may write the 32 tensor-memory lanes (warp mod 4), so it owns those rows of both
 //                sub-blocks and one 16-gene chunk (the stage is stored chunk-major: its 16-byte loads and the
 //                table's broadcast loads run without bank conflicts).  Per pair of codes a byte permute (byte ->
 //                fp16 1024 + byte), a subtraction of 1025 (exact: the code), a fused multiply-add with the genes'
@@ -54,7 +54,8 @@ constexpr int kOperandCols = kSubBlocks * 64;            // columns of one: per 
 constexpr int kOperandCol0 = 256;                        // the accumulators own the columns below
 constexpr int kTmemColumns = 512;
 constexpr int kDecodeWarps = 16;
-constexpr int kCodesThreads = (kEpilogueWarps + 3 + kDecodeWarps) * 32; // 864
+constexpr int kCodeIssuers = kSubBlocks; // MMA-issuing warps: one per 128-row sub-block
+constexpr int kCodesThreads = (kEpilogueWarps + kCodeIssuers + 2 + kDecodeWarps) * 32; // 896
 static_assert(kSubBlocks * 128 <= kOperandCol0 && kOperandCol0 + kOperandStages * kOperandCols <= kTmemColumns, "tensor memory budget");
 static_assert(kDecodeWarps == 16 && kRows == 256,
               "decode warp = (lane quarter of tensor memory it may write, 16-gene chunk); it decodes that quarter of both row sub-blocks");
@@ -186,8 +187,8 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
     std::uint64_t *b_empty = b_full + SB;      // [SB] MMA commit -> W loader
     std::uint64_t *acc_full = b_empty + SB;    // MMA commit -> epilogue warps
     std::uint64_t *acc_empty = acc_full + 1;   // epilogue warps -> MMA (one arrival per warp)
-    std::uint64_t *mma_drain = acc_empty + 1;  // the MMA warp's own: everything it issued has finished
-    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(mma_drain + 1);
+    std::uint64_t *mma_drain = acc_empty + 1;  // [issuers] an MMA warp's own: everything it issued has finished
+    std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(mma_drain + kCodeIssuers);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -201,15 +202,15 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
         }
         for (int s = 0; s < SA; ++s) {
             bar_init(smem_addr(a_full + s), kDecodeWarps);
-            bar_init(smem_addr(a_empty + s), 1);
+            bar_init(smem_addr(a_empty + s), kCodeIssuers); // one commit per MMA warp
         }
         for (int s = 0; s < SB; ++s) {
             bar_init(smem_addr(b_full + s), 1);
-            bar_init(smem_addr(b_empty + s), 1);
+            bar_init(smem_addr(b_empty + s), kCodeIssuers);
         }
-        bar_init(smem_addr(acc_full), 1);
+        bar_init(smem_addr(acc_full), kCodeIssuers);
         bar_init(smem_addr(acc_empty), kEpilogueWarps);
-        bar_init(smem_addr(mma_drain), 1);
+        for (int i = 0; i < kCodeIssuers; ++i) bar_init(smem_addr(mma_drain + i), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -248,8 +249,11 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                 if (row < p.row_end) store_row32(p.y + row * p.y_ld + h * 32, v, alpha, p.beta, p.bias, h * 32, p.epilogue);
             }
         }
-    } else if (warp == kEpilogueWarps) {
-        // ================= MMA issuer =================
+    } else if (warp < kEpilogueWarps + kCodeIssuers) {
+        // ================= MMA issuers: warp sb issues the MMAs of row sub-block sb (its own accumulator columns).  One
+        // issuing thread is held to the rate of the tensor pipe and then spends half as long again on commits and waits
+        // with the pipe running dry; two threads issue a window's MMAs side by side =================
+        const int sb = warp - kEpilogueWarps;
         const std::uint64_t b_desc0 = smem_desc(bstage0);
         const std::uint32_t b_lo0 = static_cast<std::uint32_t>(b_desc0), b_hi = static_cast<std::uint32_t>(b_desc0 >> 32);
         int sa = 0, s = 0;
@@ -267,9 +271,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                     const std::uint32_t fresh = w != 0 ? 1u : 0u; // the group's first MMAs overwrite the accumulators
 #pragma unroll
                     for (int kk = 0; kk < kWin / 16; ++kk)
-#pragma unroll
-                        for (int sb = 0; sb < kSubBlocks; ++sb)
-                            mma_f16_a_in_tmem(tmem_base + sb * NC, a_col + sb * 64 + kk * 8, b_lo + kk * 16, b_hi, IDESC, kk == 0 ? fresh : 1u);
+                        mma_f16_a_in_tmem(tmem_base + sb * NC, a_col + sb * 64 + kk * 8, b_lo + kk * 16, b_hi, IDESC, kk == 0 ? fresh : 1u);
                     mma_commit(smem_addr(a_empty + sa));
                     mma_commit(smem_addr(b_empty + s));
                     if (w == p.windows - 1) mma_commit(smem_addr(acc_full));
@@ -281,10 +283,10 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
             }
         }
         if (*abort_flag != 0 && lane == 0) { // gave up: let the MMAs in flight finish before tensor memory is freed
-            mma_commit(smem_addr(mma_drain));
-            bar_wait_drain(smem_addr(mma_drain), 0u);
+            mma_commit(smem_addr(mma_drain + sb));
+            bar_wait_drain(smem_addr(mma_drain + sb), 0u);
         }
-    } else if (warp == kEpilogueWarps + 1) {
+    } else if (warp == kEpilogueWarps + kCodeIssuers) {
         // ================= W loader =================
         if (lane == 0) {
             int s = 0, issued = 0;
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
             if (dead) // the copies still in flight land before the CTA gives up its shared memory
                 for (int i = issued > SB ? issued - SB : 0; i < issued; ++i) bar_wait_drain(smem_addr(b_full + i % SB), static_cast<std::uint32_t>((i / SB) & 1));
         }
-    } else if (warp == kEpilogueWarps + 2) {
+    } else if (warp == kEpilogueWarps + kCodeIssuers + 1) {
         // ================= code stages =================
         if (lane == 0) {
             int s = 0, issued = 0;
@@ -326,7 +328,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
         // ================= decode: bytes -> fp16 operand in tensor memory =================
         // A warp may write the 32 lanes (warp mod 4) of tensor memory: rows 32 * quarter .. + 31 of both row
         // sub-blocks.  The four warps of a quarter take one 16-gene chunk of the half window each.
-        const int dw = warp - (kEpilogueWarps + 3);
+        const int dw = warp - (kEpilogueWarps + kCodeIssuers + 2);
         const int quarter = warp & 3, chunk = dw >> 2;
         const __half2 magic = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u))); // 1024: fp16(0x6400 | byte) = 1024 + byte
         const __half2 bias1025 = __floats2half2_rn(1025.0f, 1025.0f);
@@ -410,7 +412,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
 template<int NC>
 cb200_status launch_codes(const codes_params &p, int sm_count, cudaStream_t stream) {
     constexpr int SB = codes_w_stages(NC), SC = codes_code_stages(NC);
-    constexpr std::size_t smem = SB * NC * kWin * 2 + SC * kCodeSlotBytes + (2 * SC + 2 * kOperandStages + 2 * SB + 3) * sizeof(std::uint64_t) + 16;
+    constexpr std::size_t smem = SB * NC * kWin * 2 + SC * kCodeSlotBytes + (2 * SC + 2 * kOperandStages + 2 * SB + 2 + kCodeIssuers) * sizeof(std::uint64_t) + 16;
     static_assert(smem <= 232448, "shared memory budget");
     CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_codes_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const std::int64_t groups = p.group_end - p.group_begin;
