@@ -172,9 +172,11 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         # gene by gene from a gene-major copy that prepare builds ("gene_gather").
         torch.cuda.synchronize(device)
         t_prepare = time.perf_counter()           # prepare is outside the timed region; its cost is reported
-        op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype,
-                              device, multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
-                              device_matrix=x if prepare_matrix else None, deterministic=deterministic)
+        def make_op():
+            return ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype,
+                                    device, multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
+                                    device_matrix=x if prepare_matrix else None, deterministic=deterministic)
+        op = make_op()
         kind, dbytes = "transpose", 4
     else:
         n = cfg["n"]
@@ -186,15 +188,31 @@ def build_workload(name, device, rank, world, seed=0, rows_override=None, multip
         # kernel with --no-prepare-matrix
         torch.cuda.synchronize(device)
         t_prepare = time.perf_counter()           # prepare is outside the timed region; its cost is reported
-        op = ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype, device,
-                              host_row_ptr=x.host_row_ptr,
-                              multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
-                              device_matrix=x if prepare_matrix else None, persistent_limit_bytes=persistent_limit_bytes)
+        host_row_ptr = x.host_row_ptr
+
+        def make_op():
+            return ops.PreparedSpmm(capi.PROJECTION_CSR, rows, cfg["cols"], n, x.nnz, x.bits, x.policy, dense.dtype, device,
+                                    host_row_ptr=host_row_ptr,
+                                    multiply=capi.DTYPE_BF16 if multiply == "bf16" else capi.DTYPE_F32,
+                                    device_matrix=x if prepare_matrix else None, persistent_limit_bytes=persistent_limit_bytes)
+        op = make_op()
         kind, dbytes = "forward", 2
     torch.cuda.synchronize(device)
+    first_ms = (time.perf_counter() - t_prepare) * 1e3
+    # The first prepare of a process also pays for loading the library's kernels and the first large allocations.
+    # What a matrix costs is the second one: the operation is destroyed and prepared again, and that time is reported
+    # (the first one beside it).
+    prepare_ms = first_ms
+    if op.persistent_bytes > 0:
+        op.close()
+        torch.cuda.synchronize(device)
+        t_prepare = time.perf_counter()
+        op = make_op()
+        torch.cuda.synchronize(device)
+        prepare_ms = (time.perf_counter() - t_prepare) * 1e3
     wl.update(x=x, dense=dense, out=out, op=op, units=x.nnz, kind=kind, n=n,
               bytes=algorithmic_bytes(kind, rows, cfg["cols"], n, x.nnz, x.bits, dbytes), flops=2.0 * x.nnz * n,
-              prepare_ms=(time.perf_counter() - t_prepare) * 1e3)
+              prepare_ms=prepare_ms, prepare_first_ms=first_ms)
     return wl
 
 
@@ -475,7 +493,8 @@ def measure_workload(name, args, device, rank, world, steps, warmup, fleet, mult
     rec = {"schedule": op.schedule, "steps": steps, "ms_per_step": total_ms / steps, "step_ms": summary_stats(per_step),
            "rows": wl["rows"], "cols": wl["cfg"]["cols"], "n": wl["n"], "bits": x.bits,
            "units_per_gpu": int(wl["units"]), "gpu_launches": int(launches),
-           "prepare_ms_once": round(wl.get("prepare_ms", 0.0), 2), "persistent_bytes": op.persistent_bytes}
+           "prepare_ms_once": round(wl.get("prepare_ms", 0.0), 2), "prepare_ms_first_in_process": round(wl.get("prepare_first_ms", 0.0), 2),
+           "persistent_bytes": op.persistent_bytes}
     if transpose:
         # the two halves of a step, timed apart: the partial alone, and the all-reduce alone (back to back)
         _, k_ms = timed_loop(lambda: op.run_launch(launch), min(steps, 5), 1, device)
@@ -709,7 +728,8 @@ def run_ours(args):
         result["parity_check"] = main["parity_check"]
     if main["prepare_ms_once"] > 0 and main["persistent_bytes"] > 0:
         amortised_ms = main["ms_per_step"] + main["prepare_ms_once"] / args.steps
-        result["prepared"] = {"prepare_ms": main["prepare_ms_once"], "persistent_bytes": main["persistent_bytes"],
+        result["prepared"] = {"prepare_ms": main["prepare_ms_once"], "first_prepare_of_the_process_ms": main.get("prepare_ms_first_in_process"),
+                              "persistent_bytes": main["persistent_bytes"],
                               "amortised_value_at_steps": {"steps": args.steps, "value": total_units / (amortised_ms * 1e-3) / 1e9}}
     if "ms_kernel" in main:
         result["transpose"] = {k: main[k] for k in ("ms_kernel", "ms_allreduce", "allreduce_bytes") if k in main}
