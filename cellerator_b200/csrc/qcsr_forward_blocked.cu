@@ -609,6 +609,9 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                     if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
                     ++qc;
                 }
+                // The hand-over of the tile also vouches for the window's W stage: one warp of the group waits for it here,
+                // where the group has slack, and the MMA warps then wait for a single barrier per window.
+                if (gtid < 32) bar_wait(smem_addr(w_full + static_cast<int>(q % STAGES)), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag, limit);
                 bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag, limit);
 #pragma unroll
                 for (int k = 0; k < kABufBytes / (kGroupThreads * 16); ++k)
@@ -620,10 +623,9 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                 for (int k = 0; k < kChunk2Entries / (kGroupThreads * 4); ++k) {
                     const std::uint32_t e[4] = {held[k].x, held[k].y, held[k].z, held[k].w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) { // padding words (top bit set) go to a scratch slot instead of branching
-                        unsigned char *dst = static_cast<int>(e[j]) >= 0 ? tile + (((e[j] >> 16) & 0x7fffu) << 1) : scratch_slot;
-                        *reinterpret_cast<unsigned short *>(dst) = static_cast<unsigned short>(e[j] & 0xffffu);
-                    }
+                    for (int j = 0; j < 4; ++j) // padding words (top bit set) are not stored
+                        if (static_cast<int>(e[j]) >= 0)
+                            *reinterpret_cast<unsigned short *>(tile + (((e[j] >> 16) & 0x7fffu) << 1)) = static_cast<unsigned short>(e[j] & 0xffffu);
                 }
                 int guard = 0;
                 while (!last && ++guard < (1 << 20)) { // further chunks of a long segment: scattered from shared memory
@@ -686,8 +688,7 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
             for (int w = 0; w < p.windows; ++w, ++q) {
                 const std::uint32_t b = static_cast<std::uint32_t>(q & 1);
                 const int s = static_cast<int>(q % STAGES);
-                bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag, limit);
-                bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag, limit);
+                bar_wait(smem_addr(a_full + b), static_cast<std::uint32_t>((q >> 1) & 1), abort_flag, limit); // tile and W stage
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (lane == 0) {
                     const std::uint32_t a_tile = smem0 + b * kABufBytes + sb * kSubBlockBytes;
