@@ -549,7 +549,7 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
         }
         for (int s = 0; s < STAGES; ++s) {
             bar_init(smem_addr(w_full + s), 1);
-            bar_init(smem_addr(w_empty + s), kSubBlocks);
+            bar_init(smem_addr(w_empty + s), 1); // passed on by the scatter group that sees the window's tile released
         }
         for (int s = 0; s < CHUNKS; ++s) {
             bar_init(smem_addr(c_full + s), 1);
@@ -613,6 +613,9 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                 // where the group has slack, and the MMA warps then wait for a single barrier per window.
                 if (gtid < 32) bar_wait(smem_addr(w_full + static_cast<int>(q % STAGES)), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag, limit);
                 bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag, limit);
+                // the MMAs of the group's previous window are done with the tile, hence with that window's W stage too: the
+                // MMA warps commit to the tile's barrier only, and the release of the W stage is passed on from here
+                if (gtid == 0 && q >= 2) bar_arrive(smem_addr(w_empty + static_cast<int>((q - 2) % STAGES)));
 #pragma unroll
                 for (int k = 0; k < kABufBytes / (kGroupThreads * 16); ++k)
                     *reinterpret_cast<uint4 *>(tile + k * (kGroupThreads * 16) + gtid * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -698,7 +701,6 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                         mma_bf16(tmem_base + sb * NC, smem_desc_sw128(a_tile + (kk >> 2) * kHalfBytes + (kk & 3) * 32), smem_desc(b_tile + kk * 256),
                                  IDESC, w > 0 || kk > 0);
                     mma_commit(smem_addr(a_empty + b));
-                    mma_commit(smem_addr(w_empty + s));
                     if (w == p.windows - 1) mma_commit(smem_addr(acc_full));
                 }
                 __syncwarp();
