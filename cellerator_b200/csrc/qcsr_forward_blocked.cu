@@ -294,8 +294,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_fwd_blocked_kernel(const blo
                 bar_wait(smem_addr(a_empty + b), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
                 unsigned char *tile = smem + b * kABufBytes;
 #pragma unroll
-                for (int k = 0; k < kABufBytes / (kProducerThreads * 16); ++k)
-                    *reinterpret_cast<uint4 *>(tile + k * (kProducerThreads * 16) + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                for (int k = 0; k < kABufBytes / (kProducerThreads * 8); ++k) // 8-byte stores: see the two-group kernel
+                    *reinterpret_cast<uint2 *>(tile + k * (kProducerThreads * 8) + tid * 8) = make_uint2(0u, 0u);
                 asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); // the whole tile is zero before anyone scatters
                 // the W stage carries the decode table; baked entries do not need it, only the MMA waits for W
                 if constexpr (!BAKED) bar_wait(smem_addr(w_full + s), static_cast<std::uint32_t>((q / STAGES) & 1), abort_flag);
@@ -617,8 +617,8 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                 // MMA warps commit to the tile's barrier only, and the release of the W stage is passed on from here
                 if (gtid == 0 && q >= 2) bar_arrive(smem_addr(w_empty + static_cast<int>((q - 2) % STAGES)));
 #pragma unroll
-                for (int k = 0; k < kABufBytes / (kGroupThreads * 16); ++k)
-                    *reinterpret_cast<uint4 *>(tile + k * (kGroupThreads * 16) + gtid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                for (int k = 0; k < kABufBytes / (kGroupThreads * 8); ++k) // 8-byte stores: a warp's 16-byte store costs 7 wavefronts of
+                    *reinterpret_cast<uint2 *>(tile + k * (kGroupThreads * 8) + gtid * 8) = make_uint2(0u, 0u); // the LSU data pipe for 512 bytes, two 8-byte stores 4 (4.79 -> 4.60 ms)
                 // the whole tile is zero before anyone of the group scatters (named barrier 1 or 2)
                 if (grp == 0) asm volatile("bar.sync 1, %0;" ::"n"(kGroupThreads) : "memory");
                 else asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory");

@@ -253,8 +253,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                     }
                     bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);
 #pragma unroll
-                    for (int k = 0; k < kTileBytes / (kGroupThreads * 16); ++k)
-                        *reinterpret_cast<uint4 *>(tile + k * (kGroupThreads * 16) + gtid * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int k = 0; k < kTileBytes / (kGroupThreads * 8); ++k) // 8-byte stores: fewer wavefronts of the LSU data pipe per byte than 16-byte ones
+                        *reinterpret_cast<uint2 *>(tile + k * (kGroupThreads * 8) + gtid * 8) = make_uint2(0u, 0u);
                     // the whole tile is zero before anyone of the group scatters (named barrier 2 or 3)
                     if (grp == 0) asm volatile("bar.sync 2, %0;" ::"n"(kGroupThreads) : "memory");
                     else asm volatile("bar.sync 3, %0;" ::"n"(kGroupThreads) : "memory");
