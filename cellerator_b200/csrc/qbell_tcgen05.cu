@@ -231,8 +231,11 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
             cp_async_commit();
             const std::uint32_t my_codes = codes_stage + buf * kCodesStageBytes + load_cell * 512;
             const std::uint32_t my_meta = meta_stage + buf * kMetaStageBytes + chunk * 32;
+            // the block columns of the block row: one load per lane, handed round by shuffles (a load per block put a
+            // global-memory latency at the head of every item)
+            const std::uint32_t bc_lane = lane < p.width ? __ldg(p.block_col_idx + br * p.width + lane) : 0xffffffffu;
             for (int slot = 0; slot < p.width; ++slot) {
-                const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
+                const std::uint32_t bc = __shfl_sync(0xffffffffu, bc_lane, slot);
                 if (bc == 0xffffffffu) continue;
                 const int stage = static_cast<int>(item % kStages);
                 bar_wait(smem_addr(empty_bar + stage), static_cast<std::uint32_t>(((item / kStages) & 1) ^ 1), abort_flag);
@@ -317,8 +320,9 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
             bar_wait(smem_addr(acc_empty + buf), static_cast<std::uint32_t>(((use >> 1) & 1) ^ 1), abort_flag);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             bool any = false;
+            const std::uint32_t bc_lane = lane < p.width ? __ldg(p.block_col_idx + br * p.width + lane) : 0xffffffffu;
             for (int slot = 0; slot < p.width; ++slot) {
-                const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
+                const std::uint32_t bc = __shfl_sync(0xffffffffu, bc_lane, slot);
                 if (bc == 0xffffffffu) continue;
                 const int stage = static_cast<int>(item % kStages);
                 bar_wait(smem_addr(full_bar + stage), static_cast<std::uint32_t>((item / kStages) & 1), abort_flag);
