@@ -515,13 +515,13 @@ const char *schedule_name(std::uint32_t variant) noexcept {
     case schedule_gene_tiled: fraction = 0.070; break;
     case schedule_tensor_windows: fraction = 0.062; break;
     case schedule_tensor_blocked:
-        fraction = transpose ? (split ? 0.092 : 0.275) : (split ? (shape.dense_dtype == CB200_DTYPE_BF16 ? 0.140 : 0.093) : 0.280);
+        fraction = transpose ? (split ? 0.092 : 0.275) : (split ? (shape.dense_dtype == CB200_DTYPE_BF16 ? 0.147 : 0.098) : 0.294);
         break;
     case schedule_tensor_dense: fraction = 0.395; break;
-    case schedule_tensor_codes: fraction = 0.459; break;
+    case schedule_tensor_codes: fraction = 0.465; break;
     case schedule_vector_reductions: fraction = 0.013; break;
     case schedule_gene_gather: fraction = 0.047; break;
-    case schedule_tcgen05_block_rows: fraction = 0.197; break;
+    case schedule_tcgen05_block_rows: fraction = 0.204; break;
     case schedule_cuda_cores: fraction = 0.013; break;
     default: break;
     }
