@@ -398,6 +398,10 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                 if (sa == 0) pa ^= 1u;
             }
         }
+        // a wait that ran out can end the loop between a store and its wait: nothing of this warp is in flight when the
+        // CTA frees tensor memory
+        __syncwarp();
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
