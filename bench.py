@@ -700,9 +700,9 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"],
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": f"u{main['bits']} codes -> " + ("bf16 products (tcgen05), f32 accumulate"
-                                                 if schedule in ("tensor_windows", "tcgen05_block_rows")
+                                                 if schedule == "tensor_windows"
                                                  else "fp16 products (tcgen05), f32 accumulate"
-                                                 if schedule in ("tensor_blocked", "tensor_dense", "tensor_codes")
+                                                 if schedule in ("tensor_blocked", "tensor_dense", "tensor_codes", "tcgen05_block_rows")
                                                  else "split bf16 products (tcgen05, %s passes), f32 accumulate" % schedule[-1]
                                                  if schedule in ("tensor_blocked_x2", "tensor_blocked_x3")
                                                  else "f32 products, f32 accumulate"),

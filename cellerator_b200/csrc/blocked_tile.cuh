@@ -5,6 +5,7 @@
 #pragma once
 
 #include "kernels.cuh"
+#include "operand_scaling.cuh"
 #include "sm100_primitives.cuh"
 
 #include <cuda_bf16.h>
@@ -75,67 +76,6 @@ __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
     d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
     return d;
 }
-// fp16 operands.  The decoded values and W are rounded to 16 bits before the tensor cores multiply them.  bf16
-// keeps 8 significant bits; fp16 keeps 11, which makes every product eight times more exact, but has a narrow
-// exponent range.  So an fp16 operand is stored times a power of two that brings its largest magnitude into
-// [2^14, 2^15), and the result is divided by the two factors again (exactly: they are powers of two).  Entries
-// more than 2^-29 below the largest lose bits to fp16's subnormal range, an absolute error below 2^-40 of the
-// largest magnitude.  The factor of W is found on the device at every launch (absmax_kernel), the factor of the
-// decoded values at prepare time.
-__host__ __device__ __forceinline__ float operand_scale(float absmax) {
-    if (!(absmax > 0.0f) || !(absmax < 3.0e38f)) return 1.0f; // zero, infinite or NaN: leave the operand as it is
-    int e = 0;
-    frexpf(absmax, &e); // absmax = m * 2^e, m in [0.5, 1)
-    e = e < -100 ? -100 : (e > 100 ? 100 : e);
-    return ldexpf(1.0f, 15 - e);
-}
-// Largest magnitude of a dense operand as the bits of a float in *out_bits (zeroed by the caller before).
-template<typename WT>
-__device__ __forceinline__ void absmax_body(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits, unsigned block, unsigned blocks) {
-    float m = 0.0f;
-    const std::int64_t total = rows * n;
-    for (std::int64_t i = static_cast<std::int64_t>(block) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<std::int64_t>(blocks) * blockDim.x) {
-        const std::int64_t r = i / n;
-        const int c = static_cast<int>(i - r * n);
-        float v;
-        if constexpr (sizeof(WT) == 2) v = __bfloat162float(w[r * ld + c]);
-        else v = w[r * ld + c];
-        m = fmaxf(m, fabsf(v)); // NaN entries are ignored here; they still reach the product
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(out_bits, __float_as_uint(m)); // non-negative floats order like their bits
-}
-template<typename WT>
-__global__ void __launch_bounds__(256) absmax_kernel(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits) {
-    absmax_body(w, ld, rows, n, out_bits, blockIdx.x, gridDim.x);
-}
-
-// Largest magnitude a decoded value can take, from the metadata alone: max over genes of |scale| * max code
-// (+ |offset| of the gene) in bound[0], max over rows of |row offset| in bound[1] (row-offset policy), as the
-// bits of non-negative floats.  The caller zeroes both words.
-__device__ __forceinline__ void value_bound_body(const float *scales, const float *gene_offsets, std::int64_t genes, const float *row_offsets,
-                                                 std::int64_t rows, float max_code, unsigned *bound, unsigned block) {
-    const std::int64_t i = static_cast<std::int64_t>(block) * blockDim.x + threadIdx.x;
-    float a = 0.0f, b = 0.0f;
-    if (i < genes) a = fabsf(scales != nullptr ? scales[i] : 1.0f) * max_code + (gene_offsets != nullptr ? fabsf(gene_offsets[i]) : 0.0f);
-    if (row_offsets != nullptr && i < rows) b = fabsf(row_offsets[i]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
-    }
-    if ((threadIdx.x & 31) == 0) {
-        if (a > 0.0f) atomicMax(bound, __float_as_uint(a));
-        if (b > 0.0f) atomicMax(bound + 1, __float_as_uint(b));
-    }
-}
-__global__ void __launch_bounds__(256) value_bound_kernel(const float *scales, const float *gene_offsets, std::int64_t genes,
-                                                          const float *row_offsets, std::int64_t rows, float max_code, unsigned *bound) {
-    value_bound_body(scales, gene_offsets, genes, row_offsets, rows, max_code, bound, blockIdx.x);
-}
-
 // W [genes][n] (leading dimension ld) -> one record per window of 128 genes: the n x 128 slice of
 // W^T in operand layout (byte offset of (column c, gene e) = (c/8)*2048 + (e/8)*128 + (c%8)*16 +
 // (e%8)*2, zero for genes >= cols) followed by 128 x {scale, zero-point}.  part 0 writes

@@ -16,13 +16,19 @@
 // caller's workspace, W^T per gene block of 32 (genes padded with zeros) already in that operand
 // layout; a block's N x 32 slice is then one contiguous 16 KB range.
 //
+// Operands are fp16 (eleven significant bits against bf16's eight), each stored times a power of two that brings
+// its largest magnitude into [2^14, 2^15) so that fp16's exponent range cannot overflow; the factors (found on the
+// device at every launch: largest |W|, and the bound of the decoded magnitudes from scales and offsets) are divided
+// out of the result.  The decode runs on pairs: a byte permute (code -> fp16 1024 + code), a subtraction, a fused
+// multiply-add with the pair's {scale, offset} from a table of fp16 pairs written beside W^T at launch.
+//
 // One CTA (288 threads, two CTAs per SM) streams the present blocks of its block rows, two at a time, through a
 // 2-stage ring (two blocks share a stage's waits, proxy fence and hand-over: 0.273 ms against 0.296 with one
 // block per stage and four stages, on 250k cells x 8,192 genes):
 //   warps 4-7  producers: one thread fetches the block's slice of W^T with a single bulk async copy
 //              (cp.async.bulk, byte-counted on the stage's mbarrier; fetching it as 1,024 separate
 //              16-byte cp.async chunks doubled the L2 sector traffic and ran at half the speed);
-//              all 128 decode the block's 32 x 32 codes to bf16 (per-gene scale / zero-point
+//              all 128 decode the block's 32 x 32 codes to fp16 (per-gene scale / zero-point
 //              applied in registers) straight into the operand layout.  Codes and metadata of a
 //              whole block row are staged in shared memory one block row ahead, so decoding never
 //              waits on DRAM;
@@ -34,6 +40,7 @@
 // to 0.  Every barrier wait is bounded; on a time-out a status word is set, the waits stop
 // blocking, and the kernel still runs to completion and frees its TMEM.
 #include "kernels.cuh"
+#include "operand_scaling.cuh"
 #include "sm100_primitives.cuh"
 
 #include <cuda_bf16.h>
@@ -42,7 +49,7 @@ namespace cb200 {
 
 std::uint64_t qbell_tcgen05_workspace_bytes(std::int64_t cols, std::int64_t n) {
     const std::int64_t kpad = (cols + 31) / 32 * 32;
-    return static_cast<std::uint64_t>(n * kpad * 2 + 256);
+    return static_cast<std::uint64_t>(n * kpad * 2 + 256 + kpad * 4); // status block | W^T (fp16) | {scale, offset} pairs
 }
 
 namespace {
@@ -51,12 +58,12 @@ constexpr int kStages = 2;          // ring stages; a stage holds up to kStageBl
 constexpr int kStageBlocks = 2;     // two blocks share the stage's waits, proxy fence and hand-over
 constexpr int kMaxWidth = 16;                      // blocks per block row the staging area holds
 constexpr int kCodesStageBytes = 32 * 512;         // one block row of codes: 32 cells x up to 512 bytes
-constexpr int kMetaStageBytes = kMaxWidth * 256;   // per block: 32 scales + 32 offsets
+constexpr int kMetaStageBytes = kMaxWidth * 128;   // per block: 16 gene pairs x {scale pair, offset pair} as fp16
 constexpr int kEpilogueThreads = 128; // warps 0-3
 constexpr int kProducerThreads = 128; // warps 4-7
 constexpr int kThreads = 288;         // + MMA warp 8
-constexpr int kATileBytes = 256 * 64; // 256 output columns x 32 genes bf16
-constexpr int kBTileBytes = 32 * 64;  // 32 cells x 32 genes bf16
+constexpr int kATileBytes = 256 * 64; // 256 output columns x 32 genes fp16
+constexpr int kBTileBytes = 32 * 64;  // 32 cells x 32 genes fp16
 constexpr int kBlockBytes = kATileBytes + kBTileBytes; // one block's operands: [A 16 KB | B 2 KB]
 constexpr int kStageBytes = kStageBlocks * kBlockBytes;
 
@@ -68,7 +75,11 @@ struct tc_params {
     const std::uint8_t *packed;
     const float *scales;
     const float *offsets;
-    const __nv_bfloat16 *wt; // [kpad/32 gene blocks][n x 32 slice of W^T in operand layout]
+    const __half *wt;        // [kpad/32 gene blocks][n x 32 slice of W^T in operand layout], fp16 times a power of two
+    const uint2 *pairs;      // per pair of genes {scale pair, offset pair} as fp16, times the decoded operand's power of two;
+                             // row-offset policy: the offset pair holds 1 for a gene of the matrix, 0 for padding
+    const unsigned *w_absmax;    // largest |W| of this launch as float bits
+    const unsigned *value_bound; // [2] bounds of the decoded magnitudes as float bits
     std::int64_t kpad;
     float *y;
     std::int64_t y_ld;
@@ -88,13 +99,6 @@ __device__ __forceinline__ void bar_expect_tx(std::uint32_t bar, std::uint32_t b
 __device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-// 16-byte copy of which only the first `bytes` (0..16) are read; the rest is filled with zeros
-__device__ __forceinline__ void cp_async_16_zfill(std::uint32_t dst, const void *src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void lds_f32x4(std::uint32_t addr, float &a, float &b, float &c, float &d) {
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "r"(addr));
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template<int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 // K-major, no swizzle: core matrices of 8 rows x 16 bytes; LBO (between the two core matrices a
@@ -107,10 +111,10 @@ __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
     d |= static_cast<std::uint64_t>(1) << 46; // descriptor version of this architecture
     return d;
 }
-// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 32, M = 128.
-constexpr std::uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
+// kind::f16 instruction descriptor: D fp32, A and B fp16 (format 0), both K-major, N = 32, M = 128.
+constexpr std::uint32_t kInstrDesc = (1u << 4) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
 
-__device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b, bool accumulate) {
+__device__ __forceinline__ void mma_f16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b, bool accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
@@ -121,17 +125,34 @@ __device__ __forceinline__ void mma_bf16(std::uint32_t tmem_d, std::uint64_t des
 // W [genes][n] (leading dimension ld) -> per gene block of 32, the n x 32 slice of W^T already in
 // the shared-memory operand layout (core matrices of 8 output columns x 8 genes, 128 bytes each:
 // byte offset of (column m, gene e) = (m/8)*512 + (e/8)*128 + (m%8)*16 + (e%8)*2), zero for
-// genes >= cols.  A block's slice is one contiguous n*64-byte range, so the main kernel fetches it
-// with a single bulk copy.
-__global__ void __launch_bounds__(256) pack_w_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
-                                                     __nv_bfloat16 *packed_wt) {
+// genes >= cols, as fp16(w * ws), ws = operand_scale(largest |w|) (eleven significant bits instead of bf16's
+// eight; the exponent range is kept by the power of two).  A block's slice is one contiguous n*64-byte range, so
+// the main kernel fetches it with a single bulk copy.  The block's 16 gene pairs of {scale pair, offset pair}
+// (fp16, times vs = operand_scale(bound of the decoded magnitudes)) are written beside it.
+__global__ void __launch_bounds__(256) pack_w_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n, __half *packed_wt,
+                                                     const float *scales, const float *offsets, int row_policy, const unsigned *w_absmax,
+                                                     const unsigned *value_bound, uint2 *pairs) {
     const std::int64_t block = blockIdx.x;                     // gene block
-    __nv_bfloat16 *dst = packed_wt + block * static_cast<std::int64_t>(n) * 32;
+    const float ws = operand_scale(__uint_as_float(*w_absmax));
+    __half *dst = packed_wt + block * static_cast<std::int64_t>(n) * 32;
     for (int i = threadIdx.x; i < n * 32; i += blockDim.x) {
         const int e = i / n, m = i % n;                        // consecutive threads read consecutive columns of one gene
         const std::int64_t gene = block * 32 + e;
-        const __nv_bfloat16 v = gene < cols ? w[gene * ld + m] : __float2bfloat16(0.0f);
-        dst[((m >> 3) * 512 + (e >> 3) * 128 + (m & 7) * 16 + (e & 7) * 2) >> 1] = v;
+        const float v = gene < cols ? __bfloat162float(w[gene * ld + m]) : 0.0f;
+        dst[((m >> 3) * 512 + (e >> 3) * 128 + (m & 7) * 16 + (e & 7) * 2) >> 1] = __float2half_rn(v * ws);
+    }
+    if (threadIdx.x < 16) {
+        const float vs = operand_scale(__uint_as_float(value_bound[0]) + __uint_as_float(value_bound[1]));
+        float sc[2], of[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const std::int64_t g = block * 32 + threadIdx.x * 2 + i;
+            sc[i] = g < cols ? (scales != nullptr ? scales[g] : 1.0f) * vs : 0.0f;
+            if (row_policy) of[i] = g < cols ? 1.0f : 0.0f;
+            else of[i] = g < cols && offsets != nullptr ? offsets[g] * vs : 0.0f;
+        }
+        const __half2 s2 = __floats2half2_rn(sc[0], sc[1]), o2 = __floats2half2_rn(of[0], of[1]);
+        pairs[block * 16 + threadIdx.x] = make_uint2(*reinterpret_cast<const unsigned *>(&s2), *reinterpret_cast<const unsigned *>(&o2));
     }
 }
 
@@ -193,7 +214,8 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
         const std::uint32_t meta_stage = codes_stage + 2 * kCodesStageBytes;       // [2][16 slots][32 scales | 32 offsets]
         const int row_bytes = p.width * 32 * BITS / 8;
         const int chunks_per_row = row_bytes / 16;
-        const bool stage_offsets = !row_policy && p.offsets != nullptr;
+        const float vs = operand_scale(__uint_as_float(__ldg(p.value_bound)) + __uint_as_float(__ldg(p.value_bound + 1)));
+        const __half2 magic = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u))); // 1024: fp16(0x6400 | code) = 1024 + code
 
         // Codes and per-gene metadata of a whole block row are brought into shared memory one block
         // row ahead of their use, so that decoding an item never waits on DRAM.
@@ -204,17 +226,11 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                 if (row >= p.row_begin && row < p.row_end)
                     cp_async_16(codes_stage + buf * kCodesStageBytes + c_cell * 512 + ((c ^ (c_cell & 7)) << 4), p.packed + row * p.row_stride + c * 16);
             }
-            for (int i = pt; i < p.width * 16; i += kProducerThreads) {
-                const int slot = i >> 4, q = i & 15;
-                const bool is_offset = q >= 8;
-                const float *base = is_offset ? p.offsets : p.scales;
-                if (base == nullptr || (is_offset && !stage_offsets)) continue;
+            for (int i = pt; i < p.width * 8; i += kProducerThreads) { // a block's 16 pairs: eight 16-byte pieces
+                const int slot = i >> 3, q = i & 7;
                 const std::uint32_t bc = __ldg(p.block_col_idx + br * p.width + slot);
                 if (bc == 0xffffffffu) continue;
-                const std::int64_t gene = static_cast<std::int64_t>(bc) * 32 + (q & 7) * 4;
-                const std::int64_t left = p.cols - gene;                          // genes >= cols are zero-filled
-                const int bytes = left >= 4 ? 16 : (left > 0 ? static_cast<int>(left) * 4 : 0);
-                cp_async_16_zfill(meta_stage + buf * kMetaStageBytes + slot * 256 + q * 16, bytes > 0 ? base + gene : base, bytes);
+                cp_async_16(meta_stage + buf * kMetaStageBytes + slot * 128 + q * 16, p.pairs + static_cast<std::int64_t>(bc) * 16 + q * 2);
             }
         };
 
@@ -226,7 +242,8 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
             const int buf = iteration & 1;
             const std::int64_t row = br * 32 + cell;
             const bool cell_valid = row >= p.row_begin && row < p.row_end;
-            const float row_offset = (row_policy && p.offsets != nullptr && cell_valid) ? __ldg(p.offsets + row) : 0.0f;
+            // row-offset policy: the cell's offset, times the operand's power of two, for both genes of a pair
+            const __half2 row_offset2 = __float2half2_rn((row_policy && p.offsets != nullptr && cell_valid) ? __ldg(p.offsets + row) * vs : 0.0f);
             // this block row's staged data is complete for every producer thread, and everyone has
             // finished decoding the previous block row (whose buffer the next prefetch overwrites)
             cp_async_wait<0>();
@@ -234,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
             if (br + step < p.block_row_end) prefetch_block_row(br + step, buf ^ 1);
             cp_async_commit();
             const std::uint32_t my_codes = codes_stage + buf * kCodesStageBytes + load_cell * 512;
-            const std::uint32_t my_meta = meta_stage + buf * kMetaStageBytes + chunk * 32;
+            const std::uint32_t my_meta = meta_stage + buf * kMetaStageBytes + chunk * 32; // the chunk's four gene pairs
             // the block columns of the block row: one load per lane, handed round by shuffles (a load per block put a
             // global-memory latency at the head of every item)
             const std::uint32_t bc_lane = lane < p.width ? __ldg(p.block_col_idx + br * p.width + lane) : 0xffffffffu;
@@ -265,9 +282,10 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                 const std::uint32_t b_tile = a_tile + kATileBytes;
                 if (pt == 0)
                     bulk_copy_g2s(a_tile, p.wt + static_cast<std::int64_t>(bc) * (H * 128 * 32), H * 128 * 64, smem_addr(full_bar + stage));
-                // ---- B: decode 8 codes of (cell, genes chunk) to bf16, from the staged copies
-                const std::int64_t gene0 = static_cast<std::int64_t>(bc) * 32 + chunk * 8;
-                __nv_bfloat162 out[4];
+                // ---- B: decode 8 codes of (cell, genes chunk) to fp16, from the staged copies: per pair of codes a byte
+                //      permute (code -> fp16 1024 + code), a subtraction (exact), a fused multiply-add with the pair's
+                //      {scale, offset}; genes past the matrix have scale and offset 0
+                std::uint32_t out[4];
                 // every lane reads and swaps (rows outside the launch hold stale bytes that are never decoded)
                 std::uint32_t lo = 0, hi = 0;
                 if constexpr (BITS == 8)
@@ -282,44 +300,38 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                     }
                 }
                 if (cell_valid) {
-                    unsigned code[8];
+                    std::uint32_t raw[4];
                     if constexpr (BITS == 8) {
+                        raw[0] = __byte_perm(lo, 0x64646464u, 0x4140u);
+                        raw[1] = __byte_perm(lo, 0x64646464u, 0x4342u);
+                        raw[2] = __byte_perm(hi, 0x64646464u, 0x4140u);
+                        raw[3] = __byte_perm(hi, 0x64646464u, 0x4342u);
+                    } else {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            code[e] = (lo >> (8 * e)) & 0xffu;
-                            code[4 + e] = (hi >> (8 * e)) & 0xffu;
+                            const std::uint32_t two = lo >> (8 * e); // the byte that holds the pair's two 4-bit codes
+                            raw[e] = 0x64006400u | (two & 0xfu) | ((two & 0xf0u) << 12);
                         }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) code[e] = (lo >> (4 * e)) & 0xfu;
                     }
-                    float sc[8], of[8];
-                    if (p.scales != nullptr) {
-                        lds_f32x4(my_meta + slot * 256, sc[0], sc[1], sc[2], sc[3]);
-                        lds_f32x4(my_meta + slot * 256 + 16, sc[4], sc[5], sc[6], sc[7]);
-                    } else {
+                    uint4 m0, m1; // {scale pair, offset pair} of the chunk's pairs 0-1 and 2-3
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(m0.x), "=r"(m0.y), "=r"(m0.z), "=r"(m0.w) : "r"(my_meta + slot * 128));
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(m1.x), "=r"(m1.y), "=r"(m1.z), "=r"(m1.w) : "r"(my_meta + slot * 128 + 16));
+                    const std::uint32_t sc[4] = {m0.x, m0.z, m1.x, m1.z}, of[4] = {m0.y, m0.w, m1.y, m1.w};
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) sc[e] = 1.0f;
+                    for (int e = 0; e < 4; ++e) {
+                        const __half2 code2 = __hsub2(*reinterpret_cast<const __half2 *>(&raw[e]), magic);
+                        __half2 o2 = *reinterpret_cast<const __half2 *>(&of[e]);
+                        if (row_policy) o2 = __hmul2(o2, row_offset2); // the pair's {1 | 0} times the cell's offset
+                        const __half2 v = __hfma2(code2, *reinterpret_cast<const __half2 *>(&sc[e]), o2);
+                        out[e] = *reinterpret_cast<const std::uint32_t *>(&v);
                     }
-                    if (stage_offsets) {
-                        lds_f32x4(my_meta + slot * 256 + 128, of[0], of[1], of[2], of[3]);
-                        lds_f32x4(my_meta + slot * 256 + 144, of[4], of[5], of[6], of[7]);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) of[e] = row_offset;
-                    }
-                    float v[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = gene0 + e < p.cols ? fmaf(static_cast<float>(code[e]), sc[e], of[e]) : 0.0f;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) out[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) out[e] = __floats2bfloat162_rn(0.0f, 0.0f);
+                    for (int e = 0; e < 4; ++e) out[e] = 0u;
                 }
                 {
                     const std::uint32_t dst = b_tile + (cell >> 3) * 512 + chunk * 128 + (cell & 7) * 16;
-                    const std::uint32_t *w32 = reinterpret_cast<const std::uint32_t *>(out);
+                    const std::uint32_t *w32 = out;
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w32[0]), "r"(w32[1]), "r"(w32[2]), "r"(w32[3])
                                  : "memory");
                 }
@@ -363,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                         for (int h = 0; h < H; ++h) {
 #pragma unroll
                             for (int kk = 0; kk < 2; ++kk) {
-                                mma_bf16(tmem_base + buf * (H * 32) + h * 32, smem_desc(a_tile + h * 8192 + kk * 256),
+                                mma_f16(tmem_base + buf * (H * 32) + h * 32, smem_desc(a_tile + h * 8192 + kk * 256),
                                          smem_desc(b_tile + kk * 256), any || j > 0 || kk > 0);
                             }
                         }
@@ -382,6 +394,9 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
         }
     } else if (warp < 4) {
         // ================= epilogue =================
+        // both operands were stored times powers of two (fp16 range): the result is divided by them again
+        const float alpha = p.alpha / (operand_scale(__uint_as_float(__ldg(p.w_absmax))) *
+                                       operand_scale(__uint_as_float(__ldg(p.value_bound)) + __uint_as_float(__ldg(p.value_bound + 1))));
         long long use = 0;
         for (std::int64_t br = first; br < p.block_row_end; br += step, ++use) {
             const int buf = static_cast<int>(use & 1);
@@ -407,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, 2) qbell_tcgen05_kernel(const tc_par
                     const std::int64_t row = row0 + c;
                     if (row >= p.row_begin && row < p.row_end) {
                         float *out = p.y + row * p.y_ld + col;
-                        float r = p.alpha * v[c];
+                        float r = alpha * v[c];
                         if (p.beta != 0.0f) r = fmaf(p.beta, *out, r);
                         if (composed) r = apply_epilogue(r, bias, p.epilogue);
                         *out = r;
@@ -460,16 +475,27 @@ cb200_status launch_qbell_tcgen05(const qbell_view &x, const dense_args &d, std:
 
     const std::int64_t kpad = (x.cols + 31) / 32 * 32;
     int *status = static_cast<int *>(workspace);
-    __nv_bfloat16 *wt = reinterpret_cast<__nv_bfloat16 *>(static_cast<unsigned char *>(workspace) + 256);
-    CB200_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    pack_w_kernel<<<static_cast<unsigned>(kpad / 32), 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld,
-                                                                        x.cols, static_cast<int>(d.n), wt);
-    count_launch();
+    unsigned *w_absmax = reinterpret_cast<unsigned *>(workspace) + 1;    // float bits of the largest |W|
+    unsigned *value_bound = reinterpret_cast<unsigned *>(workspace) + 2; // [2], [3]: bounds of the decoded magnitudes
+    __half *wt = reinterpret_cast<__half *>(static_cast<unsigned char *>(workspace) + 256);
+    uint2 *pairs = reinterpret_cast<uint2 *>(static_cast<unsigned char *>(workspace) + 256 + d.n * kpad * 2);
+    const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
+    CB200_CUDA_OK(cudaMemsetAsync(status, 0, 4 * sizeof(int), stream));
+    const std::int64_t elements = x.cols * d.n;
+    const unsigned w_blocks = static_cast<unsigned>(std::min<std::int64_t>((elements + 1023) / 1024, 4 * static_cast<std::int64_t>(sm_count)));
+    const std::int64_t span = std::max<std::int64_t>(x.cols, row_policy ? x.rows : 0);
+    operand_bounds_kernel<<<w_blocks + static_cast<unsigned>((span + 255) / 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), w_blocks, x.scales,
+        row_policy ? nullptr : x.offsets, row_policy ? x.offsets : nullptr, x.rows, static_cast<float>((1 << x.bits) - 1), w_absmax, value_bound);
+    pack_w_kernel<<<static_cast<unsigned>(kpad / 32), 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols,
+                                                                        static_cast<int>(d.n), wt, x.scales, x.offsets, row_policy ? 1 : 0,
+                                                                        w_absmax, value_bound, pairs);
+    count_launch(2);
     CB200_CUDA_OK(cudaGetLastError());
     tc_params p{};
     p.rows = x.rows; p.cols = x.cols; p.width = x.ell_cols / 32; p.row_stride = x.row_stride_bytes;
     p.block_col_idx = x.block_col_idx; p.packed = x.packed; p.scales = x.scales; p.offsets = x.offsets;
-    p.wt = wt; p.kpad = kpad; p.y = d.out; p.y_ld = d.out_ld;
+    p.wt = wt; p.pairs = pairs; p.w_absmax = w_absmax; p.value_bound = value_bound; p.kpad = kpad; p.y = d.out; p.y_ld = d.out_ld;
     p.block_row_begin = row_begin / 32; p.block_row_end = (row_end + 31) / 32;
     p.row_begin = row_begin; p.row_end = row_end;
     p.n = static_cast<int>(d.n); p.policy = x.policy; p.alpha = d.alpha; p.beta = d.beta; p.bias = d.bias; p.epilogue = d.epilogue; p.status = status;

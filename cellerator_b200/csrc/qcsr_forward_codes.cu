@@ -94,16 +94,6 @@ __global__ void __launch_bounds__(512) bytify_kernel(const std::uint32_t *entrie
     (void)windows;
 }
 
-// One launch for the two reductions a launch starts with: blocks [0, w_blocks) find the largest |W| (the factor of the
-// fp16 W operand), the others the bound of the decoded magnitudes from the scales and zero-points (the factor of
-// the decoded operand).
-__global__ void __launch_bounds__(256) operand_bounds_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t genes, int n, unsigned w_blocks,
-                                                             const float *scales, const float *offsets, float max_code, unsigned *w_absmax,
-                                                             unsigned *value_bound) {
-    if (blockIdx.x < w_blocks) absmax_body(w, ld, genes, n, w_absmax, blockIdx.x, w_blocks);
-    else value_bound_body(scales, offsets, genes, nullptr, 0, max_code, value_bound, blockIdx.x - w_blocks);
-}
-
 // Per window: the W slice in operand layout (pack_windows_kernel's part, grid.y column groups) and, by the blocks of
 // column group 0, the window's 64 gene pairs of {fp16(scale * s), fp16(offset * s)}, s = operand_scale(bound of the
 // decoded magnitudes): table[pair] = {scales of genes 2p and 2p+1, offsets of genes 2p and 2p+1}; genes past the
@@ -498,7 +488,7 @@ cb200_status launch_qcsr_forward_codes(const qcsr_view &x, const dense_args &d, 
     const std::int64_t elements = x.cols * d.n;
     const unsigned w_blocks = static_cast<unsigned>(std::min<std::int64_t>((elements + 1023) / 1024, 4 * static_cast<std::int64_t>(sm_count)));
     operand_bounds_kernel<<<w_blocks + static_cast<unsigned>((x.cols + 255) / 256), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), w_blocks, x.scales, x.offsets,
+        static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), w_blocks, x.scales, x.offsets, nullptr, 0,
         static_cast<float>((1 << x.bits) - 1), w_absmax, value_bound);
     pack_codes_operands_kernel<<<dim3(static_cast<unsigned>(windows), static_cast<unsigned>(d.n / kPackColumns)), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(d.dense), d.dense_ld, x.cols, static_cast<int>(d.n), x.scales, x.offsets, records, w_absmax, value_bound,
