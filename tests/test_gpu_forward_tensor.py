@@ -283,3 +283,39 @@ def test_value_generation_is_checked_by_operations_that_keep_values(cuda_device,
     exact = ops.PreparedSpmm(capi.PROJECTION_CSR, 600, 400, 64, x.nnz, 8, 1, w.dtype, cuda_device, value_generation=7)
     exact.run(x, w, y, value_generation=8)
     exact.close()
+
+
+@pytest.mark.parametrize("schedule", ["tensor_blocked", "tensor_dense", "tensor_codes"])
+@pytest.mark.parametrize("value_factor,w_factor", [(1.0e-6, 1.0e4), (3.0e5, 1.0e-5), (1.0, 0.0)])
+def test_fp16_schedules_keep_their_accuracy_over_magnitudes(cuda_device, oracle, monkeypatch, schedule, value_factor, w_factor):
+    """The schedules that multiply fp16 operands store them times powers of two (decoded values: found at prepare or,
+    for the code tiles, at launch; W: at every launch): tiny and huge scales, offsets and W keep the accuracy of
+    eleven significant bits, an all-zero W gives exact zeros."""
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, schedule)
+    rng = np.random.default_rng(97)
+    bits = 4 if schedule == "tensor_codes" else 8
+    rows, cols, n = 256 * 2 + 33, 900, 64
+    c = random_csr(rng, rows=rows, cols=cols, max_nnz=300, bits=bits, policy=1)
+    c["scales"] = (c["scales"] * value_factor).astype(np.float32)
+    c["offsets"] = (c["offsets"] * value_factor).astype(np.float32)
+    c["values"] = (c["values"] * value_factor).astype(np.float32)
+    c = host_pack(oracle, c)
+    x = to_dev(c, cuda_device)
+    w, _ = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    w = (w.float() * w_factor).to(torch.bfloat16)
+    w_host = w.float().cpu().numpy()
+    op = prepared(x, n, w, cuda_device, blocked=True)
+    assert op.schedule == schedule
+    y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert op.status() == 0
+    if w_factor == 0.0:
+        assert torch.all(y == 0.0)
+    else:
+        ref = oracle.qcsr_forward(bits, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"],
+                                  w_host, cols)
+        l1, _ = row_l1(oracle, c)
+        err = np.abs(y.cpu().numpy().astype(np.float64) - ref)
+        scale = l1[:, None] * float(np.abs(w_host).max()) + 1e-300
+        assert np.all(err <= 2e-3 * scale), f"max err/scale {np.max(err / scale):.3e}"
+    op.close()
