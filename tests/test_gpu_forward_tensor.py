@@ -1,12 +1,13 @@
-"""GPU parity of the tensor-core forward schedules (decoded values rounded to bf16, bf16 W, fp32
-accumulation in TMEM), through the C ABI, against the oracle: "tensor_windows" reads the CSR arrays
-with one thread per row, "tensor_blocked" streams the window-blocked copy that prepare builds when
-it is handed the device-resident matrix, "tensor_dense" streams the decoded operand tiles that
-prepare keeps instead of that copy when the matrix is dense enough and the device has room.
+"""GPU parity of the tensor-core forward schedules (16-bit products, fp32 accumulation in TMEM), through the
+C ABI, against the oracle: "tensor_windows" reads the CSR arrays with one thread per row (bf16 values and W),
+"tensor_blocked" streams the window-blocked copy that prepare builds when it is handed the device-resident
+matrix, "tensor_dense" streams the decoded operand tiles that prepare keeps instead of that copy when the matrix
+is dense enough and the device has room, "tensor_codes" streams tiles of 4-bit codes and decodes them at launch
+(the last three multiply fp16 values and W, stored times powers of two).
 
-Tolerance: each product carries the bf16 rounding of the decoded value (relative 2^-9), so the
-error of an output is at most 2^-9 * ||row||_1 * max|W| plus fp32 summation error; the test bound is
-the benchmark contract's 1e-2 relative, taken against ||row||_1 * max|W|."""
+Tolerance: each product carries the 16-bit rounding of the decoded value and of W (relative 2^-9 for bf16, 2^-12
+for fp16), so the error of an output is at most 2^-8 * ||row||_1 * max|W| plus fp32 summation error; the test
+bound is the benchmark contract's 1e-2 relative, taken against ||row||_1 * max|W|."""
 import numpy as np
 import pytest
 import torch
