@@ -657,6 +657,32 @@ def run_ours(args):
         if rank == 0:   # the host result against the device-resident result of the exact schedule, sampled rows vs the oracle
             e2e["parity_check"] = parity_of_what_ran(dict(wl, out=y_host), _NoStatus(), False)
         L.cb200_host_stage_destroy(stage)
+        # The same call sequence with the matrix RESIDENT, as the reference's prepared operations hold it (the shard
+        # stays on its GPU between steps; a step brings W and takes Y): the prepared operation of the timed loop above,
+        # W from pinned host memory, Y back to pinned host memory, all inside the timed region.  Reported beside the
+        # end-to-end number, not instead of it.
+        launch_r = op.make_launch(x, dense, out)
+
+        def resident_call():
+            dense.copy_(w_host, non_blocking=True)
+            op.run_launch(launch_r)
+            y_host.copy_(out, non_blocking=True)
+            torch.cuda.synchronize(device)
+        resident_call()
+        if world > 1:
+            dist.barrier()
+        r_steps = max(3, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for _ in range(r_steps):
+            resident_call()
+        r_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / r_steps], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(r_ms, op=dist.ReduceOp.MAX)
+        r_ms = float(r_ms.item())
+        e2e["resident_matrix"] = {"value": total_units / (r_ms * 1e-3) / 1e9, "unit": "Gnnz/s", "ms_per_step": r_ms, "steps": r_steps,
+                                  "h2d_bytes_per_step": int(w_host.numel() * w_host.element_size()),
+                                  "d2h_bytes_per_step": int(y_host.numel() * 4), "schedule": op.schedule,
+                                  "call": "cb200_spmm_run on the prepared operation; W from and Y to pinned host memory every step"}
         del host, y_host
 
     # ---- the other configurations on the same line (short runs; the headline workload's memory is released first)
