@@ -605,6 +605,7 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                         const int i = (k * kGroupThreads + gtid) * 4;
                         held[k] = i < count ? chunk[i >> 2] : make_uint4(kInvalidEntry, kInvalidEntry, kInvalidEntry, kInvalidEntry);
                     }
+                    fence_loads_cta(); // the words are used much later: they must have arrived before the stage is handed back
                     __syncwarp();
                     if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
                     ++qc;

@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
     if (tid == 0) {
         for (int s = 0; s < SC; ++s) {
             bar_init(smem_addr(c_full + s), 1);
-            bar_init(smem_addr(c_empty + s), kDecodeWarps);
+            bar_init(smem_addr(c_empty + s), kDecodeWarps / 2); // the warps of the stage's half window
         }
         for (int s = 0; s < SA; ++s) {
             bar_init(smem_addr(a_full + s), kDecodeWarps);
@@ -317,76 +317,70 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
     } else {
         // ================= decode: bytes -> fp16 operand in tensor memory =================
         // A warp may write the 32 lanes (warp mod 4) of tensor memory: rows 32 * quarter .. + 31 of both row
-        // sub-blocks.  The four warps of a quarter take one 16-gene chunk of the half window each.
+        // sub-blocks.  The four warps of a quarter split a window's two half windows and, within a half, its two pairs of
+        // 16-gene chunks: a warp visits one code stage per window (one wait, one hand-back) and decodes two chunks of it.
         const int dw = warp - (kEpilogueWarps + kCodeIssuers + 2);
-        const int quarter = warp & 3, chunk = dw >> 2;
+        const int quarter = warp & 3, hf = (dw >> 2) & 1, pairc = dw >> 3;
         const __half2 magic = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u))); // 1024: fp16(0x6400 | byte) = 1024 + byte
         const __half2 bias1025 = __floats2half2_rn(1025.0f, 1025.0f);
-        const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + kOperandCol0 + chunk * 8;
-        const int total = my_groups * halves;
-        int sc = 0, sa = 0;
-        std::uint32_t pc = 0, pa = 1;
-        // the codes of a half window are fetched into registers one half window ahead of their decoding
-        uint4 x[kSubBlocks];
-        bool dead = total == 0 || bar_wait(smem_addr(c_full), 0u, abort_flag);
-        if (!dead) {
-#pragma unroll
-            for (int k = 0; k < kSubBlocks; ++k) x[k] = *reinterpret_cast<const uint4 *>(cstage0 + chunk * kChunkPlaneBytes + (k * 128 + quarter * 32 + lane) * 16);
-        }
-        for (int q = 0; q < total && !dead; ++q) {
+        const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + kOperandCol0 + hf * 32 + pairc * 16;
+        const int windows_total = my_groups * p.windows;
+        int sa = 0;
+        std::uint32_t pa = 1;
+        for (int wq = 0; wq < windows_total; ++wq) {
+            const int q = 2 * wq + hf; // this warp's half window in the sequence of code stages
+            const int sc = q % SC;
+            if (bar_wait(smem_addr(c_full + sc), static_cast<std::uint32_t>((q / SC) & 1), abort_flag)) break;
             const unsigned char *in = cstage0 + sc * kCodeSlotBytes;
-            // the 16 genes' {scale, zero-point} pairs of this half window: one address for the whole warp
-            uint2 so[8];
+            uint4 x[2][kSubBlocks];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint4 t = *(reinterpret_cast<const uint4 *>(in + kCodeStageBytes + chunk * 64) + j);
-                so[2 * j] = make_uint2(t.x, t.y);
-                so[2 * j + 1] = make_uint2(t.z, t.w);
-            }
-            const int half = q & 1;
-            if (half == 0) { // a new window: its operand stage must have been read by the MMAs that used it last
-                if (bar_wait(smem_addr(a_empty + sa), pa, abort_flag)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            std::uint32_t r[kSubBlocks][8];
-#pragma unroll
-            for (int k = 0; k < kSubBlocks; ++k) {
-                const std::uint32_t w[4] = {x[k].x, x[k].y, x[k].z, x[k].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        // two bytes -> fp16 pair 1024 + byte; minus 1025 = the code (exact); code * scale + offset; 0 where the byte was 0
-                        const std::uint32_t bits = __byte_perm(w[j], 0x64646464u, hh == 0 ? 0x4140u : 0x4342u);
-                        const __half2 raw = *reinterpret_cast<const __half2 *>(&bits);
-                        const __half2 s2 = *reinterpret_cast<const __half2 *>(&so[2 * j + hh].x);
-                        const __half2 o2 = *reinterpret_cast<const __half2 *>(&so[2 * j + hh].y);
-                        const __half2 v = __hfma2(__hsub2(raw, bias1025), s2, o2);
-                        r[k][2 * j + hh] = *reinterpret_cast<const std::uint32_t *>(&v) & __hne2_mask(raw, magic);
-                    }
-                }
-            }
-            // this stage's codes and table are in registers: hand it back, and fetch the next half window's codes
-            __syncwarp();
-            if (lane == 0) bar_arrive(smem_addr(c_empty + sc));
-            if (++sc == SC) { sc = 0; pc ^= 1u; }
-            if (q + 1 < total) {
-                if (bar_wait(smem_addr(c_full + sc), pc, abort_flag)) break;
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int k = 0; k < kSubBlocks; ++k)
-                    x[k] = *reinterpret_cast<const uint4 *>(cstage0 + sc * kCodeSlotBytes + chunk * kChunkPlaneBytes + (k * 128 + quarter * 32 + lane) * 16);
-            }
-            // columns [32 * half + 8 * chunk, + 8) of the row's 64: genes 64 * half + 16 * chunk .. + 15, the even gene in the low half
+                    x[c][k] = *reinterpret_cast<const uint4 *>(in + (pairc * 2 + c) * kChunkPlaneBytes + (k * 128 + quarter * 32 + lane) * 16);
+            // a new window: its operand stage must have been read by the MMAs that used it last
+            if (bar_wait(smem_addr(a_empty + sa), pa, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < kSubBlocks; ++k) tmem_st8(lane_base + sa * kOperandCols + k * 64 + half * 32, r[k]);
-            if (half == 1) {
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) bar_arrive(smem_addr(a_full + sa));
-                sa ^= 1;
-                if (sa == 0) pa ^= 1u;
+            for (int c = 0; c < 2; ++c) {
+                // the 16 genes' {scale, zero-point} pairs of this chunk: one address for the whole warp
+                uint2 so[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 t = *(reinterpret_cast<const uint4 *>(in + kCodeStageBytes + (pairc * 2 + c) * 64) + j);
+                    so[2 * j] = make_uint2(t.x, t.y);
+                    so[2 * j + 1] = make_uint2(t.z, t.w);
+                }
+#pragma unroll
+                for (int k = 0; k < kSubBlocks; ++k) {
+                    const std::uint32_t w[4] = {x[c][k].x, x[c][k].y, x[c][k].z, x[c][k].w};
+                    std::uint32_t r[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            // two bytes -> fp16 pair 1024 + byte; minus 1025 = the code (exact); code * scale + offset; 0 where the byte was 0
+                            const std::uint32_t bits = __byte_perm(w[j], 0x64646464u, hh == 0 ? 0x4140u : 0x4342u);
+                            const __half2 raw = *reinterpret_cast<const __half2 *>(&bits);
+                            const __half2 s2 = *reinterpret_cast<const __half2 *>(&so[2 * j + hh].x);
+                            const __half2 o2 = *reinterpret_cast<const __half2 *>(&so[2 * j + hh].y);
+                            const __half2 v = __hfma2(__hsub2(raw, bias1025), s2, o2);
+                            r[2 * j + hh] = *reinterpret_cast<const std::uint32_t *>(&v) & __hne2_mask(raw, magic);
+                        }
+                    }
+                    // columns [32 * half + 8 * chunk, + 8) of the row's 64: genes 64 * half + 16 * chunk .. + 15, the even gene in the low half
+                    tmem_st8(lane_base + sa * kOperandCols + k * 64 + c * 8, r);
+                }
             }
+            // every value read from the stage has been used (not merely requested): hand it back
+            __syncwarp();
+            if (lane == 0) bar_arrive(smem_addr(c_empty + sc));
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(smem_addr(a_full + sa));
+            sa ^= 1;
+            if (sa == 0) pa ^= 1u;
         }
         // a wait that ran out can end the loop between a store and its wait: nothing of this warp is in flight when the
         // CTA frees tensor memory

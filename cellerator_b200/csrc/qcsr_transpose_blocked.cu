@@ -247,6 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                             const int i = (k * kGroupThreads + gtid) * 4;
                             held[k] = i < n_entries ? chunk[i >> 2] : make_uint4(0x80000000u, 0x80000000u, 0x80000000u, 0x80000000u);
                         }
+                        fence_loads_cta(); // the words are used much later: they must have arrived before the stage is handed back
                         __syncwarp();
                         if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
                         ++qc;

@@ -70,6 +70,12 @@ __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src
                  : "memory");
 }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Completes the thread's earlier shared-memory loads before what follows.  A barrier arrival that hands a buffer back
+// to the copy engine must not be performed while loads from that buffer are still outstanding, which can be the case
+// when their values are only used later: with the arrival straight after such loads a kernel of this library read
+// refilled data (reproducibly); with this fence between them, or with the arrival behind the first use of the
+// values, it does not.
+__device__ __forceinline__ void fence_loads_cta() { asm volatile("fence.acq_rel.cta;" ::: "memory"); }
 
 // K-major operand with the 128-byte swizzle (the A tile): 8-row atoms of 1,024 bytes follow each
 // other (SBO = 1,024 B), the leading offset is not used for this layout (encoded as 1), and a
