@@ -28,12 +28,14 @@
 //   warp 11      one thread feeds the ring of code stages with bulk async copies (16 KB of codes and the half
 //                window's 256 bytes of {scale, zero-point} pairs behind them);
 //   warps 12-27  decode: a warp may write the 32 tensor-memory lanes (warp mod 4), so it owns those rows of both
-//                sub-blocks and one 16-gene chunk (the stage is stored chunk-major: its 16-byte loads and the
+//                sub-blocks; the four warps of a lane quarter split a window into its two half windows and each half
+//                into two pairs of 16-gene chunks, so a warp visits one code stage per window (one wait, one
+//                hand-back) and decodes two chunks of it (the stage is stored chunk-major: its 16-byte loads and the
 //                table's broadcast loads run without bank conflicts).  Per pair of codes a byte permute (byte ->
 //                fp16 1024 + byte), a subtraction of 1025 (exact: the code), a fused multiply-add with the genes'
 //                {scale, zero-point} held in registers as fp16 pairs, a compare that gives the "something stored"
 //                mask, an AND; then one 8-column store per row into one of two operand stages (a window each) of
-//                tensor memory.  The next half window's codes are fetched while this one's are stored.
+//                tensor memory.  The stage goes back to the copy engine after the last use of its values.
 // Tensor memory: columns 0-255 accumulators (2 sub-blocks x N), 256-511 two operand stages of 2 x 64 columns.
 // Every barrier wait is bounded; a role whose wait ran out stops, the loaders wait for their copies in flight and
 // the MMA warp for its MMAs before the CTA frees tensor memory.  A non-zero status word means Y is not valid.
