@@ -605,8 +605,13 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                         const int i = (k * kGroupThreads + gtid) * 4;
                         held[k] = i < count ? chunk[i >> 2] : make_uint4(kInvalidEntry, kInvalidEntry, kInvalidEntry, kInvalidEntry);
                     }
-                    fence_loads_cta(); // the words are used much later: they must have arrived before the stage is handed back
-                    __syncwarp();
+                    // the words are used much later, but they must be in the registers before the stage goes back to the copy engine
+                    {
+                        std::uint32_t all = 0;
+#pragma unroll
+                        for (int k = 0; k < kChunk2Entries / (kGroupThreads * 4); ++k) all |= held[k].x | held[k].y | held[k].z | held[k].w;
+                        wait_for_loaded(all);
+                    }
                     if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
                     ++qc;
                 }

@@ -35,7 +35,7 @@
 //                fp16 1024 + byte), a subtraction of 1025 (exact: the code), a fused multiply-add with the genes'
 //                {scale, zero-point} held in registers as fp16 pairs, a compare that gives the "something stored"
 //                mask, an AND; then one 8-column store per row into one of two operand stages (a window each) of
-//                tensor memory.  The stage goes back to the copy engine after the last use of its values.
+//                tensor memory.  The stage goes back to the copy engine once its values are in the registers (a vote waits for them).
 // Tensor memory: columns 0-255 accumulators (2 sub-blocks x N), 256-511 two operand stages of 2 x 64 columns.
 // Every barrier wait is bounded; a role whose wait ran out stops, the loaders wait for their copies in flight and
 // the MMA warp for its MMAs before the CTA frees tensor memory.  A non-zero status word means Y is not valid.
@@ -353,6 +353,15 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                     so[2 * j] = make_uint2(t.x, t.y);
                     so[2 * j + 1] = make_uint2(t.z, t.w);
                 }
+                if (c == 1) { // everything the stage holds for this warp has been requested: once it is in the registers, hand the stage back
+                    std::uint32_t all = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) all |= so[j].x | so[j].y;
+#pragma unroll
+                    for (int k = 0; k < kSubBlocks; ++k) all |= x[1][k].x | x[1][k].y | x[1][k].z | x[1][k].w;
+                    wait_for_loaded(all);
+                    if (lane == 0) bar_arrive(smem_addr(c_empty + sc));
+                }
 #pragma unroll
                 for (int k = 0; k < kSubBlocks; ++k) {
                     const std::uint32_t w[4] = {x[c][k].x, x[c][k].y, x[c][k].z, x[c][k].w};
@@ -374,9 +383,6 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                     tmem_st8(lane_base + sa * kOperandCols + k * 64 + c * 8, r);
                 }
             }
-            // every value read from the stage has been used (not merely requested): hand it back
-            __syncwarp();
-            if (lane == 0) bar_arrive(smem_addr(c_empty + sc));
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
