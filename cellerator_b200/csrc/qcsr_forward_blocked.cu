@@ -610,9 +610,8 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                         std::uint32_t all = 0;
 #pragma unroll
                         for (int k = 0; k < kChunk2Entries / (kGroupThreads * 4); ++k) all |= held[k].x | held[k].y | held[k].z | held[k].w;
-                        wait_for_loaded(all);
+                        arrive_when_loaded(smem_addr(c_empty + cs), all, lane, static_cast<std::uint32_t>(p.windows) >> 31);
                     }
-                    if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
                     ++qc;
                 }
                 // The hand-over of the tile also vouches for the window's W stage: one warp of the group waits for it here,

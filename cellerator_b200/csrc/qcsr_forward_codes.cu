@@ -8,7 +8,7 @@
 // operation_core.hh:126-129).
 //
 // What is kept.  For every group of 256 cells and every half window of 64 genes one 16 KB stage: a byte per
-// (cell, gene), 0 where nothing is stored and code + 1 where a code is (a 4-bit code leaves room for that).
+// (cell, gene), 0 where nothing is stored and code + 240 where a code is (a 4-bit code leaves room for that).
 // The matrix stays QUANTIZED: the per-gene scale and zero-point are not in the copy.  They are applied at
 // every launch, in registers, on the way from the byte to the fp16 operand the MMA reads, so new scales or
 // offsets need no new prepare; only new codes (a new structure or value generation) do.  Against the decoded
@@ -47,7 +47,9 @@ namespace cb200 {
 namespace {
 
 constexpr int kCodeStageBytes = kRows * 64;              // 16 KB: 256 rows x 64 genes, one byte per slot
-constexpr int kTableBytes = 32 * 8;                      // a half window's 32 gene pairs x {scale pair, offset pair} as fp16
+constexpr int kPairTableBytes = 32 * 8;                  // a half window's 32 gene pairs x {scale pair, offset pair} as fp16
+constexpr int kTableBytes = kPairTableBytes + 16;        // + a word that says whether the half window may be decoded without masks
+constexpr int kPresentBias = 240;                        // a stored code is kept as code + 240 (4-bit codes: 240..255), nothing stored as 0
 constexpr int kCodeSlotBytes = kCodeStageBytes + kTableBytes; // what one stage of the ring holds
 constexpr int kChunkPlaneBytes = kRows * 16;             // a stage is [16-gene chunk][row][16 codes]
 constexpr int kMaxCodeStages = 8;
@@ -70,7 +72,7 @@ __host__ __device__ constexpr int codes_code_stages(int n) {
 static_assert(codes_w_stages(128) == 3 && codes_code_stages(128) == 8, "three W windows and eight code stages in flight at N = 128");
 
 // One CTA per (group, window) segment of the window-blocked copy (code words): a byte tile in shared memory,
-// 0 = nothing stored, code + 1 otherwise; written out as two stages of 64 genes, each [16-gene chunk][row][16 codes].
+// 0 = nothing stored, code + 240 otherwise; written out as two stages of 64 genes, each [16-gene chunk][row][16 codes].
 __global__ void __launch_bounds__(512) bytify_kernel(const std::uint32_t *entries, const std::int64_t *seg_ptr, int windows,
                                                      unsigned char *stages) {
     extern __shared__ __align__(16) unsigned char tile[]; // [256 rows][128 genes]
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(512) bytify_kernel(const std::uint32_t *entrie
         if (static_cast<int>(e) < 0) continue; // padding
         const std::uint32_t off = ((e >> 15) & 0x7fffu) << 1; // byte position in the fp16 operand tile: gives the row back
         const int row = static_cast<int>(((off / kSubBlockBytes) << 7) | (((off >> 10) & 15u) << 3) | ((off >> 7) & 7u));
-        tile[row * kWin + ((e >> 8) & (kWin - 1))] = static_cast<unsigned char>((e & 0xffu) + 1u);
+        tile[row * kWin + ((e >> 8) & (kWin - 1))] = static_cast<unsigned char>((e & 0xffu) + kPresentBias);
     }
     __syncthreads();
     unsigned char *out = stages + static_cast<std::size_t>(seg) * (2 * kCodeStageBytes);
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(512) bytify_kernel(const std::uint32_t *entrie
 // matrix get zeros.
 __global__ void __launch_bounds__(256) pack_codes_operands_kernel(const __nv_bfloat16 *w, std::int64_t ld, std::int64_t cols, int n,
                                                                   const float *scales, const float *offsets, unsigned char *records,
-                                                                  const unsigned *w_absmax, const unsigned *bound_bits, uint2 *table) {
+                                                                  const unsigned *w_absmax, const unsigned *bound_bits, unsigned char *table) {
     const std::int64_t window = blockIdx.x;
     __half *rec = reinterpret_cast<__half *>(records + window * record_bytes(n));
     const float ws = operand_scale(__uint_as_float(*w_absmax));
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(256) pack_codes_operands_kernel(const __nv_bfl
         const float value = gene < cols ? __bfloat162float(w[gene * ld + c]) : 0.0f;
         rec[((c >> 3) * kRowGroupBytes + (e >> 3) * 128 + (c & 7) * 16 + (e & 7) * 2) >> 1] = __float2half_rn(value * ws);
     }
-    if (blockIdx.y != 0 || threadIdx.x >= kWin / 2) return;
+    if (blockIdx.y != 0 || threadIdx.x >= kWin / 2) return; // warps 0 and 1: the pairs of the window's first and second half
     const std::int64_t pair = window * (kWin / 2) + threadIdx.x;
     const float s = operand_scale(__uint_as_float(*bound_bits));
     float sc[2], of[2];
@@ -124,13 +126,25 @@ __global__ void __launch_bounds__(256) pack_codes_operands_kernel(const __nv_bfl
         of[i] = g < cols && offsets != nullptr ? offsets[g] * s : 0.0f;
     }
     const __half2 s2 = __floats2half2_rn(sc[0], sc[1]), o2 = __floats2half2_rn(of[0], of[1]);
-    table[pair] = make_uint2(*reinterpret_cast<const unsigned *>(&s2), *reinterpret_cast<const unsigned *>(&o2));
+    unsigned char *half_table = table + (window * 2 + (threadIdx.x >> 5)) * kTableBytes;
+    reinterpret_cast<uint2 *>(half_table)[threadIdx.x & 31] = make_uint2(*reinterpret_cast<const unsigned *>(&s2), *reinterpret_cast<const unsigned *>(&o2));
+    // Without masks a slot decodes to max(0, (byte - 240) * scale + offset): right for a stored code when the value cannot
+    // be negative (scale >= 0 and offset >= 0, as the fp16 values the kernel multiplies) and right for an empty slot
+    // (byte 0) when offset - 240 * scale <= 0.  One gene that fails makes its half window take the masked form.
+    bool plain = true;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float sh = i == 0 ? __low2float(s2) : __high2float(s2), oh = i == 0 ? __low2float(o2) : __high2float(o2);
+        plain = plain && sh >= 0.0f && oh >= 0.0f && oh <= static_cast<float>(kPresentBias) * sh;
+    }
+    const bool all_plain = __all_sync(0xffffffffu, plain);
+    if ((threadIdx.x & 31) == 0) *reinterpret_cast<std::uint32_t *>(half_table + kPairTableBytes) = all_plain ? 1u : 0u;
 }
 
 struct codes_params {
     const unsigned char *stages;  // [group][window][half][16 KB]
     const unsigned char *records; // W windows in operand layout (fp16), record_bytes(N) apart
-    const uint2 *table;           // per pair of genes {scale pair, offset pair} as fp16, windows * 64 entries
+    const unsigned char *table;   // per half window kTableBytes: 32 gene pairs of {scale pair, offset pair} as fp16, then the "no masks needed" word
     float *y;
     std::int64_t y_ld;
     std::int64_t row_end; // rows >= row_end are computed but not written
@@ -307,7 +321,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                     if (bar_wait_sleeping(smem_addr(c_empty + s), pc, abort_flag, 100u)) { dead = true; break; }
                     bar_arrive_expect_tx(smem_addr(c_full + s), kCodeSlotBytes);
                     bulk_copy_g2s(smem_addr(cstage0 + s * kCodeSlotBytes), src, kCodeStageBytes, smem_addr(c_full + s));
-                    bulk_copy_g2s(smem_addr(cstage0 + s * kCodeSlotBytes + kCodeStageBytes), p.table + static_cast<std::size_t>(h) * 32, kTableBytes,
+                    bulk_copy_g2s(smem_addr(cstage0 + s * kCodeSlotBytes + kCodeStageBytes), p.table + static_cast<std::size_t>(h) * kTableBytes, kTableBytes,
                                   smem_addr(c_full + s));
                     ++issued;
                     if (++s == SC) { s = 0; pc ^= 1u; }
@@ -324,7 +338,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
         const int dw = warp - (kEpilogueWarps + kCodeIssuers + 2);
         const int quarter = warp & 3, hf = (dw >> 2) & 1, pairc = dw >> 3;
         const __half2 magic = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u))); // 1024: fp16(0x6400 | byte) = 1024 + byte
-        const __half2 bias1025 = __floats2half2_rn(1025.0f, 1025.0f);
+        const __half2 bias = __float2half2_rn(1024.0f + kPresentBias); // fp16(0x6400 | byte) - bias = the code
         const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + kOperandCol0 + hf * 32 + pairc * 16;
         const int windows_total = my_groups * p.windows;
         int sa = 0;
@@ -334,6 +348,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
             const int sc = q % SC;
             if (bar_wait(smem_addr(c_full + sc), static_cast<std::uint32_t>((q / SC) & 1), abort_flag)) break;
             const unsigned char *in = cstage0 + sc * kCodeSlotBytes;
+            const bool plain = *reinterpret_cast<const std::uint32_t *>(in + kCodeStageBytes + kPairTableBytes) != 0u; // no masks needed
             uint4 x[2][kSubBlocks];
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -353,36 +368,44 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
                     so[2 * j] = make_uint2(t.x, t.y);
                     so[2 * j + 1] = make_uint2(t.z, t.w);
                 }
-                if (c == 1) { // everything the stage holds for this warp has been requested: once it is in the registers, hand the stage back
-                    std::uint32_t all = 0;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) all |= so[j].x | so[j].y;
-#pragma unroll
-                    for (int k = 0; k < kSubBlocks; ++k) all |= x[1][k].x | x[1][k].y | x[1][k].z | x[1][k].w;
-                    wait_for_loaded(all);
-                    if (lane == 0) bar_arrive(smem_addr(c_empty + sc));
-                }
 #pragma unroll
                 for (int k = 0; k < kSubBlocks; ++k) {
                     const std::uint32_t w[4] = {x[c][k].x, x[c][k].y, x[c][k].z, x[c][k].w};
                     std::uint32_t r[8];
+                    if (plain) { // two bytes -> fp16 pair 1024 + byte; minus 1264 = the code, or -240 for an empty slot; max(0, code * scale + offset)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < 4; ++j) {
 #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            // two bytes -> fp16 pair 1024 + byte; minus 1025 = the code (exact); code * scale + offset; 0 where the byte was 0
-                            const std::uint32_t bits = __byte_perm(w[j], 0x64646464u, hh == 0 ? 0x4140u : 0x4342u);
-                            const __half2 raw = *reinterpret_cast<const __half2 *>(&bits);
-                            const __half2 s2 = *reinterpret_cast<const __half2 *>(&so[2 * j + hh].x);
-                            const __half2 o2 = *reinterpret_cast<const __half2 *>(&so[2 * j + hh].y);
-                            const __half2 v = __hfma2(__hsub2(raw, bias1025), s2, o2);
-                            r[2 * j + hh] = *reinterpret_cast<const std::uint32_t *>(&v) & __hne2_mask(raw, magic);
+                            for (int hh = 0; hh < 2; ++hh) {
+                                const std::uint32_t bits = __byte_perm(w[j], 0x64646464u, hh == 0 ? 0x4140u : 0x4342u);
+                                const __half2 v = __hfma2_relu(__hsub2(*reinterpret_cast<const __half2 *>(&bits), bias),
+                                                               *reinterpret_cast<const __half2 *>(&so[2 * j + hh].x),
+                                                               *reinterpret_cast<const __half2 *>(&so[2 * j + hh].y));
+                                r[2 * j + hh] = *reinterpret_cast<const std::uint32_t *>(&v);
+                            }
+                        }
+                    } else { // the same without the max, and 0 where the byte was 0
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                            for (int hh = 0; hh < 2; ++hh) {
+                                const std::uint32_t bits = __byte_perm(w[j], 0x64646464u, hh == 0 ? 0x4140u : 0x4342u);
+                                const __half2 raw = *reinterpret_cast<const __half2 *>(&bits);
+                                const __half2 v = __hfma2(__hsub2(raw, bias), *reinterpret_cast<const __half2 *>(&so[2 * j + hh].x),
+                                                          *reinterpret_cast<const __half2 *>(&so[2 * j + hh].y));
+                                r[2 * j + hh] = *reinterpret_cast<const std::uint32_t *>(&v) & __hne2_mask(raw, magic);
+                            }
                         }
                     }
                     // columns [32 * half + 8 * chunk, + 8) of the row's 64: genes 64 * half + 16 * chunk .. + 15, the even gene in the low half
                     tmem_st8(lane_base + sa * kOperandCols + k * 64 + c * 8, r);
                 }
             }
+            // the stage goes back to the copy engine behind the last use of what was read from it, and behind a fence that
+            // waits for this thread's loads (handed back straight after the loads, with the values not yet in their
+            // registers, the stage was refilled under them)
+            asm volatile("fence.acq_rel.cta;" ::: "memory");
+            if (lane == 0) bar_arrive(smem_addr(c_empty + sc));
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -429,11 +452,11 @@ std::uint64_t qcsr_code_tile_bytes(std::int64_t rows, std::int64_t cols) {
 
 std::uint64_t qcsr_codes_workspace_bytes(std::int64_t cols, std::int64_t n) {
     const std::uint64_t windows = static_cast<std::uint64_t>((cols + kWin - 1) / kWin);
-    return 256u + windows * static_cast<std::uint64_t>(record_bytes(static_cast<int>(n))) + windows * (kWin / 2) * sizeof(uint2);
+    return 256u + windows * static_cast<std::uint64_t>(record_bytes(static_cast<int>(n))) + windows * 2u * kTableBytes;
 }
 
 bool qcsr_codes_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits, int policy, int dense_dtype) {
-    // a byte per slot holds code + 1: codes up to 254, i.e. every width below 8 bits; per-gene zero-points only
+    // a byte per slot holds code + 240 (0 = nothing stored): 4-bit codes; per-gene zero-points only
     return bits == 4 && policy == CB200_DECODE_PER_GENE_AFFINE && dense_dtype == CB200_DTYPE_BF16 &&
            qcsr_blocked_shape_ok(rows, cols, n, bits, dense_dtype);
 }
@@ -485,7 +508,7 @@ cb200_status launch_qcsr_forward_codes(const qcsr_view &x, const dense_args &d, 
     unsigned *value_bound = reinterpret_cast<unsigned *>(workspace) + 2; // [2], [3]: bounds of the decoded magnitudes
     unsigned char *records = static_cast<unsigned char *>(workspace) + 256;
     const std::int64_t windows = layout.windows;
-    uint2 *table = reinterpret_cast<uint2 *>(records + static_cast<std::size_t>(windows) * record_bytes(static_cast<int>(d.n)));
+    unsigned char *table = records + static_cast<std::size_t>(windows) * record_bytes(static_cast<int>(d.n));
     CB200_CUDA_OK(cudaMemsetAsync(status, 0, 4 * sizeof(int), stream));
     const std::int64_t elements = x.cols * d.n;
     const unsigned w_blocks = static_cast<unsigned>(std::min<std::int64_t>((elements + 1023) / 1024, 4 * static_cast<std::int64_t>(sm_count)));

@@ -252,9 +252,8 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
                             std::uint32_t all = 0;
 #pragma unroll
                             for (int k = 0; k < kChunkEntries / (kGroupThreads * 4); ++k) all |= held[k].x | held[k].y | held[k].z | held[k].w;
-                            wait_for_loaded(all);
+                            arrive_when_loaded(smem_addr(c_empty + cs), all, lane, static_cast<std::uint32_t>(p.windows) >> 31);
                         }
-                        if (lane == 0) bar_arrive(smem_addr(c_empty + cs));
                         ++qc;
                     }
                     bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag);

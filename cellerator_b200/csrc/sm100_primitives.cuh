@@ -72,13 +72,13 @@ __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // Values loaded from a shared-memory buffer must be in their registers before a barrier arrival hands the buffer
 // back to the copy engine; when they are only used later that is not a given: with the arrival straight after such
-// loads a kernel of this library read refilled data (reproducibly).  A warp vote over a word that depends on every
-// loaded register waits for exactly those loads (pass the OR of the registers); `fence.acq_rel.cta` cures it too but
-// also waits for the thread's earlier stores (4.73-4.78 ms against 4.60 on the 1M x 33,538 forward).  An arrival
-// behind the first use of the values needs neither.
-__device__ __forceinline__ void wait_for_loaded(std::uint32_t or_of_loaded_registers) {
-    const unsigned seen = __ballot_sync(0xffffffffu, or_of_loaded_registers == 0u);
-    asm volatile("" ::"r"(seen));
+// loads a kernel of this library read refilled data (reproducibly).  Here the arrival's address depends on a warp vote
+// over a word that depends on every loaded register (pass their OR), so it cannot be issued before those loads have
+// returned; `zero` is a value that is 0 at run time without the compiler knowing it (say, the sign bit of a count
+// among the kernel's arguments), which keeps the vote in the address.
+__device__ __forceinline__ void arrive_when_loaded(std::uint32_t bar, std::uint32_t or_of_loaded_registers, int lane, std::uint32_t zero) {
+    const unsigned seen = __ballot_sync(0xffffffffu, or_of_loaded_registers != 0u);
+    if (lane == 0) bar_arrive(bar + (seen & zero));
 }
 
 // K-major operand with the 128-byte swizzle (the A tile): 8-row atoms of 1,024 bytes follow each

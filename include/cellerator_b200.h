@@ -276,7 +276,7 @@ typedef struct cb200_spmm_problem {
      * memory; otherwise "tensor_blocked" stays.
      *
      * The same with 4-bit codes and per-gene zero-points: prepare keeps dense tiles of CODES instead
-     * (schedule "tensor_codes": rows x genes bytes, a byte per slot; 0 = nothing stored, code + 1 otherwise).
+     * (schedule "tensor_codes": rows x genes bytes, a byte per slot; 0 = nothing stored, code + 240 otherwise).
      * The matrix stays quantized: a launch decodes in registers with the scales and offsets it is given, so
      * only changed codes (a new structure or value generation) need a new prepare. */
     const cb200_qcsr *device_matrix;

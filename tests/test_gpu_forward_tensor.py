@@ -112,6 +112,49 @@ def test_tensor_schedule_parity(cuda_device, oracle, monkeypatch, schedule, bits
     op.close()
 
 
+@pytest.mark.parametrize("regime", ["no_masks", "mixed", "edge"])
+def test_code_tiles_decode_with_and_without_masks(cuda_device, oracle, monkeypatch, regime):
+    """The kernel of code tiles decodes a 64-gene half window without masks, as max(0, (byte - 240) * scale +
+    zero-point) with byte 0 for an empty slot, when every gene of the half allows it (scale >= 0, zero-point >= 0,
+    zero-point <= 240 * scale, on the fp16 values it multiplies), and with masks otherwise: all halves of the first
+    kind, halves of both kinds side by side, and genes on either side of the condition's edge."""
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "tensor_codes")
+    rng = np.random.default_rng({"no_masks": 5, "mixed": 6, "edge": 7}[regime])
+    rows, cols, n = 256 * 3 + 90, 128 * 5 + 37, 64
+    c = random_csr(rng, rows=rows, cols=cols, max_nnz=260, bits=4, policy=1)
+    c["scales"] = rng.uniform(0.05, 0.5, size=cols).astype(np.float32)
+    c["offsets"] = (c["scales"] * rng.uniform(0.0, 200.0, size=cols)).astype(np.float32)   # well inside the condition
+    if regime == "mixed":
+        for first in range(0, cols, 192):                       # every third half window holds genes that need the masks
+            c["offsets"][first + 5] = -0.7                      # a negative zero-point
+            c["offsets"][first + 40] = c["scales"][first + 40] * 300.0   # an empty slot would not decode to <= 0
+        c["scales"][100] = 0.0                                  # scale 0: the value is the zero-point
+    if regime == "edge":
+        # fp16-exact scales, zero-points at 240 * scale (still without masks) and one step above it (with them)
+        c["scales"] = (rng.integers(1, 64, size=cols) / 128.0).astype(np.float32)
+        c["offsets"] = (c["scales"] * 240.0).astype(np.float32)
+        c["offsets"][64:128] = np.nextafter(np.float16(c["offsets"][64:128]), np.float16(np.inf)).astype(np.float32)
+        c["scales"][200], c["offsets"][200] = 0.0, 0.0          # both 0 is allowed: every slot of the gene decodes to 0
+    c["values"] = (c["offsets"][c["col_idx"]] + c["scales"][c["col_idx"]] * rng.uniform(-1.0, 16.5, size=len(c["col_idx"]))).astype(np.float32)
+    c = host_pack(oracle, c)
+    x = to_dev(c, cuda_device)
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    op = prepared(x, n, w, cuda_device, blocked=True)
+    assert op.schedule == "tensor_codes"
+    y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0
+    ref = oracle.qcsr_forward(4, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"],
+                              w_host, cols)
+    l1, _ = row_l1(oracle, c)
+    assert_tensor_close(y.cpu().numpy(), ref, l1, float(np.abs(w_host).max()))
+    counts = np.diff(c["row_ptr"])
+    assert torch.all(y[torch.from_numpy(counts == 0).to(cuda_device)] == 0.0)   # empty slots add nothing either way
+    for _ in range(3):
+        assert torch.equal(y, op.run(x, w, torch.empty_like(y)))
+    op.close()
+
+
 def test_tensor_schedule_is_opt_in(cuda_device, oracle):
     """Without multiply = bf16 in the request the exact kernels run; with it, and a matrix dense
     enough, prepare picks the tensor schedule and sizes the workspace for the re-laid W."""
@@ -198,6 +241,8 @@ def test_tensor_full_scale_properties(cuda_device, oracle, monkeypatch, schedule
     l1 = (csum[x.row_ptr[1:]] - csum[x.row_ptr[:-1]]).float()
     del csum
     assert torch.all((y1 - y_exact).abs() <= 1e-2 * (l1[:, None] * wmax) + 1e-30)
+    for _ in range(2):                                        # a stage handed back too early shows as runs that differ
+        assert torch.equal(op.run(x, w1, torch.empty(x.rows, n, device=cuda_device)), y1)
     for parts in (2, 8):
         brp = ops.partition_rows(x.rows, parts)
         if schedule in BLOCKED:
