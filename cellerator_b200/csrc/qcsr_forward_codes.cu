@@ -64,12 +64,14 @@ static_assert(kSubBlocks * 128 <= kOperandCol0 && kOperandCol0 + kOperandStages 
 static_assert(kDecodeWarps == 16 && kRows == 256,
               "decode warp = (lane quarter of tensor memory it may write, 16-gene chunk); it decodes that quarter of both row sub-blocks");
 __host__ __device__ constexpr int codes_w_stages(int n) { return n * kWin * 2 * 3 <= 98304 ? 3 : 98304 / (n * kWin * 2); }
+constexpr int kTurnBytes = 32 * 32 * 4;                  // an epilogue warp's 32 rows x 32 columns on their way from row-per-lane to row-per-8-lanes
+constexpr int kTurnRegionBytes = kEpilogueWarps * kTurnBytes;
 __host__ __device__ constexpr int codes_code_stages(int n) {
-    return (232448 - 512 - codes_w_stages(n) * n * kWin * 2) / kCodeSlotBytes > kMaxCodeStages
+    return (232448 - 512 - kTurnRegionBytes - codes_w_stages(n) * n * kWin * 2) / kCodeSlotBytes > kMaxCodeStages
                ? kMaxCodeStages
-               : (232448 - 512 - codes_w_stages(n) * n * kWin * 2) / kCodeSlotBytes;
+               : (232448 - 512 - kTurnRegionBytes - codes_w_stages(n) * n * kWin * 2) / kCodeSlotBytes;
 }
-static_assert(codes_w_stages(128) == 3 && codes_code_stages(128) == 8, "three W windows and eight code stages in flight at N = 128");
+static_assert(codes_w_stages(128) == 3 && codes_code_stages(128) == 6, "three W windows and six code stages in flight at N = 128");
 
 // One CTA per (group, window) segment of the window-blocked copy (code words): a byte tile in shared memory,
 // 0 = nothing stored, code + 240 otherwise; written out as two stages of 64 genes, each [16-gene chunk][row][16 codes].
@@ -183,8 +185,9 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
     constexpr int REC = record_bytes(NC);
     constexpr std::uint32_t IDESC = instr_desc(NC, true); // fp16 operands
     extern __shared__ __align__(1024) unsigned char smem[];
-    // [SB][W window] | [SC][code stage + gene table] | barriers | tmem slot | abort
-    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(smem + SB * WREC + SC * kCodeSlotBytes);
+    // [SB][W window] | [SC][code stage + gene table] | [epilogue warp][32 x 32 floats] | barriers | tmem slot | abort
+    unsigned char *turn0 = smem + SB * WREC + SC * kCodeSlotBytes;
+    std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(turn0 + kTurnRegionBytes);
     std::uint64_t *c_full = bars;              // [SC] copy engine -> decode warps
     std::uint64_t *c_empty = c_full + SC;      // [SC] decode warps -> code loader (one arrival per warp)
     std::uint64_t *a_full = c_empty + SC;      // [SA] decode warps -> MMA (one arrival per warp)
@@ -235,24 +238,66 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
     const int halves = p.windows * (kWin / 64);
 
     if (warp < kEpilogueWarps) {
-        // ================= thread t writes row t of the group: TMEM lane = row within the sub-block =================
+        // ================= a warp reads its 32 rows (TMEM lane = row within the sub-block) 32 columns at a time and turns
+        // them in shared memory, so that 8 lanes write the 128 contiguous bytes of a row: a store touches 4 lines instead
+        // of 32.  16-byte chunk c of row r sits at chunk c ^ (r & 7): stores (a lane = a row) and loads (8 lanes = a row)
+        // both spread over all banks =================
         const int sub = tid >> 7;
+        unsigned char *turn = turn0 + warp * kTurnBytes;
+        const int chunk = lane & 7, row_of_lane = lane >> 3; // on the way out: this lane's 4 columns, and its row among the 4 of a store
         // both operands were stored times powers of two (fp16 range): the result is divided by them again
         const float alpha = p.alpha / (operand_scale(__uint_as_float(__ldg(p.w_absmax))) * operand_scale(__uint_as_float(__ldg(p.value_bound))));
         for (int gi = 0; gi < my_groups; ++gi) {
-            const std::int64_t row = (first_group + static_cast<std::int64_t>(gi) * gridDim.x) * kRows + tid;
+            const std::int64_t row0 = (first_group + static_cast<std::int64_t>(gi) * gridDim.x) * kRows + sub * 128 + (warp & 3) * 32;
             if (bar_wait_sleeping(smem_addr(acc_full), static_cast<std::uint32_t>(gi & 1), abort_flag, 400u)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
+#pragma unroll 1
             for (int h = 0; h < NC / 32; ++h) {
-                float v[32];
-                tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
-                if (h == NC / 32 - 1) { // the accumulators are in registers: the next group's MMAs may start
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) bar_arrive(smem_addr(acc_empty));
+                {
+                    float v[32];
+                    tmem_ld32(tmem_base + (static_cast<std::uint32_t>((warp & 3) * 32) << 16) + sub * NC + h * 32, v);
+                    if (h == NC / 32 - 1) { // the accumulators are in registers: the next group's MMAs may start
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) bar_arrive(smem_addr(acc_empty));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<float4 *>(turn + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * c] * alpha, v[4 * c + 1] * alpha, v[4 * c + 2] * alpha, v[4 * c + 3] * alpha);
                 }
-                if (row < p.row_end) store_row32(p.y + row * p.y_ld + h * 32, v, alpha, p.beta, p.bias, h * 32, p.epilogue);
+                __syncwarp();
+                float4 t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = 4 * i + row_of_lane;
+                    t[i] = *reinterpret_cast<const float4 *>(turn + r * 128 + ((chunk ^ (r & 7)) << 4));
+                }
+                __syncwarp(); // the next 32 columns may overwrite the turn buffer
+                float *out = p.y + (row0 + row_of_lane) * p.y_ld + h * 32 + 4 * chunk;
+                const std::int64_t rows_left = p.row_end - row0 - row_of_lane; // row 4 * i + row_of_lane is written when 4 * i < rows_left
+                if (p.beta != 0.0f) {
+                    float4 o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        o[i] = 4 * i < rows_left ? *reinterpret_cast<const float4 *>(out + static_cast<std::int64_t>(4 * i) * p.y_ld) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        t[i].x = fmaf(p.beta, o[i].x, t[i].x); t[i].y = fmaf(p.beta, o[i].y, t[i].y);
+                        t[i].z = fmaf(p.beta, o[i].z, t[i].z); t[i].w = fmaf(p.beta, o[i].w, t[i].w);
+                    }
+                }
+                if (p.epilogue != CB200_EPILOGUE_NONE) {
+                    const int col = h * 32 + 4 * chunk;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        t[i].x = finish_output(t[i].x, p.bias, col, p.epilogue); t[i].y = finish_output(t[i].y, p.bias, col + 1, p.epilogue);
+                        t[i].z = finish_output(t[i].z, p.bias, col + 2, p.epilogue); t[i].w = finish_output(t[i].w, p.bias, col + 3, p.epilogue);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (4 * i < rows_left) *reinterpret_cast<float4 *>(out + static_cast<std::int64_t>(4 * i) * p.y_ld) = t[i];
             }
         }
     } else if (warp < kEpilogueWarps + kCodeIssuers) {
@@ -431,7 +476,7 @@ __global__ void __launch_bounds__(kCodesThreads, 1) qcsr_fwd_codes_kernel(const 
 template<int NC>
 cb200_status launch_codes(const codes_params &p, int sm_count, cudaStream_t stream) {
     constexpr int SB = codes_w_stages(NC), SC = codes_code_stages(NC);
-    constexpr std::size_t smem = SB * NC * kWin * 2 + SC * kCodeSlotBytes + (2 * SC + 2 * kOperandStages + 2 * SB + 2 + kCodeIssuers) * sizeof(std::uint64_t) + 16;
+    constexpr std::size_t smem = SB * NC * kWin * 2 + SC * kCodeSlotBytes + kTurnRegionBytes + (2 * SC + 2 * kOperandStages + 2 * SB + 2 + kCodeIssuers) * sizeof(std::uint64_t) + 16;
     static_assert(smem <= 232448, "shared memory budget");
     CB200_CUDA_OK(cudaFuncSetAttribute(qcsr_fwd_codes_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     const std::int64_t groups = p.group_end - p.group_begin;

@@ -518,7 +518,7 @@ const char *schedule_name(std::uint32_t variant) noexcept {
         fraction = transpose ? (split ? 0.092 : 0.275) : (split ? (shape.dense_dtype == CB200_DTYPE_BF16 ? 0.150 : 0.100) : 0.300);
         break;
     case schedule_tensor_dense: fraction = 0.395; break;
-    case schedule_tensor_codes: fraction = 0.545; break;
+    case schedule_tensor_codes: fraction = 0.570; break;
     case schedule_vector_reductions: fraction = 0.013; break;
     case schedule_gene_gather: fraction = 0.047; break;
     case schedule_tcgen05_block_rows: fraction = 0.245; break;
