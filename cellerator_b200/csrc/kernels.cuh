@@ -127,7 +127,7 @@ struct blocked_layout {
     bool half_values = false;
     float value_scale = 1.0f;
     // Code tiles (forward, 4-bit codes, schedule "tensor_codes"): per (group, half window of 64 genes) a 16 KB stage
-    // with one byte per (cell, gene), 0 = nothing stored, else code + 1.  When set, entries / seg_ptr are gone.
+    // with one byte per (cell, gene), 0 = nothing stored, else code + 240.  When set, entries / seg_ptr are gone.
     // Scales and offsets are NOT in it: they are applied at launch.
     unsigned char *code_tiles = nullptr;
 };

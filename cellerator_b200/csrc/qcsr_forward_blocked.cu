@@ -516,6 +516,11 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
     constexpr int WREC = NC * kWin * 2;     // the W part of a record (the decode table is not needed)
     constexpr int STAGES = w2_stages(NC);
     constexpr int CHUNKS = 2 * kRing2;
+    // Who releases a window's W stage.  With more W stages than tile buffers the scatter group that sees the window's
+    // tile released, one round later, passes that on (the MMA warps commit to one barrier per window).  With only as many
+    // stages as buffers (N = 128) that would be a cycle -- the group waits for its next window's W, whose copy waits for
+    // the release the group has not passed on yet -- so there the MMA warps commit to the stage's barrier themselves.
+    constexpr bool FORWARD_W_RELEASE = STAGES > 2;
     constexpr int kTmemCols = kSubBlocks * NC < 32 ? 32 : kSubBlocks * NC;
     const std::uint32_t IDESC = p.idesc;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -549,7 +554,7 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
         }
         for (int s = 0; s < STAGES; ++s) {
             bar_init(smem_addr(w_full + s), 1);
-            bar_init(smem_addr(w_empty + s), 1); // passed on by the scatter group that sees the window's tile released
+            bar_init(smem_addr(w_empty + s), FORWARD_W_RELEASE ? 1 : kSubBlocks);
         }
         for (int s = 0; s < CHUNKS; ++s) {
             bar_init(smem_addr(c_full + s), 1);
@@ -620,7 +625,7 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                 bar_wait(smem_addr(a_empty + grp), static_cast<std::uint32_t>(((q >> 1) & 1) ^ 1), abort_flag, limit);
                 // the MMAs of the group's previous window are done with the tile, hence with that window's W stage too: the
                 // MMA warps commit to the tile's barrier only, and the release of the W stage is passed on from here
-                if (gtid == 0 && q >= 2) bar_arrive(smem_addr(w_empty + static_cast<int>((q - 2) % STAGES)));
+                if (FORWARD_W_RELEASE && gtid == 0 && q >= 2) bar_arrive(smem_addr(w_empty + static_cast<int>((q - 2) % STAGES)));
 #pragma unroll
                 for (int k = 0; k < kABufBytes / (kGroupThreads * 8); ++k) // 8-byte stores: a warp's 16-byte store costs 7 wavefronts of
                     *reinterpret_cast<uint2 *>(tile + k * (kGroupThreads * 8) + gtid * 8) = make_uint2(0u, 0u); // the LSU data pipe for 512 bytes, two 8-byte stores 4 (4.79 -> 4.60 ms)
@@ -706,6 +711,7 @@ __global__ void __launch_bounds__(kThreads2, 1) qcsr_fwd_blocked2_kernel(const b
                         mma_bf16(tmem_base + sb * NC, smem_desc_sw128(a_tile + (kk >> 2) * kHalfBytes + (kk & 3) * 32), smem_desc(b_tile + kk * 256),
                                  IDESC, w > 0 || kk > 0);
                     mma_commit(smem_addr(a_empty + b));
+                    if constexpr (!FORWARD_W_RELEASE) mma_commit(smem_addr(w_empty + s));
                     if (w == p.windows - 1) mma_commit(smem_addr(acc_full));
                 }
                 __syncwarp();

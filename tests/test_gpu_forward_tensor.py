@@ -155,6 +155,31 @@ def test_code_tiles_decode_with_and_without_masks(cuda_device, oracle, monkeypat
     op.close()
 
 
+@pytest.mark.parametrize("n", [32, 64, 128])
+def test_two_group_window_kernel_at_every_width(cuda_device, oracle, monkeypatch, n):
+    """A matrix sparse enough for the window kernel with two scatter groups (a window's entries fit one chunk), at
+    every N: at N = 128 shared memory holds only as many W stages as tile buffers, and the stage's release takes
+    another route there.  Many windows per group, so that every stage and buffer is reused many times."""
+    monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_CSR, "tensor_blocked")
+    rng = np.random.default_rng(40 + n)
+    rows, cols = 256 * 5 + 33, 128 * 40 + 50
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=500, bits=8, policy=1))
+    x = to_dev(c, cuda_device)
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    op = prepared(x, n, w, cuda_device, blocked=True)
+    assert op.schedule == "tensor_blocked"
+    assert x.nnz <= 2048 * ((rows + 255) // 256) * ((cols + 127) // 128)        # the two-group kernel's condition
+    y = op.run(x, w, torch.full((rows, n), float("nan"), device=cuda_device))
+    torch.cuda.synchronize()
+    assert int(op.workspace[:4].view(torch.int32).item()) == 0                  # no bounded wait ran out
+    ref = oracle.qcsr_forward(8, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"],
+                              w_host, cols)
+    l1, _ = row_l1(oracle, c)
+    assert_tensor_close(y.cpu().numpy(), ref, l1, float(np.abs(w_host).max()))
+    assert torch.equal(y, op.run(x, w, torch.empty_like(y)))
+    op.close()
+
+
 def test_tensor_schedule_is_opt_in(cuda_device, oracle):
     """Without multiply = bf16 in the request the exact kernels run; with it, and a matrix dense
     enough, prepare picks the tensor schedule and sizes the workspace for the re-laid W."""
