@@ -10,12 +10,28 @@
 // the device (one small kernel), so the chunk is a matrix of its own for the projection kernel.  The
 // kernels are the CSR schedules that read codes and indices at launch (gene-tiled where the shape allows,
 // else warp per row): the values arrive with the call, so nothing prepared from them can be used.
+//
+// The call is bound by the host -> device link (5 bytes per stored entry: a code and a 32-bit gene index), so where
+// every gene index fits 16 bits (k <= 65,536) the indices travel as 16-bit words: a small pool of host threads narrows
+// a chunk's indices into a pinned staging buffer while the previous chunk is on the link, and a kernel widens them
+// again on the device (3 bytes per entry on the link).  The first chunk of a call times the narrowing; if the host
+// cannot narrow faster than the link moves the two bytes saved (few cores, or many processes sharing them), the
+// rest of the call copies the 32-bit indices as they are.  A chunk that holds an index outside [0, k) is also copied
+// as it is (the kernels leave such entries out; narrowed they would alias another gene).
 #include "kernels.cuh"
 
 #include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
 #include <cstring>
+#include <mutex>
 #include <new>
+#include <thread>
 #include <vector>
+
+#include <immintrin.h>
+#include <sched.h>
 
 using namespace cb200;
 
@@ -28,10 +44,147 @@ __global__ void __launch_bounds__(256) rebase_kernel(std::int64_t *ptr, std::int
     if (i < count) ptr[i] -= base;
 }
 
+// 16-bit gene indices -> the 32-bit ones the kernels read; eight per thread (the buffers are 16-byte aligned and
+// padded to a multiple of eight entries)
+__global__ void __launch_bounds__(256) widen_indices_kernel(const uint4 *narrow, int4 *wide, std::int64_t groups_of_eight) {
+    const std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= groups_of_eight) return;
+    const uint4 v = narrow[i];
+    wide[2 * i] = make_int4(static_cast<int>(v.x & 0xffffu), static_cast<int>(v.x >> 16), static_cast<int>(v.y & 0xffffu), static_cast<int>(v.y >> 16));
+    wide[2 * i + 1] = make_int4(static_cast<int>(v.z & 0xffffu), static_cast<int>(v.z >> 16), static_cast<int>(v.w & 0xffffu), static_cast<int>(v.w >> 16));
+}
+
+// Narrows src[0..n) to 16 bits; returns false if an index lies outside [0, k) (dst is then not to be used).
+// With AVX2: sixteen indices per step, written around the cache (dst is 32-byte aligned: the staging buffer is, and
+// blocks start at multiples of kNarrowBlock); the copy engine reads them from memory next, no core does.
+__attribute__((target("avx2"))) bool narrow_block_avx2(const std::int32_t *src, std::uint16_t *dst, std::int64_t n, std::uint32_t k) {
+    const __m256i limit = _mm256_set1_epi32(static_cast<int>(k - 1u));
+    __m256i above = _mm256_setzero_si256(); // non-zero where an index, as unsigned, exceeds k - 1
+    std::int64_t i = 0;
+    if ((reinterpret_cast<std::uintptr_t>(dst) & 31u) == 0u) {
+        for (; i + 16 <= n; i += 16) {
+            const __m256i a = _mm256_loadu_si256(reinterpret_cast<const __m256i *>(src + i));
+            const __m256i b = _mm256_loadu_si256(reinterpret_cast<const __m256i *>(src + i + 8));
+            above = _mm256_or_si256(above, _mm256_xor_si256(_mm256_max_epu32(a, limit), limit));
+            above = _mm256_or_si256(above, _mm256_xor_si256(_mm256_max_epu32(b, limit), limit));
+            // the pack interleaves the two sources' 128-bit halves: put them back in order
+            _mm256_stream_si256(reinterpret_cast<__m256i *>(dst + i), _mm256_permute4x64_epi64(_mm256_packus_epi32(a, b), 0xd8));
+        }
+        _mm_sfence();
+    }
+    std::uint32_t outside = _mm256_testz_si256(above, above) ? 0u : 1u;
+    for (; i < n; ++i) {
+        const std::uint32_t v = static_cast<std::uint32_t>(src[i]);
+        outside |= v >= k ? 1u : 0u;
+        dst[i] = static_cast<std::uint16_t>(v);
+    }
+    return outside == 0u;
+}
+bool narrow_block(const std::int32_t *src, std::uint16_t *dst, std::int64_t n, std::uint32_t k) {
+    static const bool avx2 = __builtin_cpu_supports("avx2") != 0;
+    if (avx2) return narrow_block_avx2(src, dst, n, k);
+    std::uint32_t outside = 0;
+    for (std::int64_t i = 0; i < n; ++i) {
+        const std::uint32_t v = static_cast<std::uint32_t>(src[i]);
+        outside |= v >= k ? 1u : 0u;
+        dst[i] = static_cast<std::uint16_t>(v);
+    }
+    return outside == 0u;
+}
+
+// A few host threads that narrow one chunk at a time, in blocks of kNarrowBlock entries claimed with an atomic counter;
+// the calling thread takes blocks too and returns when every block is done.
+constexpr std::int64_t kNarrowBlock = 1 << 18;
+struct narrow_pool {
+    std::vector<std::thread> workers;
+    std::mutex m;
+    std::condition_variable wake, done;
+    bool stop = false;
+    int active = 0; // workers inside work(): a new job is set up only when none is
+    std::uint64_t generation = 0;
+    // the job
+    const std::int32_t *src = nullptr;
+    std::uint16_t *dst = nullptr;
+    std::int64_t n = 0;
+    std::uint32_t k = 0;
+    std::atomic<std::int64_t> next{0};
+    std::atomic<std::int64_t> blocks_left{0};
+    std::atomic<int> all_inside{1};
+
+    void work() {
+        for (;;) {
+            const std::int64_t b = next.fetch_add(1, std::memory_order_relaxed);
+            const std::int64_t lo = b * kNarrowBlock;
+            if (lo >= n) return;
+            const std::int64_t len = std::min<std::int64_t>(kNarrowBlock, n - lo);
+            if (!narrow_block(src + lo, dst + lo, len, k)) all_inside.store(0, std::memory_order_relaxed);
+            if (blocks_left.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+                std::lock_guard<std::mutex> lock(m);
+                done.notify_all();
+            }
+        }
+    }
+    void loop() {
+        std::uint64_t seen = 0;
+        for (;;) {
+            {
+                std::unique_lock<std::mutex> lock(m);
+                wake.wait(lock, [&] { return stop || generation != seen; });
+                if (stop) return;
+                seen = generation;
+                ++active;
+            }
+            work();
+            {
+                std::lock_guard<std::mutex> lock(m);
+                --active;
+            }
+            done.notify_all();
+        }
+    }
+    void start(int threads) {
+        for (int i = 0; i < threads; ++i) workers.emplace_back([this] { loop(); });
+    }
+    bool run(const std::int32_t *from, std::uint16_t *to, std::int64_t count, std::uint32_t genes) {
+        if (count <= 0) return true;
+        {
+            std::unique_lock<std::mutex> lock(m);
+            done.wait(lock, [&] { return active == 0; }); // a worker still leaving the previous job reads the job's fields
+            src = from; dst = to; n = count; k = genes;
+            next.store(0, std::memory_order_relaxed);
+            blocks_left.store((count + kNarrowBlock - 1) / kNarrowBlock, std::memory_order_relaxed);
+            all_inside.store(1, std::memory_order_relaxed);
+            ++generation;
+        }
+        wake.notify_all();
+        work();
+        std::unique_lock<std::mutex> lock(m);
+        done.wait(lock, [&] { return blocks_left.load(std::memory_order_acquire) <= 0; });
+        return all_inside.load(std::memory_order_relaxed) != 0;
+    }
+    ~narrow_pool() {
+        {
+            std::lock_guard<std::mutex> lock(m);
+            stop = true;
+        }
+        wake.notify_all();
+        for (std::thread &t : workers) t.join();
+    }
+};
+
+int usable_host_threads() {
+    cpu_set_t set;
+    CPU_ZERO(&set);
+    if (sched_getaffinity(0, sizeof(set), &set) == 0) return std::max(1, CPU_COUNT(&set));
+    return std::max(1u, std::thread::hardware_concurrency());
+}
+
 struct chunk_buffer {
     std::int64_t *row_ptr = nullptr;
     std::int64_t *packed_row_ptr = nullptr; // 4-bit codes only
     std::int32_t *col_idx = nullptr;
+    std::uint16_t *narrow_idx = nullptr;     // device: the chunk's 16-bit indices as they arrive (narrow path only)
+    std::uint16_t *narrow_host = nullptr;    // pinned host staging of the same
     std::uint8_t *packed = nullptr;
     float *row_offsets = nullptr;           // row-offset policy only
     float *y = nullptr;
@@ -52,6 +205,7 @@ struct cb200_host_stage {
     chunk_buffer ring[kMaxBuffers];
     std::uint64_t device_bytes = 0;
     std::uint64_t workspace_bytes = 0;
+    narrow_pool *pool = nullptr; // non-null: gene indices may travel as 16-bit words
 };
 
 namespace {
@@ -73,7 +227,8 @@ void cb200_host_stage_destroy(cb200_host_stage *s) {
     for (cudaStream_t st : {s->h2d, s->compute, s->d2h})
         if (st != nullptr) cudaStreamSynchronize(st);
     for (chunk_buffer &b : s->ring) {
-        cudaFree(b.row_ptr); cudaFree(b.packed_row_ptr); cudaFree(b.col_idx); cudaFree(b.packed);
+        cudaFree(b.row_ptr); cudaFree(b.packed_row_ptr); cudaFree(b.col_idx); cudaFree(b.packed); cudaFree(b.narrow_idx);
+        if (b.narrow_host != nullptr) cudaFreeHost(b.narrow_host);
         cudaFree(b.row_offsets); cudaFree(b.y); cudaFree(b.workspace);
         for (cudaEvent_t e : {b.copied_in, b.computed, b.copied_out})
             if (e != nullptr) cudaEventDestroy(e);
@@ -82,6 +237,7 @@ void cb200_host_stage_destroy(cb200_host_stage *s) {
     if (s->shared_in != nullptr) cudaEventDestroy(s->shared_in);
     for (cudaStream_t st : {s->h2d, s->compute, s->d2h})
         if (st != nullptr) cudaStreamDestroy(st);
+    delete s->pool;
     delete s;
 }
 
@@ -130,7 +286,7 @@ cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_ho
         chunk_buffer &c = s->ring[b];
         err = device_alloc(&c.row_ptr, o->max_chunk_rows + 1, &s->device_bytes);
         if (err == cudaSuccess && o->bits == 4) err = device_alloc(&c.packed_row_ptr, o->max_chunk_rows + 1, &s->device_bytes);
-        if (err == cudaSuccess) err = device_alloc(&c.col_idx, o->max_chunk_nnz, &s->device_bytes);
+        if (err == cudaSuccess) err = device_alloc(&c.col_idx, o->max_chunk_nnz + 8, &s->device_bytes);
         // 4-bit rows are padded to whole bytes: at most one byte per row on top of nnz / 2
         const std::uint64_t code_bytes = o->bits == 8 ? static_cast<std::uint64_t>(o->max_chunk_nnz)
                                                       : static_cast<std::uint64_t>(o->max_chunk_nnz) / 2u + static_cast<std::uint64_t>(o->max_chunk_rows);
@@ -142,6 +298,23 @@ cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_ho
         c.workspace = ws;
         for (cudaEvent_t *e : {&c.copied_in, &c.computed, &c.copied_out})
             if (err == cudaSuccess) err = cudaEventCreateWithFlags(e, cudaEventDisableTiming);
+    }
+    // 16-bit indices on the link: needs every gene index to fit, and host threads to narrow with
+    const int host_threads = std::min(usable_host_threads(), 16);
+    if (o->narrow_indices < -1 || o->narrow_indices > 1) {
+        cb200_host_stage_destroy(s);
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "narrow_indices is -1, 0 or 1");
+    }
+    if (err == cudaSuccess && o->k <= 65536 && (o->narrow_indices == 1 || (o->narrow_indices == 0 && host_threads >= 4))) {
+        for (int b = 0; b < o->chunk_buffers && err == cudaSuccess; ++b) {
+            chunk_buffer &c = s->ring[b];
+            err = device_alloc(&c.narrow_idx, o->max_chunk_nnz + 8, &s->device_bytes);
+            if (err == cudaSuccess) err = cudaHostAlloc(reinterpret_cast<void **>(&c.narrow_host), static_cast<std::size_t>(o->max_chunk_nnz + 8) * 2u, cudaHostAllocDefault);
+        }
+        if (err == cudaSuccess) {
+            s->pool = new (std::nothrow) narrow_pool{};
+            if (s->pool != nullptr) s->pool->start(std::max(host_threads - 1, 0)); // the calling thread narrows too
+        }
     }
     if (err != cudaSuccess) {
         cudaGetLastError();
@@ -197,6 +370,11 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
     CB200_CUDA_OK(cudaStreamWaitEvent(s->compute, s->shared_in, 0));
 
     const int buffers = o.chunk_buffers;
+    // Narrow indices pay when the host narrows an entry faster than the link moves the two bytes saved: with the
+    // link at ~50 GB/s that is 25 G entries/s for a tie with the link itself, and anything above 10.6 G entries/s
+    // still beats the 32-bit copy (5 bytes at the link's rate).  The first narrowed chunk of the call decides.
+    bool narrow = s->pool != nullptr;
+    constexpr double kNarrowMinRate = 12.0e9;
     for (std::size_t c = 0; c + 1 < bounds.size(); ++c) {
         chunk_buffer &b = s->ring[c % static_cast<std::size_t>(buffers)];
         const std::int64_t r0 = bounds[c], r1 = bounds[c + 1], rows = r1 - r0;
@@ -209,10 +387,26 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
             CB200_CUDA_OK(cudaMemcpyAsync(b.packed_row_ptr, prp + r0, static_cast<std::uint64_t>(rows + 1) * 8u, cudaMemcpyHostToDevice, s->h2d));
             in_bytes += static_cast<std::uint64_t>(rows + 1) * 8u;
         }
+        bool narrowed = false;
         if (nnz > 0) {
-            CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx, x->col_idx + n0, static_cast<std::uint64_t>(nnz) * 4u, cudaMemcpyHostToDevice, s->h2d));
+            if (narrow) {
+                // the staging buffer's previous copy (buffers chunks ago) has left it
+                if (c >= static_cast<std::size_t>(buffers)) CB200_CUDA_OK(cudaEventSynchronize(b.copied_in));
+                const auto t0 = std::chrono::steady_clock::now();
+                narrowed = s->pool->run(x->col_idx + n0, b.narrow_host, nnz, static_cast<std::uint32_t>(o.k));
+                const double seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+                if (o.narrow_indices == 0 && static_cast<double>(nnz) < kNarrowMinRate * seconds) narrow = false; // too slow here: 32-bit copies from the next chunk on
+            }
+            if (narrowed) {
+                const std::uint64_t bytes = (static_cast<std::uint64_t>(nnz) * 2u + 15u) & ~static_cast<std::uint64_t>(15u);
+                CB200_CUDA_OK(cudaMemcpyAsync(b.narrow_idx, b.narrow_host, bytes, cudaMemcpyHostToDevice, s->h2d));
+                in_bytes += bytes;
+            } else {
+                CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx, x->col_idx + n0, static_cast<std::uint64_t>(nnz) * 4u, cudaMemcpyHostToDevice, s->h2d));
+                in_bytes += static_cast<std::uint64_t>(nnz) * 4u;
+            }
             CB200_CUDA_OK(cudaMemcpyAsync(b.packed, x->packed_values + p0, static_cast<std::uint64_t>(code_bytes), cudaMemcpyHostToDevice, s->h2d));
-            in_bytes += static_cast<std::uint64_t>(nnz) * 4u + static_cast<std::uint64_t>(code_bytes);
+            in_bytes += static_cast<std::uint64_t>(code_bytes);
         }
         if (row_policy && x->offsets != nullptr) {
             CB200_CUDA_OK(cudaMemcpyAsync(b.row_offsets, x->offsets + r0, static_cast<std::uint64_t>(rows) * 4u, cudaMemcpyHostToDevice, s->h2d));
@@ -226,6 +420,12 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
         rebase_kernel<<<grid, 256, 0, s->compute>>>(b.row_ptr, rows + 1, n0);
         if (o.bits == 4) rebase_kernel<<<grid, 256, 0, s->compute>>>(b.packed_row_ptr, rows + 1, p0);
         count_launch(o.bits == 4 ? 2 : 1);
+        if (narrowed) {
+            const std::int64_t eights = (nnz + 7) / 8;
+            widen_indices_kernel<<<static_cast<unsigned>((eights + 255) / 256), 256, 0, s->compute>>>(
+                reinterpret_cast<const uint4 *>(b.narrow_idx), reinterpret_cast<int4 *>(b.col_idx), eights);
+            count_launch();
+        }
         CB200_CUDA_OK(cudaGetLastError());
         const qcsr_view view{rows, o.k, nnz, o.bits, o.policy, b.row_ptr, o.bits == 4 ? b.packed_row_ptr : nullptr, b.col_idx, b.packed,
                              s->scales, row_policy ? (x->offsets != nullptr ? b.row_offsets : nullptr) : (x->offsets != nullptr ? s->offsets : nullptr)};

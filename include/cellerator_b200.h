@@ -890,6 +890,11 @@ typedef struct cb200_host_stage_options {
     int64_t max_chunk_rows;   /* rows one device chunk buffer holds */
     int64_t max_chunk_nnz;    /* stored entries one device chunk buffer holds */
     int32_t chunk_buffers;    /* chunks in flight, 2..4 */
+    /* Gene indices as 16-bit words on the host -> device link (k <= 65,536 only; host threads narrow them into a pinned
+     * staging buffer, a kernel widens them on the device): 0 = where k allows it and at least four host threads are
+     * usable, and within a call only while the host narrows faster than the link would move the bytes saved (the first
+     * narrowed chunk of a call is timed); 1 = wherever k allows it; -1 = never. */
+    int32_t narrow_indices;
 } cb200_host_stage_options;
 
 cb200_status cb200_host_stage_create(const cb200_host_stage_options *options, cb200_host_stage **out);

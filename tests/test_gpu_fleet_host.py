@@ -159,7 +159,8 @@ def test_host_buffer_forward_through_the_chunk_ring(cuda_device, oracle, bits, p
         for _ in range(2):                                         # the ring's events are reused by a second call
             capi.check(L.cb200_host_forward(stage, C.byref(xd), w_pinned.data_ptr(), n, y_host.data_ptr(), n, 1.0, C.byref(h2d), C.byref(d2h)))
         assert L.cb200_kernel_launch_count() - launches0 >= 2 * 2 * (rows // 211)
-        assert d2h.value == rows * n * 4 and h2d.value >= len(c["col_idx"]) * 4 + c["packed"].nbytes
+        # (gene indices may cross as 16-bit words where the host narrows them fast enough: k = 4,100 allows it)
+        assert d2h.value == rows * n * 4 and h2d.value >= len(c["col_idx"]) * 2 + c["packed"].nbytes
         ref = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
                                   c["offsets"], w_host, cols)
         l1, _ = row_l1(oracle, c)
@@ -181,6 +182,53 @@ def test_host_buffer_forward_through_the_chunk_ring(cuda_device, oracle, bits, p
     y_dev = ops.spmm_forward(x, w, schedule="warp_per_row")
     if n == 24:                                                    # no tiled shape: both paths run warp per row
         assert np.array_equal(y_dev.cpu().numpy(), y_host.numpy())
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_host_buffer_forward_with_narrow_and_wide_indices(cuda_device, oracle, bits):
+    """The gene indices cross the link as 16-bit words (narrow_indices = 1), as 32-bit words (-1), or as the stage
+    decides per call (0): the results are bit-identical, and the bytes on the link are what each form needs."""
+    L = capi.lib()
+    rng = np.random.default_rng(70 + bits)
+    rows, cols, n = 2100, 65536, 64                                  # the largest k whose indices fit 16 bits
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=700, bits=bits, policy=1))
+    c["col_idx"][-1] = cols - 1 if len(c["col_idx"]) else 0          # (the last row's last gene: the top index)
+    keep = []
+    xd = _host_desc(c, keep)
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    w_pinned = w.cpu().contiguous().pin_memory()
+    nnz, results, moved = len(c["col_idx"]), {}, {}
+    for mode in (1, -1, 0):
+        o = capi.header(capi.HostStageOptions())
+        o.device, o.k, o.n, o.bits, o.policy = cuda_device.index, cols, n, bits, 1
+        o.dense_dtype = capi.DTYPE_BF16
+        o.max_chunk_rows, o.max_chunk_nnz, o.chunk_buffers, o.narrow_indices = 300, 120_000, 3, mode
+        stage = C.c_void_p()
+        capi.check(L.cb200_host_stage_create(C.byref(o), C.byref(stage)))
+        try:
+            y_host = torch.full((rows, n), float("nan")).pin_memory()
+            h2d = C.c_uint64()
+            for _ in range(2):                                       # staging buffers and events are reused by a second call
+                capi.check(L.cb200_host_forward(stage, C.byref(xd), w_pinned.data_ptr(), n, y_host.data_ptr(), n, 1.0, C.byref(h2d), None))
+            results[mode], moved[mode] = y_host.clone(), h2d.value
+        finally:
+            L.cb200_host_stage_destroy(stage)
+    assert torch.equal(results[1], results[-1]) and torch.equal(results[0], results[-1])
+    assert moved[-1] - moved[1] >= 2 * nnz - 16 * (rows // 300 + 2)     # two bytes per entry saved (16-byte padding per chunk)
+    assert moved[1] <= moved[0] <= moved[-1]
+    ref = oracle.qcsr_forward(bits, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"],
+                              w_host, cols)
+    l1, _ = row_l1(oracle, c)
+    assert_forward_close(results[1].numpy(), ref, l1, float(np.abs(w_host).max()), bf16=True)
+    # k beyond 16 bits: the stage is made, and copies 32-bit indices
+    o = capi.header(capi.HostStageOptions())
+    o.device, o.k, o.n, o.bits, o.policy, o.dense_dtype = cuda_device.index, cols + 1, n, bits, 1, capi.DTYPE_BF16
+    o.max_chunk_rows, o.max_chunk_nnz, o.chunk_buffers, o.narrow_indices = 300, 120_000, 3, 1
+    stage = C.c_void_p()
+    capi.check(L.cb200_host_stage_create(C.byref(o), C.byref(stage)))
+    L.cb200_host_stage_destroy(stage)
+    o.narrow_indices = 2
+    assert L.cb200_host_stage_create(C.byref(o), C.byref(stage)) == capi.INVALID_ARGUMENT
 
 
 @pytest.mark.parametrize("bits,policy", [(8, 1), (4, 2), (2, 1), (1, 2)])
