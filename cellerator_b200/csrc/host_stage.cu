@@ -206,6 +206,7 @@ struct cb200_host_stage {
     std::uint64_t device_bytes = 0;
     std::uint64_t workspace_bytes = 0;
     narrow_pool *pool = nullptr; // non-null: gene indices may travel as 16-bit words
+    int narrow_pause = 0;        // calls that still copy 32-bit indices after one in which the host narrowed too slowly
 };
 
 namespace {
@@ -375,6 +376,11 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
     // still beats the 32-bit copy (5 bytes at the link's rate).  The first narrowed chunk of the call decides.
     bool narrow = s->pool != nullptr;
     constexpr double kNarrowMinRate = 12.0e9;
+    constexpr int kNarrowPauseCalls = 8; // a call that found the host too slow is not the only one to pay for finding out
+    if (narrow && o.narrow_indices == 0 && s->narrow_pause > 0) {
+        --s->narrow_pause;
+        narrow = false;
+    }
     for (std::size_t c = 0; c + 1 < bounds.size(); ++c) {
         chunk_buffer &b = s->ring[c % static_cast<std::size_t>(buffers)];
         const std::int64_t r0 = bounds[c], r1 = bounds[c + 1], rows = r1 - r0;
@@ -395,7 +401,10 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
                 const auto t0 = std::chrono::steady_clock::now();
                 narrowed = s->pool->run(x->col_idx + n0, b.narrow_host, nnz, static_cast<std::uint32_t>(o.k));
                 const double seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-                if (o.narrow_indices == 0 && static_cast<double>(nnz) < kNarrowMinRate * seconds) narrow = false; // too slow here: 32-bit copies from the next chunk on
+                if (o.narrow_indices == 0 && static_cast<double>(nnz) < kNarrowMinRate * seconds) {
+                    narrow = false; // too slow here: 32-bit copies from the next chunk on, and for the next calls
+                    s->narrow_pause = kNarrowPauseCalls;
+                }
             }
             if (narrowed) {
                 const std::uint64_t bytes = (static_cast<std::uint64_t>(nnz) * 2u + 15u) & ~static_cast<std::uint64_t>(15u);
