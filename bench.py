@@ -625,6 +625,8 @@ def run_ours(args):
         counts = np.diff(x.host_row_ptr[:: so.max_chunk_rows].tolist() + [int(x.host_row_ptr[-1])])
         so.max_chunk_nnz = int(counts.max()) + 1
         so.chunk_buffers = 3
+        # the ranks of a box share its cores: each stage narrows gene indices with its share of them
+        so.host_threads = max(1, len(os.sched_getaffinity(0)) // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))))
         stage = C.c_void_p()
         capi.check(L.cb200_host_stage_create(C.byref(so), C.byref(stage)))
         hd = capi.header(capi.QCsr())

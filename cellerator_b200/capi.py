@@ -198,7 +198,7 @@ class HostStageOptions(C.Structure):
     _fields_ = [("version", C.c_uint32), ("size", C.c_size_t), ("device", C.c_int32), ("k", C.c_int64), ("n", C.c_int64),
                 ("bits", C.c_int32), ("policy", C.c_int32), ("dense_dtype", C.c_int32), ("multiply", C.c_int32),
                 ("max_chunk_rows", C.c_int64), ("max_chunk_nnz", C.c_int64), ("chunk_buffers", C.c_int32),
-                ("narrow_indices", C.c_int32)]
+                ("narrow_indices", C.c_int32), ("host_threads", C.c_int32)]
 
 
 class AllocationAccounting(C.Structure):

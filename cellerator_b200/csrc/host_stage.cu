@@ -301,10 +301,10 @@ cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_ho
             if (err == cudaSuccess) err = cudaEventCreateWithFlags(e, cudaEventDisableTiming);
     }
     // 16-bit indices on the link: needs every gene index to fit, and host threads to narrow with
-    const int host_threads = std::min(usable_host_threads(), 16);
-    if (o->narrow_indices < -1 || o->narrow_indices > 1) {
+    const int host_threads = std::min(o->host_threads > 0 ? o->host_threads : usable_host_threads(), 16);
+    if (o->narrow_indices < -1 || o->narrow_indices > 1 || o->host_threads < 0) {
         cb200_host_stage_destroy(s);
-        return fail(CB200_STATUS_INVALID_ARGUMENT, "narrow_indices is -1, 0 or 1");
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "narrow_indices is -1, 0 or 1, host_threads is not negative");
     }
     if (err == cudaSuccess && o->k <= 65536 && (o->narrow_indices == 1 || (o->narrow_indices == 0 && host_threads >= 4))) {
         for (int b = 0; b < o->chunk_buffers && err == cudaSuccess; ++b) {
@@ -372,10 +372,10 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
 
     const int buffers = o.chunk_buffers;
     // Narrow indices pay when the host narrows an entry faster than the link moves the two bytes saved: with the
-    // link at ~50 GB/s that is 25 G entries/s for a tie with the link itself, and anything above 10.6 G entries/s
+    // link at ~53 GB/s that is 17.7 G entries/s for a tie with the link itself, and anything above 10.6 G entries/s
     // still beats the 32-bit copy (5 bytes at the link's rate).  The first narrowed chunk of the call decides.
     bool narrow = s->pool != nullptr;
-    constexpr double kNarrowMinRate = 12.0e9;
+    constexpr double kNarrowMinRate = 11.5e9;
     constexpr int kNarrowPauseCalls = 8; // a call that found the host too slow is not the only one to pay for finding out
     if (narrow && o.narrow_indices == 0 && s->narrow_pause > 0) {
         --s->narrow_pause;

@@ -895,6 +895,9 @@ typedef struct cb200_host_stage_options {
      * usable, and within a call only while the host narrows faster than the link would move the bytes saved (the first
      * narrowed chunk of a call is timed); 1 = wherever k allows it; -1 = never. */
     int32_t narrow_indices;
+    /* Host threads that narrow (the calling thread included): 0 = the cores this process may run on, at most 16.  A
+     * process that shares its cores with other ranks passes its share. */
+    int32_t host_threads;
 } cb200_host_stage_options;
 
 cb200_status cb200_host_stage_create(const cb200_host_stage_options *options, cb200_host_stage **out);
