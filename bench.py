@@ -653,8 +653,8 @@ def run_ours(args):
         e_ms = float(e_ms.item())
         e2e = {"value": total_units / (e_ms * 1e-3) / 1e9, "unit": "Gnnz/s", "h2d_bytes_per_step": int(h2d.value),
                "d2h_bytes_per_step": int(d2h.value), "ms_per_step": e_ms, "steps": e_steps,
-               "call": "cb200_host_forward (C ABI, pinned host buffers, 3 chunk buffers of %d rows; gene indices cross as 16-bit words "
-                       "while the host narrows them fast enough)" % so.max_chunk_rows,
+               "call": "cb200_host_forward (C ABI, pinned host buffers, 3 chunk buffers of %d rows; gene indices cross as gap bytes "
+                       "while the host rewrites them fast enough)" % so.max_chunk_rows,
                "h2d_bytes_per_entry": float(h2d.value) / max(1.0, float(x.nnz)),
                "schedule": "gene_tiled (codes read at launch)", "stage_device_bytes": int(L.cb200_host_stage_device_bytes(stage)),
                "aggregate_h2d_gbs": world * h2d.value / (e_ms * 1e-3) / 1e9}

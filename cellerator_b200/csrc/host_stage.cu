@@ -11,13 +11,18 @@
 // kernels are the CSR schedules that read codes and indices at launch (gene-tiled where the shape allows,
 // else warp per row): the values arrive with the call, so nothing prepared from them can be used.
 //
-// The call is bound by the host -> device link (5 bytes per stored entry: a code and a 32-bit gene index), so where
-// every gene index fits 16 bits (k <= 65,536) the indices travel as 16-bit words: a small pool of host threads narrows
-// a chunk's indices into a pinned staging buffer while the previous chunk is on the link, and a kernel widens them
-// again on the device (3 bytes per entry on the link).  The first chunk of a call times the narrowing; if the host
-// cannot narrow faster than the link moves the two bytes saved (few cores, or many processes sharing them), the
-// rest of the call copies the 32-bit indices as they are.  A chunk that holds an index outside [0, k) is also copied
-// as it is (the kernels leave such entries out; narrowed they would alias another gene).
+// The call is bound by the host -> device link (5 bytes per stored entry: a code and a 32-bit gene index), so the
+// indices travel in a shorter form: a small pool of host threads rewrites a chunk's indices into a pinned staging
+// buffer while the previous chunk is on the link, and a kernel restores the 32-bit indices on the device.
+//   gaps (any k): one byte per entry, gene - previous gene of the row - 1 (the row's first entry: its gene); an entry
+//     whose gap does not fit (255 or more, or a row whose genes do not ascend) is sent as the byte 255 plus a record
+//     {position, gene} in a short list.  2 bytes per entry on the link.  A warp per row restores the genes with a
+//     prefix sum.
+//   16-bit words (k <= 65,536): 3 bytes per entry on the link.  A chunk that holds an index outside [0, k) is copied as
+//     it is (the kernels leave such entries out; narrowed they would alias another gene).
+// The first rewritten chunk of a call is timed; if the host cannot rewrite faster than the link would move the bytes
+// saved (few cores, or many processes sharing them), the rest of the call copies the 32-bit indices as they are, and
+// so do the next few calls.
 #include "kernels.cuh"
 
 #include <algorithm>
@@ -52,6 +57,92 @@ __global__ void __launch_bounds__(256) widen_indices_kernel(const uint4 *narrow,
     const uint4 v = narrow[i];
     wide[2 * i] = make_int4(static_cast<int>(v.x & 0xffffu), static_cast<int>(v.x >> 16), static_cast<int>(v.y & 0xffffu), static_cast<int>(v.y >> 16));
     wide[2 * i + 1] = make_int4(static_cast<int>(v.z & 0xffffu), static_cast<int>(v.z >> 16), static_cast<int>(v.w & 0xffffu), static_cast<int>(v.w >> 16));
+}
+
+// Gap bytes -> 32-bit gene indices, a warp per row: gene = previous gene + gap + 1, the row's first gap counted from
+// -1.  The byte 255 marks an entry whose gene is in `exceptions` ({position in the chunk, gene}, ascending positions).
+__global__ void __launch_bounds__(256) gaps_to_indices_kernel(const std::uint8_t *gaps, const std::int64_t *row_ptr, std::int64_t rows,
+                                                              const int2 *exceptions, int exception_count, std::int32_t *col_idx) {
+    const int lane = threadIdx.x & 31;
+    const std::int64_t r = static_cast<std::int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return; // warp-uniform
+    const std::int64_t begin = row_ptr[r], end = row_ptr[r + 1];
+    int carry = -1;
+    for (std::int64_t base = begin; base < end; base += 32) {
+        const std::int64_t i = base + lane;
+        const unsigned byte = i < end ? gaps[i] : 0u;
+        const bool marked = i < end && byte == 255u;
+        int sum = i < end && !marked ? static_cast<int>(byte) + 1 : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, sum, d);
+            if (lane >= d) sum += up;
+        }
+        int gene = carry + sum;
+        unsigned todo = __ballot_sync(0xffffffffu, marked);
+        while (todo != 0u) { // rare: the marked entry's gene comes from the list, and the entries behind it count on from there
+            const int m = __ffs(static_cast<int>(todo)) - 1;
+            todo &= todo - 1u;
+            const int position = static_cast<int>(base - 0) + m; // positions are chunk-local, like row_ptr after its rebase
+            int lo = 0, hi = exception_count - 1, found = 0;
+            while (lo <= hi) {
+                const int mid = (lo + hi) >> 1;
+                const int at = exceptions[mid].x;
+                if (at == position) { found = exceptions[mid].y; break; }
+                if (at < position) lo = mid + 1;
+                else hi = mid - 1;
+            }
+            const int shift = found - __shfl_sync(0xffffffffu, gene, m);
+            if (lane >= m) gene += shift;
+        }
+        if (i < end) col_idx[i] = gene;
+        carry = __shfl_sync(0xffffffffu, gene, 31);
+    }
+}
+
+// One row's genes -> gap bytes at out[0..len); an entry that needs it is appended to the job's exception list through
+// `except(position in the row, gene)`.
+template<typename Except>
+inline void gaps_of_row_scalar(const std::int32_t *genes, std::int64_t from, std::int64_t to, std::uint8_t *out, Except &&except) {
+    for (std::int64_t i = from; i < to; ++i) {
+        const std::int64_t gap = static_cast<std::int64_t>(genes[i]) - (i == 0 ? -1 : static_cast<std::int64_t>(genes[i - 1])) - 1;
+        if (gap < 0 || gap >= 255) {
+            out[i] = 255u;
+            except(i, genes[i]);
+        } else {
+            out[i] = static_cast<std::uint8_t>(gap);
+        }
+    }
+}
+template<typename Except>
+__attribute__((target("avx2"))) inline void gaps_of_row_avx2(const std::int32_t *genes, std::int64_t len, std::uint8_t *out, Except &&except) {
+    if (len <= 0) return;
+    // entries up to the first 32-byte boundary of the output one by one (at least the row's first, which has no
+    // predecessor): the vector loop then writes whole aligned lines around the cache, which the copy engine reads next
+    std::int64_t i = std::min<std::int64_t>(len, 1 + static_cast<std::int64_t>((32u - ((reinterpret_cast<std::uintptr_t>(out) + 1u) & 31u)) & 31u));
+    gaps_of_row_scalar(genes, 0, i, out, except);
+    const __m256i one = _mm256_set1_epi32(1), top = _mm256_set1_epi32(254);
+    const __m256i order = _mm256_setr_epi32(0, 4, 1, 5, 2, 6, 3, 7);
+    for (; i + 32 <= len; i += 32) {
+        __m256i d[4];
+        __m256i over = _mm256_setzero_si256();
+#pragma GCC unroll 4
+        for (int j = 0; j < 4; ++j) {
+            const __m256i a = _mm256_loadu_si256(reinterpret_cast<const __m256i *>(genes + i + 8 * j));
+            const __m256i b = _mm256_loadu_si256(reinterpret_cast<const __m256i *>(genes + i + 8 * j - 1));
+            d[j] = _mm256_sub_epi32(_mm256_sub_epi32(a, b), one);
+            over = _mm256_or_si256(over, _mm256_xor_si256(_mm256_max_epu32(d[j], top), top)); // non-zero where a gap, as unsigned, exceeds 254
+        }
+        if (!_mm256_testz_si256(over, over)) {
+            gaps_of_row_scalar(genes, i, i + 32, out, except);
+            continue;
+        }
+        // 32-bit -> 16-bit -> 8-bit packs interleave the 128-bit halves: one permutation of 32-bit words puts them back
+        const __m256i bytes = _mm256_packus_epi16(_mm256_packus_epi32(d[0], d[1]), _mm256_packus_epi32(d[2], d[3]));
+        _mm256_stream_si256(reinterpret_cast<__m256i *>(out + i), _mm256_permutevar8x32_epi32(bytes, order));
+    }
+    _mm_sfence();
+    gaps_of_row_scalar(genes, i, len, out, except);
 }
 
 // Narrows src[0..n) to 16 bits; returns false if an index lies outside [0, k) (dst is then not to be used).
@@ -92,9 +183,11 @@ bool narrow_block(const std::int32_t *src, std::uint16_t *dst, std::int64_t n, s
     return outside == 0u;
 }
 
-// A few host threads that narrow one chunk at a time, in blocks of kNarrowBlock entries claimed with an atomic counter;
-// the calling thread takes blocks too and returns when every block is done.
+// A few host threads that rewrite one chunk's indices at a time, in blocks claimed with an atomic counter (kNarrowBlock
+// entries of the 16-bit form, kGapRows rows of the gap form); the calling thread takes blocks too and returns when every
+// block is done.
 constexpr std::int64_t kNarrowBlock = 1 << 18;
+constexpr std::int64_t kGapRows = 64;
 struct narrow_pool {
     std::vector<std::thread> workers;
     std::mutex m;
@@ -110,14 +203,39 @@ struct narrow_pool {
     std::atomic<std::int64_t> next{0};
     std::atomic<std::int64_t> blocks_left{0};
     std::atomic<int> all_inside{1};
+    // the gap form's job: rows [0, rows) of the chunk, row_ptr with the caller's absolute offsets (first = row_ptr[0])
+    bool gaps = false;
+    const std::int64_t *row_ptr = nullptr;
+    std::int64_t rows = 0;
+    std::uint8_t *dst8 = nullptr;
+    // exception records per block of rows: a block is rewritten by one thread, row after row, so its records ascend by
+    // position, and the blocks' lists joined in block order are the chunk's list in ascending order
+    std::vector<std::vector<int2>> block_exceptions;
 
+    void gap_rows(std::int64_t block, std::int64_t r0, std::int64_t r1) {
+        static const bool avx2 = __builtin_cpu_supports("avx2") != 0;
+        const std::int64_t first = row_ptr[0];
+        std::vector<int2> &list = block_exceptions[static_cast<std::size_t>(block)];
+        for (std::int64_t r = r0; r < r1; ++r) {
+            const std::int64_t at = row_ptr[r] - first, len = row_ptr[r + 1] - row_ptr[r];
+            auto except = [&](std::int64_t i, std::int32_t gene) { list.push_back(make_int2(static_cast<int>(at + i), gene)); };
+            if (avx2) gaps_of_row_avx2(src + at, len, dst8 + at, except);
+            else gaps_of_row_scalar(src + at, 0, len, dst8 + at, except);
+        }
+    }
     void work() {
         for (;;) {
             const std::int64_t b = next.fetch_add(1, std::memory_order_relaxed);
-            const std::int64_t lo = b * kNarrowBlock;
-            if (lo >= n) return;
-            const std::int64_t len = std::min<std::int64_t>(kNarrowBlock, n - lo);
-            if (!narrow_block(src + lo, dst + lo, len, k)) all_inside.store(0, std::memory_order_relaxed);
+            if (gaps) {
+                const std::int64_t r0 = b * kGapRows;
+                if (r0 >= rows) return;
+                gap_rows(b, r0, std::min(rows, r0 + kGapRows));
+            } else {
+                const std::int64_t lo = b * kNarrowBlock;
+                if (lo >= n) return;
+                const std::int64_t len = std::min<std::int64_t>(kNarrowBlock, n - lo);
+                if (!narrow_block(src + lo, dst + lo, len, k)) all_inside.store(0, std::memory_order_relaxed);
+            }
             if (blocks_left.fetch_sub(1, std::memory_order_acq_rel) == 1) {
                 std::lock_guard<std::mutex> lock(m);
                 done.notify_all();
@@ -145,22 +263,50 @@ struct narrow_pool {
     void start(int threads) {
         for (int i = 0; i < threads; ++i) workers.emplace_back([this] { loop(); });
     }
-    bool run(const std::int32_t *from, std::uint16_t *to, std::int64_t count, std::uint32_t genes) {
-        if (count <= 0) return true;
+    void run_job(std::int64_t blocks) {
         {
             std::unique_lock<std::mutex> lock(m);
-            done.wait(lock, [&] { return active == 0; }); // a worker still leaving the previous job reads the job's fields
-            src = from; dst = to; n = count; k = genes;
             next.store(0, std::memory_order_relaxed);
-            blocks_left.store((count + kNarrowBlock - 1) / kNarrowBlock, std::memory_order_relaxed);
-            all_inside.store(1, std::memory_order_relaxed);
+            blocks_left.store(blocks, std::memory_order_relaxed);
             ++generation;
         }
         wake.notify_all();
         work();
         std::unique_lock<std::mutex> lock(m);
         done.wait(lock, [&] { return blocks_left.load(std::memory_order_acquire) <= 0; });
+    }
+    void idle() { // a worker still leaving the previous job reads the job's fields: they change only when none is inside
+        std::unique_lock<std::mutex> lock(m);
+        done.wait(lock, [&] { return active == 0; });
+    }
+    // 16-bit words; false: an index outside [0, genes)
+    bool run(const std::int32_t *from, std::uint16_t *to, std::int64_t count, std::uint32_t genes) {
+        if (count <= 0) return true;
+        idle();
+        gaps = false; src = from; dst = to; n = count; k = genes;
+        all_inside.store(1, std::memory_order_relaxed);
+        run_job((count + kNarrowBlock - 1) / kNarrowBlock);
         return all_inside.load(std::memory_order_relaxed) != 0;
+    }
+    // gap bytes of the chunk's rows (ptr = the chunk's row pointers, absolute; from = the chunk's first index); returns the
+    // number of exception records, sorted by position, or -1 if the list has no room for them
+    int run_gaps(const std::int32_t *from, const std::int64_t *ptr, std::int64_t row_count, std::uint8_t *to, int2 *list, int room) {
+        if (row_count <= 0) return 0;
+        idle();
+        const std::int64_t blocks = (row_count + kGapRows - 1) / kGapRows;
+        gaps = true; src = from; row_ptr = ptr; rows = row_count; dst8 = to;
+        if (block_exceptions.size() < static_cast<std::size_t>(blocks)) block_exceptions.resize(static_cast<std::size_t>(blocks));
+        for (std::int64_t b = 0; b < blocks; ++b) block_exceptions[static_cast<std::size_t>(b)].clear();
+        run_job(blocks);
+        std::size_t count = 0;
+        for (std::int64_t b = 0; b < blocks; ++b) count += block_exceptions[static_cast<std::size_t>(b)].size();
+        if (count > static_cast<std::size_t>(room)) return -1;
+        for (std::int64_t b = 0; b < blocks; ++b) {
+            const std::vector<int2> &part = block_exceptions[static_cast<std::size_t>(b)];
+            if (!part.empty()) std::memcpy(list, part.data(), part.size() * sizeof(int2));
+            list += part.size();
+        }
+        return static_cast<int>(count);
     }
     ~narrow_pool() {
         {
@@ -183,8 +329,10 @@ struct chunk_buffer {
     std::int64_t *row_ptr = nullptr;
     std::int64_t *packed_row_ptr = nullptr; // 4-bit codes only
     std::int32_t *col_idx = nullptr;
-    std::uint16_t *narrow_idx = nullptr;     // device: the chunk's 16-bit indices as they arrive (narrow path only)
-    std::uint16_t *narrow_host = nullptr;    // pinned host staging of the same
+    unsigned char *narrow_idx = nullptr;     // device: the chunk's gap bytes or 16-bit indices as they arrive
+    unsigned char *narrow_host = nullptr;    // pinned host staging of the same
+    int2 *exceptions = nullptr;              // device: {position, gene} of the gap form's entries that do not fit a byte
+    int2 *exceptions_host = nullptr;         // pinned host staging of the same
     std::uint8_t *packed = nullptr;
     float *row_offsets = nullptr;           // row-offset policy only
     float *y = nullptr;
@@ -205,7 +353,9 @@ struct cb200_host_stage {
     chunk_buffer ring[kMaxBuffers];
     std::uint64_t device_bytes = 0;
     std::uint64_t workspace_bytes = 0;
-    narrow_pool *pool = nullptr; // non-null: gene indices may travel as 16-bit words
+    narrow_pool *pool = nullptr; // non-null: gene indices may travel in a shorter form
+    bool words16 = false;        // the shorter form is 16-bit words (else gap bytes)
+    int exception_room = 0;      // records the exception lists hold
     int narrow_pause = 0;        // calls that still copy 32-bit indices after one in which the host narrowed too slowly
 };
 
@@ -228,8 +378,9 @@ void cb200_host_stage_destroy(cb200_host_stage *s) {
     for (cudaStream_t st : {s->h2d, s->compute, s->d2h})
         if (st != nullptr) cudaStreamSynchronize(st);
     for (chunk_buffer &b : s->ring) {
-        cudaFree(b.row_ptr); cudaFree(b.packed_row_ptr); cudaFree(b.col_idx); cudaFree(b.packed); cudaFree(b.narrow_idx);
+        cudaFree(b.row_ptr); cudaFree(b.packed_row_ptr); cudaFree(b.col_idx); cudaFree(b.packed); cudaFree(b.narrow_idx); cudaFree(b.exceptions);
         if (b.narrow_host != nullptr) cudaFreeHost(b.narrow_host);
+        if (b.exceptions_host != nullptr) cudaFreeHost(b.exceptions_host);
         cudaFree(b.row_offsets); cudaFree(b.y); cudaFree(b.workspace);
         for (cudaEvent_t e : {b.copied_in, b.computed, b.copied_out})
             if (e != nullptr) cudaEventDestroy(e);
@@ -300,21 +451,31 @@ cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_ho
         for (cudaEvent_t *e : {&c.copied_in, &c.computed, &c.copied_out})
             if (err == cudaSuccess) err = cudaEventCreateWithFlags(e, cudaEventDisableTiming);
     }
-    // 16-bit indices on the link: needs every gene index to fit, and host threads to narrow with
+    // a shorter form of the gene indices on the link: needs host threads to rewrite them with
     const int host_threads = std::min(o->host_threads > 0 ? o->host_threads : usable_host_threads(), 16);
-    if (o->narrow_indices < -1 || o->narrow_indices > 1 || o->host_threads < 0) {
+    if (o->narrow_indices < -1 || o->narrow_indices > 2 || o->host_threads < 0) {
         cb200_host_stage_destroy(s);
-        return fail(CB200_STATUS_INVALID_ARGUMENT, "narrow_indices is -1, 0 or 1, host_threads is not negative");
+        return fail(CB200_STATUS_INVALID_ARGUMENT, "narrow_indices is -1, 0, 1 or 2, host_threads is not negative");
     }
-    if (err == cudaSuccess && o->k <= 65536 && (o->narrow_indices == 1 || (o->narrow_indices == 0 && host_threads >= 4))) {
+    const bool want_words = o->narrow_indices == 1 && o->k <= 65536;
+    const bool want_gaps = o->narrow_indices == 2 || (o->narrow_indices == 0 && host_threads >= 4);
+    if (err == cudaSuccess && (want_words || want_gaps) && o->max_chunk_nnz < 0x7fffff00ll) {
+        s->words16 = want_words;
+        s->exception_room = static_cast<int>(std::max<std::int64_t>(4096, o->max_chunk_nnz / 128));
+        const std::uint64_t bytes = (static_cast<std::uint64_t>(o->max_chunk_nnz) + 64u) * (want_words ? 2u : 1u);
         for (int b = 0; b < o->chunk_buffers && err == cudaSuccess; ++b) {
             chunk_buffer &c = s->ring[b];
-            err = device_alloc(&c.narrow_idx, o->max_chunk_nnz + 8, &s->device_bytes);
-            if (err == cudaSuccess) err = cudaHostAlloc(reinterpret_cast<void **>(&c.narrow_host), static_cast<std::size_t>(o->max_chunk_nnz + 8) * 2u, cudaHostAllocDefault);
+            err = device_alloc(&c.narrow_idx, bytes, &s->device_bytes);
+            if (err == cudaSuccess) err = cudaHostAlloc(reinterpret_cast<void **>(&c.narrow_host), bytes, cudaHostAllocDefault);
+            if (err == cudaSuccess && !want_words) {
+                err = device_alloc(&c.exceptions, static_cast<std::uint64_t>(s->exception_room), &s->device_bytes);
+                if (err == cudaSuccess)
+                    err = cudaHostAlloc(reinterpret_cast<void **>(&c.exceptions_host), static_cast<std::size_t>(s->exception_room) * sizeof(int2), cudaHostAllocDefault);
+            }
         }
         if (err == cudaSuccess) {
             s->pool = new (std::nothrow) narrow_pool{};
-            if (s->pool != nullptr) s->pool->start(std::max(host_threads - 1, 0)); // the calling thread narrows too
+            if (s->pool != nullptr) s->pool->start(std::max(host_threads - 1, 0)); // the calling thread rewrites too
         }
     }
     if (err != cudaSuccess) {
@@ -375,6 +536,8 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
     // link at ~53 GB/s that is 17.7 G entries/s for a tie with the link itself, and anything above 10.6 G entries/s
     // still beats the 32-bit copy (5 bytes at the link's rate).  The first narrowed chunk of the call decides.
     bool narrow = s->pool != nullptr;
+    int timed_chunks = 0;        // rewritten chunks of this call whose rate has been looked at (the first starts the threads cold)
+    double best_rate = 0.0;
     constexpr double kNarrowMinRate = 11.5e9;
     constexpr int kNarrowPauseCalls = 8; // a call that found the host too slow is not the only one to pay for finding out
     if (narrow && o.narrow_indices == 0 && s->narrow_pause > 0) {
@@ -394,22 +557,37 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
             in_bytes += static_cast<std::uint64_t>(rows + 1) * 8u;
         }
         bool narrowed = false;
+        int exception_count = 0;
         if (nnz > 0) {
             if (narrow) {
                 // the staging buffer's previous copy (buffers chunks ago) has left it
                 if (c >= static_cast<std::size_t>(buffers)) CB200_CUDA_OK(cudaEventSynchronize(b.copied_in));
                 const auto t0 = std::chrono::steady_clock::now();
-                narrowed = s->pool->run(x->col_idx + n0, b.narrow_host, nnz, static_cast<std::uint32_t>(o.k));
+                if (s->words16) {
+                    narrowed = s->pool->run(x->col_idx + n0, reinterpret_cast<std::uint16_t *>(b.narrow_host), nnz, static_cast<std::uint32_t>(o.k));
+                } else {
+                    exception_count = s->pool->run_gaps(x->col_idx + n0, rp + r0, rows, b.narrow_host, b.exceptions_host, s->exception_room);
+                    // worth it while the list is short: with one record per eight entries the form costs as much as 16-bit words
+                    narrowed = exception_count >= 0 && static_cast<std::int64_t>(exception_count) * 8 <= nnz;
+                    if (!narrowed) exception_count = 0;
+                }
                 const double seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-                if (o.narrow_indices == 0 && static_cast<double>(nnz) < kNarrowMinRate * seconds) {
-                    narrow = false; // too slow here: 32-bit copies from the next chunk on, and for the next calls
+                best_rate = std::max(best_rate, static_cast<double>(nnz) / std::max(seconds, 1e-9));
+                ++timed_chunks;
+                const bool last_chunk = c + 2 == bounds.size();
+                if (o.narrow_indices == 0 && (!narrowed || ((timed_chunks == 2 || last_chunk) && best_rate < kNarrowMinRate))) {
+                    narrow = false; // too slow here (or rows whose genes do not ascend): 32-bit copies from the next chunk on, and for the next calls
                     s->narrow_pause = kNarrowPauseCalls;
                 }
             }
             if (narrowed) {
-                const std::uint64_t bytes = (static_cast<std::uint64_t>(nnz) * 2u + 15u) & ~static_cast<std::uint64_t>(15u);
+                const std::uint64_t bytes = (static_cast<std::uint64_t>(nnz) * (s->words16 ? 2u : 1u) + 15u) & ~static_cast<std::uint64_t>(15u);
                 CB200_CUDA_OK(cudaMemcpyAsync(b.narrow_idx, b.narrow_host, bytes, cudaMemcpyHostToDevice, s->h2d));
                 in_bytes += bytes;
+                if (exception_count > 0) {
+                    CB200_CUDA_OK(cudaMemcpyAsync(b.exceptions, b.exceptions_host, static_cast<std::uint64_t>(exception_count) * sizeof(int2), cudaMemcpyHostToDevice, s->h2d));
+                    in_bytes += static_cast<std::uint64_t>(exception_count) * sizeof(int2);
+                }
             } else {
                 CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx, x->col_idx + n0, static_cast<std::uint64_t>(nnz) * 4u, cudaMemcpyHostToDevice, s->h2d));
                 in_bytes += static_cast<std::uint64_t>(nnz) * 4u;
@@ -429,10 +607,14 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
         rebase_kernel<<<grid, 256, 0, s->compute>>>(b.row_ptr, rows + 1, n0);
         if (o.bits == 4) rebase_kernel<<<grid, 256, 0, s->compute>>>(b.packed_row_ptr, rows + 1, p0);
         count_launch(o.bits == 4 ? 2 : 1);
-        if (narrowed) {
+        if (narrowed && s->words16) {
             const std::int64_t eights = (nnz + 7) / 8;
             widen_indices_kernel<<<static_cast<unsigned>((eights + 255) / 256), 256, 0, s->compute>>>(
                 reinterpret_cast<const uint4 *>(b.narrow_idx), reinterpret_cast<int4 *>(b.col_idx), eights);
+            count_launch();
+        } else if (narrowed) { // after the rebase: the kernel reads the chunk's own row pointers
+            gaps_to_indices_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s->compute>>>(b.narrow_idx, b.row_ptr, rows, b.exceptions, exception_count,
+                                                                                                b.col_idx);
             count_launch();
         }
         CB200_CUDA_OK(cudaGetLastError());

@@ -890,10 +890,16 @@ typedef struct cb200_host_stage_options {
     int64_t max_chunk_rows;   /* rows one device chunk buffer holds */
     int64_t max_chunk_nnz;    /* stored entries one device chunk buffer holds */
     int32_t chunk_buffers;    /* chunks in flight, 2..4 */
-    /* Gene indices as 16-bit words on the host -> device link (k <= 65,536 only; host threads narrow them into a pinned
-     * staging buffer, a kernel widens them on the device): 0 = where k allows it and at least four host threads are
-     * usable, and within a call only while the host narrows faster than the link would move the bytes saved (the first
-     * narrowed chunk of a call is timed); 1 = wherever k allows it; -1 = never. */
+    /* A shorter form of the gene indices on the host -> device link (host threads rewrite a chunk's indices into a pinned
+     * staging buffer, a kernel restores them on the device):
+     *    0 = gap bytes (see 2) where at least four host threads are usable, and within a call only while the host
+     *        rewrites faster than the link would move the bytes saved (the first rewritten chunk of a call is timed;
+     *        a call that found the host too slow also keeps the next few calls on 32-bit indices);
+     *    1 = 16-bit words (k <= 65,536 only; 32-bit elsewhere): 3 bytes per entry on the link instead of 5;
+     *    2 = gap bytes, any k: one byte per entry (gene - previous gene of the row - 1), with a short list of
+     *        {position, gene} for the entries whose gap does not fit: 2 bytes per entry on the link.  A chunk with more
+     *        such entries than the list holds (one in 128; rows whose genes do not ascend) goes as 32-bit indices;
+     *   -1 = 32-bit indices as they are. */
     int32_t narrow_indices;
     /* Host threads that narrow (the calling thread included): 0 = the cores this process may run on, at most 16.  A
      * process that shares its cores with other ranks passes its share. */

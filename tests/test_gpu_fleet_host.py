@@ -184,50 +184,93 @@ def test_host_buffer_forward_through_the_chunk_ring(cuda_device, oracle, bits, p
         assert np.array_equal(y_dev.cpu().numpy(), y_host.numpy())
 
 
-@pytest.mark.parametrize("bits", [8, 4])
-def test_host_buffer_forward_with_narrow_and_wide_indices(cuda_device, oracle, bits):
-    """The gene indices cross the link as 16-bit words (narrow_indices = 1), as 32-bit words (-1), or as the stage
-    decides per call (0): the results are bit-identical, and the bytes on the link are what each form needs."""
+def _host_forward_all_forms(cuda_device, c, w_pinned, n, modes, chunk_rows=300, chunk_nnz=120_000):
+    """cb200_host_forward over the same host matrix with each form of the gene indices on the link: {mode: (Y, bytes
+    moved host -> device)}; every stage is called twice (staging buffers and events are reused)."""
     L = capi.lib()
-    rng = np.random.default_rng(70 + bits)
-    rows, cols, n = 2100, 65536, 64                                  # the largest k whose indices fit 16 bits
-    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=700, bits=bits, policy=1))
-    c["col_idx"][-1] = cols - 1 if len(c["col_idx"]) else 0          # (the last row's last gene: the top index)
     keep = []
     xd = _host_desc(c, keep)
-    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
-    w_pinned = w.cpu().contiguous().pin_memory()
-    nnz, results, moved = len(c["col_idx"]), {}, {}
-    for mode in (1, -1, 0):
+    out = {}
+    for mode in modes:
         o = capi.header(capi.HostStageOptions())
-        o.device, o.k, o.n, o.bits, o.policy = cuda_device.index, cols, n, bits, 1
+        o.device, o.k, o.n, o.bits, o.policy = cuda_device.index, c["cols"], n, c["bits"], c["policy"]
         o.dense_dtype = capi.DTYPE_BF16
-        o.max_chunk_rows, o.max_chunk_nnz, o.chunk_buffers, o.narrow_indices = 300, 120_000, 3, mode
+        o.max_chunk_rows, o.max_chunk_nnz, o.chunk_buffers, o.narrow_indices = chunk_rows, chunk_nnz, 3, mode
         stage = C.c_void_p()
         capi.check(L.cb200_host_stage_create(C.byref(o), C.byref(stage)))
         try:
-            y_host = torch.full((rows, n), float("nan")).pin_memory()
+            y_host = torch.full((c["rows"], n), float("nan")).pin_memory()
             h2d = C.c_uint64()
-            for _ in range(2):                                       # staging buffers and events are reused by a second call
+            for _ in range(2):
                 capi.check(L.cb200_host_forward(stage, C.byref(xd), w_pinned.data_ptr(), n, y_host.data_ptr(), n, 1.0, C.byref(h2d), None))
-            results[mode], moved[mode] = y_host.clone(), h2d.value
+            out[mode] = (y_host.clone(), h2d.value)
         finally:
             L.cb200_host_stage_destroy(stage)
-    assert torch.equal(results[1], results[-1]) and torch.equal(results[0], results[-1])
-    assert moved[-1] - moved[1] >= 2 * nnz - 16 * (rows // 300 + 2)     # two bytes per entry saved (16-byte padding per chunk)
-    assert moved[1] <= moved[0] <= moved[-1]
+    return out
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_host_buffer_forward_with_shorter_index_forms(cuda_device, oracle, bits):
+    """The gene indices cross the link as gap bytes (narrow_indices = 2), 16-bit words (1), 32-bit words (-1), or as
+    the stage decides per call (0): the results are bit-identical, and the bytes on the link are what each form needs."""
+    rng = np.random.default_rng(70 + bits)
+    rows, cols, n = 2100, 4100, 64
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=700, bits=bits, policy=1))
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    w_pinned = w.cpu().contiguous().pin_memory()
+    nnz = len(c["col_idx"])
+    got = _host_forward_all_forms(cuda_device, c, w_pinned, n, (2, 1, -1, 0))
+    for mode in (2, 1, 0):
+        assert torch.equal(got[mode][0], got[-1][0])
+    slack = 16 * (rows // 300 + 2)                                       # 16-byte padding per chunk
+    gaps_over = int(np.sum(np.diff(c["col_idx"].astype(np.int64)) - 1 >= 255))   # an upper bound of the listed entries
+    assert got[-1][1] - got[1][1] >= 2 * nnz - slack                      # two bytes per entry saved
+    assert got[-1][1] - got[2][1] >= 3 * nnz - slack - 8 * (gaps_over + rows)   # three, less the list of long gaps
+    assert got[2][1] <= got[0][1] <= got[-1][1]
     ref = oracle.qcsr_forward(bits, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"],
                               w_host, cols)
     l1, _ = row_l1(oracle, c)
-    assert_forward_close(results[1].numpy(), ref, l1, float(np.abs(w_host).max()), bf16=True)
-    # k beyond 16 bits: the stage is made, and copies 32-bit indices
+    assert_forward_close(got[2][0].numpy(), ref, l1, float(np.abs(w_host).max()), bf16=True)
+
+
+@pytest.mark.parametrize("cols,max_nnz,shuffled_rows", [(65536, 700, 0), (20_000, 400, 40), (200_000, 300, 0)])
+def test_host_buffer_forward_gap_bytes_with_long_gaps(cuda_device, oracle, cols, max_nnz, shuffled_rows):
+    """Gap bytes where gaps do not fit a byte: a few per chunk (listed), rows whose genes do not ascend (every descent is
+    listed), and so many that the list overflows and the chunk goes as 32-bit indices.  Always the same bits as the
+    32-bit form."""
+    rng = np.random.default_rng(cols % 1000 + max_nnz)
+    rows, n = 1500, 32
+    c = random_csr(rng, rows=rows, cols=cols, max_nnz=max_nnz, bits=8, policy=1)
+    c["col_idx"][-1] = cols - 1                                           # the top index, in the last row's last entry
+    for r in rng.choice(rows, size=shuffled_rows, replace=False):         # rows in arbitrary gene order
+        lo, hi = int(c["row_ptr"][r]), int(c["row_ptr"][r + 1])
+        order = rng.permutation(hi - lo)
+        c["col_idx"][lo:hi] = c["col_idx"][lo:hi][order]
+        c["values"][lo:hi] = c["values"][lo:hi][order]
+    c = host_pack(oracle, c)
+    w, w_host = dense(rng, cols, n, torch.bfloat16, cuda_device)
+    w_pinned = w.cpu().contiguous().pin_memory()
+    got = _host_forward_all_forms(cuda_device, c, w_pinned, n, (2, -1, 0), chunk_rows=211, chunk_nnz=60_000)
+    assert torch.equal(got[2][0], got[-1][0]) and torch.equal(got[0][0], got[-1][0])
+    assert got[2][1] <= got[-1][1] + 16 * (rows // 211 + 2)
+    if shuffled_rows == 0:      # (the kernels behind the call take a row's genes in ascending order, like the reference's CSR)
+        ref = oracle.qcsr_forward(8, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"], w_host, cols)
+        l1, _ = row_l1(oracle, c)
+        assert_forward_close(got[2][0].numpy(), ref, l1, float(np.abs(w_host).max()), bf16=True)
+
+
+def test_host_stage_refuses_unknown_index_forms(cuda_device):
+    L = capi.lib()
     o = capi.header(capi.HostStageOptions())
-    o.device, o.k, o.n, o.bits, o.policy, o.dense_dtype = cuda_device.index, cols + 1, n, bits, 1, capi.DTYPE_BF16
+    o.device, o.k, o.n, o.bits, o.policy, o.dense_dtype = cuda_device.index, 70_000, 64, 8, 1, capi.DTYPE_BF16
     o.max_chunk_rows, o.max_chunk_nnz, o.chunk_buffers, o.narrow_indices = 300, 120_000, 3, 1
     stage = C.c_void_p()
-    capi.check(L.cb200_host_stage_create(C.byref(o), C.byref(stage)))
+    capi.check(L.cb200_host_stage_create(C.byref(o), C.byref(stage)))        # 16-bit words asked for, k too large: 32-bit copies
     L.cb200_host_stage_destroy(stage)
-    o.narrow_indices = 2
+    for bad in (3, -2):
+        o.narrow_indices = bad
+        assert L.cb200_host_stage_create(C.byref(o), C.byref(stage)) == capi.INVALID_ARGUMENT
+    o.narrow_indices, o.host_threads = 0, -1
     assert L.cb200_host_stage_create(C.byref(o), C.byref(stage)) == capi.INVALID_ARGUMENT
 
 
