@@ -357,6 +357,7 @@ struct cb200_host_stage {
     bool words16 = false;        // the shorter form is 16-bit words (else gap bytes)
     int exception_room = 0;      // records the exception lists hold
     int narrow_pause = 0;        // calls that still copy 32-bit indices after one in which the host narrowed too slowly
+    double rewrite_share = 1.0;  // gap form: share of a chunk's entries the host rewrites (the rest go as 32-bit indices)
 };
 
 namespace {
@@ -532,18 +533,24 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
     CB200_CUDA_OK(cudaStreamWaitEvent(s->compute, s->shared_in, 0));
 
     const int buffers = o.chunk_buffers;
-    // Narrow indices pay when the host narrows an entry faster than the link moves the two bytes saved: with the
-    // link at ~53 GB/s that is 17.7 G entries/s for a tie with the link itself, and anything above 10.6 G entries/s
-    // still beats the 32-bit copy (5 bytes at the link's rate).  The first narrowed chunk of the call decides.
+    // The host rewrites while the link moves: per entry the link carries 2 bytes of a rewritten entry (gap and code) and 5
+    // of one that goes as it is, and the host spends 1 / R on a rewritten one (R = its rewriting rate).  Both are busy
+    // for the same time when the host rewrites the share 5 R / (L + 3 R) of the entries, L = the link's rate, and the rest
+    // of a chunk's rows go as 32-bit indices, enqueued first so that the link has them to move while the host works.  At
+    // R = 19 G entries/s and L = 50 GB/s that is 0.89 of the entries and 21 G entries/s for the call; a host that rewrites
+    // 8 G/s rewrites 0.54 of them for 15 G/s, where 32-bit indices alone give 10.  The better of the first two rewritten
+    // chunks of a call sets the share for the rest of the call and for the next call; a host below kRewriteMinRate (or
+    // rows whose genes do not ascend) sends 32-bit indices for the rest of this call and the next few.
     bool narrow = s->pool != nullptr;
     int timed_chunks = 0;        // rewritten chunks of this call whose rate has been looked at (the first starts the threads cold)
     double best_rate = 0.0;
-    constexpr double kNarrowMinRate = 11.5e9;
+    constexpr double kRewriteMinRate = 3.0e9, kLinkRate = 50.0e9;
     constexpr int kNarrowPauseCalls = 8; // a call that found the host too slow is not the only one to pay for finding out
     if (narrow && o.narrow_indices == 0 && s->narrow_pause > 0) {
         --s->narrow_pause;
         narrow = false;
     }
+    double share = o.narrow_indices == 0 && !s->words16 ? s->rewrite_share : 1.0;
     for (std::size_t c = 0; c + 1 < bounds.size(); ++c) {
         chunk_buffer &b = s->ring[c % static_cast<std::size_t>(buffers)];
         const std::int64_t r0 = bounds[c], r1 = bounds[c + 1], rows = r1 - r0;
@@ -558,30 +565,48 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
         }
         bool narrowed = false;
         int exception_count = 0;
+        std::int64_t head_rows = rows, head_nnz = nnz; // what the host rewrites: the chunk's first rows
         if (nnz > 0) {
-            if (narrow) {
+            if (narrow && share < 1.0) {
+                const std::int64_t target = n0 + static_cast<std::int64_t>(share * static_cast<double>(nnz));
+                head_rows = std::min<std::int64_t>(rows, std::max<std::int64_t>(0, (std::upper_bound(rp + r0, rp + r1 + 1, target) - (rp + r0)) - 1));
+                head_nnz = rp[r0 + head_rows] - n0;
+            }
+            // what needs no work of the host goes first: the codes, and the indices of the rows that are not rewritten
+            CB200_CUDA_OK(cudaMemcpyAsync(b.packed, x->packed_values + p0, static_cast<std::uint64_t>(code_bytes), cudaMemcpyHostToDevice, s->h2d));
+            in_bytes += static_cast<std::uint64_t>(code_bytes);
+            if (narrow && head_nnz < nnz) {
+                CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx + head_nnz, x->col_idx + n0 + head_nnz, static_cast<std::uint64_t>(nnz - head_nnz) * 4u, cudaMemcpyHostToDevice, s->h2d));
+                in_bytes += static_cast<std::uint64_t>(nnz - head_nnz) * 4u;
+            }
+            if (narrow && head_nnz > 0) {
                 // the staging buffer's previous copy (buffers chunks ago) has left it
                 if (c >= static_cast<std::size_t>(buffers)) CB200_CUDA_OK(cudaEventSynchronize(b.copied_in));
                 const auto t0 = std::chrono::steady_clock::now();
                 if (s->words16) {
                     narrowed = s->pool->run(x->col_idx + n0, reinterpret_cast<std::uint16_t *>(b.narrow_host), nnz, static_cast<std::uint32_t>(o.k));
                 } else {
-                    exception_count = s->pool->run_gaps(x->col_idx + n0, rp + r0, rows, b.narrow_host, b.exceptions_host, s->exception_room);
+                    exception_count = s->pool->run_gaps(x->col_idx + n0, rp + r0, head_rows, b.narrow_host, b.exceptions_host, s->exception_room);
                     // worth it while the list is short: with one record per eight entries the form costs as much as 16-bit words
-                    narrowed = exception_count >= 0 && static_cast<std::int64_t>(exception_count) * 8 <= nnz;
+                    narrowed = exception_count >= 0 && static_cast<std::int64_t>(exception_count) * 8 <= head_nnz;
                     if (!narrowed) exception_count = 0;
                 }
                 const double seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-                best_rate = std::max(best_rate, static_cast<double>(nnz) / std::max(seconds, 1e-9));
+                best_rate = std::max(best_rate, static_cast<double>(head_nnz) / std::max(seconds, 1e-9));
                 ++timed_chunks;
                 const bool last_chunk = c + 2 == bounds.size();
-                if (o.narrow_indices == 0 && (!narrowed || ((timed_chunks == 2 || last_chunk) && best_rate < kNarrowMinRate))) {
-                    narrow = false; // too slow here (or rows whose genes do not ascend): 32-bit copies from the next chunk on, and for the next calls
-                    s->narrow_pause = kNarrowPauseCalls;
+                if (o.narrow_indices == 0 && (timed_chunks == 2 || last_chunk || !narrowed)) {
+                    if (!narrowed || best_rate < kRewriteMinRate) {
+                        narrow = false; // 32-bit copies from the next chunk on, and for the next calls
+                        s->narrow_pause = kNarrowPauseCalls;
+                    } else if (!s->words16 && timed_chunks <= 2) {
+                        share = std::min(1.0, std::max(0.25, 5.0 * best_rate / (kLinkRate + 3.0 * best_rate)));
+                        s->rewrite_share = share;
+                    }
                 }
             }
             if (narrowed) {
-                const std::uint64_t bytes = (static_cast<std::uint64_t>(nnz) * (s->words16 ? 2u : 1u) + 15u) & ~static_cast<std::uint64_t>(15u);
+                const std::uint64_t bytes = (static_cast<std::uint64_t>(head_nnz) * (s->words16 ? 2u : 1u) + 15u) & ~static_cast<std::uint64_t>(15u);
                 CB200_CUDA_OK(cudaMemcpyAsync(b.narrow_idx, b.narrow_host, bytes, cudaMemcpyHostToDevice, s->h2d));
                 in_bytes += bytes;
                 if (exception_count > 0) {
@@ -589,11 +614,11 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
                     in_bytes += static_cast<std::uint64_t>(exception_count) * sizeof(int2);
                 }
             } else {
-                CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx, x->col_idx + n0, static_cast<std::uint64_t>(nnz) * 4u, cudaMemcpyHostToDevice, s->h2d));
-                in_bytes += static_cast<std::uint64_t>(nnz) * 4u;
+                // (all of the chunk's indices, or the rows that were to be rewritten and could not be)
+                const std::int64_t plain = narrow || head_nnz < nnz ? head_nnz : nnz;
+                CB200_CUDA_OK(cudaMemcpyAsync(b.col_idx, x->col_idx + n0, static_cast<std::uint64_t>(plain) * 4u, cudaMemcpyHostToDevice, s->h2d));
+                in_bytes += static_cast<std::uint64_t>(plain) * 4u;
             }
-            CB200_CUDA_OK(cudaMemcpyAsync(b.packed, x->packed_values + p0, static_cast<std::uint64_t>(code_bytes), cudaMemcpyHostToDevice, s->h2d));
-            in_bytes += static_cast<std::uint64_t>(code_bytes);
         }
         if (row_policy && x->offsets != nullptr) {
             CB200_CUDA_OK(cudaMemcpyAsync(b.row_offsets, x->offsets + r0, static_cast<std::uint64_t>(rows) * 4u, cudaMemcpyHostToDevice, s->h2d));
@@ -613,8 +638,8 @@ cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const 
                 reinterpret_cast<const uint4 *>(b.narrow_idx), reinterpret_cast<int4 *>(b.col_idx), eights);
             count_launch();
         } else if (narrowed) { // after the rebase: the kernel reads the chunk's own row pointers
-            gaps_to_indices_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s->compute>>>(b.narrow_idx, b.row_ptr, rows, b.exceptions, exception_count,
-                                                                                                b.col_idx);
+            gaps_to_indices_kernel<<<static_cast<unsigned>((head_rows + 7) / 8), 256, 0, s->compute>>>(b.narrow_idx, b.row_ptr, head_rows, b.exceptions,
+                                                                                                     exception_count, b.col_idx);
             count_launch();
         }
         CB200_CUDA_OK(cudaGetLastError());

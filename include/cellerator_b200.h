@@ -892,9 +892,10 @@ typedef struct cb200_host_stage_options {
     int32_t chunk_buffers;    /* chunks in flight, 2..4 */
     /* A shorter form of the gene indices on the host -> device link (host threads rewrite a chunk's indices into a pinned
      * staging buffer, a kernel restores them on the device):
-     *    0 = gap bytes (see 2) where at least four host threads are usable, and within a call only while the host
-     *        rewrites faster than the link would move the bytes saved (the first rewritten chunk of a call is timed;
-     *        a call that found the host too slow also keeps the next few calls on 32-bit indices);
+     *    0 = gap bytes (see 2) where at least four host threads are usable, for the share of each chunk's rows that
+     *        keeps the host and the link busy for the same time (the first rewritten chunks of a call are timed and
+     *        set the share; the other rows go as 32-bit indices; a call that found the host very slow, or genes that
+     *        do not ascend, also keeps the next few calls on 32-bit indices);
      *    1 = 16-bit words (k <= 65,536 only; 32-bit elsewhere): 3 bytes per entry on the link instead of 5;
      *    2 = gap bytes, any k: one byte per entry (gene - previous gene of the row - 1), with a short list of
      *        {position, gene} for the entries whose gap does not fit: 2 bytes per entry on the link.  A chunk with more
