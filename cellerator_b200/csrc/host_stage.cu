@@ -20,9 +20,10 @@
 //     prefix sum.
 //   16-bit words (k <= 65,536): 3 bytes per entry on the link.  A chunk that holds an index outside [0, k) is copied as
 //     it is (the kernels leave such entries out; narrowed they would alias another gene).
-// The first rewritten chunk of a call is timed; if the host cannot rewrite faster than the link would move the bytes
-// saved (few cores, or many processes sharing them), the rest of the call copies the 32-bit indices as they are, and
-// so do the next few calls.
+// In the default mode the host rewrites only the share of a chunk's rows that keeps it and the link busy for the same
+// time (the first rewritten chunks of a call are timed), and the other rows' 32-bit indices are enqueued first; a host
+// that is very slow (few cores, or many processes sharing them) sends 32-bit indices for the rest of the call and the
+// next few calls.
 #include "kernels.cuh"
 
 #include <algorithm>
