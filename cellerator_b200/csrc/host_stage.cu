@@ -478,6 +478,18 @@ cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_ho
         if (err == cudaSuccess) {
             s->pool = new (std::nothrow) narrow_pool{};
             if (s->pool != nullptr) s->pool->start(std::max(host_threads - 1, 0)); // the calling thread rewrites too
+        } else if (o->narrow_indices == 0) {
+            // no room for the staging buffers (pinned host memory, mostly): the stage works without the shorter form
+            cudaGetLastError();
+            err = cudaSuccess;
+            for (int b = 0; b < o->chunk_buffers; ++b) {
+                chunk_buffer &c = s->ring[b];
+                cudaFree(c.narrow_idx); cudaFree(c.exceptions);
+                if (c.narrow_host != nullptr) cudaFreeHost(c.narrow_host);
+                if (c.exceptions_host != nullptr) cudaFreeHost(c.exceptions_host);
+                c.narrow_idx = nullptr; c.exceptions = nullptr; c.narrow_host = nullptr; c.exceptions_host = nullptr;
+            }
+            cudaGetLastError();
         }
     }
     if (err != cudaSuccess) {
