@@ -264,9 +264,14 @@ struct narrow_pool {
     void start(int threads) {
         for (int i = 0; i < threads; ++i) workers.emplace_back([this] { loop(); });
     }
-    void run_job(std::int64_t blocks) {
+    // The job's fields change only under the lock and only while no worker is inside work(): a worker that wakes late
+    // for an earlier job finds that job's counter run out, or this job complete with all its fields.
+    template<typename Setup>
+    void run_job(std::int64_t blocks, Setup &&setup) {
         {
             std::unique_lock<std::mutex> lock(m);
+            done.wait(lock, [&] { return active == 0; });
+            setup();
             next.store(0, std::memory_order_relaxed);
             blocks_left.store(blocks, std::memory_order_relaxed);
             ++generation;
@@ -276,29 +281,25 @@ struct narrow_pool {
         std::unique_lock<std::mutex> lock(m);
         done.wait(lock, [&] { return blocks_left.load(std::memory_order_acquire) <= 0; });
     }
-    void idle() { // a worker still leaving the previous job reads the job's fields: they change only when none is inside
-        std::unique_lock<std::mutex> lock(m);
-        done.wait(lock, [&] { return active == 0; });
-    }
     // 16-bit words; false: an index outside [0, genes)
     bool run(const std::int32_t *from, std::uint16_t *to, std::int64_t count, std::uint32_t genes) {
         if (count <= 0) return true;
-        idle();
-        gaps = false; src = from; dst = to; n = count; k = genes;
-        all_inside.store(1, std::memory_order_relaxed);
-        run_job((count + kNarrowBlock - 1) / kNarrowBlock);
+        run_job((count + kNarrowBlock - 1) / kNarrowBlock, [&] {
+            gaps = false; src = from; dst = to; n = count; k = genes;
+            all_inside.store(1, std::memory_order_relaxed);
+        });
         return all_inside.load(std::memory_order_relaxed) != 0;
     }
     // gap bytes of the chunk's rows (ptr = the chunk's row pointers, absolute; from = the chunk's first index); returns the
     // number of exception records, sorted by position, or -1 if the list has no room for them
     int run_gaps(const std::int32_t *from, const std::int64_t *ptr, std::int64_t row_count, std::uint8_t *to, int2 *list, int room) {
         if (row_count <= 0) return 0;
-        idle();
         const std::int64_t blocks = (row_count + kGapRows - 1) / kGapRows;
-        gaps = true; src = from; row_ptr = ptr; rows = row_count; dst8 = to;
-        if (block_exceptions.size() < static_cast<std::size_t>(blocks)) block_exceptions.resize(static_cast<std::size_t>(blocks));
-        for (std::int64_t b = 0; b < blocks; ++b) block_exceptions[static_cast<std::size_t>(b)].clear();
-        run_job(blocks);
+        run_job(blocks, [&] {
+            gaps = true; src = from; row_ptr = ptr; rows = row_count; dst8 = to;
+            if (block_exceptions.size() < static_cast<std::size_t>(blocks)) block_exceptions.resize(static_cast<std::size_t>(blocks));
+            for (std::int64_t b = 0; b < blocks; ++b) block_exceptions[static_cast<std::size_t>(b)].clear();
+        });
         std::size_t count = 0;
         for (std::int64_t b = 0; b < blocks; ++b) count += block_exceptions[static_cast<std::size_t>(b)].size();
         if (count > static_cast<std::size_t>(room)) return -1;
