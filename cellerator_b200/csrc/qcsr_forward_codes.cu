@@ -19,23 +19,26 @@
 // the accumulators, and the MMA reads its A operand from there; shared-memory bandwidth, which bounds a kernel that
 // stores decoded tiles to shared memory and lets the MMA read them back (16 KB in, 32 KB stored, 32 KB read per
 // half window), is left to the copies and the W operand.
-//   warps 0-7    write Y: thread t owns row t of the group (TMEM lane = row within the 128-row sub-block); the
-//                accumulators (256 columns) are handed back as soon as they are in registers;
+//   warps 0-7    write Y: a warp reads its 32 rows of the group (TMEM lane = row within the 128-row sub-block) 32
+//                columns at a time, turns the block in a 4 KB shared-memory buffer so that 8 lanes write a row's
+//                128 contiguous bytes, and hands the accumulators (256 columns) back as soon as they are in registers;
 //   warps 8-9    one thread each issues the MMAs of one row sub-block: per window eight K = 16 steps, A from tensor
 //                memory (row = lane, two fp16 per 32-bit column), B = the window's slice of W from shared memory;
 //   warp 10      one thread feeds the W ring with bulk async copies (W re-laid per window into the operand
 //                layout, fp16, by a small kernel before this one);
-//   warp 11      one thread feeds the ring of code stages with bulk async copies (16 KB of codes and the half
-//                window's 256 bytes of {scale, zero-point} pairs behind them);
+//   warp 11      one thread feeds the ring of code stages with bulk async copies (16 KB of codes and, behind them, the
+//                half window's 256 bytes of {scale, zero-point} pairs and the word that allows the mask-free decode);
 //   warps 12-27  decode: a warp may write the 32 tensor-memory lanes (warp mod 4), so it owns those rows of both
 //                sub-blocks; the four warps of a lane quarter split a window into its two half windows and each half
 //                into two pairs of 16-gene chunks, so a warp visits one code stage per window (one wait, one
 //                hand-back) and decodes two chunks of it (the stage is stored chunk-major: its 16-byte loads and the
 //                table's broadcast loads run without bank conflicts).  Per pair of codes a byte permute (byte ->
-//                fp16 1024 + byte), a subtraction of 1025 (exact: the code), a fused multiply-add with the genes'
-//                {scale, zero-point} held in registers as fp16 pairs, a compare that gives the "something stored"
-//                mask, an AND; then one 8-column store per row into one of two operand stages (a window each) of
-//                tensor memory.  The stage goes back to the copy engine once its values are in the registers (a vote waits for them).
+//                fp16 1024 + byte), a subtraction of 1264 (exact: the code, or -240 for an empty slot), a fused
+//                multiply-add with the genes' {scale, zero-point} held in registers as fp16 pairs -- with max(0, .)
+//                where the half window's genes allow it (pack_codes_operands_kernel), else followed by a compare that
+//                gives the "something stored" mask and an AND; then one 8-column store per row into one of two operand
+//                stages (a window each) of tensor memory.  The stage goes back to the copy engine behind the last use
+//                of its values and a fence.
 // Tensor memory: columns 0-255 accumulators (2 sub-blocks x N), 256-511 two operand stages of 2 x 64 columns.
 // Every barrier wait is bounded; a role whose wait ran out stops, the loaders wait for their copies in flight and
 // the MMA warp for its MMAs before the CTA frees tensor memory.  A non-zero status word means Y is not valid.
