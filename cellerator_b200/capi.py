@@ -257,6 +257,7 @@ EXPORTED_SYMBOLS = [
     "cb200_fleet_request_scratch", "cb200_fleet_synchronize", "cb200_fleet_partition", "cb200_fleet_run_forward",
     "cb200_fleet_run_transpose", "cb200_fleet_allreduce_sum_f32",
     "cb200_host_stage_create", "cb200_host_stage_destroy", "cb200_host_stage_device_bytes", "cb200_host_forward",
+    "cb200_host_encode_gene_gaps",
     "cb200_test_arm_wait_timeout", "cb200_test_disarm_wait_timeout",
     "cb200_session_reserve_persistent_as", "cb200_session_prepare_stream_libraries", "cb200_session_get_accounting",
     "cb200_session_graph_stable_address", "cb200_session_cache_insert", "cb200_session_cache_find",
@@ -369,6 +370,8 @@ def lib() -> C.CDLL:
         L.cb200_host_stage_destroy.argtypes = [C.c_void_p]
         L.cb200_host_stage_device_bytes.restype = C.c_uint64
         L.cb200_host_stage_device_bytes.argtypes = [C.c_void_p]
+        L.cb200_host_encode_gene_gaps.restype = C.c_int64
+        L.cb200_host_encode_gene_gaps.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]
         L.cb200_host_forward.argtypes = [C.c_void_p, C.POINTER(QCsr), C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                          C.c_float, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         L.cb200_test_arm_wait_timeout.restype = None

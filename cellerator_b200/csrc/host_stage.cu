@@ -504,6 +504,27 @@ cb200_status cb200_host_stage_create(const cb200_host_stage_options *o, cb200_ho
 
 uint64_t cb200_host_stage_device_bytes(const cb200_host_stage *s) { return s != nullptr ? s->device_bytes : 0u; }
 
+int64_t cb200_host_encode_gene_gaps(const int32_t *col_idx, const int64_t *row_ptr, int64_t rows, uint8_t *gaps, int32_t *exception_positions,
+                                    int32_t *exception_genes, int64_t room, int32_t threads) {
+    clear_error();
+    if (rows < 0 || room < 0 || threads < 1 || threads > 64 || row_ptr == nullptr || (rows > 0 && row_ptr[rows] > row_ptr[0] && (col_idx == nullptr || gaps == nullptr)) ||
+        (room > 0 && (exception_positions == nullptr || exception_genes == nullptr))) {
+        fail(CB200_STATUS_INVALID_ARGUMENT, "encode_gene_gaps: null arrays, or rows / room / threads out of range");
+        return -2;
+    }
+    if (rows == 0 || row_ptr[rows] - row_ptr[0] >= 0x7fffff00ll) return rows == 0 ? 0 : -2;
+    const int capped = static_cast<int>(std::min<std::int64_t>(room, 0x7fffffff));
+    std::vector<int2> list(static_cast<std::size_t>(capped));
+    narrow_pool pool;
+    pool.start(threads - 1);
+    const int count = pool.run_gaps(col_idx + row_ptr[0], row_ptr, rows, gaps, list.data(), capped);
+    for (int i = 0; i < count; ++i) {
+        exception_positions[i] = list[static_cast<std::size_t>(i)].x;
+        exception_genes[i] = list[static_cast<std::size_t>(i)].y;
+    }
+    return count;
+}
+
 cb200_status cb200_host_forward(cb200_host_stage *s, const cb200_qcsr *x, const void *w, int64_t w_ld, float *y, int64_t y_ld,
                                 float alpha, uint64_t *h2d_bytes, uint64_t *d2h_bytes) {
     clear_error();

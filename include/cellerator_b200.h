@@ -910,6 +910,13 @@ typedef struct cb200_host_stage_options {
 cb200_status cb200_host_stage_create(const cb200_host_stage_options *options, cb200_host_stage **out);
 void cb200_host_stage_destroy(cb200_host_stage *stage);
 uint64_t cb200_host_stage_device_bytes(const cb200_host_stage *stage);
+/* The host half of the gap form, for callers that stage their own copies (and for tests): gaps[i] for the entries
+ * [row_ptr[0], row_ptr[rows]) of col_idx, written from gaps[0] on -- gene - previous gene of the row - 1, the row's
+ * first entry its gene; 255 marks an entry whose gene is listed instead ({position relative to row_ptr[0], gene},
+ * ascending positions): a gap of 255 or more, or a gene that does not ascend.  `threads` host threads (1..64) share the
+ * rows.  Returns the number of listed entries, -1 if there are more than `room`, -2 on bad arguments (no CUDA call). */
+int64_t cb200_host_encode_gene_gaps(const int32_t *col_idx, const int64_t *row_ptr, int64_t rows, uint8_t *gaps, int32_t *exception_positions,
+                                    int32_t *exception_genes, int64_t room, int32_t threads);
 /* x: HOST arrays (row_ptr, col_idx, packed_values, packed_row_ptr for 4-bit codes, scales, offsets);
  * w: k x n HOST (dense_dtype), y: rows x n HOST fp32.  Returns after the last copy has landed in y
  * (it waits for its own streams).  h2d_bytes / d2h_bytes (optional) receive the bytes moved. */

@@ -121,3 +121,65 @@ def test_no_cpu_fallback_without_a_device():
     assert L.cb200_session_create(C.byref(opts), C.byref(sess)) == capi.CUDA_ERROR
     m = capi.header(capi.QCsr())
     assert L.cb200_dequantize_rows(C.byref(m), 0, 0, None, 0, None) == capi.CUDA_ERROR
+
+
+def _decode_gene_gaps(gaps, row_ptr, positions, genes):
+    """What the device does with the gap form: gene = previous gene of the row + gap + 1 (-1 before a row's first
+    entry); a listed entry takes its gene from the list, and the entries behind it count on from there."""
+    listed = dict(zip(positions.tolist(), genes.tolist()))
+    out = np.empty(len(gaps), dtype=np.int64)
+    base = int(row_ptr[0])
+    for r in range(len(row_ptr) - 1):
+        gene = -1
+        for i in range(int(row_ptr[r]) - base, int(row_ptr[r + 1]) - base):
+            if gaps[i] == 255:
+                gene = listed[i]
+            else:
+                gene += int(gaps[i]) + 1
+            out[i] = gene
+    return out
+
+
+@pytest.mark.parametrize("case", ["dense_rows", "long_gaps", "descending", "offset_rows"])
+@pytest.mark.parametrize("threads", [1, 5])
+def test_gene_gap_encoding_round_trip(case, threads):
+    """cb200_host_encode_gene_gaps (the host half of cb200_host_forward's short index form) against a decode in plain
+    Python: every entry comes back, whatever the gaps; marked entries are exactly those whose gap does not fit a byte;
+    a list that is too short is reported."""
+    L = capi.lib()
+    rng = np.random.default_rng(len(case) + threads)
+    rows = 300
+    cols = {"dense_rows": 3000, "long_gaps": 400_000, "descending": 3000, "offset_rows": 70_000}[case]
+    counts = rng.integers(0, 260, size=rows)
+    counts[rng.integers(0, rows, size=5)] = 0                          # empty rows
+    counts[7] = 1                                                       # a single entry
+    row_ptr = np.zeros(rows + 1, dtype=np.int64)
+    np.cumsum(counts, out=row_ptr[1:])
+    col = np.concatenate([np.sort(rng.choice(cols, size=int(c), replace=False)) for c in counts] + [np.zeros(0, dtype=np.int64)]).astype(np.int32)
+    if case == "descending":
+        for r in rng.choice(rows, size=30, replace=False):
+            lo, hi = row_ptr[r], row_ptr[r + 1]
+            col[lo:hi] = rng.permutation(col[lo:hi])
+        col[row_ptr[3]:row_ptr[4]] = -5                                 # indices the kernels would leave out survive too
+    first_row = 40 if case == "offset_rows" else 0                      # a chunk in the middle of the caller's arrays
+    ptr = np.ascontiguousarray(row_ptr[first_row:])
+    n = int(ptr[-1] - ptr[0])
+    gaps = np.full(n + 64, 0xEE, dtype=np.uint8)
+    positions, genes = np.zeros(n + 1, dtype=np.int32), np.zeros(n + 1, dtype=np.int32)
+    count = L.cb200_host_encode_gene_gaps(col.ctypes.data, ptr.ctypes.data, len(ptr) - 1, gaps.ctypes.data, positions.ctypes.data,
+                                          genes.ctypes.data, n + 1, threads)
+    assert count >= 0
+    assert np.all(gaps[n:] == 0xEE)                                     # nothing written past the last entry
+    assert np.all(np.diff(positions[:count]) > 0)                       # ascending positions, no sort needed on the device
+    chunk = col[ptr[0]:ptr[-1]].astype(np.int64)
+    assert np.array_equal(_decode_gene_gaps(gaps[:n], ptr, positions[:count], genes[:count]), chunk)
+    previous = np.concatenate([[-1], chunk[:-1]])
+    previous[(ptr[:-1] - ptr[0])[np.diff(ptr) > 0]] = -1                # a row's first entry counts from -1
+    gap = chunk - previous - 1
+    assert np.array_equal(np.flatnonzero(gaps[:n] == 255), np.flatnonzero((gap < 0) | (gap >= 255)))
+    assert count == int(np.sum((gap < 0) | (gap >= 255)))
+    if count > 0:
+        assert L.cb200_host_encode_gene_gaps(col.ctypes.data, ptr.ctypes.data, len(ptr) - 1, gaps.ctypes.data, positions.ctypes.data,
+                                             genes.ctypes.data, count - 1, threads) == -1
+    assert L.cb200_host_encode_gene_gaps(col.ctypes.data, ptr.ctypes.data, len(ptr) - 1, gaps.ctypes.data, positions.ctypes.data,
+                                         genes.ctypes.data, n + 1, 0) == -2
