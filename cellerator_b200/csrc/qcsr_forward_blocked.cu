@@ -99,12 +99,16 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
     const int rl = static_cast<int>(r & (kRows - 1));
     const std::int64_t begin = row_ptr[r], end = row_ptr[r + 1];
     const std::uint8_t *row_bytes = packed + (packed_row_ptr != nullptr ? packed_row_ptr[r] : begin);
+    // the genes of the next 32 entries are requested before this read's are worked on: two loads of a row in flight
+    std::int32_t ahead = begin + lane < end ? col_idx[begin + lane] : 0;
     for (std::int64_t base = begin; base < end; base += 32) {
         const std::int64_t i = base + lane;
+        const std::int32_t now = ahead;
+        if (i + 32 < end) ahead = col_idx[i + 32];
         int window = -2; // past the row's end
         int gl = 0;
         if (i < end) {
-            const std::int64_t gene = col_idx[i];
+            const std::int64_t gene = now;
             window = (gene >= 0 && gene < cols) ? static_cast<int>(gene >> kWinShift) : -1;
             gl = static_cast<int>(gene & (kWin - 1));
         }
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
                 const std::uint32_t code = load_code<BITS>(row_bytes, i - begin);
                 std::uint32_t word;
                 if (bake != 0) {
-                    const std::int64_t gene = col_idx[i];
+                    const std::int64_t gene = now;
                     const float scale = scales != nullptr ? scales[gene] : 1.0f;
                     const float add = offsets != nullptr ? offsets[bake == 2 ? r : gene] : 0.0f;
                     const float value = fmaf(static_cast<float>(code), scale, add);
@@ -155,32 +159,54 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
 }
 
 // seg_ptr[i] = sum of counts[0..i) rounded up to multiples of 4 (16-byte segments for the copy
-// engine), cursor = seg_ptr.  One block; every thread scans a contiguous slice.
+// engine), cursor = seg_ptr.  One block walks the segments in tiles of 4,096 (a thread takes four consecutive
+// segments, consecutive threads consecutive fours) and carries the running total from tile to tile.
 __global__ void __launch_bounds__(1024) segment_scan_kernel(const unsigned *counts, std::int64_t segments, std::int64_t *seg_ptr,
                                                             unsigned long long *cursor) {
-    __shared__ long long partial[1024];
-    const std::int64_t per = (segments + 1023) / 1024;
-    const std::int64_t lo = min(segments, per * threadIdx.x), hi = min(segments, lo + per);
-    long long sum = 0;
-    for (std::int64_t i = lo; i < hi; ++i) sum += (counts[i] + 3u) & ~3u;
-    partial[threadIdx.x] = sum;
+    __shared__ long long warp_total[32];
+    __shared__ long long carry;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        long long run = 0;
-        for (int i = 0; i < 1024; ++i) {
-            const long long v = partial[i];
-            partial[i] = run;
-            run += v;
+    for (std::int64_t tile = 0; tile < segments; tile += 4096) {
+        const std::int64_t first = tile + 4 * static_cast<std::int64_t>(threadIdx.x);
+        long long v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = first + j < segments ? static_cast<long long>((counts[first + j] + 3u) & ~3u) : 0;
+        const long long mine = v[0] + v[1] + v[2] + v[3];
+        long long sum = mine; // inclusive scan within the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const long long up = __shfl_up_sync(0xffffffffu, sum, d);
+            if (lane >= d) sum += up;
         }
+        if (lane == 31) warp_total[warp] = sum;
+        __syncthreads();
+        if (warp == 0) { // exclusive scan of the 32 warp totals
+            const long long total = warp_total[lane];
+            long long run = total;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const long long up = __shfl_up_sync(0xffffffffu, run, d);
+                if (lane >= d) run += up;
+            }
+            warp_total[lane] = run - total;
+        }
+        __syncthreads();
+        long long at = carry + warp_total[warp] + sum - mine;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (first + j < segments) {
+                seg_ptr[first + j] = at;
+                cursor[first + j] = static_cast<unsigned long long>(at);
+            }
+            at += v[j];
+        }
+        __syncthreads(); // everyone has read carry and the warp totals
+        if (threadIdx.x == 1023) carry = at;
+        __syncthreads();
     }
-    __syncthreads();
-    long long at = partial[threadIdx.x];
-    for (std::int64_t i = lo; i < hi; ++i) {
-        seg_ptr[i] = at;
-        cursor[i] = static_cast<unsigned long long>(at);
-        at += (counts[i] + 3u) & ~3u;
-    }
-    if (threadIdx.x == 1023) seg_ptr[segments] = at; // the last slice (possibly empty) ends at the total
+    if (threadIdx.x == 0) seg_ptr[segments] = carry;
 }
 
 // ---------------------------------------------------------------------------------------------
