@@ -624,7 +624,7 @@ def run_ours(args):
         so.max_chunk_rows = -(-x.rows // chunks)
         counts = np.diff(x.host_row_ptr[:: so.max_chunk_rows].tolist() + [int(x.host_row_ptr[-1])])
         so.max_chunk_nnz = int(counts.max()) + 1
-        so.chunk_buffers = 3
+        so.chunk_buffers = max(2, min(4, args.e2e_buffers))
         # the ranks of a box share its cores: each stage narrows gene indices with its share of them
         so.host_threads = max(1, len(os.sched_getaffinity(0)) // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))))
         stage = C.c_void_p()
@@ -653,8 +653,8 @@ def run_ours(args):
         e_ms = float(e_ms.item())
         e2e = {"value": total_units / (e_ms * 1e-3) / 1e9, "unit": "Gnnz/s", "h2d_bytes_per_step": int(h2d.value),
                "d2h_bytes_per_step": int(d2h.value), "ms_per_step": e_ms, "steps": e_steps,
-               "call": "cb200_host_forward (C ABI, pinned host buffers, 3 chunk buffers of %d rows; gene indices cross as gap bytes "
-                       "while the host rewrites them fast enough)" % so.max_chunk_rows,
+               "call": "cb200_host_forward (C ABI, pinned host buffers, %d chunk buffers of %d rows; gene indices cross as gap bytes "
+                       "while the host rewrites them fast enough)" % (so.chunk_buffers, so.max_chunk_rows),
                "h2d_bytes_per_entry": float(h2d.value) / max(1.0, float(x.nnz)),
                "schedule": "gene_tiled (codes read at launch)", "stage_device_bytes": int(L.cb200_host_stage_device_bytes(stage)),
                "aggregate_h2d_gbs": world * h2d.value / (e_ms * 1e-3) / 1e9}
@@ -1073,6 +1073,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16)
+    ap.add_argument("--e2e-buffers", type=int, default=3, help="chunk buffers of the host stage's ring (2..4)")
     ap.add_argument("--cpu-rows-per-thread", type=int, default=4000,
                     help="rows of the CPU sample per host thread (4,000 rows x 16 threads: ~25 CPU-seconds per pass)")
     args = ap.parse_args()
