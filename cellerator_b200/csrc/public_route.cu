@@ -20,6 +20,47 @@ __global__ void __launch_bounds__(256) widen_offsets_kernel(const std::uint32_t 
     if (i < count) dst[i] = static_cast<std::int64_t>(src[i]);
 }
 
+// 4-bit codes: the descriptor carries no packed row offsets, but the codec fixes them: a row's codes take
+// ceil(entries / 2) bytes and rows follow each other without sharing a byte (include/Cellerator/quantized/layout.cuh:
+// 111-129, build_packed_row_ptr), so packed[r] = sum of those over the rows before r.  One block walks the rows in tiles
+// of 1,024 and carries the running total; `wide` holds the widened row offsets, rows + 1 of them.
+__global__ void __launch_bounds__(1024) packed_offsets_kernel(const std::int64_t *wide, std::int64_t rows, std::int64_t *packed) {
+    __shared__ long long warp_total[32];
+    __shared__ long long carry;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (std::int64_t tile = 0; tile < rows; tile += 1024) {
+        const std::int64_t r = tile + threadIdx.x;
+        const long long mine = r < rows ? (wide[r + 1] - wide[r] + 1) / 2 : 0;
+        long long sum = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const long long up = __shfl_up_sync(0xffffffffu, sum, d);
+            if (lane >= d) sum += up;
+        }
+        if (lane == 31) warp_total[warp] = sum;
+        __syncthreads();
+        if (warp == 0) {
+            const long long total = warp_total[lane];
+            long long run = total;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const long long up = __shfl_up_sync(0xffffffffu, run, d);
+                if (lane >= d) run += up;
+            }
+            warp_total[lane] = run - total;
+        }
+        __syncthreads();
+        const long long at = carry + warp_total[warp] + sum - mine;
+        if (r < rows) packed[r] = at;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = at + mine;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) packed[rows] = carry;
+}
+
 cb200_status check_layout(const cb200_public_layout *l) {
     if (l == nullptr || l->version != CB200_ABI_VERSION || l->size < sizeof(cb200_public_layout))
         return fail(CB200_STATUS_INVALID_ARGUMENT, "layout descriptor version or size mismatch");
@@ -33,7 +74,7 @@ cb200_status check_layout(const cb200_public_layout *l) {
         if (l->block_size == 0u || l->ell_cols == 0u) return fail(CB200_STATUS_INVALID_SHAPE, "Blocked-ELL requires block_size and ell_cols");
         if (l->block_col_idx == nullptr) return fail(CB200_STATUS_INVALID_ARGUMENT, "Blocked-ELL requires block column indices");
     } else {
-        if (l->bits != 8u) return fail(CB200_STATUS_UNSUPPORTED, "the public descriptor has no packed row offsets: quantized CSR is served with 8-bit codes");
+        if (l->bits != 8u && l->bits != 4u) return fail(CB200_STATUS_UNSUPPORTED, "quantized CSR codes must be 8 or 4 bits");
         if (l->major_ptr == nullptr || (l->nnz != 0u && l->minor_idx == nullptr))
             return fail(CB200_STATUS_INVALID_ARGUMENT, "CSR layout requires row offsets and column indices");
         if (l->cols > 0x7fffffffu) return fail(CB200_STATUS_INVALID_SHAPE, "gene indices must fit 31 bits");
@@ -111,6 +152,16 @@ cb200_status route(const cb200_public_layout *l, int32_t projection, const float
         CB200_CUDA_OK(cudaGetLastError());
         csr.version = CB200_ABI_VERSION; csr.size = sizeof csr;
         csr.rows = l->rows; csr.cols = l->cols; csr.nnz = l->nnz; csr.bits = pr.bits; csr.policy = pr.policy;
+        if (l->bits == 4u) { // the packed row offsets the descriptor does not carry
+            std::int64_t *packed = static_cast<std::int64_t *>(cur.take((static_cast<std::uint64_t>(l->rows) + 1u) * 8u));
+            if (packed == nullptr)
+                return fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "scratch too small for the packed row offsets (%llu bytes)",
+                            (static_cast<unsigned long long>(l->rows) + 1u) * 8u);
+            packed_offsets_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(wide, static_cast<std::int64_t>(l->rows), packed);
+            count_launch();
+            CB200_CUDA_OK(cudaGetLastError());
+            csr.packed_row_ptr = packed;
+        }
         csr.row_ptr = wide; csr.col_idx = reinterpret_cast<const std::int32_t *>(l->minor_idx);
         csr.packed_values = l->packed_values; csr.scales = l->column_scales; csr.offsets = offsets_of(*l);
         ln.csr = &csr;
@@ -153,7 +204,8 @@ extern "C" cb200_status cb200_public_projection_scratch(const cb200_public_layou
     if (st != CB200_STATUS_SUCCESS) return st;
     // widened row offsets (CSR) + the status block of the fp32 schedules these calls select
     const std::uint64_t offsets = layout->layout == CB200_PUBLIC_LAYOUT_QUANTIZED_CSR ? (static_cast<std::uint64_t>(layout->rows) + 1u) * 8u : 0u;
-    *bytes = (offsets + 255u) / 256u * 256u + 512u;
+    const std::uint64_t arrays = layout->layout == CB200_PUBLIC_LAYOUT_QUANTIZED_CSR && layout->bits == 4u ? 2u : 1u; // + packed row offsets
+    *bytes = arrays * ((offsets + 255u) / 256u * 256u) + 512u;
     return CB200_STATUS_SUCCESS;
 }
 

@@ -674,7 +674,9 @@ typedef struct cb200_public_layout {
     const uint32_t *major_ptr;     /* CSR: rows + 1 */
     const uint32_t *minor_idx;     /* CSR: nnz gene indices */
     const uint32_t *block_col_idx; /* Blocked-ELL */
-    const uint8_t *packed_values;
+    const uint8_t *packed_values;  /* CSR, 4-bit codes: a row's codes take ceil(entries / 2) bytes and the rows follow each other
+                                    * (build_packed_row_ptr, quantized/layout.cuh:111-129); the calls derive the packed row
+                                    * offsets from major_ptr on the stream, in the scratch */
     const float *column_scales;
     const float *column_offsets; /* per-gene affine policy */
     const float *row_offsets;    /* column-scale / row-offset policy */

@@ -16,13 +16,15 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("policy", [1, 2])
 @pytest.mark.parametrize("n", [32, 64, 40])
-def test_quantized_csr_forward_and_backward(cuda_device, oracle, policy, n):
-    rng = np.random.default_rng(50 + n + policy)
-    c = host_pack(oracle, random_csr(rng, rows=700, cols=900, max_nnz=220, bits=8, policy=policy))
+@pytest.mark.parametrize("bits", [8, 4])
+def test_quantized_csr_forward_and_backward(cuda_device, oracle, policy, n, bits):
+    """(4-bit codes: the public descriptor carries no packed row offsets; the call derives them on the stream.)"""
+    rng = np.random.default_rng(50 + n + policy + bits)
+    c = host_pack(oracle, random_csr(rng, rows=700 if bits == 8 else 2300, cols=900, max_nnz=220, bits=bits, policy=policy))
     x = to_dev(c, cuda_device)
     w, w_host = dense(rng, c["cols"], n, torch.float32, cuda_device, ld=n + 4)       # explicit leading dimension
     y = ops.public_projection(x, w)
-    ref = oracle.qcsr_forward(8, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
+    ref = oracle.qcsr_forward(bits, policy, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"],
                               c["offsets"], w_host, c["cols"])
     l1, _ = row_l1(oracle, c)
     assert_forward_close(y.cpu().numpy(), ref, l1, float(np.abs(w_host).max()))
@@ -59,7 +61,7 @@ def test_rejections(cuda_device, oracle):
     l.layout = 1                                                   # CELLERATOR_LAYOUT_CSR (fp16 values): not this backend's
     assert call(l) == 3
     l = ops.public_layout(x)
-    l.bits = 4                                                     # no packed row offsets in the public descriptor
+    l.bits = 2                                                     # 8- and 4-bit codes only
     assert call(l) == 3
     l = ops.public_layout(x)
     l.size = 8
