@@ -349,8 +349,13 @@ schedule_plan plan_schedule(const cb200_spmm_problem &pr) {
         // (hi*hi + hi*lo + lo*hi) rebuild each product to ~3 * 2^-17 relative, inside the 1e-4 bound of
         // an fp32 G; that is not bit-equal to an fp32 multiply, and callers that need the fp32-FMA kernel
         // do not hand the matrix to prepare.  The cost follows the dense area, so it needs density.
-        if (pr.deterministic) {
-            plan.gene_gather = true; // same bits on every run: gather gene by gene from a gene-major copy
+        // Same bits on every run: the tensor-core kernel over the window-blocked copy gives that too (every CTA's sums go to
+        // a slot of their own and are added in a fixed order), and a deterministic request that names it gets it; the
+        // default stays the gather gene by gene from a gene-major copy, whose fp32 sums the oracle restates entry by entry.
+        const bool named_blocked = hint != nullptr && hint_starts(hint, "tensor_blocked") && pr.device_matrix != nullptr &&
+                                   qcsr_transpose_blocked_shape_ok(pr.m, pr.k, pr.n, pr.bits) && (limit == 0u || nnz * 4u <= limit);
+        if (pr.deterministic && !named_blocked) {
+            plan.gene_gather = true;
             if (limit != 0u && nnz * 5u + static_cast<std::uint64_t>(pr.k + 1) * 12u > limit) {
                 plan.status = fail(CB200_STATUS_UNSUPPORTED, "the gene-major copy of a deterministic transpose exceeds the persistent memory limit");
             }
@@ -558,7 +563,7 @@ cb200_status cb200_spmm_prepare(const cb200_spmm_problem *problem, cb200_prepare
                                                          true, p->arena, stream, &p->blocked);
             if (st != CB200_STATUS_SUCCESS) return abandon(st);
             p->schedule_name = problem->multiply == CB200_DTYPE_BF16 ? "tensor_blocked" : "tensor_blocked_x3";
-            p->workspace_bytes = qcsr_transpose_blocked_workspace_bytes(problem->m, problem->n);
+            p->workspace_bytes = qcsr_transpose_blocked_workspace_bytes(problem->m, problem->k, problem->n);
             p->persistent_bytes += p->blocked.bytes;
         }
     }

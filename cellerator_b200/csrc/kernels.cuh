@@ -176,7 +176,7 @@ cb200_status launch_qcsr_forward(const qcsr_view &x, const dense_args &d, std::i
 // Transpose on the tensor cores from the window-blocked copy (N in {32, 64}).  split_products == false:
 // one pass of bf16 products; true: fp32 products rebuilt from three bf16 passes (hi*hi + hi*lo + lo*hi).
 bool qcsr_transpose_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits);
-std::uint64_t qcsr_transpose_blocked_workspace_bytes(std::int64_t rows, std::int64_t n);
+std::uint64_t qcsr_transpose_blocked_workspace_bytes(std::int64_t rows, std::int64_t cols, std::int64_t n);
 cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args &d, std::int64_t row_begin,
                                            std::int64_t row_end, void *workspace, std::uint64_t workspace_bytes,
                                            const blocked_layout &layout, bool split_products, int sm_count,

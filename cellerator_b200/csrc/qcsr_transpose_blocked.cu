@@ -19,9 +19,11 @@
 // partial row range is honoured).  A CTA keeps the fp32 accumulators of a set of windows (four at N = 64,
 // eight at N = 32; two accumulators per window, one per MMA-issuing warp, 512 TMEM columns in all) while
 // it walks a run of groups, so the group's G record is fetched once per set; at the end of the run the
-// two accumulators of a window are added and the sums go into G' with
-// vector reductions (the (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so
-// several CTAs contribute to the same genes; G' is first scaled by beta by a small kernel).
+// two accumulators of a window are added and the sums are stored to the run's slot of a scratch array.  The
+// (window set, group) pairs are dealt to the CTAs as equal contiguous runs, so two or three CTAs contribute to
+// the same genes: ordered_sum_kernel adds a set's slots into G' in run order (G' is first scaled by beta by a
+// small kernel), which makes G' the same bits on every launch -- vector reductions straight into G', as this
+// kernel used before, are served in the order the L2 sees them.
 //
 // Entry words.  Prepare normally bakes them for this kernel: {bf16 value, byte position / 2 in the
 // gene-major tile}, a hi array and, for the split passes, a lo array with bf16(value - hi); the scatter
@@ -85,7 +87,17 @@ struct tb_params {
     float alpha;
     int *status;
     int value_part; // 0: tile holds hi = bf16(value); 1: lo = bf16(value - hi)
+    // The accumulators of a run (the consecutive units of one window set in one CTA) go to slot `global run index` of
+    // this array, [run][window of the set][gene][N]; ordered_sum_kernel adds the slots of a set into G' in run order,
+    // so that G' is the same bits on every launch (atomic adds of three or more CTAs' sums are not).
+    float *partials;
 };
+
+// Runs of CTA b of a grid over `total` units in sets of `per_set`: it owns the units [total b / grid, total (b + 1) / grid).
+__host__ __device__ inline std::int64_t runs_of_cta(std::int64_t total, std::int64_t per_set, std::int64_t grid, std::int64_t b) {
+    const std::int64_t u0 = total * b / grid, u1 = total * (b + 1) / grid;
+    return u1 > u0 ? (u1 - 1) / per_set - u0 / per_set + 1 : 0;
+}
 
 __device__ __forceinline__ std::int64_t dmin(std::int64_t a, std::int64_t b) { return a < b ? a : b; }
 // K-major operand, no swizzle (the G record): core matrices of 8 columns x 16 bytes (8 cells); the
@@ -194,6 +206,11 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
     const std::int64_t sets = (p.windows + kSetWindows - 1) / kSetWindows;
     const std::int64_t total_units = sets * p.group_count;
     const std::int64_t u0 = total_units * blockIdx.x / gridDim.x, u1 = total_units * (blockIdx.x + 1) / gridDim.x;
+    // global index of this CTA's first run: the runs of the CTAs before it (every warp adds them up for itself)
+    std::int64_t first_run = 0;
+    for (std::int64_t b = lane; b < static_cast<std::int64_t>(blockIdx.x); b += 32) first_run += runs_of_cta(total_units, p.group_count, gridDim.x, b);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) first_run += __shfl_xor_sync(0xffffffffu, first_run, d);
 
     if (warp < kProducerWarps) {
         // ================= zero, scatter, read back =================
@@ -341,11 +358,9 @@ __global__ void __launch_bounds__(kThreads, 1) qcsr_transpose_blocked_kernel(con
 #pragma unroll
                     for (int c = 0; c < 32; ++c) v[c] += second[c];
                     if (gene < p.cols && *abort_flag == 0) {
-                        float *out = p.out + gene * p.out_ld + h * 32;
+                        float *slot = p.partials + (((first_run + run) * kSetWindows + wl) * kWin + quarter * 32 + lane) * NC + h * 32;
 #pragma unroll
-                        for (int c = 0; c < 32; c += 4)
-                            atomicAdd(reinterpret_cast<float4 *>(out + c),
-                                      make_float4(p.alpha * v[c], p.alpha * v[c + 1], p.alpha * v[c + 2], p.alpha * v[c + 3]));
+                        for (int c = 0; c < 32; c += 4) *reinterpret_cast<float4 *>(slot + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
                     }
                 }
             }
@@ -454,6 +469,47 @@ template<int NC> constexpr std::size_t tb_smem_bytes() {
            (6 + 2 * kGStages + 2 * kChunkStages) * sizeof(std::uint64_t) + (kChunkStages + 1) * 4 + 16;
 }
 
+// G'[genes of window wl of set s] += alpha * (the sums of the runs of set s, added in run order).  Block = (set, window of
+// the set); the runs of a set are those of the CTAs whose unit range meets the set, in CTA order.
+template<int NC>
+__global__ void __launch_bounds__(256) ordered_sum_kernel(const float *partials, float *out, std::int64_t out_ld, std::int64_t cols, int windows,
+                                                          std::int64_t group_count, std::int64_t grid, float alpha) {
+    constexpr int kSetWindows = set_windows(NC);
+    __shared__ std::int64_t slots[512];
+    __shared__ int slot_count;
+    const std::int64_t set = blockIdx.x / kSetWindows;
+    const int wl = static_cast<int>(blockIdx.x % kSetWindows);
+    const std::int64_t window = set * kSetWindows + wl;
+    if (window >= windows) return;
+    const std::int64_t sets = (windows + kSetWindows - 1) / kSetWindows, total = sets * group_count;
+    if (threadIdx.x == 0) {
+        int count = 0;
+        std::int64_t first_run = 0;
+        for (std::int64_t b = 0; b < grid; ++b) {
+            const std::int64_t u0 = total * b / grid, u1 = total * (b + 1) / grid;
+            if (u1 > u0 && u0 < (set + 1) * group_count && u1 > set * group_count && count < 512) slots[count++] = first_run + (set - u0 / group_count);
+            first_run += runs_of_cta(total, group_count, grid, b);
+        }
+        slot_count = count;
+    }
+    __syncthreads();
+    const int count = slot_count;
+    for (int i = threadIdx.x; i < kWin * (NC / 4); i += blockDim.x) {
+        const int gl = i / (NC / 4), c4 = i % (NC / 4);
+        const std::int64_t gene = window * kWin + gl;
+        if (gene >= cols) continue;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int r = 0; r < count; ++r) {
+            const float4 v = *reinterpret_cast<const float4 *>(partials + ((slots[r] * kSetWindows + wl) * kWin + gl) * NC + 4 * c4);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        float4 *dst = reinterpret_cast<float4 *>(out + gene * out_ld + 4 * c4);
+        float4 o = *dst;
+        o.x = fmaf(alpha, sum.x, o.x); o.y = fmaf(alpha, sum.y, o.y); o.z = fmaf(alpha, sum.z, o.z); o.w = fmaf(alpha, sum.w, o.w);
+        *dst = o;
+    }
+}
+
 template<int NC, bool BAKED>
 cb200_status launch_one(const tb_params &p, int sm_count, cudaStream_t stream) {
     constexpr std::size_t smem = tb_smem_bytes<NC>();
@@ -464,17 +520,26 @@ cb200_status launch_one(const tb_params &p, int sm_count, cudaStream_t stream) {
     const std::int64_t units = sets * p.group_count;
     const unsigned grid = static_cast<unsigned>(units < sm_count ? units : sm_count);
     qcsr_transpose_blocked_kernel<NC, BAKED><<<grid, kThreads, smem, stream>>>(p);
-    count_launch();
+    ordered_sum_kernel<NC><<<static_cast<unsigned>(sets * set_windows(NC)), 256, 0, stream>>>(p.partials, p.out, p.out_ld, p.cols, p.windows, p.group_count,
+                                                                                             static_cast<std::int64_t>(grid), p.alpha);
+    count_launch(2);
     CB200_CUDA_OK(cudaGetLastError());
     return CB200_STATUS_SUCCESS;
 }
 
 } // namespace
 
-// status block + one bf16 record of G per group of 256 cells
-std::uint64_t qcsr_transpose_blocked_workspace_bytes(std::int64_t rows, std::int64_t n) {
+// status block + one bf16 record of G per group of 256 cells + the runs' sums: a run ends with its window set or with its
+// CTA's share of the units, so there are fewer than sets + CTAs of them (kMaxTransposeCtas bounds the grid)
+constexpr std::int64_t kMaxTransposeCtas = 256;
+static std::uint64_t record_part_bytes(std::int64_t rows, std::int64_t n) {
     const std::int64_t groups = (rows + kRows - 1) / kRows;
-    return static_cast<std::uint64_t>(256 + groups * g_record_bytes(static_cast<int>(n)));
+    return (static_cast<std::uint64_t>(256 + groups * g_record_bytes(static_cast<int>(n))) + 255u) & ~static_cast<std::uint64_t>(255u);
+}
+std::uint64_t qcsr_transpose_blocked_workspace_bytes(std::int64_t rows, std::int64_t cols, std::int64_t n) {
+    const std::int64_t per_set = n == 32 ? set_windows(32) : set_windows(64);
+    const std::int64_t windows = (cols + kWin - 1) / kWin, sets = (windows + per_set - 1) / per_set;
+    return record_part_bytes(rows, n) + static_cast<std::uint64_t>(sets + kMaxTransposeCtas) * per_set * kWin * n * sizeof(float);
 }
 
 bool qcsr_transpose_blocked_shape_ok(std::int64_t rows, std::int64_t cols, std::int64_t n, int bits) {
@@ -491,7 +556,8 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
         return CB200_STATUS_SUCCESS; // baked words of the forward tile, or no lo words for the split passes
     if (!qcsr_transpose_blocked_shape_ok(x.rows, x.cols, d.n, x.bits) || d.dense_dtype != CB200_DTYPE_F32) return CB200_STATUS_SUCCESS;
     if (reinterpret_cast<std::uintptr_t>(d.out) % 16u != 0u || (d.out_ld * 4u) % 16u != 0u) return CB200_STATUS_SUCCESS;
-    if (workspace == nullptr || workspace_bytes < qcsr_transpose_blocked_workspace_bytes(x.rows, d.n)) return CB200_STATUS_SUCCESS;
+    if (workspace == nullptr || workspace_bytes < qcsr_transpose_blocked_workspace_bytes(x.rows, x.cols, d.n) || sm_count > kMaxTransposeCtas)
+        return CB200_STATUS_SUCCESS;
     if (reinterpret_cast<std::uintptr_t>(workspace) % 256u != 0u) return CB200_STATUS_SUCCESS;
     const bool row_policy = x.policy == CB200_DECODE_COLUMN_SCALE_ROW_OFFSET;
     // the kernel reads 256 row offsets per group: the last group must not run past the array
@@ -522,6 +588,7 @@ cb200_status launch_qcsr_transpose_blocked(const qcsr_view &x, const dense_args 
     p.records = records; p.out = d.out; p.out_ld = d.out_ld; p.cols = x.cols;
     p.group_begin = group_begin; p.group_count = group_end - group_begin; p.windows = layout.windows;
     p.alpha = d.alpha; p.status = status;
+    p.partials = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + record_part_bytes(x.rows, d.n));
     // One pass multiplies bf16(value) with bf16(G).  With split products the fp32 product is rebuilt
     // from three passes, hi*hi + hi*lo + lo*hi (v = hi + lo + O(2^-17 v), likewise G): relative error
     // per product about 3 * 2^-17, inside the 1e-4 bound of an fp32 dense operand.  The passes run

@@ -248,7 +248,9 @@ typedef struct cb200_spmm_problem {
     /* Optional host copy of row_ptr (m+1) used to choose the row schedule; NULL = default. */
     const int64_t *host_row_ptr;
     int32_t deterministic; /* prepare_policy.deterministic, operation_core.hh:116-124; a transpose needs
-                            * device_matrix for it (schedule "gene_gather"), else prepare is refused */
+                            * device_matrix for it, else prepare is refused: schedule "gene_gather" (fp32 FMAs
+                            * entry by entry), or, with schedule_hint "tensor_blocked", the tensor-core schedules
+                            * over the window-blocked copy, whose CTAs' sums are added in a fixed order too */
     /* numeric_policy.multiply of the request: 0 or CB200_DTYPE_F32 = exact fp32 products;
      * CB200_DTYPE_BF16 = decoded values may be rounded to bf16 and multiplied on the tensor cores
      * (CSR forward with bf16 W: schedules "tensor_windows" / "tensor_blocked"; transpose with the

@@ -179,6 +179,8 @@ def test_tensor_transpose_full_scale(cuda_device):
     del vals
     gmax = float(g.abs().max())
     assert torch.all((out - exact).abs() <= 1e-2 * (col_l1[:, None] * gmax).float() + 1e-30)
+    for _ in range(3):      # every CTA's sums go to a slot of their own and are added in a fixed order: the same bits every time
+        assert torch.equal(op.run(x, g, torch.empty(x.cols, n, device=cuda_device)), out)
     half = (x.rows // 2 // 256) * 256 + 77
     a = op.run(x, g, torch.empty(x.cols, n, device=cuda_device), row_begin=0, row_end=half)
     b = op.run(x, g, a, row_begin=half, row_end=x.rows, beta=1.0)
@@ -264,6 +266,32 @@ def _row_range_on_host(x, r0, r1):
     return sub
 
 
+def test_deterministic_request_may_name_the_tensor_schedule(cuda_device, oracle, monkeypatch):
+    """deterministic = 1 selects the gather schedule by default and the tensor-core schedule when the request names it:
+    both give the same bits on every run (the tensor kernel's CTAs write their sums to slots of their own, which a
+    second kernel adds in a fixed order), both inside the fp32 bound."""
+    rng = np.random.default_rng(12)
+    rows, cols, n = 256 * 40 + 19, 128 * 9 + 30, 64
+    c = host_pack(oracle, random_csr(rng, rows=rows, cols=cols, max_nnz=150, bits=8, policy=1))
+    x = to_dev(c, cuda_device)
+    g = torch.randn(rows, n, device=cuda_device)
+    ref = oracle.qcsr_transpose(8, 1, c["row_ptr"], c["packed_row_ptr"], c["col_idx"], c["packed"], c["scales"], c["offsets"],
+                                g.cpu().numpy(), cols)
+    cl1 = col_l1_of(oracle, c)
+    gmax = float(g.abs().max())
+    for hint, expected in ((None, "gene_gather"), ("tensor_blocked", "tensor_blocked_x3")):
+        monkeypatch.setitem(ops.SCHEDULE_REQUEST, capi.PROJECTION_TRANSPOSE, hint)
+        op = ops.PreparedSpmm(capi.PROJECTION_TRANSPOSE, rows, cols, n, x.nnz, 8, 1, g.dtype, cuda_device, deterministic=True,
+                              device_matrix=x)
+        assert op.schedule == expected
+        first = op.run(x, g, torch.empty(cols, n, device=cuda_device))
+        assert op.status() == 0
+        for _ in range(4):
+            assert torch.equal(op.run(x, g, torch.empty(cols, n, device=cuda_device)), first)
+        assert_transpose_close(first.cpu().numpy(), ref, cl1, gmax)
+        op.close()
+
+
 @pytest.mark.parametrize("schedule", ["tensor_blocked_x3", "tensor_blocked", "gene_gather", "vector_reductions"])
 def test_transpose_schedules_against_the_oracle_at_scale(cuda_device, oracle, schedule):
     """Genes as in the benchmark configuration, 1/8 of its cells, the schedule prepare chooses for each kind of
@@ -297,4 +325,8 @@ def test_transpose_schedules_against_the_oracle_at_scale(cuda_device, oracle, sc
             assert_transpose_close(got, ref, cl1, gmax)
         worst = np.max(np.abs(got.astype(np.float64) - ref) / (cl1[:, None] * gmax + 1e-30))
         print(f"{schedule} rows [{r0},{r1}): max |d| / (||column||_1 max|G|) = {worst:.3e}")
+    if schedule in ("tensor_blocked_x3", "tensor_blocked", "gene_gather"):      # fixed summation order: repeatable to the bit
+        whole = op.run(x, g, torch.empty(x.cols, n, device=cuda_device))
+        for _ in range(2):
+            assert torch.equal(op.run(x, g, torch.empty(x.cols, n, device=cuda_device)), whole)
     op.close()
