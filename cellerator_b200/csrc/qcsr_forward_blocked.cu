@@ -158,55 +158,66 @@ __global__ void __launch_bounds__(256) blocked_pass_kernel(const std::int64_t *r
     }
 }
 
-// seg_ptr[i] = sum of counts[0..i) rounded up to multiples of 4 (16-byte segments for the copy
-// engine), cursor = seg_ptr.  One block walks the segments in tiles of 4,096 (a thread takes four consecutive
-// segments, consecutive threads consecutive fours) and carries the running total from tile to tile.
-__global__ void __launch_bounds__(1024) segment_scan_kernel(const unsigned *counts, std::int64_t segments, std::int64_t *seg_ptr,
-                                                            unsigned long long *cursor) {
+// seg_ptr[i] = sum of counts[0..i) rounded up to multiples of 4 (16-byte segments for the copy engine), cursor =
+// seg_ptr, in three steps over tiles of kScanTile segments: every block scans its tile and leaves the tile's total;
+// one block scans the totals; every block adds its tile's base.  Consecutive threads take consecutive segments.
+constexpr int kScanTile = 1024;
+__device__ __forceinline__ long long block_exclusive_scan(long long mine, long long *total) {
     __shared__ long long warp_total[32];
-    __shared__ long long carry;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
-    for (std::int64_t tile = 0; tile < segments; tile += 4096) {
-        const std::int64_t first = tile + 4 * static_cast<std::int64_t>(threadIdx.x);
-        long long v[4];
+    long long sum = mine;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = first + j < segments ? static_cast<long long>((counts[first + j] + 3u) & ~3u) : 0;
-        const long long mine = v[0] + v[1] + v[2] + v[3];
-        long long sum = mine; // inclusive scan within the warp
+    for (int d = 1; d < 32; d <<= 1) {
+        const long long up = __shfl_up_sync(0xffffffffu, sum, d);
+        if (lane >= d) sum += up;
+    }
+    if (lane == 31) warp_total[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        const long long t = warp_total[lane];
+        long long run = t;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const long long up = __shfl_up_sync(0xffffffffu, sum, d);
-            if (lane >= d) sum += up;
+            const long long up = __shfl_up_sync(0xffffffffu, run, d);
+            if (lane >= d) run += up;
         }
-        if (lane == 31) warp_total[warp] = sum;
+        warp_total[lane] = run - t;
+    }
+    __syncthreads();
+    const long long before = warp_total[warp] + sum - mine;
+    if (total != nullptr && threadIdx.x == kScanTile - 1) *total = before + mine;
+    __syncthreads(); // the shared array may be used again
+    return before;
+}
+__global__ void __launch_bounds__(kScanTile) segment_tile_scan_kernel(const unsigned *counts, std::int64_t segments, std::int64_t *seg_ptr,
+                                                                      long long *tile_totals) {
+    const std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * kScanTile + threadIdx.x;
+    const long long mine = i < segments ? static_cast<long long>((counts[i] + 3u) & ~3u) : 0;
+    const long long before = block_exclusive_scan(mine, tile_totals + blockIdx.x);
+    if (i < segments) seg_ptr[i] = before;
+}
+__global__ void __launch_bounds__(kScanTile) tile_totals_scan_kernel(long long *tile_totals, std::int64_t tiles, std::int64_t *grand_total) {
+    __shared__ long long carry, step_total;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (std::int64_t base = 0; base < tiles; base += kScanTile) {
+        const std::int64_t t = base + threadIdx.x;
+        const long long mine = t < tiles ? tile_totals[t] : 0;
+        const long long before = block_exclusive_scan(mine, &step_total);
+        if (t < tiles) tile_totals[t] = carry + before;
         __syncthreads();
-        if (warp == 0) { // exclusive scan of the 32 warp totals
-            const long long total = warp_total[lane];
-            long long run = total;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const long long up = __shfl_up_sync(0xffffffffu, run, d);
-                if (lane >= d) run += up;
-            }
-            warp_total[lane] = run - total;
-        }
-        __syncthreads();
-        long long at = carry + warp_total[warp] + sum - mine;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (first + j < segments) {
-                seg_ptr[first + j] = at;
-                cursor[first + j] = static_cast<unsigned long long>(at);
-            }
-            at += v[j];
-        }
-        __syncthreads(); // everyone has read carry and the warp totals
-        if (threadIdx.x == 1023) carry = at;
+        if (threadIdx.x == 0) carry += step_total;
         __syncthreads();
     }
-    if (threadIdx.x == 0) seg_ptr[segments] = carry;
+    if (threadIdx.x == 0) *grand_total = carry;
+}
+__global__ void __launch_bounds__(kScanTile) segment_add_base_kernel(const long long *tile_bases, std::int64_t segments, std::int64_t *seg_ptr,
+                                                                     unsigned long long *cursor) {
+    const std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * kScanTile + threadIdx.x;
+    if (i >= segments) return;
+    const long long at = seg_ptr[i] + tile_bases[blockIdx.x];
+    seg_ptr[i] = at;
+    cursor[i] = static_cast<unsigned long long>(at);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -867,6 +878,7 @@ std::uint64_t qcsr_blocked_layout_bytes_bound(std::int64_t rows, std::int64_t co
     // a segment is padded to a multiple of four words: at most three more per segment
     const std::uint64_t words = static_cast<std::uint64_t>(nnz) + 3u * segments;
     return device_arena::rounded((segments + 2u) * sizeof(unsigned)) + device_arena::rounded(segments * sizeof(unsigned long long)) +
+           device_arena::rounded((segments / 1024u + 2u) * sizeof(long long)) +
            device_arena::rounded((segments + 1u) * sizeof(std::int64_t)) + (bake_lo ? 2u : 1u) * device_arena::rounded(words * 4u);
 }
 
@@ -887,20 +899,23 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     const std::uint64_t count_bytes = static_cast<std::uint64_t>(segments + 2) * sizeof(unsigned);
     const std::uint64_t cursor_bytes = static_cast<std::uint64_t>(segments) * sizeof(unsigned long long);
     const std::uint64_t seg_bytes = static_cast<std::uint64_t>(segments + 1) * sizeof(std::int64_t);
+    const std::uint64_t tile_total_bytes = static_cast<std::uint64_t>((segments + kScanTile - 1) / kScanTile + 1) * sizeof(long long);
     unsigned *counts = static_cast<unsigned *>(arena.take(count_bytes));
     unsigned long long *cursor = static_cast<unsigned long long *>(arena.take(cursor_bytes));
+    long long *tile_totals = static_cast<long long *>(arena.take(tile_total_bytes));
     out->seg_ptr = static_cast<std::int64_t *>(arena.take(seg_bytes));
     std::uint64_t word_bytes = 0;
     const auto give_up = [&](cb200_status st) {
         arena.give_back(out->entries_lo, word_bytes);
         arena.give_back(out->entries, word_bytes);
         arena.give_back(out->seg_ptr, seg_bytes);
+        arena.give_back(tile_totals, tile_total_bytes);
         arena.give_back(cursor, cursor_bytes);
         arena.give_back(counts, count_bytes);
         *out = blocked_layout{};
         return st;
     };
-    if (counts == nullptr || cursor == nullptr || out->seg_ptr == nullptr)
+    if (counts == nullptr || cursor == nullptr || tile_totals == nullptr || out->seg_ptr == nullptr)
         return give_up(fail(CB200_STATUS_INSUFFICIENT_WORKSPACE, "no device memory for the segment table of the window-blocked copy"));
     cudaError_t err = cudaMemsetAsync(counts, 0, count_bytes, stream);
     const unsigned grid = static_cast<unsigned>((x.rows + 7) / 8); // one warp per row, 8 rows per block
@@ -921,8 +936,11 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
         else
             blocked_pass_kernel<4, false><<<grid, 256, 0, stream>>>(x.row_ptr, x.packed_row_ptr, x.col_idx, x.packed, x.rows, x.cols, windows, counts, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0, 0.0f);
         count_launch();
-        segment_scan_kernel<<<1, 1024, 0, stream>>>(counts, segments, out->seg_ptr, cursor);
-        count_launch();
+        const std::int64_t tiles = (segments + kScanTile - 1) / kScanTile;
+        segment_tile_scan_kernel<<<static_cast<unsigned>(tiles), kScanTile, 0, stream>>>(counts, segments, out->seg_ptr, tile_totals);
+        tile_totals_scan_kernel<<<1, kScanTile, 0, stream>>>(tile_totals, tiles, out->seg_ptr + segments);
+        segment_add_base_kernel<<<static_cast<unsigned>(tiles), kScanTile, 0, stream>>>(tile_totals, segments, out->seg_ptr, cursor);
+        count_launch(3);
         err = cudaGetLastError();
     }
     if (err == cudaSuccess) err = cudaMemcpyAsync(&total, out->seg_ptr + segments, sizeof(total), cudaMemcpyDeviceToHost, stream);
@@ -953,6 +971,7 @@ cb200_status build_blocked_layout(const qcsr_view &x, bool bake, bool bake_lo, b
     }
     if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
     if (err != cudaSuccess) return give_up(fail(CB200_STATUS_CUDA_ERROR, "building the window-blocked copy: %s", cudaGetErrorString(err)));
+    arena.give_back(tile_totals, tile_total_bytes);
     arena.give_back(cursor, cursor_bytes);
     arena.give_back(counts, count_bytes);
     out->groups = groups;

@@ -482,16 +482,28 @@ __global__ void __launch_bounds__(256) ordered_sum_kernel(const float *partials,
     const std::int64_t window = set * kSetWindows + wl;
     if (window >= windows) return;
     const std::int64_t sets = (windows + kSetWindows - 1) / kSetWindows, total = sets * group_count;
-    if (threadIdx.x == 0) {
-        int count = 0;
-        std::int64_t first_run = 0;
-        for (std::int64_t b = 0; b < grid; ++b) {
-            const std::int64_t u0 = total * b / grid, u1 = total * (b + 1) / grid;
-            if (u1 > u0 && u0 < (set + 1) * group_count && u1 > set * group_count && count < 512) slots[count++] = first_run + (set - u0 / group_count);
-            first_run += runs_of_cta(total, group_count, grid, b);
+    // thread b looks at CTA b: how many runs it has and whether one of them belongs to this set; two scans over the block
+    // turn that into the global index of each CTA's first run and the place of its slot in the list (CTA order)
+    __shared__ int scan[256];
+    const std::int64_t b = threadIdx.x;
+    const std::int64_t u0 = b < grid ? total * b / grid : 0, u1 = b < grid ? total * (b + 1) / grid : 0;
+    const int runs = b < grid ? static_cast<int>(runs_of_cta(total, group_count, grid, b)) : 0;
+    const int meets = (u1 > u0 && u0 < (set + 1) * group_count && u1 > set * group_count) ? 1 : 0;
+    int before_runs = 0, before_meets = 0; // exclusive sums over the CTAs before b
+    for (int which = 0; which < 2; ++which) {
+        scan[threadIdx.x] = which == 0 ? runs : meets;
+        __syncthreads();
+        for (int d = 1; d < 256; d <<= 1) {
+            const int add = threadIdx.x >= static_cast<unsigned>(d) ? scan[threadIdx.x - d] : 0;
+            __syncthreads();
+            scan[threadIdx.x] += add;
+            __syncthreads();
         }
-        slot_count = count;
+        (which == 0 ? before_runs : before_meets) = scan[threadIdx.x] - (which == 0 ? runs : meets);
+        if (which == 1 && threadIdx.x == 255) slot_count = scan[255];
+        __syncthreads();
     }
+    if (meets) slots[before_meets] = before_runs + (set - u0 / group_count);
     __syncthreads();
     const int count = slot_count;
     for (int i = threadIdx.x; i < kWin * (NC / 4); i += blockDim.x) {
