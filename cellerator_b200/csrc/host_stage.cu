@@ -127,8 +127,7 @@ __attribute__((target("avx2"))) inline void gaps_of_row_avx2(const std::int32_t 
     for (; i + 32 <= len; i += 32) {
         __m256i d[4];
         __m256i over = _mm256_setzero_si256();
-#pragma GCC unroll 4
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 4; ++j) { // (four iterations: the host compiler unrolls them)
             const __m256i a = _mm256_loadu_si256(reinterpret_cast<const __m256i *>(genes + i + 8 * j));
             const __m256i b = _mm256_loadu_si256(reinterpret_cast<const __m256i *>(genes + i + 8 * j - 1));
             d[j] = _mm256_sub_epi32(_mm256_sub_epi32(a, b), one);
