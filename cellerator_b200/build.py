@@ -101,7 +101,7 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
     ref = reference_root()
     candidates = os.path.join(HOST, "b200_candidates.cc")
     if ref is not None and os.path.exists(candidates):
-        # the product's own C++ host layer: operation_candidate records over the C ABI (INTEGRATION.md)
+        # the product's own C++ host layer: operation_candidate records over the C ABI
         path = os.path.join(LIB, "libcb200_candidates.so")
         deps = [candidates] + _headers()
         if force or _newer(path, deps + [out["libcellerator_b200.so"]]):

@@ -432,7 +432,7 @@ ORC_API int orc_spmm_reference(uint64_t m, uint64_t k, uint64_t n, int transpose
 }
 
 /*
- * The composed CPU path that BASELINE times: decode (packing.cuh:279-292) then the referee,
+ * The composed CPU path the benchmark times as the CPU baseline: decode (packing.cuh:279-292) then the referee,
  * forward only, on the row range [row_begin, row_end) of a quantized CSR with int64 row
  * pointers.  Offsets are rebased so the referee sees row_offsets[0] == 0
  * (referee.cc:143-148).  `scratch_values` holds the decoded floats (nnz of the range),
