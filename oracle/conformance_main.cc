@@ -758,6 +758,37 @@ int main(int argc, char **argv) {
             std::printf("  transpose (ordered) max |d| / (||column||_1 max|G|) = %.3e\n", worst_ordered);
             CHECK(worst_ordered <= 1.0e-4, "ordered transpose within the fp32 bound of the reference referee's result");
             host::release_prepared(&po);
+            // the same candidate with the tensor_blocked variant: the tensor-core transpose, whose CTAs' sums are added in a
+            // fixed order, under the same deterministic policy
+            core::projection_key tensor_variant = t.projection;
+            tensor_variant.variant = host::schedule_tensor_blocked;
+            core::prepared_operation pb{};
+            st = core::prepare_candidate(*ord, t.problem, t.structures, tensor_variant, policy_u8(ex::numeric_type::f32), det_pre, &pb);
+            CHECK(static_cast<bool>(st), "prepare_candidate(ordered transpose, tensor_blocked variant, deterministic policy)");
+            if (!st) std::printf("  message: %s\n", st.message);
+            CHECK(std::strcmp(host::prepared_schedule(pb), "tensor_blocked_x3") == 0, "deterministic transpose, tensor_blocked variant -> split-product tensor schedule");
+            ex::launch_bindings l3 = l2;
+            l3.structures = l2.structures;
+            cudaMemset(d_gt, 0xff, first.size() * sizeof(float));
+            st = core::run_prepared_operation(pb, l3);
+            CHECK(static_cast<bool>(st), "run_prepared_operation(ordered transpose, tensor_blocked variant)");
+            if (!st) std::printf("  message: %s (binding %d)\n", st.message, static_cast<int>(st.binding));
+            cudaStreamSynchronize(stream);
+            cudaMemcpy(first.data(), d_gt, first.size() * sizeof(float), cudaMemcpyDeviceToHost);
+            cudaMemset(d_gt, 0xff, first.size() * sizeof(float));
+            st = core::run_prepared_operation(pb, l3);
+            cudaStreamSynchronize(stream);
+            cudaMemcpy(second.data(), d_gt, second.size() * sizeof(float), cudaMemcpyDeviceToHost);
+            CHECK(static_cast<bool>(st) && std::memcmp(first.data(), second.data(), first.size() * sizeof(float)) == 0,
+                  "tensor transpose under the deterministic policy: the second run repeats every bit of the first");
+            double worst_tensor = 0.0;
+            for (std::int64_t gene = 0; gene < K; ++gene)
+                for (std::int64_t c = 0; c < N; ++c)
+                    worst_tensor = std::max(worst_tensor, std::fabs(static_cast<double>(first[gene * N + c]) - ref[gene * N + c]) /
+                                                              (col_l1[gene] * gmax + 1e-30));
+            std::printf("  transpose (ordered candidate, tensor_blocked variant) max |d| / (||column||_1 max|G|) = %.3e\n", worst_tensor);
+            CHECK(worst_tensor <= 1.0e-4, "tensor transpose under the deterministic policy within the fp32 bound");
+            host::release_prepared(&pb);
         }
         host::release_prepared(&pt);
         cudaFree(d_ws2);

@@ -35,6 +35,8 @@ def test_reference_operation_core_drives_the_backend_on_the_gpu():
     for line in ("PASS run_prepared_operation(forward)", "PASS forward result within tolerance of the reference referee",
                  "PASS deterministic candidate: identical digest on a second run",
                  "PASS a launch with another structure epoch is stale", "PASS run_prepared_operation(transpose)",
-                 "PASS transpose result within tolerance of the reference referee"):
+                 "PASS transpose result within tolerance of the reference referee",
+                 "PASS tensor transpose under the deterministic policy: the second run repeats every bit of the first",
+                 "PASS tensor transpose under the deterministic policy within the fp32 bound"):
         assert line in proc.stdout, line
     assert "FAIL" not in proc.stdout
