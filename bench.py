@@ -748,7 +748,9 @@ def run_ours(args):
                                       "at launch, in registers: the timed kernel streams dense tiles of codes (a byte per slot) that "
                                       "prepare laid out; scales and offsets are read at every launch"
                                       if schedule == "tensor_codes" else "at launch: codes, scales and offsets are read by the timed kernel"),
-                   "prepare_ms_once": main["prepare_ms_once"], "persistent_bytes": main["persistent_bytes"]},
+                   "prepare_ms_once": main["prepare_ms_once"], "persistent_bytes": main["persistent_bytes"],
+                   "summation_order": ("atomic (order of arrival at L2)" if schedule in ("vector_reductions",) else
+                                       "fixed: the same bits on every launch")},
         "step_ms": main["step_ms"], "value_at_median": main["value_at_median"],
         "gpu_launches": main["gpu_launches"],
         "clocks": clocks,
