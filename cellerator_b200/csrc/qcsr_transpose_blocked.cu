@@ -129,14 +129,29 @@ __global__ void __launch_bounds__(256) pack_g_kernel(const float *g, std::int64_
                                                      std::int64_t row_end, std::int64_t group_begin, int part,
                                                      unsigned char *records) {
     const std::int64_t group = group_begin + blockIdx.x;
-    __nv_bfloat16 *rec = reinterpret_cast<__nv_bfloat16 *>(records + static_cast<std::size_t>(blockIdx.x) * g_record_bytes(n));
-    for (int i = threadIdx.x; i < kRows * n; i += blockDim.x) {
-        const int r = i / n, c = i % n; // consecutive threads read consecutive columns of one cell
-        const std::int64_t row = group * kRows + r;
-        const float v = (row >= row_begin && row < row_end) ? g[row * ld + c] : 0.0f;
-        __nv_bfloat16 b = __float2bfloat16_rn(v);
-        if (part != 0) b = __float2bfloat16_rn(v - __bfloat162float(b));
-        rec[((c >> 3) * (kRows * 16) + (r >> 3) * 128 + (c & 7) * 16 + (r & 7) * 2) >> 1] = b;
+    unsigned char *rec = records + static_cast<std::size_t>(blockIdx.x) * g_record_bytes(n);
+    // A thread makes one 16-byte piece: a column's values of eight consecutive cells.  Consecutive threads take consecutive
+    // columns of the same eight cells: their loads of a cell's row are contiguous, and their pieces are too (8 columns =
+    // 128 bytes of the record).
+    for (int item = threadIdx.x; item < n * (kRows / 8); item += blockDim.x) {
+        const int c = item % n, r8 = item / n;
+        std::uint32_t packed[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            float v[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const std::int64_t row = group * kRows + r8 * 8 + j + k;
+                v[k] = (row >= row_begin && row < row_end) ? g[row * ld + c] : 0.0f;
+            }
+            __nv_bfloat16 b0 = __float2bfloat16_rn(v[0]), b1 = __float2bfloat16_rn(v[1]);
+            if (part != 0) {
+                b0 = __float2bfloat16_rn(v[0] - __bfloat162float(b0));
+                b1 = __float2bfloat16_rn(v[1] - __bfloat162float(b1));
+            }
+            packed[j >> 1] = static_cast<std::uint32_t>(__bfloat16_as_ushort(b0)) | (static_cast<std::uint32_t>(__bfloat16_as_ushort(b1)) << 16);
+        }
+        *reinterpret_cast<uint4 *>(rec + (c >> 3) * (kRows * 16) + r8 * 128 + (c & 7) * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
 }
 
