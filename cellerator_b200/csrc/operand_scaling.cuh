@@ -28,6 +28,25 @@ template<typename WT>
 __device__ __forceinline__ void absmax_body(const WT *w, std::int64_t ld, std::int64_t rows, int n, unsigned *out_bits, unsigned block, unsigned blocks) {
     float m = 0.0f;
     const std::int64_t total = rows * n;
+    // a contiguous, 16-byte aligned operand is read 16 bytes at a time (the usual case: a launch of the 8,192 x 256
+    // Blocked-ELL configuration spent 12.6 us here reading element by element, with a 64-bit division each)
+    if (ld == n && (reinterpret_cast<std::uintptr_t>(w) & 15u) == 0u && total % (16 / static_cast<std::int64_t>(sizeof(WT))) == 0) {
+        const std::int64_t vectors = total / (16 / static_cast<std::int64_t>(sizeof(WT)));
+        const uint4 *v4 = reinterpret_cast<const uint4 *>(w);
+        for (std::int64_t i = static_cast<std::int64_t>(block) * blockDim.x + threadIdx.x; i < vectors; i += static_cast<std::int64_t>(blocks) * blockDim.x) {
+            const uint4 q = __ldg(v4 + i);
+            const std::uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if constexpr (sizeof(WT) == 2) { // two bf16: their magnitudes are the words' halves without the sign bits, shifted up
+                    m = fmaxf(m, __uint_as_float((words[k] & 0x7fffu) << 16));
+                    m = fmaxf(m, __uint_as_float(words[k] & 0x7fff0000u));
+                } else {
+                    m = fmaxf(m, fabsf(__uint_as_float(words[k])));
+                }
+            }
+        }
+    } else
     for (std::int64_t i = static_cast<std::int64_t>(block) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<std::int64_t>(blocks) * blockDim.x) {
         const std::int64_t r = i / n;

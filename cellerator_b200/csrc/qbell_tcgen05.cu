@@ -135,11 +135,24 @@ __global__ void __launch_bounds__(256) pack_w_kernel(const __nv_bfloat16 *w, std
     const std::int64_t block = blockIdx.x;                     // gene block
     const float ws = operand_scale(__uint_as_float(*w_absmax));
     __half *dst = packed_wt + block * static_cast<std::int64_t>(n) * 32;
-    for (int i = threadIdx.x; i < n * 32; i += blockDim.x) {
-        const int e = i / n, m = i % n;                        // consecutive threads read consecutive columns of one gene
-        const std::int64_t gene = block * 32 + e;
-        const float v = gene < cols ? __bfloat162float(w[gene * ld + m]) : 0.0f;
-        dst[((m >> 3) * 512 + (e >> 3) * 128 + (m & 7) * 16 + (e & 7) * 2) >> 1] = __float2half_rn(v * ws);
+    // a thread makes one 16-byte piece: a column's values of eight consecutive genes; consecutive threads take consecutive
+    // columns, so that their loads of a gene's row and their pieces are contiguous
+    for (int item = threadIdx.x; item < n * 4; item += blockDim.x) {
+        const int m = item % n, e8 = item / n;
+        std::uint32_t packed[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            float v[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const std::int64_t gene = block * 32 + e8 * 8 + j + k;
+                v[k] = gene < cols ? __bfloat162float(w[gene * ld + m]) : 0.0f;
+            }
+            const __half2 h = __floats2half2_rn(v[0] * ws, v[1] * ws);
+            packed[j >> 1] = *reinterpret_cast<const std::uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(dst) + (m >> 3) * 512 + e8 * 128 + (m & 7) * 16) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     if (threadIdx.x < 16) {
         const float vs = operand_scale(__uint_as_float(value_bound[0]) + __uint_as_float(value_bound[1]));

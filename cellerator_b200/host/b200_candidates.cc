@@ -521,7 +521,7 @@ const char *schedule_name(std::uint32_t variant) noexcept {
     case schedule_tensor_codes: fraction = 0.570; break;
     case schedule_vector_reductions: fraction = 0.013; break;
     case schedule_gene_gather: fraction = 0.047; break;
-    case schedule_tcgen05_block_rows: fraction = 0.245; break;
+    case schedule_tcgen05_block_rows: fraction = 0.267; break;
     case schedule_cuda_cores: fraction = 0.013; break;
     default: break;
     }
