@@ -114,11 +114,24 @@ __global__ void __launch_bounds__(256) pack_codes_operands_kernel(const __nv_bfl
     __half *rec = reinterpret_cast<__half *>(records + window * record_bytes(n));
     const float ws = operand_scale(__uint_as_float(*w_absmax));
     const int group_cols = n / static_cast<int>(gridDim.y), c_first = static_cast<int>(blockIdx.y) * group_cols;
-    for (int i = threadIdx.x; i < group_cols * kWin; i += blockDim.x) {
-        const int e = i / group_cols, c = c_first + i % group_cols; // consecutive threads read consecutive columns of one gene
-        const std::int64_t gene = window * kWin + e;
-        const float value = gene < cols ? __bfloat162float(w[gene * ld + c]) : 0.0f;
-        rec[((c >> 3) * kRowGroupBytes + (e >> 3) * 128 + (c & 7) * 16 + (e & 7) * 2) >> 1] = __float2half_rn(value * ws);
+    // a thread makes one 16-byte piece: a column's values of eight consecutive genes; consecutive threads take consecutive
+    // columns, so that their loads of a gene's row and their pieces are contiguous
+    for (int item = threadIdx.x; item < group_cols * (kWin / 8); item += blockDim.x) {
+        const int e8 = item / group_cols, c = c_first + item % group_cols;
+        std::uint32_t packed[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            float v[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const std::int64_t gene = window * kWin + e8 * 8 + j + k;
+                v[k] = gene < cols ? __bfloat162float(w[gene * ld + c]) : 0.0f;
+            }
+            const __half2 h = __floats2half2_rn(v[0] * ws, v[1] * ws);
+            packed[j >> 1] = *reinterpret_cast<const std::uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(rec) + (c >> 3) * kRowGroupBytes + e8 * 128 + (c & 7) * 16) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     if (blockIdx.y != 0 || threadIdx.x >= kWin / 2) return; // warps 0 and 1: the pairs of the window's first and second half
     const std::int64_t pair = window * (kWin / 2) + threadIdx.x;
